@@ -1,0 +1,254 @@
+"""Each CUDA kernel alone against its plain PyTorch statement, at sizes other than the
+models' (odd widths, head sizes that are no power of two, ragged batches)."""
+import math
+
+import pytest
+import torch
+
+from tinyllama_c_b200 import ops
+from plain import ops_plain
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# output tolerance relative to the output's largest magnitude: float32 accumulation order /
+# one bfloat16 rounding of the stored result
+TOL = {torch.float32: 2e-5, torch.bfloat16: 6e-3}
+
+
+def gen(seed):
+    g = torch.Generator()
+    g.manual_seed(seed)
+    return g
+
+
+def rnd(g, *shape, dtype=torch.float32, scale=1.0):
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def cmp(name, args_cpu, outs, tol_of=None):
+    """Calls ops.<name> on CUDA copies and ops_plain.<name> on the CPU tensors; compares the
+    tensors at positions `outs`."""
+    args_gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args_cpu]
+    getattr(ops, name)(*args_gpu)
+    torch.cuda.synchronize()
+    getattr(ops_plain, name)(*args_cpu)
+    for i in outs:
+        ref, got = args_cpu[i].double(), args_gpu[i].cpu().double()
+        tol = (tol_of or TOL[args_cpu[i].dtype]) * max(1e-6, ref.abs().max().item())
+        err = (ref - got).abs().max().item()
+        assert err <= tol, f"{name}: output {i} differs by {err:.3e} (allowed {tol:.3e})"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    g = gen(0)
+    table = rnd(g, 301, 72, dtype=DT[dtype])
+    tokens = torch.randint(0, 301, (19,), generator=g, dtype=torch.int32)
+    cmp("embed", [tokens, table, 2.5, torch.empty(19, 72)], [3])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("D", [72, 1000, 2049])
+def test_rmsnorm(dtype, D):
+    g = gen(1)
+    x = rnd(g, 7, D, scale=3.0)
+    w = 1 + rnd(g, D, scale=0.2)
+    cmp("rmsnorm", [x, w, 1e-5, torch.empty(7, D, dtype=DT[dtype]), None], [3])
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    cmp("rmsnorm", [x, w, 1e-6, torch.empty(3, D, dtype=DT[dtype]), rows], [3])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("groups,before,with_w", [(1, False, True), (3, True, True), (2, False, False)])
+def test_gated_rmsnorm(dtype, groups, before, with_w):
+    g = gen(2)
+    T, Di = 5, 6 * 26
+    y = rnd(g, T, Di, scale=2.0)
+    proj = rnd(g, T, Di + 11, dtype=DT[dtype])
+    z = proj[:, 4:4 + Di]
+    w = 1 + rnd(g, Di, scale=0.2) if with_w else None
+    args = [y, z, w, 1e-5, groups, before, torch.empty(T, Di, dtype=DT[dtype])]
+    gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args]
+    gpu[1] = proj.cuda()[:, 4:4 + Di]
+    ops.gated_rmsnorm(*gpu)
+    ops_plain.gated_rmsnorm(*args)
+    ref, got = args[6].double(), gpu[6].cpu().double()
+    assert (ref - got).abs().max() <= TOL[DT[dtype]] * ref.abs().max() * 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(dtype):
+    g = gen(3)
+    gu = rnd(g, 9, 2 * 77, dtype=DT[dtype], scale=2.0)
+    cmp("swiglu", [gu, torch.empty(9, 77, dtype=DT[dtype])], [1])
+
+
+@pytest.mark.parametrize("a_dt,w_dt,o_dt", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),
+                                            ("bfloat16", "bfloat16", "float32"), ("bfloat16", "float32", "bfloat16")])
+@pytest.mark.parametrize("M,N,K", [(1, 130, 72), (5, 67, 200), (16, 64, 64), (17, 129, 100), (150, 70, 257),
+                                   (8, 96, 1024)])
+def test_linear(a_dt, w_dt, o_dt, M, N, K):
+    g = gen(4)
+    a_full = rnd(g, M, K + 8, dtype=DT[a_dt])
+    w = rnd(g, N, K, dtype=DT[w_dt], scale=1 / math.sqrt(K))
+    cs, cb = 1 + rnd(g, N, scale=0.3), rnd(g, N)
+    for accumulate in (False, True):
+        for scale, bias in ((None, None), (cs, cb)):
+            out_cpu = rnd(g, M, N + 3, dtype=DT[o_dt])
+            out_gpu = out_cpu.cuda()
+            a_gpu = a_full.cuda()
+            ops.linear(a_gpu[:, :K], w.cuda(), out_gpu[:, :N], None if scale is None else scale.cuda(),
+                       None if bias is None else bias.cuda(), accumulate)
+            untouched = out_cpu[:, N:].clone()
+            ops_plain.linear(a_full[:, :K], w, out_cpu[:, :N], scale, bias, accumulate)
+            ref, got = out_cpu[:, :N].double(), out_gpu.cpu()[:, :N].double()
+            tol = TOL[DT[o_dt]] * ref.abs().max().item() * (2 if a_dt == "float32" else 1)
+            assert (ref - got).abs().max().item() <= tol
+            assert torch.equal(out_gpu.cpu()[:, N:], untouched), "linear wrote outside its columns"
+
+
+def _paged_setup(g, B, lens_total, KV, hd, dtype, n_slots=5, extra_pages=3):
+    """Random slots and shuffled pages for sequences of the given total lengths."""
+    pages_needed = [(n + 63) // 64 for n in lens_total]
+    n_pages = sum(pages_needed) + extra_pages
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    max_pages = max(pages_needed) + 1
+    table = torch.full((n_slots, max_pages), 0, dtype=torch.int32)
+    slots = torch.randperm(n_slots, generator=g)[:B].to(torch.int32)
+    for b in range(B):
+        for i in range(pages_needed[b]):
+            table[int(slots[b]), i] = perm.pop()
+    k_pages = rnd(g, n_pages, KV, 64, hd, dtype=dtype)
+    v_pages = rnd(g, n_pages, KV, 64, hd, dtype=dtype)
+    return slots, table, k_pages, v_pages
+
+
+def _step_arrays(starts, lens):
+    pos, row_seq, cu = [], [], [0]
+    for b, (s, n) in enumerate(zip(starts, lens)):
+        pos += list(range(s, s + n))
+        row_seq += [b] * n
+        cu.append(cu[-1] + n)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)
+    return i32(pos), i32(row_seq), i32(cu), i32(starts)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,hd,rope", [(6, 3, 24, 24), (4, 1, 48, 32), (8, 2, 128, 128), (5, 5, 16, 0)])
+def test_rope_kv_store(dtype, H, KV, hd, rope):
+    g = gen(5)
+    starts, lens = [0, 70, 130], [5, 3, 66]
+    pos, row_seq, cu, _ = _step_arrays(starts, lens)
+    slots, table, k_pages, v_pages = _paged_setup(g, 3, [s + n for s, n in zip(starts, lens)], KV, hd, DT[dtype])
+    T = sum(lens)
+    width = (H + 2 * KV) * hd
+    qkv = rnd(g, T, width + 5, dtype=DT[dtype])
+    inv = (1.0 / torch.pow(torch.tensor(1e6, dtype=torch.float64),
+                           torch.arange(rope // 2, dtype=torch.float64) * 2 / max(rope, 1))).float()
+    args = [qkv[:, 2:2 + width], 0, H * hd, (H + KV) * hd, torch.empty(T, H * hd, dtype=DT[dtype]), k_pages, v_pages,
+            inv, pos, row_seq, slots, table, H, KV, hd, True]
+    gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args]
+    gpu[0] = qkv.cuda()[:, 2:2 + width]
+    ops.rope_kv_store(*gpu)
+    ops_plain.rope_kv_store(*args)
+    for i in (4, 5, 6):
+        ref, got = args[i].double(), gpu[i].cpu().double()
+        assert (ref - got).abs().max() <= TOL[DT[dtype]] * ref.abs().max() * 2, f"output {i}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,hd,window", [(6, 3, 24, 0), (4, 1, 48, 0), (8, 2, 128, 0), (6, 2, 16, 37), (4, 4, 80, 70)])
+def test_attention(dtype, H, KV, hd, window):
+    g = gen(6)
+    starts, lens = [0, 200, 63, 5], [70, 1, 2, 1]
+    pos, row_seq, cu, _ = _step_arrays(starts, lens)
+    slots, table, k_pages, v_pages = _paged_setup(g, 4, [s + n for s, n in zip(starts, lens)], KV, hd, DT[dtype])
+    T = sum(lens)
+    q = rnd(g, T, H * hd, dtype=DT[dtype])
+    # one far key stands out for the single-token query of the 201-position sequence
+    b1_page = int(table[int(slots[1]), 0])
+    k_pages[b1_page, :, 3, :] *= 6.0
+    cmp("attention", [q, k_pages, v_pages, table, pos, row_seq, slots, torch.empty(T, H * hd, dtype=DT[dtype]), H, KV,
+                      hd, 1.0 / math.sqrt(hd), window], [7], tol_of=TOL[DT[dtype]] * 2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("Di,G,N,K,Hs,bias", [(48, 1, 16, 4, 3, True), (144, 2, 32, 3, 6, False), (40, 1, 8, 2, 5, True)])
+def test_mamba_conv(dtype, Di, G, N, K, Hs, bias):
+    g = gen(7)
+    Cd = Di + 2 * G * N
+    Pd = Di + Cd + Hs
+    starts, lens = [0, 9, 0, 31], [7, 1, 2, 5]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    slots = torch.tensor([4, 0, 2, 1], dtype=torch.int32)
+    T = sum(lens)
+    proj = rnd(g, T, Pd, dtype=DT[dtype])
+    state = rnd(g, 5, K - 1, Cd)
+    args = [proj, Di, Di + Cd, rnd(g, Cd, K, scale=0.5), rnd(g, Cd) if bias else None, rnd(g, Hs),
+            -torch.rand(Hs, generator=g) * 8, state, cu, row_seq, slots, start_pos, torch.empty(T, Cd),
+            torch.empty(T, Hs), torch.empty(T, Hs)]
+    cmp("mamba_conv", args, [7, 12, 13, 14], tol_of=2e-5)
+
+
+@pytest.mark.parametrize("Hs,P,N,G", [(3, 16, 16, 1), (6, 24, 32, 2), (4, 64, 256, 1), (2, 20, 100, 2), (5, 7, 40, 1)])
+def test_ssm_scan(Hs, P, N, G):
+    g = gen(8)
+    Di, Cd = Hs * P, Hs * P + 2 * G * N
+    starts, lens = [0, 9, 0], [19, 1, 3]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32)
+    T = sum(lens)
+    dt = torch.rand(T, Hs, generator=g) * 0.1
+    dA = torch.exp(-dt * torch.rand(Hs, generator=g) * 8)
+    args = [rnd(g, T, Cd), dt, dA, 1 + rnd(g, Hs, scale=0.1), rnd(g, 4, Hs, P, N), cu, slots, start_pos,
+            torch.empty(T, Di), Hs, P, N, G]
+    cmp("ssm_scan", args, [4, 8], tol_of=2e-5)
+
+
+def test_argmax_takes_the_first_maximum():
+    g = gen(9)
+    logits = rnd(g, 6, 1000)
+    logits[2, 17] = logits[2, 900] = 50.0
+    logits[4, 999] = 60.0
+    cmp("argmax", [logits, torch.empty(6, dtype=torch.int32)], [1], tol_of=0.0)
+
+
+@pytest.mark.parametrize("params", [
+    dict(temperature=0.8, top_k=40, top_p=0.9, min_p=0.05, rp=1.1, fp=0.0, pp=0.0),
+    dict(temperature=1.3, top_k=0, top_p=0.7, min_p=0.0, rp=1.0, fp=0.2, pp=0.1),
+    dict(temperature=0.5, top_k=5, top_p=1.0, min_p=0.0, rp=1.0, fp=0.0, pp=0.0),
+    dict(temperature=1.0, top_k=0, top_p=1.0, min_p=0.2, rp=1.3, fp=0.0, pp=0.0),
+    dict(temperature=0.0, top_k=40, top_p=0.9, min_p=0.05, rp=1.2, fp=0.0, pp=0.0),
+])
+def test_sample_equals_the_plain_sampler(params):
+    g = gen(10)
+    R, V = 24, 777
+    logits = rnd(g, R, V, scale=2.5)
+    hist = torch.randint(0, V, (R, 20), generator=g, dtype=torch.int32)
+    hist[:, 15:] = -1
+    hist[3, :4] = 5
+    u = torch.rand(R, generator=g)
+    args = [logits, torch.empty(R, V), hist, u, params["temperature"], params["top_k"], params["top_p"],
+            params["min_p"], params["rp"], params["fp"], params["pp"], torch.empty(R, dtype=torch.int32)]
+    gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args]
+    ops.sample(*gpu)
+    ops_plain.sample(*args)
+    got, ref = gpu[11].cpu(), args[11]
+    # a draw that lands within float32 rounding of a boundary of the CDF may pick the neighbour
+    assert (got != ref).sum().item() <= 1, f"{(got != ref).sum().item()} of {R} draws differ: {got} vs {ref}"
+
+
+def test_sample_frequencies_follow_the_filtered_distribution():
+    g = gen(11)
+    V, R = 50, 4000
+    row = rnd(g, 1, V, scale=1.5)
+    logits = row.repeat(R, 1).contiguous()
+    u = torch.rand(R, generator=g)
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops.sample(logits.cuda(), torch.empty(R, V, device="cuda"), None, u.cuda(), 0.9, 8, 0.95, 0.02, 1.0, 0.0, 0.0, out)
+    from plain.falcon_h1_plain import filtered_distribution
+    ids, probs = filtered_distribution(row[0].numpy(), 0.9, 8, 0.95, 0.02)
+    counts = torch.bincount(out.cpu().long(), minlength=V).double() / R
+    assert set(counts.nonzero().flatten().tolist()) <= set(int(i) for i in ids)
+    for i, p in zip(ids, probs):
+        assert abs(counts[int(i)].item() - p) < 4 * math.sqrt(p * (1 - p) / R) + 2e-3

@@ -1,0 +1,153 @@
+// Rotary position encoding with the key/value store, and attention over the paged cache.
+//
+// CodeClaper/tinyllama.c: split-half rotation of the first rope_dim dims of each head,
+// theta_i = 1/base^(2i/r), angle = pos*theta_i (cpu_op.c:637-651); K/V rows written to
+// the cache at their absolute position (cpu_op.c:995-1008); causal grouped-query
+// attention with kv head h/(H/KV), scale 1/sqrt(head_dim), max-subtracted softmax and an
+// optional window of the last w keys (cpu_op.c:1010-1062, 338-349; graph.c:1275).
+//
+// Here the cache is paged: a sequence's position p lives in page
+// block_table[slot][p / 64] at row p % 64; a layer's pages are [page][kv head][64][hd].
+// Scores, softmax statistics and the output accumulator are 32-bit.
+#include "common.cuh"
+
+// ---- rope + store -----------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kv_store_kernel(const T* __restrict__ qkv, int ld, int q_off, int k_off, int v_off,
+                                     T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                     const float* __restrict__ inv_freq, int rope_dim,
+                                     const int* __restrict__ positions, const int* __restrict__ row_seq,
+                                     const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
+                                     int H, int KV, int hd, int write_kv) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rope_dim >> 1;
+  const T* row = qkv + (size_t)t * ld;
+  const int n_heads_total = H + 2 * KV;
+  int page = -1;
+  if (write_kv) page = block_table[(size_t)slots[row_seq[t]] * max_pages + pos / TLC_PAGE];
+  const int prow = pos % TLC_PAGE;
+  for (int idx = threadIdx.x; idx < n_heads_total * hd; idx += blockDim.x) {
+    const int head = idx / hd, d = idx % hd;
+    const T* src;
+    int kind;  // 0 q, 1 k, 2 v
+    int h;
+    if (head < H) { kind = 0; h = head; src = row + q_off + (size_t)h * hd; }
+    else if (head < H + KV) { kind = 1; h = head - H; src = row + k_off + (size_t)h * hd; }
+    else { kind = 2; h = head - H - KV; src = row + v_off + (size_t)h * hd; }
+    if (kind != 0 && !write_kv) continue;
+    float v;
+    if (kind == 2 || d >= rope_dim) {
+      v = to_f32(src[d]);
+    } else {
+      const int i = d < half ? d : d - half;
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      const float a = to_f32(src[i]), b = to_f32(src[i + half]);
+      v = d < half ? a * cs - b * sn : a * sn + b * cs;
+    }
+    if (kind == 0) {
+      q_out[(size_t)t * H * hd + (size_t)h * hd + d] = from_f32<T>(v);
+    } else if (page >= 0) {
+      T* dst = (kind == 1 ? k_pages : v_pages) + (((size_t)page * KV + h) * TLC_PAGE + prow) * hd + d;
+      *dst = from_f32<T>(v);
+    }
+  }
+}
+
+extern "C" int tlc_rope_kv_store(const void* qkv, int dtype, int ld, int q_off, int k_off, int v_off, void* q_out,
+                                 void* k_pages, void* v_pages, const float* inv_freq, int rope_dim,
+                                 const int* positions, const int* row_seq, const int* slots, const int* block_table,
+                                 int max_pages, int T, int H, int KV, int hd, int write_kv, cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(rope_dim % 2 == 0 && rope_dim <= hd, "rope: rotated width %d must be even and at most head_dim %d", rope_dim, hd);
+  TLC_DISPATCH_DTYPE(dtype, TT, rope_kv_store_kernel<TT><<<T, 256, 0, stream>>>(
+      (const TT*)qkv, ld, q_off, k_off, v_off, (TT*)q_out, (TT*)k_pages, (TT*)v_pages, inv_freq, rope_dim, positions,
+      row_seq, slots, block_table, max_pages, H, KV, hd, write_kv));
+  TLC_CHECK_LAUNCH("rope_kv_store");
+  return 0;
+}
+
+// ---- attention, one warp per (query row, head) ----------------------------------------------
+// Streams the keys 32 at a time: lane j scores key k0+j, the warp keeps a running maximum
+// and sum, and every lane owns the output dims lane, lane+32, ...  Any head size up to
+// 32*MAXD, any number of heads and groups.
+#define ATT_MAXD 8
+template <typename T>
+__global__ void __launch_bounds__(128)
+attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                      const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
+                      const int* __restrict__ row_seq, const int* __restrict__ slots, T* __restrict__ out, int H, int KV,
+                      int hd, float scale, int window) {
+  extern __shared__ float qs_all[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int h = blockIdx.y * 4 + warp;
+  if (h >= H) return;
+  float* qs = qs_all + (size_t)warp * hd;
+  const int g = h / (H / KV);
+  const int pos = positions[t];
+  const int* table = block_table + (size_t)slots[row_seq[t]] * max_pages;
+  const T* qr = q + ((size_t)t * H + h) * hd;
+  for (int d = lane; d < hd; d += 32) qs[d] = to_f32(qr[d]) * scale;
+  __syncwarp();
+  const int n_keys = pos + 1;
+  const int start = (window > 0 && n_keys > window) ? n_keys - window : 0;
+  float m = -INFINITY, l = 0.f;
+  float acc[ATT_MAXD];
+#pragma unroll
+  for (int i = 0; i < ATT_MAXD; i++) acc[i] = 0.f;
+  for (int k0 = start; k0 < n_keys; k0 += 32) {
+    const int kp = k0 + lane;
+    float s = -INFINITY;
+    if (kp < n_keys) {
+      const int page = table[kp / TLC_PAGE];
+      const T* kr = k_pages + (((size_t)page * KV + g) * TLC_PAGE + kp % TLC_PAGE) * hd;
+      float dot = 0.f;
+      for (int d = 0; d < hd; d++) dot = fmaf(to_f32(kr[d]), qs[d], dot);
+      s = dot;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float p = kp < n_keys ? expf(s - m_new) : 0.f;
+    const float corr = expf(m - m_new);      // exp(-inf) = 0 on the first chunk
+    l = l * corr + warp_sum(p);
+#pragma unroll
+    for (int i = 0; i < ATT_MAXD; i++) acc[i] *= corr;
+    const int nk = min(32, n_keys - k0);
+    for (int j = 0; j < nk; j++) {
+      const float pj = __shfl_sync(0xffffffffu, p, j);
+      const int kj = k0 + j;
+      const int page = table[kj / TLC_PAGE];
+      const T* vr = v_pages + (((size_t)page * KV + g) * TLC_PAGE + kj % TLC_PAGE) * hd;
+#pragma unroll
+      for (int i = 0; i < ATT_MAXD; i++) {
+        const int d = lane + 32 * i;
+        if (d < hd) acc[i] = fmaf(pj, to_f32(vr[d]), acc[i]);
+      }
+    }
+    m = m_new;
+  }
+  const float inv = 1.0f / l;
+  T* o = out + ((size_t)t * H + h) * hd;
+#pragma unroll
+  for (int i = 0; i < ATT_MAXD; i++) {
+    const int d = lane + 32 * i;
+    if (d < hd) o[d] = from_f32<T>(acc[i] * inv);
+  }
+}
+
+extern "C" int tlc_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
+                             const int* block_table, int max_pages, const int* positions, const int* row_seq,
+                             const int* slots, void* out, int T, int H, int KV, int hd, float scale, int window,
+                             cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(KV > 0 && H % KV == 0, "attention: %d heads are not a multiple of %d key/value heads", H, KV);
+  TLC_REQUIRE(hd <= 32 * ATT_MAXD, "attention: head size %d exceeds the kernel's limit of %d", hd, 32 * ATT_MAXD);
+  dim3 grid(T, (H + 3) / 4);
+  const size_t smem = (size_t)4 * hd * sizeof(float);
+  TLC_DISPATCH_DTYPE(dtype, TT, attention_warp_kernel<TT><<<grid, 128, smem, stream>>>(
+      (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, (TT*)out,
+      H, KV, hd, scale, window));
+  TLC_CHECK_LAUNCH("attention");
+  return 0;
+}

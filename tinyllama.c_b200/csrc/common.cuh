@@ -1,0 +1,77 @@
+// Shared device helpers and the host-side error channel of the kernel library.
+//
+// Every exported function returns 0 on success or a negative code after storing a
+// message that tlc_last_error() returns; nothing here exits or traps (the reference
+// prints and exits on any CUDA error, gpu.h:41-50 -- a library must not).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define TLC_F32 0
+#define TLC_BF16 1
+
+#define TLC_PAGE 64   // tokens per page of the paged key/value store
+
+extern "C" const char* tlc_last_error();
+int tlc_fail(int code, const char* fmt, ...);
+
+#define TLC_CHECK_LAUNCH(name)                                                  \
+  do {                                                                          \
+    cudaError_t e__ = cudaGetLastError();                                       \
+    if (e__ != cudaSuccess) return tlc_fail(-2, "%s: %s", name, cudaGetErrorString(e__)); \
+  } while (0)
+
+#define TLC_REQUIRE(cond, ...)                       \
+  do {                                               \
+    if (!(cond)) return tlc_fail(-1, __VA_ARGS__);   \
+  } while (0)
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `red` is a
+// shared array of 33 floats.  The tree is fixed by the block size alone, so a row's
+// result does not depend on what else is in the batch.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+// softplus with the reference's cut-over (cpu_op.c:354-356)
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+// Dispatch a lambda-like macro over the two element types.
+#define TLC_DISPATCH_DTYPE(code, T, ...)                                  \
+  if ((code) == TLC_F32) { using T = float; __VA_ARGS__; }                \
+  else if ((code) == TLC_BF16) { using T = __nv_bfloat16; __VA_ARGS__; }  \
+  else return tlc_fail(-1, "unknown dtype code %d", (int)(code));

@@ -1,0 +1,138 @@
+// Embedding gather, RMSNorm, gated grouped RMSNorm and the SwiGLU product.
+//
+// Math follows CodeClaper/tinyllama.c's CPU ops: embedding row gather (cpu_op.c:508-524),
+// RMSNorm ss=sum x^2, s=1/sqrt(ss/n+eps), o=x*s*w (cpu_op.c:44-64), SiLU x/(1+exp(-x))
+// (cpu_op.c:332-335), the Mamba2 gate and grouped norm (cpu_op.c:950-958).  All
+// statistics are 32-bit; only the stored result takes the activation type.
+#include "common.cuh"
+#include <stdarg.h>
+
+static thread_local char g_err[512];
+extern "C" const char* tlc_last_error() { return g_err; }
+int tlc_fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+// ---- embedding ---------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, int D, int V,
+                             float scale, float* __restrict__ out) {
+  const int t = blockIdx.x;
+  int tok = tokens[t];
+  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);   // ids are validated on the host; never read out of bounds
+  const TW* row = table + (size_t)tok * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) out[(size_t)t * D + d] = to_f32(row[d]) * scale;
+}
+
+extern "C" int tlc_embed(const int* tokens, const void* table, int table_dtype, int T, int D, int V, float scale,
+                         float* out, cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_DISPATCH_DTYPE(table_dtype, TW,
+                     embed_kernel<TW><<<T, 256, 0, stream>>>(tokens, (const TW*)table, D, V, scale, out));
+  TLC_CHECK_LAUNCH("embed");
+  return 0;
+}
+
+// ---- RMSNorm of 32-bit rows ----------------------------------------------------------
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                               float eps, int D, TO* __restrict__ out) {
+  __shared__ float red[33];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) { float v = xr[d]; ss += v * v; }
+  ss = block_sum(ss, red);
+  const float s = 1.0f / sqrtf(ss / (float)D + eps);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) out[(size_t)r * D + d] = from_f32<TO>(xr[d] * s * w[d]);
+}
+
+extern "C" int tlc_rmsnorm(const float* x, const int* rows, const float* w, float eps, int R, int D, void* out,
+                           int out_dtype, cudaStream_t stream) {
+  if (R == 0) return 0;
+  TLC_DISPATCH_DTYPE(out_dtype, TO, rmsnorm_kernel<TO><<<R, 256, 0, stream>>>(x, rows, w, eps, D, (TO*)out));
+  TLC_CHECK_LAUNCH("rmsnorm");
+  return 0;
+}
+
+// ---- gate and grouped RMSNorm of the scan output ---------------------------------------
+// y [T, Di] 32-bit; z a strided slice of the input projection; one block per (row, group).
+template <typename TZ, typename TO>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int ldz,
+                                     const float* __restrict__ w, float eps, int Di, int gs, int norm_before_gate,
+                                     TO* __restrict__ out) {
+  __shared__ float red[33];
+  const int t = blockIdx.x, g = blockIdx.y;
+  const float* yr = y + (size_t)t * Di + (size_t)g * gs;
+  const TZ* zr = z + (size_t)t * ldz + (size_t)g * gs;
+  TO* o = out + (size_t)t * Di + (size_t)g * gs;
+  if (w == nullptr) {                                   // no norm: y * silu(z)
+    for (int d = threadIdx.x; d < gs; d += blockDim.x) o[d] = from_f32<TO>(yr[d] * silu_f(to_f32(zr[d])));
+    return;
+  }
+  const float* wg = w + (size_t)g * gs;
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < gs; d += blockDim.x) {
+    float v = yr[d];
+    if (!norm_before_gate) v *= silu_f(to_f32(zr[d]));
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float s = 1.0f / sqrtf(ss / (float)gs + eps);
+  for (int d = threadIdx.x; d < gs; d += blockDim.x) {
+    const float gate = silu_f(to_f32(zr[d]));
+    float v = yr[d];
+    v = norm_before_gate ? (v * s * wg[d]) * gate : (v * gate) * s * wg[d];
+    o[d] = from_f32<TO>(v);
+  }
+}
+
+extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int ldz, const float* w, float eps, int T,
+                                 int Di, int n_groups, int norm_before_gate, void* out, int out_dtype,
+                                 cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(n_groups > 0 && Di % n_groups == 0, "gated_rmsnorm: width %d is not a multiple of %d groups", Di, n_groups);
+  const int gs = Di / n_groups;
+  dim3 grid(T, n_groups);
+  TLC_DISPATCH_DTYPE(z_dtype, TZ, TLC_DISPATCH_DTYPE(out_dtype, TO, gated_rmsnorm_kernel<TZ, TO><<<grid, 256, 0, stream>>>(
+      y, (const TZ*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out)));
+  TLC_CHECK_LAUNCH("gated_rmsnorm");
+  return 0;
+}
+
+// ---- SwiGLU product: out = silu(gate) * up, gate|up side by side in one row ---------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t t = i / F;
+  const int f = (int)(i % F);
+  const float g = to_f32(gu[t * ld + f]), u = to_f32(gu[t * ld + F + f]);
+  out[i] = from_f32<T>(silu_f(g) * u);
+}
+
+extern "C" int tlc_swiglu(const void* gu, int dtype, int ld, int F, int T, void* out, cudaStream_t stream) {
+  const size_t total = (size_t)T * F;
+  if (total == 0) return 0;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  TLC_DISPATCH_DTYPE(dtype, TT, swiglu_kernel<TT><<<blocks, 256, 0, stream>>>((const TT*)gu, ld, F, (TT*)out, total));
+  TLC_CHECK_LAUNCH("swiglu");
+  return 0;
+}
+
+// ---- gather rows of a 32-bit matrix ------------------------------------------------------
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, int D,
+                                   float* __restrict__ out) {
+  const float* xr = x + (size_t)rows[blockIdx.x] * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) out[(size_t)blockIdx.x * D + d] = xr[d];
+}
+extern "C" int tlc_gather_rows(const float* x, const int* rows, int R, int D, float* out, cudaStream_t stream) {
+  if (R == 0) return 0;
+  gather_rows_kernel<<<R, 256, 0, stream>>>(x, rows, D, out);
+  TLC_CHECK_LAUNCH("gather_rows");
+  return 0;
+}

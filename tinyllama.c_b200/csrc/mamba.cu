@@ -1,0 +1,210 @@
+// Mamba2 mixer kernels: causal depthwise convolution with its per-sequence window,
+// the time-step transform, and the selective state scan with its per-sequence state.
+//
+// CodeClaper/tinyllama.c states the math on the CPU only: convolution over the last K
+// raw samples, tap K-1 on the newest, bias, SiLU, then the window shifts and stores the
+// raw sample (cpu_op.c:836-889); dt = softplus(dt + bias), dA = exp(dt*A),
+// S = S*dA + B*(x*dt), y = sum_n S*C + x*D (cpu_op.c:924-951).  Here a step carries
+// several sequences of unequal length packed back to back; a sequence that starts at
+// position 0 starts from a zero window and a zero state, any other continues from its
+// slot.  Convolution, dt, the decay and the state are 32-bit.
+#include "common.cuh"
+
+#define CONV_MAX_TAPS 16
+
+// ---- convolution + SiLU over packed rows, and softplus / decay of dt ---------------------
+// grid (T, ceil(Cd/256)); also writes dt and dA for the row (first blocks of a row).
+template <typename T>
+__global__ void mamba_conv_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_off,
+                                  const float* __restrict__ w, const float* __restrict__ bias,
+                                  const float* __restrict__ dt_bias, const float* __restrict__ A,
+                                  const float* __restrict__ conv_state, const int* __restrict__ cu_seqlens,
+                                  const int* __restrict__ row_seq, const int* __restrict__ slots,
+                                  const int* __restrict__ start_pos, float* __restrict__ xbc_out,
+                                  float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs) {
+  const int t = blockIdx.x;
+  const int b = row_seq[t];
+  const int i = t - cu_seqlens[b];                  // index of this row inside its sequence's new tokens
+  const bool has_state = start_pos[b] > 0;
+  const float* st = conv_state + (size_t)slots[b] * (K - 1) * Cd;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c < Cd) {
+    float sum = 0.f;
+    for (int k = 0; k < K; k++) {
+      const int j = i - (K - 1 - k);                // new-token index that tap k reads
+      float x;
+      if (j >= 0) x = to_f32(proj[(size_t)(t - (K - 1 - k)) * ld + xbc_off + c]);
+      else x = has_state ? st[(size_t)(K - 1 + j) * Cd + c] : 0.f;
+      sum = fmaf(x, w[(size_t)c * K + k], sum);
+    }
+    if (bias) sum += bias[c];
+    xbc_out[(size_t)t * Cd + c] = silu_f(sum);
+  }
+  if (c < Hs) {
+    const float dtv = softplus_f(to_f32(proj[(size_t)t * ld + dt_off + c]) + dt_bias[c]);
+    dt_out[(size_t)t * Hs + c] = dtv;
+    dA_out[(size_t)t * Hs + c] = expf(dtv * A[c]);
+  }
+}
+
+// New window of each sequence: its last K-1 raw samples (old window rows where the step
+// brought fewer).  One thread owns one (sequence, channel), reads all it needs, then writes.
+template <typename T>
+__global__ void mamba_conv_state_kernel(const T* __restrict__ proj, int ld, int xbc_off, float* __restrict__ conv_state,
+                                        const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                                        const int* __restrict__ start_pos, int Cd, int K) {
+  const int b = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= Cd) return;
+  const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
+  if (n == 0) return;
+  const bool has_state = start_pos[b] > 0;
+  float* st = conv_state + (size_t)slots[b] * (K - 1) * Cd;
+  float v[CONV_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; j++) {
+    if (j < K - 1) {
+      const int idx = n - (K - 1) + j;              // new-token index that lands in window row j
+      if (idx >= 0) v[j] = to_f32(proj[(size_t)(t0 + idx) * ld + xbc_off + c]);
+      else v[j] = has_state ? st[(size_t)(K - 1 + idx) * Cd + c] : 0.f;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; j++)
+    if (j < K - 1) st[(size_t)j * Cd + c] = v[j];
+}
+
+extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, int dt_off, const float* w,
+                              const float* bias, const float* dt_bias, const float* A, float* conv_state,
+                              const int* cu_seqlens, const int* row_seq, const int* slots, const int* start_pos,
+                              float* xbc_out, float* dt_out, float* dA_out, int T, int B, int Cd, int K, int Hs,
+                              cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(K >= 1 && K - 1 <= CONV_MAX_TAPS, "mamba_conv: %d taps exceed the kernel's limit of %d", K, CONV_MAX_TAPS + 1);
+  TLC_REQUIRE(Hs <= Cd, "mamba_conv: more heads (%d) than conv channels (%d)", Hs, Cd);
+  dim3 grid(T, (Cd + 255) / 256);
+  dim3 grid2(B, (Cd + 255) / 256);
+  TLC_DISPATCH_DTYPE(dtype, TT, {
+    mamba_conv_kernel<TT><<<grid, 256, 0, stream>>>((const TT*)proj, ld, xbc_off, dt_off, w, bias, dt_bias, A,
+                                                    conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out,
+                                                    dA_out, Cd, K, Hs);
+    if (K > 1)
+      mamba_conv_state_kernel<TT><<<grid2, 256, 0, stream>>>((const TT*)proj, ld, xbc_off, conv_state, cu_seqlens, slots,
+                                                             start_pos, Cd, K);
+  });
+  TLC_CHECK_LAUNCH("mamba_conv");
+  return 0;
+}
+
+// ---- selective scan ---------------------------------------------------------------------------
+// grid (B, Hs, ceil(P / (4*RP))), 128 threads: each warp owns RP rows p of one head's state
+// [P, N], each lane the columns lane, lane+32, ... (NPL of them) in registers.  Tokens of the
+// sequence run in order; the inputs of TT tokens are staged in shared memory at a time.
+#define SCAN_TT 8
+template <int NPL, int RP>
+__global__ void __launch_bounds__(128)
+ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ dA,
+                const float* __restrict__ Dskip, float* __restrict__ state, const int* __restrict__ cu_seqlens,
+                const int* __restrict__ slots, const int* __restrict__ start_pos, float* __restrict__ y, int Hs, int P,
+                int N, int G, int Cd) {
+  extern __shared__ float sm[];
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_per_block = 4 * RP;
+  const int p_blk = blockIdx.z * rows_per_block;
+  const int p_base = p_blk + warp * RP;
+  const int Di = Hs * P;
+  const int g = h / (Hs / G);
+  const int t0 = cu_seqlens[b], n_tok = cu_seqlens[b + 1] - t0;
+  if (n_tok == 0) return;
+  float* S = state + (((size_t)slots[b] * Hs + h) * P) * N;
+  float s[RP][NPL];
+  const bool has_state = start_pos[b] > 0;
+#pragma unroll
+  for (int r = 0; r < RP; r++)
+#pragma unroll
+    for (int j = 0; j < NPL; j++) {
+      const int p = p_base + r, n = lane + 32 * j;
+      s[r][j] = (has_state && p < P && n < N) ? S[(size_t)p * N + n] : 0.f;
+    }
+  // shared staging: per token  B[N] | C[N] | x[rows_per_block] | dt | dA
+  const int per_tok = 2 * N + rows_per_block + 2;
+  const float Dh = Dskip[h];
+  for (int tt0 = 0; tt0 < n_tok; tt0 += SCAN_TT) {
+    const int nt = min(SCAN_TT, n_tok - tt0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nt * per_tok; idx += blockDim.x) {
+      const int k = idx / per_tok, e = idx % per_tok;
+      const size_t t = (size_t)(t0 + tt0 + k);
+      float v;
+      if (e < N) v = xbc[t * Cd + Di + (size_t)g * N + e];
+      else if (e < 2 * N) v = xbc[t * Cd + Di + (size_t)G * N + (size_t)g * N + (e - N)];
+      else if (e < 2 * N + rows_per_block) {
+        const int p = p_blk + (e - 2 * N);
+        v = p < P ? xbc[t * Cd + (size_t)h * P + p] : 0.f;
+      } else if (e == 2 * N + rows_per_block) v = dt[t * Hs + h];
+      else v = dA[t * Hs + h];
+      sm[idx] = v;
+    }
+    __syncthreads();
+    for (int k = 0; k < nt; k++) {
+      const float* tk = sm + (size_t)k * per_tok;
+      const float dtv = tk[2 * N + rows_per_block], dAv = tk[2 * N + rows_per_block + 1];
+      float Bv[NPL], Cv[NPL];
+#pragma unroll
+      for (int j = 0; j < NPL; j++) {
+        const int n = lane + 32 * j;
+        Bv[j] = n < N ? tk[n] : 0.f;
+        Cv[j] = n < N ? tk[N + n] : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < RP; r++) {
+        const float xv = tk[2 * N + warp * RP + r];
+        const float xdt = xv * dtv;
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < NPL; j++) {
+          const float sv = fmaf(s[r][j], dAv, Bv[j] * xdt);
+          s[r][j] = sv;
+          sum = fmaf(sv, Cv[j], sum);
+        }
+        sum = warp_sum(sum);
+        const int p = p_base + r;
+        if (lane == 0 && p < P) y[(size_t)(t0 + tt0 + k) * Di + (size_t)h * P + p] = sum + xv * Dh;
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < RP; r++)
+#pragma unroll
+    for (int j = 0; j < NPL; j++) {
+      const int p = p_base + r, n = lane + 32 * j;
+      if (p < P && n < N) S[(size_t)p * N + n] = s[r][j];
+    }
+}
+
+template <int NPL>
+static int launch_scan(const float* xbc, const float* dt, const float* dA, const float* Dskip, float* state,
+                       const int* cu_seqlens, const int* slots, const int* start_pos, float* y, int B, int Hs, int P,
+                       int N, int G, int Cd, cudaStream_t stream) {
+  constexpr int RP = 4;
+  dim3 grid(B, Hs, (P + 4 * RP - 1) / (4 * RP));
+  const size_t smem = (size_t)SCAN_TT * (2 * N + 4 * RP + 2) * sizeof(float);
+  ssm_scan_kernel<NPL, RP><<<grid, 128, smem, stream>>>(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, Hs,
+                                                        P, N, G, Cd);
+  TLC_CHECK_LAUNCH("ssm_scan");
+  return 0;
+}
+
+extern "C" int tlc_ssm_scan(const float* xbc, const float* dt, const float* dA, const float* Dskip, float* state,
+                            const int* cu_seqlens, const int* slots, const int* start_pos, float* y, int B, int Hs,
+                            int P, int N, int G, int Cd, cudaStream_t stream) {
+  if (B == 0) return 0;
+  TLC_REQUIRE(G > 0 && Hs % G == 0, "ssm_scan: %d heads are not a multiple of %d groups", Hs, G);
+  TLC_REQUIRE(N >= 1 && N <= 256, "ssm_scan: state size %d is outside the kernel's range 1..256", N);
+  TLC_REQUIRE(Hs <= 65535, "ssm_scan: too many heads (%d)", Hs);
+  if (N <= 32) return launch_scan<1>(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, B, Hs, P, N, G, Cd, stream);
+  if (N <= 64) return launch_scan<2>(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, B, Hs, P, N, G, Cd, stream);
+  if (N <= 128) return launch_scan<4>(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, B, Hs, P, N, G, Cd, stream);
+  return launch_scan<8>(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, B, Hs, P, N, G, Cd, stream);
+}

@@ -1,0 +1,95 @@
+"""The step function: run the tokens a step brings, as one batch, from the cache.
+
+CodeClaper/tinyllama.c's step is graph_execute(session, tokens, n): it appends n tokens
+of the one sequence at the session's position, in chunks of n_ubatch, and returns the
+logits of the last row (graph.c:1360-1421, 1282-1283).  Here a step carries several
+sequences: each brings its next tokens (a whole prompt, a chunk of one, or a single
+token), all are packed back to back into one batch without padding, every part reads
+what came before from the sequence's cache slot, and logits come back for the rows that
+were asked for.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache import Cache, CacheError
+from ..models.model import Model
+from ..parts.base import StepInfo
+
+
+@dataclass
+class StepEntry:
+    """One sequence's share of a step: its slot, its next tokens, and the indices among
+    these tokens whose logits are wanted."""
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class StepError(ValueError):
+    pass
+
+
+def pack(entries: Sequence[StepEntry], starts: Sequence[int], vocab: int, device) -> Tuple[StepInfo, torch.Tensor, int]:
+    """Host lists -> one int32 buffer -> one copy to the device -> StepInfo views.
+    Returns (step, packed rows whose logits are wanted, their count)."""
+    tokens, positions, row_seq, cu, want_rows = [], [], [], [0], []
+    for b, (e, start) in enumerate(zip(entries, starts)):
+        n = len(e.tokens)
+        for t in e.tokens:
+            if not (0 <= int(t) < vocab):
+                raise StepError(f"token id {t} is outside the vocabulary 0..{vocab - 1}")
+        for w in e.want:
+            if not (0 <= int(w) < n):
+                raise StepError(f"wanted index {w} is outside this step's {n} tokens")
+            want_rows.append(cu[-1] + int(w))
+        tokens += [int(t) for t in e.tokens]
+        positions += list(range(start, start + n))
+        row_seq += [b] * n
+        cu.append(cu[-1] + n)
+    T, B, W = len(tokens), len(entries), len(want_rows)
+    flat = tokens + positions + row_seq + cu + [e.slot for e in entries] + list(starts) + want_rows
+    host = torch.tensor(flat, dtype=torch.int32)
+    if torch.device(device).type == "cuda":
+        host = host.pin_memory()
+    dev = host.to(device, non_blocking=True)
+    o = 0
+
+    def take(n):
+        nonlocal o
+        v = dev[o:o + n]
+        o += n
+        return v
+
+    lens = [len(e.tokens) for e in entries]
+    step = StepInfo(n_rows=T, n_seqs=B, tokens=take(T), positions=take(T), row_seq=take(T), cu_seqlens=take(B + 1),
+                    slots=take(B), start_pos=take(B), max_new=max(lens) if lens else 0,
+                    max_context=max((s + n for s, n in zip(starts, lens)), default=0),
+                    host_lens=tuple(lens), host_start=tuple(starts), host_slots=tuple(e.slot for e in entries))
+    return step, take(W), W
+
+
+def step(model: Model, cache: Cache, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    """Runs one step; returns float32 logits [n_wanted, vocab] on the device in the order of
+    the entries and of their ``want`` lists (None when nothing is wanted).
+
+    The slots of the entries must be held (Cache.acquire) and distinct.  Nothing is launched
+    before every entry has been checked and its pages reserved."""
+    entries = [e for e in entries]
+    if not entries:
+        return None
+    if len({e.slot for e in entries}) != len(entries):
+        raise StepError("a step names the same sequence slot twice")
+    for e in entries:
+        if len(e.tokens) == 0:
+            raise StepError("a step entry brings no tokens")
+    starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
+    info, want_rows, n_want = pack(entries, starts, model.vocab, model.device)
+    cache.upload_tables()
+    logits = model.forward(info, cache, want_rows if n_want else None)
+    for e in entries:
+        cache.commit(e.slot, len(e.tokens))
+    return logits

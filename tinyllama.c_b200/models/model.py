@@ -1,0 +1,89 @@
+"""A model: embedding, layers, the order they run in, final norm, output head.
+
+CodeClaper/tinyllama.c's architecture file builds one static node list per model
+(falcon_h1.c:256-417) and the executor walks it (graph.c:1278-1302), evaluating the
+output head for the last row only (graph.c:1282-1283).  Here the walk is over
+``schedule``, a list of (layer, cache) pairs that is data of the model, and the head
+runs on the rows whose logits are wanted.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..parts.base import LayerCache, LayerRun, LayerSpec, Part, PartSpec, StepInfo, WeightSpec
+from ..parts.block import Block
+from ..parts.linear import StackedLinear, matrix_dtype
+
+
+class Model:
+    def __init__(self, config, layer_specs: Sequence[LayerSpec], schedule: Optional[Sequence[LayerRun]],
+                 final_norm: PartSpec, embed_name: str, head_name: Optional[str], vocab: int, hidden: int,
+                 embed_scale: float = 1.0, head_scale: float = 1.0):
+        self.config = config
+        self.vocab, self.hidden = int(vocab), int(hidden)
+        self.layers: List[Block] = [Block(s) for s in layer_specs]
+        self.schedule: List[LayerRun] = list(schedule) if schedule is not None \
+            else [LayerRun(i) for i in range(len(self.layers))]
+        for run in self.schedule:
+            if not (0 <= run.layer < len(self.layers)) or not (0 <= run.cache_id < len(self.layers)):
+                raise ValueError(f"schedule entry {run} names a layer that does not exist")
+        self.final_norm = final_norm.build()
+        self.embed_name, self.head_name = embed_name, head_name            # head_name None: tied (core.c:1246-1249)
+        self.embed_scale = float(embed_scale)
+        self.head = StackedLinear(hidden)
+        self.head.add(head_name or embed_name, vocab, None, 1.0, head_scale)
+        self.embed_table: Optional[torch.Tensor] = None
+        self.dtype: Optional[torch.dtype] = None
+        self.device: Optional[torch.device] = None
+
+    # ---- declarations ----------------------------------------------------------------------
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [WeightSpec(self.embed_name, (self.vocab, self.hidden), "normal")]
+        if self.head_name:
+            specs.append(WeightSpec(self.head_name, (self.vocab, self.hidden), "normal"))
+        for layer in self.layers:
+            specs += layer.weight_specs()
+        specs += self.final_norm.weight_specs()
+        seen, out = set(), []
+        for s in specs:
+            if s.name not in seen:
+                seen.add(s.name)
+                out.append(s)
+        return out
+
+    def cache_requests(self) -> Dict[int, list]:
+        """Cache needs of every layer whose cache some schedule entry uses."""
+        used = {run.cache_id for run in self.schedule}
+        return {i: self.layers[i].cache_requests() for i in sorted(used)}
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
+        self.dtype, self.device = dtype, torch.device(device)
+        for layer in self.layers:
+            layer.bind(tensors, dtype, device)
+        self.final_norm.bind(tensors, dtype, device)
+        emb = tensors[self.embed_name]
+        self.embed_table = emb.to(device=device, dtype=matrix_dtype(emb.dtype, dtype)).contiguous()
+        if self.head_name is None:
+            self.head.bind({self.embed_name: self.embed_table}, dtype, device)     # shares the table's storage
+        else:
+            self.head.bind(tensors, dtype, device)
+
+    # ---- forward ------------------------------------------------------------------------------
+    def forward(self, step: StepInfo, cache, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Runs the step's rows through every scheduled layer; returns float32 logits
+        [n_wanted, vocab] for the packed rows in want_rows (None: no logits)."""
+        x = torch.empty((step.n_rows, self.hidden), dtype=torch.float32, device=self.device)
+        ops.embed(step.tokens, self.embed_table, self.embed_scale, x)
+        for run in self.schedule:
+            self.layers[run.layer].forward(x, step, cache.layer_view(run.cache_id, run.writes))
+        if want_rows is None or want_rows.numel() == 0:
+            return None
+        n = want_rows.numel()
+        normed = torch.empty((n, self.hidden), dtype=self.dtype, device=self.device)
+        self.final_norm.forward(x, normed, want_rows)
+        logits = torch.empty((n, self.vocab), dtype=torch.float32, device=self.device)
+        self.head.forward(normed, logits)
+        return logits

@@ -1,0 +1,310 @@
+"""Tensor-level entry points of the CUDA kernels.
+
+Each function checks devices, element types and strides, then calls one exported C
+function of the kernel library on the current CUDA stream.  Nothing here computes on
+the CPU or calls a library kernel: if the tensors are not on a GPU, or the library
+cannot be built, the call raises.  Parts of the model call these through the module
+(``ops.linear(...)``), which is also the seam a test uses to observe calls.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc import build as _build
+
+F32, BF16 = 0, 1
+PAGE = 64          # tokens per page of the key/value store (TLC_PAGE in common.cuh)
+
+_vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_SIGNATURES = {
+    "tlc_embed": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp],
+    "tlc_rmsnorm": [_vp, _vp, _vp, _f, _i, _i, _vp, _i, _vp],
+    "tlc_gated_rmsnorm": [_vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _vp],
+    "tlc_swiglu": [_vp, _i, _i, _i, _i, _vp, _vp],
+    "tlc_gather_rows": [_vp, _vp, _i, _i, _vp, _vp],
+    "tlc_linear_simt": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
+    "tlc_rope_kv_store": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                          _i, _vp],
+    "tlc_attention": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "tlc_mamba_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
+                       _i, _i, _vp],
+    "tlc_ssm_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "tlc_argmax": [_vp, _i, _i, _vp, _vp],
+    "tlc_sample": [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp],
+}
+_lib = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    """Loads (building first if needed) the kernel library and declares its functions."""
+    global _lib
+    if _lib is None:
+        lib = _build.load()
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = ctypes.c_int
+        lib.tlc_last_error.restype = ctypes.c_char_p
+        _lib = lib
+    return _lib
+
+
+def _call(name: str, *args) -> None:
+    lib = library()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise KernelError(f"{name}: {lib.tlc_last_error().decode()}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"unsupported element type {dt}; the kernels take float32 and bfloat16")
+
+
+def _gpu(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("tinyllama.c_b200 kernels run on a CUDA device only (got a CPU tensor); "
+                              "there is no CPU path")
+
+
+def _rows(t: torch.Tensor, what: str) -> int:
+    """Row stride of a 2-D tensor whose rows are dense."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{what}: expected a 2-D tensor with dense rows, got shape {tuple(t.shape)} "
+                          f"strides {t.stride()}")
+    return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _f32vec(t: Optional[torch.Tensor], n: int, what: str) -> None:
+    if t is None:
+        return
+    if t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n:
+        raise KernelError(f"{what}: expected {n} contiguous float32 values, got {tuple(t.shape)} {t.dtype}")
+
+
+def _i32(t: torch.Tensor, what: str) -> None:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{what}: expected a contiguous int32 tensor, got {t.dtype}")
+
+
+# ---- elementwise ---------------------------------------------------------------------
+def embed(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: torch.Tensor) -> None:
+    """out[t] = table[tokens[t]] * scale; out is float32 [T, D]."""
+    _gpu(tokens, table, out)
+    _i32(tokens, "embed tokens")
+    T, (V, D) = tokens.numel(), table.shape
+    if out.dtype != torch.float32 or not out.is_contiguous() or tuple(out.shape) != (T, D) or not table.is_contiguous():
+        raise KernelError("embed: out must be contiguous float32 [T, D] and the table contiguous")
+    _call("tlc_embed", tokens.data_ptr(), table.data_ptr(), dtype_code(table.dtype), T, D, V, float(scale),
+          out.data_ptr(), _stream())
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight; x float32 [*, D]."""
+    _gpu(x, weight, out, rows)
+    D = x.shape[1]
+    R = out.shape[0]
+    if x.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous() or out.shape[1] != D:
+        raise KernelError("rmsnorm: x must be contiguous float32 and out contiguous [R, D]")
+    _f32vec(weight, D, "rmsnorm weight")
+    if rows is not None:
+        _i32(rows, "rmsnorm rows")
+        if rows.numel() != R:
+            raise KernelError("rmsnorm: one row index per output row")
+    elif x.shape[0] != R:
+        raise KernelError("rmsnorm: x and out differ in rows")
+    _call("tlc_rmsnorm", x.data_ptr(), _p(rows), weight.data_ptr(), float(eps), R, D, out.data_ptr(),
+          dtype_code(out.dtype), _stream())
+
+
+def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: Optional[torch.Tensor], eps: float, n_groups: int,
+                  norm_before_gate: bool, out: torch.Tensor) -> None:
+    """Gate y by silu(z) and RMS-normalise per group (either order); weight None = gate only."""
+    _gpu(y, z, weight, out)
+    T, Di = y.shape
+    if y.dtype != torch.float32 or not y.is_contiguous() or not out.is_contiguous() or tuple(out.shape) != (T, Di):
+        raise KernelError("gated_rmsnorm: y must be contiguous float32 [T, Di] and out contiguous [T, Di]")
+    if z.shape != y.shape:
+        raise KernelError("gated_rmsnorm: gate and input differ in shape")
+    _f32vec(weight, Di, "gated_rmsnorm weight")
+    _call("tlc_gated_rmsnorm", y.data_ptr(), z.data_ptr(), dtype_code(z.dtype), _rows(z, "gate"), _p(weight),
+          float(eps), T, Di, int(n_groups), int(bool(norm_before_gate)), out.data_ptr(), dtype_code(out.dtype),
+          _stream())
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate_up[:, :F]) * gate_up[:, F:]."""
+    _gpu(gate_up, out)
+    T, F2 = gate_up.shape
+    F = F2 // 2
+    if out.dtype != gate_up.dtype or not out.is_contiguous() or tuple(out.shape) != (T, F) or F2 != 2 * F:
+        raise KernelError("swiglu: out must be contiguous [T, F] of the input's type")
+    _call("tlc_swiglu", gate_up.data_ptr(), dtype_code(gate_up.dtype), _rows(gate_up, "gate_up"), F, T,
+          out.data_ptr(), _stream())
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    _gpu(x, rows, out)
+    _i32(rows, "gather rows")
+    if x.dtype != torch.float32 or out.dtype != torch.float32 or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("gather_rows: float32 contiguous tensors")
+    _call("tlc_gather_rows", x.data_ptr(), rows.data_ptr(), rows.numel(), x.shape[1], out.data_ptr(), _stream())
+
+
+# ---- linear -----------------------------------------------------------------------------
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale: Optional[torch.Tensor] = None,
+           colbias: Optional[torch.Tensor] = None, accumulate: bool = False) -> None:
+    """out[m, n] (+)= (sum_k a[m, k] w[n, k]) * colscale[n] + colbias[n].
+
+    a [M, K] and out [M, N] may be row-strided views; w is [N, K].  Accumulation is
+    32-bit.  float32 operands run on the CUDA cores in true 32-bit arithmetic."""
+    _gpu(a, w, out, colscale, colbias)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (M, N):
+        raise KernelError(f"linear: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
+    _f32vec(colscale, N, "linear colscale")
+    _f32vec(colbias, N, "linear colbias")
+    _call("tlc_linear_simt", a.data_ptr(), dtype_code(a.dtype), _rows(a, "linear input"), w.data_ptr(),
+          dtype_code(w.dtype), _rows(w, "linear weight"), out.data_ptr(), dtype_code(out.dtype),
+          _rows(out, "linear output"), _p(colscale), _p(colbias), int(bool(accumulate)), M, N, K, _stream())
+
+
+# ---- attention -------------------------------------------------------------------------------
+def rope_kv_store(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, k_pages: torch.Tensor,
+                  v_pages: torch.Tensor, inv_freq: torch.Tensor, positions: torch.Tensor, row_seq: torch.Tensor,
+                  slots: torch.Tensor, block_table: torch.Tensor, H: int, KV: int, hd: int,
+                  write_kv: bool = True) -> None:
+    """Rotates q and k at their absolute positions; writes q to q_out [T, H*hd] and k, v into
+    the pages of their sequences ([page, KV, 64, hd])."""
+    _gpu(qkv, q_out, k_pages, v_pages, inv_freq, positions, row_seq, slots, block_table)
+    T = qkv.shape[0]
+    for t, n in ((positions, "positions"), (row_seq, "row_seq"), (slots, "slots"), (block_table, "block_table")):
+        _i32(t, n)
+    if q_out.dtype != qkv.dtype or k_pages.dtype != qkv.dtype or v_pages.dtype != qkv.dtype:
+        raise KernelError("rope_kv_store: q, the pages and the projection must share one element type")
+    if not q_out.is_contiguous() or tuple(q_out.shape) != (T, H * hd) or not k_pages.is_contiguous() \
+            or not v_pages.is_contiguous() or tuple(k_pages.shape[1:]) != (KV, PAGE, hd):
+        raise KernelError("rope_kv_store: q_out must be contiguous [T, H*hd], pages contiguous [n, KV, 64, hd]")
+    _f32vec(inv_freq, inv_freq.numel(), "rope inv_freq")
+    _call("tlc_rope_kv_store", qkv.data_ptr(), dtype_code(qkv.dtype), _rows(qkv, "qkv"), q_off, k_off, v_off,
+          q_out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), inv_freq.data_ptr(), 2 * inv_freq.numel(),
+          positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+          T, H, KV, hd, int(bool(write_kv)), _stream())
+
+
+def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+              positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, H: int, KV: int,
+              hd: int, scale: float, window: int = 0) -> None:
+    """Causal grouped-query attention of every row over its sequence's pages (keys 0..position,
+    or the last `window` of them)."""
+    _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out)
+    T = q.shape[0]
+    if not q.is_contiguous() or not out.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.shape != q.shape \
+            or out.dtype != q.dtype or k_pages.dtype != q.dtype:
+        raise KernelError("attention: q and out must be contiguous [T, H*hd] of the pages' type")
+    _call("tlc_attention", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
+          block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(),
+          out.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), _stream())
+
+
+# ---- Mamba2 -------------------------------------------------------------------------------------
+def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, bias: Optional[torch.Tensor],
+               dt_bias: torch.Tensor, A: torch.Tensor, conv_state: torch.Tensor, cu_seqlens: torch.Tensor,
+               row_seq: torch.Tensor, slots: torch.Tensor, start_pos: torch.Tensor, xbc_out: torch.Tensor,
+               dt_out: torch.Tensor, dA_out: torch.Tensor) -> None:
+    """Causal depthwise convolution + SiLU of the xBC columns of proj, continuing each
+    sequence's window (conv_state [n_slots, K-1, Cd], updated in place); also
+    dt = softplus(dt + dt_bias) and dA = exp(dt * A) per row and head."""
+    _gpu(proj, w, bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out, dA_out)
+    T = proj.shape[0]
+    Cd, K = w.shape
+    Hs = dt_bias.numel()
+    B = slots.numel()
+    _f32vec(w, Cd * K, "conv weight")
+    _f32vec(bias, Cd, "conv bias")
+    _f32vec(dt_bias, Hs, "dt_bias")
+    _f32vec(A, Hs, "A")
+    for t, n in ((cu_seqlens, "cu_seqlens"), (row_seq, "row_seq"), (slots, "slots"), (start_pos, "start_pos")):
+        _i32(t, n)
+    if conv_state.dtype != torch.float32 or not conv_state.is_contiguous() or tuple(conv_state.shape[1:]) != (K - 1, Cd):
+        raise KernelError("mamba_conv: conv_state must be contiguous float32 [n_slots, K-1, Cd]")
+    for t, shp, n in ((xbc_out, (T, Cd), "xbc_out"), (dt_out, (T, Hs), "dt_out"), (dA_out, (T, Hs), "dA_out")):
+        if t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != shp:
+            raise KernelError(f"mamba_conv: {n} must be contiguous float32 {shp}")
+    _call("tlc_mamba_conv", proj.data_ptr(), dtype_code(proj.dtype), _rows(proj, "proj"), xbc_off, dt_off,
+          w.data_ptr(), _p(bias), dt_bias.data_ptr(), A.data_ptr(), conv_state.data_ptr(), cu_seqlens.data_ptr(),
+          row_seq.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), xbc_out.data_ptr(), dt_out.data_ptr(),
+          dA_out.data_ptr(), T, B, Cd, K, Hs, _stream())
+
+
+def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch.Tensor, state: torch.Tensor,
+             cu_seqlens: torch.Tensor, slots: torch.Tensor, start_pos: torch.Tensor, y: torch.Tensor, Hs: int, P: int,
+             N: int, G: int) -> None:
+    """Selective scan of every sequence in order, from its slot's state (zero at position 0);
+    state [n_slots, Hs, P, N] float32 is updated in place; y [T, Hs*P] float32 is before gating."""
+    _gpu(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y)
+    T, Cd = xbc.shape
+    if Cd != Hs * P + 2 * G * N:
+        raise KernelError("ssm_scan: xbc width does not match Hs*P + 2*G*N")
+    for t, shp, n in ((xbc, (T, Cd), "xbc"), (dt, (T, Hs), "dt"), (dA, (T, Hs), "dA"), (y, (T, Hs * P), "y")):
+        if t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != shp:
+            raise KernelError(f"ssm_scan: {n} must be contiguous float32 {shp}")
+    _f32vec(Dskip, Hs, "D")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (Hs, P, N):
+        raise KernelError("ssm_scan: state must be contiguous float32 [n_slots, Hs, P, N]")
+    _call("tlc_ssm_scan", xbc.data_ptr(), dt.data_ptr(), dA.data_ptr(), Dskip.data_ptr(), state.data_ptr(),
+          cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), y.data_ptr(), slots.numel(), Hs, P, N, G, Cd,
+          _stream())
+
+
+# ---- sampling -------------------------------------------------------------------------------------
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = first index of the maximum of logits[r]."""
+    _gpu(logits, out)
+    _i32(out, "argmax out")
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise KernelError("argmax: logits must be contiguous float32")
+    _call("tlc_argmax", logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(), _stream())
+
+
+def sample(logits: torch.Tensor, work: torch.Tensor, history: Optional[torch.Tensor], uniforms: torch.Tensor,
+           temperature: float, top_k: int, top_p: float, min_p: float, repeat_penalty: float,
+           frequency_penalty: float, presence_penalty: float, out: torch.Tensor) -> None:
+    """One token per row from penalised, temperature-scaled, top-k / min-p / top-p filtered
+    logits; `history` [R, n] int32 (-1 = empty) is the penalty window, `uniforms` [R] the draws,
+    `work` a [R, V] float32 scratch."""
+    _gpu(logits, work, history, uniforms, out)
+    R, V = logits.shape
+    _i32(out, "sample out")
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or work.dtype != torch.float32 \
+            or not work.is_contiguous() or work.numel() < R * V:
+        raise KernelError("sample: logits and work must be contiguous float32 [R, V]")
+    _f32vec(uniforms, R, "sample uniforms")
+    n_hist = 0
+    if history is not None:
+        _i32(history, "sample history")
+        n_hist = history.shape[1]
+    _call("tlc_sample", logits.data_ptr(), work.data_ptr(), _p(history), uniforms.data_ptr(), R, V,
+          float(temperature), int(top_k), float(top_p), float(min_p), float(repeat_penalty), n_hist,
+          float(frequency_penalty), float(presence_penalty), out.data_ptr(), _stream())

@@ -1,0 +1,50 @@
+"""A layer: norm -> mixers in parallel on the same normed input -> residual; norm ->
+feed-forward -> residual.
+
+CodeClaper/tinyllama.c falcon_h1.c:311-395: n = norm(x); x = (x + attn(n)) + ssm(n);
+x = x + ffn(norm(x)).  The residual stream is 32-bit; each mixer and the feed-forward add
+their output into it in the order they are listed.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .base import LayerCache, LayerSpec, Part, StepInfo, WeightSpec, act_empty
+
+
+class Block(Part):
+    def __init__(self, spec: LayerSpec, act_dtype_of=None):
+        self.spec = spec
+        self.mixer_norm = spec.mixer_norm.build()
+        self.mixers = [m.build() for m in spec.mixers]
+        self.ffn_norm = spec.ffn_norm.build() if spec.ffn_norm is not None else None
+        self.ffn = spec.ffn.build() if spec.ffn is not None else None
+        self.dtype: Optional[torch.dtype] = None
+
+    def parts(self) -> List[Part]:
+        return [p for p in [self.mixer_norm, *self.mixers, self.ffn_norm, self.ffn] if p is not None]
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [s for p in self.parts() for s in p.weight_specs()]
+
+    def cache_requests(self) -> list:
+        return [r for m in self.mixers for r in m.cache_requests()]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
+        self.dtype = dtype
+        for p in self.parts():
+            p.bind(tensors, dtype, device)
+
+    def forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
+        """Updates the float32 residual stream x32 [T, D] in place."""
+        if self.mixers:
+            normed = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+            self.mixer_norm.forward(x32, normed)
+            for m in self.mixers:
+                m.forward(normed, step, cache, x32)
+        if self.ffn is not None:
+            normed = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+            self.ffn_norm.forward(x32, normed)
+            self.ffn.forward(normed, x32)

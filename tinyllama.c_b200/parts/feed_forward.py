@@ -1,0 +1,44 @@
+"""Dense gated feed-forward (SwiGLU).
+
+d = W_down (silu(W_gate x) * (W_up x))  (CodeClaper/tinyllama.c falcon_h1.c:382-395).
+The gate and up projections are stacked into one product.  The multiplier on the gate's
+pre-activation, the one on the output, and the biases have no counterpart in the
+reference.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import ops
+from .base import Part, WeightSpec, act_empty, register_feed_forward
+from .linear import StackedLinear
+
+
+@register_feed_forward("swiglu")
+class SwiGLU(Part):
+    def __init__(self, hidden: int, intermediate: int, prefix: str, bias: bool = False, gate_scale: float = 1.0,
+                 down_scale: float = 1.0):
+        self.hidden, self.F = int(hidden), int(intermediate)
+        b = (lambda n: prefix + n + ".bias") if bias else (lambda n: None)
+        self.gate_up = StackedLinear(hidden)
+        self.gate_up.add(prefix + "gate_proj.weight", self.F, b("gate_proj"), 1.0, gate_scale)
+        self.gate_up.add(prefix + "up_proj.weight", self.F, b("up_proj"))
+        self.down = StackedLinear(self.F)
+        self.down.add(prefix + "down_proj.weight", hidden, b("down_proj"), 1.0, down_scale)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return self.gate_up.weight_specs() + self.down.weight_specs()
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
+        self.gate_up.bind(tensors, dtype, device)
+        self.down.bind(tensors, dtype, device)
+
+    def forward(self, normed: torch.Tensor, residual: torch.Tensor) -> None:
+        T = normed.shape[0]
+        gu = act_empty((T, 2 * self.F), normed)
+        self.gate_up.forward(normed, gu)
+        act = act_empty((T, self.F), normed)
+        ops.swiglu(gu, act)
+        self.down.forward(act, residual, accumulate=True)

@@ -1,0 +1,89 @@
+"""A projection y = (x W^T) * colscale + colbias, with the weights of several projections
+stacked row-wise so that one matrix product serves them all.
+
+The reference multiplies by one weight tensor per graph node (falcon_h1.c:315-317,
+342-343, 383-386) and adds an optional bias as a separate node (falcon_h1.c:319-330).
+Here the stacked rows, every constant multiplier and the bias are prepared once at
+load time: y[:, n] = acc[n] * colscale[n] + colbias[n], where a scalar that multiplies
+the input or the output and a per-row multiplier vector all fold into colscale, and
+the bias times the output multiplier into colbias.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from .base import WeightSpec
+
+
+def matrix_dtype(stored: torch.dtype, run: torch.dtype) -> torch.dtype:
+    """float32 runs use float32 weights; bfloat16 runs keep bfloat16 weights in bfloat16 and
+    leave a matrix that was stored in 32-bit as it is."""
+    if run == torch.float32 or stored == torch.float32:
+        return torch.float32
+    return torch.bfloat16
+
+
+class StackedLinear:
+    """Rows of several named weights (and optional biases) stacked into one projection."""
+
+    def __init__(self, in_features: int):
+        self.in_features = int(in_features)
+        self.segments: List[dict] = []
+        self.weight: Optional[torch.Tensor] = None
+        self.colscale: Optional[torch.Tensor] = None
+        self.colbias: Optional[torch.Tensor] = None
+
+    def add(self, weight_name: str, rows: int, bias_name: Optional[str] = None, in_scale: float = 1.0,
+            out_scale=1.0) -> int:
+        """Adds `rows` output rows; returns their first column in the stacked output.
+        y = ((x * in_scale) W^T + bias) * out_scale, out_scale a number or one value per row."""
+        off = self.out_features
+        self.segments.append(dict(w=weight_name, b=bias_name, rows=int(rows), in_scale=float(in_scale),
+                                  out_scale=out_scale, off=off))
+        return off
+
+    @property
+    def out_features(self) -> int:
+        return sum(s["rows"] for s in self.segments)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = []
+        for s in self.segments:
+            specs.append(WeightSpec(s["w"], (s["rows"], self.in_features), "normal"))
+            if s["b"]:
+                specs.append(WeightSpec(s["b"], (s["rows"],), "normal"))
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
+        mats = [tensors[s["w"]] for s in self.segments]
+        mdt = torch.bfloat16
+        for m in mats:
+            if matrix_dtype(m.dtype, dtype) == torch.float32:
+                mdt = torch.float32
+        if len(mats) == 1:
+            self.weight = mats[0].to(device=device, dtype=mdt).contiguous()
+        else:
+            self.weight = torch.cat([m.to(device=device, dtype=mdt) for m in mats], dim=0).contiguous()
+        scale = torch.ones(self.out_features, dtype=torch.float64)
+        bias = torch.zeros(self.out_features, dtype=torch.float64)
+        any_scale = any_bias = False
+        for s in self.segments:
+            sl = slice(s["off"], s["off"] + s["rows"])
+            osc = s["out_scale"]
+            osc = torch.as_tensor(osc, dtype=torch.float64) if not isinstance(osc, (int, float)) \
+                else torch.full((s["rows"],), float(osc), dtype=torch.float64)
+            scale[sl] = osc * s["in_scale"]
+            if s["b"]:
+                bias[sl] = tensors[s["b"]].to(torch.float64) * osc
+                any_bias = True
+            if bool((scale[sl] != 1.0).any()):
+                any_scale = True
+        self.colscale = scale.to(torch.float32).to(device) if any_scale else None
+        self.colbias = bias.to(torch.float32).to(device) if any_bias else None
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
+        ops.linear(x, self.weight, out, self.colscale, self.colbias, accumulate)
+        return out

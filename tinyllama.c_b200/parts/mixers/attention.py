@@ -1,0 +1,64 @@
+"""Grouped-query attention mixer over the paged key/value cache.
+
+CodeClaper/tinyllama.c: q/k/v projections with optional biases (falcon_h1.c:315-330),
+rotation of q and k (falcon_h1.c:332-333), K/V write-through and causal attention with
+kv head h/(H/KV), scale 1/sqrt(head_dim) and an optional window (cpu_op.c:964-1064;
+graph.c:1275), output projection (falcon_h1.c:338).  The multipliers on the input, the
+keys and the output have no counterpart there; they fold into the projections.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from ... import ops
+from ..base import KVRequest, LayerCache, Part, PartSpec, StepInfo, WeightSpec, act_empty, register_mixer
+from ..linear import StackedLinear
+
+
+@register_mixer("attention")
+class AttentionMixer(Part):
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, prefix: str,
+                 position: PartSpec, bias: bool = False, window: Optional[int] = None, in_scale: float = 1.0,
+                 out_scale: float = 1.0, key_scale: float = 1.0, cache_key: str = "kv"):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
+        self.hidden, self.H, self.KV, self.hd = int(hidden), int(n_heads), int(n_kv_heads), int(head_dim)
+        self.window = int(window) if window else None
+        self.cache_key = cache_key
+        self.position = position.build()
+        b = (lambda n: prefix + n + ".bias") if bias else (lambda n: None)
+        self.qkv = StackedLinear(hidden)
+        self.q_off = self.qkv.add(prefix + "q_proj.weight", self.H * self.hd, b("q_proj"), in_scale)
+        self.k_off = self.qkv.add(prefix + "k_proj.weight", self.KV * self.hd, b("k_proj"), in_scale, key_scale)
+        self.v_off = self.qkv.add(prefix + "v_proj.weight", self.KV * self.hd, b("v_proj"), in_scale)
+        self.o = StackedLinear(self.H * self.hd)
+        self.o.add(prefix + "o_proj.weight", hidden, b("o_proj"), 1.0, out_scale)
+        self.dtype = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return self.qkv.weight_specs() + self.o.weight_specs() + self.position.weight_specs()
+
+    def cache_requests(self) -> list:
+        return [KVRequest(self.cache_key, self.KV, self.hd, self.window)]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
+        self.dtype = dtype
+        self.qkv.bind(tensors, dtype, device)
+        self.o.bind(tensors, dtype, device)
+        self.position.bind(tensors, dtype, device)
+
+    def forward(self, normed: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor) -> None:
+        T = step.n_rows
+        kv = cache.kv[self.cache_key]
+        qkv = act_empty((T, self.qkv.out_features), normed)
+        self.qkv.forward(normed, qkv)
+        q = act_empty((T, self.H * self.hd), normed)
+        self.position.rotate_and_store(qkv, self.q_off, self.k_off, self.v_off, q, kv, step, self.H, self.KV, self.hd,
+                                       cache.writes)
+        att = act_empty((T, self.H * self.hd), normed)
+        ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
+                      self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0)
+        self.o.forward(att, residual, accumulate=True)

@@ -1,0 +1,94 @@
+"""Mamba2 (selective state-space) mixer with a per-sequence conv window and state.
+
+CodeClaper/tinyllama.c: in_proj of width d_ssm + conv_dim + n_heads laid out
+z | x | B | C | dt (falcon_h1.c:342-343; cpu_op.c:849, 865, 925-929); causal depthwise
+convolution + SiLU over x|B|C with a window of d_conv-1 raw samples (cpu_op.c:836-889);
+dt = softplus(dt + dt_bias), dA = exp(dt * A) with A = -exp(A_log) (cpu_op.c:933-934,
+806-808); S = S*dA + B*(x*dt), y = S.C + x*D (cpu_op.c:939-951); gate by silu(z) and
+grouped RMSNorm (cpu_op.c:950-958); out_proj (falcon_h1.c:367-368).  The reference keeps
+one window and one state per layer for its single sequence (falcon_h1.c:136-147); here
+they are fixed-size per-sequence cache entries.  The five multipliers on the in_proj
+slices, the in/out multipliers, the projection biases and norm-before-gate have no
+counterpart in the reference.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ... import ops
+from ..base import LayerCache, Part, StateRequest, StepInfo, WeightSpec, act_empty, register_mixer, to_vec
+from ..linear import StackedLinear
+
+
+@register_mixer("mamba2")
+class Mamba2Mixer(Part):
+    def __init__(self, hidden: int, d_ssm: int, n_heads: int, d_head: int, n_groups: int, d_state: int, d_conv: int,
+                 prefix: str, eps: float, conv_bias: bool = True, proj_bias: bool = False, rms_norm: bool = True,
+                 norm_before_gate: bool = False, slice_scales: Sequence[float] = (1.0,) * 5, in_scale: float = 1.0,
+                 out_scale: float = 1.0, cache_key: str = "mamba"):
+        if n_heads * d_head != d_ssm or n_heads % n_groups or d_ssm % n_groups:
+            raise ValueError("mamba2: n_heads*d_head must equal d_ssm and both be multiples of n_groups")
+        self.hidden, self.Di, self.Hs, self.P = int(hidden), int(d_ssm), int(n_heads), int(d_head)
+        self.G, self.N, self.K = int(n_groups), int(d_state), int(d_conv)
+        self.Cd = self.Di + 2 * self.G * self.N                      # falcon_h1.c:124
+        self.eps, self.rms_norm, self.norm_before_gate = float(eps), bool(rms_norm), bool(norm_before_gate)
+        self.prefix, self.cache_key = prefix, cache_key
+        self.conv_bias = bool(conv_bias)
+        mz, mx, mb, mc, mdt = [float(v) for v in slice_scales]
+        rows = [mz] * self.Di + [mx] * self.Di + [mb] * (self.G * self.N) + [mc] * (self.G * self.N) + [mdt] * self.Hs
+        self.in_proj = StackedLinear(hidden)
+        self.in_proj.add(prefix + "in_proj.weight", self.Di + self.Cd + self.Hs,
+                         prefix + "in_proj.bias" if proj_bias else None, in_scale, rows)
+        self.out_proj = StackedLinear(self.Di)
+        self.out_proj.add(prefix + "out_proj.weight", hidden, prefix + "out_proj.bias" if proj_bias else None,
+                          1.0, out_scale)
+        self.conv_w = self.conv_b = self.A = self.D = self.dt_bias = self.norm_w = None
+
+    # ---- declarations ------------------------------------------------------------------
+    def weight_specs(self) -> List[WeightSpec]:
+        p = self.prefix
+        specs = self.in_proj.weight_specs() + self.out_proj.weight_specs()
+        specs.append(WeightSpec(p + "conv1d.weight", (self.Cd, 1, self.K), "conv"))
+        if self.conv_bias:
+            specs.append(WeightSpec(p + "conv1d.bias", (self.Cd,), "normal"))
+        specs += [WeightSpec(p + "A_log", (self.Hs,), "a_log"), WeightSpec(p + "D", (self.Hs,), "d_skip"),
+                  WeightSpec(p + "dt_bias", (self.Hs,), "dt_bias")]
+        if self.rms_norm:
+            specs.append(WeightSpec(p + "norm.weight", (self.Di,), "ones"))
+        return specs
+
+    def cache_requests(self) -> list:
+        return [StateRequest(self.cache_key + ".conv", (self.K - 1, self.Cd)),
+                StateRequest(self.cache_key + ".ssm", (self.Hs, self.P, self.N))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
+        p = self.prefix
+        self.in_proj.bind(tensors, dtype, device)
+        self.out_proj.bind(tensors, dtype, device)
+        self.conv_w = to_vec(tensors[p + "conv1d.weight"].reshape(self.Cd, self.K), device)
+        self.conv_b = to_vec(tensors[p + "conv1d.bias"], device) if self.conv_bias else None
+        self.A = (-torch.exp(tensors[p + "A_log"].to(torch.float32))).to(device).contiguous()    # cpu_op.c:806-808
+        self.D = to_vec(tensors[p + "D"], device)
+        self.dt_bias = to_vec(tensors[p + "dt_bias"], device)
+        self.norm_w = to_vec(tensors[p + "norm.weight"], device) if self.rms_norm else None
+
+    # ---- one step --------------------------------------------------------------------------
+    def forward(self, normed: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor) -> None:
+        T, f32 = step.n_rows, torch.float32
+        conv_state = cache.state[self.cache_key + ".conv"]
+        ssm_state = cache.state[self.cache_key + ".ssm"]
+        proj = act_empty((T, self.in_proj.out_features), normed)
+        self.in_proj.forward(normed, proj)
+        xbc = act_empty((T, self.Cd), normed, f32)
+        dt = act_empty((T, self.Hs), normed, f32)
+        dA = act_empty((T, self.Hs), normed, f32)
+        ops.mamba_conv(proj, self.Di, self.Di + self.Cd, self.conv_w, self.conv_b, self.dt_bias, self.A, conv_state,
+                       step.cu_seqlens, step.row_seq, step.slots, step.start_pos, xbc, dt, dA)
+        y = act_empty((T, self.Di), normed, f32)
+        ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs, self.P,
+                     self.N, self.G)
+        gated = act_empty((T, self.Di), normed)
+        ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated)
+        self.out_proj.forward(gated, residual, accumulate=True)
