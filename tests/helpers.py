@@ -26,9 +26,25 @@ def read_config(model_dir: str) -> dict:
         return json.load(f)
 
 
-def plain_logits(model_dir: str, tokens) -> np.ndarray:
-    return plain.forward(read_config(model_dir), read_weights(model_dir), list(tokens))
+def plain_logits(model_dir: str, tokens, dtype: str = "float32") -> np.ndarray:
+    """Logits of the plain implementation; for "bfloat16" with its model of a bfloat16 engine
+    (inputs of matrix products and stored q/k/v rounded, everything else exact)."""
+    rnd = plain.bf16_round if dtype == "bfloat16" else plain._same
+    return plain.forward(read_config(model_dir), read_weights(model_dir), list(tokens), rnd=rnd)
+
+
+def release_all(llm) -> None:
+    """Gives back slots that an earlier, failed test left held."""
+    for s in llm.cache.slots.held():
+        llm.cache.release(s)
 
 
 def random_tokens(vocab: int, n: int, seed: int):
     return np.random.default_rng(seed).integers(0, vocab, n).tolist()
+
+
+STATS = {}      # (dtype, kind) -> largest error seen as a fraction of its allowance (printed after the run)
+
+
+def record(dtype: str, kind: str, ratio: float) -> None:
+    STATS[(dtype, kind)] = max(STATS.get((dtype, kind), 0.0), float(ratio))

@@ -51,6 +51,21 @@ def derived(cfg: dict) -> dict:
                 L=cfg["num_hidden_layers"])
 
 
+def bf16_round(x):
+    """Round to the nearest bfloat16 (ties to even), keeping the array's type.  Passed as
+    ``rnd`` to forward() it models a bfloat16 engine that keeps 32-bit accumulators: the
+    inputs of every matrix product and the stored queries, keys and values are rounded,
+    nothing else is."""
+    x32 = np.ascontiguousarray(x, dtype=np.float32)
+    u = x32.view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32).astype(np.asarray(x).dtype).reshape(np.shape(x))
+
+
+def _same(x):
+    return x
+
+
 def silu(x):
     """x / (1 + exp(-x))  (cpu_op.c:332-335)."""
     return x / (1.0 + np.exp(-x))
@@ -185,7 +200,7 @@ def gated_norm(y, z, w, eps, G, rms_norm_on, norm_before_gate):
     return grouped(y * silu(z))
 
 
-def attention_mixer(n, W, pre, cfg, d, positions):
+def attention_mixer(n, W, pre, cfg, d, positions, rnd=_same):
     """q/k/v projection, optional bias, RoPE, attention, output projection
     (falcon_h1.c:315-338).  key_multiplier scales k after its bias (not in the reference)."""
     q = linear(n, W[pre + "self_attn.q_proj.weight"], W.get(pre + "self_attn.q_proj.bias"))
@@ -194,13 +209,13 @@ def attention_mixer(n, W, pre, cfg, d, positions):
     k = k * _get(cfg, "key_multiplier", 1.0)
     theta = _get(cfg, "rope_theta", 10000.0)                  # falcon_h1.c:126-128
     rope_dim = d["hd"]                                         # falcon_h1.c:265
-    q = rope_neox(q, positions, d["H"], d["hd"], rope_dim, theta)
-    k = rope_neox(k, positions, d["KV"], d["hd"], rope_dim, theta)
-    o = causal_attention(q, k, v, d["H"], d["KV"], d["hd"], int(_get(cfg, "sliding_window", 0) or 0))
-    return linear(o, W[pre + "self_attn.o_proj.weight"], W.get(pre + "self_attn.o_proj.bias"))
+    q = rnd(rope_neox(q, positions, d["H"], d["hd"], rope_dim, theta))
+    k = rnd(rope_neox(k, positions, d["KV"], d["hd"], rope_dim, theta))
+    o = causal_attention(q, k, rnd(v), d["H"], d["KV"], d["hd"], int(_get(cfg, "sliding_window", 0) or 0))
+    return linear(rnd(o), W[pre + "self_attn.o_proj.weight"], W.get(pre + "self_attn.o_proj.bias"))
 
 
-def mamba2_mixer(n, W, pre, cfg, d):
+def mamba2_mixer(n, W, pre, cfg, d, rnd=_same):
     """in_proj -> conv -> scan -> gate/norm -> out_proj (falcon_h1.c:342-368).
 
     The in_proj row order is z | x | B | C | dt (cpu_op.c:849, 865, 925-929).  The five
@@ -221,43 +236,44 @@ def mamba2_mixer(n, W, pre, cfg, d):
     y = gated_norm(y, z, W.get(pre + "mamba.norm.weight"), cfg["rms_norm_eps"], G,
                    bool(_get(cfg, "mamba_rms_norm", True)) and (pre + "mamba.norm.weight") in W,
                    bool(_get(cfg, "mamba_norm_before_gate", False)))
-    return linear(y, W[pre + "mamba.out_proj.weight"], W.get(pre + "mamba.out_proj.bias"))
+    return linear(rnd(y), W[pre + "mamba.out_proj.weight"], W.get(pre + "mamba.out_proj.bias"))
 
 
-def swiglu_mlp(hn, W, pre, cfg):
+def swiglu_mlp(hn, W, pre, cfg, rnd=_same):
     """down(silu(gate(x)) * up(x)) (falcon_h1.c:382-395); mlp_multipliers = [gate, down]
     scale the gate pre-activation and the down output (not in the reference)."""
     mg, md = _get(cfg, "mlp_multipliers", [1.0, 1.0])
     g = linear(hn, W[pre + "feed_forward.gate_proj.weight"], W.get(pre + "feed_forward.gate_proj.bias"))
     u = linear(hn, W[pre + "feed_forward.up_proj.weight"], W.get(pre + "feed_forward.up_proj.bias"))
-    a = silu(g * mg) * u
+    a = rnd(silu(g * mg) * u)
     return linear(a, W[pre + "feed_forward.down_proj.weight"], W.get(pre + "feed_forward.down_proj.bias")) * md
 
 
-def block(x, W, layer, cfg, d, positions):
+def block(x, W, layer, cfg, d, positions, rnd=_same):
     """x = (x + attn(n)) + ssm(n); x = x + mlp(norm(x))  (falcon_h1.c:311-395)."""
     pre = f"model.layers.{layer}."
     eps = cfg["rms_norm_eps"]
-    n = rms_norm(x, W[pre + "input_layernorm.weight"], eps)
-    a = attention_mixer(n * _get(cfg, "attention_in_multiplier", 1.0), W, pre, cfg, d, positions)
+    n = rnd(rms_norm(x, W[pre + "input_layernorm.weight"], eps))
+    a = attention_mixer(n * _get(cfg, "attention_in_multiplier", 1.0), W, pre, cfg, d, positions, rnd)
     a = a * _get(cfg, "attention_out_multiplier", 1.0)
-    m = mamba2_mixer(n * _get(cfg, "ssm_in_multiplier", 1.0), W, pre, cfg, d)
+    m = mamba2_mixer(n * _get(cfg, "ssm_in_multiplier", 1.0), W, pre, cfg, d, rnd)
     m = m * _get(cfg, "ssm_out_multiplier", 1.0)
     x = (x + a) + m                                            # falcon_h1.c:372-375
-    hn = rms_norm(x, W[pre + "pre_ff_layernorm.weight"], eps)
-    return x + swiglu_mlp(hn, W, pre, cfg)
+    hn = rnd(rms_norm(x, W[pre + "pre_ff_layernorm.weight"], eps))
+    return x + swiglu_mlp(hn, W, pre, cfg, rnd)
 
 
-def forward(cfg: dict, weights: dict, tokens, dtype=np.float64) -> np.ndarray:
-    """Logits [T, V] of one whole sequence starting at position 0 (falcon_h1.c:256-417)."""
+def forward(cfg: dict, weights: dict, tokens, dtype=np.float64, rnd=_same) -> np.ndarray:
+    """Logits [T, V] of one whole sequence starting at position 0 (falcon_h1.c:256-417).
+    rnd: identity, or bf16_round to model a bfloat16 engine (see bf16_round)."""
     W = {k: np.asarray(v).astype(dtype) for k, v in weights.items()}
     d = derived(cfg)
     T = len(tokens)
     positions = np.arange(T)
     x = embedding(W["model.embed_tokens.weight"], tokens, _get(cfg, "embedding_multiplier", 1.0))
     for layer in range(d["L"]):
-        x = block(x, W, layer, cfg, d, positions)
-    f = rms_norm(x, W["model.final_layernorm.weight"], cfg["rms_norm_eps"])
+        x = block(x, W, layer, cfg, d, positions, rnd)
+    f = rnd(rms_norm(x, W["model.final_layernorm.weight"], cfg["rms_norm_eps"]))
     head = W["model.embed_tokens.weight"] if _get(cfg, "tie_word_embeddings", False) \
         else W["lm_head.weight"]                               # core.c:1246-1249
     return linear(f, head) * _get(cfg, "lm_head_multiplier", 1.0)

@@ -34,7 +34,7 @@ def cmp(name, args_cpu, outs, tol_of=None):
     getattr(ops_plain, name)(*args_cpu)
     for i in outs:
         ref, got = args_cpu[i].double(), args_gpu[i].cpu().double()
-        tol = (tol_of or TOL[args_cpu[i].dtype]) * max(1e-6, ref.abs().max().item())
+        tol = (tol_of if tol_of is not None else TOL[args_cpu[i].dtype]) * max(1e-6, ref.abs().max().item())
         err = (ref - got).abs().max().item()
         assert err <= tol, f"{name}: output {i} differs by {err:.3e} (allowed {tol:.3e})"
 
@@ -79,8 +79,9 @@ def test_gated_rmsnorm(dtype, groups, before, with_w):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_swiglu(dtype):
     g = gen(3)
-    gu = rnd(g, 9, 2 * 77, dtype=DT[dtype], scale=2.0)
-    cmp("swiglu", [gu, torch.empty(9, 77, dtype=DT[dtype])], [1])
+    for in_dt in (torch.float32, DT[dtype]):
+        gu = rnd(g, 9, 2 * 77, dtype=in_dt, scale=2.0)
+        cmp("swiglu", [gu, torch.empty(9, 77, dtype=DT[dtype])], [1])
 
 
 @pytest.mark.parametrize("a_dt,w_dt,o_dt", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),
@@ -142,7 +143,7 @@ def test_rope_kv_store(dtype, H, KV, hd, rope):
     slots, table, k_pages, v_pages = _paged_setup(g, 3, [s + n for s, n in zip(starts, lens)], KV, hd, DT[dtype])
     T = sum(lens)
     width = (H + 2 * KV) * hd
-    qkv = rnd(g, T, width + 5, dtype=DT[dtype])
+    qkv = rnd(g, T, width + 5, dtype=torch.float32 if H != 4 else DT[dtype])
     inv = (1.0 / torch.pow(torch.tensor(1e6, dtype=torch.float64),
                            torch.arange(rope // 2, dtype=torch.float64) * 2 / max(rope, 1))).float()
     args = [qkv[:, 2:2 + width], 0, H * hd, (H + KV) * hd, torch.empty(T, H * hd, dtype=DT[dtype]), k_pages, v_pages,

@@ -16,22 +16,26 @@ import tinyllama_c_b200 as tlc
 from tinyllama_c_b200.engine import StepEntry
 
 import configs
-from helpers import make_model_dir, plain_logits, random_tokens, read_config, read_weights
+from helpers import make_model_dir, plain_logits, random_tokens, read_config, read_weights, record, release_all
 from plain import falcon_h1_plain as plain
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 # Largest allowed |engine - plain| as a fraction of the largest |logit| of the request.
-# float32: accumulation order only.  bfloat16: activations are rounded to 8 bits of mantissa
-# (2^-9 relative each) at about six places per layer; errors add up like a random walk.
-TOL = {"float32": 1e-4, "bfloat16": 4e-2}
-MEAN_TOL = {"float32": 2e-5, "bfloat16": 8e-3}
+# float32 is compared with the exact plain implementation: accumulation order only.
+# bfloat16 is compared with the plain implementation's model of a bfloat16 engine (the same
+# values rounded at the same places); what remains is 32-bit accumulation order, which now and
+# then tips one rounding of a matrix-product input by 2^-8 of its value.
+TOL = {"float32": 1e-4, "bfloat16": 1.5e-2}
+MEAN_TOL = {"float32": 2e-5, "bfloat16": 2e-3}
 
 
 def check(got, want, dtype, what):
     scale = np.abs(want).max()
     err = np.abs(got - want)
+    record(dtype, "max", err.max() / (TOL[dtype] * scale))
+    record(dtype, "mean", err.mean() / (MEAN_TOL[dtype] * scale))
     assert err.max() <= TOL[dtype] * scale, f"{what}: max error {err.max():.3e} of scale {scale:.3e}"
     assert err.mean() <= MEAN_TOL[dtype] * scale, f"{what}: mean error {err.mean():.3e} of scale {scale:.3e}"
 
@@ -49,18 +53,20 @@ def engines(folders):
     def get(name, dtype):
         if (name, dtype) not in cache:
             cache[(name, dtype)] = tlc.LLM(folders[name], dtype=dtype, max_tokens=64 * 24, max_seqs=4)
+        release_all(cache[(name, dtype)])
         return cache[(name, dtype)]
     return get
 
 
 @pytest.fixture(scope="module")
 def requests_of(folders):
-    """Per configuration: five requests of unequal lengths and the plain logits of each."""
+    """(configuration, dtype) -> five requests of unequal lengths and the plain logits of each."""
     out = {}
     for name, cfg in configs.ALL.items():
         lens = [1, 40, 9, 150, 97]
         toks = [random_tokens(cfg["vocab_size"], n, 50 + i) for i, n in enumerate(lens)]
-        out[name] = (toks, [plain_logits(folders[name], t) for t in toks])
+        for dtype in ("float32", "bfloat16"):
+            out[(name, dtype)] = (toks, [plain_logits(folders[name], t, dtype) for t in toks])
     return out
 
 
@@ -68,7 +74,7 @@ def requests_of(folders):
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_each_request_alone_and_whole(engines, requests_of, name, dtype):
     llm = engines(name, dtype)
-    for toks, want in zip(*requests_of[name]):
+    for toks, want in zip(*requests_of[(name, dtype)]):
         s = llm.cache.acquire()
         got = llm.step([StepEntry(s, toks, list(range(len(toks))))]).cpu().numpy()
         llm.cache.release(s)
@@ -80,7 +86,7 @@ def test_each_request_alone_and_whole(engines, requests_of, name, dtype):
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_last_32_tokens_one_by_one(engines, requests_of, name, dtype):
     llm = engines(name, dtype)
-    for toks, want in zip(*requests_of[name]):
+    for toks, want in zip(*requests_of[(name, dtype)]):
         n = len(toks)
         head = max(1, n - 32)
         s = llm.cache.acquire()
@@ -100,7 +106,7 @@ def test_unequal_batches_with_slot_reuse(engines, requests_of, name, dtype):
     """Two batches one after the other on a cache of 4 slots; in each, prompts (all but the last
     k tokens) run in one step, then one token each; shorter requests end earlier."""
     llm = engines(name, dtype)
-    toks, want = requests_of[name]
+    toks, want = requests_of[(name, dtype)]
     for batch in ([0, 1, 2, 3], [4, 2, 1]):
         slots = {i: llm.cache.acquire() for i in batch}
         decode = {i: min(len(toks[i]) - 1, 3 + 5 * k) for k, i in enumerate(batch)}     # unequal decode lengths
@@ -108,7 +114,12 @@ def test_unequal_batches_with_slot_reuse(engines, requests_of, name, dtype):
         got = llm.step([StepEntry(slots[i], toks[i][:cut[i]], [0, cut[i] - 1]) for i in batch]).cpu().numpy()
         for r, i in enumerate(batch):
             check(got[2 * r:2 * r + 2], want[i][[0, cut[i] - 1]], dtype, f"{name} batch prefill of request {i}")
-        live = list(batch)
+        live = []
+        for i in batch:                                   # a request whose prompt was all of it ends here
+            if cut[i] < len(toks[i]):
+                live.append(i)
+            else:
+                llm.cache.release(slots[i])
         k = 0
         while live:
             ents = [StepEntry(slots[i], [toks[i][cut[i] + k]], [0]) for i in live]
@@ -130,7 +141,7 @@ def test_long_decoding(engines, folders, dtype):
     """A 3-token prompt followed by 200 single-token steps (crosses three pages)."""
     llm = engines("A", dtype)
     toks = random_tokens(configs.TINY_A["vocab_size"], 203, 77)
-    want = plain_logits(folders["A"], toks)
+    want = plain_logits(folders["A"], toks, dtype)
     s = llm.cache.acquire()
     rows = [llm.step([StepEntry(s, toks[:3], [0, 1, 2])]).cpu().numpy()]
     for t in toks[3:]:
@@ -144,7 +155,7 @@ def test_long_decoding(engines, folders, dtype):
 def test_first_tokens_of_a_sequence(engines, requests_of, name, dtype):
     """Token by token from the very first one: the conv window and the state start empty."""
     llm = engines(name, dtype)
-    toks, want = requests_of[name][0][1][:8], requests_of[name][1][1][:8]
+    toks, want = requests_of[(name, dtype)][0][1][:8], requests_of[(name, dtype)][1][1][:8]
     s = llm.cache.acquire()
     rows = [llm.step([StepEntry(s, [t], [0])]).cpu().numpy() for t in toks]
     llm.cache.release(s)
@@ -164,7 +175,7 @@ def test_peaked_attention_over_a_far_key(tmp_path, dtype):
             w[k] = (w[k].float() * 4.0).to(w[k].dtype)
     save_file(w, os.path.join(d, "model.safetensors"))
     toks = random_tokens(cfg["vocab_size"], 230, 91)
-    want = plain_logits(d, toks)
+    want = plain_logits(d, toks, dtype)
     llm = tlc.LLM(d, dtype=dtype, max_tokens=512, max_seqs=2)
     s = llm.cache.acquire()
     rows = [llm.step([StepEntry(s, toks[:190], list(range(190)))]).cpu().numpy()]
@@ -183,9 +194,10 @@ def test_greedy_generation_through_the_entry_point(engines, folders, name, dtype
     assert llm.cache.slots.n_held == 0
     w = read_weights(folders[name])
     c = read_config(folders[name])
+    rnd = plain.bf16_round if dtype == "bfloat16" else plain._same
     for p, r in zip(prompts, res):
         assert len(r.tokens) == 10 and r.finish_reason == "length"
-        ref = plain.forward(c, w, (p + r.tokens)[:-1])
+        ref = plain.forward(c, w, (p + r.tokens)[:-1], rnd=rnd)
         for k, tok in enumerate(r.tokens):
             row = ref[len(p) - 1 + k]
             best = int(np.argmax(row))
@@ -216,7 +228,7 @@ def test_generation_stops_and_samples_reproducibly(engines):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_as_a_program(folders, requests_of, tmp_path, dtype):
-    toks, want = requests_of["B"]
+    toks, want = requests_of[("B", dtype)]
     out = str(tmp_path / "out")
     steps = [{"step": 0, "entries": [{"id": "r1", "tokens": toks[1][:30], "want": [0, 29]},
                                      {"id": "r2", "tokens": toks[2][:8], "want": [7]}], "end": []}]

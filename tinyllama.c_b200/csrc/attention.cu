@@ -12,8 +12,8 @@
 #include "common.cuh"
 
 // ---- rope + store -----------------------------------------------------------------------
-template <typename T>
-__global__ void rope_kv_store_kernel(const T* __restrict__ qkv, int ld, int q_off, int k_off, int v_off,
+template <typename TI, typename T>
+__global__ void rope_kv_store_kernel(const TI* __restrict__ qkv, int ld, int q_off, int k_off, int v_off,
                                      T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
                                      const float* __restrict__ inv_freq, int rope_dim,
                                      const int* __restrict__ positions, const int* __restrict__ row_seq,
@@ -22,14 +22,14 @@ __global__ void rope_kv_store_kernel(const T* __restrict__ qkv, int ld, int q_of
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = rope_dim >> 1;
-  const T* row = qkv + (size_t)t * ld;
+  const TI* row = qkv + (size_t)t * ld;
   const int n_heads_total = H + 2 * KV;
   int page = -1;
   if (write_kv) page = block_table[(size_t)slots[row_seq[t]] * max_pages + pos / TLC_PAGE];
   const int prow = pos % TLC_PAGE;
   for (int idx = threadIdx.x; idx < n_heads_total * hd; idx += blockDim.x) {
     const int head = idx / hd, d = idx % hd;
-    const T* src;
+    const TI* src;
     int kind;  // 0 q, 1 k, 2 v
     int h;
     if (head < H) { kind = 0; h = head; src = row + q_off + (size_t)h * hd; }
@@ -55,15 +55,15 @@ __global__ void rope_kv_store_kernel(const T* __restrict__ qkv, int ld, int q_of
   }
 }
 
-extern "C" int tlc_rope_kv_store(const void* qkv, int dtype, int ld, int q_off, int k_off, int v_off, void* q_out,
+extern "C" int tlc_rope_kv_store(const void* qkv, int in_dtype, int dtype, int ld, int q_off, int k_off, int v_off, void* q_out,
                                  void* k_pages, void* v_pages, const float* inv_freq, int rope_dim,
                                  const int* positions, const int* row_seq, const int* slots, const int* block_table,
                                  int max_pages, int T, int H, int KV, int hd, int write_kv, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(rope_dim % 2 == 0 && rope_dim <= hd, "rope: rotated width %d must be even and at most head_dim %d", rope_dim, hd);
-  TLC_DISPATCH_DTYPE(dtype, TT, rope_kv_store_kernel<TT><<<T, 256, 0, stream>>>(
-      (const TT*)qkv, ld, q_off, k_off, v_off, (TT*)q_out, (TT*)k_pages, (TT*)v_pages, inv_freq, rope_dim, positions,
-      row_seq, slots, block_table, max_pages, H, KV, hd, write_kv));
+  TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, rope_kv_store_kernel<TI, TT><<<T, 256, 0, stream>>>(
+      (const TI*)qkv, ld, q_off, k_off, v_off, (TT*)q_out, (TT*)k_pages, (TT*)v_pages, inv_freq, rope_dim, positions,
+      row_seq, slots, block_table, max_pages, H, KV, hd, write_kv)));
   TLC_CHECK_LAUNCH("rope_kv_store");
   return 0;
 }

@@ -105,8 +105,8 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int
 }
 
 // ---- SwiGLU product: out = silu(gate) * up, gate|up side by side in one row ---------------
-template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total) {
+template <typename TI, typename T>
+__global__ void swiglu_kernel(const TI* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t t = i / F;
@@ -115,11 +115,13 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, int ld, int F, T* __rest
   out[i] = from_f32<T>(silu_f(g) * u);
 }
 
-extern "C" int tlc_swiglu(const void* gu, int dtype, int ld, int F, int T, void* out, cudaStream_t stream) {
+extern "C" int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype,
+                          cudaStream_t stream) {
   const size_t total = (size_t)T * F;
   if (total == 0) return 0;
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  TLC_DISPATCH_DTYPE(dtype, TT, swiglu_kernel<TT><<<blocks, 256, 0, stream>>>((const TT*)gu, ld, F, (TT*)out, total));
+  TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, swiglu_kernel<TI, TT><<<blocks, 256, 0, stream>>>(
+      (const TI*)gu, ld, F, (TT*)out, total)));
   TLC_CHECK_LAUNCH("swiglu");
   return 0;
 }

@@ -23,10 +23,10 @@ _SIGNATURES = {
     "tlc_embed": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp],
     "tlc_rmsnorm": [_vp, _vp, _vp, _f, _i, _i, _vp, _i, _vp],
     "tlc_gated_rmsnorm": [_vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _vp],
-    "tlc_swiglu": [_vp, _i, _i, _i, _i, _vp, _vp],
+    "tlc_swiglu": [_vp, _i, _i, _i, _i, _vp, _i, _vp],
     "tlc_gather_rows": [_vp, _vp, _i, _i, _vp, _vp],
     "tlc_linear_simt": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
-    "tlc_rope_kv_store": [_vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+    "tlc_rope_kv_store": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                           _i, _vp],
     "tlc_attention": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "tlc_mamba_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
@@ -157,10 +157,10 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _gpu(gate_up, out)
     T, F2 = gate_up.shape
     F = F2 // 2
-    if out.dtype != gate_up.dtype or not out.is_contiguous() or tuple(out.shape) != (T, F) or F2 != 2 * F:
-        raise KernelError("swiglu: out must be contiguous [T, F] of the input's type")
+    if not out.is_contiguous() or tuple(out.shape) != (T, F) or F2 != 2 * F:
+        raise KernelError("swiglu: out must be contiguous [T, F]")
     _call("tlc_swiglu", gate_up.data_ptr(), dtype_code(gate_up.dtype), _rows(gate_up, "gate_up"), F, T,
-          out.data_ptr(), _stream())
+          out.data_ptr(), dtype_code(out.dtype), _stream())
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
@@ -201,13 +201,14 @@ def rope_kv_store(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: 
     T = qkv.shape[0]
     for t, n in ((positions, "positions"), (row_seq, "row_seq"), (slots, "slots"), (block_table, "block_table")):
         _i32(t, n)
-    if q_out.dtype != qkv.dtype or k_pages.dtype != qkv.dtype or v_pages.dtype != qkv.dtype:
-        raise KernelError("rope_kv_store: q, the pages and the projection must share one element type")
+    if k_pages.dtype != q_out.dtype or v_pages.dtype != q_out.dtype:
+        raise KernelError("rope_kv_store: q and the pages must share one element type")
     if not q_out.is_contiguous() or tuple(q_out.shape) != (T, H * hd) or not k_pages.is_contiguous() \
             or not v_pages.is_contiguous() or tuple(k_pages.shape[1:]) != (KV, PAGE, hd):
         raise KernelError("rope_kv_store: q_out must be contiguous [T, H*hd], pages contiguous [n, KV, 64, hd]")
     _f32vec(inv_freq, inv_freq.numel(), "rope inv_freq")
-    _call("tlc_rope_kv_store", qkv.data_ptr(), dtype_code(qkv.dtype), _rows(qkv, "qkv"), q_off, k_off, v_off,
+    _call("tlc_rope_kv_store", qkv.data_ptr(), dtype_code(qkv.dtype), dtype_code(q_out.dtype), _rows(qkv, "qkv"),
+          q_off, k_off, v_off,
           q_out.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), inv_freq.data_ptr(), 2 * inv_freq.numel(),
           positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(), block_table.data_ptr(), block_table.shape[1],
           T, H, KV, hd, int(bool(write_kv)), _stream())

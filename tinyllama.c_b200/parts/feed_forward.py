@@ -37,7 +37,7 @@ class SwiGLU(Part):
 
     def forward(self, normed: torch.Tensor, residual: torch.Tensor) -> None:
         T = normed.shape[0]
-        gu = act_empty((T, 2 * self.F), normed)
+        gu = act_empty((T, 2 * self.F), normed, torch.float32)
         self.gate_up.forward(normed, gu)
         act = act_empty((T, self.F), normed)
         ops.swiglu(gu, act)

@@ -53,7 +53,7 @@ class AttentionMixer(Part):
     def forward(self, normed: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor) -> None:
         T = step.n_rows
         kv = cache.kv[self.cache_key]
-        qkv = act_empty((T, self.qkv.out_features), normed)
+        qkv = act_empty((T, self.qkv.out_features), normed, torch.float32)
         self.qkv.forward(normed, qkv)
         q = act_empty((T, self.H * self.hd), normed)
         self.position.rotate_and_store(qkv, self.q_off, self.k_off, self.v_off, q, kv, step, self.H, self.KV, self.hd,

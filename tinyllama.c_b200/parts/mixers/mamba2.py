@@ -79,7 +79,7 @@ class Mamba2Mixer(Part):
         T, f32 = step.n_rows, torch.float32
         conv_state = cache.state[self.cache_key + ".conv"]
         ssm_state = cache.state[self.cache_key + ".ssm"]
-        proj = act_empty((T, self.in_proj.out_features), normed)
+        proj = act_empty((T, self.in_proj.out_features), normed, f32)
         self.in_proj.forward(normed, proj)
         xbc = act_empty((T, self.Cd), normed, f32)
         dt = act_empty((T, self.Hs), normed, f32)
