@@ -87,7 +87,8 @@ def test_swiglu(dtype):
 @pytest.mark.parametrize("a_dt,w_dt,o_dt", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),
                                             ("bfloat16", "bfloat16", "float32"), ("bfloat16", "float32", "bfloat16")])
 @pytest.mark.parametrize("M,N,K", [(1, 130, 72), (5, 67, 200), (16, 64, 64), (17, 129, 100), (150, 70, 257),
-                                   (8, 96, 1024)])
+                                   (8, 96, 1024), (17, 130, 72), (129, 257, 200), (300, 128, 64), (64, 1000, 1096),
+                                   (2048, 384, 512)])
 def test_linear(a_dt, w_dt, o_dt, M, N, K):
     g = gen(4)
     a_full = rnd(g, M, K + 8, dtype=DT[a_dt])
@@ -102,6 +103,8 @@ def test_linear(a_dt, w_dt, o_dt, M, N, K):
                        None if bias is None else bias.cuda(), accumulate)
             untouched = out_cpu[:, N:].clone()
             ops_plain.linear(a_full[:, :K], w, out_cpu[:, :N], scale, bias, accumulate)
+            torch.cuda.synchronize()
+            ops.check_errors()
             ref, got = out_cpu[:, :N].double(), out_gpu.cpu()[:, :N].double()
             tol = TOL[DT[o_dt]] * ref.abs().max().item() * (2 if a_dt == "float32" else 1)
             assert (ref - got).abs().max().item() <= tol

@@ -1,0 +1,347 @@
+// bfloat16 linear layers on the 5th-generation tensor cores (sm_100a):
+//   out[m, n] (+)= (sum_k a[m, k] * w[n, k]) * colscale[n] + colbias[n],  32-bit accumulation.
+//
+// The reference multiplies with hand-written kernels of its own: FP32 FMA tiles
+// (gpu.cu:1542, matmul_kernel_tiled) and a warp-per-row product (gpu.cu:1008); it has no
+// tensor-core path for 16-bit weights.  This file is the B200 form of the same product:
+//   * both operands are K-major ([rows, K] with K contiguous), so TMA
+//     (cp.async.bulk.tensor.2d, 128-byte swizzle) stages [128 x 64] tiles of each into a
+//     ring of shared-memory buffers; out-of-range rows and the K tail arrive as zeros;
+//   * one elected thread issues tcgen05.mma (M=128, N=BN, K=16 per instruction) with the
+//     accumulator [128 x BN] in tensor memory, and tcgen05.commit hands each ring slot
+//     back to the loader;
+//   * four warps read the accumulator back with tcgen05.ld (each warp its 32 lanes = rows)
+//     and apply the epilogue in registers: column scale, column bias, optional add into
+//     the 32-bit residual, store as bfloat16 or float32.
+// Warp roles: 0 = TMA loader, 1 = MMA issuer and owner of the tensor-memory allocation,
+// 2..5 = epilogue.  Every wait on an mbarrier is bounded; a wait that runs out records an
+// error code that the host reads, and the kernel frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+extern "C" int tlc_linear_simt(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,
+                               int out_dtype, int ldo, const float* colscale, const float* colbias, int accumulate,
+                               int M, int N, int K, cudaStream_t stream);
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // about a second
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false (and the error code recorded) if the phase does not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try(bar, parity)) {
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      atomicExch(err, code);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle:
+// start address >> 4 in bits 0-13, leading byte offset (unused for this layout) in 16-29,
+// stride byte offset = 1024 bytes (8 rows) >> 4 in 32-45, descriptor version 1 at bit 46,
+// swizzle mode 2 (128 bytes) in bits 61-63.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+// Instruction descriptor, kind::f16: D format f32 (bits 4-5 = 1), A and B bfloat16
+// (bits 7-9 = 1, 10-12 = 1), both K-major (bits 15, 16 = 0), N >> 3 in 17-22, M >> 4 in 24-28.
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN, int STAGES>
+struct Smem {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int TILES = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int TOTAL = TILES + (2 * STAGES + 1) * 8 + 16 + 1024;   // + barriers + tmem slot + alignment slack
+};
+
+template <typename TO, int BN, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
+                    const float* __restrict__ colbias, int accumulate, int M, int N, int K, int* err) {
+  using S = Smem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* a_tiles = smem;
+  uint8_t* b_tiles = smem + STAGES * S::A_BYTES;
+  uint64_t* bars = (uint64_t*)(smem + S::TILES);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), done_bar = smem_u32(bars + 2 * STAGES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int num_k = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    mbar_init(done_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {   // the whole warp allocates BN columns of tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {                                   // ---- TMA loader ----
+      int issued = 0;
+      bool ok = true;
+      for (int k = 0; k < num_k && ok; k++) {
+        const int s = k % STAGES;
+        const uint32_t ph = (k / STAGES) & 1;
+        ok = mbar_wait(empty0 + 8 * s, ph ^ 1, err, 1);
+        if (!ok) break;
+        mbar_expect_tx(full0 + 8 * s, S::A_BYTES + S::B_BYTES);
+        tma_load_2d(smem_u32(a_tiles + s * S::A_BYTES), &map_a, full0 + 8 * s, k * BK, m0);
+        tma_load_2d(smem_u32(b_tiles + s * S::B_BYTES), &map_b, full0 + 8 * s, k * BK, n0);
+        issued = k + 1;
+      }
+      if (!ok || *(volatile int*)err != 0) {
+        // something went wrong elsewhere: let the copies still in flight land before the block exits
+        for (int k = max(0, issued - STAGES); k < issued; k++)
+          mbar_wait(full0 + 8 * (k % STAGES), (k / STAGES) & 1, err, 4);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {                                   // ---- MMA issuer ----
+      constexpr uint32_t idesc = instr_desc(BM, BN);
+      bool ok = true;
+      for (int k = 0; k < num_k && ok; k++) {
+        const int s = k % STAGES;
+        const uint32_t ph = (k / STAGES) & 1;
+        ok = mbar_wait(full0 + 8 * s, ph, err, 2);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_u32(a_tiles + s * S::A_BYTES), b_addr = smem_u32(b_tiles + s * S::B_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BK / UMMA_K; kk++)
+          umma(tmem, smem_desc(a_addr + kk * UMMA_K * 2), smem_desc(b_addr + kk * UMMA_K * 2), idesc,
+               (k > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(empty0 + 8 * s);                   // the slot is free once these MMAs have read it
+      }
+      umma_commit(done_bar);                           // the accumulator is complete
+    }
+  } else {                                             // ---- epilogue, warps 2..5 ----
+    const bool ok = mbar_wait(done_bar, 0, err, 3);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int quarter = warp & 3;                      // a warp may touch lanes 32*(warp%4) .. +31 only
+    const int m = m0 + quarter * 32 + lane;
+    if (ok) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c++) {
+        uint32_t r[32];
+        tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
+        if (m < M) {
+          TO* orow = out + (size_t)m * ldo;
+#pragma unroll
+          for (int j = 0; j < 32; j++) {
+            const int n = n0 + c * 32 + j;
+            if (n < N) {
+              float v = __uint_as_float(r[j]);
+              if (colscale) v *= colscale[n];
+              if (colbias) v += colbias[n];
+              if (accumulate) v += to_f32(orow[n]);
+              orow[n] = from_f32<TO>(v);
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+}
+
+// ---- host side ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled g_encode = nullptr;
+int* g_err_dev = nullptr;     // device view of a host-mapped error word
+int* g_err_host = nullptr;
+std::mutex g_mu;
+
+struct MapKey {
+  const void* p; int rows, k, ld, box_rows;
+  bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && k == o.k && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.p;
+    for (int v : {k.rows, k.k, k.ld, k.box_rows}) h = h * 1000003u ^ (size_t)v;
+    return h;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;
+
+template <typename TO, int BN, int STAGES>
+int configure() {
+  if (cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           Smem<BN, STAGES>::TOTAL) != cudaSuccess)
+    return tlc_fail(-2, "linear: cannot reserve %d bytes of shared memory", Smem<BN, STAGES>::TOTAL);
+  return 0;
+}
+
+int init_once() {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_encode) return 0;
+  if (int rc = configure<float, 128, 6>()) return rc;
+  if (int rc = configure<__nv_bfloat16, 128, 6>()) return rc;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn)
+    return tlc_fail(-3, "linear: the CUDA driver does not export cuTensorMapEncodeTiled");
+  if (cudaHostAlloc((void**)&g_err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+      cudaHostGetDevicePointer((void**)&g_err_dev, g_err_host, 0) != cudaSuccess)
+    return tlc_fail(-3, "linear: cannot allocate the error word");
+  *g_err_host = 0;
+  g_encode = (EncodeTiled)fn;
+  return 0;
+}
+
+int get_map(const void* p, int rows, int k, int ld, int box_rows, CUtensorMap* out) {
+  MapKey key{p, rows, k, ld, box_rows};
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) { *out = it->second; return 0; }
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(p), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return tlc_fail(-3, "linear: cuTensorMapEncodeTiled failed with %d (rows %d, k %d, ld %d)", (int)r, rows, k, ld);
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps[key] = m;
+  *out = m;
+  return 0;
+}
+
+template <typename TO, int BN, int STAGES>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, const float* colscale, const float* colbias,
+           int accumulate, int M, int N, int K, cudaStream_t stream) {
+  using S = Smem<BN, STAGES>;
+  auto kern = gemm_tcgen05_kernel<TO, BN, STAGES>;
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  kern<<<grid, THREADS, S::TOTAL, stream>>>(ma, mb, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, g_err_dev);
+  TLC_CHECK_LAUNCH("linear(tcgen05)");
+  return 0;
+}
+
+}  // namespace
+
+// Error word of the tensor-core kernels: 0, or which bounded wait ran out
+// (1 loader, 2 MMA issuer, 3 epilogue, 4 drain).  Reading it does not synchronise.
+extern "C" int tlc_linear_error() { return g_err_host ? *(volatile int*)g_err_host : 0; }
+extern "C" void tlc_linear_error_clear() { if (g_err_host) *g_err_host = 0; }
+
+// Prepares everything that must not happen inside a stream capture (driver entry point, the
+// error word, shared-memory attributes).  Called once when the library is loaded.
+extern "C" int tlc_linear_init() { return init_once(); }
+
+extern "C" int tlc_linear_tcgen05_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int K) {
+  return a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
+         ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0);
+}
+
+// The linear layer of the library: tensor cores where the operands allow it, CUDA cores otherwise.
+extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,
+                          int out_dtype, int ldo, const float* colscale, const float* colbias, int accumulate, int M,
+                          int N, int K, int min_rows_for_tensor_cores, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (M < min_rows_for_tensor_cores || !tlc_linear_tcgen05_ok(a_dtype, lda, a, w_dtype, ldw, w, K))
+    return tlc_linear_simt(a, a_dtype, lda, w, w_dtype, ldw, out, out_dtype, ldo, colscale, colbias, accumulate, M, N, K,
+                           stream);
+  TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N, K,
+              lda, ldw, ldo);
+  if (int rc = init_once()) return rc;
+  CUtensorMap ma, mb;
+  constexpr int BN = 128, STAGES = 6;
+  if (int rc = get_map(a, M, K, lda, BM, &ma)) return rc;
+  if (int rc = get_map(w, N, K, ldw, BN, &mb)) return rc;
+  if (out_dtype == TLC_F32)
+    return launch<float, BN, STAGES>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  if (out_dtype == TLC_BF16)
+    return launch<__nv_bfloat16, BN, STAGES>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
+}

@@ -9,6 +9,7 @@ cannot be built, the call raises.  Parts of the model call these through the mod
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -26,6 +27,7 @@ _SIGNATURES = {
     "tlc_swiglu": [_vp, _i, _i, _i, _i, _vp, _i, _vp],
     "tlc_gather_rows": [_vp, _vp, _i, _i, _vp, _vp],
     "tlc_linear_simt": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
+    "tlc_linear": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "tlc_rope_kv_store": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                           _i, _vp],
     "tlc_attention": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
@@ -52,7 +54,10 @@ def library() -> ctypes.CDLL:
             fn.argtypes = argtypes
             fn.restype = ctypes.c_int
         lib.tlc_last_error.restype = ctypes.c_char_p
+        lib.tlc_linear_error.restype = ctypes.c_int
         _lib = lib
+        if torch.cuda.is_available() and lib.tlc_linear_init() != 0:     # before any stream capture
+            raise KernelError(f"tlc_linear_init: {lib.tlc_last_error().decode()}")
     return _lib
 
 
@@ -172,6 +177,21 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
 
 
 # ---- linear -----------------------------------------------------------------------------
+# Fewest rows for which bfloat16 products go to the tensor-core kernel; below it the weight
+# matrix is streamed once by the warp-per-column kernel.  TLC_TENSOR_CORE_MIN_ROWS overrides
+# it (a huge value keeps everything on the CUDA cores).
+TENSOR_CORE_MIN_ROWS = int(os.environ.get("TLC_TENSOR_CORE_MIN_ROWS", "17"))
+
+
+def check_errors() -> None:
+    """Raises if a tensor-core kernel gave up on a bounded wait (does not synchronise)."""
+    code = library().tlc_linear_error()
+    if code:
+        library().tlc_linear_error_clear()
+        raise KernelError(f"a tensor-core linear kernel gave up waiting (code {code}: 1 loader, 2 issuer, "
+                          f"3 epilogue, 4 drain); its output is incomplete")
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale: Optional[torch.Tensor] = None,
            colbias: Optional[torch.Tensor] = None, accumulate: bool = False) -> None:
     """out[m, n] (+)= (sum_k a[m, k] w[n, k]) * colscale[n] + colbias[n].
@@ -185,9 +205,10 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale: Option
         raise KernelError(f"linear: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
     _f32vec(colscale, N, "linear colscale")
     _f32vec(colbias, N, "linear colbias")
-    _call("tlc_linear_simt", a.data_ptr(), dtype_code(a.dtype), _rows(a, "linear input"), w.data_ptr(),
+    _call("tlc_linear", a.data_ptr(), dtype_code(a.dtype), _rows(a, "linear input"), w.data_ptr(),
           dtype_code(w.dtype), _rows(w, "linear weight"), out.data_ptr(), dtype_code(out.dtype),
-          _rows(out, "linear output"), _p(colscale), _p(colbias), int(bool(accumulate)), M, N, K, _stream())
+          _rows(out, "linear output"), _p(colscale), _p(colbias), int(bool(accumulate)), M, N, K,
+          TENSOR_CORE_MIN_ROWS, _stream())
 
 
 # ---- attention -------------------------------------------------------------------------------
