@@ -1,0 +1,268 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of Falcon-H1 (1.5B layer sizes, random weights) on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+A step is one decode step of the whole batch (8 sequences by default, each continuing a
+512-token prompt; the cache is sized for the 4096-token benchmark context).  The line
+printed is one JSON object:
+  value      decoded tokens per second, timed on the device (CUDA events around K replayed steps
+             of the engine's captured decode step, sampling included)
+  e2e        the same through the Python entry point LLM.generate(): host token ids in, host
+             token ids out, every step copying its inputs from pinned memory and reading its
+             result back
+  prefill    one 2,048-token prompt: tokens per second, milliseconds, fraction of the bf16 peak
+  roofline   bytes a decode step has to read (every weight once + the live cache) / its time,
+             against the measured HBM bandwidth
+  points     decode at batch 1 and 64
+The reference publishes no Falcon-H1 number and runs the model on the CPU only
+(falcon_h1.c:78-83), so vs_baseline is null; --impl reference reports why it is unavailable.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Falcon-H1-1.5B layer sizes (context 4096, tied embeddings, muP multipliers set)
+CONFIG_1P5B = dict(
+    architectures=["FalconH1ForCausalLM"], model_type="falcon_h1", vocab_size=65536, hidden_size=2048,
+    num_hidden_layers=24, num_attention_heads=8, num_key_value_heads=2, head_dim=128, intermediate_size=4096,
+    rope_theta=1e11, max_position_embeddings=4096, rms_norm_eps=1e-5, tie_word_embeddings=True,
+    mamba_d_ssm=3072, mamba_n_heads=48, mamba_d_head=64, mamba_n_groups=1, mamba_d_state=256, mamba_d_conv=4,
+    mamba_chunk_size=128, mamba_conv_bias=True, mamba_proj_bias=False, mamba_rms_norm=True,
+    mamba_norm_before_gate=False, embedding_multiplier=5.66, lm_head_multiplier=0.039, key_multiplier=0.39,
+    attention_in_multiplier=1.0, attention_out_multiplier=0.94, ssm_in_multiplier=1.25, ssm_out_multiplier=0.24,
+    mlp_multipliers=[0.88, 0.3], ssm_multipliers=[0.35, 0.25, 0.7, 0.5, 0.35])
+FULL_LAYERS = 24
+
+
+def peaks():
+    p = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            m = json.load(open(path))
+            p = dict(hbm_gbs=float(m.get("hbm_gbs", p["hbm_gbs"])), bf16_tflops=float(m.get("bf16_tflops", p["bf16_tflops"])),
+                     source="measured")
+        except Exception:
+            pass
+    return p
+
+
+def sizes(cfg):
+    D, F, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    H, KV, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    Di, Hs, N, G, K = cfg["mamba_d_ssm"], cfg["mamba_n_heads"], cfg["mamba_d_state"], cfg["mamba_n_groups"], cfg["mamba_d_conv"]
+    Cd = Di + 2 * G * N
+    Pd = Di + Cd + Hs
+    layer_w = D * (H * hd + 2 * KV * hd) + H * hd * D + D * Pd + Di * D + 2 * D * F + F * D
+    return dict(D=D, F=F, V=V, L=L, H=H, KV=KV, hd=hd, Di=Di, Hs=Hs, N=N, G=G, K=K, Cd=Cd, Pd=Pd, layer_w=layer_w,
+                P=Di // Hs)
+
+
+def decode_bytes(cfg, batch, context):
+    """Bytes one decode step has to read: every weight it uses once (bf16 matrices, head
+    included), and the cache of the live sequences (bf16 keys and values up to `context`,
+    the 32-bit conv window and SSM state)."""
+    s = sizes(cfg)
+    weights = (s["L"] * s["layer_w"] + s["V"] * s["D"]) * 2
+    kv = 2 * s["L"] * s["KV"] * s["hd"] * 2 * context
+    state = s["L"] * (s["Hs"] * s["P"] * s["N"] + (s["K"] - 1) * s["Cd"]) * 4
+    return weights + batch * (kv + state)
+
+
+def prefill_flops(cfg, T):
+    s = sizes(cfg)
+    gemm = 2 * T * s["L"] * s["layer_w"] + 2 * s["V"] * s["D"]          # head on one row
+    attn = s["L"] * 2 * 2 * s["H"] * s["hd"] * T * (T + 1) / 2           # QK^T and PV, causal
+    ssd = s["L"] * T * s["Hs"] * s["P"] * s["N"] * 6                       # state update + readout
+    return gemm + attn + ssd
+
+
+class Clocks:
+    """Samples nvidia-smi while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __enter__(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.p = None
+        return self
+
+    def __exit__(self, *a):
+        self.result = dict(sm_mhz=None, sm_max_mhz=None, reasons=[])
+        if self.p is None:
+            return
+        time.sleep(0.15)
+        self.p.terminate()
+        out, _ = self.p.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6 or not f[0].isdigit():
+                continue
+            sm.append(int(f[0]))
+            mx.append(int(f[1]))
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            sm.sort()
+            self.result = dict(sm_mhz=sm[len(sm) // 2], sm_max_mhz=max(mx), reasons=sorted(reasons))
+
+
+def time_decode(llm, tlc, batch, prompt_len, steps, warmup, seed):
+    """Device time of `steps` replays of the captured decode step for `batch` sequences."""
+    import torch
+    from tinyllama_c_b200 import ops
+    from tinyllama_c_b200.engine import StepEntry
+    from tinyllama_c_b200.engine.decode_graph import DecodeGraph
+    g = torch.Generator().manual_seed(seed)
+    V = llm.config.vocab_size
+    slots = [llm.cache.acquire() for _ in range(batch)]
+    prompts = torch.randint(0, V, (batch, prompt_len), generator=g).tolist()
+    # prompts in groups of 8 sequences to bound activation memory
+    for i in range(0, batch, 8):
+        llm.step([StepEntry(s, p, ()) for s, p in zip(slots[i:i + 8], prompts[i:i + 8])])
+    from tinyllama_c_b200.engine.generate import context_bucket
+    graph = DecodeGraph(llm.model, llm.cache, tlc.GREEDY, batch, context_bucket(prompt_len + max(3, warmup) + steps + 1))
+    toks = torch.randint(0, V, (batch,), generator=g).tolist()
+
+    def one():
+        nonlocal toks
+        pos = [llm.cache.reserve(s, 1) for s in slots]
+        llm.cache.upload_tables()
+        toks = graph.run(slots, toks, pos)
+        for s in slots:
+            llm.cache.commit(s, 1)
+
+    for _ in range(max(3, warmup)):
+        one()
+    torch.cuda.synchronize()
+    l0 = ops.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with Clocks() as clk:
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = ops.launch_count() - l0
+    ctx = prompt_len + max(3, warmup) + steps // 2
+    for s in slots:
+        llm.cache.release(s)
+    ops.check_errors()
+    return ms, launches, clk.result, ctx
+
+
+def time_prefill(llm, T, seed, reps=3):
+    import torch
+    from tinyllama_c_b200 import ops
+    from tinyllama_c_b200.engine import StepEntry
+    g = torch.Generator().manual_seed(seed)
+    best = None
+    for r in range(reps + 2):
+        toks = torch.randint(0, llm.config.vocab_size, (T,), generator=g).tolist()
+        s = llm.cache.acquire()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        llm.step([StepEntry(s, toks, (T - 1,))])
+        e1.record()
+        torch.cuda.synchronize()
+        llm.cache.release(s)
+        if r >= 2:
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+    ops.check_errors()
+    return best
+
+
+def e2e_decode(llm, tlc, batch, prompt_len, steps, seed):
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    prompts = torch.randint(0, llm.config.vocab_size, (batch, prompt_len), generator=g).tolist()
+    llm.generate(prompts, tlc.GREEDY, max_new_tokens=4, ignore_eos=True, max_batch=batch)      # warm-up, captures the graph
+    llm.generate(prompts, tlc.GREEDY, max_new_tokens=steps + 1, ignore_eos=True, max_batch=batch)
+    st = llm.last_stats
+    return st["decode_tokens"] / st["decode_s"], st["h2d_bytes"] // max(1, st["decode_steps"]), \
+        st["d2h_bytes"] // max(1, st["decode_steps"])
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "tinyllama.c is a C program, not a Python package (pip: neither setup.py nor pyproject.toml "
+                          "found), publishes no Falcon-H1 number and forces Falcon-H1 onto the CPU (falcon_h1.c:78-83)"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU library")
+        return 2
+
+    import torch
+    import tinyllama_c_b200 as tlc
+    cfg = dict(CONFIG_1P5B, num_hidden_layers=args.layers)
+    pk = peaks()
+    ctx_len = cfg["max_position_embeddings"]
+    model = tlc.random_model(cfg, seed=0, dtype="bfloat16")
+    # room for 64 sequences of prompt + decoded tokens, and for the 2,048-token prompt
+    llm = tlc.LLM(model, max_tokens=64 * 1024, max_seqs=64)
+
+    ms, launches, clocks, ctx = time_decode(llm, tlc, args.batch, args.prompt_len, args.steps, args.warmup, seed=1)
+    value = args.batch * 1000.0 / ms
+    nbytes = decode_bytes(cfg, args.batch, ctx)
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    e2e_v, h2d, d2h = e2e_decode(llm, tlc, args.batch, args.prompt_len, args.steps, seed=2)
+    rec = {
+        "metric": "decode tok/s at batch 8 (Falcon-H1-1.5B sizes, 512-token prompts, context 4096)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
+        "config": {"model": "Falcon-H1-1.5B sizes", "global_batch": args.batch, "seq_len": ctx_len,
+                   "prompt_len": args.prompt_len, "parallelism": "single GPU", "layers": args.layers,
+                   "layers_full": FULL_LAYERS, "hidden": cfg["hidden_size"], "heads": "8q/2kv x128",
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "mamba": "48 heads x64, state 256, groups 1, conv 4", "tied": True,
+                   "l2": "inputs larger than L2 (2.7 GB of weights per step)"},
+        "clocks": clocks, "gpu_launches": launches,
+        "e2e": {"value": round(e2e_v, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]},
+    }
+    if not args.no_points:
+        T = 2048
+        pms = time_prefill(llm, T, seed=3)
+        fl = prefill_flops(cfg, T)
+        rec["prefill"] = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
+                          "frac": round(fl / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        pts = {}
+        for b in (1, 64):
+            m, _, _, _ = time_decode(llm, tlc, b, args.prompt_len, max(8, args.steps // 2), 3, seed=4 + b)
+            pts[f"decode_b{b}"] = round(b * 1000.0 / m, 1)
+        rec["points"] = pts
+    print(json.dumps(rec))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

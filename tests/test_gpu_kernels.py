@@ -87,7 +87,7 @@ def test_swiglu(dtype):
 @pytest.mark.parametrize("a_dt,w_dt,o_dt", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),
                                             ("bfloat16", "bfloat16", "float32"), ("bfloat16", "float32", "bfloat16")])
 @pytest.mark.parametrize("M,N,K", [(1, 130, 72), (5, 67, 200), (16, 64, 64), (17, 129, 100), (150, 70, 257),
-                                   (8, 96, 1024), (17, 130, 72), (129, 257, 200), (300, 128, 64), (64, 1000, 1096),
+                                   (8, 96, 1024), (17, 130, 72), (32, 40, 136), (33, 130, 72), (9, 2048, 2048), (129, 257, 200), (300, 128, 64), (64, 1000, 1096),
                                    (2048, 384, 512)])
 def test_linear(a_dt, w_dt, o_dt, M, N, K):
     g = gen(4)
@@ -174,6 +174,20 @@ def test_attention(dtype, H, KV, hd, window):
     k_pages[b1_page, :, 3, :] *= 6.0
     cmp("attention", [q, k_pages, v_pages, table, pos, row_seq, slots, torch.empty(T, H * hd, dtype=DT[dtype]), H, KV,
                       hd, 1.0 / math.sqrt(hd), window], [7], tol_of=TOL[DT[dtype]] * 2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,hd,window", [(6, 3, 24, 0), (4, 1, 48, 0), (8, 2, 128, 0), (6, 2, 16, 37), (8, 1, 80, 170)])
+def test_attention_of_single_token_steps(dtype, H, KV, hd, window):
+    g = gen(12)
+    starts, lens = [0, 200, 63, 700, 128], [1, 1, 1, 1, 1]
+    pos, row_seq, cu, _ = _step_arrays(starts, lens)
+    slots, table, k_pages, v_pages = _paged_setup(g, 5, [s + n for s, n in zip(starts, lens)], KV, hd, DT[dtype], n_slots=6)
+    q = rnd(g, 5, H * hd, dtype=DT[dtype])
+    k_pages[int(table[int(slots[3]), 0]), :, 3, :] *= 6.0        # a far key stands out
+    for max_keys in (701, 1024):
+        cmp("attention", [q, k_pages, v_pages, table, pos, row_seq, slots, torch.empty(5, H * hd, dtype=DT[dtype]), H, KV,
+                          hd, 1.0 / math.sqrt(hd), window, max_keys], [7], tol_of=TOL[DT[dtype]] * 2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

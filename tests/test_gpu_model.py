@@ -22,22 +22,49 @@ from plain import falcon_h1_plain as plain
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
-# Largest allowed |engine - plain| as a fraction of the largest |logit| of the request.
-# float32 is compared with the exact plain implementation: accumulation order only.
-# bfloat16 is compared with the plain implementation's model of a bfloat16 engine (the same
-# values rounded at the same places); what remains is 32-bit accumulation order, which now and
-# then tips one rounding of a matrix-product input by 2^-8 of its value.
-TOL = {"float32": 1e-4, "bfloat16": 1.5e-2}
-MEAN_TOL = {"float32": 2e-5, "bfloat16": 2e-3}
+# float32 is compared with the exact plain implementation; what differs is accumulation order:
+# at most 1e-4 (mean 2e-5) of the request's largest |logit|.
+# bfloat16 is compared with the plain implementation's model of a bfloat16 engine (the same values
+# rounded to bfloat16 at the same places).  What remains is 32-bit accumulation order, which now
+# and then tips a rounding by 2^-8 of a value; the allowance is the rounding noise itself: the
+# engine must agree with the bfloat16 model at least as closely as that model agrees with exact
+# arithmetic on the same request (`Want.noise_max`, `Want.noise_mean`; measured: the engine uses
+# less than half of it).  A cache or batching fault moves logits by about their own size,
+# fifty times more.
+TOL = {"float32": 1e-4}
+MEAN_TOL = {"float32": 2e-5}
+
+
+class Want(np.ndarray):
+    """Expected logits [T, V] that carry the request's allowance in absolute units."""
+
+    def __new__(cls, arr, noise_max, noise_mean):
+        o = np.asarray(arr).view(cls)
+        o.noise_max, o.noise_mean = float(noise_max), float(noise_mean)
+        return o
+
+    def __array_finalize__(self, obj):
+        if obj is not None:
+            self.noise_max = getattr(obj, "noise_max", None)
+            self.noise_mean = getattr(obj, "noise_mean", None)
+
+
+def expected(model_dir, toks, dtype) -> Want:
+    exact = plain_logits(model_dir, toks, "float32")
+    scale = np.abs(exact).max()
+    if dtype == "float32":
+        return Want(exact, TOL[dtype] * scale, MEAN_TOL[dtype] * scale)
+    model = plain_logits(model_dir, toks, "bfloat16")
+    noise = np.abs(model - exact)
+    return Want(model, noise.max(), noise.mean())
 
 
 def check(got, want, dtype, what):
-    scale = np.abs(want).max()
-    err = np.abs(got - want)
-    record(dtype, "max", err.max() / (TOL[dtype] * scale))
-    record(dtype, "mean", err.mean() / (MEAN_TOL[dtype] * scale))
-    assert err.max() <= TOL[dtype] * scale, f"{what}: max error {err.max():.3e} of scale {scale:.3e}"
-    assert err.mean() <= MEAN_TOL[dtype] * scale, f"{what}: mean error {err.mean():.3e} of scale {scale:.3e}"
+    err = np.abs(got - np.asarray(want))
+    record(dtype, "max", err.max() / want.noise_max)
+    record(dtype, "mean", err.mean() / want.noise_mean)
+    assert err.max() <= want.noise_max, f"{what}: max error {err.max():.3e}, allowed {want.noise_max:.3e}"
+    assert err.mean() <= want.noise_mean, f"{what}: mean error {err.mean():.3e}, allowed {want.noise_mean:.3e}"
 
 
 @pytest.fixture(scope="module")
@@ -66,7 +93,7 @@ def requests_of(folders):
         lens = [1, 40, 9, 150, 97]
         toks = [random_tokens(cfg["vocab_size"], n, 50 + i) for i, n in enumerate(lens)]
         for dtype in ("float32", "bfloat16"):
-            out[(name, dtype)] = (toks, [plain_logits(folders[name], t, dtype) for t in toks])
+            out[(name, dtype)] = (toks, [expected(folders[name], t, dtype) for t in toks])
     return out
 
 
@@ -141,7 +168,7 @@ def test_long_decoding(engines, folders, dtype):
     """A 3-token prompt followed by 200 single-token steps (crosses three pages)."""
     llm = engines("A", dtype)
     toks = random_tokens(configs.TINY_A["vocab_size"], 203, 77)
-    want = plain_logits(folders["A"], toks, dtype)
+    want = expected(folders["A"], toks, dtype)
     s = llm.cache.acquire()
     rows = [llm.step([StepEntry(s, toks[:3], [0, 1, 2])]).cpu().numpy()]
     for t in toks[3:]:
@@ -175,7 +202,7 @@ def test_peaked_attention_over_a_far_key(tmp_path, dtype):
             w[k] = (w[k].float() * 4.0).to(w[k].dtype)
     save_file(w, os.path.join(d, "model.safetensors"))
     toks = random_tokens(cfg["vocab_size"], 230, 91)
-    want = plain_logits(d, toks, dtype)
+    want = expected(d, toks, dtype)
     llm = tlc.LLM(d, dtype=dtype, max_tokens=512, max_seqs=2)
     s = llm.cache.acquire()
     rows = [llm.step([StepEntry(s, toks[:190], list(range(190)))]).cpu().numpy()]
@@ -201,7 +228,8 @@ def test_greedy_generation_through_the_entry_point(engines, folders, name, dtype
         for k, tok in enumerate(r.tokens):
             row = ref[len(p) - 1 + k]
             best = int(np.argmax(row))
-            assert tok == best or row[best] - row[tok] <= TOL[dtype] * np.abs(ref).max(), \
+            margin = 1e-4 * np.abs(ref).max() if dtype == "float32" else 0.03 * np.abs(ref).max()
+            assert tok == best or row[best] - row[tok] <= margin, \
                 f"{name} {dtype}: generated token {k} = {tok}, plain argmax {best}"
     # one request alone gives the same tokens as inside the batches (float32: exactly)
     alone = llm.generate([prompts[3]], tlc.GREEDY, max_new_tokens=10, ignore_eos=True)
@@ -244,8 +272,10 @@ def test_trace_run_as_a_program(folders, requests_of, tmp_path, dtype):
     assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(5)]
     V = configs.TINY_B["vocab_size"]
     rd = lambda i: np.fromfile(os.path.join(out, f"{i}.f32"), "<f4").reshape(-1, V)
-    check(rd(0), np.stack([want[1][0], want[1][29], want[2][7]]), dtype, "trace step 0")
-    check(rd(1), np.stack([want[1][30], want[2][8]]), dtype, "trace step 1")
+    check(rd(0)[:2], want[1][[0, 29]], dtype, "trace step 0, first request")
+    check(rd(0)[2:], want[2][7:8], dtype, "trace step 0, second request")
+    check(rd(1)[:1], want[1][30:31], dtype, "trace step 1, first request")
+    check(rd(1)[1:], want[2][8:9], dtype, "trace step 1, second request")
     assert not os.path.exists(os.path.join(out, "2.f32"))
     check(rd(3), want[1][32:33], dtype, "trace step 3")
     check(rd(4), want[4][-1:], dtype, "trace step 4")

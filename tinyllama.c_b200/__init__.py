@@ -36,15 +36,20 @@ class LLM:
     rounded up to 64); max_seqs the number of live sequences (default: as many as max_tokens
     allows, at most 256)."""
 
-    def __init__(self, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", max_tokens: int = 8192,
-                 max_seqs: Optional[int] = None, device: str = "cuda:0"):
+    def __init__(self, model_dir, dtype: Union[str, torch.dtype] = "bfloat16", max_tokens: int = 8192,
+                 max_seqs: Optional[int] = None, device: str = "cuda:0", use_graphs: bool = True):
+        """model_dir: a folder with config.json and model.safetensors, or a model that is
+        already bound to its weights on `device` (see random_model)."""
         if not torch.cuda.is_available():
             raise RuntimeError("tinyllama.c_b200 needs a CUDA device (NVIDIA B200); there is no CPU path")
         from . import ops
         ops.library()                                   # build / load the kernels now, loudly
         torch.cuda.set_device(torch.device(device))
-        self.model = load_model(model_dir, dtype, device)
+        self.model = load_model(model_dir, dtype, device) if isinstance(model_dir, (str, bytes)) else model_dir
         self.config = self.model.config
+        self.use_graphs = use_graphs
+        self._graphs: dict = {}
+        self.last_stats: dict = {}
         n_pages = (int(max_tokens) + 63) // 64
         self.max_seqs = int(max_seqs) if max_seqs else max(1, min(n_pages, 256))
         self.cache = Cache(self.model.cache_requests(), max_tokens, self.max_seqs, self.model.dtype, device)
@@ -59,5 +64,38 @@ class LLM:
         """Token ids in, token ids out (host lists)."""
         if stop_ids is None:
             stop_ids = getattr(self.config, "stop_token_ids", ())
-        backend = EngineBackend(self.model, self.cache, params)
-        return generate(backend, prompts, max_new_tokens, stop_ids, max_batch, self.max_context, ignore_eos)
+        backend = EngineBackend(self.model, self.cache, params, self._graphs, self.use_graphs)
+        try:
+            return generate(backend, prompts, max_new_tokens, stop_ids, max_batch, self.max_context, ignore_eos)
+        finally:
+            self.last_stats = backend.stats
+
+
+def random_model(config: dict, seed: int = 0, dtype: Union[str, torch.dtype] = "bfloat16", device: str = "cuda:0",
+                 std: Optional[float] = None):
+    """A model with random weights drawn on the device (no folder is written): for benchmarks
+    of configurations too large to be worth a round trip through a file."""
+    from .config import config_from_dict
+    from .weights.loader import run_dtype
+    cfg = config_from_dict(dict(config))
+    model = build_model(cfg)
+    rd = run_dtype(dtype)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    std = float(std if std is not None else getattr(cfg, "initializer_range", 0.02))
+    tensors = {}
+    for s in model.weight_specs():
+        if s.init in ("normal", "conv"):
+            t = torch.empty(s.shape, dtype=torch.float32, device=device).normal_(0.0, std, generator=gen).to(rd)
+        elif s.init in ("ones", "d_skip"):
+            t = 1.0 + torch.empty(s.shape, dtype=torch.float32, device=device).normal_(0.0, 0.1, generator=gen)
+        elif s.init == "a_log":
+            t = torch.log(1.0 + 15.0 * torch.rand(s.shape, generator=gen, device=device))
+        elif s.init == "dt_bias":
+            step = torch.exp(torch.rand(s.shape, generator=gen, device=device) * 4.605170186 - 6.907755279)
+            t = step + torch.log(-torch.expm1(-step))
+        else:
+            t = torch.zeros(s.shape, dtype=rd, device=device)
+        tensors[s.name] = t
+    model.bind(tensors, rd, torch.device(device))
+    return model

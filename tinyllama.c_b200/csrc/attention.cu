@@ -151,3 +151,126 @@ extern "C" int tlc_attention(const void* q, int dtype, const void* k_pages, cons
   TLC_CHECK_LAUNCH("attention");
   return 0;
 }
+
+// ---- attention for one-token steps: keys split across blocks ------------------------------------
+// A decode step has one query row per sequence and hundreds or thousands of keys.  The grid is
+// (row, kv head, split): a block scores 128 keys of its sequence for all query heads that share
+// the kv head (keys and values are read once per group), and writes an unnormalised partial
+// output with its running maximum and sum; a second kernel merges the splits.  The split count
+// of the grid is an upper bound from the host; a block whose keys lie past the row's length or
+// before its window exits at once, so the same launch serves any lengths (and a captured graph).
+#define DEC_KEYS 128
+#define DEC_MAXG 8
+template <typename T>
+__global__ void __launch_bounds__(DEC_KEYS)
+attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                                const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
+                                const int* __restrict__ row_seq, const int* __restrict__ slots, float* __restrict__ part_o,
+                                float* __restrict__ part_ml, int H, int KV, int hd, float scale, int window, int n_splits) {
+  extern __shared__ float sh[];
+  const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+  const int G = H / KV;
+  const int pos = positions[t];
+  const int n_keys = pos + 1;
+  const int start = (window > 0 && n_keys > window) ? n_keys - window : 0;
+  const int k0 = split * DEC_KEYS;
+  float* ml = part_ml + (((size_t)t * H + (size_t)g * G) * n_splits + split) * 2;   // + hg * n_splits * 2
+  if (k0 >= n_keys || k0 + DEC_KEYS <= start) {
+    if (threadIdx.x < G) { ml[(size_t)threadIdx.x * n_splits * 2] = -INFINITY; ml[(size_t)threadIdx.x * n_splits * 2 + 1] = 0.f; }
+    return;
+  }
+  float* qs = sh;                          // [G][hd]
+  float* ps = sh + (size_t)G * hd;         // [G][DEC_KEYS]
+  float* red = ps + (size_t)G * DEC_KEYS;  // [33]
+  const int* table = block_table + (size_t)slots[row_seq[t]] * max_pages;
+  for (int i = threadIdx.x; i < G * hd; i += blockDim.x)
+    qs[i] = to_f32(q[((size_t)t * H + (size_t)g * G) * hd + i]) * scale;
+  __syncthreads();
+  const int kp = k0 + threadIdx.x;
+  const bool valid = kp >= start && kp < n_keys;
+  float s[DEC_MAXG];
+#pragma unroll
+  for (int hg = 0; hg < DEC_MAXG; hg++) s[hg] = 0.f;
+  if (valid) {
+    const T* kr = k_pages + (((size_t)table[kp / TLC_PAGE] * KV + g) * TLC_PAGE + kp % TLC_PAGE) * hd;
+    for (int d = 0; d < hd; d++) {
+      const float kv = to_f32(kr[d]);
+#pragma unroll
+      for (int hg = 0; hg < DEC_MAXG; hg++)
+        if (hg < G) s[hg] = fmaf(kv, qs[hg * hd + d], s[hg]);
+    }
+  }
+  // per head: maximum and sum over the block's keys
+  for (int hg = 0; hg < G; hg++) {
+    const float sv = valid ? s[hg] : -INFINITY;
+    float m = warp_max(sv);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    const float p = valid ? expf(sv - m) : 0.f;
+    ps[hg * DEC_KEYS + threadIdx.x] = p;
+    const float l = block_sum(p, red);
+    if (threadIdx.x == 0) { ml[(size_t)hg * n_splits * 2] = m; ml[(size_t)hg * n_splits * 2 + 1] = l; }
+  }
+  __syncthreads();
+  const int nk = min(DEC_KEYS, n_keys - k0);
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc[DEC_MAXG];
+#pragma unroll
+    for (int hg = 0; hg < DEC_MAXG; hg++) acc[hg] = 0.f;
+    for (int j = 0; j < nk; j++) {
+      const int kj = k0 + j;
+      const float vv = to_f32(v_pages[(((size_t)table[kj / TLC_PAGE] * KV + g) * TLC_PAGE + kj % TLC_PAGE) * hd + d]);
+#pragma unroll
+      for (int hg = 0; hg < DEC_MAXG; hg++)
+        if (hg < G) acc[hg] = fmaf(ps[hg * DEC_KEYS + j], vv, acc[hg]);
+    }
+#pragma unroll
+    for (int hg = 0; hg < DEC_MAXG; hg++)
+      if (hg < G) part_o[((((size_t)t * H + (size_t)g * G + hg) * n_splits) + split) * hd + d] = acc[hg];
+  }
+}
+
+template <typename T>
+__global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              T* __restrict__ out, int hd, int n_splits) {
+  const size_t th = blockIdx.x;                       // row * H + head
+  const float* ml = part_ml + th * n_splits * 2;
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
+  float l = 0.f;
+  for (int s = 0; s < n_splits; s++) if (ml[2 * s + 1] > 0.f) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
+  const float inv = 1.0f / l;
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_splits; s++)
+      if (ml[2 * s + 1] > 0.f) acc = fmaf(part_o[(th * n_splits + s) * hd + d], expf(ml[2 * s] - m), acc);
+    out[th * hd + d] = from_f32<T>(acc * inv);
+  }
+}
+
+// scratch: part_o [T, H, n_splits, hd] and part_ml [T, H, n_splits, 2] floats, n_splits = ceil(max_keys / 128)
+extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_pages, const void* v_pages,
+                                    const int* block_table, int max_pages, const int* positions, const int* row_seq,
+                                    const int* slots, void* out, float* part_o, float* part_ml, int T, int H, int KV,
+                                    int hd, float scale, int window, int max_keys, cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(KV > 0 && H % KV == 0, "attention: %d heads are not a multiple of %d key/value heads", H, KV);
+  TLC_REQUIRE(H / KV <= DEC_MAXG, "attention(decode): %d query heads per key/value head exceed the kernel's limit of %d", H / KV, DEC_MAXG);
+  TLC_REQUIRE(KV <= 65535, "attention(decode): too many key/value heads (%d)", KV);
+  const int n_splits = (max_keys + DEC_KEYS - 1) / DEC_KEYS;
+  TLC_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention(decode): %d keys are outside the kernel's range", max_keys);
+  const int G = H / KV;
+  const size_t smem = ((size_t)G * hd + (size_t)G * DEC_KEYS + 33) * sizeof(float);
+  TLC_REQUIRE(smem <= 48 * 1024, "attention(decode): head size %d with %d heads per group needs too much shared memory", hd, G);
+  dim3 grid(T, KV, n_splits);
+  TLC_DISPATCH_DTYPE(dtype, TT, {
+    attention_decode_partial_kernel<TT><<<grid, DEC_KEYS, smem, stream>>>(
+        (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, part_o,
+        part_ml, H, KV, hd, scale, window, n_splits);
+    attention_decode_merge_kernel<TT><<<T * H, 128, 0, stream>>>(part_o, part_ml, (TT*)out, hd, n_splits);
+  });
+  TLC_CHECK_LAUNCH("attention(decode)");
+  return 0;
+}

@@ -180,3 +180,124 @@ extern "C" int tlc_linear_simt(const void* a, int a_dtype, int lda, const void* 
       return (launch_simt<TA, TW, TO>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K, stream)))));
   return 0;
 }
+
+// ---- few rows, bfloat16, tensor cores as the reducer ----------------------------------------
+// A decode step multiplies up to a few dozen rows by every weight matrix; the time is the time
+// to stream the weights once.  One block owns 16 output columns (= 16 weight rows); its four
+// warps take interleaved 32-wide slices of K.  Each lane reads 16 contiguous bytes of two
+// weight rows (g, g+8) and of one activation row per group of 8 rows, and feeds them to
+// mma.sync.m16n8k16 with the weight rows as the M side and the activation rows as the N side.
+// The contraction index is permuted the same way on both sides (a lane's 8 contiguous values
+// serve two instructions), which a dot product does not notice.  Accumulators stay in
+// registers; the four warps' partial sums meet in shared memory.
+template <int MG> struct SkinnyAcc { float d[MG][2][4]; };
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename TO, int MG>
+__global__ void __launch_bounds__(128)
+gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
+                       TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
+                       const float* __restrict__ colbias, int accumulate, int M, int N, int K) {
+  __shared__ float red[3][MG][32][4];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int n0 = blockIdx.x * 16;
+  const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);     // clamped rows are never stored
+  const uint4* w0 = reinterpret_cast<const uint4*>(w + (size_t)r0 * ldw);
+  const uint4* w1 = reinterpret_cast<const uint4*>(w + (size_t)r1 * ldw);
+  float acc[MG][4];
+#pragma unroll
+  for (int i = 0; i < MG; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+  const int K8 = K >> 3;                                             // 16-byte chunks per row
+  const int n_steps = (K8 + 3) >> 2;                                 // a step is 4 chunks = 32 values of K
+  constexpr int U = 4;                                               // steps in flight per warp
+  for (int s0 = warp * U; s0 < n_steps; s0 += 4 * U) {
+    uint4 wa[U], wb[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int c = (s0 + u) * 4 + t;
+      const bool in = (s0 + u) < n_steps && c < K8;
+      wa[u] = in ? __ldg(w0 + c) : make_uint4(0, 0, 0, 0);
+      wb[u] = in ? __ldg(w1 + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int c = (s0 + u) * 4 + t;
+      const bool in = (s0 + u) < n_steps && c < K8;
+#pragma unroll
+      for (int mg = 0; mg < MG; mg++) {
+        const int row = mg * 8 + g;
+        uint4 xb = make_uint4(0, 0, 0, 0);
+        if (in && row < M) xb = *(reinterpret_cast<const uint4*>(a + (size_t)row * lda) + c);
+        mma_bf16_16816(acc[mg], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xb.x, xb.y);
+        mma_bf16_16816(acc[mg], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xb.z, xb.w);
+      }
+    }
+  }
+  if (warp > 0) {
+#pragma unroll
+    for (int mg = 0; mg < MG; mg++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) red[warp - 1][mg][lane][j] = acc[mg][j];
+  }
+  __syncthreads();
+  if (warp == 0) {
+#pragma unroll
+    for (int mg = 0; mg < MG; mg++) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        float v = acc[mg][j] + red[0][mg][lane][j] + red[1][mg][lane][j] + red[2][mg][lane][j];
+        const int n = n0 + g + (j >= 2 ? 8 : 0);
+        const int m = mg * 8 + 2 * t + (j & 1);
+        if (n < N && m < M) {
+          if (colscale) v *= colscale[n];
+          if (colbias) v += colbias[n];
+          TO* o = out + (size_t)m * ldo + n;
+          if (accumulate) v += to_f32(*o);
+          *o = from_f32<TO>(v);
+        }
+      }
+    }
+  }
+}
+
+template <typename TO>
+static int launch_skinny_mma(const void* a, int lda, const void* w, int ldw, void* out, int ldo, const float* colscale,
+                             const float* colbias, int accumulate, int M, int N, int K, cudaStream_t stream) {
+  const unsigned blocks = (unsigned)((N + 15) / 16);
+  const __nv_bfloat16* ap = (const __nv_bfloat16*)a;
+  const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
+  if (M <= 8)
+    gemm_skinny_mma_kernel<TO, 1><<<blocks, 128, 0, stream>>>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K);
+  else if (M <= 16)
+    gemm_skinny_mma_kernel<TO, 2><<<blocks, 128, 0, stream>>>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K);
+  else
+    gemm_skinny_mma_kernel<TO, 4><<<blocks, 128, 0, stream>>>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K);
+  TLC_CHECK_LAUNCH("linear(skinny mma)");
+  return 0;
+}
+
+// bfloat16 operands with 16-byte aligned rows and at most 32 rows: the weight-streaming kernel.
+extern "C" int tlc_linear_skinny_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int M, int K) {
+  return a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && M <= 32 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
+         ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0);
+}
+
+extern "C" int tlc_linear_skinny(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
+                                 const float* colscale, const float* colbias, int accumulate, int M, int N, int K,
+                                 cudaStream_t stream) {
+  if (out_dtype == TLC_F32)
+    return launch_skinny_mma<float>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  if (out_dtype == TLC_BF16)
+    return launch_skinny_mma<__nv_bfloat16>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
+}

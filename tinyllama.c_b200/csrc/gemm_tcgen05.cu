@@ -25,6 +25,11 @@ extern "C" int tlc_linear_simt(const void* a, int a_dtype, int lda, const void* 
                                int out_dtype, int ldo, const float* colscale, const float* colbias, int accumulate,
                                int M, int N, int K, cudaStream_t stream);
 
+extern "C" int tlc_linear_skinny_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int M, int K);
+extern "C" int tlc_linear_skinny(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
+                                 const float* colscale, const float* colbias, int accumulate, int M, int N, int K,
+                                 cudaStream_t stream);
+
 namespace {
 
 constexpr int BM = 128;
@@ -329,6 +334,11 @@ extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, in
                           int out_dtype, int ldo, const float* colscale, const float* colbias, int accumulate, int M,
                           int N, int K, int min_rows_for_tensor_cores, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
+  if (M < min_rows_for_tensor_cores && tlc_linear_skinny_ok(a_dtype, lda, a, w_dtype, ldw, w, M, K)) {
+    TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N,
+                K, lda, ldw, ldo);
+    return tlc_linear_skinny(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  }
   if (M < min_rows_for_tensor_cores || !tlc_linear_tcgen05_ok(a_dtype, lda, a, w_dtype, ldw, w, K))
     return tlc_linear_simt(a, a_dtype, lda, w, w_dtype, ldw, out, out_dtype, ldo, colscale, colbias, accumulate, M, N, K,
                            stream);

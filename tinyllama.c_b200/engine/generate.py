@@ -29,10 +29,14 @@ class GenerationResult:
 class EngineBackend:
     """The real backend: the model, its cache and the GPU sampler."""
 
-    def __init__(self, model, cache, params: SamplingParams):
+    def __init__(self, model, cache, params: SamplingParams, graphs: Optional[dict] = None, use_graphs: bool = True):
         from ..sampling.sampler import Sampler
-        self.model, self.cache = model, cache
+        self.model, self.cache, self.params = model, cache, params
         self.sampler = Sampler(params, model.device)
+        self.graphs = graphs if graphs is not None else {}        # (params, batch size) -> DecodeGraph
+        self.use_graphs = use_graphs and model.device.type == "cuda"
+        self.stats = dict(prefill_s=0.0, prefill_tokens=0, decode_s=0.0, decode_steps=0, decode_tokens=0,
+                          h2d_bytes=0, d2h_bytes=0)
 
     def acquire(self) -> int:
         return self.cache.acquire()
@@ -48,10 +52,60 @@ class EngineBackend:
     def step_and_sample(self, entries, histories, sequence_ids, steps) -> List[int]:
         """entries: (slot, tokens) pairs; logits are taken at each entry's last token.
         Returns the next token of every entry (host integers)."""
+        import time
+        from ..sampling.sampler import uniform
         from .step import StepEntry, step
-        logits = step(self.model, self.cache, [StepEntry(s, t, (len(t) - 1,)) for s, t in entries])
-        tokens = self.sampler.sample(logits, histories, sequence_ids, steps)
-        return tokens.cpu().tolist()
+        t0 = time.perf_counter()
+        decode = all(len(t) == 1 for _, t in entries)
+        if decode and self.use_graphs:
+            out = self._graph_step(entries, histories, sequence_ids, steps, uniform)
+        else:
+            logits = step(self.model, self.cache, [StepEntry(s, t, (len(t) - 1,)) for s, t in entries])
+            out = self.sampler.sample(logits, histories, sequence_ids, steps).cpu().tolist()
+        dt = time.perf_counter() - t0
+        n = sum(len(t) for _, t in entries)
+        if decode:
+            self.stats["decode_s"] += dt
+            self.stats["decode_steps"] += 1
+            self.stats["decode_tokens"] += n
+        else:
+            self.stats["prefill_s"] += dt
+            self.stats["prefill_tokens"] += n
+        return out
+
+    MAX_GRAPHS = 24
+
+    def _graph_step(self, entries, histories, sequence_ids, steps, uniform) -> List[int]:
+        """A one-token step through the captured graph of this batch size."""
+        from .. import ops
+        from .decode_graph import DecodeGraph
+        B = len(entries)
+        slots = [s for s, _ in entries]
+        positions = [self.cache.reserve(s, 1) for s in slots]
+        bucket = context_bucket(max(positions) + 1)
+        key = (self.params, B, bucket)
+        g = self.graphs.get(key)
+        if g is None:
+            if len(self.graphs) >= self.MAX_GRAPHS:
+                self.graphs.pop(next(iter(self.graphs)))
+            g = self.graphs[key] = DecodeGraph(self.model, self.cache, self.params, B, bucket)
+        self.cache.upload_tables()
+        u = [uniform(self.params.seed, i, t) for i, t in zip(sequence_ids, steps)] if g.work is not None else None
+        out = g.run(slots, [t[0] for _, t in entries], positions, u, histories)
+        for s in slots:
+            self.cache.commit(s, 1)
+        ops.check_errors()
+        self.stats["h2d_bytes"] += g.h2d_bytes
+        self.stats["d2h_bytes"] += g.d2h_bytes
+        return out
+
+
+def context_bucket(n: int) -> int:
+    """Sequence lengths share a captured graph up to the next power of two (at least 512)."""
+    b = 512
+    while b < n:
+        b *= 2
+    return b
 
 
 def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_batch: int, free_slots: int,

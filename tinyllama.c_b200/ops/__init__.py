@@ -31,6 +31,7 @@ _SIGNATURES = {
     "tlc_rope_kv_store": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                           _i, _vp],
     "tlc_attention": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
+    "tlc_attention_decode": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
     "tlc_mamba_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
                        _i, _i, _vp],
     "tlc_ssm_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
@@ -61,8 +62,24 @@ def library() -> ctypes.CDLL:
     return _lib
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel-launching library calls were made (captured calls count once at capture;
+    a graph replay adds its calls through count_launches)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += int(n)
+
+
 def _call(name: str, *args) -> None:
+    global _launches
     lib = library()
+    _launches += 1
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise KernelError(f"{name}: {lib.tlc_last_error().decode()}")
@@ -180,7 +197,7 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
 # Fewest rows for which bfloat16 products go to the tensor-core kernel; below it the weight
 # matrix is streamed once by the warp-per-column kernel.  TLC_TENSOR_CORE_MIN_ROWS overrides
 # it (a huge value keeps everything on the CUDA cores).
-TENSOR_CORE_MIN_ROWS = int(os.environ.get("TLC_TENSOR_CORE_MIN_ROWS", "17"))
+TENSOR_CORE_MIN_ROWS = int(os.environ.get("TLC_TENSOR_CORE_MIN_ROWS", "33"))
 
 
 def check_errors() -> None:
@@ -237,14 +254,24 @@ def rope_kv_store(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: 
 
 def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
               positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, H: int, KV: int,
-              hd: int, scale: float, window: int = 0) -> None:
+              hd: int, scale: float, window: int = 0, decode_max_keys: int = 0) -> None:
     """Causal grouped-query attention of every row over its sequence's pages (keys 0..position,
-    or the last `window` of them)."""
+    or the last `window` of them).  decode_max_keys > 0 says that the rows are single-token
+    steps of sequences no longer than that: keys are then split across blocks."""
     _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out)
     T = q.shape[0]
     if not q.is_contiguous() or not out.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.shape != q.shape \
             or out.dtype != q.dtype or k_pages.dtype != q.dtype:
         raise KernelError("attention: q and out must be contiguous [T, H*hd] of the pages' type")
+    if decode_max_keys > 0 and H // KV <= 8:
+        n_splits = (int(decode_max_keys) + 127) // 128
+        part_o = torch.empty((T, H, n_splits, hd), dtype=torch.float32, device=q.device)
+        part_ml = torch.empty((T, H, n_splits, 2), dtype=torch.float32, device=q.device)
+        _call("tlc_attention_decode", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
+              block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(),
+              slots.data_ptr(), out.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), T, H, KV, hd, float(scale),
+              int(window or 0), int(decode_max_keys), _stream())
+        return
     _call("tlc_attention", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(),
           out.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), _stream())
