@@ -221,6 +221,7 @@ attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k
     for (int hg = 0; hg < DEC_MAXG; hg++) acc[hg] = 0.f;
     for (int j = 0; j < nk; j++) {
       const int kj = k0 + j;
+      if (kj < start) continue;            // outside the window: its page may have been given back
       const float vv = to_f32(v_pages[(((size_t)table[kj / TLC_PAGE] * KV + g) * TLC_PAGE + kj % TLC_PAGE) * hd + d]);
 #pragma unroll
       for (int hg = 0; hg < DEC_MAXG; hg++)
@@ -229,6 +230,124 @@ attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k
 #pragma unroll
     for (int hg = 0; hg < DEC_MAXG; hg++)
       if (hg < G) part_o[((((size_t)t * H + (size_t)g * G + hg) * n_splits) + split) * hd + d] = acc[hg];
+  }
+}
+
+// bfloat16 with a head size of 64, 128 or 256: 16-byte loads.  Scoring: a thread per key reads
+// its key row in 16-byte pieces.  Values: hd/8 lanes cover a value row, 128/(hd/8) keys are
+// in flight at a time, and the groups' partial outputs meet in shared memory.
+template <int HD>
+__global__ void __launch_bounds__(DEC_KEYS)
+attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
+                                    const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table,
+                                    int max_pages, const int* __restrict__ positions, const int* __restrict__ row_seq,
+                                    const int* __restrict__ slots, float* __restrict__ part_o,
+                                    float* __restrict__ part_ml, int H, int KV, float scale, int window, int n_splits) {
+  extern __shared__ float sh[];
+  constexpr int DL = HD / 8;                 // lanes per value row
+  constexpr int GROUPS = DEC_KEYS / DL;      // value rows in flight
+  const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
+  const int G = H / KV;
+  const int pos = positions[t];
+  const int n_keys = pos + 1;
+  const int start = (window > 0 && n_keys > window) ? n_keys - window : 0;
+  const int k0 = split * DEC_KEYS;
+  float* ml = part_ml + (((size_t)t * H + (size_t)g * G) * n_splits + split) * 2;
+  if (k0 >= n_keys || k0 + DEC_KEYS <= start) {
+    if (threadIdx.x < G) { ml[(size_t)threadIdx.x * n_splits * 2] = -INFINITY; ml[(size_t)threadIdx.x * n_splits * 2 + 1] = 0.f; }
+    return;
+  }
+  float* qs = sh;                                   // [G][HD]
+  float* ps = qs + (size_t)G * HD;                  // [G][DEC_KEYS]
+  float* red = ps + (size_t)G * DEC_KEYS;           // [36]
+  float* os = red + 36;                             // [GROUPS][G][HD]
+  __shared__ int pages[DEC_KEYS / TLC_PAGE + 1];
+  const int* table = block_table + (size_t)slots[row_seq[t]] * max_pages;
+  if (threadIdx.x <= DEC_KEYS / TLC_PAGE) {
+    const int pi = k0 / TLC_PAGE + threadIdx.x;
+    pages[threadIdx.x] = (pi * TLC_PAGE < n_keys) ? table[pi] : 0;
+  }
+  for (int i = threadIdx.x; i < G * HD; i += blockDim.x)
+    qs[i] = __bfloat162float(q[((size_t)t * H + (size_t)g * G) * HD + i]) * scale;
+  __syncthreads();
+  const int kp = k0 + threadIdx.x;
+  const bool valid = kp >= start && kp < n_keys;
+  float s[DEC_MAXG];
+#pragma unroll
+  for (int hg = 0; hg < DEC_MAXG; hg++) s[hg] = 0.f;
+  if (valid) {
+    const uint4* kr = reinterpret_cast<const uint4*>(
+        k_pages + (((size_t)pages[threadIdx.x / TLC_PAGE] * KV + g) * TLC_PAGE + kp % TLC_PAGE) * HD);
+#pragma unroll 4
+    for (int d8 = 0; d8 < DL; d8++) {
+      const uint4 kq = __ldg(kr + d8);
+      const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&kq);
+      float kf[8];
+#pragma unroll
+      for (int i = 0; i < 4; i++) { const float2 f = __bfloat1622float2(kb[i]); kf[2 * i] = f.x; kf[2 * i + 1] = f.y; }
+#pragma unroll
+      for (int hg = 0; hg < DEC_MAXG; hg++) {
+        if (hg < G) {
+          const float4 qa = *reinterpret_cast<const float4*>(qs + hg * HD + d8 * 8);
+          const float4 qb = *reinterpret_cast<const float4*>(qs + hg * HD + d8 * 8 + 4);
+          s[hg] = fmaf(kf[0], qa.x, s[hg]); s[hg] = fmaf(kf[1], qa.y, s[hg]);
+          s[hg] = fmaf(kf[2], qa.z, s[hg]); s[hg] = fmaf(kf[3], qa.w, s[hg]);
+          s[hg] = fmaf(kf[4], qb.x, s[hg]); s[hg] = fmaf(kf[5], qb.y, s[hg]);
+          s[hg] = fmaf(kf[6], qb.z, s[hg]); s[hg] = fmaf(kf[7], qb.w, s[hg]);
+        }
+      }
+    }
+  }
+  for (int hg = 0; hg < G; hg++) {
+    const float sv = valid ? s[hg] : -INFINITY;
+    float m = warp_max(sv);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    const float p = valid ? expf(sv - m) : 0.f;
+    ps[hg * DEC_KEYS + threadIdx.x] = p;
+    const float l = block_sum(p, red);
+    if (threadIdx.x == 0) { ml[(size_t)hg * n_splits * 2] = m; ml[(size_t)hg * n_splits * 2 + 1] = l; }
+  }
+  __syncthreads();
+  const int nk = min(DEC_KEYS, n_keys - k0);
+  const int dl = threadIdx.x % DL, grp = threadIdx.x / DL;
+  float acc[DEC_MAXG][8];
+#pragma unroll
+  for (int hg = 0; hg < DEC_MAXG; hg++)
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[hg][i] = 0.f;
+  for (int j = grp; j < nk; j += GROUPS) {
+    const int kj = k0 + j;
+    if (kj < start) continue;              // outside the window: its page may have been given back
+    const uint4 vq = __ldg(reinterpret_cast<const uint4*>(
+                               v_pages + (((size_t)pages[j / TLC_PAGE] * KV + g) * TLC_PAGE + kj % TLC_PAGE) * HD) + dl);
+    const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&vq);
+    float vf[8];
+#pragma unroll
+    for (int i = 0; i < 4; i++) { const float2 f = __bfloat1622float2(vb[i]); vf[2 * i] = f.x; vf[2 * i + 1] = f.y; }
+#pragma unroll
+    for (int hg = 0; hg < DEC_MAXG; hg++) {
+      if (hg < G) {
+        const float p = ps[hg * DEC_KEYS + j];
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[hg][i] = fmaf(p, vf[i], acc[hg][i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int hg = 0; hg < DEC_MAXG; hg++)
+    if (hg < G)
+#pragma unroll
+      for (int i = 0; i < 8; i++) os[((size_t)grp * G + hg) * HD + dl * 8 + i] = acc[hg][i];
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * HD; idx += blockDim.x) {
+    float v = 0.f;
+#pragma unroll
+    for (int gr = 0; gr < GROUPS; gr++) v += os[(size_t)gr * G * HD + idx];
+    const int hg = idx / HD, d = idx % HD;
+    part_o[((((size_t)t * H + (size_t)g * G + hg) * n_splits) + split) * HD + d] = v;
   }
 }
 
@@ -265,6 +384,21 @@ extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_page
   const size_t smem = ((size_t)G * hd + (size_t)G * DEC_KEYS + 33) * sizeof(float);
   TLC_REQUIRE(smem <= 48 * 1024, "attention(decode): head size %d with %d heads per group needs too much shared memory", hd, G);
   dim3 grid(T, KV, n_splits);
+  if (dtype == TLC_BF16 && (hd == 64 || hd == 128 || hd == 256)) {
+    const size_t vsmem = ((size_t)G * hd + (size_t)G * DEC_KEYS + 36 + (size_t)(DEC_KEYS / (hd / 8)) * G * hd) * sizeof(float);
+    if (vsmem <= 48 * 1024) {
+      const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
+      if (hd == 64)
+        attention_decode_partial_vec_kernel<64><<<grid, DEC_KEYS, vsmem, stream>>>(qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
+      else if (hd == 128)
+        attention_decode_partial_vec_kernel<128><<<grid, DEC_KEYS, vsmem, stream>>>(qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
+      else
+        attention_decode_partial_vec_kernel<256><<<grid, DEC_KEYS, vsmem, stream>>>(qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
+      attention_decode_merge_kernel<__nv_bfloat16><<<T * H, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits);
+      TLC_CHECK_LAUNCH("attention(decode)");
+      return 0;
+    }
+  }
   TLC_DISPATCH_DTYPE(dtype, TT, {
     attention_decode_partial_kernel<TT><<<grid, DEC_KEYS, smem, stream>>>(
         (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, part_o,

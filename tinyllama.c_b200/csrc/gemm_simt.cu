@@ -200,12 +200,14 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <typename TO, int MG>
-__global__ void __launch_bounds__(128)
+constexpr int SK_WARPS = 16;          // warps per block, each with its own slices of K
+
+template <typename TO, int MG, int U>
+__global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                        TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                        const float* __restrict__ colbias, int accumulate, int M, int N, int K) {
-  __shared__ float red[3][MG][32][4];
+  __shared__ float red[SK_WARPS][MG][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
@@ -219,9 +221,9 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
     for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
   const int K8 = K >> 3;                                             // 16-byte chunks per row
   const int n_steps = (K8 + 3) >> 2;                                 // a step is 4 chunks = 32 values of K
-  constexpr int U = 4;                                               // steps in flight per warp
-  for (int s0 = warp * U; s0 < n_steps; s0 += 4 * U) {
-    uint4 wa[U], wb[U];
+  // all of a warp's loads of one round are issued before the first multiply: one trip to memory
+  for (int s0 = warp * U; s0 < n_steps; s0 += SK_WARPS * U) {
+    uint4 wa[U], wb[U], x0[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int c = (s0 + u) * 4 + t;
@@ -233,55 +235,69 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
     for (int u = 0; u < U; u++) {
       const int c = (s0 + u) * 4 + t;
       const bool in = (s0 + u) < n_steps && c < K8;
+      x0[u] = (in && g < M) ? *(reinterpret_cast<const uint4*>(a + (size_t)g * lda) + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int c = (s0 + u) * 4 + t;
+      const bool in = (s0 + u) < n_steps && c < K8;
 #pragma unroll
       for (int mg = 0; mg < MG; mg++) {
-        const int row = mg * 8 + g;
-        uint4 xb = make_uint4(0, 0, 0, 0);
-        if (in && row < M) xb = *(reinterpret_cast<const uint4*>(a + (size_t)row * lda) + c);
+        uint4 xb = x0[u];
+        if (mg > 0) {
+          const int row = mg * 8 + g;
+          xb = (in && row < M) ? *(reinterpret_cast<const uint4*>(a + (size_t)row * lda) + c) : make_uint4(0, 0, 0, 0);
+        }
         mma_bf16_16816(acc[mg], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xb.x, xb.y);
         mma_bf16_16816(acc[mg], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xb.z, xb.w);
       }
     }
   }
-  if (warp > 0) {
 #pragma unroll
-    for (int mg = 0; mg < MG; mg++)
+  for (int mg = 0; mg < MG; mg++)
 #pragma unroll
-      for (int j = 0; j < 4; j++) red[warp - 1][mg][lane][j] = acc[mg][j];
-  }
+    for (int j = 0; j < 4; j++) red[warp][mg][lane][j] = acc[mg][j];
   __syncthreads();
-  if (warp == 0) {
+  // one thread per output value: sum the warps' partial sums in warp order, epilogue, store
+  for (int idx = threadIdx.x; idx < MG * 128; idx += blockDim.x) {
+    const int mg = idx >> 7, ln = (idx & 127) >> 2, j = idx & 3;
+    float v = 0.f;
 #pragma unroll
-    for (int mg = 0; mg < MG; mg++) {
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        float v = acc[mg][j] + red[0][mg][lane][j] + red[1][mg][lane][j] + red[2][mg][lane][j];
-        const int n = n0 + g + (j >= 2 ? 8 : 0);
-        const int m = mg * 8 + 2 * t + (j & 1);
-        if (n < N && m < M) {
-          if (colscale) v *= colscale[n];
-          if (colbias) v += colbias[n];
-          TO* o = out + (size_t)m * ldo + n;
-          if (accumulate) v += to_f32(*o);
-          *o = from_f32<TO>(v);
-        }
-      }
+    for (int ww = 0; ww < SK_WARPS; ww++) v += red[ww][mg][ln][j];
+    const int n = n0 + (ln >> 2) + (j >= 2 ? 8 : 0);
+    const int m = mg * 8 + 2 * (ln & 3) + (j & 1);
+    if (n < N && m < M) {
+      if (colscale) v *= colscale[n];
+      if (colbias) v += colbias[n];
+      TO* o = out + (size_t)m * ldo + n;
+      if (accumulate) v += to_f32(*o);
+      *o = from_f32<TO>(v);
     }
   }
+}
+
+template <typename TO, int MG>
+static void launch_skinny_mg(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, int ldw, TO* out, int ldo,
+                             const float* colscale, const float* colbias, int accumulate, int M, int N, int K,
+                             cudaStream_t stream) {
+  const unsigned blocks = (unsigned)((N + 15) / 16);
+  const int n_steps = ((K >> 3) + 3) >> 2;
+  if (n_steps <= SK_WARPS * 2)
+    gemm_skinny_mma_kernel<TO, MG, 2><<<blocks, SK_WARPS * 32, 0, stream>>>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+  else if (n_steps <= SK_WARPS * 4)
+    gemm_skinny_mma_kernel<TO, MG, 4><<<blocks, SK_WARPS * 32, 0, stream>>>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+  else
+    gemm_skinny_mma_kernel<TO, MG, 8><<<blocks, SK_WARPS * 32, 0, stream>>>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
 }
 
 template <typename TO>
 static int launch_skinny_mma(const void* a, int lda, const void* w, int ldw, void* out, int ldo, const float* colscale,
                              const float* colbias, int accumulate, int M, int N, int K, cudaStream_t stream) {
-  const unsigned blocks = (unsigned)((N + 15) / 16);
   const __nv_bfloat16* ap = (const __nv_bfloat16*)a;
   const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
-  if (M <= 8)
-    gemm_skinny_mma_kernel<TO, 1><<<blocks, 128, 0, stream>>>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K);
-  else if (M <= 16)
-    gemm_skinny_mma_kernel<TO, 2><<<blocks, 128, 0, stream>>>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K);
-  else
-    gemm_skinny_mma_kernel<TO, 4><<<blocks, 128, 0, stream>>>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K);
+  if (M <= 8) launch_skinny_mg<TO, 1>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  else if (M <= 16) launch_skinny_mg<TO, 2>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  else launch_skinny_mg<TO, 4>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
   TLC_CHECK_LAUNCH("linear(skinny mma)");
   return 0;
 }
