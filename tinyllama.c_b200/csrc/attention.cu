@@ -408,3 +408,44 @@ extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_page
   TLC_CHECK_LAUNCH("attention(decode)");
   return 0;
 }
+
+// ---- single-token attention for callers that cannot allocate ---------------------------------------
+// Declared in no_alloc.h (it has no counterpart in the reference).  Same kernels as
+// tlc_attention_decode; the split partials live in a fixed array of this library instead of
+// buffers the caller provides.
+#include "no_alloc.h"
+
+static __device__ __align__(256) float g_decode_scratch[TLC_NO_ALLOC_SCRATCH_FLOATS];
+static float* g_decode_scratch_addr[TLC_NO_ALLOC_MAX_DEVICES];      // device address of the array, per device
+
+extern "C" int tlc_attention_decode_no_alloc(const void* q, int dtype, const void* k_pages, const void* v_pages,
+                                             const int* block_table, int max_pages, const int* positions,
+                                             const int* row_seq, const int* slots, void* out, int T, int H, int KV,
+                                             int hd, float scale, int window, int max_keys, cudaStream_t stream) {
+  if (T == 0) return 0;
+  TLC_REQUIRE(T > 0 && H > 0 && hd > 0 && max_keys > 0, "attention(no alloc): sizes must be positive");
+  const long long n_splits = ((long long)max_keys + DEC_KEYS - 1) / DEC_KEYS;
+  const long long need = (long long)T * H * n_splits * ((long long)hd + 2);
+  TLC_REQUIRE(need <= (long long)TLC_NO_ALLOC_SCRATCH_FLOATS,
+              "attention(no alloc): %d rows x %d heads x %lld splits x (head size %d + 2) = %lld floats of partial "
+              "results exceed the built-in scratch of %d floats; use tlc_attention_decode with caller buffers",
+              T, H, n_splits, hd, need, (int)TLC_NO_ALLOC_SCRATCH_FLOATS);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return tlc_fail(-2, "attention(no alloc): cudaGetDevice: %s", cudaGetErrorString(e));
+  TLC_REQUIRE(dev >= 0 && dev < TLC_NO_ALLOC_MAX_DEVICES, "attention(no alloc): device %d is beyond the %d this library tracks",
+              dev, TLC_NO_ALLOC_MAX_DEVICES);
+  if (g_decode_scratch_addr[dev] == nullptr) {
+    // First call on this device: ask the runtime where this device's copy of the array lives.
+    // (In host code the array's name is only a handle, not an address a kernel could use.)
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_decode_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return tlc_fail(-2, "attention(no alloc): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_decode_scratch_addr[dev] = p;
+  }
+  float* part_o = g_decode_scratch_addr[dev];
+  float* part_ml = part_o + (size_t)T * H * n_splits * hd;
+  return tlc_attention_decode(q, dtype, k_pages, v_pages, block_table, max_pages, positions, row_seq, slots, out, part_o,
+                              part_ml, T, H, KV, hd, scale, window, max_keys, stream);
+}
