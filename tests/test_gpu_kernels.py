@@ -176,6 +176,22 @@ def test_attention(dtype, H, KV, hd, window):
                       hd, 1.0 / math.sqrt(hd), window], [7], tol_of=TOL[DT[dtype]] * 2)
 
 
+@pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 128, 0), (6, 3, 64, 0), (4, 4, 128, 100), (2, 1, 64, 17)])
+def test_attention_of_prompts_on_tensor_cores(H, KV, hd, window):
+    g = gen(13)
+    starts, lens = [0, 130, 63, 5, 0], [200, 70, 2, 65, 1]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    slots, table, k_pages, v_pages = _paged_setup(g, 5, [s + n for s, n in zip(starts, lens)], KV, hd, torch.bfloat16,
+                                                  n_slots=7)
+    T = sum(lens)
+    q = rnd(g, T, H * hd, dtype=torch.bfloat16)
+    k_pages[int(table[int(slots[0]), 0]), :, 5, :] *= 5.0        # a far key stands out for late rows
+    args = [q, k_pages, v_pages, table, pos, row_seq, slots, torch.empty(T, H * hd, dtype=torch.bfloat16), H, KV, hd,
+            1.0 / math.sqrt(hd), window, 0, cu, start_pos]
+    # probabilities are rounded to bfloat16 before the second product: 2^-9 of the output's scale more
+    cmp("attention", args, [7], tol_of=TOL[torch.bfloat16] * 2.5)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,KV,hd,window", [(6, 3, 24, 0), (4, 1, 48, 0), (8, 2, 128, 0), (6, 2, 16, 37), (8, 1, 80, 170)])
 def test_attention_of_single_token_steps(dtype, H, KV, hd, window):

@@ -32,6 +32,7 @@ _SIGNATURES = {
                           _i, _vp],
     "tlc_attention": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "tlc_attention_decode": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "tlc_attention_prefill": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
     "tlc_mamba_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
                        _i, _i, _vp],
     "tlc_ssm_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
@@ -57,8 +58,10 @@ def library() -> ctypes.CDLL:
         lib.tlc_last_error.restype = ctypes.c_char_p
         lib.tlc_linear_error.restype = ctypes.c_int
         _lib = lib
-        if torch.cuda.is_available() and lib.tlc_linear_init() != 0:     # before any stream capture
-            raise KernelError(f"tlc_linear_init: {lib.tlc_last_error().decode()}")
+        if torch.cuda.is_available():                                     # before any stream capture
+            for init in (lib.tlc_linear_init, lib.tlc_attention_prefill_init):
+                if init() != 0:
+                    raise KernelError(f"kernel library set-up: {lib.tlc_last_error().decode()}")
     return _lib
 
 
@@ -229,6 +232,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale: Option
 
 
 # ---- attention -------------------------------------------------------------------------------
+DISABLE_TILED_ATTENTION = bool(int(os.environ.get("TLC_DISABLE_TILED_ATTENTION", "0")))
+
 def rope_kv_store(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, k_pages: torch.Tensor,
                   v_pages: torch.Tensor, inv_freq: torch.Tensor, positions: torch.Tensor, row_seq: torch.Tensor,
                   slots: torch.Tensor, block_table: torch.Tensor, H: int, KV: int, hd: int,
@@ -254,10 +259,13 @@ def rope_kv_store(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: 
 
 def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
               positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, H: int, KV: int,
-              hd: int, scale: float, window: int = 0, decode_max_keys: int = 0) -> None:
+              hd: int, scale: float, window: int = 0, decode_max_keys: int = 0,
+              cu_seqlens: Optional[torch.Tensor] = None, start_pos: Optional[torch.Tensor] = None) -> None:
     """Causal grouped-query attention of every row over its sequence's pages (keys 0..position,
     or the last `window` of them).  decode_max_keys > 0 says that the rows are single-token
-    steps of sequences no longer than that: keys are then split across blocks."""
+    steps of sequences no longer than that: keys are then split across blocks.  With
+    cu_seqlens and start_pos (rows of a sequence are consecutive positions from start_pos) the
+    tiled tensor-core kernel serves bfloat16 heads of 64 or 128."""
     _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out)
     T = q.shape[0]
     if not q.is_contiguous() or not out.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.shape != q.shape \
@@ -271,6 +279,13 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(),
               slots.data_ptr(), out.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), T, H, KV, hd, float(scale),
               int(window or 0), int(decode_max_keys), _stream())
+        return
+    if decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
+            and hd in (64, 128) and not DISABLE_TILED_ATTENTION:
+        B = slots.numel()
+        _call("tlc_attention_prefill", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+              block_table.shape[1], cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), out.data_ptr(), B,
+              T // 64 + B, H, KV, hd, float(scale), int(window or 0), _stream())
         return
     _call("tlc_attention", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(),

@@ -61,5 +61,5 @@ class AttentionMixer(Part):
         att = act_empty((T, self.H * self.hd), normed)
         ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
                       self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
-                      step.max_context if step.max_new == 1 else 0)
+                      step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos)
         self.o.forward(att, residual, accumulate=True)
