@@ -58,12 +58,16 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: false (and the error code recorded) if the phase does not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
+// `err` points at two words: [0] in device memory (what kernels read), [1] the address of a
+// host-mapped word that is written on failure only, so that the host can look without a copy.
+struct ErrWords { int flag; int* host; };
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, ErrWords* err, int code) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try(bar, parity)) {
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-      atomicExch(err, code);
+      atomicExch(&err->flag, code);
+      *(volatile int*)err->host = code;
       return false;
     }
   }
@@ -126,35 +130,44 @@ struct Smem {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int TILES = STAGES * (A_BYTES + B_BYTES);
-  static constexpr int TOTAL = TILES + (2 * STAGES + 1) * 8 + 16 + 1024;   // + barriers + tmem slot + alignment slack
+  static constexpr int STAGING = 4 * 32 * 33 * 4;          // one padded 32x32 float tile per epilogue warp
+  static constexpr int N_BARS = 2 * STAGES + 4;            // full, empty per stage; accumulator full, empty x2
+  static constexpr int TOTAL = TILES + STAGING + N_BARS * 8 + 16 + 1024;   // + tmem slot + alignment slack
 };
 
+// Persistent: a block walks tiles blockIdx.x, blockIdx.x + gridDim.x, ... (row tiles fastest, so
+// that blocks running together share a weight tile in L2).  The shared-memory ring runs on across
+// tiles; the accumulator alternates between two halves of tensor memory so that the epilogue of
+// one tile overlaps the products of the next.
 template <typename TO, int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
-                    const float* __restrict__ colbias, int accumulate, int M, int N, int K, int* err) {
+                    const float* __restrict__ colbias, int accumulate, int M, int N, int K, ErrWords* err) {
   using S = Smem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* a_tiles = smem;
   uint8_t* b_tiles = smem + STAGES * S::A_BYTES;
-  uint64_t* bars = (uint64_t*)(smem + S::TILES);
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
-  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), done_bar = smem_u32(bars + 2 * STAGES);
+  float* staging = (float*)(smem + S::TILES);
+  uint64_t* bars = (uint64_t*)(smem + S::TILES + S::STAGING);
+  uint32_t* tmem_slot = (uint32_t*)(bars + S::N_BARS);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+  const uint32_t acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
   const int num_k = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    mbar_init(done_bar, 1);
+    for (int s = 0; s < 2; s++) { mbar_init(acc_full0 + 8 * s, 1); mbar_init(acc_empty0 + 8 * s, 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) {   // the whole warp allocates BN columns of tensor memory
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(BN)
+  if (warp == 1) {   // the whole warp allocates two accumulators of BN columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -165,74 +178,111 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {                                   // ---- TMA loader ----
-      int issued = 0;
+      int it = 0, issued = 0;
       bool ok = true;
-      for (int k = 0; k < num_k && ok; k++) {
-        const int s = k % STAGES;
-        const uint32_t ph = (k / STAGES) & 1;
-        ok = mbar_wait(empty0 + 8 * s, ph ^ 1, err, 1);
-        if (!ok) break;
-        mbar_expect_tx(full0 + 8 * s, S::A_BYTES + S::B_BYTES);
-        tma_load_2d(smem_u32(a_tiles + s * S::A_BYTES), &map_a, full0 + 8 * s, k * BK, m0);
-        tma_load_2d(smem_u32(b_tiles + s * S::B_BYTES), &map_b, full0 + 8 * s, k * BK, n0);
-        issued = k + 1;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+        for (int k = 0; k < num_k; k++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(empty0 + 8 * s, ph ^ 1, err, 1);
+          if (!ok) break;
+          mbar_expect_tx(full0 + 8 * s, S::A_BYTES + S::B_BYTES);
+          tma_load_2d(smem_u32(a_tiles + s * S::A_BYTES), &map_a, full0 + 8 * s, k * BK, m0);
+          tma_load_2d(smem_u32(b_tiles + s * S::B_BYTES), &map_b, full0 + 8 * s, k * BK, n0);
+          issued = it + 1;
+        }
       }
-      if (!ok || *(volatile int*)err != 0) {
-        // something went wrong elsewhere: let the copies still in flight land before the block exits
-        for (int k = max(0, issued - STAGES); k < issued; k++)
-          mbar_wait(full0 + 8 * (k % STAGES), (k / STAGES) & 1, err, 4);
+      if (!ok || *(volatile int*)&err->flag != 0) {
+        // something went wrong: let the copies still in flight land before the block exits
+        for (int i = max(0, issued - STAGES); i < issued; i++)
+          mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, err, 4);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {                                   // ---- MMA issuer ----
       constexpr uint32_t idesc = instr_desc(BM, BN);
+      int it = 0, local = 0;
       bool ok = true;
-      for (int k = 0; k < num_k && ok; k++) {
-        const int s = k % STAGES;
-        const uint32_t ph = (k / STAGES) & 1;
-        ok = mbar_wait(full0 + 8 * s, ph, err, 2);
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
+        const int as = local & 1;
+        ok = mbar_wait(acc_empty0 + 8 * as, ((local >> 1) & 1) ^ 1, err, 5);   // the epilogue has drained this half
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = smem_u32(a_tiles + s * S::A_BYTES), b_addr = smem_u32(b_tiles + s * S::B_BYTES);
+        const uint32_t d_tmem = tmem + (uint32_t)(as * BN);
+        for (int k = 0; k < num_k; k++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(full0 + 8 * s, ph, err, 2);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = smem_u32(a_tiles + s * S::A_BYTES), b_addr = smem_u32(b_tiles + s * S::B_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < BK / UMMA_K; kk++)
-          umma(tmem, smem_desc(a_addr + kk * UMMA_K * 2), smem_desc(b_addr + kk * UMMA_K * 2), idesc,
-               (k > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(empty0 + 8 * s);                   // the slot is free once these MMAs have read it
+          for (int kk = 0; kk < BK / UMMA_K; kk++)
+            umma(d_tmem, smem_desc(a_addr + kk * UMMA_K * 2), smem_desc(b_addr + kk * UMMA_K * 2), idesc,
+                 (k > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(empty0 + 8 * s);                 // the slot is free once these MMAs have read it
+        }
+        if (ok) umma_commit(acc_full0 + 8 * as);       // this tile's accumulator is complete
       }
-      umma_commit(done_bar);                           // the accumulator is complete
     }
   } else {                                             // ---- epilogue, warps 2..5 ----
-    const bool ok = mbar_wait(done_bar, 0, err, 3);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const int quarter = warp & 3;                      // a warp may touch lanes 32*(warp%4) .. +31 only
-    const int m = m0 + quarter * 32 + lane;
-    if (ok) {
+    float* st = staging + quarter * 32 * 33;
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
+      const int as = local & 1;
+      const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+      ok = mbar_wait(acc_full0 + 8 * as, (local >> 1) & 1, err, 3);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int mrow0 = m0 + quarter * 32;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
+        const int nc0 = n0 + c * 32;
+        if (nc0 >= N) break;
         uint32_t r[32];
-        tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
-        if (m < M) {
-          TO* orow = out + (size_t)m * ldo;
+        tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN + c * 32), r);
+        // registers (row = lane, 32 columns) -> shared (padded) -> rows of 32 consecutive columns
 #pragma unroll
-          for (int j = 0; j < 32; j++) {
-            const int n = n0 + c * 32 + j;
-            if (n < N) {
-              float v = __uint_as_float(r[j]);
-              if (colscale) v *= colscale[n];
-              if (colbias) v += colbias[n];
-              if (accumulate) v += to_f32(orow[n]);
-              orow[n] = from_f32<TO>(v);
-            }
+        for (int j = 0; j < 32; j++) st[lane * 33 + j] = __uint_as_float(r[j]);
+        __syncwarp();
+        const int n = nc0 + lane;
+        const bool n_ok = n < N;
+        const float cs = (colscale && n_ok) ? colscale[n] : 1.0f;
+        const float cb = (colbias && n_ok) ? colbias[n] : 0.0f;
+        if (accumulate) {
+          // all 32 reads of the old values are in flight before the first add
+          float old[32];
+#pragma unroll
+          for (int rr = 0; rr < 32; rr++) {
+            const int m = mrow0 + rr;
+            old[rr] = (m < M && n_ok) ? to_f32(out[(size_t)m * ldo + n]) : 0.f;
+          }
+#pragma unroll
+          for (int rr = 0; rr < 32; rr++) {
+            const int m = mrow0 + rr;
+            if (m < M && n_ok) out[(size_t)m * ldo + n] = from_f32<TO>(st[rr * 33 + lane] * cs + cb + old[rr]);
+          }
+        } else {
+#pragma unroll 8
+          for (int rr = 0; rr < 32; rr++) {
+            const int m = mrow0 + rr;
+            if (m < M && n_ok) out[(size_t)m * ldo + n] = from_f32<TO>(st[rr * 33 + lane] * cs + cb);
           }
         }
+        __syncwarp();
       }
+      // hand the accumulator half back to the MMA issuer
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * as) : "memory");
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -240,8 +290,9 @@ typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, v
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiled g_encode = nullptr;
-int* g_err_dev = nullptr;     // device view of a host-mapped error word
-int* g_err_host = nullptr;
+int g_sms = 148;
+ErrWords* g_err_dev = nullptr;   // device memory: the flag kernels read + where its host-visible copy lives
+int* g_err_host = nullptr;       // host-mapped word, written by a kernel on failure only
 std::mutex g_mu;
 
 struct MapKey {
@@ -270,14 +321,24 @@ int init_once() {
   if (g_encode) return 0;
   if (int rc = configure<float, 128, 6>()) return rc;
   if (int rc = configure<__nv_bfloat16, 128, 6>()) return rc;
+  if (int rc = configure<float, 256, 4>()) return rc;
+  if (int rc = configure<__nv_bfloat16, 256, 4>()) return rc;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+  if (g_sms <= 0) g_sms = 148;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult q;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn)
     return tlc_fail(-3, "linear: the CUDA driver does not export cuTensorMapEncodeTiled");
+  int* host_dev_view = nullptr;
   if (cudaHostAlloc((void**)&g_err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
-      cudaHostGetDevicePointer((void**)&g_err_dev, g_err_host, 0) != cudaSuccess)
-    return tlc_fail(-3, "linear: cannot allocate the error word");
+      cudaHostGetDevicePointer((void**)&host_dev_view, g_err_host, 0) != cudaSuccess ||
+      cudaMalloc((void**)&g_err_dev, sizeof(ErrWords)) != cudaSuccess)
+    return tlc_fail(-3, "linear: cannot allocate the error words");
   *g_err_host = 0;
+  ErrWords init{0, host_dev_view};
+  if (cudaMemcpy(g_err_dev, &init, sizeof(init), cudaMemcpyHostToDevice) != cudaSuccess)
+    return tlc_fail(-3, "linear: cannot initialise the error words");
   g_encode = (EncodeTiled)fn;
   return 0;
 }
@@ -307,7 +368,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, con
            int accumulate, int M, int N, int K, cudaStream_t stream) {
   using S = Smem<BN, STAGES>;
   auto kern = gemm_tcgen05_kernel<TO, BN, STAGES>;
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  dim3 grid(tiles < g_sms ? tiles : g_sms);
   kern<<<grid, THREADS, S::TOTAL, stream>>>(ma, mb, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, g_err_dev);
   TLC_CHECK_LAUNCH("linear(tcgen05)");
   return 0;
@@ -318,11 +380,18 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, con
 // Error word of the tensor-core kernels: 0, or which bounded wait ran out
 // (1 loader, 2 MMA issuer, 3 epilogue, 4 drain).  Reading it does not synchronise.
 extern "C" int tlc_linear_error() { return g_err_host ? *(volatile int*)g_err_host : 0; }
-extern "C" void tlc_linear_error_clear() { if (g_err_host) *g_err_host = 0; }
+extern "C" void tlc_linear_error_clear() {
+  if (g_err_host) *g_err_host = 0;
+  if (g_err_dev) cudaMemset(&g_err_dev->flag, 0, sizeof(int));
+}
 
 // Prepares everything that must not happen inside a stream capture (driver entry point, the
 // error word, shared-memory attributes).  Called once when the library is loaded.
 extern "C" int tlc_linear_init() { return init_once(); }
+
+// Test hook: 0 = choose the tile width from the sizes, 128 or 256 = force it.
+static int g_tile_override = 0;
+extern "C" void tlc_linear_tile_override(int bn) { g_tile_override = bn; }
 
 extern "C" int tlc_linear_tcgen05_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int K) {
   return a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
@@ -346,12 +415,17 @@ extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, in
               lda, ldw, ldo);
   if (int rc = init_once()) return rc;
   CUtensorMap ma, mb;
-  constexpr int BN = 128, STAGES = 6;
+  if (out_dtype != TLC_F32 && out_dtype != TLC_BF16) return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
   if (int rc = get_map(a, M, K, lda, BM, &ma)) return rc;
-  if (int rc = get_map(w, N, K, ldw, BN, &mb)) return rc;
-  if (out_dtype == TLC_F32)
-    return launch<float, BN, STAGES>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
-  if (out_dtype == TLC_BF16)
-    return launch<__nv_bfloat16, BN, STAGES>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
-  return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
+  // 256-wide tiles halve the shared-memory traffic per flop; 128-wide ones fill the GPU when the product is small
+  const long long tiles256 = (long long)((N + 255) / 256) * ((M + BM - 1) / BM);
+  const bool wide = tiles256 >= 2LL * g_sms && g_tile_override != 128;
+  if (wide || g_tile_override == 256) {
+    if (int rc = get_map(w, N, K, ldw, 256, &mb)) return rc;
+    return out_dtype == TLC_F32 ? launch<float, 256, 4>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream)
+                                : launch<__nv_bfloat16, 256, 4>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  }
+  if (int rc = get_map(w, N, K, ldw, 128, &mb)) return rc;
+  return out_dtype == TLC_F32 ? launch<float, 128, 6>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream)
+                              : launch<__nv_bfloat16, 128, 6>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
 }
