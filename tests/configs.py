@@ -25,4 +25,13 @@ TINY_B = dict(
 TINY_C = dict(TINY_B, mamba_rms_norm=True, mamba_norm_before_gate=True, sliding_window=40, mamba_conv_bias=True,
               num_key_value_heads=1, mamba_d_conv=2)
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# head size 64: the tensor-core attention of prompts; state size 64; query width != hidden size
+TINY_D = dict(
+    architectures=["FalconH1ForCausalLM"], model_type="falcon_h1",
+    vocab_size=320, hidden_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+    head_dim=64, intermediate_size=192, rope_theta=100000.0, max_position_embeddings=512, rms_norm_eps=1e-5,
+    tie_word_embeddings=True, mamba_d_ssm=128, mamba_n_heads=2, mamba_d_head=64, mamba_n_groups=1,
+    mamba_d_state=64, mamba_d_conv=4, mamba_conv_bias=True, mamba_rms_norm=True, key_multiplier=0.5,
+    ssm_multipliers=[1.0, 0.5, 1.0, 1.0, 0.5], eos_token_id=3)
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}

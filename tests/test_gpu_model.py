@@ -98,7 +98,7 @@ def requests_of(folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_each_request_alone_and_whole(engines, requests_of, name, dtype):
     llm = engines(name, dtype)
     for toks, want in zip(*requests_of[(name, dtype)]):
@@ -110,7 +110,7 @@ def test_each_request_alone_and_whole(engines, requests_of, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_last_32_tokens_one_by_one(engines, requests_of, name, dtype):
     llm = engines(name, dtype)
     for toks, want in zip(*requests_of[(name, dtype)]):
@@ -128,7 +128,7 @@ def test_last_32_tokens_one_by_one(engines, requests_of, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_unequal_batches_with_slot_reuse(engines, requests_of, name, dtype):
     """Two batches one after the other on a cache of 4 slots; in each, prompts (all but the last
     k tokens) run in one step, then one token each; shorter requests end earlier."""
@@ -279,3 +279,25 @@ def test_trace_run_as_a_program(folders, requests_of, tmp_path, dtype):
     assert not os.path.exists(os.path.join(out, "2.f32"))
     check(rd(3), want[1][32:33], dtype, "trace step 3")
     check(rd(4), want[4][-1:], dtype, "trace step 4")
+
+
+def test_prompts_in_pieces_and_the_command_line(engines, folders, requests_of, tmp_path):
+    """Prompts cut into steps of at most 48 tokens give the tokens of prompts run whole; the
+    bench program generates the same tokens as the entry point."""
+    llm = engines("D", "float32")
+    cfg = configs.TINY_D
+    prompts = [random_tokens(cfg["vocab_size"], n, 400 + n) for n in (130, 20, 61)]
+    whole = llm.generate(prompts, tlc.GREEDY, max_new_tokens=6, ignore_eos=True)
+    pieces = llm.generate(prompts, tlc.GREEDY, max_new_tokens=6, ignore_eos=True, max_step_tokens=48)
+    assert [r.tokens for r in whole] == [r.tokens for r in pieces]
+    assert llm.cache.slots.n_held == 0
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "bench"), "-m", folders["D"], "--dtype", "float32", "-t", "0",
+                        "-n", "6", "-i", " ".join(map(str, prompts[1])), "--ignore-eos", "-ub", "16"],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert p.stdout.strip().splitlines()[-1].split() == [str(t) for t in whole[1].tokens]
+    chat = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "chat"), "-m", folders["D"], "--dtype", "float32", "-t", "0",
+                           "-n", "6", "--ignore-eos"], input=" ".join(map(str, prompts[1])) + "\n/clear\n5 6 7\n/quit\n",
+                          capture_output=True, text=True, timeout=600)
+    assert chat.returncode == 0, chat.stderr[-2000:]
+    assert chat.stdout.strip().splitlines()[0].split() == [str(t) for t in whole[1].tokens]

@@ -60,11 +60,11 @@ class LLM:
 
     def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams = SamplingParams(),
                  max_new_tokens: int = 128, stop_ids: Optional[Sequence[int]] = None, max_batch: int = 64,
-                 ignore_eos: bool = False) -> List[GenerationResult]:
+                 ignore_eos: bool = False, max_step_tokens: int = 8192) -> List[GenerationResult]:
         """Token ids in, token ids out (host lists)."""
         if stop_ids is None:
             stop_ids = getattr(self.config, "stop_token_ids", ())
-        backend = EngineBackend(self.model, self.cache, params, self._graphs, self.use_graphs)
+        backend = EngineBackend(self.model, self.cache, params, self._graphs, self.use_graphs, max_step_tokens)
         try:
             return generate(backend, prompts, max_new_tokens, stop_ids, max_batch, self.max_context, ignore_eos)
         finally:

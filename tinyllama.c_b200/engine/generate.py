@@ -29,12 +29,14 @@ class GenerationResult:
 class EngineBackend:
     """The real backend: the model, its cache and the GPU sampler."""
 
-    def __init__(self, model, cache, params: SamplingParams, graphs: Optional[dict] = None, use_graphs: bool = True):
+    def __init__(self, model, cache, params: SamplingParams, graphs: Optional[dict] = None, use_graphs: bool = True,
+                 max_step_tokens: int = 8192):
         from ..sampling.sampler import Sampler
         self.model, self.cache, self.params = model, cache, params
         self.sampler = Sampler(params, model.device)
         self.graphs = graphs if graphs is not None else {}        # (params, batch size) -> DecodeGraph
         self.use_graphs = use_graphs and model.device.type == "cuda"
+        self.max_step_tokens = max(1, int(max_step_tokens))      # the reference's n_ubatch (graph.c:1397-1412)
         self.stats = dict(prefill_s=0.0, prefill_tokens=0, decode_s=0.0, decode_steps=0, decode_tokens=0,
                           h2d_bytes=0, d2h_bytes=0)
 
@@ -60,8 +62,7 @@ class EngineBackend:
         if decode and self.use_graphs:
             out = self._graph_step(entries, histories, sequence_ids, steps, uniform)
         else:
-            logits = step(self.model, self.cache, [StepEntry(s, t, (len(t) - 1,)) for s, t in entries])
-            out = self.sampler.sample(logits, histories, sequence_ids, steps).cpu().tolist()
+            out = self._prompt_steps(entries, histories, sequence_ids, steps)
         dt = time.perf_counter() - t0
         n = sum(len(t) for _, t in entries)
         if decode:
@@ -71,6 +72,37 @@ class EngineBackend:
         else:
             self.stats["prefill_s"] += dt
             self.stats["prefill_tokens"] += n
+        return out
+
+    def _prompt_steps(self, entries, histories, sequence_ids, steps) -> List[int]:
+        """Prompts in steps of at most max_step_tokens tokens: whole prompts while they fit, a
+        longer one in pieces that continue from the cache; the next token of an entry is
+        sampled in the step that brings its last piece."""
+        from .step import StepEntry, step
+        done = [0] * len(entries)
+        out: List[Optional[int]] = [None] * len(entries)
+        i = 0
+        while i < len(entries):
+            budget, batch, finished = self.max_step_tokens, [], []
+            j = i
+            while j < len(entries) and budget > 0:
+                slot, toks = entries[j]
+                piece = toks[done[j]:done[j] + budget]
+                done[j] += len(piece)
+                budget -= len(piece)
+                last = done[j] == len(toks)
+                batch.append(StepEntry(slot, piece, (len(piece) - 1,) if last else ()))
+                if not last:
+                    break
+                finished.append(j)
+                j += 1
+            logits = step(self.model, self.cache, batch)
+            if finished:
+                toks = self.sampler.sample(logits, [histories[k] for k in finished], [sequence_ids[k] for k in finished],
+                                           [steps[k] for k in finished]).cpu().tolist()
+                for k, t in zip(finished, toks):
+                    out[k] = t
+            i = j
         return out
 
     MAX_GRAPHS = 24

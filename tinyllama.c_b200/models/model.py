@@ -27,9 +27,11 @@ class Model:
         self.layers: List[Block] = [Block(s) for s in layer_specs]
         self.schedule: List[LayerRun] = list(schedule) if schedule is not None \
             else [LayerRun(i) for i in range(len(self.layers))]
-        for run in self.schedule:
-            if not (0 <= run.layer < len(self.layers)) or not (0 <= run.cache_id < len(self.layers)):
-                raise ValueError(f"schedule entry {run} names a layer that does not exist")
+        for r, run in enumerate(self.schedule):
+            if not (0 <= run.layer < len(self.layers)):
+                raise ValueError(f"run-order entry {r} names layer {run.layer}, which does not exist")
+            if run.cache is not None and not (0 <= run.cache < len(self.schedule) and self.schedule[run.cache].cache is None):
+                raise ValueError(f"run-order entry {r} reads the cache of entry {run.cache}, which has none of its own")
         self.final_norm = final_norm.build()
         self.embed_name, self.head_name = embed_name, head_name            # head_name None: tied (core.c:1246-1249)
         self.embed_scale = float(embed_scale)
@@ -55,9 +57,8 @@ class Model:
         return out
 
     def cache_requests(self) -> Dict[int, list]:
-        """Cache needs of every layer whose cache some schedule entry uses."""
-        used = {run.cache_id for run in self.schedule}
-        return {i: self.layers[i].cache_requests() for i in sorted(used)}
+        """Cache needs per entry of the run order that owns a cache (key: its index)."""
+        return {r: self.layers[run.layer].cache_requests() for r, run in enumerate(self.schedule) if run.cache is None}
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype: torch.dtype, device) -> None:
         self.dtype, self.device = dtype, torch.device(device)
@@ -77,8 +78,8 @@ class Model:
         [n_wanted, vocab] for the packed rows in want_rows (None: no logits)."""
         x = torch.empty((step.n_rows, self.hidden), dtype=torch.float32, device=self.device)
         ops.embed(step.tokens, self.embed_table, self.embed_scale, x)
-        for run in self.schedule:
-            self.layers[run.layer].forward(x, step, cache.layer_view(run.cache_id, run.writes))
+        for r, run in enumerate(self.schedule):
+            self.layers[run.layer].forward(x, step, cache.layer_view(r if run.cache is None else run.cache, run.writes))
         if want_rows is None or want_rows.numel() == 0:
             return None
         n = want_rows.numel()

@@ -164,18 +164,16 @@ class LayerSpec:
 @dataclass(frozen=True)
 class LayerRun:
     """One entry of the order in which layers run.  ``layer`` indexes the model's layers and
-    may repeat; ``cache`` names whose cache the layer uses (default: its own); a layer that
-    uses another's cache reads it without storing."""
+    may repeat (the weights are shared; every entry has a cache of its own, so a sequence's
+    state is the same whether its tokens come at once or one by one).  ``cache`` names another
+    entry of the run order (by its index) whose cache this entry reads instead, without
+    storing into it."""
     layer: int
     cache: Optional[int] = None
 
     @property
-    def cache_id(self) -> int:
-        return self.layer if self.cache is None else self.cache
-
-    @property
     def writes(self) -> bool:
-        return self.cache is None or self.cache == self.layer
+        return self.cache is None
 
 
 def to_vec(t: torch.Tensor, device) -> torch.Tensor:
