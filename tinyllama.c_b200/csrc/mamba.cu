@@ -97,37 +97,58 @@ extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, 
 }
 
 // ---- selective scan ---------------------------------------------------------------------------
-// grid (B, Hs, ceil(P / (4*RP))), 128 threads: each warp owns RP rows p of one head's state
-// [P, N], each lane the columns lane, lane+32, ... (NPL of them) in registers.  Tokens of the
-// sequence run in order; the inputs of TT tokens are staged in shared memory at a time.
+// The scan runs over *segments* of consecutive rows.  In the plain mode a segment is a whole
+// sequence: it starts from its slot's state (zero at position 0) and leaves its final state there.
+// Long prompts are cut into chunks that run in parallel, in three passes:
+//   1. every chunk from a zero state, keeping only its final state  S_c           (mode 1)
+//   2. per sequence, in chunk order: S_in[c] = S_in[c-1] * decay[c-1] + S_[c-1]    (state pass)
+//   3. every chunk again from its true incoming state S_in[c], now writing y      (mode 3)
+// which is the same recurrence, because the state is linear in its initial value.
+//
+// grid (segment, Hs, ceil(P / (4*RP))), 128 threads: each warp owns RP rows p of one head's state
+// [P, N], each lane the columns lane, lane+32, ... (NPL of them) in registers.  Rows run in
+// order; the inputs of SCAN_TT rows are staged in shared memory at a time.
 #define SCAN_TT 8
+#define SCAN_PLAIN 0
+#define SCAN_CHUNK_STATE 1
+#define SCAN_CHUNK_OUT 3
 template <int NPL, int RP>
 __global__ void __launch_bounds__(128)
 ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ dA,
-                const float* __restrict__ Dskip, float* __restrict__ state, const int* __restrict__ cu_seqlens,
-                const int* __restrict__ slots, const int* __restrict__ start_pos, float* __restrict__ y, int Hs, int P,
-                int N, int G, int Cd) {
+                const float* __restrict__ Dskip, float* __restrict__ state, float* __restrict__ chunk_state,
+                const int* __restrict__ seg_start, const int* __restrict__ seg_seq,
+                const int* __restrict__ seq_seg_start, const int* __restrict__ slots,
+                const int* __restrict__ start_pos, float* __restrict__ y, int mode, int Hs, int P, int N, int G, int Cd) {
   extern __shared__ float sm[];
-  const int b = blockIdx.x, h = blockIdx.y;
+  const int seg = blockIdx.x, h = blockIdx.y;
+  const int b = seg_seq ? seg_seq[seg] : seg;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rows_per_block = 4 * RP;
   const int p_blk = blockIdx.z * rows_per_block;
   const int p_base = p_blk + warp * RP;
   const int Di = Hs * P;
   const int g = h / (Hs / G);
-  const int t0 = cu_seqlens[b], n_tok = cu_seqlens[b + 1] - t0;
+  const int t0 = seg_start[seg], n_tok = seg_start[seg + 1] - t0;
   if (n_tok == 0) return;
-  float* S = state + (((size_t)slots[b] * Hs + h) * P) * N;
+  float* S_slot = state + (((size_t)slots[b] * Hs + h) * P) * N;
+  float* S_chunk = chunk_state ? chunk_state + (((size_t)seg * Hs + h) * P) * N : nullptr;
+  const float* S_init = nullptr;
+  if (mode == SCAN_PLAIN) { if (start_pos[b] > 0) S_init = S_slot; }
+  else if (mode == SCAN_CHUNK_OUT) S_init = S_chunk;
+  float* S_final = nullptr;
+  if (mode == SCAN_PLAIN) S_final = S_slot;
+  else if (mode == SCAN_CHUNK_STATE) S_final = S_chunk;
+  else if (seg + 1 == seq_seg_start[b + 1]) S_final = S_slot;        // the sequence's last chunk
+  const bool want_y = mode != SCAN_CHUNK_STATE;
   float s[RP][NPL];
-  const bool has_state = start_pos[b] > 0;
 #pragma unroll
   for (int r = 0; r < RP; r++)
 #pragma unroll
     for (int j = 0; j < NPL; j++) {
       const int p = p_base + r, n = lane + 32 * j;
-      s[r][j] = (has_state && p < P && n < N) ? S[(size_t)p * N + n] : 0.f;
+      s[r][j] = (S_init && p < P && n < N) ? S_init[(size_t)p * N + n] : 0.f;
     }
-  // shared staging: per token  B[N] | C[N] | x[rows_per_block] | dt | dA
+  // shared staging: per row  B[N] | C[N] | x[rows_per_block] | dt | dA
   const int per_tok = 2 * N + rows_per_block + 2;
   const float Dh = Dskip[h];
   for (int tt0 = 0; tt0 < n_tok; tt0 += SCAN_TT) {
@@ -138,7 +159,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
       const size_t t = (size_t)(t0 + tt0 + k);
       float v;
       if (e < N) v = xbc[t * Cd + Di + (size_t)g * N + e];
-      else if (e < 2 * N) v = xbc[t * Cd + Di + (size_t)G * N + (size_t)g * N + (e - N)];
+      else if (e < 2 * N) v = want_y ? xbc[t * Cd + Di + (size_t)G * N + (size_t)g * N + (e - N)] : 0.f;
       else if (e < 2 * N + rows_per_block) {
         const int p = p_blk + (e - 2 * N);
         v = p < P ? xbc[t * Cd + (size_t)h * P + p] : 0.f;
@@ -157,42 +178,99 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
         Bv[j] = n < N ? tk[n] : 0.f;
         Cv[j] = n < N ? tk[N + n] : 0.f;
       }
+      if (want_y) {
 #pragma unroll
-      for (int r = 0; r < RP; r++) {
-        const float xv = tk[2 * N + warp * RP + r];
-        const float xdt = xv * dtv;
-        float sum = 0.f;
+        for (int r = 0; r < RP; r++) {
+          const float xv = tk[2 * N + warp * RP + r];
+          const float xdt = xv * dtv;
+          float sum = 0.f;
 #pragma unroll
-        for (int j = 0; j < NPL; j++) {
-          const float sv = fmaf(s[r][j], dAv, Bv[j] * xdt);
-          s[r][j] = sv;
-          sum = fmaf(sv, Cv[j], sum);
+          for (int j = 0; j < NPL; j++) {
+            const float sv = fmaf(s[r][j], dAv, Bv[j] * xdt);
+            s[r][j] = sv;
+            sum = fmaf(sv, Cv[j], sum);
+          }
+          sum = warp_sum(sum);
+          const int p = p_base + r;
+          if (lane == 0 && p < P) y[(size_t)(t0 + tt0 + k) * Di + (size_t)h * P + p] = sum + xv * Dh;
         }
-        sum = warp_sum(sum);
-        const int p = p_base + r;
-        if (lane == 0 && p < P) y[(size_t)(t0 + tt0 + k) * Di + (size_t)h * P + p] = sum + xv * Dh;
+      } else {
+#pragma unroll
+        for (int r = 0; r < RP; r++) {
+          const float xdt = tk[2 * N + warp * RP + r] * dtv;
+#pragma unroll
+          for (int j = 0; j < NPL; j++) s[r][j] = fmaf(s[r][j], dAv, Bv[j] * xdt);
+        }
       }
     }
   }
+  if (S_final) {
 #pragma unroll
-  for (int r = 0; r < RP; r++)
+    for (int r = 0; r < RP; r++)
 #pragma unroll
-    for (int j = 0; j < NPL; j++) {
-      const int p = p_base + r, n = lane + 32 * j;
-      if (p < P && n < N) S[(size_t)p * N + n] = s[r][j];
+      for (int j = 0; j < NPL; j++) {
+        const int p = p_base + r, n = lane + 32 * j;
+        if (p < P && n < N) S_final[(size_t)p * N + n] = s[r][j];
+      }
+  }
+}
+
+// Pass 2: carries the state through a sequence's chunks.  chunk_state[c] holds the chunk's own
+// contribution on entry and the state *before* the chunk on exit.  grid (B, Hs, blocks over P*N).
+__global__ void __launch_bounds__(256)
+ssm_state_pass_kernel(const float* __restrict__ dA, const float* __restrict__ state, float* __restrict__ chunk_state,
+                      const int* __restrict__ seg_start, const int* __restrict__ seq_seg_start,
+                      const int* __restrict__ slots, const int* __restrict__ start_pos, int Hs, int PN) {
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int e = blockIdx.z * blockDim.x + threadIdx.x;
+  const int c0 = seq_seg_start[b], c1 = seq_seg_start[b + 1];
+  if (c1 - c0 <= 0) return;
+  float s = 0.f;
+  if (e < PN && start_pos[b] > 0) s = state[((size_t)slots[b] * Hs + h) * PN + e];
+  for (int c = c0; c < c1; c++) {
+    // decay of the whole chunk: the product of its rows' decays (every thread computes it; the
+    // rows are few and the loads are broadcast)
+    float decay = 1.f;
+    for (int t = seg_start[c]; t < seg_start[c + 1]; t++) decay *= dA[(size_t)t * Hs + h];
+    if (e < PN) {
+      float* cs = chunk_state + ((size_t)c * Hs + h) * PN + e;
+      const float own = *cs;
+      *cs = s;
+      s = fmaf(s, decay, own);
     }
+  }
 }
 
 template <int NPL>
 static int launch_scan(const float* xbc, const float* dt, const float* dA, const float* Dskip, float* state,
-                       const int* cu_seqlens, const int* slots, const int* start_pos, float* y, int B, int Hs, int P,
-                       int N, int G, int Cd, cudaStream_t stream) {
+                       float* chunk_state, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
+                       const int* slots, const int* start_pos, float* y, int mode, int n_seg, int Hs, int P, int N,
+                       int G, int Cd, cudaStream_t stream) {
   constexpr int RP = 4;
-  dim3 grid(B, Hs, (P + 4 * RP - 1) / (4 * RP));
+  dim3 grid(n_seg, Hs, (P + 4 * RP - 1) / (4 * RP));
   const size_t smem = (size_t)SCAN_TT * (2 * N + 4 * RP + 2) * sizeof(float);
-  ssm_scan_kernel<NPL, RP><<<grid, 128, smem, stream>>>(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, Hs,
-                                                        P, N, G, Cd);
+  ssm_scan_kernel<NPL, RP><<<grid, 128, smem, stream>>>(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq,
+                                                        seq_seg_start, slots, start_pos, y, mode, Hs, P, N, G, Cd);
   TLC_CHECK_LAUNCH("ssm_scan");
+  return 0;
+}
+
+static int scan_dispatch(const float* xbc, const float* dt, const float* dA, const float* Dskip, float* state,
+                         float* chunk_state, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
+                         const int* slots, const int* start_pos, float* y, int mode, int n_seg, int Hs, int P, int N,
+                         int G, int Cd, cudaStream_t stream) {
+#define TLC_SCAN(NPL) launch_scan<NPL>(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos, y, mode, n_seg, Hs, P, N, G, Cd, stream)
+  if (N <= 32) return TLC_SCAN(1);
+  if (N <= 64) return TLC_SCAN(2);
+  if (N <= 128) return TLC_SCAN(4);
+  return TLC_SCAN(8);
+#undef TLC_SCAN
+}
+
+static int scan_checks(int Hs, int N, int G) {
+  TLC_REQUIRE(G > 0 && Hs % G == 0, "ssm_scan: %d heads are not a multiple of %d groups", Hs, G);
+  TLC_REQUIRE(N >= 1 && N <= 256, "ssm_scan: state size %d is outside the kernel's range 1..256", N);
+  TLC_REQUIRE(Hs <= 65535, "ssm_scan: too many heads (%d)", Hs);
   return 0;
 }
 
@@ -200,11 +278,26 @@ extern "C" int tlc_ssm_scan(const float* xbc, const float* dt, const float* dA, 
                             const int* cu_seqlens, const int* slots, const int* start_pos, float* y, int B, int Hs,
                             int P, int N, int G, int Cd, cudaStream_t stream) {
   if (B == 0) return 0;
-  TLC_REQUIRE(G > 0 && Hs % G == 0, "ssm_scan: %d heads are not a multiple of %d groups", Hs, G);
-  TLC_REQUIRE(N >= 1 && N <= 256, "ssm_scan: state size %d is outside the kernel's range 1..256", N);
-  TLC_REQUIRE(Hs <= 65535, "ssm_scan: too many heads (%d)", Hs);
-  if (N <= 32) return launch_scan<1>(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, B, Hs, P, N, G, Cd, stream);
-  if (N <= 64) return launch_scan<2>(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, B, Hs, P, N, G, Cd, stream);
-  if (N <= 128) return launch_scan<4>(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, B, Hs, P, N, G, Cd, stream);
-  return launch_scan<8>(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, B, Hs, P, N, G, Cd, stream);
+  if (int rc = scan_checks(Hs, N, G)) return rc;
+  return scan_dispatch(xbc, dt, dA, Dskip, state, nullptr, cu_seqlens, nullptr, nullptr, slots, start_pos, y, SCAN_PLAIN,
+                       B, Hs, P, N, G, Cd, stream);
+}
+
+// The same scan with every sequence cut into chunks that run in parallel.  seg_start [n_seg + 1]:
+// first row of every chunk; seg_seq [n_seg]: its sequence; seq_seg_start [B + 1]: first chunk of
+// every sequence; chunk_state: scratch [n_seg, Hs, P, N] floats.
+extern "C" int tlc_ssm_scan_chunked(const float* xbc, const float* dt, const float* dA, const float* Dskip,
+                                    float* state, float* chunk_state, const int* seg_start, const int* seg_seq,
+                                    const int* seq_seg_start, const int* slots, const int* start_pos, float* y,
+                                    int B, int n_seg, int Hs, int P, int N, int G, int Cd, cudaStream_t stream) {
+  if (B == 0 || n_seg == 0) return 0;
+  if (int rc = scan_checks(Hs, N, G)) return rc;
+  if (int rc = scan_dispatch(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos,
+                             y, SCAN_CHUNK_STATE, n_seg, Hs, P, N, G, Cd, stream)) return rc;
+  dim3 grid(B, Hs, (P * N + 255) / 256);
+  ssm_state_pass_kernel<<<grid, 256, 0, stream>>>(dA, state, chunk_state, seg_start, seq_seg_start, slots, start_pos, Hs,
+                                                  P * N);
+  TLC_CHECK_LAUNCH("ssm_state_pass");
+  return scan_dispatch(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos, y,
+                       SCAN_CHUNK_OUT, n_seg, Hs, P, N, G, Cd, stream);
 }

@@ -17,7 +17,7 @@ import torch
 
 from ..cache import Cache, CacheError
 from ..models.model import Model
-from ..parts.base import StepInfo
+from ..parts.base import SCAN_CHUNK, StepInfo
 
 
 @dataclass
@@ -51,7 +51,19 @@ def pack(entries: Sequence[StepEntry], starts: Sequence[int], vocab: int, device
         row_seq += [b] * n
         cu.append(cu[-1] + n)
     T, B, W = len(tokens), len(entries), len(want_rows)
+    # chunk table for recurrent mixers: sequences longer than a chunk are cut so that chunks run in parallel
+    seg_start, seg_seq, seq_seg_start = [], [], [0]
+    if any(len(e.tokens) > SCAN_CHUNK for e in entries):
+        for b, e in enumerate(entries):
+            for off in range(0, len(e.tokens), SCAN_CHUNK):
+                seg_start.append(cu[b] + off)
+                seg_seq.append(b)
+            seq_seg_start.append(len(seg_seq))
+        seg_start.append(T)
+    n_seg = len(seg_seq)
     flat = tokens + positions + row_seq + cu + [e.slot for e in entries] + list(starts) + want_rows
+    if n_seg:
+        flat += seg_start + seg_seq + seq_seg_start
     host = torch.tensor(flat, dtype=torch.int32)
     if torch.device(device).type == "cuda":
         host = host.pin_memory()
@@ -69,7 +81,10 @@ def pack(entries: Sequence[StepEntry], starts: Sequence[int], vocab: int, device
                     slots=take(B), start_pos=take(B), max_new=max(lens) if lens else 0,
                     max_context=max((s + n for s, n in zip(starts, lens)), default=0),
                     host_lens=tuple(lens), host_start=tuple(starts), host_slots=tuple(e.slot for e in entries))
-    return step, take(W), W
+    want = take(W)
+    if n_seg:
+        step.chunks = (take(n_seg + 1), take(n_seg), take(B + 1))
+    return step, want, W
 
 
 def step(model: Model, cache: Cache, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:

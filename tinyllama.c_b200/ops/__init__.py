@@ -36,6 +36,7 @@ _SIGNATURES = {
     "tlc_mamba_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
                        _i, _i, _vp],
     "tlc_ssm_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "tlc_ssm_scan_chunked": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "tlc_argmax": [_vp, _i, _i, _vp, _vp],
     "tlc_sample": [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp],
 }
@@ -324,9 +325,11 @@ def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, b
 
 def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch.Tensor, state: torch.Tensor,
              cu_seqlens: torch.Tensor, slots: torch.Tensor, start_pos: torch.Tensor, y: torch.Tensor, Hs: int, P: int,
-             N: int, G: int) -> None:
+             N: int, G: int, chunks=None) -> None:
     """Selective scan of every sequence in order, from its slot's state (zero at position 0);
-    state [n_slots, Hs, P, N] float32 is updated in place; y [T, Hs*P] float32 is before gating."""
+    state [n_slots, Hs, P, N] float32 is updated in place; y [T, Hs*P] float32 is before gating.
+    chunks = (seg_start [n+1], seg_seq [n], seq_seg_start [B+1]) cuts the sequences into
+    chunks that run in parallel (three passes, same result up to rounding)."""
     _gpu(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y)
     T, Cd = xbc.shape
     if Cd != Hs * P + 2 * G * N:
@@ -337,6 +340,17 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch
     _f32vec(Dskip, Hs, "D")
     if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (Hs, P, N):
         raise KernelError("ssm_scan: state must be contiguous float32 [n_slots, Hs, P, N]")
+    if chunks is not None:
+        seg_start, seg_seq, seq_seg_start = chunks
+        for t, n in ((seg_start, "seg_start"), (seg_seq, "seg_seq"), (seq_seg_start, "seq_seg_start")):
+            _gpu(t)
+            _i32(t, n)
+        n_seg = seg_seq.numel()
+        scratch = torch.empty((n_seg, Hs, P, N), dtype=torch.float32, device=xbc.device)
+        _call("tlc_ssm_scan_chunked", xbc.data_ptr(), dt.data_ptr(), dA.data_ptr(), Dskip.data_ptr(), state.data_ptr(),
+              scratch.data_ptr(), seg_start.data_ptr(), seg_seq.data_ptr(), seq_seg_start.data_ptr(), slots.data_ptr(),
+              start_pos.data_ptr(), y.data_ptr(), slots.numel(), n_seg, Hs, P, N, G, Cd, _stream())
+        return
     _call("tlc_ssm_scan", xbc.data_ptr(), dt.data_ptr(), dA.data_ptr(), Dskip.data_ptr(), state.data_ptr(),
           cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), y.data_ptr(), slots.numel(), Hs, P, N, G, Cd,
           _stream())

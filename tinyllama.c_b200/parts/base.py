@@ -75,6 +75,12 @@ class StepInfo:
     host_lens: Tuple[int, ...] = ()
     host_start: Tuple[int, ...] = ()
     host_slots: Tuple[int, ...] = ()
+    # sequences cut into chunks of SCAN_CHUNK rows (None when no sequence is longer than a chunk):
+    # (first row of every chunk [n+1], sequence of every chunk [n], first chunk of every sequence [B+1])
+    chunks: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None
+
+
+SCAN_CHUNK = 128      # rows per chunk of a recurrent mixer's parallel scan
 
 
 @dataclass

@@ -88,7 +88,7 @@ class Mamba2Mixer(Part):
                        step.cu_seqlens, step.row_seq, step.slots, step.start_pos, xbc, dt, dA)
         y = act_empty((T, self.Di), normed, f32)
         ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs, self.P,
-                     self.N, self.G)
+                     self.N, self.G, step.chunks)
         gated = act_empty((T, self.Di), normed)
         ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated)
         self.out_proj.forward(gated, residual, accumulate=True)
