@@ -118,7 +118,8 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
                 const float* __restrict__ Dskip, float* __restrict__ state, float* __restrict__ chunk_state,
                 const int* __restrict__ seg_start, const int* __restrict__ seg_seq,
                 const int* __restrict__ seq_seg_start, const int* __restrict__ slots,
-                const int* __restrict__ start_pos, float* __restrict__ y, int mode, int Hs, int P, int N, int G, int Cd) {
+                const int* __restrict__ start_pos, float* __restrict__ y, float* __restrict__ chunk_decay, int mode,
+                int Hs, int P, int N, int G, int Cd) {
   extern __shared__ float sm[];
   const int seg = blockIdx.x, h = blockIdx.y;
   const int b = seg_seq ? seg_seq[seg] : seg;
@@ -154,18 +155,23 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
   for (int tt0 = 0; tt0 < n_tok; tt0 += SCAN_TT) {
     const int nt = min(SCAN_TT, n_tok - tt0);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < nt * per_tok; idx += blockDim.x) {
-      const int k = idx / per_tok, e = idx % per_tok;
-      const size_t t = (size_t)(t0 + tt0 + k);
-      float v;
-      if (e < N) v = xbc[t * Cd + Di + (size_t)g * N + e];
-      else if (e < 2 * N) v = want_y ? xbc[t * Cd + Di + (size_t)G * N + (size_t)g * N + (e - N)] : 0.f;
-      else if (e < 2 * N + rows_per_block) {
-        const int p = p_blk + (e - 2 * N);
-        v = p < P ? xbc[t * Cd + (size_t)h * P + p] : 0.f;
-      } else if (e == 2 * N + rows_per_block) v = dt[t * Hs + h];
-      else v = dA[t * Hs + h];
-      sm[idx] = v;
+    for (int k = 0; k < nt; k++) {
+      const float* row = xbc + (size_t)(t0 + tt0 + k) * Cd;
+      float* dst = sm + (size_t)k * per_tok;
+      const float* Bg = row + Di + (size_t)g * N;
+      const float* Cg = row + Di + (size_t)G * N + (size_t)g * N;
+      for (int e = threadIdx.x; e < N; e += blockDim.x) {
+        dst[e] = Bg[e];
+        dst[N + e] = want_y ? Cg[e] : 0.f;
+      }
+      if (threadIdx.x < rows_per_block) {
+        const int p = p_blk + threadIdx.x;
+        dst[2 * N + threadIdx.x] = p < P ? row[(size_t)h * P + p] : 0.f;
+      } else if (threadIdx.x == 32 + rows_per_block) {
+        dst[2 * N + rows_per_block] = dt[(size_t)(t0 + tt0 + k) * Hs + h];
+      } else if (threadIdx.x == 64 + rows_per_block) {
+        dst[2 * N + rows_per_block + 1] = dA[(size_t)(t0 + tt0 + k) * Hs + h];
+      }
     }
     __syncthreads();
     for (int k = 0; k < nt; k++) {
@@ -204,6 +210,11 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
       }
     }
   }
+  if (mode == SCAN_CHUNK_STATE && blockIdx.z == 0 && threadIdx.x == 0) {
+    float d = 1.f;                         // decay of the whole chunk: the product of its rows' decays
+    for (int k = 0; k < n_tok; k++) d *= dA[(size_t)(t0 + k) * Hs + h];
+    chunk_decay[(size_t)seg * Hs + h] = d;
+  }
   if (S_final) {
 #pragma unroll
     for (int r = 0; r < RP; r++)
@@ -218,8 +229,8 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
 // Pass 2: carries the state through a sequence's chunks.  chunk_state[c] holds the chunk's own
 // contribution on entry and the state *before* the chunk on exit.  grid (B, Hs, blocks over P*N).
 __global__ void __launch_bounds__(256)
-ssm_state_pass_kernel(const float* __restrict__ dA, const float* __restrict__ state, float* __restrict__ chunk_state,
-                      const int* __restrict__ seg_start, const int* __restrict__ seq_seg_start,
+ssm_state_pass_kernel(const float* __restrict__ chunk_decay, const float* __restrict__ state,
+                      float* __restrict__ chunk_state, const int* __restrict__ seq_seg_start,
                       const int* __restrict__ slots, const int* __restrict__ start_pos, int Hs, int PN) {
   const int b = blockIdx.x, h = blockIdx.y;
   const int e = blockIdx.z * blockDim.x + threadIdx.x;
@@ -228,10 +239,7 @@ ssm_state_pass_kernel(const float* __restrict__ dA, const float* __restrict__ st
   float s = 0.f;
   if (e < PN && start_pos[b] > 0) s = state[((size_t)slots[b] * Hs + h) * PN + e];
   for (int c = c0; c < c1; c++) {
-    // decay of the whole chunk: the product of its rows' decays (every thread computes it; the
-    // rows are few and the loads are broadcast)
-    float decay = 1.f;
-    for (int t = seg_start[c]; t < seg_start[c + 1]; t++) decay *= dA[(size_t)t * Hs + h];
+    const float decay = chunk_decay[(size_t)c * Hs + h];
     if (e < PN) {
       float* cs = chunk_state + ((size_t)c * Hs + h) * PN + e;
       const float own = *cs;
@@ -244,22 +252,23 @@ ssm_state_pass_kernel(const float* __restrict__ dA, const float* __restrict__ st
 template <int NPL>
 static int launch_scan(const float* xbc, const float* dt, const float* dA, const float* Dskip, float* state,
                        float* chunk_state, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
-                       const int* slots, const int* start_pos, float* y, int mode, int n_seg, int Hs, int P, int N,
-                       int G, int Cd, cudaStream_t stream) {
+                       const int* slots, const int* start_pos, float* y, float* chunk_decay, int mode, int n_seg, int Hs,
+                       int P, int N, int G, int Cd, cudaStream_t stream) {
   constexpr int RP = 4;
   dim3 grid(n_seg, Hs, (P + 4 * RP - 1) / (4 * RP));
   const size_t smem = (size_t)SCAN_TT * (2 * N + 4 * RP + 2) * sizeof(float);
   ssm_scan_kernel<NPL, RP><<<grid, 128, smem, stream>>>(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq,
-                                                        seq_seg_start, slots, start_pos, y, mode, Hs, P, N, G, Cd);
+                                                        seq_seg_start, slots, start_pos, y, chunk_decay, mode, Hs, P, N, G,
+                                                        Cd);
   TLC_CHECK_LAUNCH("ssm_scan");
   return 0;
 }
 
 static int scan_dispatch(const float* xbc, const float* dt, const float* dA, const float* Dskip, float* state,
                          float* chunk_state, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
-                         const int* slots, const int* start_pos, float* y, int mode, int n_seg, int Hs, int P, int N,
-                         int G, int Cd, cudaStream_t stream) {
-#define TLC_SCAN(NPL) launch_scan<NPL>(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos, y, mode, n_seg, Hs, P, N, G, Cd, stream)
+                         const int* slots, const int* start_pos, float* y, float* chunk_decay, int mode, int n_seg,
+                         int Hs, int P, int N, int G, int Cd, cudaStream_t stream) {
+#define TLC_SCAN(NPL) launch_scan<NPL>(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos, y, chunk_decay, mode, n_seg, Hs, P, N, G, Cd, stream)
   if (N <= 32) return TLC_SCAN(1);
   if (N <= 64) return TLC_SCAN(2);
   if (N <= 128) return TLC_SCAN(4);
@@ -279,25 +288,26 @@ extern "C" int tlc_ssm_scan(const float* xbc, const float* dt, const float* dA, 
                             int P, int N, int G, int Cd, cudaStream_t stream) {
   if (B == 0) return 0;
   if (int rc = scan_checks(Hs, N, G)) return rc;
-  return scan_dispatch(xbc, dt, dA, Dskip, state, nullptr, cu_seqlens, nullptr, nullptr, slots, start_pos, y, SCAN_PLAIN,
-                       B, Hs, P, N, G, Cd, stream);
+  return scan_dispatch(xbc, dt, dA, Dskip, state, nullptr, cu_seqlens, nullptr, nullptr, slots, start_pos, y, nullptr,
+                       SCAN_PLAIN, B, Hs, P, N, G, Cd, stream);
 }
 
 // The same scan with every sequence cut into chunks that run in parallel.  seg_start [n_seg + 1]:
 // first row of every chunk; seg_seq [n_seg]: its sequence; seq_seg_start [B + 1]: first chunk of
-// every sequence; chunk_state: scratch [n_seg, Hs, P, N] floats.
+// every sequence; chunk_state: scratch [n_seg, Hs, P, N] + [n_seg, Hs] floats.
 extern "C" int tlc_ssm_scan_chunked(const float* xbc, const float* dt, const float* dA, const float* Dskip,
                                     float* state, float* chunk_state, const int* seg_start, const int* seg_seq,
                                     const int* seq_seg_start, const int* slots, const int* start_pos, float* y,
                                     int B, int n_seg, int Hs, int P, int N, int G, int Cd, cudaStream_t stream) {
   if (B == 0 || n_seg == 0) return 0;
   if (int rc = scan_checks(Hs, N, G)) return rc;
+  float* chunk_decay = chunk_state + (size_t)n_seg * Hs * P * N;
   if (int rc = scan_dispatch(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos,
-                             y, SCAN_CHUNK_STATE, n_seg, Hs, P, N, G, Cd, stream)) return rc;
+                             y, chunk_decay, SCAN_CHUNK_STATE, n_seg, Hs, P, N, G, Cd, stream)) return rc;
   dim3 grid(B, Hs, (P * N + 255) / 256);
-  ssm_state_pass_kernel<<<grid, 256, 0, stream>>>(dA, state, chunk_state, seg_start, seq_seg_start, slots, start_pos, Hs,
+  ssm_state_pass_kernel<<<grid, 256, 0, stream>>>(chunk_decay, state, chunk_state, seq_seg_start, slots, start_pos, Hs,
                                                   P * N);
   TLC_CHECK_LAUNCH("ssm_state_pass");
   return scan_dispatch(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos, y,
-                       SCAN_CHUNK_OUT, n_seg, Hs, P, N, G, Cd, stream);
+                       chunk_decay, SCAN_CHUNK_OUT, n_seg, Hs, P, N, G, Cd, stream);
 }

@@ -346,7 +346,7 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch
             _gpu(t)
             _i32(t, n)
         n_seg = seg_seq.numel()
-        scratch = torch.empty((n_seg, Hs, P, N), dtype=torch.float32, device=xbc.device)
+        scratch = torch.empty(n_seg * Hs * (P * N + 1), dtype=torch.float32, device=xbc.device)
         _call("tlc_ssm_scan_chunked", xbc.data_ptr(), dt.data_ptr(), dA.data_ptr(), Dskip.data_ptr(), state.data_ptr(),
               scratch.data_ptr(), seg_start.data_ptr(), seg_seq.data_ptr(), seq_seg_start.data_ptr(), slots.data_ptr(),
               start_pos.data_ptr(), y.data_ptr(), slots.numel(), n_seg, Hs, P, N, G, Cd, _stream())
