@@ -222,6 +222,13 @@ def test_mamba_conv(dtype, Di, G, N, K, Hs, bias):
             -torch.rand(Hs, generator=g) * 8, state, cu, row_seq, slots, start_pos, torch.empty(T, Cd),
             torch.empty(T, Hs), torch.empty(T, Hs)]
     cmp("mamba_conv", args, [7, 12, 13, 14], tol_of=2e-5)
+    # one row per sequence: the fused kernel of decode steps
+    starts, lens = [0, 9, 1, 31, 2], [1, 1, 1, 1, 1]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    slots = torch.tensor([4, 0, 2, 1, 3], dtype=torch.int32)
+    args = [rnd(g, 5, Pd, dtype=DT[dtype]), Di, Di + Cd, args[3], args[4], args[5], args[6], rnd(g, 5, K - 1, Cd), cu,
+            row_seq, slots, start_pos, torch.empty(5, Cd), torch.empty(5, Hs), torch.empty(5, Hs), True]
+    cmp("mamba_conv", args, [7, 12, 13, 14], tol_of=2e-5)
 
 
 @pytest.mark.parametrize("Hs,P,N,G", [(3, 16, 16, 1), (6, 24, 32, 2), (4, 64, 256, 1), (2, 20, 100, 2), (5, 7, 40, 1)])

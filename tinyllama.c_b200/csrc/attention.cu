@@ -19,6 +19,7 @@ __global__ void rope_kv_store_kernel(const TI* __restrict__ qkv, int ld, int q_o
                                      const int* __restrict__ positions, const int* __restrict__ row_seq,
                                      const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
                                      int H, int KV, int hd, int write_kv) {
+  tlc_pdl();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = rope_dim >> 1;
@@ -61,7 +62,7 @@ extern "C" int tlc_rope_kv_store(const void* qkv, int in_dtype, int dtype, int l
                                  int max_pages, int T, int H, int KV, int hd, int write_kv, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(rope_dim % 2 == 0 && rope_dim <= hd, "rope: rotated width %d must be even and at most head_dim %d", rope_dim, hd);
-  TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, rope_kv_store_kernel<TI, TT><<<T, 256, 0, stream>>>(
+  TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(rope_kv_store_kernel<TI, TT>, dim3(T), dim3(256), 0, stream, 
       (const TI*)qkv, ld, q_off, k_off, v_off, (TT*)q_out, (TT*)k_pages, (TT*)v_pages, inv_freq, rope_dim, positions,
       row_seq, slots, block_table, max_pages, H, KV, hd, write_kv)));
   TLC_CHECK_LAUNCH("rope_kv_store");
@@ -79,6 +80,7 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
                       const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
                       const int* __restrict__ row_seq, const int* __restrict__ slots, T* __restrict__ out, int H, int KV,
                       int hd, float scale, int window) {
+  tlc_pdl();
   extern __shared__ float qs_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -145,7 +147,7 @@ extern "C" int tlc_attention(const void* q, int dtype, const void* k_pages, cons
   TLC_REQUIRE(hd <= 32 * ATT_MAXD, "attention: head size %d exceeds the kernel's limit of %d", hd, 32 * ATT_MAXD);
   dim3 grid(T, (H + 3) / 4);
   const size_t smem = (size_t)4 * hd * sizeof(float);
-  TLC_DISPATCH_DTYPE(dtype, TT, attention_warp_kernel<TT><<<grid, 128, smem, stream>>>(
+  TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(attention_warp_kernel<TT>, dim3(grid), dim3(128), smem, stream, 
       (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, (TT*)out,
       H, KV, hd, scale, window));
   TLC_CHECK_LAUNCH("attention");
@@ -167,6 +169,7 @@ attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k
                                 const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
                                 const int* __restrict__ row_seq, const int* __restrict__ slots, float* __restrict__ part_o,
                                 float* __restrict__ part_ml, int H, int KV, int hd, float scale, int window, int n_splits) {
+  tlc_pdl();
   extern __shared__ float sh[];
   const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
   const int G = H / KV;
@@ -243,6 +246,7 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
                                     int max_pages, const int* __restrict__ positions, const int* __restrict__ row_seq,
                                     const int* __restrict__ slots, float* __restrict__ part_o,
                                     float* __restrict__ part_ml, int H, int KV, float scale, int window, int n_splits) {
+  tlc_pdl();
   extern __shared__ float sh[];
   constexpr int DL = HD / 8;                 // lanes per value row
   constexpr int GROUPS = DEC_KEYS / DL;      // value rows in flight
@@ -278,7 +282,7 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
   if (valid) {
     const uint4* kr = reinterpret_cast<const uint4*>(
         k_pages + (((size_t)pages[threadIdx.x / TLC_PAGE] * KV + g) * TLC_PAGE + kp % TLC_PAGE) * HD);
-#pragma unroll 4
+#pragma unroll
     for (int d8 = 0; d8 < DL; d8++) {
       const uint4 kq = __ldg(kr + d8);
       const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&kq);
@@ -298,17 +302,42 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
       }
     }
   }
-  for (int hg = 0; hg < G; hg++) {
-    const float sv = valid ? s[hg] : -INFINITY;
-    float m = warp_max(sv);
+  // maximum and sum over the block's keys, all heads of the group at once
+  {
+    float* redm = red;                        // [4 warps][DEC_MAXG]
+    const int wp = threadIdx.x >> 5, ln = threadIdx.x & 31;
+#pragma unroll
+    for (int hg = 0; hg < DEC_MAXG; hg++) {
+      if (hg < G) {
+        const float m = warp_max(valid ? s[hg] : -INFINITY);
+        if (ln == 0) redm[wp * DEC_MAXG + hg] = m;
+      }
+    }
     __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    float lsum[DEC_MAXG];
+#pragma unroll
+    for (int hg = 0; hg < DEC_MAXG; hg++) {
+      if (hg < G) {
+        const float m = fmaxf(fmaxf(redm[hg], redm[DEC_MAXG + hg]), fmaxf(redm[2 * DEC_MAXG + hg], redm[3 * DEC_MAXG + hg]));
+        const float p = valid ? expf(s[hg] - m) : 0.f;
+        ps[hg * DEC_KEYS + threadIdx.x] = p;
+        lsum[hg] = warp_sum(p);
+        s[hg] = m;
+      }
+    }
     __syncthreads();
-    m = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-    const float p = valid ? expf(sv - m) : 0.f;
-    ps[hg * DEC_KEYS + threadIdx.x] = p;
-    const float l = block_sum(p, red);
-    if (threadIdx.x == 0) { ml[(size_t)hg * n_splits * 2] = m; ml[(size_t)hg * n_splits * 2 + 1] = l; }
+#pragma unroll
+    for (int hg = 0; hg < DEC_MAXG; hg++)
+      if (hg < G && ln == 0) redm[wp * DEC_MAXG + hg] = lsum[hg];
+    __syncthreads();
+    if (threadIdx.x < G) {
+      const int hg = threadIdx.x;
+      float mm = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < DEC_MAXG; i++) if (i == hg) mm = s[i];
+      ml[(size_t)hg * n_splits * 2] = mm;
+      ml[(size_t)hg * n_splits * 2 + 1] = redm[hg] + redm[DEC_MAXG + hg] + redm[2 * DEC_MAXG + hg] + redm[3 * DEC_MAXG + hg];
+    }
   }
   __syncthreads();
   const int nk = min(DEC_KEYS, n_keys - k0);
@@ -318,21 +347,35 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
   for (int hg = 0; hg < DEC_MAXG; hg++)
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[hg][i] = 0.f;
-  for (int j = grp; j < nk; j += GROUPS) {
-    const int kj = k0 + j;
-    if (kj < start) continue;              // outside the window: its page may have been given back
-    const uint4 vq = __ldg(reinterpret_cast<const uint4*>(
-                               v_pages + (((size_t)pages[j / TLC_PAGE] * KV + g) * TLC_PAGE + kj % TLC_PAGE) * HD) + dl);
-    const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&vq);
-    float vf[8];
+  // value rows of this thread's group, 16 at a time: all loads are issued before the first use
+  constexpr int VB = DL < 16 ? DL : 16;
+#pragma unroll 1
+  for (int jb = 0; jb < DL; jb += VB) {
+    uint4 vq[VB];
 #pragma unroll
-    for (int i = 0; i < 4; i++) { const float2 f = __bfloat1622float2(vb[i]); vf[2 * i] = f.x; vf[2 * i + 1] = f.y; }
+    for (int u = 0; u < VB; u++) {
+      const int j = grp + (jb + u) * GROUPS;
+      const int kj = k0 + j;
+      const bool use = j < nk && kj >= start;          // outside the window a page may have been given back
+      vq[u] = use ? __ldg(reinterpret_cast<const uint4*>(
+                              v_pages + (((size_t)pages[j / TLC_PAGE] * KV + g) * TLC_PAGE + kj % TLC_PAGE) * HD) + dl)
+                  : make_uint4(0, 0, 0, 0);
+    }
 #pragma unroll
-    for (int hg = 0; hg < DEC_MAXG; hg++) {
-      if (hg < G) {
-        const float p = ps[hg * DEC_KEYS + j];
+    for (int u = 0; u < VB; u++) {
+      const int j = grp + (jb + u) * GROUPS;
+      if (j >= nk) continue;
+      const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&vq[u]);
+      float vf[8];
 #pragma unroll
-        for (int i = 0; i < 8; i++) acc[hg][i] = fmaf(p, vf[i], acc[hg][i]);
+      for (int i = 0; i < 4; i++) { const float2 f = __bfloat1622float2(vb[i]); vf[2 * i] = f.x; vf[2 * i + 1] = f.y; }
+#pragma unroll
+      for (int hg = 0; hg < DEC_MAXG; hg++) {
+        if (hg < G) {
+          const float p = ps[hg * DEC_KEYS + j];
+#pragma unroll
+          for (int i = 0; i < 8; i++) acc[hg][i] = fmaf(p, vf[i], acc[hg][i]);
+        }
       }
     }
   }
@@ -354,6 +397,7 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
 template <typename T>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               T* __restrict__ out, int hd, int n_splits) {
+  tlc_pdl();
   const size_t th = blockIdx.x;                       // row * H + head
   const float* ml = part_ml + th * n_splits * 2;
   float m = -INFINITY;
@@ -389,21 +433,21 @@ extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_page
     if (vsmem <= 48 * 1024) {
       const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
       if (hd == 64)
-        attention_decode_partial_vec_kernel<64><<<grid, DEC_KEYS, vsmem, stream>>>(qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
+        tlc_launch(attention_decode_partial_vec_kernel<64>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
       else if (hd == 128)
-        attention_decode_partial_vec_kernel<128><<<grid, DEC_KEYS, vsmem, stream>>>(qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
+        tlc_launch(attention_decode_partial_vec_kernel<128>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
       else
-        attention_decode_partial_vec_kernel<256><<<grid, DEC_KEYS, vsmem, stream>>>(qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
-      attention_decode_merge_kernel<__nv_bfloat16><<<T * H, 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits);
+        tlc_launch(attention_decode_partial_vec_kernel<256>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
+      tlc_launch(attention_decode_merge_kernel<__nv_bfloat16>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits);
       TLC_CHECK_LAUNCH("attention(decode)");
       return 0;
     }
   }
   TLC_DISPATCH_DTYPE(dtype, TT, {
-    attention_decode_partial_kernel<TT><<<grid, DEC_KEYS, smem, stream>>>(
+    tlc_launch(attention_decode_partial_kernel<TT>, dim3(grid), dim3(DEC_KEYS), smem, stream, 
         (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, part_o,
         part_ml, H, KV, hd, scale, window, n_splits);
-    attention_decode_merge_kernel<TT><<<T * H, 128, 0, stream>>>(part_o, part_ml, (TT*)out, hd, n_splits);
+    tlc_launch(attention_decode_merge_kernel<TT>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (TT*)out, hd, n_splits);
   });
   TLC_CHECK_LAUNCH("attention(decode)");
   return 0;

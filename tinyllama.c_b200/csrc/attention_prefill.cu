@@ -52,6 +52,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                          const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int H, int KV,
                          float scale_log2, int window) {
+  tlc_pdl();
   constexpr int CH = HD / 8;                  // 16-byte chunks per row
   constexpr int TILE_BYTES = FA_BN * HD * 2;
   extern __shared__ __align__(128) uint8_t fa_smem[];
@@ -256,9 +257,9 @@ extern "C" int tlc_attention_prefill(const void* q, const void* k_pages, const v
   const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
   const int smem = (FA_BM + 4 * FA_BN) * hd * 2;
   if (hd == 64)
-    attention_prefill_kernel<64><<<grid, 128, smem, stream>>>(qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window);
+    tlc_launch(attention_prefill_kernel<64>, dim3(grid), dim3(128), smem, stream, qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window);
   else if (hd == 128)
-    attention_prefill_kernel<128><<<grid, 128, smem, stream>>>(qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window);
+    tlc_launch(attention_prefill_kernel<128>, dim3(grid), dim3(128), smem, stream, qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window);
   else
     return tlc_fail(-1, "attention(prefill): head size %d is not built (64 and 128 are)", hd);
   TLC_CHECK_LAUNCH("attention(prefill)");

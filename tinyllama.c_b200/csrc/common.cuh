@@ -29,6 +29,37 @@ int tlc_fail(int code, const char* fmt, ...);
     if (!(cond)) return tlc_fail(-1, __VA_ARGS__);   \
   } while (0)
 
+// ---- launches -----------------------------------------------------------------------------
+// Every kernel begins with tlc_pdl(): it lets the next kernel of the stream be scheduled early
+// and then waits until the previous kernel has finished and its writes are visible.  Both
+// instructions do nothing unless the launch carries the programmatic-serialization attribute,
+// which tlc_launch() adds when tlc_set_pdl(1) is in effect (the decode graph turns it on while
+// it is captured: a decode step is hundreds of short kernels, and this hides the gap between
+// one kernel's last block and the next kernel's first).
+extern int g_tlc_pdl;
+extern "C" void tlc_set_pdl(int on);
+
+__device__ __forceinline__ void tlc_pdl() {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t tlc_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_tlc_pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -7,6 +7,9 @@
 #include "common.cuh"
 #include <stdarg.h>
 
+int g_tlc_pdl = 0;
+extern "C" void tlc_set_pdl(int on) { g_tlc_pdl = on; }
+
 static thread_local char g_err[512];
 extern "C" const char* tlc_last_error() { return g_err; }
 int tlc_fail(int code, const char* fmt, ...) {
@@ -21,6 +24,7 @@ int tlc_fail(int code, const char* fmt, ...) {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, int D, int V,
                              float scale, float* __restrict__ out) {
+  tlc_pdl();
   const int t = blockIdx.x;
   int tok = tokens[t];
   tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);   // ids are validated on the host; never read out of bounds
@@ -32,19 +36,41 @@ extern "C" int tlc_embed(const int* tokens, const void* table, int table_dtype, 
                          float* out, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_DISPATCH_DTYPE(table_dtype, TW,
-                     embed_kernel<TW><<<T, 256, 0, stream>>>(tokens, (const TW*)table, D, V, scale, out));
+                     tlc_launch(embed_kernel<TW>, dim3(T), dim3(256), 0, stream, tokens, (const TW*)table, D, V, scale, out));
   TLC_CHECK_LAUNCH("embed");
   return 0;
 }
 
 // ---- RMSNorm of 32-bit rows ----------------------------------------------------------
+// One block per row.  The row stays in registers between the sum of squares and the scaling
+// when it fits (up to RMS_MAX_PER_THREAD values per thread), otherwise it is read twice.
+#define RMS_MAX_PER_THREAD 16
 template <typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
-                               float eps, int D, TO* __restrict__ out) {
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+               float eps, int D, TO* __restrict__ out) {
+  tlc_pdl();
   __shared__ float red[33];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
   float ss = 0.f;
+  if (D <= 256 * RMS_MAX_PER_THREAD) {
+    float v[RMS_MAX_PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < RMS_MAX_PER_THREAD; i++) {
+      const int d = threadIdx.x + i * 256;
+      v[i] = d < D ? xr[d] : 0.f;
+      ss += v[i] * v[i];
+    }
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < RMS_MAX_PER_THREAD; i++) {
+      const int d = threadIdx.x + i * 256;
+      if (d < D) out[(size_t)r * D + d] = from_f32<TO>(v[i] * s * w[d]);
+    }
+    return;
+  }
   for (int d = threadIdx.x; d < D; d += blockDim.x) { float v = xr[d]; ss += v * v; }
   ss = block_sum(ss, red);
   const float s = 1.0f / sqrtf(ss / (float)D + eps);
@@ -54,7 +80,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 extern "C" int tlc_rmsnorm(const float* x, const int* rows, const float* w, float eps, int R, int D, void* out,
                            int out_dtype, cudaStream_t stream) {
   if (R == 0) return 0;
-  TLC_DISPATCH_DTYPE(out_dtype, TO, rmsnorm_kernel<TO><<<R, 256, 0, stream>>>(x, rows, w, eps, D, (TO*)out));
+  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_kernel<TO>, dim3(R), dim3(256), 0, stream, x, rows, w, eps, D, (TO*)out));
   TLC_CHECK_LAUNCH("rmsnorm");
   return 0;
 }
@@ -62,9 +88,11 @@ extern "C" int tlc_rmsnorm(const float* x, const int* rows, const float* w, floa
 // ---- gate and grouped RMSNorm of the scan output ---------------------------------------
 // y [T, Di] 32-bit; z a strided slice of the input projection; one block per (row, group).
 template <typename TZ, typename TO>
-__global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int ldz,
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int ldz,
                                      const float* __restrict__ w, float eps, int Di, int gs, int norm_before_gate,
                                      TO* __restrict__ out) {
+  tlc_pdl();
   __shared__ float red[33];
   const int t = blockIdx.x, g = blockIdx.y;
   const float* yr = y + (size_t)t * Di + (size_t)g * gs;
@@ -76,6 +104,30 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __re
   }
   const float* wg = w + (size_t)g * gs;
   float ss = 0.f;
+  if (gs <= 256 * RMS_MAX_PER_THREAD) {
+    // one pass: y and the gate are read once; what is normalised stays in registers
+    float v[RMS_MAX_PER_THREAD], gate[RMS_MAX_PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < RMS_MAX_PER_THREAD; i++) {          // every load is issued before the first exp
+      const int d = threadIdx.x + i * 256;
+      gate[i] = d < gs ? to_f32(zr[d]) : 0.f;
+      v[i] = d < gs ? yr[d] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < RMS_MAX_PER_THREAD; i++) {
+      gate[i] = silu_f(gate[i]);
+      if (!norm_before_gate) v[i] *= gate[i];
+      ss += v[i] * v[i];
+    }
+    ss = block_sum(ss, red);
+    const float s = 1.0f / sqrtf(ss / (float)gs + eps);
+#pragma unroll
+    for (int i = 0; i < RMS_MAX_PER_THREAD; i++) {
+      const int d = threadIdx.x + i * 256;
+      if (d < gs) o[d] = from_f32<TO>(norm_before_gate ? (v[i] * s * wg[d]) * gate[i] : v[i] * s * wg[d]);
+    }
+    return;
+  }
   for (int d = threadIdx.x; d < gs; d += blockDim.x) {
     float v = yr[d];
     if (!norm_before_gate) v *= silu_f(to_f32(zr[d]));
@@ -98,7 +150,7 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int
   TLC_REQUIRE(n_groups > 0 && Di % n_groups == 0, "gated_rmsnorm: width %d is not a multiple of %d groups", Di, n_groups);
   const int gs = Di / n_groups;
   dim3 grid(T, n_groups);
-  TLC_DISPATCH_DTYPE(z_dtype, TZ, TLC_DISPATCH_DTYPE(out_dtype, TO, gated_rmsnorm_kernel<TZ, TO><<<grid, 256, 0, stream>>>(
+  TLC_DISPATCH_DTYPE(z_dtype, TZ, TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_kernel<TZ, TO>, dim3(grid), dim3(256), 0, stream, 
       y, (const TZ*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out)));
   TLC_CHECK_LAUNCH("gated_rmsnorm");
   return 0;
@@ -107,6 +159,7 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int
 // ---- SwiGLU product: out = silu(gate) * up, gate|up side by side in one row ---------------
 template <typename TI, typename T>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total) {
+  tlc_pdl();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t t = i / F;
@@ -120,7 +173,7 @@ extern "C" int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, vo
   const size_t total = (size_t)T * F;
   if (total == 0) return 0;
   const unsigned blocks = (unsigned)((total + 255) / 256);
-  TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, swiglu_kernel<TI, TT><<<blocks, 256, 0, stream>>>(
+  TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(swiglu_kernel<TI, TT>, dim3(blocks), dim3(256), 0, stream, 
       (const TI*)gu, ld, F, (TT*)out, total)));
   TLC_CHECK_LAUNCH("swiglu");
   return 0;
@@ -129,12 +182,13 @@ extern "C" int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, vo
 // ---- gather rows of a 32-bit matrix ------------------------------------------------------
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, int D,
                                    float* __restrict__ out) {
+  tlc_pdl();
   const float* xr = x + (size_t)rows[blockIdx.x] * D;
   for (int d = threadIdx.x; d < D; d += blockDim.x) out[(size_t)blockIdx.x * D + d] = xr[d];
 }
 extern "C" int tlc_gather_rows(const float* x, const int* rows, int R, int D, float* out, cudaStream_t stream) {
   if (R == 0) return 0;
-  gather_rows_kernel<<<R, 256, 0, stream>>>(x, rows, D, out);
+  tlc_launch(gather_rows_kernel, dim3(R), dim3(256), 0, stream, x, rows, D, out);
   TLC_CHECK_LAUNCH("gather_rows");
   return 0;
 }

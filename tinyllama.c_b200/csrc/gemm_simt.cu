@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(256)
 gemm_tiled_kernel(const TA* __restrict__ a, int lda, const TW* __restrict__ w, int ldw, TO* __restrict__ out, int ldo,
                   const float* __restrict__ colscale, const float* __restrict__ colbias, int accumulate, int M, int N,
                   int K) {
+  tlc_pdl();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -71,6 +72,7 @@ __global__ void __launch_bounds__(256)
 gemm_skinny_kernel(const TA* __restrict__ a, int lda, const TW* __restrict__ w, int ldw, TO* __restrict__ out, int ldo,
                    const float* __restrict__ colscale, const float* __restrict__ colbias, int accumulate, int M, int N,
                    int K, int m_base) {
+  tlc_pdl();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * (blockDim.x >> 5) + warp;
   if (n >= N) return;
@@ -103,6 +105,7 @@ __global__ void __launch_bounds__(256)
 gemm_skinny_bf16x8_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                           TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                           const float* __restrict__ colbias, int accumulate, int M, int N, int K, int m_base) {
+  tlc_pdl();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * (blockDim.x >> 5) + warp;
   if (n >= N) return;
@@ -154,16 +157,16 @@ static int launch_simt(const void* a, int lda, const void* w, int ldw, void* out
     const unsigned blocks = (unsigned)((N + 7) / 8);
     for (int mb = 0; mb < M; mb += MT) {
       if (vec)
-        gemm_skinny_bf16x8_kernel<TO, MT><<<blocks, 256, 0, stream>>>(
+        tlc_launch(gemm_skinny_bf16x8_kernel<TO, MT>, dim3(blocks), dim3(256), 0, stream, 
             (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)w, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M,
             N, K, mb);
       else
-        gemm_skinny_kernel<TA, TW, TO, MT><<<blocks, 256, 0, stream>>>((const TA*)a, lda, (const TW*)w, ldw, (TO*)out,
+        tlc_launch(gemm_skinny_kernel<TA, TW, TO, MT>, dim3(blocks), dim3(256), 0, stream, (const TA*)a, lda, (const TW*)w, ldw, (TO*)out,
                                                                        ldo, colscale, colbias, accumulate, M, N, K, mb);
     }
   } else {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_tiled_kernel<TA, TW, TO><<<grid, 256, 0, stream>>>((const TA*)a, lda, (const TW*)w, ldw, (TO*)out, ldo,
+    tlc_launch(gemm_tiled_kernel<TA, TW, TO>, dim3(grid), dim3(256), 0, stream, (const TA*)a, lda, (const TW*)w, ldw, (TO*)out, ldo,
                                                             colscale, colbias, accumulate, M, N, K);
   }
   TLC_CHECK_LAUNCH("linear(simt)");
@@ -207,6 +210,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                        TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                        const float* __restrict__ colbias, int accumulate, int M, int N, int K) {
+  tlc_pdl();
   __shared__ float red[SK_WARPS][MG][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -283,11 +287,11 @@ static void launch_skinny_mg(const __nv_bfloat16* a, int lda, const __nv_bfloat1
   const unsigned blocks = (unsigned)((N + 15) / 16);
   const int n_steps = ((K >> 3) + 3) >> 2;
   if (n_steps <= SK_WARPS * 2)
-    gemm_skinny_mma_kernel<TO, MG, 2><<<blocks, SK_WARPS * 32, 0, stream>>>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 2>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
   else if (n_steps <= SK_WARPS * 4)
-    gemm_skinny_mma_kernel<TO, MG, 4><<<blocks, SK_WARPS * 32, 0, stream>>>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 4>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
   else
-    gemm_skinny_mma_kernel<TO, MG, 8><<<blocks, SK_WARPS * 32, 0, stream>>>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 8>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
 }
 
 template <typename TO>

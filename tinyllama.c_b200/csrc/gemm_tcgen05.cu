@@ -144,6 +144,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                     const float* __restrict__ colbias, int accumulate, int M, int N, int K, ErrWords* err) {
+  tlc_pdl();
   using S = Smem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -370,7 +371,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, con
   auto kern = gemm_tcgen05_kernel<TO, BN, STAGES>;
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
   dim3 grid(tiles < g_sms ? tiles : g_sms);
-  kern<<<grid, THREADS, S::TOTAL, stream>>>(ma, mb, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, g_err_dev);
+  tlc_launch(kern, dim3(grid), dim3(THREADS), S::TOTAL, stream, ma, mb, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, g_err_dev);
   TLC_CHECK_LAUNCH("linear(tcgen05)");
   return 0;
 }

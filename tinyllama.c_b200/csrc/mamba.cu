@@ -22,6 +22,7 @@ __global__ void mamba_conv_kernel(const T* __restrict__ proj, int ld, int xbc_of
                                   const int* __restrict__ row_seq, const int* __restrict__ slots,
                                   const int* __restrict__ start_pos, float* __restrict__ xbc_out,
                                   float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs) {
+  tlc_pdl();
   const int t = blockIdx.x;
   const int b = row_seq[t];
   const int i = t - cu_seqlens[b];                  // index of this row inside its sequence's new tokens
@@ -53,6 +54,7 @@ template <typename T>
 __global__ void mamba_conv_state_kernel(const T* __restrict__ proj, int ld, int xbc_off, float* __restrict__ conv_state,
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                                         const int* __restrict__ start_pos, int Cd, int K) {
+  tlc_pdl();
   const int b = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= Cd) return;
@@ -74,22 +76,69 @@ __global__ void mamba_conv_state_kernel(const T* __restrict__ proj, int ld, int 
     if (j < K - 1) st[(size_t)j * Cd + c] = v[j];
 }
 
+// One-token steps: every sequence brings exactly one row, so a thread owns one (sequence, channel):
+// it reads the window, convolves, and writes the shifted window back -- one kernel instead of two.
+template <typename T>
+__global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_off,
+                                         const float* __restrict__ w, const float* __restrict__ bias,
+                                         const float* __restrict__ dt_bias, const float* __restrict__ A,
+                                         float* __restrict__ conv_state, const int* __restrict__ slots,
+                                         const int* __restrict__ start_pos, float* __restrict__ xbc_out,
+                                         float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs) {
+  tlc_pdl();
+  const int b = blockIdx.x;                          // row b belongs to sequence b
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const bool has_state = start_pos[b] > 0;
+  float* st = conv_state + (size_t)slots[b] * (K - 1) * Cd;
+  if (c < Cd) {
+    const float cur = to_f32(proj[(size_t)b * ld + xbc_off + c]);
+    float sum = cur * w[(size_t)c * K + (K - 1)];
+    float prev[CONV_MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_TAPS; k++) {
+      if (k < K - 1) {
+        prev[k] = has_state ? st[(size_t)k * Cd + c] : 0.f;
+        sum = fmaf(prev[k], w[(size_t)c * K + k], sum);
+      }
+    }
+    if (bias) sum += bias[c];
+    xbc_out[(size_t)b * Cd + c] = silu_f(sum);
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_TAPS; k++) {
+      if (k < K - 2) st[(size_t)k * Cd + c] = prev[k + 1];
+      else if (k == K - 2) st[(size_t)k * Cd + c] = cur;
+    }
+  }
+  if (c < Hs) {
+    const float dtv = softplus_f(to_f32(proj[(size_t)b * ld + dt_off + c]) + dt_bias[c]);
+    dt_out[(size_t)b * Hs + c] = dtv;
+    dA_out[(size_t)b * Hs + c] = expf(dtv * A[c]);
+  }
+}
+
 extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, int dt_off, const float* w,
                               const float* bias, const float* dt_bias, const float* A, float* conv_state,
                               const int* cu_seqlens, const int* row_seq, const int* slots, const int* start_pos,
                               float* xbc_out, float* dt_out, float* dA_out, int T, int B, int Cd, int K, int Hs,
-                              cudaStream_t stream) {
+                              int single_rows, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(K >= 1 && K - 1 <= CONV_MAX_TAPS, "mamba_conv: %d taps exceed the kernel's limit of %d", K, CONV_MAX_TAPS + 1);
   TLC_REQUIRE(Hs <= Cd, "mamba_conv: more heads (%d) than conv channels (%d)", Hs, Cd);
   dim3 grid(T, (Cd + 255) / 256);
   dim3 grid2(B, (Cd + 255) / 256);
+  if (single_rows && T == B) {
+    TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(mamba_conv_decode_kernel<TT>, dim3(grid2), dim3(256), 0, stream, 
+        (const TT*)proj, ld, xbc_off, dt_off, w, bias, dt_bias, A, conv_state, slots, start_pos, xbc_out, dt_out, dA_out,
+        Cd, K, Hs));
+    TLC_CHECK_LAUNCH("mamba_conv(decode)");
+    return 0;
+  }
   TLC_DISPATCH_DTYPE(dtype, TT, {
-    mamba_conv_kernel<TT><<<grid, 256, 0, stream>>>((const TT*)proj, ld, xbc_off, dt_off, w, bias, dt_bias, A,
+    tlc_launch(mamba_conv_kernel<TT>, dim3(grid), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, w, bias, dt_bias, A,
                                                     conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out,
                                                     dA_out, Cd, K, Hs);
     if (K > 1)
-      mamba_conv_state_kernel<TT><<<grid2, 256, 0, stream>>>((const TT*)proj, ld, xbc_off, conv_state, cu_seqlens, slots,
+      tlc_launch(mamba_conv_state_kernel<TT>, dim3(grid2), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, conv_state, cu_seqlens, slots,
                                                              start_pos, Cd, K);
   });
   TLC_CHECK_LAUNCH("mamba_conv");
@@ -120,6 +169,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
                 const int* __restrict__ seq_seg_start, const int* __restrict__ slots,
                 const int* __restrict__ start_pos, float* __restrict__ y, float* __restrict__ chunk_decay, int mode,
                 int Hs, int P, int N, int G, int Cd) {
+  tlc_pdl();
   extern __shared__ float sm[];
   const int seg = blockIdx.x, h = blockIdx.y;
   const int b = seg_seq ? seg_seq[seg] : seg;
@@ -232,6 +282,7 @@ __global__ void __launch_bounds__(256)
 ssm_state_pass_kernel(const float* __restrict__ chunk_decay, const float* __restrict__ state,
                       float* __restrict__ chunk_state, const int* __restrict__ seq_seg_start,
                       const int* __restrict__ slots, const int* __restrict__ start_pos, int Hs, int PN) {
+  tlc_pdl();
   const int b = blockIdx.x, h = blockIdx.y;
   const int e = blockIdx.z * blockDim.x + threadIdx.x;
   const int c0 = seq_seg_start[b], c1 = seq_seg_start[b + 1];
@@ -257,7 +308,7 @@ static int launch_scan(const float* xbc, const float* dt, const float* dA, const
   constexpr int RP = 4;
   dim3 grid(n_seg, Hs, (P + 4 * RP - 1) / (4 * RP));
   const size_t smem = (size_t)SCAN_TT * (2 * N + 4 * RP + 2) * sizeof(float);
-  ssm_scan_kernel<NPL, RP><<<grid, 128, smem, stream>>>(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq,
+  tlc_launch(ssm_scan_kernel<NPL, RP>, dim3(grid), dim3(128), smem, stream, xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq,
                                                         seq_seg_start, slots, start_pos, y, chunk_decay, mode, Hs, P, N, G,
                                                         Cd);
   TLC_CHECK_LAUNCH("ssm_scan");
@@ -305,7 +356,7 @@ extern "C" int tlc_ssm_scan_chunked(const float* xbc, const float* dt, const flo
   if (int rc = scan_dispatch(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos,
                              y, chunk_decay, SCAN_CHUNK_STATE, n_seg, Hs, P, N, G, Cd, stream)) return rc;
   dim3 grid(B, Hs, (P * N + 255) / 256);
-  ssm_state_pass_kernel<<<grid, 256, 0, stream>>>(chunk_decay, state, chunk_state, seq_seg_start, slots, start_pos, Hs,
+  tlc_launch(ssm_state_pass_kernel, dim3(grid), dim3(256), 0, stream, chunk_decay, state, chunk_state, seq_seg_start, slots, start_pos, Hs,
                                                   P * N);
   TLC_CHECK_LAUNCH("ssm_state_pass");
   return scan_dispatch(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos, y,

@@ -62,6 +62,7 @@ __device__ int block_argmax(const float* v, int V, float* red, int* redi) {
 }
 
 __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+  tlc_pdl();
   __shared__ float red[33];
   __shared__ int redi[33];
   const int r = block_argmax(logits + (size_t)blockIdx.x * V, V, red, redi);
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __res
 
 extern "C" int tlc_argmax(const float* logits, int R, int V, int* out, cudaStream_t stream) {
   if (R == 0) return 0;
-  argmax_kernel<<<R, SAMP_THREADS, 0, stream>>>(logits, V, out);
+  tlc_launch(argmax_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, logits, V, out);
   TLC_CHECK_LAUNCH("argmax");
   return 0;
 }
@@ -126,6 +127,7 @@ __device__ float block_exclusive_scan(float v, float* scan_buf, float* total) {
 __global__ void __launch_bounds__(SAMP_THREADS)
 sample_kernel(const float* __restrict__ logits, float* __restrict__ work, const int* __restrict__ history,
               const float* __restrict__ uniforms, SampleParams sp, int V, int* __restrict__ out) {
+  tlc_pdl();
   __shared__ float red[33];
   __shared__ int redi[33];
   __shared__ float scan_buf[33];
@@ -287,7 +289,7 @@ extern "C" int tlc_sample(const float* logits, float* work, const int* history, 
   TLC_REQUIRE(min_p >= 0.f && min_p <= 1.f, "sample: min-p must be in [0, 1], got %g", min_p);
   SampleParams sp{temperature, top_p, min_p, repeat_penalty, frequency_penalty, presence_penalty, top_k,
                   history ? n_history : 0};
-  sample_kernel<<<R, SAMP_THREADS, 0, stream>>>(logits, work, history, uniforms, sp, V, out);
+  tlc_launch(sample_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, logits, work, history, uniforms, sp, V, out);
   TLC_CHECK_LAUNCH("sample");
   return 0;
 }

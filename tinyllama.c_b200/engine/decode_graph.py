@@ -11,6 +11,7 @@ contents of the buffers.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -18,6 +19,9 @@ import torch
 from .. import ops
 from ..parts.base import StepInfo
 from ..sampling.params import SamplingParams
+
+
+USE_PDL = bool(int(os.environ.get("TLC_PDL", "1")))
 
 
 class DecodeGraph:
@@ -69,9 +73,14 @@ class DecodeGraph:
         stream = torch.cuda.Stream(device=self.model.device)
         stream.wait_stream(torch.cuda.current_stream())
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(stream):
-            with torch.cuda.graph(self.graph, stream=stream):
-                self._body()
+        lib = ops.library()
+        lib.tlc_set_pdl(1 if USE_PDL else 0)      # kernels of the graph overlap their launch with their predecessor's tail
+        try:
+            with torch.cuda.stream(stream):
+                with torch.cuda.graph(self.graph, stream=stream):
+                    self._body()
+        finally:
+            lib.tlc_set_pdl(0)
         torch.cuda.current_stream().wait_stream(stream)
         self.launches = ops.launch_count() - before
 

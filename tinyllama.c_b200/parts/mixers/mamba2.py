@@ -85,7 +85,8 @@ class Mamba2Mixer(Part):
         dt = act_empty((T, self.Hs), normed, f32)
         dA = act_empty((T, self.Hs), normed, f32)
         ops.mamba_conv(proj, self.Di, self.Di + self.Cd, self.conv_w, self.conv_b, self.dt_bias, self.A, conv_state,
-                       step.cu_seqlens, step.row_seq, step.slots, step.start_pos, xbc, dt, dA)
+                       step.cu_seqlens, step.row_seq, step.slots, step.start_pos, xbc, dt, dA,
+                       step.max_new == 1)
         y = act_empty((T, self.Di), normed, f32)
         ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs, self.P,
                      self.N, self.G, step.chunks)
