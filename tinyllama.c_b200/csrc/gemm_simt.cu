@@ -211,7 +211,7 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
                        TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                        const float* __restrict__ colbias, int accumulate, int M, int N, int K) {
   tlc_pdl();
-  __shared__ float red[SK_WARPS][MG][32][4];
+  __shared__ float red[SK_WARPS][MG < 4 ? MG : 4][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int n0 = blockIdx.x * 16;
@@ -257,25 +257,32 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
       }
     }
   }
+  // the warps' partial sums meet in shared memory, at most four row groups at a time
+  constexpr int RG = MG < 4 ? MG : 4;
+#pragma unroll 1
+  for (int g0 = 0; g0 < MG; g0 += RG) {
+    if (g0 > 0) __syncthreads();
 #pragma unroll
-  for (int mg = 0; mg < MG; mg++)
+    for (int mg = 0; mg < MG; mg++)
+      if (mg >= g0 && mg < g0 + RG)
 #pragma unroll
-    for (int j = 0; j < 4; j++) red[warp][mg][lane][j] = acc[mg][j];
-  __syncthreads();
-  // one thread per output value: sum the warps' partial sums in warp order, epilogue, store
-  for (int idx = threadIdx.x; idx < MG * 128; idx += blockDim.x) {
-    const int mg = idx >> 7, ln = (idx & 127) >> 2, j = idx & 3;
-    float v = 0.f;
+        for (int j = 0; j < 4; j++) red[warp][mg - g0][lane][j] = acc[mg][j];
+    __syncthreads();
+    // one thread per output value: sum the warps' partial sums in warp order, epilogue, store
+    for (int idx = threadIdx.x; idx < RG * 128; idx += blockDim.x) {
+      const int mg = idx >> 7, ln = (idx & 127) >> 2, j = idx & 3;
+      float v = 0.f;
 #pragma unroll
-    for (int ww = 0; ww < SK_WARPS; ww++) v += red[ww][mg][ln][j];
-    const int n = n0 + (ln >> 2) + (j >= 2 ? 8 : 0);
-    const int m = mg * 8 + 2 * (ln & 3) + (j & 1);
-    if (n < N && m < M) {
-      if (colscale) v *= colscale[n];
-      if (colbias) v += colbias[n];
-      TO* o = out + (size_t)m * ldo + n;
-      if (accumulate) v += to_f32(*o);
-      *o = from_f32<TO>(v);
+      for (int ww = 0; ww < SK_WARPS; ww++) v += red[ww][mg][ln][j];
+      const int n = n0 + (ln >> 2) + (j >= 2 ? 8 : 0);
+      const int m = (g0 + mg) * 8 + 2 * (ln & 3) + (j & 1);
+      if (n < N && m < M) {
+        if (colscale) v *= colscale[n];
+        if (colbias) v += colbias[n];
+        TO* o = out + (size_t)m * ldo + n;
+        if (accumulate) v += to_f32(*o);
+        *o = from_f32<TO>(v);
+      }
     }
   }
 }
@@ -301,14 +308,15 @@ static int launch_skinny_mma(const void* a, int lda, const void* w, int ldw, voi
   const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
   if (M <= 8) launch_skinny_mg<TO, 1>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
   else if (M <= 16) launch_skinny_mg<TO, 2>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
-  else launch_skinny_mg<TO, 4>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  else if (M <= 32) launch_skinny_mg<TO, 4>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  else launch_skinny_mg<TO, 8>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
   TLC_CHECK_LAUNCH("linear(skinny mma)");
   return 0;
 }
 
-// bfloat16 operands with 16-byte aligned rows and at most 32 rows: the weight-streaming kernel.
+// bfloat16 operands with 16-byte aligned rows and at most 64 rows: the weight-streaming kernel.
 extern "C" int tlc_linear_skinny_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int M, int K) {
-  return a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && M <= 32 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
+  return a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && M <= 64 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
          ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0);
 }
 

@@ -404,12 +404,16 @@ extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, in
                           int out_dtype, int ldo, const float* colscale, const float* colbias, int accumulate, int M,
                           int N, int K, int min_rows_for_tensor_cores, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
-  if (M < min_rows_for_tensor_cores && tlc_linear_skinny_ok(a_dtype, lda, a, w_dtype, ldw, w, M, K)) {
+  // Up to 32 rows the weight-streaming kernel is always best.  From 33 to 64 rows it re-reads the
+  // activations once per 16 output columns, which only pays while the tiled kernel would have too
+  // few tiles to keep the GPU busy (narrow outputs).
+  const bool tiled_ok = M >= min_rows_for_tensor_cores && tlc_linear_tcgen05_ok(a_dtype, lda, a, w_dtype, ldw, w, K);
+  if (tlc_linear_skinny_ok(a_dtype, lda, a, w_dtype, ldw, w, M, K) && (M <= 32 || N <= 3072 || !tiled_ok)) {
     TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N,
                 K, lda, ldw, ldo);
     return tlc_linear_skinny(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, accumulate, M, N, K, stream);
   }
-  if (M < min_rows_for_tensor_cores || !tlc_linear_tcgen05_ok(a_dtype, lda, a, w_dtype, ldw, w, K))
+  if (!tiled_ok)
     return tlc_linear_simt(a, a_dtype, lda, w, w_dtype, ldw, out, out_dtype, ldo, colscale, colbias, accumulate, M, N, K,
                            stream);
   TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N, K,

@@ -198,9 +198,9 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
 
 
 # ---- linear -----------------------------------------------------------------------------
-# Fewest rows for which bfloat16 products go to the tensor-core kernel; below it the weight
-# matrix is streamed once by the warp-per-column kernel.  TLC_TENSOR_CORE_MIN_ROWS overrides
-# it (a huge value keeps everything on the CUDA cores).
+# Fewest rows for which bfloat16 products may go to the tiled tcgen05 kernel; with fewer rows
+# (and, up to 64 rows, for narrow outputs) the weight matrix is streamed once by the mma.sync
+# kernel.  TLC_TENSOR_CORE_MIN_ROWS overrides it (a huge value keeps the tiled kernel out).
 TENSOR_CORE_MIN_ROWS = int(os.environ.get("TLC_TENSOR_CORE_MIN_ROWS", "33"))
 
 
