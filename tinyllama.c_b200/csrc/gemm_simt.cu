@@ -206,7 +206,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 constexpr int SK_WARPS = 16;          // warps per block, each with its own slices of K
 
 template <typename TO, int MG, int U>
-__global__ void __launch_bounds__(SK_WARPS * 32)
+__global__ void __launch_bounds__(SK_WARPS * 32, (MG <= 2 && U <= 4) ? 2 : 1)
 gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                        TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                        const float* __restrict__ colbias, int accumulate, int M, int N, int K) {
@@ -293,12 +293,11 @@ static void launch_skinny_mg(const __nv_bfloat16* a, int lda, const __nv_bfloat1
                              cudaStream_t stream) {
   const unsigned blocks = (unsigned)((N + 15) / 16);
   const int n_steps = ((K >> 3) + 3) >> 2;
+  // U steps per warp and round; with U <= 4 and few row groups two blocks fit on an SM
   if (n_steps <= SK_WARPS * 2)
     tlc_launch(gemm_skinny_mma_kernel<TO, MG, 2>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
-  else if (n_steps <= SK_WARPS * 4)
-    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 4>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
   else
-    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 8>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 4>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
 }
 
 template <typename TO>
