@@ -144,7 +144,7 @@ def mamba_conv(proj, xbc_off, dt_off, w, bias, dt_bias, A, conv_state, cu_seqlen
     dA_out.copy_(torch.exp(dtv * _f(A)).to(dA_out.dtype))
 
 
-def ssm_scan(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, Hs, P, N, G, chunks=None):
+def ssm_scan(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, Hs, P, N, G, chunks=None, A=None):
     Di = Hs * P
     for b in range(slots.numel()):
         t0, t1 = int(cu_seqlens[b]), int(cu_seqlens[b + 1])

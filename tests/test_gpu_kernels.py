@@ -276,6 +276,40 @@ def test_ssm_scan_in_parallel_chunks(Hs, P, N, G):
         assert (ref - got).abs().max() <= 3e-5 * ref.abs().max(), f"output {i}"
 
 
+@pytest.mark.parametrize("Hs,P,N,G", [(4, 64, 256, 1), (6, 64, 64, 2), (2, 128, 128, 1)])
+def test_ssm_scan_in_matrix_form_on_tensor_cores(Hs, P, N, G):
+    """The chunked matrix form (TF32 operands) against the sequential recurrence; one sequence
+    continues from its slot's state, one is shorter than a chunk, one ends mid-chunk."""
+    g = gen(15)
+    Di, Cd = Hs * P, Hs * P + 2 * G * N
+    starts, lens = [0, 9, 0], [300, 70, 129]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32)
+    T = sum(lens)
+    seg_start, seg_seq, seq_seg_start = [], [], [0]
+    for b, n in enumerate(lens):
+        for off in range(0, n, 128):
+            seg_start.append(int(cu[b]) + off)
+            seg_seq.append(b)
+        seq_seg_start.append(len(seg_seq))
+    seg_start.append(T)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32)
+    dt = torch.rand(T, Hs, generator=g) * 0.1
+    A = -torch.rand(Hs, generator=g) * 8
+    dA = torch.exp(dt * A)
+    args = [rnd(g, T, Cd), dt, dA, 1 + rnd(g, Hs, scale=0.1), rnd(g, 4, Hs, P, N), cu, slots, start_pos,
+            torch.empty(T, Di), Hs, P, N, G, (i32(seg_start), i32(seg_seq), i32(seq_seg_start)), A]
+    gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args]
+    gpu[13] = tuple(t.cuda() for t in args[13])
+    ops.ssm_scan(*gpu)
+    ops_plain.ssm_scan(*args)
+    for i in (4, 8):
+        ref, got = args[i].double(), gpu[i].cpu().double()
+        # TF32 operands carry 11 bits: products are good to 2^-11 of their size, sums of ~N of them more
+        assert (ref - got).abs().max() <= 2e-3 * ref.abs().max(), f"output {i}: {(ref - got).abs().max()} of {ref.abs().max()}"
+        assert (ref - got).abs().mean() <= 2e-4 * ref.abs().max(), f"output {i} (mean)"
+
+
 def test_argmax_takes_the_first_maximum():
     g = gen(9)
     logits = rnd(g, 6, 1000)

@@ -278,26 +278,47 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
 
 // Pass 2: carries the state through a sequence's chunks.  chunk_state[c] holds the chunk's own
 // contribution on entry and the state *before* the chunk on exit.  grid (B, Hs, blocks over P*N).
+// With write_final the state after the last chunk goes to the sequence's slot.
 __global__ void __launch_bounds__(256)
-ssm_state_pass_kernel(const float* __restrict__ chunk_decay, const float* __restrict__ state,
+ssm_state_pass_kernel(const float* __restrict__ chunk_decay, float* __restrict__ state,
                       float* __restrict__ chunk_state, const int* __restrict__ seq_seg_start,
-                      const int* __restrict__ slots, const int* __restrict__ start_pos, int Hs, int PN) {
+                      const int* __restrict__ slots, const int* __restrict__ start_pos, int Hs, int PN, int write_final) {
   tlc_pdl();
   const int b = blockIdx.x, h = blockIdx.y;
   const int e = blockIdx.z * blockDim.x + threadIdx.x;
   const int c0 = seq_seg_start[b], c1 = seq_seg_start[b + 1];
-  if (c1 - c0 <= 0) return;
-  float s = 0.f;
-  if (e < PN && start_pos[b] > 0) s = state[((size_t)slots[b] * Hs + h) * PN + e];
-  for (int c = c0; c < c1; c++) {
-    const float decay = chunk_decay[(size_t)c * Hs + h];
-    if (e < PN) {
-      float* cs = chunk_state + ((size_t)c * Hs + h) * PN + e;
-      const float own = *cs;
-      *cs = s;
-      s = fmaf(s, decay, own);
+  if (c1 - c0 <= 0 || e >= PN) return;
+  float* slot = state + ((size_t)slots[b] * Hs + h) * PN + e;
+  float s = start_pos[b] > 0 ? *slot : 0.f;
+  constexpr int BATCH = 8;                 // chunks whose values are fetched together
+  for (int cb = c0; cb < c1; cb += BATCH) {
+    float own[BATCH], decay[BATCH];
+#pragma unroll
+    for (int i = 0; i < BATCH; i++) {
+      const int c = cb + i;
+      own[i] = c < c1 ? chunk_state[((size_t)c * Hs + h) * PN + e] : 0.f;
+      decay[i] = c < c1 ? chunk_decay[(size_t)c * Hs + h] : 1.f;
+    }
+#pragma unroll
+    for (int i = 0; i < BATCH; i++) {
+      const int c = cb + i;
+      if (c < c1) {
+        chunk_state[((size_t)c * Hs + h) * PN + e] = s;
+        s = fmaf(s, decay[i], own[i]);
+      }
     }
   }
+  if (write_final) *slot = s;
+}
+
+int tlc_ssm_state_pass_launch(const float* chunk_decay, float* state, float* chunk_state, const int* seq_seg_start,
+                              const int* slots, const int* start_pos, int B, int Hs, int PN, int write_final,
+                              cudaStream_t stream) {
+  dim3 grid(B, Hs, (PN + 255) / 256);
+  tlc_launch(ssm_state_pass_kernel, grid, dim3(256), 0, stream, chunk_decay, state, chunk_state, seq_seg_start, slots,
+             start_pos, Hs, PN, write_final);
+  TLC_CHECK_LAUNCH("ssm_state_pass");
+  return 0;
 }
 
 template <int NPL>
@@ -355,10 +376,8 @@ extern "C" int tlc_ssm_scan_chunked(const float* xbc, const float* dt, const flo
   float* chunk_decay = chunk_state + (size_t)n_seg * Hs * P * N;
   if (int rc = scan_dispatch(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos,
                              y, chunk_decay, SCAN_CHUNK_STATE, n_seg, Hs, P, N, G, Cd, stream)) return rc;
-  dim3 grid(B, Hs, (P * N + 255) / 256);
-  tlc_launch(ssm_state_pass_kernel, dim3(grid), dim3(256), 0, stream, chunk_decay, state, chunk_state, seq_seg_start, slots, start_pos, Hs,
-                                                  P * N);
-  TLC_CHECK_LAUNCH("ssm_state_pass");
+  if (int rc = tlc_ssm_state_pass_launch(chunk_decay, state, chunk_state, seq_seg_start, slots, start_pos, B, Hs, P * N, 0,
+                                         stream)) return rc;
   return scan_dispatch(xbc, dt, dA, Dskip, state, chunk_state, seg_start, seg_seq, seq_seg_start, slots, start_pos, y,
                        chunk_decay, SCAN_CHUNK_OUT, n_seg, Hs, P, N, G, Cd, stream);
 }

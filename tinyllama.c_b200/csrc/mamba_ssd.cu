@@ -1,0 +1,378 @@
+// Selective scan of long prompts in chunked matrix form, on the tensor cores.
+//
+// The recurrence is the reference's (cpu_op.c:932-951):
+//     S_t = S_{t-1} * exp(dt_t A) + (dt_t x_t) (x) B_t ,   y_t = S_t . C_t + D x_t
+// Over a chunk of rows i, j (L <= 128) with cum_i = sum_{k<=i} dt_k A this is three products:
+//     y_i  = sum_{j<=i} (C_i . B_j) exp(cum_i - cum_j) dt_j x_j        "inside the chunk"
+//          + exp(cum_i) * (S_in C_i)                                  "what came before"
+//          + D x_i
+//     S_c  = sum_j exp(cum_last - cum_j) dt_j x_j (x) B_j               the chunk's own contribution
+//     S_in(c+1) = exp(cum_last) S_in(c) + S_c                           carried in chunk order
+// Kernels: cumulative decay per (chunk, head); C B^T per (chunk, group) (shared by the group's
+// heads); the chunk states; the carry (ssm_state_pass in mamba.cu); the outputs.  The products
+// run on mma.sync.m16n8k8 with TF32 operands (10-bit mantissa; the 32-bit path of the library
+// never comes here) and 32-bit accumulation; decays are exponentials of non-positive numbers.
+// State, cumulative sums and all scalings are 32-bit.
+#include "common.cuh"
+
+int tlc_ssm_state_pass_launch(const float* chunk_decay, float* state, float* chunk_state, const int* seq_seg_start,
+                              const int* slots, const int* start_pos, int B, int Hs, int PN, int write_final,
+                              cudaStream_t stream);
+
+namespace {
+
+constexpr int Q = 128;       // rows per chunk (SCAN_CHUNK of the engine)
+
+__device__ __forceinline__ uint32_t tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---- cumulative log-decay per (chunk, head) --------------------------------------------------------
+// cum[t, h] = sum of dt*A over the chunk's rows up to t; chunk_decay[seg, h] = exp(cum at the last row)
+__global__ void ssd_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A,
+                                  const int* __restrict__ seg_start, float* __restrict__ cum,
+                                  float* __restrict__ chunk_decay, int Hs) {
+  tlc_pdl();
+  const int seg = blockIdx.x;
+  const int h = blockIdx.y * blockDim.x + threadIdx.x;
+  if (h >= Hs) return;
+  const int t0 = seg_start[seg], t1 = seg_start[seg + 1];
+  const float a = A[h];
+  float c = 0.f;
+  for (int t = t0; t < t1; t++) {
+    c = fmaf(dt[(size_t)t * Hs + h], a, c);
+    cum[(size_t)t * Hs + h] = c;
+  }
+  chunk_decay[(size_t)seg * Hs + h] = expf(c);
+}
+
+// ---- C B^T per (chunk, group): cb[seg, g, i, j] for j <= i -----------------------------------------
+// grid (seg, G, 2): a block of 4 warps computes 64 rows x 128 columns; K = N in slabs of 64.
+__global__ void __launch_bounds__(128)
+ssd_cb_kernel(const float* __restrict__ xbc, const int* __restrict__ seg_start, float* __restrict__ cb, int Di, int N,
+              int G, int Cd) {
+  tlc_pdl();
+  constexpr int LD = 68;
+  extern __shared__ uint32_t ssd_sm[];
+  uint32_t* Cs = ssd_sm;                 // [64][LD]   rows i, columns n
+  uint32_t* Bs = ssd_sm + 64 * LD;       // [Q][LD]    rows j, columns n
+  const int seg = blockIdx.x, g = blockIdx.y, half = blockIdx.z;
+  const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  const int i_base = half * 64 + warp * 16;                // this warp's 16 rows
+  const int n_tiles = min(16, (i_base + 16 + 7) / 8);      // columns j <= i only
+  float acc[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; j++)
+#pragma unroll
+    for (int k = 0; k < 4; k++) acc[j][k] = 0.f;
+  const float* Bg = xbc + Di + (size_t)g * N;
+  const float* Cg = xbc + Di + (size_t)G * N + (size_t)g * N;
+  for (int n0 = 0; n0 < N; n0 += 64) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < Q * 16; idx += 128) {           // 16 float4 per row
+      const int r = idx >> 4, c4 = (idx & 15) * 4;
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f), c = b;
+      if (r < L && n0 + c4 < N) b = *reinterpret_cast<const float4*>(Bg + (size_t)(t0 + r) * Cd + n0 + c4);
+      uint32_t* bd = Bs + r * LD + c4;
+      bd[0] = tf32(b.x); bd[1] = tf32(b.y); bd[2] = tf32(b.z); bd[3] = tf32(b.w);
+      if (r < 64) {
+        const int ri = half * 64 + r;
+        if (ri < L && n0 + c4 < N) c = *reinterpret_cast<const float4*>(Cg + (size_t)(t0 + ri) * Cd + n0 + c4);
+        uint32_t* cd = Cs + r * LD + c4;
+        cd[0] = tf32(c.x); cd[1] = tf32(c.y); cd[2] = tf32(c.z); cd[3] = tf32(c.w);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 8; kk++) {
+      const uint32_t* ar = Cs + (warp * 16 + gq) * LD + kk * 8 + tq;
+      const uint32_t a0 = ar[0], a1 = ar[8 * LD], a2 = ar[4], a3 = ar[8 * LD + 4];
+#pragma unroll
+      for (int j = 0; j < 16; j++) {
+        if (j < n_tiles) {
+          const uint32_t* br = Bs + (j * 8 + gq) * LD + kk * 8 + tq;
+          mma_tf32(acc[j], a0, a1, a2, a3, br[0], br[4]);
+        }
+      }
+    }
+  }
+  float* out = cb + (((size_t)seg * G + g) * Q) * Q;
+#pragma unroll
+  for (int j = 0; j < 16; j++) {
+    if (j < n_tiles) {
+      const int col = j * 8 + 2 * tq;
+      *reinterpret_cast<float2*>(out + (size_t)(i_base + gq) * Q + col) = make_float2(acc[j][0], acc[j][1]);
+      *reinterpret_cast<float2*>(out + (size_t)(i_base + gq + 8) * Q + col) = make_float2(acc[j][2], acc[j][3]);
+    }
+  }
+}
+
+// ---- chunk states: S_c[p, n] = sum_j w_j x[j, p] B[j, n],  w_j = exp(cum_last - cum_j) dt_j ----------
+// grid (seg, Hs, N / 128); 8 warps; output P x 128 with K = 128 rows of the chunk.
+template <int P>
+__global__ void __launch_bounds__(256)
+ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ cum,
+                       const int* __restrict__ seg_start, float* __restrict__ chunk_state, int Hs, int N, int G, int Cd) {
+  tlc_pdl();
+  constexpr int LDX = P + 8, LDB = 128 + 8;
+  extern __shared__ uint32_t ssd_sm[];
+  uint32_t* Xs = ssd_sm;                 // [j][p]   x * w
+  uint32_t* Bs = Xs + Q * LDX;           // [j][n]   128 columns of B
+  const int seg = blockIdx.x, h = blockIdx.y, nb = blockIdx.z * 128;
+  const int g = h / (Hs / G);
+  const int Di = Hs * P;
+  const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
+  const float cum_last = cum[(size_t)(t0 + L - 1) * Hs + h];
+  for (int idx = threadIdx.x; idx < Q * (P / 4); idx += 256) {
+    const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < L) {
+      v = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + (size_t)h * P + c4);
+      const float w = expf(cum_last - cum[(size_t)(t0 + r) * Hs + h]) * dt[(size_t)(t0 + r) * Hs + h];
+      v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+    }
+    uint32_t* d = Xs + r * LDX + c4;
+    d[0] = tf32(v.x); d[1] = tf32(v.y); d[2] = tf32(v.z); d[3] = tf32(v.w);
+  }
+  for (int idx = threadIdx.x; idx < Q * 32; idx += 256) {
+    const int r = idx >> 5, c4 = (idx & 31) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < L && nb + c4 < N) v = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + Di + (size_t)g * N + nb + c4);
+    uint32_t* d = Bs + r * LDB + c4;
+    d[0] = tf32(v.x); d[1] = tf32(v.y); d[2] = tf32(v.z); d[3] = tf32(v.w);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  // warp w: columns n in [16w, 16w+16) (2 tiles) x all P rows (P/16 tiles)
+  float acc[P / 16][2][4];
+#pragma unroll
+  for (int m = 0; m < P / 16; m++)
+#pragma unroll
+    for (int j = 0; j < 2; j++)
+#pragma unroll
+      for (int k = 0; k < 4; k++) acc[m][j][k] = 0.f;
+#pragma unroll 4
+  for (int kk = 0; kk < Q / 8; kk++) {
+    uint32_t b[2][2];
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+      const uint32_t* br = Bs + (kk * 8 + tq) * LDB + warp * 16 + j * 8 + gq;
+      b[j][0] = br[0];
+      b[j][1] = br[4 * LDB];
+    }
+#pragma unroll
+    for (int m = 0; m < P / 16; m++) {
+      const uint32_t* ar = Xs + (kk * 8 + tq) * LDX + m * 16 + gq;           // A(row p, col j) = Xs[j][p]
+      const uint32_t a0 = ar[0], a1 = ar[8], a2 = ar[4 * LDX], a3 = ar[4 * LDX + 8];
+#pragma unroll
+      for (int j = 0; j < 2; j++) mma_tf32(acc[m][j], a0, a1, a2, a3, b[j][0], b[j][1]);
+    }
+  }
+  float* out = chunk_state + (((size_t)seg * Hs + h) * P) * N;
+#pragma unroll
+  for (int m = 0; m < P / 16; m++)
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+      const int n = nb + warp * 16 + j * 8 + 2 * tq;
+      if (n < N) {
+        *reinterpret_cast<float2*>(out + (size_t)(m * 16 + gq) * N + n) = make_float2(acc[m][j][0], acc[m][j][1]);
+        *reinterpret_cast<float2*>(out + (size_t)(m * 16 + gq + 8) * N + n) = make_float2(acc[m][j][2], acc[m][j][3]);
+      }
+    }
+}
+
+// ---- chunk outputs ------------------------------------------------------------------------------------
+// grid (seg, Hs); 8 warps, warp w owns rows [16w, 16w+16) and all P columns.
+//   acc = M Xd + Cs S_in^T,  M[i,j] = cb[i,j] exp(cum_i - cum_j) (j <= i),  Xd[j,p] = dt_j x[j,p],
+//   Cs[i,n] = exp(cum_i) C[i,n];   y = acc + D x
+template <int P>
+__global__ void __launch_bounds__(256)
+ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ cum,
+                     const float* __restrict__ cb, const float* __restrict__ s_in, const float* __restrict__ Dskip,
+                     const int* __restrict__ seg_start, float* __restrict__ y, int Hs, int N, int G, int Cd) {
+  tlc_pdl();
+  constexpr int LDM = Q + 4, LDX = P + 8, LDC = 64 + 4;
+  extern __shared__ uint32_t ssd_sm[];
+  uint32_t* Ms = ssd_sm;                  // [i][j]
+  uint32_t* Xs = Ms + Q * LDM;            // [j][p]
+  uint32_t* Cs = Xs + Q * LDX;            // [i][n slab of 64]
+  uint32_t* Ss = Cs + Q * LDC;            // [p][n slab of 64]
+  float* cums = reinterpret_cast<float*>(Ss + P * LDC);     // [Q]
+  const int seg = blockIdx.x, h = blockIdx.y;
+  const int g = h / (Hs / G);
+  const int Di = Hs * P;
+  const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
+  if (threadIdx.x < Q) cums[threadIdx.x] = cum[(size_t)(t0 + min((int)threadIdx.x, L - 1)) * Hs + h];
+  __syncthreads();
+  const float* cbg = cb + (((size_t)seg * G + g) * Q) * Q;
+  for (int idx = threadIdx.x; idx < Q * 32; idx += 256) {
+    const int i = idx >> 5, j4 = (idx & 31) * 4;
+    uint32_t* d = Ms + i * LDM + j4;
+    if (j4 > i || i >= L) { d[0] = d[1] = d[2] = d[3] = 0u; continue; }
+    const float4 v = *reinterpret_cast<const float4*>(cbg + (size_t)i * Q + j4);
+    const float ci = cums[i];
+    d[0] = tf32(v.x * expf(ci - cums[j4]));
+    d[1] = (j4 + 1 <= i) ? tf32(v.y * expf(ci - cums[j4 + 1])) : 0u;
+    d[2] = (j4 + 2 <= i) ? tf32(v.z * expf(ci - cums[j4 + 2])) : 0u;
+    d[3] = (j4 + 3 <= i) ? tf32(v.w * expf(ci - cums[j4 + 3])) : 0u;
+  }
+  for (int idx = threadIdx.x; idx < Q * (P / 4); idx += 256) {
+    const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < L) {
+      v = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + (size_t)h * P + c4);
+      const float w = dt[(size_t)(t0 + r) * Hs + h];
+      v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+    }
+    uint32_t* d = Xs + r * LDX + c4;
+    d[0] = tf32(v.x); d[1] = tf32(v.y); d[2] = tf32(v.z); d[3] = tf32(v.w);
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  const int i_base = warp * 16;
+  float acc[P / 8][4];
+#pragma unroll
+  for (int j = 0; j < P / 8; j++)
+#pragma unroll
+    for (int k = 0; k < 4; k++) acc[j][k] = 0.f;
+  // inside the chunk: columns j <= i only
+  const int k_steps = (i_base + 16) / 8;
+  for (int kk = 0; kk < k_steps; kk++) {
+    const uint32_t* ar = Ms + (i_base + gq) * LDM + kk * 8 + tq;
+    const uint32_t a0 = ar[0], a1 = ar[8 * LDM], a2 = ar[4], a3 = ar[8 * LDM + 4];
+#pragma unroll
+    for (int j = 0; j < P / 8; j++) {
+      const uint32_t* br = Xs + (kk * 8 + tq) * LDX + j * 8 + gq;
+      mma_tf32(acc[j], a0, a1, a2, a3, br[0], br[4 * LDX]);
+    }
+  }
+  // what came before the chunk: rows of C scaled by exp(cum_i), times the incoming state
+  const float* Cg = xbc + Di + (size_t)G * N + (size_t)g * N;
+  const float* Sg = s_in + (((size_t)seg * Hs + h) * P) * N;
+  for (int n0 = 0; n0 < N; n0 += 64) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < Q * 16; idx += 256) {
+      const int r = idx >> 4, c4 = (idx & 15) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < L && n0 + c4 < N) {
+        v = *reinterpret_cast<const float4*>(Cg + (size_t)(t0 + r) * Cd + n0 + c4);
+        const float e = expf(cums[r]);
+        v.x *= e; v.y *= e; v.z *= e; v.w *= e;
+      }
+      uint32_t* d = Cs + r * LDC + c4;
+      d[0] = tf32(v.x); d[1] = tf32(v.y); d[2] = tf32(v.z); d[3] = tf32(v.w);
+    }
+    for (int idx = threadIdx.x; idx < P * 16; idx += 256) {
+      const int p = idx >> 4, c4 = (idx & 15) * 4;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (n0 + c4 < N) v = *reinterpret_cast<const float4*>(Sg + (size_t)p * N + n0 + c4);
+      uint32_t* d = Ss + p * LDC + c4;
+      d[0] = tf32(v.x); d[1] = tf32(v.y); d[2] = tf32(v.z); d[3] = tf32(v.w);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 8; kk++) {
+      const uint32_t* ar = Cs + (i_base + gq) * LDC + kk * 8 + tq;
+      const uint32_t a0 = ar[0], a1 = ar[8 * LDC], a2 = ar[4], a3 = ar[8 * LDC + 4];
+#pragma unroll
+      for (int j = 0; j < P / 8; j++) {
+        const uint32_t* br = Ss + (j * 8 + gq) * LDC + kk * 8 + tq;        // B(k = n, col = p) = S_in[p][n]
+        mma_tf32(acc[j], a0, a1, a2, a3, br[0], br[4]);
+      }
+    }
+  }
+  const float Dh = Dskip[h];
+#pragma unroll
+  for (int j = 0; j < P / 8; j++) {
+    const int p = j * 8 + 2 * tq;
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      const int i = i_base + gq + 8 * r;
+      if (i < L) {
+        const float2 xv = *reinterpret_cast<const float2*>(xbc + (size_t)(t0 + i) * Cd + (size_t)h * P + p);
+        *reinterpret_cast<float2*>(y + (size_t)(t0 + i) * Di + (size_t)h * P + p) =
+            make_float2(acc[j][2 * r] + Dh * xv.x, acc[j][2 * r + 1] + Dh * xv.y);
+      }
+    }
+  }
+}
+
+// The state after a sequence's last chunk, decay * S_in + S_c, is what the carry would hand to a
+// next chunk; the carry kernel (ssm_state_pass_kernel in mamba.cu) writes it to the slot.
+
+inline size_t pad64(size_t n) { return (n + 63) / 64 * 64; }
+
+template <int P> size_t state_smem() { return (size_t)(Q * (P + 8) + Q * 136) * 4; }
+template <int P> size_t out_smem() { return (size_t)(Q * (Q + 4) + Q * (P + 8) + Q * 68 + P * 68) * 4 + Q * 4; }
+
+template <int P> int configure() {
+  if (cudaFuncSetAttribute(ssd_chunk_state_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)state_smem<P>()) != cudaSuccess ||
+      cudaFuncSetAttribute(ssd_chunk_out_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)out_smem<P>()) != cudaSuccess)
+    return tlc_fail(-2, "ssm_scan(chunked): cannot reserve shared memory");
+  return 0;
+}
+
+template <int P>
+int run(const float* xbc, const float* dt, const float* A, const float* Dskip, float* state, float* scratch,
+        const int* seg_start, const int* seg_seq, const int* seq_seg_start, const int* slots, const int* start_pos, float* y,
+        int B, int n_seg, int T, int Hs, int N, int G, int Cd, cudaStream_t stream) {
+  const int Di = Hs * P;
+  // every part starts on a 256-byte boundary of the scratch (float4 loads need 16)
+  float* chunk_state = scratch;                                          // [n_seg, Hs, P, N]
+  float* chunk_decay = chunk_state + pad64((size_t)n_seg * Hs * P * N);  // [n_seg, Hs]
+  float* cum = chunk_decay + pad64((size_t)n_seg * Hs);                  // [T, Hs]
+  float* cb = cum + pad64((size_t)T * Hs);                               // [n_seg, G, Q, Q]
+  tlc_launch(ssd_cumsum_kernel, dim3(n_seg, (Hs + 63) / 64), dim3(64), 0, stream, dt, A, seg_start, cum, chunk_decay, Hs);
+  tlc_launch(ssd_cb_kernel, dim3(n_seg, G, 2), dim3(128), (64 + Q) * 68 * 4, stream, xbc, seg_start, cb, Di, N, G, Cd);
+  tlc_launch(ssd_chunk_state_kernel<P>, dim3(n_seg, Hs, (N + 127) / 128), dim3(256), state_smem<P>(), stream, xbc, dt,
+             (const float*)cum, seg_start, chunk_state, Hs, N, G, Cd);
+  TLC_CHECK_LAUNCH("ssm_scan(chunk states)");
+  if (int rc = tlc_ssm_state_pass_launch(chunk_decay, state, chunk_state, seq_seg_start, slots, start_pos, B, Hs, P * N, 1, stream))
+    return rc;
+  tlc_launch(ssd_chunk_out_kernel<P>, dim3(n_seg, Hs), dim3(256), out_smem<P>(), stream, xbc, dt, (const float*)cum,
+             (const float*)cb, (const float*)chunk_state, Dskip, seg_start, y, Hs, N, G, Cd);
+  TLC_CHECK_LAUNCH("ssm_scan(chunk outputs)");
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int tlc_ssd_init() {
+  if (cudaFuncSetAttribute(ssd_cb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + Q) * 68 * 4) != cudaSuccess)
+    return tlc_fail(-2, "ssm_scan(chunked): cannot reserve shared memory");
+  if (int rc = configure<64>()) return rc;
+  return configure<128>();
+}
+
+// Sizes this form is built for: head size 64 or 128, state size a multiple of 64, 16-byte aligned rows.
+extern "C" int tlc_ssd_ok(int Hs, int P, int N, int G, int Cd) {
+  return (P == 64 || P == 128) && N % 64 == 0 && N >= 64 && Cd % 4 == 0 && G > 0 && Hs % G == 0;
+}
+
+// floats of scratch for n_seg chunks of T rows in all
+extern "C" long long tlc_ssd_scratch_floats(int n_seg, int T, int Hs, int P, int N, int G) {
+  return (long long)(pad64((size_t)n_seg * Hs * P * N) + pad64((size_t)n_seg * Hs) + pad64((size_t)T * Hs) +
+                     pad64((size_t)n_seg * G * Q * Q));
+}
+
+extern "C" int tlc_ssm_scan_ssd(const float* xbc, const float* dt, const float* A, const float* Dskip, float* state,
+                                float* scratch, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
+                                const int* slots, const int* start_pos, float* y, int B, int n_seg, int T, int Hs, int P,
+                                int N, int G, int Cd, cudaStream_t stream) {
+  if (B == 0 || n_seg == 0) return 0;
+  TLC_REQUIRE(tlc_ssd_ok(Hs, P, N, G, Cd), "ssm_scan(chunked, tensor cores): sizes Hs=%d P=%d N=%d G=%d are not built", Hs, P, N, G);
+  TLC_REQUIRE(Hs <= 65535 && G <= 65535, "ssm_scan: too many heads or groups");
+  if (P == 64)
+    return run<64>(xbc, dt, A, Dskip, state, scratch, seg_start, seg_seq, seq_seg_start, slots, start_pos, y, B, n_seg, T, Hs, N, G, Cd, stream);
+  return run<128>(xbc, dt, A, Dskip, state, scratch, seg_start, seg_seq, seq_seg_start, slots, start_pos, y, B, n_seg, T, Hs, N, G, Cd, stream);
+}

@@ -37,6 +37,7 @@ _SIGNATURES = {
                        _i, _i, _i, _vp],
     "tlc_ssm_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "tlc_ssm_scan_chunked": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
+    "tlc_ssm_scan_ssd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     "tlc_argmax": [_vp, _i, _i, _vp, _vp],
     "tlc_sample": [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp],
 }
@@ -58,9 +59,10 @@ def library() -> ctypes.CDLL:
             fn.restype = ctypes.c_int
         lib.tlc_last_error.restype = ctypes.c_char_p
         lib.tlc_linear_error.restype = ctypes.c_int
+        lib.tlc_ssd_scratch_floats.restype = ctypes.c_longlong
         _lib = lib
         if torch.cuda.is_available():                                     # before any stream capture
-            for init in (lib.tlc_linear_init, lib.tlc_attention_prefill_init):
+            for init in (lib.tlc_linear_init, lib.tlc_attention_prefill_init, lib.tlc_ssd_init):
                 if init() != 0:
                     raise KernelError(f"kernel library set-up: {lib.tlc_last_error().decode()}")
     return _lib
@@ -293,6 +295,9 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
           out.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), _stream())
 
 
+DISABLE_SSD = bool(int(os.environ.get("TLC_DISABLE_SSD", "0")))
+
+
 # ---- Mamba2 -------------------------------------------------------------------------------------
 def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, bias: Optional[torch.Tensor],
                dt_bias: torch.Tensor, A: torch.Tensor, conv_state: torch.Tensor, cu_seqlens: torch.Tensor,
@@ -326,11 +331,13 @@ def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, b
 
 def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch.Tensor, state: torch.Tensor,
              cu_seqlens: torch.Tensor, slots: torch.Tensor, start_pos: torch.Tensor, y: torch.Tensor, Hs: int, P: int,
-             N: int, G: int, chunks=None) -> None:
+             N: int, G: int, chunks=None, A: Optional[torch.Tensor] = None) -> None:
     """Selective scan of every sequence in order, from its slot's state (zero at position 0);
     state [n_slots, Hs, P, N] float32 is updated in place; y [T, Hs*P] float32 is before gating.
     chunks = (seg_start [n+1], seg_seq [n], seq_seg_start [B+1]) cuts the sequences into
-    chunks that run in parallel (three passes, same result up to rounding)."""
+    chunks that run in parallel (same result up to rounding).  With A (the per-head decay rate,
+    dA = exp(dt * A)) the chunks run in matrix form on the tensor cores with TF32 operands, for
+    head sizes of 64 or 128 and state sizes that are multiples of 64; a 32-bit run passes no A."""
     _gpu(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y)
     T, Cd = xbc.shape
     if Cd != Hs * P + 2 * G * N:
@@ -347,6 +354,14 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch
             _gpu(t)
             _i32(t, n)
         n_seg = seg_seq.numel()
+        lib = library()
+        if A is not None and lib.tlc_ssd_ok(Hs, P, N, G, Cd) and not DISABLE_SSD:
+            _f32vec(A, Hs, "A")
+            scratch = torch.empty(lib.tlc_ssd_scratch_floats(n_seg, T, Hs, P, N, G), dtype=torch.float32, device=xbc.device)
+            _call("tlc_ssm_scan_ssd", xbc.data_ptr(), dt.data_ptr(), A.data_ptr(), Dskip.data_ptr(), state.data_ptr(),
+                  scratch.data_ptr(), seg_start.data_ptr(), seg_seq.data_ptr(), seq_seg_start.data_ptr(),
+                  slots.data_ptr(), start_pos.data_ptr(), y.data_ptr(), slots.numel(), n_seg, T, Hs, P, N, G, Cd, _stream())
+            return
         scratch = torch.empty(n_seg * Hs * (P * N + 1), dtype=torch.float32, device=xbc.device)
         _call("tlc_ssm_scan_chunked", xbc.data_ptr(), dt.data_ptr(), dA.data_ptr(), Dskip.data_ptr(), state.data_ptr(),
               scratch.data_ptr(), seg_start.data_ptr(), seg_seq.data_ptr(), seq_seg_start.data_ptr(), slots.data_ptr(),

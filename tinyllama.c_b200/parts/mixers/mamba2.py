@@ -89,7 +89,7 @@ class Mamba2Mixer(Part):
                        step.max_new == 1)
         y = act_empty((T, self.Di), normed, f32)
         ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs, self.P,
-                     self.N, self.G, step.chunks)
+                     self.N, self.G, step.chunks, self.A if normed.dtype == torch.bfloat16 else None)
         gated = act_empty((T, self.Di), normed)
         ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated)
         self.out_proj.forward(gated, residual, accumulate=True)
