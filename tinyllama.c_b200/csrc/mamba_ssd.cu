@@ -48,9 +48,17 @@ __global__ void ssd_cumsum_kernel(const float* __restrict__ dt, const float* __r
   const int t0 = seg_start[seg], t1 = seg_start[seg + 1];
   const float a = A[h];
   float c = 0.f;
-  for (int t = t0; t < t1; t++) {
-    c = fmaf(dt[(size_t)t * Hs + h], a, c);
-    cum[(size_t)t * Hs + h] = c;
+  for (int tb = t0; tb < t1; tb += 8) {
+    float d[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) d[u] = tb + u < t1 ? dt[(size_t)(tb + u) * Hs + h] : 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      if (tb + u < t1) {
+        c = fmaf(d[u], a, c);
+        cum[(size_t)(tb + u) * Hs + h] = c;
+      }
+    }
   }
   chunk_decay[(size_t)seg * Hs + h] = expf(c);
 }
@@ -79,17 +87,29 @@ ssd_cb_kernel(const float* __restrict__ xbc, const int* __restrict__ seg_start, 
   const float* Cg = xbc + Di + (size_t)G * N + (size_t)g * N;
   for (int n0 = 0; n0 < N; n0 += 64) {
     __syncthreads();
-    for (int idx = threadIdx.x; idx < Q * 16; idx += 128) {           // 16 float4 per row
-      const int r = idx >> 4, c4 = (idx & 15) * 4;
-      float4 b = make_float4(0.f, 0.f, 0.f, 0.f), c = b;
-      if (r < L && n0 + c4 < N) b = *reinterpret_cast<const float4*>(Bg + (size_t)(t0 + r) * Cd + n0 + c4);
-      uint32_t* bd = Bs + r * LD + c4;
-      bd[0] = tf32(b.x); bd[1] = tf32(b.y); bd[2] = tf32(b.z); bd[3] = tf32(b.w);
-      if (r < 64) {
+    // 16 float4 per row; all loads of a batch are issued before the first conversion
+#pragma unroll 1
+    for (int it0 = 0; it0 < 16; it0 += 8) {
+      float4 bv[8], cv[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int idx = threadIdx.x + (it0 + u) * 128;
+        const int r = idx >> 4, c4 = (idx & 15) * 4;
+        bv[u] = cv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < L && n0 + c4 < N) bv[u] = *reinterpret_cast<const float4*>(Bg + (size_t)(t0 + r) * Cd + n0 + c4);
         const int ri = half * 64 + r;
-        if (ri < L && n0 + c4 < N) c = *reinterpret_cast<const float4*>(Cg + (size_t)(t0 + ri) * Cd + n0 + c4);
-        uint32_t* cd = Cs + r * LD + c4;
-        cd[0] = tf32(c.x); cd[1] = tf32(c.y); cd[2] = tf32(c.z); cd[3] = tf32(c.w);
+        if (r < 64 && ri < L && n0 + c4 < N) cv[u] = *reinterpret_cast<const float4*>(Cg + (size_t)(t0 + ri) * Cd + n0 + c4);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int idx = threadIdx.x + (it0 + u) * 128;
+        const int r = idx >> 4, c4 = (idx & 15) * 4;
+        uint32_t* bd = Bs + r * LD + c4;
+        bd[0] = tf32(bv[u].x); bd[1] = tf32(bv[u].y); bd[2] = tf32(bv[u].z); bd[3] = tf32(bv[u].w);
+        if (r < 64) {
+          uint32_t* cd = Cs + r * LD + c4;
+          cd[0] = tf32(cv[u].x); cd[1] = tf32(cv[u].y); cd[2] = tf32(cv[u].z); cd[3] = tf32(cv[u].w);
+        }
       }
     }
     __syncthreads();
@@ -133,23 +153,50 @@ ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ 
   const int Di = Hs * P;
   const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
   const float cum_last = cum[(size_t)(t0 + L - 1) * Hs + h];
-  for (int idx = threadIdx.x; idx < Q * (P / 4); idx += 256) {
-    const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < L) {
-      v = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + (size_t)h * P + c4);
-      const float w = expf(cum_last - cum[(size_t)(t0 + r) * Hs + h]) * dt[(size_t)(t0 + r) * Hs + h];
-      v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+  // x * w: Q * P / 4 float4, 8 in flight per thread
+#pragma unroll 1
+  for (int it0 = 0; it0 < Q * (P / 4) / 256; it0 += 8) {
+    float4 v[8];
+    float w[8], dtv[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int idx = threadIdx.x + (it0 + u) * 256;
+      const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      w[u] = dtv[u] = 0.f;
+      if (r < L) {
+        v[u] = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + (size_t)h * P + c4);
+        w[u] = cum[(size_t)(t0 + r) * Hs + h];
+        dtv[u] = dt[(size_t)(t0 + r) * Hs + h];
+      }
     }
-    uint32_t* d = Xs + r * LDX + c4;
-    d[0] = tf32(v.x); d[1] = tf32(v.y); d[2] = tf32(v.z); d[3] = tf32(v.w);
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int idx = threadIdx.x + (it0 + u) * 256;
+      const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
+      const float ww = r < L ? expf(cum_last - w[u]) * dtv[u] : 0.f;
+      uint32_t* d = Xs + r * LDX + c4;
+      d[0] = tf32(v[u].x * ww); d[1] = tf32(v[u].y * ww); d[2] = tf32(v[u].z * ww); d[3] = tf32(v[u].w * ww);
+    }
   }
-  for (int idx = threadIdx.x; idx < Q * 32; idx += 256) {
-    const int r = idx >> 5, c4 = (idx & 31) * 4;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < L && nb + c4 < N) v = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + Di + (size_t)g * N + nb + c4);
-    uint32_t* d = Bs + r * LDB + c4;
-    d[0] = tf32(v.x); d[1] = tf32(v.y); d[2] = tf32(v.z); d[3] = tf32(v.w);
+  // 128 columns of B: Q * 32 float4
+#pragma unroll 1
+  for (int it0 = 0; it0 < Q * 32 / 256; it0 += 8) {
+    float4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int idx = threadIdx.x + (it0 + u) * 256;
+      const int r = idx >> 5, c4 = (idx & 31) * 4;
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < L && nb + c4 < N) v[u] = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + Di + (size_t)g * N + nb + c4);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int idx = threadIdx.x + (it0 + u) * 256;
+      const int r = idx >> 5, c4 = (idx & 31) * 4;
+      uint32_t* d = Bs + r * LDB + c4;
+      d[0] = tf32(v[u].x); d[1] = tf32(v[u].y); d[2] = tf32(v[u].z); d[3] = tf32(v[u].w);
+    }
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
@@ -192,54 +239,82 @@ ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ 
 }
 
 // ---- chunk outputs ------------------------------------------------------------------------------------
-// grid (seg, Hs); 8 warps, warp w owns rows [16w, 16w+16) and all P columns.
+// grid (seg, Hs, 2); a block of 4 warps owns 64 rows of the chunk, warp w rows [16w, 16w+16), all P columns.
 //   acc = M Xd + Cs S_in^T,  M[i,j] = cb[i,j] exp(cum_i - cum_j) (j <= i),  Xd[j,p] = dt_j x[j,p],
 //   Cs[i,n] = exp(cum_i) C[i,n];   y = acc + D x
 template <int P>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ cum,
                      const float* __restrict__ cb, const float* __restrict__ s_in, const float* __restrict__ Dskip,
                      const int* __restrict__ seg_start, float* __restrict__ y, int Hs, int N, int G, int Cd) {
   tlc_pdl();
+  constexpr int R = 64;                   // rows of the chunk per block
   constexpr int LDM = Q + 4, LDX = P + 8, LDC = 64 + 4;
   extern __shared__ uint32_t ssd_sm[];
-  uint32_t* Ms = ssd_sm;                  // [i][j]
-  uint32_t* Xs = Ms + Q * LDM;            // [j][p]
-  uint32_t* Cs = Xs + Q * LDX;            // [i][n slab of 64]
-  uint32_t* Ss = Cs + Q * LDC;            // [p][n slab of 64]
+  uint32_t* Ms = ssd_sm;                  // [R][j]
+  uint32_t* Xs = Ms + R * LDM;            // [j][p]
+  uint32_t* Cs = Xs + Q * LDX;            // [R][n slab of 64]
+  uint32_t* Ss = Cs + R * LDC;            // [p][n slab of 64]
   float* cums = reinterpret_cast<float*>(Ss + P * LDC);     // [Q]
-  const int seg = blockIdx.x, h = blockIdx.y;
+  const int seg = blockIdx.x, h = blockIdx.y, r0 = blockIdx.z * R;
   const int g = h / (Hs / G);
   const int Di = Hs * P;
   const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
-  if (threadIdx.x < Q) cums[threadIdx.x] = cum[(size_t)(t0 + min((int)threadIdx.x, L - 1)) * Hs + h];
+  if (r0 >= L) return;
+  const int jmax = min(L, r0 + R);        // columns j < jmax matter for these rows
+  cums[threadIdx.x] = cum[(size_t)(t0 + min((int)threadIdx.x, L - 1)) * Hs + h];
   __syncthreads();
   const float* cbg = cb + (((size_t)seg * G + g) * Q) * Q;
-  for (int idx = threadIdx.x; idx < Q * 32; idx += 256) {
-    const int i = idx >> 5, j4 = (idx & 31) * 4;
-    uint32_t* d = Ms + i * LDM + j4;
-    if (j4 > i || i >= L) { d[0] = d[1] = d[2] = d[3] = 0u; continue; }
-    const float4 v = *reinterpret_cast<const float4*>(cbg + (size_t)i * Q + j4);
-    const float ci = cums[i];
-    d[0] = tf32(v.x * expf(ci - cums[j4]));
-    d[1] = (j4 + 1 <= i) ? tf32(v.y * expf(ci - cums[j4 + 1])) : 0u;
-    d[2] = (j4 + 2 <= i) ? tf32(v.z * expf(ci - cums[j4 + 2])) : 0u;
-    d[3] = (j4 + 3 <= i) ? tf32(v.w * expf(ci - cums[j4 + 3])) : 0u;
-  }
-  for (int idx = threadIdx.x; idx < Q * (P / 4); idx += 256) {
-    const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (r < L) {
-      v = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + (size_t)h * P + c4);
-      const float w = dt[(size_t)(t0 + r) * Hs + h];
-      v.x *= w; v.y *= w; v.z *= w; v.w *= w;
+  // M: R rows x 32 float4, 8 loads in flight per thread
+#pragma unroll 1
+  for (int it0 = 0; it0 < R * 32 / 128; it0 += 8) {
+    float4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int idx = threadIdx.x + (it0 + u) * 128;
+      const int i = r0 + (idx >> 5), j4 = (idx & 31) * 4;
+      v[u] = (j4 <= i && i < L) ? *reinterpret_cast<const float4*>(cbg + (size_t)i * Q + j4) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    uint32_t* d = Xs + r * LDX + c4;
-    d[0] = tf32(v.x); d[1] = tf32(v.y); d[2] = tf32(v.z); d[3] = tf32(v.w);
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int idx = threadIdx.x + (it0 + u) * 128;
+      const int il = idx >> 5, i = r0 + il, j4 = (idx & 31) * 4;
+      uint32_t* d = Ms + il * LDM + j4;
+      if (j4 > i || i >= L) { d[0] = d[1] = d[2] = d[3] = 0u; continue; }
+      const float ci = cums[i];
+      d[0] = tf32(v[u].x * expf(ci - cums[j4]));
+      d[1] = (j4 + 1 <= i) ? tf32(v[u].y * expf(ci - cums[j4 + 1])) : 0u;
+      d[2] = (j4 + 2 <= i) ? tf32(v[u].z * expf(ci - cums[j4 + 2])) : 0u;
+      d[3] = (j4 + 3 <= i) ? tf32(v[u].w * expf(ci - cums[j4 + 3])) : 0u;
+    }
+  }
+  // Xd: rows j < jmax
+#pragma unroll 1
+  for (int it0 = 0; it0 < Q * (P / 4) / 128; it0 += 8) {
+    float4 v[8];
+    float w[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int idx = threadIdx.x + (it0 + u) * 128;
+      const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      w[u] = 0.f;
+      if (r < jmax) {
+        v[u] = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + (size_t)h * P + c4);
+        w[u] = dt[(size_t)(t0 + r) * Hs + h];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const int idx = threadIdx.x + (it0 + u) * 128;
+      const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
+      uint32_t* d = Xs + r * LDX + c4;
+      d[0] = tf32(v[u].x * w[u]); d[1] = tf32(v[u].y * w[u]); d[2] = tf32(v[u].z * w[u]); d[3] = tf32(v[u].w * w[u]);
+    }
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-  const int i_base = warp * 16;
+  const int il_base = warp * 16, i_base = r0 + il_base;
   float acc[P / 8][4];
 #pragma unroll
   for (int j = 0; j < P / 8; j++)
@@ -248,7 +323,7 @@ ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt
   // inside the chunk: columns j <= i only
   const int k_steps = (i_base + 16) / 8;
   for (int kk = 0; kk < k_steps; kk++) {
-    const uint32_t* ar = Ms + (i_base + gq) * LDM + kk * 8 + tq;
+    const uint32_t* ar = Ms + (il_base + gq) * LDM + kk * 8 + tq;
     const uint32_t a0 = ar[0], a1 = ar[8 * LDM], a2 = ar[4], a3 = ar[8 * LDM + 4];
 #pragma unroll
     for (int j = 0; j < P / 8; j++) {
@@ -261,28 +336,45 @@ ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt
   const float* Sg = s_in + (((size_t)seg * Hs + h) * P) * N;
   for (int n0 = 0; n0 < N; n0 += 64) {
     __syncthreads();
-    for (int idx = threadIdx.x; idx < Q * 16; idx += 256) {
-      const int r = idx >> 4, c4 = (idx & 15) * 4;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (r < L && n0 + c4 < N) {
-        v = *reinterpret_cast<const float4*>(Cg + (size_t)(t0 + r) * Cd + n0 + c4);
-        const float e = expf(cums[r]);
-        v.x *= e; v.y *= e; v.z *= e; v.w *= e;
+    {
+      float4 v[8];                          // R rows x 16 float4 of C = 8 per thread
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int idx = threadIdx.x + u * 128;
+        const int r = r0 + (idx >> 4), c4 = (idx & 15) * 4;
+        v[u] = (r < L && n0 + c4 < N) ? *reinterpret_cast<const float4*>(Cg + (size_t)(t0 + r) * Cd + n0 + c4)
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      uint32_t* d = Cs + r * LDC + c4;
-      d[0] = tf32(v.x); d[1] = tf32(v.y); d[2] = tf32(v.z); d[3] = tf32(v.w);
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int idx = threadIdx.x + u * 128;
+        const int rl = idx >> 4, c4 = (idx & 15) * 4;
+        const float e = expf(cums[min(r0 + rl, Q - 1)]);
+        uint32_t* d = Cs + rl * LDC + c4;
+        d[0] = tf32(v[u].x * e); d[1] = tf32(v[u].y * e); d[2] = tf32(v[u].z * e); d[3] = tf32(v[u].w * e);
+      }
     }
-    for (int idx = threadIdx.x; idx < P * 16; idx += 256) {
-      const int p = idx >> 4, c4 = (idx & 15) * 4;
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (n0 + c4 < N) v = *reinterpret_cast<const float4*>(Sg + (size_t)p * N + n0 + c4);
-      uint32_t* d = Ss + p * LDC + c4;
-      d[0] = tf32(v.x); d[1] = tf32(v.y); d[2] = tf32(v.z); d[3] = tf32(v.w);
+#pragma unroll 1
+    for (int it0 = 0; it0 < P * 16 / 128; it0 += 8) {      // P rows x 16 float4 of the incoming state
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int idx = threadIdx.x + (it0 + u) * 128;
+        const int p = idx >> 4, c4 = (idx & 15) * 4;
+        v[u] = (n0 + c4 < N) ? *reinterpret_cast<const float4*>(Sg + (size_t)p * N + n0 + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int idx = threadIdx.x + (it0 + u) * 128;
+        const int p = idx >> 4, c4 = (idx & 15) * 4;
+        uint32_t* d = Ss + p * LDC + c4;
+        d[0] = tf32(v[u].x); d[1] = tf32(v[u].y); d[2] = tf32(v[u].z); d[3] = tf32(v[u].w);
+      }
     }
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < 8; kk++) {
-      const uint32_t* ar = Cs + (i_base + gq) * LDC + kk * 8 + tq;
+      const uint32_t* ar = Cs + (il_base + gq) * LDC + kk * 8 + tq;
       const uint32_t a0 = ar[0], a1 = ar[8 * LDC], a2 = ar[4], a3 = ar[8 * LDC + 4];
 #pragma unroll
       for (int j = 0; j < P / 8; j++) {
@@ -313,7 +405,7 @@ ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt
 inline size_t pad64(size_t n) { return (n + 63) / 64 * 64; }
 
 template <int P> size_t state_smem() { return (size_t)(Q * (P + 8) + Q * 136) * 4; }
-template <int P> size_t out_smem() { return (size_t)(Q * (Q + 4) + Q * (P + 8) + Q * 68 + P * 68) * 4 + Q * 4; }
+template <int P> size_t out_smem() { return (size_t)(64 * (Q + 4) + Q * (P + 8) + 64 * 68 + P * 68) * 4 + Q * 4; }
 
 template <int P> int configure() {
   if (cudaFuncSetAttribute(ssd_chunk_state_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)state_smem<P>()) != cudaSuccess ||
@@ -339,7 +431,7 @@ int run(const float* xbc, const float* dt, const float* A, const float* Dskip, f
   TLC_CHECK_LAUNCH("ssm_scan(chunk states)");
   if (int rc = tlc_ssm_state_pass_launch(chunk_decay, state, chunk_state, seq_seg_start, slots, start_pos, B, Hs, P * N, 1, stream))
     return rc;
-  tlc_launch(ssd_chunk_out_kernel<P>, dim3(n_seg, Hs), dim3(256), out_smem<P>(), stream, xbc, dt, (const float*)cum,
+  tlc_launch(ssd_chunk_out_kernel<P>, dim3(n_seg, Hs, 2), dim3(128), out_smem<P>(), stream, xbc, dt, (const float*)cum,
              (const float*)cb, (const float*)chunk_state, Dskip, seg_start, y, Hs, N, G, Cd);
   TLC_CHECK_LAUNCH("ssm_scan(chunk outputs)");
   return 0;
