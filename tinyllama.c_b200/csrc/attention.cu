@@ -246,7 +246,10 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
                                     int max_pages, const int* __restrict__ positions, const int* __restrict__ row_seq,
                                     const int* __restrict__ slots, float* __restrict__ part_o,
                                     float* __restrict__ part_ml, int H, int KV, float scale, int window, int n_splits) {
-  tlc_pdl();
+  // Keys of earlier positions were stored by earlier steps; only the row at the query's own
+  // position is written by the kernel before this one.  Everything else is fetched before the
+  // wait on that kernel (see tlc_pdl).
+  asm volatile("griddepcontrol.launch_dependents;");
   extern __shared__ float sh[];
   constexpr int DL = HD / 8;                 // lanes per value row
   constexpr int GROUPS = DEC_KEYS / DL;      // value rows in flight
@@ -258,6 +261,7 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
   const int k0 = split * DEC_KEYS;
   float* ml = part_ml + (((size_t)t * H + (size_t)g * G) * n_splits + split) * 2;
   if (k0 >= n_keys || k0 + DEC_KEYS <= start) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (threadIdx.x < G) { ml[(size_t)threadIdx.x * n_splits * 2] = -INFINITY; ml[(size_t)threadIdx.x * n_splits * 2 + 1] = 0.f; }
     return;
   }
@@ -267,25 +271,36 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
   float* os = red + 36;                             // [GROUPS][G][HD]
   __shared__ int pages[DEC_KEYS / TLC_PAGE + 1];
   const int* table = block_table + (size_t)slots[row_seq[t]] * max_pages;
+  const int kp = k0 + threadIdx.x;
+  const bool valid = kp >= start && kp < n_keys;
+  uint4 kq[DL];
+  const uint4* kr = nullptr;
+  if (valid) {
+    kr = reinterpret_cast<const uint4*>(k_pages + (((size_t)table[kp / TLC_PAGE] * KV + g) * TLC_PAGE + kp % TLC_PAGE) * HD);
+    if (kp != pos) {
+#pragma unroll
+      for (int d8 = 0; d8 < DL; d8++) kq[d8] = __ldg(kr + d8);
+    }
+  }
   if (threadIdx.x <= DEC_KEYS / TLC_PAGE) {
     const int pi = k0 / TLC_PAGE + threadIdx.x;
     pages[threadIdx.x] = (pi * TLC_PAGE < n_keys) ? table[pi] : 0;
   }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (valid && kp == pos) {
+#pragma unroll
+    for (int d8 = 0; d8 < DL; d8++) kq[d8] = kr[d8];
+  }
   for (int i = threadIdx.x; i < G * HD; i += blockDim.x)
     qs[i] = __bfloat162float(q[((size_t)t * H + (size_t)g * G) * HD + i]) * scale;
   __syncthreads();
-  const int kp = k0 + threadIdx.x;
-  const bool valid = kp >= start && kp < n_keys;
   float s[DEC_MAXG];
 #pragma unroll
   for (int hg = 0; hg < DEC_MAXG; hg++) s[hg] = 0.f;
   if (valid) {
-    const uint4* kr = reinterpret_cast<const uint4*>(
-        k_pages + (((size_t)pages[threadIdx.x / TLC_PAGE] * KV + g) * TLC_PAGE + kp % TLC_PAGE) * HD);
 #pragma unroll
     for (int d8 = 0; d8 < DL; d8++) {
-      const uint4 kq = __ldg(kr + d8);
-      const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&kq);
+      const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&kq[d8]);
       float kf[8];
 #pragma unroll
       for (int i = 0; i < 4; i++) { const float2 f = __bfloat1622float2(kb[i]); kf[2 * i] = f.x; kf[2 * i + 1] = f.y; }

@@ -210,7 +210,10 @@ __global__ void __launch_bounds__(SK_WARPS * 32, (MG <= 2 && U <= 4) ? 2 : 1)
 gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                        TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                        const float* __restrict__ colbias, int accumulate, int M, int N, int K) {
-  tlc_pdl();
+  // The weights do not depend on the previous kernel of the stream, the activations do: when this
+  // kernel is launched early (programmatic dependent launch), the first round of weight loads is
+  // in flight while the previous kernel is still finishing; only then does it wait for it.
+  asm volatile("griddepcontrol.launch_dependents;");
   __shared__ float red[SK_WARPS][MG < 4 ? MG : 4][32][4];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -235,6 +238,7 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
       wa[u] = in ? __ldg(w0 + c) : make_uint4(0, 0, 0, 0);
       wb[u] = in ? __ldg(w1 + c) : make_uint4(0, 0, 0, 0);
     }
+    if (s0 == warp * U) asm volatile("griddepcontrol.wait;" ::: "memory");     // first round only
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int c = (s0 + u) * 4 + t;
@@ -257,6 +261,7 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
       }
     }
   }
+  if (warp * U >= n_steps) asm volatile("griddepcontrol.wait;" ::: "memory");  // warps without a round of their own
   // the warps' partial sums meet in shared memory, at most four row groups at a time
   constexpr int RG = MG < 4 ? MG : 4;
 #pragma unroll 1

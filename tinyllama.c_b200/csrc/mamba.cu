@@ -169,7 +169,10 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
                 const int* __restrict__ seq_seg_start, const int* __restrict__ slots,
                 const int* __restrict__ start_pos, float* __restrict__ y, float* __restrict__ chunk_decay, int mode,
                 int Hs, int P, int N, int G, int Cd) {
-  tlc_pdl();
+  // In the plain mode the state this block starts from was written by an earlier step, not by
+  // the kernel before this one: it is fetched before the wait on that kernel (see tlc_pdl).
+  asm volatile("griddepcontrol.launch_dependents;");
+  if (mode != SCAN_PLAIN) asm volatile("griddepcontrol.wait;" ::: "memory");
   extern __shared__ float sm[];
   const int seg = blockIdx.x, h = blockIdx.y;
   const int b = seg_seq ? seg_seq[seg] : seg;
@@ -199,6 +202,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
       const int p = p_base + r, n = lane + 32 * j;
       s[r][j] = (S_init && p < P && n < N) ? S_init[(size_t)p * N + n] : 0.f;
     }
+  if (mode == SCAN_PLAIN) asm volatile("griddepcontrol.wait;" ::: "memory");
   // shared staging: per row  B[N] | C[N] | x[rows_per_block] | dt | dA
   const int per_tok = 2 * N + rows_per_block + 2;
   const float Dh = Dskip[h];
