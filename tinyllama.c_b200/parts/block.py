@@ -12,6 +12,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .base import LayerCache, LayerSpec, Part, StepInfo, WeightSpec, act_empty
+from .linear import StackedLinear
 
 
 class Block(Part):
@@ -36,14 +37,32 @@ class Block(Part):
         self.dtype = dtype
         for p in self.parts():
             p.bind(tensors, dtype, device)
+        # Mixers that run in parallel on the same normed input and say what they first project it to
+        # share one product: their input projections are stacked.  Any other mixer gets the normed
+        # input as a tensor.
+        self.fused_in, self.fused_offsets = None, []
+        if len(self.mixers) > 1 and all(hasattr(m, "input_projection") and hasattr(m, "forward_projected")
+                                        for m in self.mixers):
+            projs = [m.input_projection() for m in self.mixers]
+            self.fused_in = StackedLinear.fuse_bound(projs)
+            off = 0
+            for pr in projs:
+                self.fused_offsets.append((off, pr.out_features))
+                off += pr.out_features
 
     def forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
         """Updates the float32 residual stream x32 [T, D] in place."""
         if self.mixers:
             normed = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
             self.mixer_norm.forward(x32, normed)
-            for m in self.mixers:
-                m.forward(normed, step, cache, x32)
+            if self.fused_in is not None:
+                proj = torch.empty((x32.shape[0], self.fused_in.out_features), dtype=torch.float32, device=x32.device)
+                self.fused_in.forward(normed, proj)
+                for m, (off, n) in zip(self.mixers, self.fused_offsets):
+                    m.forward_projected(proj[:, off:off + n], step, cache, x32)
+            else:
+                for m in self.mixers:
+                    m.forward(normed, step, cache, x32)
         if self.ffn is not None:
             normed = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
             self.ffn_norm.forward(x32, normed)

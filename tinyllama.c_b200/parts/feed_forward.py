@@ -42,3 +42,4 @@ class SwiGLU(Part):
         act = act_empty((T, self.F), normed)
         ops.swiglu(gu, act)
         self.down.forward(act, residual, accumulate=True)
+

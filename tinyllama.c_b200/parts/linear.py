@@ -87,3 +87,27 @@ class StackedLinear:
     def forward(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
         ops.linear(x, self.weight, out, self.colscale, self.colbias, accumulate)
         return out
+
+    @staticmethod
+    def fuse_bound(parts: Sequence["StackedLinear"]) -> Optional["StackedLinear"]:
+        """One projection over the rows of several bound projections of the same input.  The
+        parts then share the fused storage (their weights become row ranges of it).  None if
+        the parts cannot share one product (different input widths or element types)."""
+        if len(parts) < 2 or len({p.in_features for p in parts}) != 1 or len({p.weight.dtype for p in parts}) != 1:
+            return None
+        fused = StackedLinear(parts[0].in_features)
+        dev = parts[0].weight.device
+        fused.weight = torch.cat([p.weight for p in parts], dim=0).contiguous()
+        ones = lambda n: torch.ones(n, dtype=torch.float32, device=dev)
+        zeros = lambda n: torch.zeros(n, dtype=torch.float32, device=dev)
+        if any(p.colscale is not None for p in parts):
+            fused.colscale = torch.cat([p.colscale if p.colscale is not None else ones(p.out_features) for p in parts])
+        if any(p.colbias is not None for p in parts):
+            fused.colbias = torch.cat([p.colbias if p.colbias is not None else zeros(p.out_features) for p in parts])
+        off = 0
+        for p in parts:
+            for seg in p.segments:
+                fused.segments.append(dict(seg, off=off + seg["off"]))
+            p.weight = fused.weight[off:off + p.out_features]          # the part's rows inside the fused storage
+            off += p.out_features
+        return fused

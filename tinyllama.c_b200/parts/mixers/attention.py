@@ -50,15 +50,24 @@ class AttentionMixer(Part):
         self.o.bind(tensors, dtype, device)
         self.position.bind(tensors, dtype, device)
 
+    def input_projection(self) -> StackedLinear:
+        """What this mixer computes from the normed input before anything else (a block may stack
+        the input projections of its mixers into one product)."""
+        return self.qkv
+
     def forward(self, normed: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor) -> None:
+        qkv = act_empty((step.n_rows, self.qkv.out_features), normed, torch.float32)
+        self.qkv.forward(normed, qkv)
+        self.forward_projected(qkv, step, cache, residual)
+
+    def forward_projected(self, qkv: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor) -> None:
+        """qkv: this mixer's input projection, float32 [T, q|k|v] (rows may be strided)."""
         T = step.n_rows
         kv = cache.kv[self.cache_key]
-        qkv = act_empty((T, self.qkv.out_features), normed, torch.float32)
-        self.qkv.forward(normed, qkv)
-        q = act_empty((T, self.H * self.hd), normed)
+        q = torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
         self.position.rotate_and_store(qkv, self.q_off, self.k_off, self.v_off, q, kv, step, self.H, self.KV, self.hd,
                                        cache.writes)
-        att = act_empty((T, self.H * self.hd), normed)
+        att = torch.empty_like(q)
         ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
                       self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
                       step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos)

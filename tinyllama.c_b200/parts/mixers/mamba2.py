@@ -45,6 +45,7 @@ class Mamba2Mixer(Part):
         self.out_proj.add(prefix + "out_proj.weight", hidden, prefix + "out_proj.bias" if proj_bias else None,
                           1.0, out_scale)
         self.conv_w = self.conv_b = self.A = self.D = self.dt_bias = self.norm_w = None
+        self.dtype = None
 
     # ---- declarations ------------------------------------------------------------------
     def weight_specs(self) -> List[WeightSpec]:
@@ -65,6 +66,7 @@ class Mamba2Mixer(Part):
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
         p = self.prefix
+        self.dtype = dtype
         self.in_proj.bind(tensors, dtype, device)
         self.out_proj.bind(tensors, dtype, device)
         self.conv_w = to_vec(tensors[p + "conv1d.weight"].reshape(self.Cd, self.K), device)
@@ -75,21 +77,27 @@ class Mamba2Mixer(Part):
         self.norm_w = to_vec(tensors[p + "norm.weight"], device) if self.rms_norm else None
 
     # ---- one step --------------------------------------------------------------------------
+    def input_projection(self) -> StackedLinear:
+        return self.in_proj
+
     def forward(self, normed: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor) -> None:
+        proj = act_empty((step.n_rows, self.in_proj.out_features), normed, torch.float32)
+        self.in_proj.forward(normed, proj)
+        self.forward_projected(proj, step, cache, residual)
+
+    def forward_projected(self, proj: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor) -> None:
+        """proj: this mixer's input projection, float32 [T, z|x|B|C|dt] (rows may be strided)."""
         T, f32 = step.n_rows, torch.float32
         conv_state = cache.state[self.cache_key + ".conv"]
         ssm_state = cache.state[self.cache_key + ".ssm"]
-        proj = act_empty((T, self.in_proj.out_features), normed, f32)
-        self.in_proj.forward(normed, proj)
-        xbc = act_empty((T, self.Cd), normed, f32)
-        dt = act_empty((T, self.Hs), normed, f32)
-        dA = act_empty((T, self.Hs), normed, f32)
+        new = lambda shape, dtype: torch.empty(shape, dtype=dtype, device=proj.device)
+        xbc, dt, dA = new((T, self.Cd), f32), new((T, self.Hs), f32), new((T, self.Hs), f32)
         ops.mamba_conv(proj, self.Di, self.Di + self.Cd, self.conv_w, self.conv_b, self.dt_bias, self.A, conv_state,
                        step.cu_seqlens, step.row_seq, step.slots, step.start_pos, xbc, dt, dA,
                        step.max_new == 1)
-        y = act_empty((T, self.Di), normed, f32)
+        y = new((T, self.Di), f32)
         ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs, self.P,
-                     self.N, self.G, step.chunks, self.A if normed.dtype == torch.bfloat16 else None)
-        gated = act_empty((T, self.Di), normed)
+                     self.N, self.G, step.chunks, self.A if self.dtype == torch.bfloat16 else None)
+        gated = new((T, self.Di), self.dtype)
         ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated)
         self.out_proj.forward(gated, residual, accumulate=True)
