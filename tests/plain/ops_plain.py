@@ -48,9 +48,22 @@ def gated_rmsnorm(y, z, weight, eps, n_groups, norm_before_gate, out):
     out.copy_(res.to(out.dtype))
 
 
-def swiglu(gate_up, out):
+def _gate_up(gate_up, interleaved):
     F = gate_up.shape[1] // 2
-    g, u = _f(gate_up[:, :F]), _f(gate_up[:, F:])
+    if not interleaved:
+        return _f(gate_up[:, :F]), _f(gate_up[:, F:])
+    r = _f(gate_up).reshape(gate_up.shape[0], F // 8, 2, 8)
+    return r[:, :, 0, :].reshape(-1, F), r[:, :, 1, :].reshape(-1, F)
+
+
+def linear_swiglu(a, w, out, colscale=None, colbias=None):
+    gu = torch.empty((a.shape[0], w.shape[0]), dtype=torch.float64)
+    linear(a, w, gu, colscale, colbias)
+    swiglu(gu, out, interleaved=True)
+
+
+def swiglu(gate_up, out, interleaved=False):
+    g, u = _gate_up(gate_up, interleaved)
     out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
 
 
@@ -214,7 +227,7 @@ def sample(logits, work, history, uniforms, temperature, top_k, top_p, min_p, re
                             temperature, top_k, top_p, min_p, repeat_penalty, frequency_penalty, presence_penalty)
 
 
-ALL = ["embed", "rmsnorm", "gated_rmsnorm", "swiglu", "gather_rows", "linear", "rope_kv_store", "attention",
+ALL = ["embed", "rmsnorm", "gated_rmsnorm", "swiglu", "gather_rows", "linear", "linear_swiglu", "rope_kv_store", "attention",
        "mamba_conv", "ssm_scan", "argmax", "sample"]
 
 

@@ -82,6 +82,20 @@ def test_swiglu(dtype):
     for in_dt in (torch.float32, DT[dtype]):
         gu = rnd(g, 9, 2 * 77, dtype=in_dt, scale=2.0)
         cmp("swiglu", [gu, torch.empty(9, 77, dtype=DT[dtype])], [1])
+        gu = rnd(g, 9, 2 * 80, dtype=in_dt, scale=2.0)
+        cmp("swiglu", [gu, torch.empty(9, 80, dtype=DT[dtype]), True], [1])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,F,K", [(1, 24, 72), (8, 4096, 2048), (30, 160, 96), (33, 72, 200), (200, 328, 264), (2048, 512, 256)])
+def test_linear_with_the_swiglu_epilogue(dtype, M, F, K):
+    g = gen(17)
+    a = rnd(g, M, K, dtype=DT[dtype])
+    w = rnd(g, 2 * F, K, dtype=DT[dtype], scale=2 / math.sqrt(K))
+    cs, cb = 1 + rnd(g, 2 * F, scale=0.3), rnd(g, 2 * F, scale=0.3)
+    for scale, bias in ((None, None), (cs, cb)):
+        cmp("linear_swiglu", [a, w, torch.empty(M, F, dtype=DT[dtype]), scale, bias], [2], tol_of=TOL[DT[dtype]] * 2)
+    ops.check_errors()
 
 
 @pytest.mark.parametrize("a_dt,w_dt,o_dt", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "bfloat16"),

@@ -157,24 +157,26 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int
 }
 
 // ---- SwiGLU product: out = silu(gate) * up, gate|up side by side in one row ---------------
+// interleave: gate and up come in groups of 16 columns (8 gates, then their 8 ups) instead of as two halves
 template <typename TI, typename T>
-__global__ void swiglu_kernel(const TI* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total) {
+__global__ void swiglu_kernel(const TI* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total, int interleave) {
   tlc_pdl();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t t = i / F;
   const int f = (int)(i % F);
-  const float g = to_f32(gu[t * ld + f]), u = to_f32(gu[t * ld + F + f]);
+  const int gc = interleave ? (f >> 3) * 16 + (f & 7) : f, uc = interleave ? gc + 8 : F + f;
+  const float g = to_f32(gu[t * ld + gc]), u = to_f32(gu[t * ld + uc]);
   out[i] = from_f32<T>(silu_f(g) * u);
 }
 
-extern "C" int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype,
+extern "C" int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, void* out, int dtype, int interleave,
                           cudaStream_t stream) {
   const size_t total = (size_t)T * F;
   if (total == 0) return 0;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(swiglu_kernel<TI, TT>, dim3(blocks), dim3(256), 0, stream, 
-      (const TI*)gu, ld, F, (TT*)out, total)));
+      (const TI*)gu, ld, F, (TT*)out, total, interleave)));
   TLC_CHECK_LAUNCH("swiglu");
   return 0;
 }

@@ -205,7 +205,9 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 
 constexpr int SK_WARPS = 16;          // warps per block, each with its own slices of K
 
-template <typename TO, int MG, int U>
+// With SWIGLU a block's 16 weight rows are 8 gate rows followed by their 8 up rows, and the block
+// writes silu(gate) * up for its 8 features (out is [M, N/2]).
+template <typename TO, int MG, int U, bool SWIGLU>
 __global__ void __launch_bounds__(SK_WARPS * 32, (MG <= 2 && U <= 4) ? 2 : 1)
 gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                        TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
@@ -273,6 +275,23 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
 #pragma unroll
         for (int j = 0; j < 4; j++) red[warp][mg - g0][lane][j] = acc[mg][j];
     __syncthreads();
+    if (SWIGLU) {
+      // one thread per output value: gate (rows 0..7 of the tile) and up (rows 8..15) of one feature and row
+      for (int idx = threadIdx.x; idx < RG * 64; idx += blockDim.x) {
+        const int mg = idx >> 6, ln = (idx & 63) >> 1, j = idx & 1;
+        float vg = 0.f, vu = 0.f;
+#pragma unroll
+        for (int ww = 0; ww < SK_WARPS; ww++) { vg += red[ww][mg][ln][j]; vu += red[ww][mg][ln][j + 2]; }
+        const int ng = n0 + (ln >> 2), nu = ng + 8;
+        const int m = (g0 + mg) * 8 + 2 * (ln & 3) + j;
+        if (nu < N && m < M) {
+          if (colscale) { vg *= colscale[ng]; vu *= colscale[nu]; }
+          if (colbias) { vg += colbias[ng]; vu += colbias[nu]; }
+          out[(size_t)m * ldo + (n0 >> 1) + (ln >> 2)] = from_f32<TO>(silu_f(vg) * vu);
+        }
+      }
+      continue;
+    }
     // one thread per output value: sum the warps' partial sums in warp order, epilogue, store
     for (int idx = threadIdx.x; idx < RG * 128; idx += blockDim.x) {
       const int mg = idx >> 7, ln = (idx & 127) >> 2, j = idx & 3;
@@ -292,7 +311,7 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
   }
 }
 
-template <typename TO, int MG>
+template <typename TO, int MG, bool SWIGLU>
 static void launch_skinny_mg(const __nv_bfloat16* a, int lda, const __nv_bfloat16* w, int ldw, TO* out, int ldo,
                              const float* colscale, const float* colbias, int accumulate, int M, int N, int K,
                              cudaStream_t stream) {
@@ -300,20 +319,20 @@ static void launch_skinny_mg(const __nv_bfloat16* a, int lda, const __nv_bfloat1
   const int n_steps = ((K >> 3) + 3) >> 2;
   // U steps per warp and round; with U <= 4 and few row groups two blocks fit on an SM
   if (n_steps <= SK_WARPS * 2)
-    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 2>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 2, SWIGLU>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
   else
-    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 4>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 4, SWIGLU>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
 }
 
-template <typename TO>
+template <typename TO, bool SWIGLU>
 static int launch_skinny_mma(const void* a, int lda, const void* w, int ldw, void* out, int ldo, const float* colscale,
                              const float* colbias, int accumulate, int M, int N, int K, cudaStream_t stream) {
   const __nv_bfloat16* ap = (const __nv_bfloat16*)a;
   const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
-  if (M <= 8) launch_skinny_mg<TO, 1>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
-  else if (M <= 16) launch_skinny_mg<TO, 2>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
-  else if (M <= 32) launch_skinny_mg<TO, 4>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
-  else launch_skinny_mg<TO, 8>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  if (M <= 8) launch_skinny_mg<TO, 1, SWIGLU>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  else if (M <= 16) launch_skinny_mg<TO, 2, SWIGLU>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  else if (M <= 32) launch_skinny_mg<TO, 4, SWIGLU>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  else launch_skinny_mg<TO, 8, SWIGLU>(ap, lda, wp, ldw, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, stream);
   TLC_CHECK_LAUNCH("linear(skinny mma)");
   return 0;
 }
@@ -328,8 +347,18 @@ extern "C" int tlc_linear_skinny(const void* a, int lda, const void* w, int ldw,
                                  const float* colscale, const float* colbias, int accumulate, int M, int N, int K,
                                  cudaStream_t stream) {
   if (out_dtype == TLC_F32)
-    return launch_skinny_mma<float>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+    return launch_skinny_mma<float, false>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
   if (out_dtype == TLC_BF16)
-    return launch_skinny_mma<__nv_bfloat16>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+    return launch_skinny_mma<__nv_bfloat16, false>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
+}
+
+extern "C" int tlc_linear_skinny_swiglu(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
+                                        const float* colscale, const float* colbias, int M, int N, int K,
+                                        cudaStream_t stream) {
+  if (out_dtype == TLC_F32)
+    return launch_skinny_mma<float, true>(a, lda, w, ldw, out, ldo, colscale, colbias, 0, M, N, K, stream);
+  if (out_dtype == TLC_BF16)
+    return launch_skinny_mma<__nv_bfloat16, true>(a, lda, w, ldw, out, ldo, colscale, colbias, 0, M, N, K, stream);
   return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
 }

@@ -139,7 +139,9 @@ struct Smem {
 // that blocks running together share a weight tile in L2).  The shared-memory ring runs on across
 // tiles; the accumulator alternates between two halves of tensor memory so that the epilogue of
 // one tile overlaps the products of the next.
-template <typename TO, int BN, int STAGES>
+// With SWIGLU the weight rows come in groups of 16 = 8 gate rows followed by their 8 up rows;
+// the epilogue writes silu(gate) * up, half as many columns ([M, N/2], row stride ldo).
+template <typename TO, int BN, int STAGES, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
@@ -253,7 +255,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const bool n_ok = n < N;
         const float cs = (colscale && n_ok) ? colscale[n] : 1.0f;
         const float cb = (colbias && n_ok) ? colbias[n] : 0.0f;
-        if (accumulate) {
+        if (SWIGLU) {
+          // 16 features per 32 columns: lanes 0..15 take one row, lanes 16..31 the next; a lane reads
+          // its feature's gate and up columns from the staged tile and writes one value
+          const int f = lane & 15, gcol = ((f >> 3) << 4) + (f & 7);
+          const int ng = nc0 + gcol, nu = ng + 8;
+          const bool f_ok = nu < N;
+          const float csg = (colscale && f_ok) ? colscale[ng] : 1.0f, csu = (colscale && f_ok) ? colscale[nu] : 1.0f;
+          const float cbg = (colbias && f_ok) ? colbias[ng] : 0.0f, cbu = (colbias && f_ok) ? colbias[nu] : 0.0f;
+          const int oc = (nc0 >> 1) + f;
+#pragma unroll 4
+          for (int rr = lane >> 4; rr < 32; rr += 2) {
+            const int m = mrow0 + rr;
+            const float vg = st[rr * 33 + gcol] * csg + cbg, vu = st[rr * 33 + gcol + 8] * csu + cbu;
+            if (m < M && f_ok) out[(size_t)m * ldo + oc] = from_f32<TO>(silu_f(vg) * vu);
+          }
+        } else if (accumulate) {
           // all 32 reads of the old values are in flight before the first add
           float old[32];
 #pragma unroll
@@ -309,9 +326,9 @@ struct MapHash {
 };
 std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;
 
-template <typename TO, int BN, int STAGES>
+template <typename TO, int BN, int STAGES, bool SWIGLU = false>
 int configure() {
-  if (cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, BN, STAGES, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            Smem<BN, STAGES>::TOTAL) != cudaSuccess)
     return tlc_fail(-2, "linear: cannot reserve %d bytes of shared memory", Smem<BN, STAGES>::TOTAL);
   return 0;
@@ -324,6 +341,10 @@ int init_once() {
   if (int rc = configure<__nv_bfloat16, 128, 6>()) return rc;
   if (int rc = configure<float, 256, 4>()) return rc;
   if (int rc = configure<__nv_bfloat16, 256, 4>()) return rc;
+  if (int rc = configure<float, 128, 6, true>()) return rc;
+  if (int rc = configure<__nv_bfloat16, 128, 6, true>()) return rc;
+  if (int rc = configure<float, 256, 4, true>()) return rc;
+  if (int rc = configure<__nv_bfloat16, 256, 4, true>()) return rc;
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
   if (g_sms <= 0) g_sms = 148;
@@ -364,11 +385,11 @@ int get_map(const void* p, int rows, int k, int ld, int box_rows, CUtensorMap* o
   return 0;
 }
 
-template <typename TO, int BN, int STAGES>
+template <typename TO, int BN, int STAGES, bool SWIGLU = false>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, const float* colscale, const float* colbias,
            int accumulate, int M, int N, int K, cudaStream_t stream) {
   using S = Smem<BN, STAGES>;
-  auto kern = gemm_tcgen05_kernel<TO, BN, STAGES>;
+  auto kern = gemm_tcgen05_kernel<TO, BN, STAGES, SWIGLU>;
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
   dim3 grid(tiles < g_sms ? tiles : g_sms);
   tlc_launch(kern, dim3(grid), dim3(THREADS), S::TOTAL, stream, ma, mb, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, g_err_dev);
@@ -400,6 +421,38 @@ extern "C" int tlc_linear_tcgen05_ok(int a_dtype, int lda, const void* a, int w_
 }
 
 // The linear layer of the library: tensor cores where the operands allow it, CUDA cores otherwise.
+extern "C" int tlc_linear_skinny_swiglu(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
+                                        const float* colscale, const float* colbias, int M, int N, int K,
+                                        cudaStream_t stream);
+
+// The fused feed-forward front: out[M, N/2] = silu(gate) * up, where the rows of w come in groups of
+// 16 (8 gate rows, then their 8 up rows) and gate/up = (a w^T) * colscale + colbias.  Returns 1 if no
+// kernel takes these operands (the caller then runs the product and the activation separately).
+extern "C" int tlc_linear_swiglu(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,
+                                 int out_dtype, int ldo, const float* colscale, const float* colbias, int M, int N, int K,
+                                 int min_rows_for_tensor_cores, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (N % 16 != 0 || !tlc_linear_tcgen05_ok(a_dtype, lda, a, w_dtype, ldw, w, K)) return 1;
+  TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N / 2, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N, K,
+              lda, ldw, ldo);
+  if (out_dtype != TLC_F32 && out_dtype != TLC_BF16) return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
+  if (M <= 32 && tlc_linear_skinny_ok(a_dtype, lda, a, w_dtype, ldw, w, M, K))
+    return tlc_linear_skinny_swiglu(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, M, N, K, stream);
+  if (M < min_rows_for_tensor_cores) return 1;
+  if (int rc = init_once()) return rc;
+  CUtensorMap ma, mb;
+  if (int rc = get_map(a, M, K, lda, BM, &ma)) return rc;
+  const long long tiles256 = (long long)((N + 255) / 256) * ((M + BM - 1) / BM);
+  if ((tiles256 >= 2LL * g_sms && g_tile_override != 128) || g_tile_override == 256) {
+    if (int rc = get_map(w, N, K, ldw, 256, &mb)) return rc;
+    return out_dtype == TLC_F32 ? launch<float, 256, 4, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream)
+                                : launch<__nv_bfloat16, 256, 4, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream);
+  }
+  if (int rc = get_map(w, N, K, ldw, 128, &mb)) return rc;
+  return out_dtype == TLC_F32 ? launch<float, 128, 6, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream)
+                              : launch<__nv_bfloat16, 128, 6, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream);
+}
+
 extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,
                           int out_dtype, int ldo, const float* colscale, const float* colbias, int accumulate, int M,
                           int N, int K, int min_rows_for_tensor_cores, cudaStream_t stream) {

@@ -24,10 +24,11 @@ _SIGNATURES = {
     "tlc_embed": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp],
     "tlc_rmsnorm": [_vp, _vp, _vp, _f, _i, _i, _vp, _i, _vp],
     "tlc_gated_rmsnorm": [_vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _vp],
-    "tlc_swiglu": [_vp, _i, _i, _i, _i, _vp, _i, _vp],
+    "tlc_swiglu": [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "tlc_gather_rows": [_vp, _vp, _i, _i, _vp, _vp],
     "tlc_linear_simt": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
     "tlc_linear": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "tlc_linear_swiglu": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
     "tlc_rope_kv_store": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                           _i, _vp],
     "tlc_attention": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
@@ -180,15 +181,18 @@ def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: Optional[torch.Tenso
           _stream())
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out = silu(gate_up[:, :F]) * gate_up[:, F:]."""
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """out = silu(gate) * up, where gate_up holds gate | up as two halves, or (interleaved) in
+    groups of 16 columns: 8 gates followed by their 8 ups."""
     _gpu(gate_up, out)
     T, F2 = gate_up.shape
     F = F2 // 2
     if not out.is_contiguous() or tuple(out.shape) != (T, F) or F2 != 2 * F:
         raise KernelError("swiglu: out must be contiguous [T, F]")
+    if interleaved and F % 8:
+        raise KernelError("swiglu: the interleaved layout needs a multiple of 8 features")
     _call("tlc_swiglu", gate_up.data_ptr(), dtype_code(gate_up.dtype), _rows(gate_up, "gate_up"), F, T,
-          out.data_ptr(), dtype_code(out.dtype), _stream())
+          out.data_ptr(), dtype_code(out.dtype), int(bool(interleaved)), _stream())
 
 
 def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
@@ -204,6 +208,33 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
 # (and, up to 64 rows, for narrow outputs) the weight matrix is streamed once by the mma.sync
 # kernel.  TLC_TENSOR_CORE_MIN_ROWS overrides it (a huge value keeps the tiled kernel out).
 TENSOR_CORE_MIN_ROWS = int(os.environ.get("TLC_TENSOR_CORE_MIN_ROWS", "33"))
+
+
+def linear_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale: Optional[torch.Tensor] = None,
+                  colbias: Optional[torch.Tensor] = None) -> None:
+    """out[M, F] = silu(gate) * up with gate | up = (a w^T) * colscale + colbias, the 2F rows of w in
+    groups of 16 (8 gate rows followed by their 8 up rows).  One kernel where the operands allow it
+    (bfloat16, 16-byte aligned rows), else the product and the activation one after the other."""
+    _gpu(a, w, out, colscale, colbias)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or N % 16 or tuple(out.shape) != (M, N // 2) or not out.is_contiguous():
+        raise KernelError(f"linear_swiglu: shapes a{tuple(a.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not agree")
+    _f32vec(colscale, N, "linear colscale")
+    _f32vec(colbias, N, "linear colbias")
+    global _launches
+    lib = library()
+    _launches += 1
+    rc = lib.tlc_linear_swiglu(a.data_ptr(), dtype_code(a.dtype), _rows(a, "linear input"), w.data_ptr(), dtype_code(w.dtype),
+                               _rows(w, "linear weight"), out.data_ptr(), dtype_code(out.dtype), N // 2, _p(colscale),
+                               _p(colbias), M, N, K, TENSOR_CORE_MIN_ROWS, _stream())
+    if rc == 1:                                   # no fused kernel for these operands
+        _launches -= 1
+        gu = torch.empty((M, N), dtype=torch.float32, device=a.device)
+        linear(a, w, gu, colscale, colbias)
+        swiglu(gu, out, interleaved=True)
+    elif rc != 0:
+        raise KernelError(f"tlc_linear_swiglu: {lib.tlc_last_error().decode()}")
 
 
 def check_errors() -> None:

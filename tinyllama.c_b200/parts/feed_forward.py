@@ -34,12 +34,26 @@ class SwiGLU(Part):
     def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
         self.gate_up.bind(tensors, dtype, device)
         self.down.bind(tensors, dtype, device)
+        # Rows regrouped as 8 gate rows followed by their 8 up rows, so that the product's epilogue
+        # has a feature's gate and up side by side and writes silu(gate) * up directly.
+        self.interleaved = self.F % 8 == 0
+        if self.interleaved:
+            F = self.F
+            idx = torch.arange(2 * F, device=self.gate_up.weight.device).reshape(2, F // 8, 8).permute(1, 0, 2).reshape(-1)
+            self.gate_up.weight = self.gate_up.weight[idx].contiguous()
+            if self.gate_up.colscale is not None:
+                self.gate_up.colscale = self.gate_up.colscale[idx].contiguous()
+            if self.gate_up.colbias is not None:
+                self.gate_up.colbias = self.gate_up.colbias[idx].contiguous()
 
     def forward(self, normed: torch.Tensor, residual: torch.Tensor) -> None:
         T = normed.shape[0]
-        gu = act_empty((T, 2 * self.F), normed, torch.float32)
-        self.gate_up.forward(normed, gu)
         act = act_empty((T, self.F), normed)
-        ops.swiglu(gu, act)
+        if self.interleaved:
+            ops.linear_swiglu(normed, self.gate_up.weight, act, self.gate_up.colscale, self.gate_up.colbias)
+        else:
+            gu = act_empty((T, 2 * self.F), normed, torch.float32)
+            self.gate_up.forward(normed, gu)
+            ops.swiglu(gu, act)
         self.down.forward(act, residual, accumulate=True)
 
