@@ -72,14 +72,16 @@ class LLM:
 
 
 def random_model(config: dict, seed: int = 0, dtype: Union[str, torch.dtype] = "bfloat16", device: str = "cuda:0",
-                 std: Optional[float] = None):
+                 std: Optional[float] = None, run_dtype: Union[str, torch.dtype, None] = None):
     """A model with random weights drawn on the device (no folder is written): for benchmarks
-    of configurations too large to be worth a round trip through a file."""
+    of configurations too large to be worth a round trip through a file.  `dtype` is what the
+    matrices are stored as, `run_dtype` (default: the same) what the model computes in: bfloat16
+    weights in a float32 run are widened exactly."""
     from .config import config_from_dict
-    from .weights.loader import run_dtype
+    from .weights.loader import run_dtype as _run_dtype
     cfg = config_from_dict(dict(config))
     model = build_model(cfg)
-    rd = run_dtype(dtype)
+    rd = _run_dtype(dtype)
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
     std = float(std if std is not None else getattr(cfg, "initializer_range", 0.02))
@@ -97,5 +99,5 @@ def random_model(config: dict, seed: int = 0, dtype: Union[str, torch.dtype] = "
         else:
             t = torch.zeros(s.shape, dtype=rd, device=device)
         tensors[s.name] = t
-    model.bind(tensors, rd, torch.device(device))
+    model.bind(tensors, rd if run_dtype is None else _run_dtype(run_dtype), torch.device(device))
     return model
