@@ -29,5 +29,5 @@ def test_config_is_flat_and_names_both_layer_counts():
     import bench
     assert bench.FULL_LAYERS == bench.CONFIG_1P5B["num_hidden_layers"] == 24
     nbytes = bench.decode_bytes(bench.CONFIG_1P5B, 8, 512)
-    assert 3.5e9 < nbytes < 4.5e9           # 2.7 GB of weights + 8 x (151 MB of state + 12.6 MB of keys and values)
+    assert 3.3e9 < nbytes < 3.5e9           # 2.69 GB of weights + 8 x (76.5 MB of state to read + 12.6 MB of keys and values)
     assert 5.0e12 < bench.prefill_flops(bench.CONFIG_1P5B, 2048) < 6.0e12
