@@ -102,7 +102,7 @@ def test_linear_with_the_swiglu_epilogue(dtype, M, F, K):
                                             ("bfloat16", "bfloat16", "float32"), ("bfloat16", "float32", "bfloat16")])
 @pytest.mark.parametrize("M,N,K", [(1, 130, 72), (5, 67, 200), (16, 64, 64), (17, 129, 100), (150, 70, 257),
                                    (8, 96, 1024), (17, 130, 72), (32, 40, 136), (33, 130, 72), (64, 200, 264), (65, 130, 72), (9, 2048, 2048), (129, 257, 200), (300, 128, 64), (64, 1000, 1096),
-                                   (2048, 384, 512)])
+                                   (2048, 384, 512), (100, 1000, 520)])
 def test_linear(a_dt, w_dt, o_dt, M, N, K):
     g = gen(4)
     a_full = rnd(g, M, K + 8, dtype=DT[a_dt])

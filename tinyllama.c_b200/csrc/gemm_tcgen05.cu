@@ -341,6 +341,10 @@ int init_once() {
   if (int rc = configure<__nv_bfloat16, 128, 6>()) return rc;
   if (int rc = configure<float, 256, 4>()) return rc;
   if (int rc = configure<__nv_bfloat16, 256, 4>()) return rc;
+  if (int rc = configure<float, 64, 8>()) return rc;
+  if (int rc = configure<__nv_bfloat16, 64, 8>()) return rc;
+  if (int rc = configure<float, 64, 8, true>()) return rc;
+  if (int rc = configure<__nv_bfloat16, 64, 8, true>()) return rc;
   if (int rc = configure<float, 128, 6, true>()) return rc;
   if (int rc = configure<__nv_bfloat16, 128, 6, true>()) return rc;
   if (int rc = configure<float, 256, 4, true>()) return rc;
@@ -415,6 +419,12 @@ extern "C" int tlc_linear_init() { return init_once(); }
 static int g_tile_override = 0;
 extern "C" void tlc_linear_tile_override(int bn) { g_tile_override = bn; }
 
+static bool narrow_tiles(int M, int N) {
+  const long long tiles128 = (long long)((N + 127) / 128) * ((M + BM - 1) / BM);
+  return g_tile_override == 64 || (g_tile_override == 0 && M <= BM && tiles128 < g_sms);
+}
+
+
 extern "C" int tlc_linear_tcgen05_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int K) {
   return a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
          ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0);
@@ -447,6 +457,11 @@ extern "C" int tlc_linear_swiglu(const void* a, int a_dtype, int lda, const void
     if (int rc = get_map(w, N, K, ldw, 256, &mb)) return rc;
     return out_dtype == TLC_F32 ? launch<float, 256, 4, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream)
                                 : launch<__nv_bfloat16, 256, 4, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream);
+  }
+  if (narrow_tiles(M, N)) {
+    if (int rc = get_map(w, N, K, ldw, 64, &mb)) return rc;
+    return out_dtype == TLC_F32 ? launch<float, 64, 8, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream)
+                                : launch<__nv_bfloat16, 64, 8, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream);
   }
   if (int rc = get_map(w, N, K, ldw, 128, &mb)) return rc;
   return out_dtype == TLC_F32 ? launch<float, 128, 6, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream)
@@ -482,6 +497,12 @@ extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, in
     if (int rc = get_map(w, N, K, ldw, 256, &mb)) return rc;
     return out_dtype == TLC_F32 ? launch<float, 256, 4>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream)
                                 : launch<__nv_bfloat16, 256, 4>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  }
+  // few rows and not enough 128-wide tiles to occupy the GPU: 64-wide tiles, twice as many blocks stream the weights
+  if (narrow_tiles(M, N)) {
+    if (int rc = get_map(w, N, K, ldw, 64, &mb)) return rc;
+    return out_dtype == TLC_F32 ? launch<float, 64, 8>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream)
+                                : launch<__nv_bfloat16, 64, 8>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
   }
   if (int rc = get_map(w, N, K, ldw, 128, &mb)) return rc;
   return out_dtype == TLC_F32 ? launch<float, 128, 6>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream)
