@@ -7,12 +7,18 @@ their output into it in the order they are listed.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
 
 from .base import LayerCache, LayerSpec, Part, StepInfo, WeightSpec, act_empty
 from .linear import StackedLinear
+
+
+# One-token steps are chains of short kernels: mixers that are independent of one another between their
+# input and output projections then run side by side on streams of their own.
+PARALLEL_MIXERS = bool(int(os.environ.get("TLC_PARALLEL_MIXERS", "1")))
 
 
 class Block(Part):
@@ -50,6 +56,30 @@ class Block(Part):
                 self.fused_offsets.append((off, pr.out_features))
                 off += pr.out_features
 
+    def _mix_in_parallel(self, parts, step: StepInfo, cache: LayerCache, x32: torch.Tensor) -> None:
+        """The first mixer runs on the current stream, every other on a side stream that starts after
+        the shared input projection.  Output projections add into the residual stream one after the
+        other on the current stream, each after its mixer has finished.  (Under stream capture the
+        side streams become parallel branches of the graph.)"""
+        main = torch.cuda.current_stream()
+        if not hasattr(self, "_side"):
+            self._side = [torch.cuda.Stream(device=x32.device) for _ in self.mixers[1:]]
+        fork = torch.cuda.Event()
+        fork.record(main)
+        pending = []
+        for m, part, side in zip(self.mixers[1:], parts[1:], self._side):
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                act = m.mix(part, step, cache)
+                done = torch.cuda.Event()
+                done.record(side)
+            pending.append((m, act, done))
+        first = self.mixers[0]
+        first.output(first.mix(parts[0], step, cache), x32)
+        for m, act, done in pending:
+            main.wait_event(done)
+            m.output(act, x32)
+
     def forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
         """Updates the float32 residual stream x32 [T, D] in place."""
         if self.mixers:
@@ -58,8 +88,12 @@ class Block(Part):
             if self.fused_in is not None:
                 proj = torch.empty((x32.shape[0], self.fused_in.out_features), dtype=torch.float32, device=x32.device)
                 self.fused_in.forward(normed, proj)
-                for m, (off, n) in zip(self.mixers, self.fused_offsets):
-                    m.forward_projected(proj[:, off:off + n], step, cache, x32)
+                parts = [proj[:, off:off + n] for off, n in self.fused_offsets]
+                if step.max_new == 1 and x32.is_cuda and PARALLEL_MIXERS and all(hasattr(m, "mix") for m in self.mixers):
+                    self._mix_in_parallel(parts, step, cache, x32)
+                else:
+                    for m, part in zip(self.mixers, parts):
+                        m.forward_projected(part, step, cache, x32)
             else:
                 for m in self.mixers:
                     m.forward(normed, step, cache, x32)

@@ -62,6 +62,10 @@ class AttentionMixer(Part):
 
     def forward_projected(self, qkv: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor) -> None:
         """qkv: this mixer's input projection, float32 [T, q|k|v] (rows may be strided)."""
+        self.output(self.mix(qkv, step, cache), residual)
+
+    def mix(self, qkv: torch.Tensor, step: StepInfo, cache: LayerCache) -> torch.Tensor:
+        """Everything between the input projection and the output projection: [T, H*hd]."""
         T = step.n_rows
         kv = cache.kv[self.cache_key]
         q = torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
@@ -71,4 +75,8 @@ class AttentionMixer(Part):
         ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
                       self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
                       step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos)
+        return att
+
+    def output(self, att: torch.Tensor, residual: torch.Tensor) -> None:
+        """Adds the output projection of `att` into the residual stream."""
         self.o.forward(att, residual, accumulate=True)

@@ -87,6 +87,10 @@ class Mamba2Mixer(Part):
 
     def forward_projected(self, proj: torch.Tensor, step: StepInfo, cache: LayerCache, residual: torch.Tensor) -> None:
         """proj: this mixer's input projection, float32 [T, z|x|B|C|dt] (rows may be strided)."""
+        self.output(self.mix(proj, step, cache), residual)
+
+    def mix(self, proj: torch.Tensor, step: StepInfo, cache: LayerCache) -> torch.Tensor:
+        """Everything between the input projection and the output projection: [T, d_ssm]."""
         T, f32 = step.n_rows, torch.float32
         conv_state = cache.state[self.cache_key + ".conv"]
         ssm_state = cache.state[self.cache_key + ".ssm"]
@@ -100,4 +104,8 @@ class Mamba2Mixer(Part):
                      self.N, self.G, step.chunks, self.A if self.dtype == torch.bfloat16 else None)
         gated = new((T, self.Di), self.dtype)
         ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated)
+        return gated
+
+    def output(self, gated: torch.Tensor, residual: torch.Tensor) -> None:
+        """Adds the output projection of `gated` into the residual stream."""
         self.out_proj.forward(gated, residual, accumulate=True)
