@@ -220,6 +220,49 @@ def test_attention_of_single_token_steps(dtype, H, KV, hd, window):
                           hd, 1.0 / math.sqrt(hd), window, max_keys], [7], tol_of=TOL[DT[dtype]] * 2)
 
 
+@pytest.mark.parametrize("write", [True, False])
+@pytest.mark.parametrize("H,KV,hd,rope,window", [(8, 2, 128, 128, 0), (6, 3, 64, 32, 0), (4, 4, 128, 0, 100), (7, 1, 64, 64, 17),
+                                                 (2, 2, 256, 128, 0)])
+def test_attention_of_single_token_steps_in_one_kernel(H, KV, hd, rope, window, write):
+    """Rotation, store of the new row and attention in one launch, against the three plain steps;
+    run twice so that the arrival counters are seen to come back to zero."""
+    g = gen(14)
+    starts = [0, 200, 63, 700, 127, 128]
+    lens = [1] * len(starts)
+    B = len(starts)
+    pos, row_seq, cu, _ = _step_arrays(starts, lens)
+    slots, table, k_pages, v_pages = _paged_setup(g, B, [s + 1 for s in starts], KV, hd, torch.bfloat16, n_slots=7)
+    k_pages[int(table[int(slots[3]), 0]), :, 3, :] *= 4.0        # a far key stands out
+    width = (H + 2 * KV) * hd
+    qkv = rnd(g, B, width + 7)
+    view = lambda t: t[:, 3:3 + width]
+    inv = (1.0 / torch.pow(torch.tensor(1e4, dtype=torch.float64),
+                           torch.arange(rope // 2, dtype=torch.float64) * 2 / max(rope, 1))).float()
+    scale = 1.0 / math.sqrt(hd)
+    # plain: rotate and store, then attend
+    k_ref, v_ref = k_pages.clone(), v_pages.clone()
+    q_ref = torch.empty(B, H * hd, dtype=torch.bfloat16)
+    ops_plain.rope_kv_store(view(qkv), 0, H * hd, (H + KV) * hd, q_ref, k_ref, v_ref, inv, pos, row_seq, slots, table, H, KV,
+                            hd, write)
+    out_ref = torch.empty(B, H * hd, dtype=torch.bfloat16)
+    ops_plain.attention(q_ref, k_ref, v_ref, table, pos, row_seq, slots, out_ref, H, KV, hd, scale, window)
+    for max_keys in (701, 1024, 701):
+        k_gpu, v_gpu = k_pages.cuda(), v_pages.cuda()
+        out = torch.empty(B, H * hd, dtype=torch.bfloat16, device="cuda")
+        qkv_gpu = qkv.cuda()
+        assert ops.attention_decode_fused_ok(view(qkv_gpu), torch.bfloat16, H, KV, hd)
+        ops.attention_decode_fused(view(qkv_gpu), 0, H * hd, (H + KV) * hd, k_gpu, v_gpu, inv.cuda(), write, table.cuda(),
+                                   pos.cuda(), row_seq.cuda(), slots.cuda(), out, H, KV, hd, scale, window, max_keys)
+        ref = out_ref.double()
+        assert (ref - out.cpu().double()).abs().max() <= TOL[torch.bfloat16] * 2 * ref.abs().max()
+        for name, got, want in (("keys", k_gpu, k_ref), ("values", v_gpu, v_ref)):
+            d = (got.cpu().double() - want.double()).abs().max()
+            assert d <= TOL[torch.bfloat16] * want.double().abs().max(), f"{name} in the pages differ by {d}"
+            if not write:
+                assert torch.equal(got.cpu(), want), f"{name} were written although the layer only reads"
+    assert not ops.attention_decode_fused_ok(view(qkv_gpu), torch.bfloat16, H, KV, 80)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("Di,G,N,K,Hs,bias", [(48, 1, 16, 4, 3, True), (144, 2, 32, 3, 6, False), (40, 1, 8, 2, 5, True)])
 def test_mamba_conv(dtype, Di, G, N, K, Hs, bias):

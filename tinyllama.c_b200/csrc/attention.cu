@@ -19,7 +19,7 @@ __global__ void rope_kv_store_kernel(const TI* __restrict__ qkv, int ld, int q_o
                                      const int* __restrict__ positions, const int* __restrict__ row_seq,
                                      const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
                                      int H, int KV, int hd, int write_kv) {
-  tlc_pdl();
+  tlc_pdl(qkv, q_out, k_pages, v_pages);
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = rope_dim >> 1;
@@ -80,7 +80,7 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
                       const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
                       const int* __restrict__ row_seq, const int* __restrict__ slots, T* __restrict__ out, int H, int KV,
                       int hd, float scale, int window) {
-  tlc_pdl();
+  tlc_pdl(q, k_pages, v_pages, out);
   extern __shared__ float qs_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -169,7 +169,7 @@ attention_decode_partial_kernel(const T* __restrict__ q, const T* __restrict__ k
                                 const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
                                 const int* __restrict__ row_seq, const int* __restrict__ slots, float* __restrict__ part_o,
                                 float* __restrict__ part_ml, int H, int KV, int hd, float scale, int window, int n_splits) {
-  tlc_pdl();
+  tlc_pdl(q, k_pages, v_pages, part_o, part_ml);
   extern __shared__ float sh[];
   const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
   const int G = H / KV;
@@ -261,7 +261,7 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
   const int k0 = split * DEC_KEYS;
   float* ml = part_ml + (((size_t)t * H + (size_t)g * G) * n_splits + split) * 2;
   if (k0 >= n_keys || k0 + DEC_KEYS <= start) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    tlc_wait(ml);
     if (threadIdx.x < G) { ml[(size_t)threadIdx.x * n_splits * 2] = -INFINITY; ml[(size_t)threadIdx.x * n_splits * 2 + 1] = 0.f; }
     return;
   }
@@ -286,7 +286,7 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
     const int pi = k0 / TLC_PAGE + threadIdx.x;
     pages[threadIdx.x] = (pi * TLC_PAGE < n_keys) ? table[pi] : 0;
   }
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  tlc_wait(q, kr, v_pages, part_o, ml);     // the row at the query's own position is new: kr, v_pages
   if (valid && kp == pos) {
 #pragma unroll
     for (int d8 = 0; d8 < DL; d8++) kq[d8] = kr[d8];
@@ -412,7 +412,7 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
 template <typename T>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                               T* __restrict__ out, int hd, int n_splits) {
-  tlc_pdl();
+  tlc_pdl(part_o, part_ml, out);
   const size_t th = blockIdx.x;                       // row * H + head
   const float* ml = part_ml + th * n_splits * 2;
   float m = -INFINITY;

@@ -52,7 +52,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                          const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int H, int KV,
                          float scale_log2, int window) {
-  tlc_pdl();
+  tlc_pdl(q, k_pages, v_pages, out);
   constexpr int CH = HD / 8;                  // 16-byte chunks per row
   constexpr int TILE_BYTES = FA_BN * HD * 2;
   extern __shared__ __align__(128) uint8_t fa_smem[];

@@ -39,9 +39,22 @@ int tlc_fail(int code, const char* fmt, ...);
 extern int g_tlc_pdl;
 extern "C" void tlc_set_pdl(int on);
 
-__device__ __forceinline__ void tlc_pdl() {
-  asm volatile("griddepcontrol.launch_dependents;");
+//
+// The wait takes the pointers through which the kernel reads what earlier kernels of the stream
+// wrote (or writes what they read): a load through a const __restrict__ pointer may otherwise be
+// moved above the wait by the compiler, which knows that nothing in the kernel writes there; after
+// tlc_wait the pointer's value comes out of an asm statement that follows the wait, so no access
+// through it can start earlier.  Weights and tables that the host uploaded need not be listed.
+template <typename P> __device__ __forceinline__ void tlc_launder(P& p) { asm volatile("" : "+l"(p) : : "memory"); }
+
+template <typename... P> __device__ __forceinline__ void tlc_wait(P&... ptrs) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  (tlc_launder(ptrs), ...);
+}
+
+template <typename... P> __device__ __forceinline__ void tlc_pdl(P&... ptrs) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  tlc_wait(ptrs...);
 }
 
 template <typename... KArgs, typename... Args>

@@ -24,7 +24,7 @@ int tlc_fail(int code, const char* fmt, ...) {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table, int D, int V,
                              float scale, float* __restrict__ out) {
-  tlc_pdl();
+  tlc_pdl(tokens, out);
   const int t = blockIdx.x;
   int tok = tokens[t];
   tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);   // ids are validated on the host; never read out of bounds
@@ -49,7 +49,7 @@ template <typename TO>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
                float eps, int D, TO* __restrict__ out) {
-  tlc_pdl();
+  tlc_pdl(x, rows, out);
   __shared__ float red[33];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
@@ -77,9 +77,82 @@ rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows, const 
   for (int d = threadIdx.x; d < D; d += blockDim.x) out[(size_t)r * D + d] = from_f32<TO>(xr[d] * s * w[d]);
 }
 
+// Rows whose width is a multiple of 4 (up to 16384): NT threads take PT float4 each.  The weight
+// does not depend on the kernel before this one and is fetched before the wait on it.  NT and PT
+// follow from the width alone, so a row's sum has the same tree whatever else is in the batch.
+template <typename TO> struct Out4;
+template <> struct Out4<float> {
+  static __device__ __forceinline__ void put(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+  }
+};
+template <> struct Out4<__nv_bfloat16> {
+  static __device__ __forceinline__ void put(__nv_bfloat16* p, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&lo);
+    u.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+
+template <typename TO, int NT, int PT>
+__global__ void __launch_bounds__(NT)
+rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                   float eps, int D, TO* __restrict__ out) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  __shared__ float red[33];
+  const int n4 = D >> 2;
+  float4 wv[PT], v[PT];
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    wv[i] = c < n4 ? __ldg(reinterpret_cast<const float4*>(w) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  tlc_wait(x, rows, out);
+  const int r = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * D);
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    v[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+#pragma unroll
+  for (int i = 0; i < PT; i++) ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  ss = block_sum(ss, red);
+  const float s = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    if (c < n4)
+      Out4<TO>::put(out + (size_t)r * D + 4 * c, v[i].x * s * wv[i].x, v[i].y * s * wv[i].y, v[i].z * s * wv[i].z,
+                    v[i].w * s * wv[i].w);
+  }
+}
+
+// picks NT, PT from the number of float4 in a row (at most 4096 of them)
+#define TLC_VEC_SHAPES(n4, LAUNCH)            \
+  if ((n4) <= 128) { LAUNCH(128, 1); }        \
+  else if ((n4) <= 256) { LAUNCH(256, 1); }   \
+  else if ((n4) <= 512) { LAUNCH(512, 1); }   \
+  else if ((n4) <= 1024) { LAUNCH(1024, 1); } \
+  else if ((n4) <= 2048) { LAUNCH(1024, 2); } \
+  else { LAUNCH(1024, 4); }
+
 extern "C" int tlc_rmsnorm(const float* x, const int* rows, const float* w, float eps, int R, int D, void* out,
                            int out_dtype, cudaStream_t stream) {
   if (R == 0) return 0;
+  if (D % 4 == 0 && D <= 16384 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    const int n4 = D / 4;
+#define TLC_RMS_LAUNCH(NT, PT)                                                                                        \
+  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_vec_kernel<TO, NT, PT>, dim3(R), dim3(NT), 0, stream, x, rows, w, \
+                                               eps, D, (TO*)out))
+    TLC_VEC_SHAPES(n4, TLC_RMS_LAUNCH)
+#undef TLC_RMS_LAUNCH
+    TLC_CHECK_LAUNCH("rmsnorm");
+    return 0;
+  }
   TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_kernel<TO>, dim3(R), dim3(256), 0, stream, x, rows, w, eps, D, (TO*)out));
   TLC_CHECK_LAUNCH("rmsnorm");
   return 0;
@@ -92,7 +165,7 @@ __global__ void __launch_bounds__(256)
 gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int ldz,
                                      const float* __restrict__ w, float eps, int Di, int gs, int norm_before_gate,
                                      TO* __restrict__ out) {
-  tlc_pdl();
+  tlc_pdl(y, z, out);
   __shared__ float red[33];
   const int t = blockIdx.x, g = blockIdx.y;
   const float* yr = y + (size_t)t * Di + (size_t)g * gs;
@@ -143,6 +216,54 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int 
   }
 }
 
+// Groups whose width is a multiple of 4 (up to 16384), 32-bit gate: NT threads take PT float4 each;
+// the weight is fetched before the wait on the previous kernel.
+template <typename TO, int NT, int PT>
+__global__ void __launch_bounds__(NT)
+gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ z, int ldz, const float* __restrict__ w,
+                         float eps, int Di, int gs, int norm_before_gate, TO* __restrict__ out) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  __shared__ float red[33];
+  const int t = blockIdx.x, g = blockIdx.y;
+  const int n4 = gs >> 2;
+  float4 wv[PT], v[PT], gate[PT];
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    wv[i] = c < n4 ? __ldg(reinterpret_cast<const float4*>(w + (size_t)g * gs) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  tlc_wait(y, z, out);
+  const float4* yr = reinterpret_cast<const float4*>(y + (size_t)t * Di + (size_t)g * gs);
+  const float4* zr = reinterpret_cast<const float4*>(z + (size_t)t * ldz + (size_t)g * gs);
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    v[i] = c < n4 ? yr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    gate[i] = c < n4 ? zr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    gate[i] = make_float4(silu_f(gate[i].x), silu_f(gate[i].y), silu_f(gate[i].z), silu_f(gate[i].w));
+    if (!norm_before_gate) { v[i].x *= gate[i].x; v[i].y *= gate[i].y; v[i].z *= gate[i].z; v[i].w *= gate[i].w; }
+    ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  }
+  ss = block_sum(ss, red);
+  const float s = 1.0f / sqrtf(ss / (float)gs + eps);
+  TO* o = out + (size_t)t * Di + (size_t)g * gs;
+#pragma unroll
+  for (int i = 0; i < PT; i++) {
+    const int c = threadIdx.x + i * NT;
+    if (c < n4) {
+      if (norm_before_gate)
+        Out4<TO>::put(o + 4 * c, (v[i].x * s * wv[i].x) * gate[i].x, (v[i].y * s * wv[i].y) * gate[i].y,
+                      (v[i].z * s * wv[i].z) * gate[i].z, (v[i].w * s * wv[i].w) * gate[i].w);
+      else
+        Out4<TO>::put(o + 4 * c, v[i].x * s * wv[i].x, v[i].y * s * wv[i].y, v[i].z * s * wv[i].z, v[i].w * s * wv[i].w);
+    }
+  }
+}
+
 extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int ldz, const float* w, float eps, int T,
                                  int Di, int n_groups, int norm_before_gate, void* out, int out_dtype,
                                  cudaStream_t stream) {
@@ -150,6 +271,17 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int
   TLC_REQUIRE(n_groups > 0 && Di % n_groups == 0, "gated_rmsnorm: width %d is not a multiple of %d groups", Di, n_groups);
   const int gs = Di / n_groups;
   dim3 grid(T, n_groups);
+  if (w != nullptr && z_dtype == TLC_F32 && gs % 4 == 0 && gs <= 16384 && ldz % 4 == 0 && ((uintptr_t)y % 16) == 0 &&
+      ((uintptr_t)z % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    const int n4 = gs / 4;
+#define TLC_GRMS_LAUNCH(NT, PT)                                                                                         \
+  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_vec_kernel<TO, NT, PT>, grid, dim3(NT), 0, stream, y,        \
+                                               (const float*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out))
+    TLC_VEC_SHAPES(n4, TLC_GRMS_LAUNCH)
+#undef TLC_GRMS_LAUNCH
+    TLC_CHECK_LAUNCH("gated_rmsnorm");
+    return 0;
+  }
   TLC_DISPATCH_DTYPE(z_dtype, TZ, TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_kernel<TZ, TO>, dim3(grid), dim3(256), 0, stream, 
       y, (const TZ*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out)));
   TLC_CHECK_LAUNCH("gated_rmsnorm");
@@ -160,7 +292,7 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int
 // interleave: gate and up come in groups of 16 columns (8 gates, then their 8 ups) instead of as two halves
 template <typename TI, typename T>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, int ld, int F, T* __restrict__ out, size_t total, int interleave) {
-  tlc_pdl();
+  tlc_pdl(gu, out);
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t t = i / F;
@@ -184,7 +316,7 @@ extern "C" int tlc_swiglu(const void* gu, int in_dtype, int ld, int F, int T, vo
 // ---- gather rows of a 32-bit matrix ------------------------------------------------------
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, int D,
                                    float* __restrict__ out) {
-  tlc_pdl();
+  tlc_pdl(x, rows, out);
   const float* xr = x + (size_t)rows[blockIdx.x] * D;
   for (int d = threadIdx.x; d < D; d += blockDim.x) out[(size_t)blockIdx.x * D + d] = xr[d];
 }

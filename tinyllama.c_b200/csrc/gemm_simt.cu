@@ -18,7 +18,7 @@ __global__ void __launch_bounds__(256)
 gemm_tiled_kernel(const TA* __restrict__ a, int lda, const TW* __restrict__ w, int ldw, TO* __restrict__ out, int ldo,
                   const float* __restrict__ colscale, const float* __restrict__ colbias, int accumulate, int M, int N,
                   int K) {
-  tlc_pdl();
+  tlc_pdl(a, out);
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(256)
 gemm_skinny_kernel(const TA* __restrict__ a, int lda, const TW* __restrict__ w, int ldw, TO* __restrict__ out, int ldo,
                    const float* __restrict__ colscale, const float* __restrict__ colbias, int accumulate, int M, int N,
                    int K, int m_base) {
-  tlc_pdl();
+  tlc_pdl(a, out);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * (blockDim.x >> 5) + warp;
   if (n >= N) return;
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(256)
 gemm_skinny_bf16x8_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                           TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                           const float* __restrict__ colbias, int accumulate, int M, int N, int K, int m_base) {
-  tlc_pdl();
+  tlc_pdl(a, out);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.x * (blockDim.x >> 5) + warp;
   if (n >= N) return;
@@ -240,7 +240,7 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
       wa[u] = in ? __ldg(w0 + c) : make_uint4(0, 0, 0, 0);
       wb[u] = in ? __ldg(w1 + c) : make_uint4(0, 0, 0, 0);
     }
-    if (s0 == warp * U) asm volatile("griddepcontrol.wait;" ::: "memory");     // first round only
+    if (s0 == warp * U) tlc_wait(a, out);                                      // first round only
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int c = (s0 + u) * 4 + t;
@@ -263,7 +263,7 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
       }
     }
   }
-  if (warp * U >= n_steps) asm volatile("griddepcontrol.wait;" ::: "memory");  // warps without a round of their own
+  if (warp * U >= n_steps) tlc_wait(a, out);                                   // warps without a round of their own
   // the warps' partial sums meet in shared memory, at most four row groups at a time
   constexpr int RG = MG < 4 ? MG : 4;
 #pragma unroll 1

@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                     const float* __restrict__ colbias, int accumulate, int M, int N, int K, ErrWords* err) {
-  tlc_pdl();
+  tlc_pdl(out);
   using S = Smem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);

@@ -22,7 +22,7 @@ __global__ void mamba_conv_kernel(const T* __restrict__ proj, int ld, int xbc_of
                                   const int* __restrict__ row_seq, const int* __restrict__ slots,
                                   const int* __restrict__ start_pos, float* __restrict__ xbc_out,
                                   float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs) {
-  tlc_pdl();
+  tlc_pdl(proj, conv_state, xbc_out, dt_out, dA_out);
   const int t = blockIdx.x;
   const int b = row_seq[t];
   const int i = t - cu_seqlens[b];                  // index of this row inside its sequence's new tokens
@@ -54,7 +54,7 @@ template <typename T>
 __global__ void mamba_conv_state_kernel(const T* __restrict__ proj, int ld, int xbc_off, float* __restrict__ conv_state,
                                         const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                                         const int* __restrict__ start_pos, int Cd, int K) {
-  tlc_pdl();
+  tlc_pdl(proj, conv_state);
   const int b = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= Cd) return;
@@ -85,7 +85,7 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
                                          float* __restrict__ conv_state, const int* __restrict__ slots,
                                          const int* __restrict__ start_pos, float* __restrict__ xbc_out,
                                          float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs) {
-  tlc_pdl();
+  tlc_pdl(proj, conv_state, xbc_out, dt_out, dA_out);
   const int b = blockIdx.x;                          // row b belongs to sequence b
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   const bool has_state = start_pos[b] > 0;
@@ -172,7 +172,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
   // In the plain mode the state this block starts from was written by an earlier step, not by
   // the kernel before this one: it is fetched before the wait on that kernel (see tlc_pdl).
   asm volatile("griddepcontrol.launch_dependents;");
-  if (mode != SCAN_PLAIN) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (mode != SCAN_PLAIN) tlc_wait(xbc, dt, dA, state, chunk_state, y, chunk_decay);
   extern __shared__ float sm[];
   const int seg = blockIdx.x, h = blockIdx.y;
   const int b = seg_seq ? seg_seq[seg] : seg;
@@ -202,7 +202,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
       const int p = p_base + r, n = lane + 32 * j;
       s[r][j] = (S_init && p < P && n < N) ? S_init[(size_t)p * N + n] : 0.f;
     }
-  if (mode == SCAN_PLAIN) asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (mode == SCAN_PLAIN) tlc_wait(xbc, dt, dA, y);
   // shared staging: per row  B[N] | C[N] | x[rows_per_block] | dt | dA
   const int per_tok = 2 * N + rows_per_block + 2;
   const float Dh = Dskip[h];
@@ -287,7 +287,7 @@ __global__ void __launch_bounds__(256)
 ssm_state_pass_kernel(const float* __restrict__ chunk_decay, float* __restrict__ state,
                       float* __restrict__ chunk_state, const int* __restrict__ seq_seg_start,
                       const int* __restrict__ slots, const int* __restrict__ start_pos, int Hs, int PN, int write_final) {
-  tlc_pdl();
+  tlc_pdl(chunk_decay, state, chunk_state);
   const int b = blockIdx.x, h = blockIdx.y;
   const int e = blockIdx.z * blockDim.x + threadIdx.x;
   const int c0 = seq_seg_start[b], c1 = seq_seg_start[b + 1];

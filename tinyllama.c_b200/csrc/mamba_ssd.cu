@@ -41,7 +41,7 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1
 __global__ void ssd_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A,
                                   const int* __restrict__ seg_start, float* __restrict__ cum,
                                   float* __restrict__ chunk_decay, int Hs) {
-  tlc_pdl();
+  tlc_pdl(dt, cum, chunk_decay);
   const int seg = blockIdx.x;
   const int h = blockIdx.y * blockDim.x + threadIdx.x;
   if (h >= Hs) return;
@@ -68,7 +68,7 @@ __global__ void ssd_cumsum_kernel(const float* __restrict__ dt, const float* __r
 __global__ void __launch_bounds__(128)
 ssd_cb_kernel(const float* __restrict__ xbc, const int* __restrict__ seg_start, float* __restrict__ cb, int Di, int N,
               int G, int Cd) {
-  tlc_pdl();
+  tlc_pdl(xbc, cb);
   constexpr int LD = 68;
   extern __shared__ uint32_t ssd_sm[];
   uint32_t* Cs = ssd_sm;                 // [64][LD]   rows i, columns n
@@ -143,7 +143,7 @@ template <int P>
 __global__ void __launch_bounds__(256)
 ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ cum,
                        const int* __restrict__ seg_start, float* __restrict__ chunk_state, int Hs, int N, int G, int Cd) {
-  tlc_pdl();
+  tlc_pdl(xbc, dt, cum, chunk_state);
   constexpr int LDX = P + 8, LDB = 128 + 8;
   extern __shared__ uint32_t ssd_sm[];
   uint32_t* Xs = ssd_sm;                 // [j][p]   x * w
@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(128)
 ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ cum,
                      const float* __restrict__ cb, const float* __restrict__ s_in, const float* __restrict__ Dskip,
                      const int* __restrict__ seg_start, float* __restrict__ y, int Hs, int N, int G, int Cd) {
-  tlc_pdl();
+  tlc_pdl(xbc, dt, cum, cb, s_in, y);
   constexpr int R = 64;                   // rows of the chunk per block
   constexpr int LDM = Q + 4, LDX = P + 8, LDC = 64 + 4;
   extern __shared__ uint32_t ssd_sm[];

@@ -62,7 +62,7 @@ __device__ int block_argmax(const float* v, int V, float* red, int* redi) {
 }
 
 __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
-  tlc_pdl();
+  tlc_pdl(logits, out);
   __shared__ float red[33];
   __shared__ int redi[33];
   const int r = block_argmax(logits + (size_t)blockIdx.x * V, V, red, redi);
@@ -127,7 +127,7 @@ __device__ float block_exclusive_scan(float v, float* scan_buf, float* total) {
 __global__ void __launch_bounds__(SAMP_THREADS)
 sample_kernel(const float* __restrict__ logits, float* __restrict__ work, const int* __restrict__ history,
               const float* __restrict__ uniforms, SampleParams sp, int V, int* __restrict__ out) {
-  tlc_pdl();
+  tlc_pdl(logits, work, history, uniforms, out);
   __shared__ float red[33];
   __shared__ int redi[33];
   __shared__ float scan_buf[33];

@@ -33,6 +33,9 @@ _SIGNATURES = {
                           _i, _vp],
     "tlc_attention": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
     "tlc_attention_decode": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "tlc_attention_decode_fused": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                                   _i, _i, _i, _i, _f, _i, _i, _vp],
+    "tlc_attention_decode_fused_ok": [_i, _i, _i],
     "tlc_attention_prefill": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
     "tlc_mamba_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
                        _i, _i, _i, _vp],
@@ -324,6 +327,51 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     _call("tlc_attention", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(),
           out.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), _stream())
+
+
+DISABLE_FUSED_DECODE_ATTENTION = bool(int(os.environ.get("TLC_DISABLE_FUSED_DECODE_ATTENTION", "0")))
+_arrivals: dict = {}      # device -> counters of the fused single-token attention (zero between launches)
+
+
+def attention_decode_fused_ok(qkv: torch.Tensor, cache_dtype: torch.dtype, H: int, KV: int, hd: int) -> bool:
+    """Whether attention_decode_fused takes this projection, cache type and these sizes."""
+    return bool(qkv.is_cuda and qkv.dtype == torch.float32 and cache_dtype == torch.bfloat16
+                and not DISABLE_FUSED_DECODE_ATTENTION and library().tlc_attention_decode_fused_ok(H, KV, hd))
+
+
+def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, k_pages: torch.Tensor,
+                           v_pages: torch.Tensor, inv_freq: torch.Tensor, write_kv: bool, block_table: torch.Tensor,
+                           positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
+                           H: int, KV: int, hd: int, scale: float, window: int, max_keys: int) -> None:
+    """Single-token steps in one kernel: rotates the row's queries and new key (2 * len(inv_freq)
+    leading dims of each head), stores the new key/value row into its page when write_kv, attends
+    over the sequence's pages and writes out [T, H*hd] bfloat16.  qkv is float32 with dense rows."""
+    _gpu(qkv, k_pages, v_pages, inv_freq, block_table, positions, row_seq, slots, out)
+    T = qkv.shape[0]
+    for t, n in ((positions, "positions"), (row_seq, "row_seq"), (slots, "slots"), (block_table, "block_table")):
+        _i32(t, n)
+    if qkv.dtype != torch.float32 or k_pages.dtype != torch.bfloat16 or v_pages.dtype != torch.bfloat16 \
+            or out.dtype != torch.bfloat16:
+        raise KernelError("attention_decode_fused: float32 projections, bfloat16 pages and output")
+    if not out.is_contiguous() or tuple(out.shape) != (T, H * hd) or not k_pages.is_contiguous() \
+            or not v_pages.is_contiguous() or tuple(k_pages.shape[1:]) != (KV, PAGE, hd) or v_pages.shape != k_pages.shape:
+        raise KernelError("attention_decode_fused: out must be contiguous [T, H*hd], pages contiguous [n, KV, 64, hd]")
+    ld = _rows(qkv, "qkv")
+    if max(q_off + H * hd, k_off + KV * hd, v_off + KV * hd) > max(ld, qkv.shape[1]):
+        raise KernelError("attention_decode_fused: q, k or v lies outside the projection's row")
+    _f32vec(inv_freq, inv_freq.numel(), "rope inv_freq")
+    n_splits = (int(max_keys) + 127) // 128
+    part_o = torch.empty((T, H, n_splits, hd), dtype=torch.float32, device=qkv.device)
+    part_ml = torch.empty((T, H, n_splits, 2), dtype=torch.float32, device=qkv.device)
+    # One array of counters per device: launches that use it must not overlap on the GPU (those of
+    # one model never do: its attention layers follow one another).
+    arrivals = _arrivals.get(qkv.device.index)
+    if arrivals is None or arrivals.numel() < T * KV:
+        arrivals = _arrivals[qkv.device.index] = torch.zeros(max(65536, 2 * T * KV), dtype=torch.int32, device=qkv.device)
+    _call("tlc_attention_decode_fused", qkv.data_ptr(), ld, q_off, k_off, v_off, k_pages.data_ptr(), v_pages.data_ptr(),
+          inv_freq.data_ptr(), 2 * inv_freq.numel(), int(bool(write_kv)), block_table.data_ptr(), block_table.shape[1],
+          positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(), out.data_ptr(), part_o.data_ptr(),
+          part_ml.data_ptr(), arrivals.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), int(max_keys), _stream())
 
 
 DISABLE_SSD = bool(int(os.environ.get("TLC_DISABLE_SSD", "0")))

@@ -19,6 +19,7 @@ from .linear import StackedLinear
 # One-token steps are chains of short kernels: mixers that are independent of one another between their
 # input and output projections then run side by side on streams of their own.
 PARALLEL_MIXERS = bool(int(os.environ.get("TLC_PARALLEL_MIXERS", "1")))
+_MAIN_MIXER = int(os.environ["TLC_MAIN_MIXER"]) if "TLC_MAIN_MIXER" in os.environ else None
 
 
 class Block(Part):
@@ -57,28 +58,35 @@ class Block(Part):
                 off += pr.out_features
 
     def _mix_in_parallel(self, parts, step: StepInfo, cache: LayerCache, x32: torch.Tensor) -> None:
-        """The first mixer runs on the current stream, every other on a side stream that starts after
-        the shared input projection.  Output projections add into the residual stream one after the
-        other on the current stream, each after its mixer has finished.  (Under stream capture the
+        """One mixer runs on the current stream, every other on a side stream that starts after the
+        shared input projection.  Output projections add into the residual stream one after the
+        other on the current stream, in the mixers' order, each after its mixer has finished.  (Under stream capture the
         side streams become parallel branches of the graph.)"""
         main = torch.cuda.current_stream()
         if not hasattr(self, "_side"):
             self._side = [torch.cuda.Stream(device=x32.device) for _ in self.mixers[1:]]
+        # the mixer with the longest chain of kernels stays on the current stream, where every
+        # kernel follows its predecessor by a programmatic edge
+        lengths = [int(getattr(m, "single_token_launches", 1)) for m in self.mixers]
+        here = _MAIN_MIXER if _MAIN_MIXER is not None else lengths.index(max(lengths))
         fork = torch.cuda.Event()
         fork.record(main)
-        pending = []
-        for m, part, side in zip(self.mixers[1:], parts[1:], self._side):
+        acts, done = [None] * len(self.mixers), [None] * len(self.mixers)
+        sides = iter(self._side)
+        for i, (m, part) in enumerate(zip(self.mixers, parts)):
+            if i == here:
+                continue
+            side = next(sides)
             side.wait_event(fork)
             with torch.cuda.stream(side):
-                act = m.mix(part, step, cache)
-                done = torch.cuda.Event()
-                done.record(side)
-            pending.append((m, act, done))
-        first = self.mixers[0]
-        first.output(first.mix(parts[0], step, cache), x32)
-        for m, act, done in pending:
-            main.wait_event(done)
-            m.output(act, x32)
+                acts[i] = m.mix(part, step, cache)
+                done[i] = torch.cuda.Event()
+                done[i].record(side)
+        acts[here] = self.mixers[here].mix(parts[here], step, cache)
+        for i, m in enumerate(self.mixers):          # outputs in the mixers' order, whatever ran where
+            if done[i] is not None:
+                main.wait_event(done[i])
+            m.output(acts[i], x32)
 
     def forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
         """Updates the float32 residual stream x32 [T, D] in place."""

@@ -20,6 +20,8 @@ from ..linear import StackedLinear
 
 @register_mixer("attention")
 class AttentionMixer(Part):
+    single_token_launches = 1      # what a one-token step launches in mix() (three without the fused kernel)
+
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, prefix: str,
                  position: PartSpec, bias: bool = False, window: Optional[int] = None, in_scale: float = 1.0,
                  out_scale: float = 1.0, key_scale: float = 1.0, cache_key: str = "kv"):
@@ -68,6 +70,15 @@ class AttentionMixer(Part):
         """Everything between the input projection and the output projection: [T, H*hd]."""
         T = step.n_rows
         kv = cache.kv[self.cache_key]
+        table = getattr(self.position, "rotation_table", None)
+        if step.max_new == 1 and table is not None and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
+            # one token per sequence: rotation, store and attention in one kernel
+            att = torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
+            ops.attention_decode_fused(qkv, self.q_off, self.k_off, self.v_off, kv.k_pages, kv.v_pages, table(),
+                                       cache.writes, kv.block_table, step.positions, step.row_seq, step.slots, att,
+                                       self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
+                                       step.max_context)
+            return att
         q = torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
         self.position.rotate_and_store(qkv, self.q_off, self.k_off, self.v_off, q, kv, step, self.H, self.KV, self.hd,
                                        cache.writes)

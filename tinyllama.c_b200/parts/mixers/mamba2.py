@@ -24,6 +24,8 @@ from ..linear import StackedLinear
 
 @register_mixer("mamba2")
 class Mamba2Mixer(Part):
+    single_token_launches = 3      # convolution, scan, gated norm: what a one-token step launches in mix()
+
     def __init__(self, hidden: int, d_ssm: int, n_heads: int, d_head: int, n_groups: int, d_state: int, d_conv: int,
                  prefix: str, eps: float, conv_bias: bool = True, proj_bias: bool = False, rms_norm: bool = True,
                  norm_before_gate: bool = False, slice_scales: Sequence[float] = (1.0,) * 5, in_scale: float = 1.0,

@@ -39,6 +39,11 @@ class RotaryNeox(Part):
                           step.row_seq, step.slots, kv.block_table, n_heads, n_kv, head_dim, write)
 
 
+    def rotation_table(self) -> torch.Tensor:
+        """The inverse frequencies (float32 [rope_dim/2]) for kernels that rotate by themselves."""
+        return self.inv_freq
+
+
 @register_position("none")
 class NoPosition(RotaryNeox):
     """No position encoding: queries and keys are stored as projected."""
