@@ -17,6 +17,7 @@
 // 2..5 = epilogue.  Every wait on an mbarrier is bounded; a wait that runs out records an
 // error code that the host reads, and the kernel frees its tensor memory and returns.
 #include "common.cuh"
+#include "mbarrier.cuh"
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
@@ -36,44 +37,6 @@ constexpr int BM = 128;
 constexpr int BK = 64;                 // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;   // about a second
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: false (and the error code recorded) if the phase does not complete in time.
-// `err` points at two words: [0] in device memory (what kernels read), [1] the address of a
-// host-mapped word that is written on failure only, so that the host can look without a copy.
-struct ErrWords { int flag; int* host; };
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, ErrWords* err, int code) {
-  if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try(bar, parity)) {
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-      atomicExch(&err->flag, code);
-      *(volatile int*)err->host = code;
-      return false;
-    }
-  }
-  return true;
-}
-
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
@@ -405,6 +368,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, con
 
 // Error word of the tensor-core kernels: 0, or which bounded wait ran out
 // (1 loader, 2 MMA issuer, 3 epilogue, 4 drain).  Reading it does not synchronise.
+ErrWords* tlc_error_words() { return g_err_dev; }
+
 extern "C" int tlc_linear_error() { return g_err_host ? *(volatile int*)g_err_host : 0; }
 extern "C" void tlc_linear_error_clear() {
   if (g_err_host) *g_err_host = 0;
