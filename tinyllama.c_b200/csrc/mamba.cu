@@ -13,7 +13,80 @@
 #define CONV_MAX_TAPS 16
 
 // ---- convolution + SiLU over packed rows, and softplus / decay of dt ---------------------
-// grid (T, ceil(Cd/256)); also writes dt and dA for the row (first blocks of a row).
+// grid (ceil(T / 8), ceil(Cd/256)): a thread owns one channel of 8 consecutive rows.  It reads the
+// raw samples of those rows and of the K-1 rows before them once (all loads issued together), and
+// takes a tap from the sequence's stored window only where the row is among the first K-1 of a
+// sequence that continues from a slot.  Also writes dt and dA of the rows (first blocks along y).
+#define CONV_ROWS 8
+template <typename T, int K>
+__global__ void __launch_bounds__(256)
+mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_off,
+                  const float* __restrict__ w, const float* __restrict__ bias,
+                  const float* __restrict__ dt_bias, const float* __restrict__ A,
+                  const float* __restrict__ conv_state, const int* __restrict__ cu_seqlens,
+                  const int* __restrict__ row_seq, const int* __restrict__ slots,
+                  const int* __restrict__ start_pos, float* __restrict__ xbc_out,
+                  float* __restrict__ dt_out, float* __restrict__ dA_out, int n_rows, int Cd, int Hs) {
+  tlc_pdl(proj, conv_state, xbc_out, dt_out, dA_out);
+  __shared__ int s_i[CONV_ROWS], s_has[CONV_ROWS], s_slot[CONV_ROWS];
+  const int t0 = blockIdx.x * CONV_ROWS;
+  if (threadIdx.x < CONV_ROWS) {
+    const int t = t0 + threadIdx.x;
+    int i = 0, has = 0, slot = 0;
+    if (t < n_rows) {
+      const int b = row_seq[t];
+      i = t - cu_seqlens[b];                          // index of the row inside its sequence's new tokens
+      has = start_pos[b] > 0;
+      slot = slots[b];
+    }
+    s_i[threadIdx.x] = i;
+    s_has[threadIdx.x] = has;
+    s_slot[threadIdx.x] = slot;
+  }
+  __syncthreads();
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c < Cd) {
+    // raw[q] is the sample of packed row t0 - (K-1) + q; rows before the step's first are never used
+    float raw[CONV_ROWS + K - 1], wk[K];
+#pragma unroll
+    for (int q = 0; q < CONV_ROWS + K - 1; q++) {
+      const int t = t0 - (K - 1) + q;
+      raw[q] = (t >= 0 && t < n_rows) ? to_f32(proj[(size_t)t * ld + xbc_off + c]) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < K; k++) wk[k] = w[(size_t)c * K + k];
+    const float bv = bias ? bias[c] : 0.f;
+#pragma unroll
+    for (int r = 0; r < CONV_ROWS; r++) {
+      const int t = t0 + r;
+      if (t >= n_rows) break;
+      const int i = s_i[r];
+      float sum = 0.f;
+#pragma unroll
+      for (int k = 0; k < K; k++) {
+        const int j = i - (K - 1 - k);                // new-token index that tap k reads
+        float x;
+        if (j >= 0) x = raw[r + k];                   // row t - (K-1-k) is raw row (t - (K-1-k)) - (t0 - (K-1)) = r + k
+        else x = s_has[r] ? conv_state[((size_t)s_slot[r] * (K - 1) + (K - 1 + j)) * Cd + c] : 0.f;
+        sum = fmaf(x, wk[k], sum);
+      }
+      xbc_out[(size_t)t * Cd + c] = silu_f(sum + bv);
+    }
+  }
+  if (c < Hs) {
+    const float db = dt_bias[c], Ac = A[c];
+#pragma unroll
+    for (int r = 0; r < CONV_ROWS; r++) {
+      const int t = t0 + r;
+      if (t >= n_rows) break;
+      const float dtv = softplus_f(to_f32(proj[(size_t)t * ld + dt_off + c]) + db);
+      dt_out[(size_t)t * Hs + c] = dtv;
+      dA_out[(size_t)t * Hs + c] = expf(dtv * Ac);
+    }
+  }
+}
+
+// Any number of taps: grid (T, ceil(Cd/256)), a thread per (row, channel).
 template <typename T>
 __global__ void mamba_conv_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_off,
                                   const float* __restrict__ w, const float* __restrict__ bias,
@@ -116,6 +189,9 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
   }
 }
 
+#define TLC_CONV_ROWS(KT)                                                                                              \
+  tlc_launch(mamba_conv_rows_kernel<TT, KT>, dim3(grid8), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, w, \
+             bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out, dA_out, T, Cd, Hs)
 extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, int dt_off, const float* w,
                               const float* bias, const float* dt_bias, const float* A, float* conv_state,
                               const int* cu_seqlens, const int* row_seq, const int* slots, const int* start_pos,
@@ -125,6 +201,7 @@ extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, 
   TLC_REQUIRE(K >= 1 && K - 1 <= CONV_MAX_TAPS, "mamba_conv: %d taps exceed the kernel's limit of %d", K, CONV_MAX_TAPS + 1);
   TLC_REQUIRE(Hs <= Cd, "mamba_conv: more heads (%d) than conv channels (%d)", Hs, Cd);
   dim3 grid(T, (Cd + 255) / 256);
+  dim3 grid8((T + CONV_ROWS - 1) / CONV_ROWS, (Cd + 255) / 256);
   dim3 grid2(B, (Cd + 255) / 256);
   if (single_rows && T == B) {
     TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(mamba_conv_decode_kernel<TT>, dim3(grid2), dim3(256), 0, stream, 
@@ -134,7 +211,11 @@ extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, 
     return 0;
   }
   TLC_DISPATCH_DTYPE(dtype, TT, {
-    tlc_launch(mamba_conv_kernel<TT>, dim3(grid), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, w, bias, dt_bias, A,
+    if (K == 4) TLC_CONV_ROWS(4);
+    else if (K == 3) TLC_CONV_ROWS(3);
+    else if (K == 2) TLC_CONV_ROWS(2);
+    else
+      tlc_launch(mamba_conv_kernel<TT>, dim3(grid), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, w, bias, dt_bias, A,
                                                     conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out,
                                                     dA_out, Cd, K, Hs);
     if (K > 1)
