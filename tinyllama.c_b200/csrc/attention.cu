@@ -20,9 +20,13 @@ __global__ void rope_kv_store_kernel(const TI* __restrict__ qkv, int ld, int q_o
                                      const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages,
                                      int H, int KV, int hd, int write_kv) {
   tlc_pdl(qkv, q_out, k_pages, v_pages);
+  // the row's angles once: cos and sin of position * inv_freq[i], shared by all heads
+  extern __shared__ float rope_cs[];                 // [half] cos | [half] sin
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int half = rope_dim >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &rope_cs[half + i], &rope_cs[i]);
+  __syncthreads();
   const TI* row = qkv + (size_t)t * ld;
   const int n_heads_total = H + 2 * KV;
   int page = -1;
@@ -42,8 +46,7 @@ __global__ void rope_kv_store_kernel(const TI* __restrict__ qkv, int ld, int q_o
       v = to_f32(src[d]);
     } else {
       const int i = d < half ? d : d - half;
-      float sn, cs;
-      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      const float cs = rope_cs[i], sn = rope_cs[half + i];
       const float a = to_f32(src[i]), b = to_f32(src[i + half]);
       v = d < half ? a * cs - b * sn : a * sn + b * cs;
     }
@@ -62,7 +65,7 @@ extern "C" int tlc_rope_kv_store(const void* qkv, int in_dtype, int dtype, int l
                                  int max_pages, int T, int H, int KV, int hd, int write_kv, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(rope_dim % 2 == 0 && rope_dim <= hd, "rope: rotated width %d must be even and at most head_dim %d", rope_dim, hd);
-  TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(rope_kv_store_kernel<TI, TT>, dim3(T), dim3(256), 0, stream, 
+  TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(rope_kv_store_kernel<TI, TT>, dim3(T), dim3(256), (size_t)rope_dim * sizeof(float), stream, 
       (const TI*)qkv, ld, q_off, k_off, v_off, (TT*)q_out, (TT*)k_pages, (TT*)v_pages, inv_freq, rope_dim, positions,
       row_seq, slots, block_table, max_pages, H, KV, hd, write_kv)));
   TLC_CHECK_LAUNCH("rope_kv_store");

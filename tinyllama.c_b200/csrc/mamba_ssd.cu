@@ -239,161 +239,153 @@ ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ 
 }
 
 // ---- chunk outputs ------------------------------------------------------------------------------------
-// grid (seg, Hs, 2); a block of 4 warps owns 64 rows of the chunk, warp w rows [16w, 16w+16), all P columns.
-//   acc = M Xd + Cs S_in^T,  M[i,j] = cb[i,j] exp(cum_i - cum_j) (j <= i),  Xd[j,p] = dt_j x[j,p],
-//   Cs[i,n] = exp(cum_i) C[i,n];   y = acc + D x
+// grid (seg, Hs, 2); a block of 8 warps owns 64 rows of the chunk: warp w has rows [16 (w & 3), +16) and
+// the columns of half w >> 2 of the head.
+//   acc  = M X,        M[i,j] = cb[i,j] exp(cum_i - cum_j) dt_j (j <= i),  X[j,p] = x[j,p]
+//   acc2 = C S_in^T    (the state the chunk starts from), scaled by exp(cum_i) at the end
+//   y = acc + exp(cum_i) acc2 + D x
+// M is built in shared memory by the block (it needs the exponentials); X, C and S_in arrive as they
+// are, by cp.async, and are rounded to TF32 in registers: X and the first slab of 32 state columns
+// are on their way while M is built, and each further slab while the one before it is multiplied.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+  const int bytes = pred ? 16 : 0;                 // 0: the 16 bytes are filled with zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N_> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
+
+constexpr int OUT_R = 64;                  // rows of the chunk per block
+constexpr int OUT_SL = 32;                 // state columns per slab
+constexpr int OUT_LDM = Q + 4, OUT_LDS = OUT_SL + 4;
+
 template <int P>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ cum,
                      const float* __restrict__ cb, const float* __restrict__ s_in, const float* __restrict__ Dskip,
                      const int* __restrict__ seg_start, float* __restrict__ y, int Hs, int N, int G, int Cd) {
   tlc_pdl(xbc, dt, cum, cb, s_in, y);
-  constexpr int R = 64;                   // rows of the chunk per block
-  constexpr int LDM = Q + 4, LDX = P + 8, LDC = 64 + 4;
-  extern __shared__ uint32_t ssd_sm[];
-  uint32_t* Ms = ssd_sm;                  // [R][j]
-  uint32_t* Xs = Ms + R * LDM;            // [j][p]
-  uint32_t* Cs = Xs + Q * LDX;            // [R][n slab of 64]
-  uint32_t* Ss = Cs + R * LDC;            // [p][n slab of 64]
-  float* cums = reinterpret_cast<float*>(Ss + P * LDC);     // [Q]
+  constexpr int R = OUT_R, LDM = OUT_LDM, LDX = P + 8, LDS = OUT_LDS, SL = OUT_SL;
+  constexpr int NT = P / 16;               // 8-column tiles of a warp's half of the head
+  extern __shared__ __align__(16) uint32_t ssd_sm[];
+  uint32_t* Ms = ssd_sm;                   // [R][j]            TF32
+  float* Xs = reinterpret_cast<float*>(Ms + R * LDM);        // [j][p]            raw
+  float* Cb = Xs + Q * LDX;                // [2][R][slab]      raw
+  float* Sb = Cb + 2 * R * LDS;            // [2][p][slab]      raw
+  float* cums = Sb + 2 * P * LDS;          // [Q]
+  float* dts = cums + Q;                   // [Q]
   const int seg = blockIdx.x, h = blockIdx.y, r0 = blockIdx.z * R;
   const int g = h / (Hs / G);
   const int Di = Hs * P;
   const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
   if (r0 >= L) return;
-  const int jmax = min(L, r0 + R);        // columns j < jmax matter for these rows
-  cums[threadIdx.x] = cum[(size_t)(t0 + min((int)threadIdx.x, L - 1)) * Hs + h];
+  const int jmax = min(L, r0 + R);         // columns j < jmax matter for these rows
+  const int tid = threadIdx.x;
+  const float* Cg = xbc + Di + (size_t)G * N + (size_t)g * N;
+  const float* Sg = s_in + (((size_t)seg * Hs + h) * P) * N;
+  const uint32_t xs0 = (uint32_t)__cvta_generic_to_shared(Xs), cb0 = (uint32_t)__cvta_generic_to_shared(Cb),
+                 sb0 = (uint32_t)__cvta_generic_to_shared(Sb);
+  // X: rows j < jmax, zeros below
+  for (int idx = tid; idx < Q * (P / 4); idx += 256) {
+    const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
+    const bool in = r < jmax;
+    cp_async16(xs0 + (uint32_t)(r * LDX + c4) * 4, xbc + (size_t)(t0 + (in ? r : 0)) * Cd + (size_t)h * P + c4, in);
+  }
+  cp_async_commit();
+  auto fetch_slab = [&](int n0, int buf) {
+    for (int idx = tid; idx < R * (SL / 4); idx += 256) {           // C rows of this block
+      const int rl = idx / (SL / 4), c4 = (idx % (SL / 4)) * 4;
+      const bool in = r0 + rl < L;
+      cp_async16(cb0 + (uint32_t)((buf * R + rl) * LDS + c4) * 4, Cg + (size_t)(t0 + (in ? r0 + rl : 0)) * Cd + n0 + c4, in);
+    }
+    for (int idx = tid; idx < P * (SL / 4); idx += 256) {           // the incoming state
+      const int p = idx / (SL / 4), c4 = (idx % (SL / 4)) * 4;
+      cp_async16(sb0 + (uint32_t)((buf * P + p) * LDS + c4) * 4, Sg + (size_t)p * N + n0 + c4, true);
+    }
+    cp_async_commit();
+  };
+  fetch_slab(0, 0);
+  if (tid < Q) {
+    const int r = min(tid, L - 1);
+    cums[tid] = cum[(size_t)(t0 + r) * Hs + h];
+    dts[tid] = tid < L ? dt[(size_t)(t0 + tid) * Hs + h] : 0.f;
+  }
   __syncthreads();
-  const float* cbg = cb + (((size_t)seg * G + g) * Q) * Q;
   // M: R rows x 32 float4, 8 loads in flight per thread
-#pragma unroll 1
-  for (int it0 = 0; it0 < R * 32 / 128; it0 += 8) {
+  const float* cbg = cb + (((size_t)seg * G + g) * Q) * Q;
+  {
     float4 v[8];
 #pragma unroll
     for (int u = 0; u < 8; u++) {
-      const int idx = threadIdx.x + (it0 + u) * 128;
+      const int idx = tid + u * 256;
       const int i = r0 + (idx >> 5), j4 = (idx & 31) * 4;
       v[u] = (j4 <= i && i < L) ? *reinterpret_cast<const float4*>(cbg + (size_t)i * Q + j4) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
     for (int u = 0; u < 8; u++) {
-      const int idx = threadIdx.x + (it0 + u) * 128;
+      const int idx = tid + u * 256;
       const int il = idx >> 5, i = r0 + il, j4 = (idx & 31) * 4;
-      uint32_t* d = Ms + il * LDM + j4;
-      if (j4 > i || i >= L) { d[0] = d[1] = d[2] = d[3] = 0u; continue; }
-      const float ci = cums[i];
-      d[0] = tf32(v[u].x * expf(ci - cums[j4]));
-      d[1] = (j4 + 1 <= i) ? tf32(v[u].y * expf(ci - cums[j4 + 1])) : 0u;
-      d[2] = (j4 + 2 <= i) ? tf32(v[u].z * expf(ci - cums[j4 + 2])) : 0u;
-      d[3] = (j4 + 3 <= i) ? tf32(v[u].w * expf(ci - cums[j4 + 3])) : 0u;
-    }
-  }
-  // Xd: rows j < jmax
-#pragma unroll 1
-  for (int it0 = 0; it0 < Q * (P / 4) / 128; it0 += 8) {
-    float4 v[8];
-    float w[8];
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-      const int idx = threadIdx.x + (it0 + u) * 128;
-      const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
-      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      w[u] = 0.f;
-      if (r < jmax) {
-        v[u] = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + (size_t)h * P + c4);
-        w[u] = dt[(size_t)(t0 + r) * Hs + h];
+      uint4 d = make_uint4(0u, 0u, 0u, 0u);
+      if (j4 <= i && i < L) {
+        const float ci = cums[i];
+        d.x = tf32(v[u].x * expf(ci - cums[j4]) * dts[j4]);
+        if (j4 + 1 <= i) d.y = tf32(v[u].y * expf(ci - cums[j4 + 1]) * dts[j4 + 1]);
+        if (j4 + 2 <= i) d.z = tf32(v[u].z * expf(ci - cums[j4 + 2]) * dts[j4 + 2]);
+        if (j4 + 3 <= i) d.w = tf32(v[u].w * expf(ci - cums[j4 + 3]) * dts[j4 + 3]);
       }
-    }
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-      const int idx = threadIdx.x + (it0 + u) * 128;
-      const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
-      uint32_t* d = Xs + r * LDX + c4;
-      d[0] = tf32(v[u].x * w[u]); d[1] = tf32(v[u].y * w[u]); d[2] = tf32(v[u].z * w[u]); d[3] = tf32(v[u].w * w[u]);
+      *reinterpret_cast<uint4*>(Ms + il * LDM + j4) = d;
     }
   }
+  cp_async_wait<1>();                      // X has arrived (the first slab may still be on its way)
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-  const int il_base = warp * 16, i_base = r0 + il_base;
-  float acc[P / 8][4];
+  const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+  const int il_base = (warp & 3) * 16, i_base = r0 + il_base, p_base = (warp >> 2) * (P / 2);
+  float acc[NT][4], acc2[NT][4];
 #pragma unroll
-  for (int j = 0; j < P / 8; j++)
+  for (int j = 0; j < NT; j++)
 #pragma unroll
-    for (int k = 0; k < 4; k++) acc[j][k] = 0.f;
+    for (int k = 0; k < 4; k++) acc[j][k] = acc2[j][k] = 0.f;
   // inside the chunk: columns j <= i only
   const int k_steps = (i_base + 16) / 8;
   for (int kk = 0; kk < k_steps; kk++) {
     const uint32_t* ar = Ms + (il_base + gq) * LDM + kk * 8 + tq;
     const uint32_t a0 = ar[0], a1 = ar[8 * LDM], a2 = ar[4], a3 = ar[8 * LDM + 4];
 #pragma unroll
-    for (int j = 0; j < P / 8; j++) {
-      const uint32_t* br = Xs + (kk * 8 + tq) * LDX + j * 8 + gq;
-      mma_tf32(acc[j], a0, a1, a2, a3, br[0], br[4 * LDX]);
+    for (int j = 0; j < NT; j++) {
+      const float* br = Xs + (kk * 8 + tq) * LDX + p_base + j * 8 + gq;
+      mma_tf32(acc[j], a0, a1, a2, a3, tf32(br[0]), tf32(br[4 * LDX]));
     }
   }
-  // what came before the chunk: rows of C scaled by exp(cum_i), times the incoming state
-  const float* Cg = xbc + Di + (size_t)G * N + (size_t)g * N;
-  const float* Sg = s_in + (((size_t)seg * Hs + h) * P) * N;
-  for (int n0 = 0; n0 < N; n0 += 64) {
-    __syncthreads();
-    {
-      float4 v[8];                          // R rows x 16 float4 of C = 8 per thread
+  // what came before the chunk: C times the incoming state, a slab of state columns at a time
+  const int n_slabs = N / SL;
+  for (int sl = 0; sl < n_slabs; sl++) {
+    cp_async_wait<0>();
+    __syncthreads();                       // slab sl is in shared memory; everybody is done with slab sl-1
+    if (sl + 1 < n_slabs) fetch_slab((sl + 1) * SL, (sl + 1) & 1);
+    const float* Cs = Cb + (size_t)(sl & 1) * R * LDS;
+    const float* Ss = Sb + (size_t)(sl & 1) * P * LDS;
 #pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int idx = threadIdx.x + u * 128;
-        const int r = r0 + (idx >> 4), c4 = (idx & 15) * 4;
-        v[u] = (r < L && n0 + c4 < N) ? *reinterpret_cast<const float4*>(Cg + (size_t)(t0 + r) * Cd + n0 + c4)
-                                      : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+    for (int kk = 0; kk < SL / 8; kk++) {
+      const float* ar = Cs + (il_base + gq) * LDS + kk * 8 + tq;
+      const uint32_t a0 = tf32(ar[0]), a1 = tf32(ar[8 * LDS]), a2 = tf32(ar[4]), a3 = tf32(ar[8 * LDS + 4]);
 #pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int idx = threadIdx.x + u * 128;
-        const int rl = idx >> 4, c4 = (idx & 15) * 4;
-        const float e = expf(cums[min(r0 + rl, Q - 1)]);
-        uint32_t* d = Cs + rl * LDC + c4;
-        d[0] = tf32(v[u].x * e); d[1] = tf32(v[u].y * e); d[2] = tf32(v[u].z * e); d[3] = tf32(v[u].w * e);
-      }
-    }
-#pragma unroll 1
-    for (int it0 = 0; it0 < P * 16 / 128; it0 += 8) {      // P rows x 16 float4 of the incoming state
-      float4 v[8];
-#pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int idx = threadIdx.x + (it0 + u) * 128;
-        const int p = idx >> 4, c4 = (idx & 15) * 4;
-        v[u] = (n0 + c4 < N) ? *reinterpret_cast<const float4*>(Sg + (size_t)p * N + n0 + c4) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-#pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int idx = threadIdx.x + (it0 + u) * 128;
-        const int p = idx >> 4, c4 = (idx & 15) * 4;
-        uint32_t* d = Ss + p * LDC + c4;
-        d[0] = tf32(v[u].x); d[1] = tf32(v[u].y); d[2] = tf32(v[u].z); d[3] = tf32(v[u].w);
-      }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int kk = 0; kk < 8; kk++) {
-      const uint32_t* ar = Cs + (il_base + gq) * LDC + kk * 8 + tq;
-      const uint32_t a0 = ar[0], a1 = ar[8 * LDC], a2 = ar[4], a3 = ar[8 * LDC + 4];
-#pragma unroll
-      for (int j = 0; j < P / 8; j++) {
-        const uint32_t* br = Ss + (j * 8 + gq) * LDC + kk * 8 + tq;        // B(k = n, col = p) = S_in[p][n]
-        mma_tf32(acc[j], a0, a1, a2, a3, br[0], br[4]);
+      for (int j = 0; j < NT; j++) {
+        const float* br = Ss + (p_base + j * 8 + gq) * LDS + kk * 8 + tq;       // B(k = n, col = p) = S_in[p][n]
+        mma_tf32(acc2[j], a0, a1, a2, a3, tf32(br[0]), tf32(br[4]));
       }
     }
   }
   const float Dh = Dskip[h];
 #pragma unroll
-  for (int j = 0; j < P / 8; j++) {
-    const int p = j * 8 + 2 * tq;
+  for (int r = 0; r < 2; r++) {
+    const int i = i_base + gq + 8 * r;
+    if (i < L) {
+      const float e = expf(cums[i]);
 #pragma unroll
-    for (int r = 0; r < 2; r++) {
-      const int i = i_base + gq + 8 * r;
-      if (i < L) {
-        const float2 xv = *reinterpret_cast<const float2*>(xbc + (size_t)(t0 + i) * Cd + (size_t)h * P + p);
+      for (int j = 0; j < NT; j++) {
+        const int p = p_base + j * 8 + 2 * tq;
+        const float2 xv = *reinterpret_cast<const float2*>(Xs + i * LDX + p);
         *reinterpret_cast<float2*>(y + (size_t)(t0 + i) * Di + (size_t)h * P + p) =
-            make_float2(acc[j][2 * r] + Dh * xv.x, acc[j][2 * r + 1] + Dh * xv.y);
+            make_float2(acc[j][2 * r] + e * acc2[j][2 * r] + Dh * xv.x, acc[j][2 * r + 1] + e * acc2[j][2 * r + 1] + Dh * xv.y);
       }
     }
   }
@@ -405,7 +397,9 @@ ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt
 inline size_t pad64(size_t n) { return (n + 63) / 64 * 64; }
 
 template <int P> size_t state_smem() { return (size_t)(Q * (P + 8) + Q * 136) * 4; }
-template <int P> size_t out_smem() { return (size_t)(64 * (Q + 4) + Q * (P + 8) + 64 * 68 + P * 68) * 4 + Q * 4; }
+template <int P> size_t out_smem() {
+  return (size_t)(OUT_R * OUT_LDM + Q * (P + 8) + 2 * OUT_R * OUT_LDS + 2 * P * OUT_LDS + 2 * Q) * 4;
+}
 
 template <int P> int configure() {
   if (cudaFuncSetAttribute(ssd_chunk_state_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)state_smem<P>()) != cudaSuccess ||
@@ -431,7 +425,7 @@ int run(const float* xbc, const float* dt, const float* A, const float* Dskip, f
   TLC_CHECK_LAUNCH("ssm_scan(chunk states)");
   if (int rc = tlc_ssm_state_pass_launch(chunk_decay, state, chunk_state, seq_seg_start, slots, start_pos, B, Hs, P * N, 1, stream))
     return rc;
-  tlc_launch(ssd_chunk_out_kernel<P>, dim3(n_seg, Hs, 2), dim3(128), out_smem<P>(), stream, xbc, dt, (const float*)cum,
+  tlc_launch(ssd_chunk_out_kernel<P>, dim3(n_seg, Hs, 2), dim3(256), out_smem<P>(), stream, xbc, dt, (const float*)cum,
              (const float*)cb, (const float*)chunk_state, Dskip, seg_start, y, Hs, N, G, Cd);
   TLC_CHECK_LAUNCH("ssm_scan(chunk outputs)");
   return 0;
