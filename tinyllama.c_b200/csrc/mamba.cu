@@ -375,7 +375,7 @@ ssm_state_pass_kernel(const float* __restrict__ chunk_decay, float* __restrict__
   if (c1 - c0 <= 0 || e >= PN) return;
   float* slot = state + ((size_t)slots[b] * Hs + h) * PN + e;
   float s = start_pos[b] > 0 ? *slot : 0.f;
-  constexpr int BATCH = 8;                 // chunks whose values are fetched together
+  constexpr int BATCH = 16;                // chunks whose values are fetched together
   for (int cb = c0; cb < c1; cb += BATCH) {
     float own[BATCH], decay[BATCH];
 #pragma unroll

@@ -38,49 +38,60 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1
 
 // ---- cumulative log-decay per (chunk, head) --------------------------------------------------------
 // cum[t, h] = sum of dt*A over the chunk's rows up to t; chunk_decay[seg, h] = exp(cum at the last row)
-__global__ void ssd_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A,
-                                  const int* __restrict__ seg_start, float* __restrict__ cum,
-                                  float* __restrict__ chunk_decay, int Hs) {
+__global__ void __launch_bounds__(128)
+ssd_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A, const int* __restrict__ seg_start,
+                  float* __restrict__ cum, float* __restrict__ chunk_decay, int Hs) {
   tlc_pdl(dt, cum, chunk_decay);
+  // a warp per (chunk, head): lane l owns rows 4l .. 4l+3 of the chunk; prefix sums by shuffles
   const int seg = blockIdx.x;
-  const int h = blockIdx.y * blockDim.x + threadIdx.x;
+  const int h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (h >= Hs) return;
-  const int t0 = seg_start[seg], t1 = seg_start[seg + 1];
+  const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
   const float a = A[h];
-  float c = 0.f;
-  for (int tb = t0; tb < t1; tb += 8) {
-    float d[8];
+  float d[Q / 32];
 #pragma unroll
-    for (int u = 0; u < 8; u++) d[u] = tb + u < t1 ? dt[(size_t)(tb + u) * Hs + h] : 0.f;
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-      if (tb + u < t1) {
-        c = fmaf(d[u], a, c);
-        cum[(size_t)(tb + u) * Hs + h] = c;
-      }
-    }
+  for (int u = 0; u < Q / 32; u++) {
+    const int r = lane * (Q / 32) + u;
+    d[u] = r < L ? dt[(size_t)(t0 + r) * Hs + h] * a : 0.f;
   }
-  chunk_decay[(size_t)seg * Hs + h] = expf(c);
+#pragma unroll
+  for (int u = 1; u < Q / 32; u++) d[u] += d[u - 1];
+  float run = d[Q / 32 - 1];                            // inclusive sum of the lanes up to this one
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float v = __shfl_up_sync(0xffffffffu, run, o);
+    if (lane >= o) run += v;
+  }
+  const float before = run - d[Q / 32 - 1];
+#pragma unroll
+  for (int u = 0; u < Q / 32; u++) {
+    const int r = lane * (Q / 32) + u;
+    if (r < L) cum[(size_t)(t0 + r) * Hs + h] = before + d[u];
+  }
+  if (lane == 31) chunk_decay[(size_t)seg * Hs + h] = expf(run);   // rows past L add nothing
 }
 
 // ---- C B^T per (chunk, group): cb[seg, g, i, j] for j <= i -----------------------------------------
-// grid (seg, G, 2): a block of 4 warps computes 64 rows x 128 columns; K = N in slabs of 64.
+// grid (seg, G, 8): a block of 4 warps computes a strip of 16 rows x 128 columns, warp w the columns
+// [32 w, 32 w + 32); K = N in slabs of 64.
 __global__ void __launch_bounds__(128)
 ssd_cb_kernel(const float* __restrict__ xbc, const int* __restrict__ seg_start, float* __restrict__ cb, int Di, int N,
               int G, int Cd) {
   tlc_pdl(xbc, cb);
   constexpr int LD = 68;
   extern __shared__ uint32_t ssd_sm[];
-  uint32_t* Cs = ssd_sm;                 // [64][LD]   rows i, columns n
-  uint32_t* Bs = ssd_sm + 64 * LD;       // [Q][LD]    rows j, columns n
-  const int seg = blockIdx.x, g = blockIdx.y, half = blockIdx.z;
+  uint32_t* Cs = ssd_sm;                 // [16][LD]   rows i, columns n
+  uint32_t* Bs = ssd_sm + 16 * LD;       // [Q][LD]    rows j, columns n
+  const int seg = blockIdx.x, g = blockIdx.y;
   const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-  const int i_base = half * 64 + warp * 16;                // this warp's 16 rows
+  const int i_base = blockIdx.z * 16;                      // the block's 16 rows
+  if (i_base >= L) return;
   const int n_tiles = min(16, (i_base + 16 + 7) / 8);      // columns j <= i only
-  float acc[16][4];
+  const int j_rows = min(Q, n_tiles * 8);                  // rows of B that matter
+  float acc[4][4];
 #pragma unroll
-  for (int j = 0; j < 16; j++)
+  for (int j = 0; j < 4; j++)
 #pragma unroll
     for (int k = 0; k < 4; k++) acc[j][k] = 0.f;
   const float* Bg = xbc + Di + (size_t)g * N;
@@ -96,9 +107,9 @@ ssd_cb_kernel(const float* __restrict__ xbc, const int* __restrict__ seg_start, 
         const int idx = threadIdx.x + (it0 + u) * 128;
         const int r = idx >> 4, c4 = (idx & 15) * 4;
         bv[u] = cv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < L && n0 + c4 < N) bv[u] = *reinterpret_cast<const float4*>(Bg + (size_t)(t0 + r) * Cd + n0 + c4);
-        const int ri = half * 64 + r;
-        if (r < 64 && ri < L && n0 + c4 < N) cv[u] = *reinterpret_cast<const float4*>(Cg + (size_t)(t0 + ri) * Cd + n0 + c4);
+        if (r < L && r < j_rows && n0 + c4 < N) bv[u] = *reinterpret_cast<const float4*>(Bg + (size_t)(t0 + r) * Cd + n0 + c4);
+        const int ri = i_base + r;
+        if (r < 16 && ri < L && n0 + c4 < N) cv[u] = *reinterpret_cast<const float4*>(Cg + (size_t)(t0 + ri) * Cd + n0 + c4);
       }
 #pragma unroll
       for (int u = 0; u < 8; u++) {
@@ -106,7 +117,7 @@ ssd_cb_kernel(const float* __restrict__ xbc, const int* __restrict__ seg_start, 
         const int r = idx >> 4, c4 = (idx & 15) * 4;
         uint32_t* bd = Bs + r * LD + c4;
         bd[0] = tf32(bv[u].x); bd[1] = tf32(bv[u].y); bd[2] = tf32(bv[u].z); bd[3] = tf32(bv[u].w);
-        if (r < 64) {
+        if (r < 16) {
           uint32_t* cd = Cs + r * LD + c4;
           cd[0] = tf32(cv[u].x); cd[1] = tf32(cv[u].y); cd[2] = tf32(cv[u].z); cd[3] = tf32(cv[u].w);
         }
@@ -115,12 +126,12 @@ ssd_cb_kernel(const float* __restrict__ xbc, const int* __restrict__ seg_start, 
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < 8; kk++) {
-      const uint32_t* ar = Cs + (warp * 16 + gq) * LD + kk * 8 + tq;
+      const uint32_t* ar = Cs + gq * LD + kk * 8 + tq;
       const uint32_t a0 = ar[0], a1 = ar[8 * LD], a2 = ar[4], a3 = ar[8 * LD + 4];
 #pragma unroll
-      for (int j = 0; j < 16; j++) {
-        if (j < n_tiles) {
-          const uint32_t* br = Bs + (j * 8 + gq) * LD + kk * 8 + tq;
+      for (int j = 0; j < 4; j++) {
+        if (warp * 4 + j < n_tiles) {
+          const uint32_t* br = Bs + ((warp * 4 + j) * 8 + gq) * LD + kk * 8 + tq;
           mma_tf32(acc[j], a0, a1, a2, a3, br[0], br[4]);
         }
       }
@@ -128,9 +139,9 @@ ssd_cb_kernel(const float* __restrict__ xbc, const int* __restrict__ seg_start, 
   }
   float* out = cb + (((size_t)seg * G + g) * Q) * Q;
 #pragma unroll
-  for (int j = 0; j < 16; j++) {
-    if (j < n_tiles) {
-      const int col = j * 8 + 2 * tq;
+  for (int j = 0; j < 4; j++) {
+    if (warp * 4 + j < n_tiles) {
+      const int col = (warp * 4 + j) * 8 + 2 * tq;
       *reinterpret_cast<float2*>(out + (size_t)(i_base + gq) * Q + col) = make_float2(acc[j][0], acc[j][1]);
       *reinterpret_cast<float2*>(out + (size_t)(i_base + gq + 8) * Q + col) = make_float2(acc[j][2], acc[j][3]);
     }
@@ -418,8 +429,8 @@ int run(const float* xbc, const float* dt, const float* A, const float* Dskip, f
   float* chunk_decay = chunk_state + pad64((size_t)n_seg * Hs * P * N);  // [n_seg, Hs]
   float* cum = chunk_decay + pad64((size_t)n_seg * Hs);                  // [T, Hs]
   float* cb = cum + pad64((size_t)T * Hs);                               // [n_seg, G, Q, Q]
-  tlc_launch(ssd_cumsum_kernel, dim3(n_seg, (Hs + 63) / 64), dim3(64), 0, stream, dt, A, seg_start, cum, chunk_decay, Hs);
-  tlc_launch(ssd_cb_kernel, dim3(n_seg, G, 2), dim3(128), (64 + Q) * 68 * 4, stream, xbc, seg_start, cb, Di, N, G, Cd);
+  tlc_launch(ssd_cumsum_kernel, dim3(n_seg, (Hs + 3) / 4), dim3(128), 0, stream, dt, A, seg_start, cum, chunk_decay, Hs);
+  tlc_launch(ssd_cb_kernel, dim3(n_seg, G, Q / 16), dim3(128), (16 + Q) * 68 * 4, stream, xbc, seg_start, cb, Di, N, G, Cd);
   tlc_launch(ssd_chunk_state_kernel<P>, dim3(n_seg, Hs, (N + 127) / 128), dim3(256), state_smem<P>(), stream, xbc, dt,
              (const float*)cum, seg_start, chunk_state, Hs, N, G, Cd);
   TLC_CHECK_LAUNCH("ssm_scan(chunk states)");
@@ -434,7 +445,7 @@ int run(const float* xbc, const float* dt, const float* A, const float* Dskip, f
 }  // namespace
 
 extern "C" int tlc_ssd_init() {
-  if (cudaFuncSetAttribute(ssd_cb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + Q) * 68 * 4) != cudaSuccess)
+  if (cudaFuncSetAttribute(ssd_cb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (16 + Q) * 68 * 4) != cudaSuccess)
     return tlc_fail(-2, "ssm_scan(chunked): cannot reserve shared memory");
   if (int rc = configure<64>()) return rc;
   return configure<128>();
