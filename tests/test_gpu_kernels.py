@@ -221,13 +221,15 @@ def test_attention_of_single_token_steps(dtype, H, KV, hd, window):
 
 
 @pytest.mark.parametrize("write", [True, False])
-@pytest.mark.parametrize("H,KV,hd,rope,window", [(8, 2, 128, 128, 0), (6, 3, 64, 32, 0), (4, 4, 128, 0, 100), (7, 1, 64, 64, 17),
-                                                 (2, 2, 256, 128, 0)])
-def test_attention_of_single_token_steps_in_one_kernel(H, KV, hd, rope, window, write):
+@pytest.mark.parametrize("H,KV,hd,rope,window,longest", [
+    (8, 2, 128, 128, 0, 700), (6, 3, 64, 32, 0, 700), (4, 4, 128, 0, 100, 700), (7, 1, 64, 64, 17, 700), (2, 2, 256, 128, 0, 700),
+    (8, 2, 128, 128, 0, 5000), (6, 3, 64, 64, 300, 3400)])
+def test_attention_of_single_token_steps_in_one_kernel(H, KV, hd, rope, window, longest, write):
     """Rotation, store of the new row and attention in one launch, against the three plain steps;
-    run twice so that the arrival counters are seen to come back to zero."""
+    run several times so that the arrival counters are seen to come back to zero.  The long
+    contexts take the blocks of 256 keys."""
     g = gen(14)
-    starts = [0, 200, 63, 700, 127, 128]
+    starts = [0, 200, 63, longest, 127, 128]
     lens = [1] * len(starts)
     B = len(starts)
     pos, row_seq, cu, _ = _step_arrays(starts, lens)
@@ -246,7 +248,7 @@ def test_attention_of_single_token_steps_in_one_kernel(H, KV, hd, rope, window, 
                             hd, write)
     out_ref = torch.empty(B, H * hd, dtype=torch.bfloat16)
     ops_plain.attention(q_ref, k_ref, v_ref, table, pos, row_seq, slots, out_ref, H, KV, hd, scale, window)
-    for max_keys in (701, 1024, 701):
+    for max_keys in (longest + 1, (longest // 1024 + 1) * 1024, longest + 1):
         k_gpu, v_gpu = k_pages.cuda(), v_pages.cuda()
         out = torch.empty(B, H * hd, dtype=torch.bfloat16, device="cuda")
         qkv_gpu = qkv.cuda()

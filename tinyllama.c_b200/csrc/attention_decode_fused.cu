@@ -13,17 +13,16 @@
 // ends and needs no clearing between launches.  It must be zero before the first launch.
 #include "common.cuh"
 
-#define FD_KEYS 128     // keys per block
-#define FD_TPK 4        // threads per key while scoring
-#define FD_NT (FD_KEYS * FD_TPK)
+#define FD_NT 512       // threads per block
 #define FD_NW (FD_NT / 32)
 #define FD_MAXG 8
 
-// HD: head size; GT: compile-time bound of the query heads per key/value head (G <= GT).
-// The block's 512 threads score its 128 keys four to a key (each takes every fourth 16-byte
+// HD: head size; GT: compile-time bound of the query heads per key/value head (G <= GT); KEYS: keys
+// per block, 128 or (long contexts, so that the grid stays near one wave) 256.
+// The block's 512 threads score its keys four (or two) to a key (each takes every fourth 16-byte
 // piece of the key row), then take the value rows HD/8 lanes to a row; partial outputs of the
 // rows of a warp meet by shuffles, those of the warps in shared memory.
-template <int HD, int GT>
+template <int HD, int GT, int KEYS>
 __global__ void __launch_bounds__(FD_NT)
 attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, int v_off,
                               __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
@@ -36,36 +35,37 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
   // wait on the previous kernel; the row's own projection is read after it.
   asm volatile("griddepcontrol.launch_dependents;");
   extern __shared__ float sh[];
+  constexpr int TPK = FD_NT / KEYS;          // threads per key while scoring
   constexpr int CH = HD / 8;                 // 16-byte pieces of a row = lanes per value row
-  constexpr int CPT = CH / FD_TPK;           // pieces of a key row per scoring thread
+  constexpr int CPT = CH / TPK;           // pieces of a key row per scoring thread
   constexpr int ROWS = FD_NT / CH;           // value rows in flight
-  constexpr int RPT = FD_KEYS / ROWS;        // value rows per thread
-  static_assert(CH % FD_TPK == 0 && FD_KEYS % ROWS == 0 && CH <= 32, "head size");
+  constexpr int RPT = KEYS / ROWS;        // value rows per thread
+  static_assert(CH % TPK == 0 && KEYS % ROWS == 0 && CH <= 32, "head size");
   const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
   const int t = blockIdx.x, g = blockIdx.y, split = blockIdx.z;
   const int G = H / KV;
   const int pos = positions[t];
   const int n_keys = pos + 1;
   const int start = (window > 0 && n_keys > window) ? n_keys - window : 0;
-  const int k0 = split * FD_KEYS;
-  const int smem_floats = G * HD + G * FD_KEYS + FD_NW * GT + FD_NW * G * HD;     // floats of dynamic shared memory
+  const int k0 = split * KEYS;
+  const int smem_floats = G * HD + G * KEYS + FD_NW * GT + FD_NW * G * HD;     // floats of dynamic shared memory
   float* ml = part_ml + (((size_t)t * H + (size_t)g * G) * n_splits + split) * 2;
-  const bool empty = k0 >= n_keys || k0 + FD_KEYS <= start;     // the same for all threads of the block
-  __shared__ int pages[FD_KEYS / TLC_PAGE + 1];
+  const bool empty = k0 >= n_keys || k0 + KEYS <= start;     // the same for all threads of the block
+  __shared__ int pages[KEYS / TLC_PAGE + 1];
   __shared__ int s_last;
   if (empty) {
     tlc_wait(ml);
     if (tid < G) { ml[(size_t)tid * n_splits * 2] = -INFINITY; ml[(size_t)tid * n_splits * 2 + 1] = 0.f; }
   } else {
     float* qs = sh;                                   // [G][HD]
-    float* ps = qs + (size_t)G * HD;                  // [G][FD_KEYS]
-    float* red = ps + (size_t)G * FD_KEYS;            // [FD_NW][GT]
+    float* ps = qs + (size_t)G * HD;                  // [G][KEYS]
+    float* red = ps + (size_t)G * KEYS;            // [FD_NW][GT]
     float* os = red + FD_NW * GT;                     // [FD_NW][G][HD]
     __nv_bfloat16* knew = reinterpret_cast<__nv_bfloat16*>(os + (size_t)FD_NW * G * HD);   // [HD]
     __nv_bfloat16* vnew = knew + HD;                                                       // [HD]
     const int* table = block_table + (size_t)slots[row_seq[t]] * max_pages;
-    const bool has_new = write_kv && pos >= k0 && pos < k0 + FD_KEYS;   // this block holds the row's own key
-    const int key = tid / FD_TPK, piece = tid % FD_TPK;
+    const bool has_new = write_kv && pos >= k0 && pos < k0 + KEYS;   // this block holds the row's own key
+    const int key = tid / TPK, piece = tid % TPK;
     const int kp = k0 + key;
     const bool valid = kp >= start && kp < n_keys;
     uint4 kq[CPT];
@@ -74,10 +74,10 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
       kr = reinterpret_cast<const uint4*>(k_pages + (((size_t)table[kp / TLC_PAGE] * KV + g) * TLC_PAGE + kp % TLC_PAGE) * HD);
       if (kp != pos) {
 #pragma unroll
-        for (int i = 0; i < CPT; i++) kq[i] = __ldg(kr + piece + FD_TPK * i);
+        for (int i = 0; i < CPT; i++) kq[i] = __ldg(kr + piece + TPK * i);
       }
     }
-    if (tid <= FD_KEYS / TLC_PAGE) {
+    if (tid <= KEYS / TLC_PAGE) {
       const int pi = k0 / TLC_PAGE + tid;
       pages[tid] = (pi * TLC_PAGE < n_keys) ? table[pi] : 0;
     }
@@ -131,11 +131,11 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
       }
       if (kp == pos) {
 #pragma unroll
-        for (int i = 0; i < CPT; i++) kq[i] = reinterpret_cast<const uint4*>(knew)[piece + FD_TPK * i];
+        for (int i = 0; i < CPT; i++) kq[i] = reinterpret_cast<const uint4*>(knew)[piece + TPK * i];
       }
     } else if (valid && kp == pos) {
 #pragma unroll
-      for (int i = 0; i < CPT; i++) kq[i] = kr[piece + FD_TPK * i];
+      for (int i = 0; i < CPT; i++) kq[i] = kr[piece + TPK * i];
     }
     float s[GT];
 #pragma unroll
@@ -143,7 +143,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
     if (valid) {
 #pragma unroll
       for (int i = 0; i < CPT; i++) {
-        const int c = piece + FD_TPK * i;
+        const int c = piece + TPK * i;
         const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&kq[i]);
         float kf[8];
 #pragma unroll
@@ -165,7 +165,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
 #pragma unroll
     for (int hg = 0; hg < GT; hg++)
 #pragma unroll
-      for (int o = 1; o < FD_TPK; o <<= 1) s[hg] += __shfl_xor_sync(0xffffffffu, s[hg], o);
+      for (int o = 1; o < TPK; o <<= 1) s[hg] += __shfl_xor_sync(0xffffffffu, s[hg], o);
     // maximum and sum over the block's keys, all heads of the group at once
     {
 #pragma unroll
@@ -184,7 +184,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
 #pragma unroll
           for (int w = 1; w < FD_NW; w++) m = fmaxf(m, red[w * GT + hg]);
           const float p = valid ? expf(s[hg] - m) : 0.f;
-          if (piece == 0) ps[hg * FD_KEYS + key] = p;
+          if (piece == 0) ps[hg * KEYS + key] = p;
           lsum[hg] = warp_sum(piece == 0 ? p : 0.f);
           s[hg] = m;
         }
@@ -207,7 +207,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
       }
     }
     __syncthreads();
-    const int nk = min(FD_KEYS, n_keys - k0);
+    const int nk = min(KEYS, n_keys - k0);
     const int dl = tid % CH, rg = tid / CH;
     float acc[GT][8];
 #pragma unroll
@@ -240,7 +240,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
 #pragma unroll
         for (int hg = 0; hg < GT; hg++) {
           if (hg < G) {
-            const float p = ps[hg * FD_KEYS + j];
+            const float p = ps[hg * KEYS + j];
 #pragma unroll
             for (int i = 0; i < 8; i++) acc[hg][i] = fmaf(p, vf[i], acc[hg][i]);
           }
@@ -348,8 +348,8 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
 
 static int bound_of(int G) { return G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : 8; }
 
-static size_t fused_smem(int G, int hd) {
-  return ((size_t)G * hd + (size_t)G * FD_KEYS + (size_t)FD_NW * bound_of(G) + (size_t)FD_NW * G * hd) * sizeof(float) +
+static size_t fused_smem(int G, int hd, int keys) {
+  return ((size_t)G * hd + (size_t)G * keys + (size_t)FD_NW * bound_of(G) + (size_t)FD_NW * G * hd) * sizeof(float) +
          2 * (size_t)hd * sizeof(__nv_bfloat16);
 }
 
@@ -357,20 +357,20 @@ static size_t fused_smem(int G, int hd) {
 extern "C" int tlc_attention_decode_fused_ok(int H, int KV, int hd) {
   if (KV <= 0 || H % KV != 0 || H / KV > FD_MAXG || KV > 65535) return 0;
   if (hd != 64 && hd != 128 && hd != 256) return 0;
-  return fused_smem(H / KV, hd) <= 200 * 1024;
+  return fused_smem(H / KV, hd, 256) <= 200 * 1024;
 }
 
-template <int HD, int GT, typename... Args>
+template <int HD, int GT, int KEYS, typename... Args>
 static cudaError_t launch_fused(dim3 grid, size_t smem, cudaStream_t stream, Args... args) {
   static bool raised[64] = {};          // per device: the kernel may use more than 48 KB of shared memory
   int dev = 0;
   cudaGetDevice(&dev);
   if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !raised[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_fused_kernel<HD, GT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_fused_kernel<HD, GT, KEYS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     raised[dev] = true;
   }
-  return tlc_launch(attention_decode_fused_kernel<HD, GT>, grid, dim3(FD_NT), smem, stream, args...);
+  return tlc_launch(attention_decode_fused_kernel<HD, GT, KEYS>, grid, dim3(FD_NT), smem, stream, args...);
 }
 
 // qkv: float32 rows of `ld` elements with the queries, keys and values of the row at q_off, k_off,
@@ -385,29 +385,37 @@ extern "C" int tlc_attention_decode_fused(const float* qkv, int ld, int q_off, i
   if (T == 0) return 0;
   TLC_REQUIRE(tlc_attention_decode_fused_ok(H, KV, hd), "attention(decode, fused): %d heads, %d key/value heads of size %d are outside the kernel's range", H, KV, hd);
   TLC_REQUIRE(rope_dim % 2 == 0 && rope_dim >= 0 && rope_dim <= hd, "attention(decode, fused): rotated width %d must be even and at most head_dim %d", rope_dim, hd);
-  const int n_splits = (max_keys + FD_KEYS - 1) / FD_KEYS;
+  // 128 keys a block while that keeps the grid within about one wave (two blocks an SM), else 256
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long blocks128 = (long long)T * KV * ((max_keys + 127) / 128);
+  const int keys = blocks128 > 2LL * sms ? 256 : 128;
+  const int n_splits = (max_keys + keys - 1) / keys;
   TLC_REQUIRE(n_splits >= 1 && n_splits <= 65535, "attention(decode, fused): %d keys are outside the kernel's range", max_keys);
-  const size_t smem = fused_smem(H / KV, hd);
+  const size_t smem = fused_smem(H / KV, hd, keys);
   dim3 grid(T, KV, n_splits);
   __nv_bfloat16 *kp = (__nv_bfloat16*)k_pages, *vp = (__nv_bfloat16*)v_pages, *op = (__nv_bfloat16*)out;
   cudaError_t e = cudaSuccess;
-#define TLC_FD_LAUNCH(HDV, GTV)                                                                                          \
-  e = launch_fused<HDV, GTV>(grid, smem, stream, qkv, ld, q_off, k_off, v_off, kp, vp, inv_freq, rope_dim, write_kv,      \
-                             block_table, max_pages, positions, row_seq, slots, part_o, part_ml, arrivals, op, H, KV,   \
-                             scale, window, n_splits)
-#define TLC_FD_HEAD(HDV)                                                  \
+#define TLC_FD_LAUNCH(HDV, GTV, KV_)                                                                                    \
+  e = launch_fused<HDV, GTV, KV_>(grid, smem, stream, qkv, ld, q_off, k_off, v_off, kp, vp, inv_freq, rope_dim, write_kv, \
+                                  block_table, max_pages, positions, row_seq, slots, part_o, part_ml, arrivals, op, H,  \
+                                  KV, scale, window, n_splits)
+#define TLC_FD_GROUP(HDV, KV_)                                            \
   do {                                                                    \
     switch (bound_of(H / KV)) {                                           \
-      case 1: TLC_FD_LAUNCH(HDV, 1); break;                               \
-      case 2: TLC_FD_LAUNCH(HDV, 2); break;                               \
-      case 4: TLC_FD_LAUNCH(HDV, 4); break;                               \
-      default: TLC_FD_LAUNCH(HDV, 8); break;                              \
+      case 1: TLC_FD_LAUNCH(HDV, 1, KV_); break;                          \
+      case 2: TLC_FD_LAUNCH(HDV, 2, KV_); break;                          \
+      case 4: TLC_FD_LAUNCH(HDV, 4, KV_); break;                          \
+      default: TLC_FD_LAUNCH(HDV, 8, KV_); break;                         \
     }                                                                     \
   } while (0)
+#define TLC_FD_HEAD(HDV)                                                  \
+  do { if (keys == 128) TLC_FD_GROUP(HDV, 128); else TLC_FD_GROUP(HDV, 256); } while (0)
   if (hd == 64) TLC_FD_HEAD(64);
   else if (hd == 128) TLC_FD_HEAD(128);
   else TLC_FD_HEAD(256);
 #undef TLC_FD_HEAD
+#undef TLC_FD_GROUP
 #undef TLC_FD_LAUNCH
   if (e != cudaSuccess) return tlc_fail(-2, "attention(decode, fused): %s", cudaGetErrorString(e));
   TLC_CHECK_LAUNCH("attention(decode, fused)");

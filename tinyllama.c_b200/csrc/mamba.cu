@@ -158,23 +158,36 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
                                          float* __restrict__ conv_state, const int* __restrict__ slots,
                                          const int* __restrict__ start_pos, float* __restrict__ xbc_out,
                                          float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs) {
-  tlc_pdl(proj, conv_state, xbc_out, dt_out, dA_out);
+  // The window was stored by the step before and the weights never change: both are fetched before the
+  // wait on the previous kernel; only the row's projection is read after it.
+  asm volatile("griddepcontrol.launch_dependents;");
   const int b = blockIdx.x;                          // row b belongs to sequence b
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   const bool has_state = start_pos[b] > 0;
   float* st = conv_state + (size_t)slots[b] * (K - 1) * Cd;
+  float prev[CONV_MAX_TAPS], wk[CONV_MAX_TAPS + 1];
+  float bv = 0.f, db = 0.f, Ac = 0.f;
   if (c < Cd) {
-    const float cur = to_f32(proj[(size_t)b * ld + xbc_off + c]);
-    float sum = cur * w[(size_t)c * K + (K - 1)];
-    float prev[CONV_MAX_TAPS];
 #pragma unroll
     for (int k = 0; k < CONV_MAX_TAPS; k++) {
-      if (k < K - 1) {
-        prev[k] = has_state ? st[(size_t)k * Cd + c] : 0.f;
-        sum = fmaf(prev[k], w[(size_t)c * K + k], sum);
-      }
+      prev[k] = (k < K - 1 && has_state) ? st[(size_t)k * Cd + c] : 0.f;
+      wk[k] = k < K ? w[(size_t)c * K + k] : 0.f;
     }
-    if (bias) sum += bias[c];
+    wk[CONV_MAX_TAPS] = CONV_MAX_TAPS < K ? w[(size_t)c * K + CONV_MAX_TAPS] : 0.f;
+    if (bias) bv = bias[c];
+  }
+  if (c < Hs) { db = dt_bias[c]; Ac = A[c]; }
+  tlc_wait(proj, xbc_out, dt_out, dA_out);
+  if (c < Cd) {
+    const float cur = to_f32(proj[(size_t)b * ld + xbc_off + c]);
+    float sum = bv;
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_TAPS; k++)
+      if (k < K - 1) sum = fmaf(prev[k], wk[k], sum);
+    float wl = 0.f;
+#pragma unroll
+    for (int k = 0; k <= CONV_MAX_TAPS; k++) if (k == K - 1) wl = wk[k];
+    sum = fmaf(cur, wl, sum);
     xbc_out[(size_t)b * Cd + c] = silu_f(sum);
 #pragma unroll
     for (int k = 0; k < CONV_MAX_TAPS; k++) {
@@ -183,9 +196,9 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
     }
   }
   if (c < Hs) {
-    const float dtv = softplus_f(to_f32(proj[(size_t)b * ld + dt_off + c]) + dt_bias[c]);
+    const float dtv = softplus_f(to_f32(proj[(size_t)b * ld + dt_off + c]) + db);
     dt_out[(size_t)b * Hs + c] = dtv;
-    dA_out[(size_t)b * Hs + c] = expf(dtv * A[c]);
+    dA_out[(size_t)b * Hs + c] = expf(dtv * Ac);
   }
 }
 
@@ -275,14 +288,30 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
   else if (mode == SCAN_CHUNK_STATE) S_final = S_chunk;
   else if (seg + 1 == seq_seg_start[b + 1]) S_final = S_slot;        // the sequence's last chunk
   const bool want_y = mode != SCAN_CHUNK_STATE;
+  // A lane owns the columns lane, lane + 32, ... of its rows, or (VEC: more than 64 columns, a multiple of 4)
+  // four consecutive columns 4 lane + 128 jj, which it loads and stores 16 bytes at a time.
+  const bool VEC = NPL % 4 == 0 && N % 4 == 0;
+  auto col = [&](int j) { return VEC ? 4 * lane + 128 * (j >> 2) + (j & 3) : lane + 32 * j; };
   float s[RP][NPL];
 #pragma unroll
-  for (int r = 0; r < RP; r++)
+  for (int r = 0; r < RP; r++) {
+    const int p = p_base + r;
+    if (VEC) {
 #pragma unroll
-    for (int j = 0; j < NPL; j++) {
-      const int p = p_base + r, n = lane + 32 * j;
-      s[r][j] = (S_init && p < P && n < N) ? S_init[(size_t)p * N + n] : 0.f;
+      for (int jj = 0; jj < NPL / 4; jj++) {
+        const int n = 4 * lane + 128 * jj;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (S_init && p < P && n < N) v = *reinterpret_cast<const float4*>(S_init + (size_t)p * N + n);
+        s[r][4 * jj] = v.x; s[r][4 * jj + 1] = v.y; s[r][4 * jj + 2] = v.z; s[r][4 * jj + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < NPL; j++) {
+        const int n = lane + 32 * j;
+        s[r][j] = (S_init && p < P && n < N) ? S_init[(size_t)p * N + n] : 0.f;
+      }
     }
+  }
   if (mode == SCAN_PLAIN) tlc_wait(xbc, dt, dA, y);
   // shared staging: per row  B[N] | C[N] | x[rows_per_block] | dt | dA
   const int per_tok = 2 * N + rows_per_block + 2;
@@ -315,7 +344,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
       float Bv[NPL], Cv[NPL];
 #pragma unroll
       for (int j = 0; j < NPL; j++) {
-        const int n = lane + 32 * j;
+        const int n = col(j);
         Bv[j] = n < N ? tk[n] : 0.f;
         Cv[j] = n < N ? tk[N + n] : 0.f;
       }
@@ -352,12 +381,24 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, con
   }
   if (S_final) {
 #pragma unroll
-    for (int r = 0; r < RP; r++)
+    for (int r = 0; r < RP; r++) {
+      const int p = p_base + r;
+      if (VEC) {
 #pragma unroll
-      for (int j = 0; j < NPL; j++) {
-        const int p = p_base + r, n = lane + 32 * j;
-        if (p < P && n < N) S_final[(size_t)p * N + n] = s[r][j];
+        for (int jj = 0; jj < NPL / 4; jj++) {
+          const int n = 4 * lane + 128 * jj;
+          if (p < P && n < N)
+            *reinterpret_cast<float4*>(S_final + (size_t)p * N + n) =
+                make_float4(s[r][4 * jj], s[r][4 * jj + 1], s[r][4 * jj + 2], s[r][4 * jj + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < NPL; j++) {
+          const int n = lane + 32 * j;
+          if (p < P && n < N) S_final[(size_t)p * N + n] = s[r][j];
+        }
       }
+    }
   }
 }
 

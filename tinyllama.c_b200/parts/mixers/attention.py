@@ -20,8 +20,6 @@ from ..linear import StackedLinear
 
 @register_mixer("attention")
 class AttentionMixer(Part):
-    single_token_launches = 1      # what a one-token step launches in mix() (three without the fused kernel)
-
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, prefix: str,
                  position: PartSpec, bias: bool = False, window: Optional[int] = None, in_scale: float = 1.0,
                  out_scale: float = 1.0, key_scale: float = 1.0, cache_key: str = "kv"):
@@ -39,6 +37,16 @@ class AttentionMixer(Part):
         self.o = StackedLinear(self.H * self.hd)
         self.o.add(prefix + "o_proj.weight", hidden, b("o_proj"), 1.0, out_scale)
         self.dtype = None
+
+    @property
+    def single_token_launches(self) -> int:
+        """Kernels that mix() launches in a one-token step: one where the fused kernel serves (a
+        bfloat16 cache, a head size it is built for, a position part with a rotation table), else
+        rotation + split keys + merge."""
+        fused = self.dtype == torch.bfloat16 and hasattr(self.position, "rotation_table") \
+            and ops.library().tlc_attention_decode_fused_ok(self.H, self.KV, self.hd) \
+            and not ops.DISABLE_FUSED_DECODE_ATTENTION
+        return 1 if fused else 3
 
     def weight_specs(self) -> List[WeightSpec]:
         return self.qkv.weight_specs() + self.o.weight_specs() + self.position.weight_specs()
