@@ -189,11 +189,14 @@ def test_first_tokens_of_a_sequence(engines, requests_of, name, dtype):
     check(np.concatenate(rows), want, dtype, f"{name} first tokens")
 
 
+@pytest.mark.parametrize("window", [None, 37])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_peaked_attention_over_a_far_key(tmp_path, dtype):
+def test_peaked_attention_over_a_far_key(tmp_path, dtype, window):
     """Queries and keys scaled so that scores are spread wide: a query's mass sits on a few
-    keys, often far ones, and a wrong page or position shows as a large error."""
-    cfg = dict(configs.TINY_A)
+    keys, often far ones, and a wrong page or position shows as a large error.  With a window
+    of 37 the mass often sits on a key near the window's edge: one key too many or too few shows
+    too, and so does a page behind the window that was given back too early."""
+    cfg = dict(configs.TINY_A, sliding_window=window)
     d = make_model_dir(tmp_path, cfg, seed=5, name="peaked")
     from safetensors.torch import load_file, save_file
     w = load_file(os.path.join(d, "model.safetensors"))
