@@ -6,7 +6,7 @@ plays both roles for this library:
 
     bin/probe decode  --batch 8 --layers 2 --prompt 512     three eager one-token steps (for ncu)
     bin/probe prefill --layers 2 --prompt 2048              one prompt, twice (for ncu)
-    bin/probe linear  --rows 2048 --n 6704 --k 2048 [--accumulate] [--tile 128|256]
+    bin/probe linear  --rows 2048 --n 6704 --k 2048 [--accumulate] [--swiglu] [--bf16-out] [--tile 64|128|256]
     bin/probe kernels --batch 8                             every decode-step kernel, warm, in a CUDA graph
 
 Models are random, with the layer sizes of bench.py (Falcon-H1-1.5B) and --layers layers.
@@ -80,8 +80,14 @@ def run_linear(args) -> None:
     lib.tlc_linear_tile_override(args.tile)
     M, N, K = args.rows, args.n, args.k
     a = torch.randn(M, K, device="cuda").bfloat16()
-    w = torch.randn(N, K, device="cuda").bfloat16()
-    out = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+    w = (torch.randn(N, K, device="cuda") * K ** -0.5).bfloat16()      # outputs of order one, as in a model
+    if args.swiglu:
+        act = torch.zeros(M, N // 2, dtype=torch.bfloat16, device="cuda")
+        timeit(f"linear+swiglu {M}x{N}x{K} tile={args.tile or 'auto'}", lambda: ops.linear_swiglu(a, w, act, None, None),
+               flops=2.0 * M * N * K, reps=20)
+        ops.check_errors()
+        return
+    out = torch.zeros(M, N, dtype=torch.bfloat16 if args.bf16_out else torch.float32, device="cuda")
     timeit(f"linear {M}x{N}x{K} tile={args.tile or 'auto'}", lambda: ops.linear(a, w, out, None, None, args.accumulate),
            flops=2.0 * M * N * K, reps=20)
     ops.check_errors()
@@ -171,7 +177,9 @@ def main(argv=None) -> int:
     ap.add_argument("--n", type=int, default=6704)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--accumulate", action="store_true")
-    ap.add_argument("--tile", type=int, default=0, choices=[0, 128, 256])
+    ap.add_argument("--tile", type=int, default=0, choices=[0, 64, 128, 256])
+    ap.add_argument("--swiglu", action="store_true", help="linear: gate|up rows interleaved by 8, SwiGLU in the epilogue")
+    ap.add_argument("--bf16-out", action="store_true", help="linear: bfloat16 output instead of float32")
     args = ap.parse_args(argv)
     if args.what in ("decode", "prefill"):
         run_steps(args)

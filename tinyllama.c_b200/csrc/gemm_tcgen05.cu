@@ -88,6 +88,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// SiLU for the bfloat16 epilogue: exp and reciprocal by the special-function unit (a few units in the last
+// place of 32 bits, far below the rounding of the stored bfloat16); the 32-bit path keeps silu_f.
+__device__ __forceinline__ float silu_quick(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 template <int BN, int STAGES>
 struct Smem {
   static constexpr int A_BYTES = BM * BK * 2;
@@ -204,12 +213,58 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int mrow0 = m0 + quarter * 32;
+      const bool scaled = SWIGLU && (colscale != nullptr || colbias != nullptr);
+      if (scaled) {
+        // the tile's column scales and biases once into the warp's staging area: every lane needs all of them
+        __syncwarp();
+        for (int j = lane; j < BN; j += 32) {
+          const int n = n0 + j;
+          st[j] = (colscale && n < N) ? colscale[n] : 1.0f;
+          st[BN + j] = (colbias && n < N) ? colbias[n] : 0.0f;
+        }
+        __syncwarp();
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c++) {
         const int nc0 = n0 + c * 32;
         if (nc0 >= N) break;
         uint32_t r[32];
         tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN + c * 32), r);
+        if (SWIGLU) {
+          // A lane holds 32 columns of its row: gates 0..7 | ups 8..15 | gates 16..23 | ups 24..31, i.e. 16
+          // features whose gate and up are both in its registers.  It writes 16 consecutive values.
+          const int m = mrow0 + lane;
+          const int oc0 = nc0 >> 1;
+          float o16[16];
+#pragma unroll
+          for (int f = 0; f < 16; f++) {
+            const int gcol = ((f >> 3) << 4) + (f & 7);
+            float vg = __uint_as_float(r[gcol]), vu = __uint_as_float(r[gcol + 8]);
+            if (scaled) {
+              const int jg = c * 32 + gcol;
+              vg = vg * st[jg] + st[BN + jg];
+              vu = vu * st[jg + 8] + st[BN + jg + 8];
+            }
+            o16[f] = silu_quick(vg) * vu;
+          }
+          if (m < M) {
+            TO* dst = out + (size_t)m * ldo + oc0;
+            if (nc0 + 32 <= N && (((uintptr_t)dst) & 15) == 0 && sizeof(TO) == 2) {
+              uint4 lo, hi;
+              lo.x = pack2(o16[0], o16[1]); lo.y = pack2(o16[2], o16[3]); lo.z = pack2(o16[4], o16[5]); lo.w = pack2(o16[6], o16[7]);
+              hi.x = pack2(o16[8], o16[9]); hi.y = pack2(o16[10], o16[11]); hi.z = pack2(o16[12], o16[13]); hi.w = pack2(o16[14], o16[15]);
+              reinterpret_cast<uint4*>(dst)[0] = lo;
+              reinterpret_cast<uint4*>(dst)[1] = hi;
+            } else {
+#pragma unroll
+              for (int f = 0; f < 16; f++) {
+                const int gcol = ((f >> 3) << 4) + (f & 7);
+                if (nc0 + gcol + 8 < N) dst[f] = from_f32<TO>(o16[f]);
+              }
+            }
+          }
+          continue;
+        }
         // registers (row = lane, 32 columns) -> shared (padded) -> rows of 32 consecutive columns
 #pragma unroll
         for (int j = 0; j < 32; j++) st[lane * 33 + j] = __uint_as_float(r[j]);
@@ -218,22 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const bool n_ok = n < N;
         const float cs = (colscale && n_ok) ? colscale[n] : 1.0f;
         const float cb = (colbias && n_ok) ? colbias[n] : 0.0f;
-        if (SWIGLU) {
-          // 16 features per 32 columns: lanes 0..15 take one row, lanes 16..31 the next; a lane reads
-          // its feature's gate and up columns from the staged tile and writes one value
-          const int f = lane & 15, gcol = ((f >> 3) << 4) + (f & 7);
-          const int ng = nc0 + gcol, nu = ng + 8;
-          const bool f_ok = nu < N;
-          const float csg = (colscale && f_ok) ? colscale[ng] : 1.0f, csu = (colscale && f_ok) ? colscale[nu] : 1.0f;
-          const float cbg = (colbias && f_ok) ? colbias[ng] : 0.0f, cbu = (colbias && f_ok) ? colbias[nu] : 0.0f;
-          const int oc = (nc0 >> 1) + f;
-#pragma unroll 4
-          for (int rr = lane >> 4; rr < 32; rr += 2) {
-            const int m = mrow0 + rr;
-            const float vg = st[rr * 33 + gcol] * csg + cbg, vu = st[rr * 33 + gcol + 8] * csu + cbu;
-            if (m < M && f_ok) out[(size_t)m * ldo + oc] = from_f32<TO>(silu_f(vg) * vu);
-          }
-        } else if (accumulate) {
+        if (accumulate) {
           // all 32 reads of the old values are in flight before the first add
           float old[32];
 #pragma unroll
