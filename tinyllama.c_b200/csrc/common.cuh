@@ -111,6 +111,11 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+// SiLU for bfloat16 runs: exp and reciprocal by the special-function unit, a few units in the last place
+// of 32 bits (far below the rounding of a bfloat16 or TF32 operand); the 32-bit path keeps silu_f, whose
+// full-precision division costs several times as much.
+__device__ __forceinline__ float silu_quick(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+template <bool QUICK> __device__ __forceinline__ float silu_of(float x) { return QUICK ? silu_quick(x) : silu_f(x); }
 // softplus with the reference's cut-over (cpu_op.c:354-356)
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
 

@@ -244,7 +244,8 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ 
   float ss = 0.f;
 #pragma unroll
   for (int i = 0; i < PT; i++) {
-    gate[i] = make_float4(silu_f(gate[i].x), silu_f(gate[i].y), silu_f(gate[i].z), silu_f(gate[i].w));
+    constexpr bool QUICK = sizeof(TO) == 2;              // a bfloat16 output means a bfloat16 run
+    gate[i] = make_float4(silu_of<QUICK>(gate[i].x), silu_of<QUICK>(gate[i].y), silu_of<QUICK>(gate[i].z), silu_of<QUICK>(gate[i].w));
     if (!norm_before_gate) { v[i].x *= gate[i].x; v[i].y *= gate[i].y; v[i].z *= gate[i].z; v[i].w *= gate[i].w; }
     ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
   }

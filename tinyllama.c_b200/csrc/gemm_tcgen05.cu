@@ -88,10 +88,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// SiLU for the bfloat16 epilogue: exp and reciprocal by the special-function unit (a few units in the last
-// place of 32 bits, far below the rounding of the stored bfloat16); the 32-bit path keeps silu_f.
-__device__ __forceinline__ float silu_quick(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
-
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);

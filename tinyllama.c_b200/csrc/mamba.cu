@@ -18,7 +18,7 @@
 // takes a tap from the sequence's stored window only where the row is among the first K-1 of a
 // sequence that continues from a slot.  Also writes dt and dA of the rows (first blocks along y).
 #define CONV_ROWS 8
-template <typename T, int K>
+template <typename T, int K, bool QUICK>
 __global__ void __launch_bounds__(256)
 mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_off,
                   const float* __restrict__ w, const float* __restrict__ bias,
@@ -70,7 +70,7 @@ mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_o
         else x = s_has[r] ? conv_state[((size_t)s_slot[r] * (K - 1) + (K - 1 + j)) * Cd + c] : 0.f;
         sum = fmaf(x, wk[k], sum);
       }
-      xbc_out[(size_t)t * Cd + c] = silu_f(sum + bv);
+      xbc_out[(size_t)t * Cd + c] = silu_of<QUICK>(sum + bv);
     }
   }
   if (c < Hs) {
@@ -202,14 +202,15 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
   }
 }
 
-#define TLC_CONV_ROWS(KT)                                                                                              \
-  tlc_launch(mamba_conv_rows_kernel<TT, KT>, dim3(grid8), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, w, \
-             bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out, dA_out, T, Cd, Hs)
+#define TLC_CONV_ROWS_Q(KT, QK)                                                                                           \
+  tlc_launch(mamba_conv_rows_kernel<TT, KT, QK>, dim3(grid8), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, \
+             w, bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out, dA_out, T, Cd, Hs)
+#define TLC_CONV_ROWS(KT) do { if (quick) TLC_CONV_ROWS_Q(KT, true); else TLC_CONV_ROWS_Q(KT, false); } while (0)
 extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, int dt_off, const float* w,
                               const float* bias, const float* dt_bias, const float* A, float* conv_state,
                               const int* cu_seqlens, const int* row_seq, const int* slots, const int* start_pos,
                               float* xbc_out, float* dt_out, float* dA_out, int T, int B, int Cd, int K, int Hs,
-                              int single_rows, cudaStream_t stream) {
+                              int single_rows, int quick, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(K >= 1 && K - 1 <= CONV_MAX_TAPS, "mamba_conv: %d taps exceed the kernel's limit of %d", K, CONV_MAX_TAPS + 1);
   TLC_REQUIRE(Hs <= Cd, "mamba_conv: more heads (%d) than conv channels (%d)", Hs, Cd);

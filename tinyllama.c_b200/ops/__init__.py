@@ -38,7 +38,7 @@ _SIGNATURES = {
     "tlc_attention_decode_fused_ok": [_i, _i, _i],
     "tlc_attention_prefill": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
     "tlc_mamba_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
-                       _i, _i, _i, _vp],
+                       _i, _i, _i, _i, _vp],
     "tlc_ssm_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "tlc_ssm_scan_chunked": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
     "tlc_ssm_scan_ssd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
@@ -381,11 +381,12 @@ DISABLE_SSD = bool(int(os.environ.get("TLC_DISABLE_SSD", "0")))
 def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, bias: Optional[torch.Tensor],
                dt_bias: torch.Tensor, A: torch.Tensor, conv_state: torch.Tensor, cu_seqlens: torch.Tensor,
                row_seq: torch.Tensor, slots: torch.Tensor, start_pos: torch.Tensor, xbc_out: torch.Tensor,
-               dt_out: torch.Tensor, dA_out: torch.Tensor, single_rows: bool = False) -> None:
+               dt_out: torch.Tensor, dA_out: torch.Tensor, single_rows: bool = False, quick: bool = False) -> None:
     """Causal depthwise convolution + SiLU of the xBC columns of proj, continuing each
     sequence's window (conv_state [n_slots, K-1, Cd], updated in place); also
     dt = softplus(dt + dt_bias) and dA = exp(dt * A) per row and head.  single_rows says
-    that every sequence brings exactly one row (row b belongs to sequence b)."""
+    that every sequence brings exactly one row (row b belongs to sequence b); quick allows the
+    SiLU of prompts its fast exponential and reciprocal (bfloat16 runs)."""
     _gpu(proj, w, bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out, dA_out)
     T = proj.shape[0]
     Cd, K = w.shape
@@ -405,7 +406,7 @@ def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, b
     _call("tlc_mamba_conv", proj.data_ptr(), dtype_code(proj.dtype), _rows(proj, "proj"), xbc_off, dt_off,
           w.data_ptr(), _p(bias), dt_bias.data_ptr(), A.data_ptr(), conv_state.data_ptr(), cu_seqlens.data_ptr(),
           row_seq.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), xbc_out.data_ptr(), dt_out.data_ptr(),
-          dA_out.data_ptr(), T, B, Cd, K, Hs, int(bool(single_rows)), _stream())
+          dA_out.data_ptr(), T, B, Cd, K, Hs, int(bool(single_rows)), int(bool(quick)), _stream())
 
 
 def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch.Tensor, state: torch.Tensor,

@@ -100,7 +100,7 @@ class Mamba2Mixer(Part):
         xbc, dt, dA = new((T, self.Cd), f32), new((T, self.Hs), f32), new((T, self.Hs), f32)
         ops.mamba_conv(proj, self.Di, self.Di + self.Cd, self.conv_w, self.conv_b, self.dt_bias, self.A, conv_state,
                        step.cu_seqlens, step.row_seq, step.slots, step.start_pos, xbc, dt, dA,
-                       step.max_new == 1)
+                       step.max_new == 1, self.dtype == torch.bfloat16)
         y = new((T, self.Di), f32)
         ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs, self.P,
                      self.N, self.G, step.chunks, self.A if self.dtype == torch.bfloat16 else None)
