@@ -148,69 +148,56 @@ ssd_cb_kernel(const float* __restrict__ xbc, const int* __restrict__ seg_start, 
   }
 }
 
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
+  const int bytes = pred ? 16 : 0;                 // 0: the 16 bytes are filled with zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N_> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
+
 // ---- chunk states: S_c[p, n] = sum_j w_j x[j, p] B[j, n],  w_j = exp(cum_last - cum_j) dt_j ----------
-// grid (seg, Hs, N / 128); 8 warps; output P x 128 with K = 128 rows of the chunk.
+// grid (seg, Hs, N / 128); 8 warps; output P x 128 with K = 128 rows of the chunk.  x and B arrive as they
+// are, by cp.async, all at once; the weights w_j are computed meanwhile and applied to the x fragments in
+// registers, where both operands are rounded to TF32.
 template <int P>
 __global__ void __launch_bounds__(256)
 ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ cum,
                        const int* __restrict__ seg_start, float* __restrict__ chunk_state, int Hs, int N, int G, int Cd) {
   tlc_pdl(xbc, dt, cum, chunk_state);
   constexpr int LDX = P + 8, LDB = 128 + 8;
-  extern __shared__ uint32_t ssd_sm[];
-  uint32_t* Xs = ssd_sm;                 // [j][p]   x * w
-  uint32_t* Bs = Xs + Q * LDX;           // [j][n]   128 columns of B
+  extern __shared__ __align__(16) uint32_t ssd_sm[];
+  float* Xs = reinterpret_cast<float*>(ssd_sm);     // [j][p]   raw x
+  float* Bs = Xs + Q * LDX;                         // [j][n]   128 columns of B, raw
+  float* ws = Bs + Q * LDB;                         // [j]      w_j
   const int seg = blockIdx.x, h = blockIdx.y, nb = blockIdx.z * 128;
   const int g = h / (Hs / G);
   const int Di = Hs * P;
   const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
-  const float cum_last = cum[(size_t)(t0 + L - 1) * Hs + h];
-  // x * w: Q * P / 4 float4, 8 in flight per thread
-#pragma unroll 1
-  for (int it0 = 0; it0 < Q * (P / 4) / 256; it0 += 8) {
-    float4 v[8];
-    float w[8], dtv[8];
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-      const int idx = threadIdx.x + (it0 + u) * 256;
-      const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
-      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      w[u] = dtv[u] = 0.f;
-      if (r < L) {
-        v[u] = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + (size_t)h * P + c4);
-        w[u] = cum[(size_t)(t0 + r) * Hs + h];
-        dtv[u] = dt[(size_t)(t0 + r) * Hs + h];
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-      const int idx = threadIdx.x + (it0 + u) * 256;
-      const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
-      const float ww = r < L ? expf(cum_last - w[u]) * dtv[u] : 0.f;
-      uint32_t* d = Xs + r * LDX + c4;
-      d[0] = tf32(v[u].x * ww); d[1] = tf32(v[u].y * ww); d[2] = tf32(v[u].z * ww); d[3] = tf32(v[u].w * ww);
-    }
+  const int tid = threadIdx.x;
+  const uint32_t xs0 = (uint32_t)__cvta_generic_to_shared(Xs), bs0 = (uint32_t)__cvta_generic_to_shared(Bs);
+  for (int idx = tid; idx < Q * (P / 4); idx += 256) {
+    const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
+    const bool in = r < L;
+    cp_async16(xs0 + (uint32_t)(r * LDX + c4) * 4, xbc + (size_t)(t0 + (in ? r : 0)) * Cd + (size_t)h * P + c4, in);
   }
-  // 128 columns of B: Q * 32 float4
-#pragma unroll 1
-  for (int it0 = 0; it0 < Q * 32 / 256; it0 += 8) {
-    float4 v[8];
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-      const int idx = threadIdx.x + (it0 + u) * 256;
-      const int r = idx >> 5, c4 = (idx & 31) * 4;
-      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (r < L && nb + c4 < N) v[u] = *reinterpret_cast<const float4*>(xbc + (size_t)(t0 + r) * Cd + Di + (size_t)g * N + nb + c4);
-    }
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-      const int idx = threadIdx.x + (it0 + u) * 256;
-      const int r = idx >> 5, c4 = (idx & 31) * 4;
-      uint32_t* d = Bs + r * LDB + c4;
-      d[0] = tf32(v[u].x); d[1] = tf32(v[u].y); d[2] = tf32(v[u].z); d[3] = tf32(v[u].w);
-    }
+  for (int idx = tid; idx < Q * 32; idx += 256) {
+    const int r = idx >> 5, c4 = (idx & 31) * 4;
+    const bool in = r < L && nb + c4 < N;
+    cp_async16(bs0 + (uint32_t)(r * LDB + c4) * 4,
+               xbc + (size_t)(t0 + (r < L ? r : 0)) * Cd + Di + (size_t)g * N + (in ? nb + c4 : 0), in);
   }
+  cp_async_commit();
+  if (tid < Q) {
+    float w = 0.f;
+    if (tid < L) {
+      const float cum_last = cum[(size_t)(t0 + L - 1) * Hs + h];
+      w = expf(cum_last - cum[(size_t)(t0 + tid) * Hs + h]) * dt[(size_t)(t0 + tid) * Hs + h];
+    }
+    ws[tid] = w;
+  }
+  cp_async_wait<0>();
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
   // warp w: columns n in [16w, 16w+16) (2 tiles) x all P rows (P/16 tiles)
   float acc[P / 16][2][4];
 #pragma unroll
@@ -224,14 +211,15 @@ ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ 
     uint32_t b[2][2];
 #pragma unroll
     for (int j = 0; j < 2; j++) {
-      const uint32_t* br = Bs + (kk * 8 + tq) * LDB + warp * 16 + j * 8 + gq;
-      b[j][0] = br[0];
-      b[j][1] = br[4 * LDB];
+      const float* br = Bs + (kk * 8 + tq) * LDB + warp * 16 + j * 8 + gq;
+      b[j][0] = tf32(br[0]);
+      b[j][1] = tf32(br[4 * LDB]);
     }
+    const float w0 = ws[kk * 8 + tq], w1 = ws[kk * 8 + tq + 4];
 #pragma unroll
     for (int m = 0; m < P / 16; m++) {
-      const uint32_t* ar = Xs + (kk * 8 + tq) * LDX + m * 16 + gq;           // A(row p, col j) = Xs[j][p]
-      const uint32_t a0 = ar[0], a1 = ar[8], a2 = ar[4 * LDX], a3 = ar[4 * LDX + 8];
+      const float* ar = Xs + (kk * 8 + tq) * LDX + m * 16 + gq;              // A(row p, col j) = x[j][p] w_j
+      const uint32_t a0 = tf32(ar[0] * w0), a1 = tf32(ar[8] * w0), a2 = tf32(ar[4 * LDX] * w1), a3 = tf32(ar[4 * LDX + 8] * w1);
 #pragma unroll
       for (int j = 0; j < 2; j++) mma_tf32(acc[m][j], a0, a1, a2, a3, b[j][0], b[j][1]);
     }
@@ -258,13 +246,6 @@ ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ 
 // M is built in shared memory by the block (it needs the exponentials); X, C and S_in arrive as they
 // are, by cp.async, and are rounded to TF32 in registers: X and the first slab of 32 state columns
 // are on their way while M is built, and each further slab while the one before it is multiplied.
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
-  const int bytes = pred ? 16 : 0;                 // 0: the 16 bytes are filled with zeros, nothing is read
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N_> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
-
 constexpr int OUT_R = 64;                  // rows of the chunk per block
 constexpr int OUT_SL = 32;                 // state columns per slab
 constexpr int OUT_LDM = Q + 4, OUT_LDS = OUT_SL + 4;
@@ -407,7 +388,7 @@ ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt
 
 inline size_t pad64(size_t n) { return (n + 63) / 64 * 64; }
 
-template <int P> size_t state_smem() { return (size_t)(Q * (P + 8) + Q * 136) * 4; }
+template <int P> size_t state_smem() { return (size_t)(Q * (P + 8) + Q * 136 + Q) * 4; }
 template <int P> size_t out_smem() {
   return (size_t)(OUT_R * OUT_LDM + Q * (P + 8) + 2 * OUT_R * OUT_LDS + 2 * P * OUT_LDS + 2 * Q) * 4;
 }
