@@ -81,6 +81,19 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
       const int pi = k0 / TLC_PAGE + tid;
       pages[tid] = (pi * TLC_PAGE < n_keys) ? table[pi] : 0;
     }
+    // this thread's value rows, too, are on their way before the wait (all but the row's own position)
+    const int nk = min(KEYS, n_keys - k0);
+    const int dl = tid % CH, rg = tid / CH;
+    uint4 vq[RPT];
+#pragma unroll
+    for (int u = 0; u < RPT; u++) {
+      const int j = rg + u * ROWS;
+      const int kj = k0 + j;
+      const bool use = j < nk && kj >= start && kj != pos;     // outside the window a page may have been given back
+      vq[u] = use ? __ldg(reinterpret_cast<const uint4*>(
+                              v_pages + (((size_t)table[kj / TLC_PAGE] * KV + g) * TLC_PAGE + kj % TLC_PAGE) * HD) + dl)
+                  : make_uint4(0, 0, 0, 0);
+    }
     tlc_wait(qkv, kr, k_pages, v_pages, part_o, ml);
     // rotation: the thread of dim d turns that dim of every query head of the group and of the key;
     // all of its loads are issued before the first use
@@ -207,27 +220,23 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
       }
     }
     __syncthreads();
-    const int nk = min(KEYS, n_keys - k0);
-    const int dl = tid % CH, rg = tid / CH;
     float acc[GT][8];
 #pragma unroll
     for (int hg = 0; hg < GT; hg++)
 #pragma unroll
       for (int i = 0; i < 8; i++) acc[hg][i] = 0.f;
     {
-      // this thread's value rows: all loads are issued before the first use
-      uint4 vq[RPT];
+      // the value row at the row's own position: written above by this block, or (a layer that only reads) by
+      // an earlier kernel
 #pragma unroll
       for (int u = 0; u < RPT; u++) {
         const int j = rg + u * ROWS;
         const int kj = k0 + j;
-        const bool use = j < nk && kj >= start;          // outside the window a page may have been given back
-        if (use && has_new && kj == pos)
-          vq[u] = reinterpret_cast<const uint4*>(vnew)[dl];          // written above by this block
-        else
-          vq[u] = use ? __ldg(reinterpret_cast<const uint4*>(
-                                  v_pages + (((size_t)pages[j / TLC_PAGE] * KV + g) * TLC_PAGE + kj % TLC_PAGE) * HD) + dl)
-                      : make_uint4(0, 0, 0, 0);
+        if (j < nk && kj >= start && kj == pos) {
+          if (has_new) vq[u] = reinterpret_cast<const uint4*>(vnew)[dl];
+          else vq[u] = *(reinterpret_cast<const uint4*>(
+                             v_pages + (((size_t)pages[j / TLC_PAGE] * KV + g) * TLC_PAGE + kj % TLC_PAGE) * HD) + dl);
+        }
       }
 #pragma unroll
       for (int u = 0; u < RPT; u++) {
