@@ -206,6 +206,23 @@ def test_attention_of_prompts_on_tensor_cores(H, KV, hd, window):
     cmp("attention", args, [7], tol_of=TOL[torch.bfloat16] * 2.5)
 
 
+@pytest.mark.parametrize("H,KV,hd,window", [(4, 2, 128, 0), (2, 1, 64, 0), (4, 4, 64, 700)])
+def test_attention_of_long_prompts_in_pieces(H, KV, hd, window):
+    """Key ranges of more than 8 pages are cut into pieces that run side by side and are merged: a prompt of
+    1,500 rows, one that continues at position 900, and a short one whose rows are written whole."""
+    g = gen(23)
+    starts, lens = [0, 900, 40], [1500, 300, 30]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    slots, table, k_pages, v_pages = _paged_setup(g, 3, [s + n for s, n in zip(starts, lens)], KV, hd, torch.bfloat16,
+                                                  n_slots=4)
+    T = sum(lens)
+    q = rnd(g, T, H * hd, dtype=torch.bfloat16)
+    k_pages[int(table[int(slots[0]), 1]), :, 9, :] *= 4.0        # a far key (position 73) stands out for late rows
+    args = [q, k_pages, v_pages, table, pos, row_seq, slots, torch.empty(T, H * hd, dtype=torch.bfloat16), H, KV, hd,
+            1.0 / math.sqrt(hd), window, 0, cu, start_pos, 1500]
+    cmp("attention", args, [7], tol_of=TOL[torch.bfloat16] * 2.5)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,KV,hd,window", [(6, 3, 24, 0), (4, 1, 48, 0), (8, 2, 128, 0), (6, 2, 16, 37), (8, 1, 80, 170)])
 def test_attention_of_single_token_steps(dtype, H, KV, hd, window):

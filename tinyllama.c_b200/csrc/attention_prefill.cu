@@ -51,8 +51,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                          const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int H, int KV,
-                         float scale_log2, int window) {
-  tlc_pdl(q, k_pages, v_pages, out);
+                         float scale_log2, int window, int chunk_tiles, int n_chunks_max, float* __restrict__ part_o,
+                         float* __restrict__ part_ml) {
+  tlc_pdl(q, k_pages, v_pages, out, part_o, part_ml);
   constexpr int CH = HD / 8;                  // 16-byte chunks per row
   constexpr int TILE_BYTES = FA_BN * HD * 2;
   extern __shared__ __align__(128) uint8_t fa_smem[];
@@ -83,8 +84,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   const int p0 = start_pos[b] + i0;                       // position of the block's first row
   const int q_max = p0 + rows - 1;
   const int* table = block_table + (size_t)slots[b] * max_pages;
-  const int tile_hi = q_max / FA_BN;
-  const int tile_lo = window > 0 ? max(0, p0 + 1 - window) / FA_BN : 0;
+  const int tile_hi_all = q_max / FA_BN;
+  const int tile_lo_all = window > 0 ? max(0, p0 + 1 - window) / FA_BN : 0;
+  // Long rows are cut: block z of the row tile takes key tiles [lo + z * chunk, lo + (z + 1) * chunk), so that
+  // the last rows of a long prompt do not set the kernel's length; a second kernel merges the pieces.
+  const int n_chunks = (tile_hi_all - tile_lo_all) / chunk_tiles + 1;
+  const int tile_lo = tile_lo_all + (int)blockIdx.z * chunk_tiles;
+  if (tile_lo > tile_hi_all) return;
+  const int tile_hi = min(tile_hi_all, tile_lo + chunk_tiles - 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t q_u = (uint32_t)__cvta_generic_to_shared(q_s), k_u = (uint32_t)__cvta_generic_to_shared(k_s),
@@ -214,6 +221,25 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     __syncthreads();          // everyone is done with this buffer before it is filled again
   }
 
+  if (n_chunks > 1) {
+    // a piece of the row: the sums as they are, with the maximum and the denominator they refer to
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      const int lr = warp * 16 + gq + 8 * r;
+      if (lr < rows) {
+        const size_t at = (((size_t)(t0 + i0 + lr) * H + h) * n_chunks_max + blockIdx.z);
+        float* orow = part_o + at * HD;
+#pragma unroll
+        for (int j = 0; j < HD / 8; j++)
+          *reinterpret_cast<float2*>(orow + j * 8 + 2 * tq) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+        if (tq == 0) {
+          part_ml[at * 2] = m_run[r];
+          part_ml[at * 2 + 1] = l_run[r];
+        }
+      }
+    }
+    return;
+  }
   // normalise and store
 #pragma unroll
   for (int r = 0; r < 2; r++) {
@@ -225,6 +251,60 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       for (int j = 0; j < HD / 8; j++)
         *reinterpret_cast<uint32_t*>(orow + j * 8 + 2 * tq) = pack_bf16(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
     }
+  }
+}
+
+// Rows that were cut into pieces: out = sum_z o_z 2^((m_z - m) scale) / sum_z l_z 2^((m_z - m) scale).
+// grid (T, ceil(H / 4)); a warp per (row, head), a lane per 4 head dims (and their next 128, 256, ...); at most
+// FA_MAX_CHUNKS pieces, all of whose values are in flight together.
+constexpr int FA_MAX_CHUNKS = 16;
+__global__ void __launch_bounds__(128)
+attention_prefill_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                               const int* __restrict__ cu_seqlens, const int* __restrict__ row_seq,
+                               const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int H, int hd,
+                               float scale_log2, int window, int chunk_tiles, int n_chunks_max) {
+  tlc_pdl(part_o, part_ml, out);
+  const int t = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (h >= H) return;
+  const int b = row_seq[t];
+  const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
+  const int i0 = ((t - t0) / FA_BM) * FA_BM;
+  const int rows = min(FA_BM, n_new - i0);
+  const int p0 = start_pos[b] + i0;
+  const int tile_hi = (p0 + rows - 1) / FA_BN;
+  const int tile_lo = window > 0 ? max(0, p0 + 1 - window) / FA_BN : 0;
+  const int n_chunks = (tile_hi - tile_lo) / chunk_tiles + 1;
+  if (n_chunks <= 1) return;                         // the row was written whole
+  const size_t at = ((size_t)t * H + h) * n_chunks_max;
+  float2 ml[FA_MAX_CHUNKS];
+#pragma unroll
+  for (int z = 0; z < FA_MAX_CHUNKS; z++)
+    ml[z] = z < n_chunks ? *reinterpret_cast<const float2*>(part_ml + (at + z) * 2) : make_float2(-INFINITY, 0.f);
+  float m = -INFINITY;
+#pragma unroll
+  for (int z = 0; z < FA_MAX_CHUNKS; z++) if (ml[z].y > 0.f) m = fmaxf(m, ml[z].x);
+  float w[FA_MAX_CHUNKS], l = 0.f;
+#pragma unroll
+  for (int z = 0; z < FA_MAX_CHUNKS; z++) {
+    w[z] = ml[z].y > 0.f ? exp2f((ml[z].x - m) * scale_log2) : 0.f;
+    l += ml[z].y * w[z];
+  }
+  const float inv = 1.0f / l;
+  for (int d = lane * 4; d < hd; d += 128) {
+    float4 v[FA_MAX_CHUNKS];
+#pragma unroll
+    for (int z = 0; z < FA_MAX_CHUNKS; z++)
+      v[z] = (z < n_chunks && w[z] != 0.f) ? *reinterpret_cast<const float4*>(part_o + (at + z) * hd + d) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int z = 0; z < FA_MAX_CHUNKS; z++) {
+      acc.x = fmaf(v[z].x, w[z], acc.x); acc.y = fmaf(v[z].y, w[z], acc.y);
+      acc.z = fmaf(v[z].z, w[z], acc.z); acc.w = fmaf(v[z].w, w[z], acc.w);
+    }
+    uint2 o2;
+    o2.x = pack_bf16(acc.x * inv, acc.y * inv);
+    o2.y = pack_bf16(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + ((size_t)t * H + h) * hd + d) = o2;
   }
 }
 
@@ -244,24 +324,49 @@ extern "C" int tlc_attention_prefill_init() {
 
 extern "C" int tlc_attention_prefill_ok(int dtype, int hd) { return dtype == TLC_BF16 && (hd == 64 || hd == 128); }
 
-// n_tiles_bound: an upper bound of sum_b ceil(n_new_b / 64) (e.g. T/64 + n_seqs)
+// How many pieces the key range of a row tile is cut into, for `max_tiles` key tiles at most: none while the
+// grid fills the GPU anyway, else pieces of 8 tiles.
+extern "C" int tlc_attention_prefill_chunks(int n_tiles_bound, int H, int max_tiles, int* chunk_tiles) {
+  const int piece = 8;
+  *chunk_tiles = max_tiles > 0 ? max_tiles : 1;
+  if (max_tiles <= piece || (long long)n_tiles_bound * H >= 1184) return 1;     // 1184 = 148 SMs x 2 blocks x 4 rounds
+  // at most FA_MAX_CHUNKS pieces: longer pieces for very long prompts
+  int per = piece;
+  while ((max_tiles + per - 1) / per > FA_MAX_CHUNKS) per *= 2;
+  *chunk_tiles = per;
+  return (max_tiles + per - 1) / per;
+}
+
+// n_tiles_bound: an upper bound of sum_b ceil(n_new_b / 64) (e.g. T/64 + n_seqs); max_tiles: key tiles of the
+// longest sequence after this step; part_o [T, H, n_chunks, hd] and part_ml [T, H, n_chunks, 2] floats and
+// row_seq are needed when tlc_attention_prefill_chunks(...) says more than one piece.
 extern "C" int tlc_attention_prefill(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                                      int max_pages, const int* cu_seqlens, const int* slots, const int* start_pos,
                                      void* out, int n_seqs, int n_tiles_bound, int H, int KV, int hd, float scale,
-                                     int window, cudaStream_t stream) {
+                                     int window, int max_tiles, const int* row_seq, float* part_o, float* part_ml, int T,
+                                     cudaStream_t stream) {
   if (n_seqs == 0 || n_tiles_bound == 0) return 0;
   TLC_REQUIRE(KV > 0 && H % KV == 0, "attention: %d heads are not a multiple of %d key/value heads", H, KV);
   TLC_REQUIRE(H <= 65535, "attention(prefill): too many heads (%d)", H);
-  dim3 grid(n_tiles_bound, H);
+  int chunk_tiles = 1;
+  int n_chunks = tlc_attention_prefill_chunks(n_tiles_bound, H, max_tiles, &chunk_tiles);
+  if (part_o == nullptr || part_ml == nullptr || row_seq == nullptr) { n_chunks = 1; chunk_tiles = 1 << 30; }
+  if (n_chunks == 1) chunk_tiles = 1 << 30;
+  TLC_REQUIRE(n_chunks <= 65535, "attention(prefill): too many pieces (%d)", n_chunks);
+  dim3 grid(n_tiles_bound, H, n_chunks);
   const float scale_log2 = scale * 1.4426950408889634f;
   const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
   const int smem = (FA_BM + 4 * FA_BN) * hd * 2;
   if (hd == 64)
-    tlc_launch(attention_prefill_kernel<64>, dim3(grid), dim3(128), smem, stream, qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window);
+    tlc_launch(attention_prefill_kernel<64>, dim3(grid), dim3(128), smem, stream, qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window, chunk_tiles, n_chunks, part_o, part_ml);
   else if (hd == 128)
-    tlc_launch(attention_prefill_kernel<128>, dim3(grid), dim3(128), smem, stream, qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window);
+    tlc_launch(attention_prefill_kernel<128>, dim3(grid), dim3(128), smem, stream, qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window, chunk_tiles, n_chunks, part_o, part_ml);
   else
     return tlc_fail(-1, "attention(prefill): head size %d is not built (64 and 128 are)", hd);
+  if (n_chunks > 1)
+    tlc_launch(attention_prefill_merge_kernel, dim3(T, (H + 3) / 4), dim3(128), 0, stream, (const float*)part_o,
+               (const float*)part_ml, cu_seqlens, row_seq, start_pos, (__nv_bfloat16*)out, H, hd, scale_log2, window,
+               chunk_tiles, n_chunks);
   TLC_CHECK_LAUNCH("attention(prefill)");
   return 0;
 }

@@ -36,7 +36,9 @@ _SIGNATURES = {
     "tlc_attention_decode_fused": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                    _i, _i, _i, _i, _f, _i, _i, _vp],
     "tlc_attention_decode_fused_ok": [_i, _i, _i],
-    "tlc_attention_prefill": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "tlc_attention_prefill": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp,
+                              _i, _vp],
+    "tlc_attention_prefill_chunks": [_i, _i, _i, _vp],
     "tlc_mamba_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
                        _i, _i, _i, _i, _vp],
     "tlc_ssm_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
@@ -297,12 +299,14 @@ def rope_kv_store(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: 
 def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
               positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, H: int, KV: int,
               hd: int, scale: float, window: int = 0, decode_max_keys: int = 0,
-              cu_seqlens: Optional[torch.Tensor] = None, start_pos: Optional[torch.Tensor] = None) -> None:
+              cu_seqlens: Optional[torch.Tensor] = None, start_pos: Optional[torch.Tensor] = None,
+              max_keys: int = 0) -> None:
     """Causal grouped-query attention of every row over its sequence's pages (keys 0..position,
     or the last `window` of them).  decode_max_keys > 0 says that the rows are single-token
     steps of sequences no longer than that: keys are then split across blocks.  With
     cu_seqlens and start_pos (rows of a sequence are consecutive positions from start_pos) the
-    tiled tensor-core kernel serves bfloat16 heads of 64 or 128."""
+    tiled tensor-core kernel serves bfloat16 heads of 64 or 128; with max_keys (the longest sequence
+    after this step) it cuts the key range of long rows into pieces that run side by side."""
     _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out)
     T = q.shape[0]
     if not q.is_contiguous() or not out.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.shape != q.shape \
@@ -320,9 +324,18 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     if decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
             and hd in (64, 128) and not DISABLE_TILED_ATTENTION:
         B = slots.numel()
+        n_tiles = T // 64 + B
+        chunk = ctypes.c_int(0)
+        n_chunks = library().tlc_attention_prefill_chunks(n_tiles, H, (int(max_keys) + 63) // 64, ctypes.byref(chunk)) \
+            if max_keys > 0 else 1
+        part_o = part_ml = None
+        if n_chunks > 1:
+            part_o = torch.empty((T, H, n_chunks, hd), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((T, H, n_chunks, 2), dtype=torch.float32, device=q.device)
         _call("tlc_attention_prefill", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), out.data_ptr(), B,
-              T // 64 + B, H, KV, hd, float(scale), int(window or 0), _stream())
+              n_tiles, H, KV, hd, float(scale), int(window or 0), (int(max_keys) + 63) // 64 if n_chunks > 1 else 0,
+              row_seq.data_ptr(), _p(part_o), _p(part_ml), T, _stream())
         return
     _call("tlc_attention", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(),

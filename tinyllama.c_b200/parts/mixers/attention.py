@@ -93,7 +93,7 @@ class AttentionMixer(Part):
         att = torch.empty_like(q)
         ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
                       self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
-                      step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos)
+                      step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos, step.max_context)
         return att
 
     def output(self, att: torch.Tensor, residual: torch.Tensor) -> None:
