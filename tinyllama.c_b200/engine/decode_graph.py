@@ -21,7 +21,6 @@ from ..parts.base import StepInfo
 from ..sampling.params import SamplingParams
 
 
-USE_PDL = bool(int(os.environ.get("TLC_PDL", "1")))
 
 
 class DecodeGraph:
@@ -73,14 +72,9 @@ class DecodeGraph:
         stream = torch.cuda.Stream(device=self.model.device)
         stream.wait_stream(torch.cuda.current_stream())
         self.graph = torch.cuda.CUDAGraph()
-        lib = ops.library()
-        lib.tlc_set_pdl(1 if USE_PDL else 0)      # kernels of the graph overlap their launch with their predecessor's tail
-        try:
-            with torch.cuda.stream(stream):
-                with torch.cuda.graph(self.graph, stream=stream):
-                    self._body()
-        finally:
-            lib.tlc_set_pdl(0)
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(self.graph, stream=stream):
+                self._body()
         torch.cuda.current_stream().wait_stream(stream)
         self.launches = ops.launch_count() - before
 

@@ -71,9 +71,13 @@ def library() -> ctypes.CDLL:
             for init in (lib.tlc_linear_init, lib.tlc_attention_prefill_init, lib.tlc_ssd_init):
                 if init() != 0:
                     raise KernelError(f"kernel library set-up: {lib.tlc_last_error().decode()}")
+        # Programmatic dependent launch for every kernel of the library, captured or not: a kernel's blocks are
+        # scheduled (and fetch what does not depend on its predecessor) while the predecessor's last blocks finish.
+        lib.tlc_set_pdl(1 if USE_PDL else 0)
     return _lib
 
 
+USE_PDL = bool(int(os.environ.get("TLC_PDL", "1")))
 _launches = 0
 
 
