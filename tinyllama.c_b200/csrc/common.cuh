@@ -33,9 +33,9 @@ int tlc_fail(int code, const char* fmt, ...);
 // Every kernel begins with tlc_pdl(): it lets the next kernel of the stream be scheduled early
 // and then waits until the previous kernel has finished and its writes are visible.  Both
 // instructions do nothing unless the launch carries the programmatic-serialization attribute,
-// which tlc_launch() adds when tlc_set_pdl(1) is in effect (the decode graph turns it on while
-// it is captured: a decode step is hundreds of short kernels, and this hides the gap between
-// one kernel's last block and the next kernel's first).
+// which tlc_launch() adds while tlc_set_pdl(1) is in effect (the library turns it on when it is
+// loaded): a step is hundreds of short kernels, and this hides the gap between one kernel's last
+// block and the next kernel's first.
 extern int g_tlc_pdl;
 extern "C" void tlc_set_pdl(int on);
 
