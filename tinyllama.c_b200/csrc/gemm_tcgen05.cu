@@ -114,7 +114,10 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                     const float* __restrict__ colbias, int accumulate, int M, int N, int K, ErrWords* err) {
-  tlc_pdl(out);
+  // The set-up and the first weight tiles do not depend on the previous kernel of the stream: they go ahead of
+  // the wait on it.  The loader waits before its first activation tile, the epilogue warps before they touch
+  // `out`; the issuer reads shared memory only.
+  asm volatile("griddepcontrol.launch_dependents;");
   using S = Smem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -151,6 +154,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (lane == 0) {                                   // ---- TMA loader ----
       int it = 0, issued = 0;
       bool ok = true;
+      bool waited = false;                             // on the previous kernel of the stream
+      int3 pending_a[STAGES];                          // activation tiles (stage, k, m) held back until then
+      int n_pending = 0;
+      const int my_tiles = (int)blockIdx.x < total_tiles ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+      const int first_run = my_tiles * num_k;          // stage fills this block issues in all
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
         for (int k = 0; k < num_k; k++, it++) {
@@ -159,8 +167,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           ok = mbar_wait(empty0 + 8 * s, ph ^ 1, err, 1);
           if (!ok) break;
           mbar_expect_tx(full0 + 8 * s, S::A_BYTES + S::B_BYTES);
-          tma_load_2d(smem_u32(a_tiles + s * S::A_BYTES), &map_a, full0 + 8 * s, k * BK, m0);
           tma_load_2d(smem_u32(b_tiles + s * S::B_BYTES), &map_b, full0 + 8 * s, k * BK, n0);
+          if (!waited) {
+            // the weight tiles of the first stages are on their way; the activations need the previous kernel
+            if (it + 1 < STAGES && it + 1 < first_run) { pending_a[n_pending++] = make_int3(s, k * BK, m0); issued = it + 1; continue; }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            waited = true;
+            for (int i = 0; i < n_pending; i++)
+              tma_load_2d(smem_u32(a_tiles + pending_a[i].x * S::A_BYTES), &map_a, full0 + 8 * pending_a[i].x, pending_a[i].y, pending_a[i].z);
+          }
+          tma_load_2d(smem_u32(a_tiles + s * S::A_BYTES), &map_a, full0 + 8 * s, k * BK, m0);
           issued = it + 1;
         }
       }
@@ -202,6 +218,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     float* st = staging + quarter * 32 * 33;
     int local = 0;
     bool ok = true;
+    tlc_wait(out);                                     // `out` may still be read or written by the previous kernel
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
       const int as = local & 1;
       const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
