@@ -98,7 +98,7 @@ struct Smem {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int TILES = STAGES * (A_BYTES + B_BYTES);
-  static constexpr int STAGING = 4 * 32 * 33 * 4;          // one padded 32x32 float tile per epilogue warp
+  static constexpr int STAGING = 4 * (32 * 33 + 2 * BN) * 4;   // per epilogue warp: a padded 32x32 float tile, the tile's column scales and biases
   static constexpr int N_BARS = 2 * STAGES + 4;            // full, empty per stage; accumulator full, empty x2
   static constexpr int TOTAL = TILES + STAGING + N_BARS * 8 + 16 + 1024;   // + tmem slot + alignment slack
 };
@@ -215,9 +215,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   } else {                                             // ---- epilogue, warps 2..5 ----
     const int quarter = warp & 3;                      // a warp may touch lanes 32*(warp%4) .. +31 only
-    float* st = staging + quarter * 32 * 33;
+    float* st = staging + quarter * (32 * 33 + 2 * BN);
+    float* sc = st + 32 * 33;                          // [BN] column scales | [BN] column biases of the tile
     int local = 0;
     bool ok = true;
+    // a lane can write 32 consecutive columns of its row 16 bytes at a time when rows start on 16-byte boundaries
+    const bool rows_aligned = (((uintptr_t)out) & 15) == 0 && ((size_t)ldo * sizeof(TO)) % 16 == 0;
     tlc_wait(out);                                     // `out` may still be read or written by the previous kernel
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
       const int as = local & 1;
@@ -226,14 +229,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int mrow0 = m0 + quarter * 32;
-      const bool scaled = SWIGLU && (colscale != nullptr || colbias != nullptr);
+      const bool scaled = colscale != nullptr || colbias != nullptr;
       if (scaled) {
         // the tile's column scales and biases once into the warp's staging area: every lane needs all of them
         __syncwarp();
         for (int j = lane; j < BN; j += 32) {
           const int n = n0 + j;
-          st[j] = (colscale && n < N) ? colscale[n] : 1.0f;
-          st[BN + j] = (colbias && n < N) ? colbias[n] : 0.0f;
+          sc[j] = (colscale && n < N) ? colscale[n] : 1.0f;
+          sc[BN + j] = (colbias && n < N) ? colbias[n] : 0.0f;
         }
         __syncwarp();
       }
@@ -255,8 +258,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             float vg = __uint_as_float(r[gcol]), vu = __uint_as_float(r[gcol + 8]);
             if (scaled) {
               const int jg = c * 32 + gcol;
-              vg = vg * st[jg] + st[BN + jg];
-              vu = vu * st[jg + 8] + st[BN + jg + 8];
+              vg = vg * sc[jg] + sc[BN + jg];
+              vu = vu * sc[jg + 8] + sc[BN + jg + 8];
             }
             o16[f] = silu_quick(vg) * vu;
           }
@@ -273,6 +276,57 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               for (int f = 0; f < 16; f++) {
                 const int gcol = ((f >> 3) << 4) + (f & 7);
                 if (nc0 + gcol + 8 < N) dst[f] = from_f32<TO>(o16[f]);
+              }
+            }
+          }
+          continue;
+        }
+        if (rows_aligned && nc0 + 32 <= N && (nc0 * sizeof(TO)) % 16 == 0) {
+          // the whole piece lies inside the matrix: a lane finishes the 32 columns of its row in registers and
+          // writes them 16 bytes at a time (no trip through shared memory)
+          const int m = mrow0 + lane;
+          if (m < M) {
+            TO* dst = out + (size_t)m * ldo + nc0;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+            if (scaled) {
+#pragma unroll
+              for (int j = 0; j < 32; j++) v[j] = v[j] * sc[c * 32 + j] + sc[BN + c * 32 + j];
+            }
+            if (sizeof(TO) == 4) {
+              float4* d4 = reinterpret_cast<float4*>(dst);
+              if (accumulate) {
+                float4 old[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) old[q] = d4[q];
+#pragma unroll
+                for (int q = 0; q < 8; q++) { v[4 * q] += old[q].x; v[4 * q + 1] += old[q].y; v[4 * q + 2] += old[q].z; v[4 * q + 3] += old[q].w; }
+              }
+#pragma unroll
+              for (int q = 0; q < 8; q++) d4[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+              uint4* d4 = reinterpret_cast<uint4*>(dst);
+              if (accumulate) {
+                uint4 old[4];
+#pragma unroll
+                for (int q = 0; q < 4; q++) old[q] = d4[q];
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                  const uint32_t w4[4] = {old[q].x, old[q].y, old[q].z, old[q].w};
+#pragma unroll
+                  for (int e = 0; e < 4; e++) {
+                    v[8 * q + 2 * e] += __uint_as_float(w4[e] << 16);
+                    v[8 * q + 2 * e + 1] += __uint_as_float(w4[e] & 0xffff0000u);
+                  }
+                }
+              }
+#pragma unroll
+              for (int q = 0; q < 4; q++) {
+                uint4 o;
+                o.x = pack2(v[8 * q], v[8 * q + 1]); o.y = pack2(v[8 * q + 2], v[8 * q + 3]);
+                o.z = pack2(v[8 * q + 4], v[8 * q + 5]); o.w = pack2(v[8 * q + 6], v[8 * q + 7]);
+                d4[q] = o;
               }
             }
           }
