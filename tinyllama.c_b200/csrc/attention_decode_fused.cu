@@ -3,7 +3,7 @@
 // What the separate kernels do in three launches happens here in one: the rotation of the row's
 // queries and of its new key (split-half form, angle = position * inv_freq[i] in 32-bit;
 // CodeClaper/tinyllama.c cpu_op.c:637-651), the store of the new key/value row into its page
-// (cpu_op.c:995-1008), attention of the row over a split of 128 keys per block with 32-bit
+// (cpu_op.c:995-1008), attention of the row over a split of 128 or 256 keys per block with 32-bit
 // scores, statistics and accumulator (cpu_op.c:1010-1062), and the merge of the splits, which
 // the last block of a (row, key/value head) to finish does.  A single-token step is a chain of
 // short dependent kernels; every launch taken out of the chain shortens the step.

@@ -7,12 +7,15 @@
 //   * both operands are K-major ([rows, K] with K contiguous), so TMA
 //     (cp.async.bulk.tensor.2d, 128-byte swizzle) stages [128 x 64] tiles of each into a
 //     ring of shared-memory buffers; out-of-range rows and the K tail arrive as zeros;
-//   * one elected thread issues tcgen05.mma (M=128, N=BN, K=16 per instruction) with the
-//     accumulator [128 x BN] in tensor memory, and tcgen05.commit hands each ring slot
-//     back to the loader;
-//   * four warps read the accumulator back with tcgen05.ld (each warp its 32 lanes = rows)
-//     and apply the epilogue in registers: column scale, column bias, optional add into
-//     the 32-bit residual, store as bfloat16 or float32.
+//   * one elected thread issues tcgen05.mma (M=128, N=BN = 64, 128 or 256, K=16 per
+//     instruction) with the accumulator [128 x BN] in tensor memory, and tcgen05.commit hands
+//     each ring slot back to the loader;
+//   * four warps read the accumulator back with tcgen05.ld (each warp its 32 lanes = rows,
+//     32 columns at a time) and apply the epilogue in registers: column scale and bias (staged
+//     once a tile in shared memory), optional add into the 32-bit residual or SwiGLU of
+//     interleaved gate|up columns; a lane writes the 32 columns of its row 16 bytes at a time
+//     (pieces that stick out of the matrix, or rows off 16-byte boundaries, go through a padded
+//     shared-memory tile instead and are written a row of 32 columns per instruction).
 // Warp roles: 0 = TMA loader, 1 = MMA issuer and owner of the tensor-memory allocation,
 // 2..5 = epilogue.  Every wait on an mbarrier is bounded; a wait that runs out records an
 // error code that the host reads, and the kernel frees its tensor memory and returns.
