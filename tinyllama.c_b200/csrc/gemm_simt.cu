@@ -208,7 +208,7 @@ constexpr int SK_WARPS = 16;          // warps per block, each with its own slic
 // With SWIGLU a block's 16 weight rows are 8 gate rows followed by their 8 up rows, and the block
 // writes silu(gate) * up for its 8 features (out is [M, N/2]).
 template <typename TO, int MG, int U, bool SWIGLU>
-__global__ void __launch_bounds__(SK_WARPS * 32, (MG <= 2 && U <= 4) ? 2 : 1)
+__global__ void __launch_bounds__(SK_WARPS * 32, ((MG == 1 && U <= 4) || (MG == 2 && U <= 2)) ? 2 : 1)
 gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                        TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                        const float* __restrict__ colbias, int accumulate, int M, int N, int K) {
@@ -232,7 +232,7 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
   const int n_steps = (K8 + 3) >> 2;                                 // a step is 4 chunks = 32 values of K
   // all of a warp's loads of one round are issued before the first multiply: one trip to memory
   for (int s0 = warp * U; s0 < n_steps; s0 += SK_WARPS * U) {
-    uint4 wa[U], wb[U], x0[U];
+    uint4 wa[U], wb[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int c = (s0 + u) * 4 + t;
@@ -241,25 +241,24 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
       wb[u] = in ? __ldg(w1 + c) : make_uint4(0, 0, 0, 0);
     }
     if (s0 == warp * U) tlc_wait(a, out);                                      // first round only
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-      const int c = (s0 + u) * 4 + t;
-      const bool in = (s0 + u) < n_steps && c < K8;
-      x0[u] = (in && g < M) ? *(reinterpret_cast<const uint4*>(a + (size_t)g * lda) + c) : make_uint4(0, 0, 0, 0);
-    }
+    // the activations of every row group, too, before the first multiply
+    uint4 xq[MG][U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int c = (s0 + u) * 4 + t;
       const bool in = (s0 + u) < n_steps && c < K8;
 #pragma unroll
       for (int mg = 0; mg < MG; mg++) {
-        uint4 xb = x0[u];
-        if (mg > 0) {
-          const int row = mg * 8 + g;
-          xb = (in && row < M) ? *(reinterpret_cast<const uint4*>(a + (size_t)row * lda) + c) : make_uint4(0, 0, 0, 0);
-        }
-        mma_bf16_16816(acc[mg], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xb.x, xb.y);
-        mma_bf16_16816(acc[mg], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xb.z, xb.w);
+        const int row = mg * 8 + g;
+        xq[mg][u] = (in && row < M) ? *(reinterpret_cast<const uint4*>(a + (size_t)row * lda) + c) : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+#pragma unroll
+      for (int mg = 0; mg < MG; mg++) {
+        mma_bf16_16816(acc[mg], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xq[mg][u].x, xq[mg][u].y);
+        mma_bf16_16816(acc[mg], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xq[mg][u].z, xq[mg][u].w);
       }
     }
   }
@@ -317,8 +316,9 @@ static void launch_skinny_mg(const __nv_bfloat16* a, int lda, const __nv_bfloat1
                              cudaStream_t stream) {
   const unsigned blocks = (unsigned)((N + 15) / 16);
   const int n_steps = ((K >> 3) + 3) >> 2;
-  // U steps per warp and round; with U <= 4 and few row groups two blocks fit on an SM
-  if (n_steps <= SK_WARPS * 2)
+  // U steps per warp and round: with one row group and U <= 4, or two and U = 2, two blocks fit on an SM
+  // (a warp holds the weights and the activations of a round in registers)
+  if (n_steps <= SK_WARPS * 2 || MG == 2)
     tlc_launch(gemm_skinny_mma_kernel<TO, MG, 2, SWIGLU>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
   else
     tlc_launch(gemm_skinny_mma_kernel<TO, MG, 4, SWIGLU>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
