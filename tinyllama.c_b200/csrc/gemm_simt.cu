@@ -208,7 +208,7 @@ constexpr int SK_WARPS = 16;          // warps per block, each with its own slic
 // With SWIGLU a block's 16 weight rows are 8 gate rows followed by their 8 up rows, and the block
 // writes silu(gate) * up for its 8 features (out is [M, N/2]).
 template <typename TO, int MG, int U, bool SWIGLU>
-__global__ void __launch_bounds__(SK_WARPS * 32, ((MG == 1 && U <= 4) || (MG == 2 && U <= 2)) ? 2 : 1)
+__global__ void __launch_bounds__(SK_WARPS * 32, ((MG == 1 && U <= 4) || (MG == 2 && U <= 2) || (MG == 4 && U == 1)) ? 2 : 1)
 gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                        TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                        const float* __restrict__ colbias, int accumulate, int M, int N, int K) {
@@ -318,7 +318,9 @@ static void launch_skinny_mg(const __nv_bfloat16* a, int lda, const __nv_bfloat1
   const int n_steps = ((K >> 3) + 3) >> 2;
   // U steps per warp and round: with one row group and U <= 4, or two and U = 2, two blocks fit on an SM
   // (a warp holds the weights and the activations of a round in registers)
-  if (n_steps <= SK_WARPS * 2 || MG == 2)
+  if (MG == 4 && blocks > 296)      // 17..32 rows, many row tiles: one step a round keeps two blocks on an SM
+    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 1, SWIGLU>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+  else if (n_steps <= SK_WARPS * 2 || MG == 2)
     tlc_launch(gemm_skinny_mma_kernel<TO, MG, 2, SWIGLU>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
   else
     tlc_launch(gemm_skinny_mma_kernel<TO, MG, 4, SWIGLU>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
