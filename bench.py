@@ -38,7 +38,13 @@ CONFIG_1P5B = dict(
     mamba_norm_before_gate=False, embedding_multiplier=5.66, lm_head_multiplier=0.039, key_multiplier=0.39,
     attention_in_multiplier=1.0, attention_out_multiplier=0.94, ssm_in_multiplier=1.25, ssm_out_multiplier=0.24,
     mlp_multipliers=[0.88, 0.3], ssm_multipliers=[0.35, 0.25, 0.7, 0.5, 0.35])
-FULL_LAYERS = 24
+# the 3B and 7B layer sizes (their other options as above): --sizes 3B / 7B
+CONFIG_3B = dict(CONFIG_1P5B, hidden_size=2560, num_hidden_layers=32, num_attention_heads=10, intermediate_size=8192,
+                 mamba_d_ssm=4096, mamba_n_heads=32, mamba_d_head=128)
+CONFIG_7B = dict(CONFIG_1P5B, hidden_size=3072, num_hidden_layers=44, num_attention_heads=12, intermediate_size=12288,
+                 vocab_size=130048, max_position_embeddings=8192, tie_word_embeddings=False,
+                 mamba_d_ssm=3072, mamba_n_heads=24, mamba_d_head=128)
+CONFIGS = {"1.5B": CONFIG_1P5B, "3B": CONFIG_3B, "7B": CONFIG_7B}
 
 
 def peaks():
@@ -70,7 +76,7 @@ def decode_bytes(cfg, batch, context):
     included), and the cache of the live sequences (bf16 keys and values up to `context`,
     the 32-bit conv window and SSM state)."""
     s = sizes(cfg)
-    weights = (s["L"] * s["layer_w"] + s["V"] * s["D"]) * 2
+    weights = (s["L"] * s["layer_w"] + s["V"] * s["D"]) * 2          # the head's matrix; a token's embedding row is 4 KB
     kv = 2 * s["L"] * s["KV"] * s["hd"] * 2 * context
     state = s["L"] * (s["Hs"] * s["P"] * s["N"] + (s["K"] - 1) * s["Cd"]) * 4
     return weights + batch * (kv + state)
@@ -198,6 +204,28 @@ def e2e_decode(llm, tlc, batch, prompt_len, steps, seed):
         st["d2h_bytes"] // max(1, st["decode_steps"])
 
 
+def time_generate(llm, tlc, n_prompts, lo, hi, new_tokens, temperature, seed):
+    """Unequal prompts (lengths uniform in [lo, hi]) generated together through LLM.generate() with temperature
+    sampling, every sequence to new_tokens: host token ids in and out, the second of two runs timed."""
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(lo, hi + 1, (n_prompts,), generator=g).tolist()
+    prompts = [torch.randint(0, llm.config.vocab_size, (n,), generator=g).tolist() for n in lens]
+    sampling = tlc.SamplingParams(temperature=temperature, seed=seed)
+    out = {}
+    for run in range(2):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        llm.generate(prompts, sampling, max_new_tokens=new_tokens, ignore_eos=True, max_batch=n_prompts)
+        torch.cuda.synchronize()
+        out = dict(llm.last_stats, wall_s=time.perf_counter() - t0)
+    return {"prompts": n_prompts, "prompt_tokens": sum(lens), "new_tokens": n_prompts * new_tokens,
+            "temperature": temperature, "wall_s": round(out["wall_s"], 4),
+            "prefill_tok_s": round(out["prefill_tokens"] / out["prefill_s"], 1),
+            "decode_tok_s": round(out["decode_tokens"] / out["decode_s"], 1),
+            "tok_s": round(n_prompts * new_tokens / out["wall_s"], 1)}
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -205,9 +233,13 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--sizes", default="1.5B", choices=sorted(CONFIGS), help="layer sizes of this Falcon-H1 model")
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--generate", type=int, default=0, metavar="N",
+                    help="also generate 256 tokens for N prompts of 64..2048 tokens at temperature 0.7")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -221,12 +253,18 @@ def main() -> int:
 
     import torch
     import tinyllama_c_b200 as tlc
-    cfg = dict(CONFIG_1P5B, num_hidden_layers=args.layers)
+    full_layers = CONFIGS[args.sizes]["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = full_layers
+    cfg = dict(CONFIGS[args.sizes], num_hidden_layers=args.layers)
+    s = sizes(cfg)
     pk = peaks()
     ctx_len = cfg["max_position_embeddings"]
     model = tlc.random_model(cfg, seed=0, dtype="bfloat16")
-    # room for 64 sequences of prompt + decoded tokens, and for the 2,048-token prompt
-    llm = tlc.LLM(model, max_tokens=64 * 1024, max_seqs=64)
+    # room for 64 sequences of prompt + decoded tokens, for the long prompt and for the unequal batch
+    per_seq = -(-(args.prompt_len + 2 * args.steps + 80) // 64) * 64
+    room = max(64 * 1024, max(64, args.batch) * per_seq, args.prefill_tokens + 64, args.generate * (2048 + 256 + 64))
+    llm = tlc.LLM(model, max_tokens=room, max_seqs=max(64, args.batch, args.generate))
 
     ms, launches, clocks, ctx = time_decode(llm, tlc, args.batch, args.prompt_len, args.steps, args.warmup, seed=1)
     value = args.batch * 1000.0 / ms
@@ -234,23 +272,26 @@ def main() -> int:
     achieved = nbytes / (ms * 1e-3) / 1e9
     e2e_v, h2d, d2h = e2e_decode(llm, tlc, args.batch, args.prompt_len, args.steps, seed=2)
     rec = {
-        "metric": "decode tok/s at batch 8 (Falcon-H1-1.5B sizes, 512-token prompts, context 4096)",
+        "metric": f"decode tok/s at batch {args.batch} (Falcon-H1-{args.sizes} sizes, {args.prompt_len}-token prompts, "
+                  f"context {ctx_len})",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
-        "config": {"model": "Falcon-H1-1.5B sizes", "global_batch": args.batch, "seq_len": ctx_len,
+        "config": {"model": f"Falcon-H1-{args.sizes} sizes", "global_batch": args.batch, "seq_len": ctx_len,
                    "prompt_len": args.prompt_len, "parallelism": "single GPU", "layers": args.layers,
-                   "layers_full": FULL_LAYERS, "hidden": cfg["hidden_size"], "heads": "8q/2kv x128",
+                   "layers_full": full_layers, "hidden": cfg["hidden_size"],
+                   "heads": f"{s['H']}q/{s['KV']}kv x{s['hd']}",
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "mamba": "48 heads x64, state 256, groups 1, conv 4", "tied": True,
-                   "l2": "inputs larger than L2 (2.7 GB of weights per step)"},
+                   "mamba": f"{s['Hs']} heads x{s['P']}, state {s['N']}, groups {s['G']}, conv {s['K']}",
+                   "tied": cfg["tie_word_embeddings"],
+                   "l2": f"inputs larger than L2 ({decode_bytes(cfg, 0, 0) / 1e9:.1f} GB of weights per step)"},
         "clocks": clocks, "gpu_launches": launches,
         "e2e": {"value": round(e2e_v, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peak_source": pk["source"]},
     }
     if not args.no_points:
-        T = 2048
+        T = args.prefill_tokens
         pms = time_prefill(llm, T, seed=3)
         fl = prefill_flops(cfg, T)
         rec["prefill"] = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
@@ -260,6 +301,8 @@ def main() -> int:
             m, _, _, _ = time_decode(llm, tlc, b, args.prompt_len, max(8, args.steps // 2), 3, seed=4 + b)
             pts[f"decode_b{b}"] = round(b * 1000.0 / m, 1)
         rec["points"] = pts
+    if args.generate:
+        rec["generate"] = time_generate(llm, tlc, args.generate, 64, 2048, 256, 0.7, seed=9)
     print(json.dumps(rec))
     return 0
 

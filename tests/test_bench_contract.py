@@ -27,7 +27,11 @@ def test_reference_arm_reports_unavailable():
 def test_config_is_flat_and_names_both_layer_counts():
     sys.path.insert(0, ROOT)
     import bench
-    assert bench.FULL_LAYERS == bench.CONFIG_1P5B["num_hidden_layers"] == 24
+    assert bench.CONFIGS["1.5B"] is bench.CONFIG_1P5B and bench.CONFIG_1P5B["num_hidden_layers"] == 24
+    assert (bench.CONFIG_3B["num_hidden_layers"], bench.CONFIG_7B["num_hidden_layers"]) == (32, 44)
+    # the matrices a step reads: 3.5 G weights at 3B, 7.2 G at 7B (its head is untied)
+    assert 6.5e9 < bench.decode_bytes(bench.CONFIG_3B, 0, 0) < 7.5e9
+    assert 14e9 < bench.decode_bytes(bench.CONFIG_7B, 0, 0) < 15e9
     nbytes = bench.decode_bytes(bench.CONFIG_1P5B, 8, 512)
     assert 3.3e9 < nbytes < 3.5e9           # 2.69 GB of weights + 8 x (76.5 MB of state to read + 12.6 MB of keys and values)
     assert 5.0e12 < bench.prefill_flops(bench.CONFIG_1P5B, 2048) < 6.0e12

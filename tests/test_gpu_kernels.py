@@ -419,6 +419,37 @@ def test_sample_equals_the_plain_sampler(params):
     assert (got != ref).sum().item() <= 1, f"{(got != ref).sum().item()} of {R} draws differ: {got} vs {ref}"
 
 
+@pytest.mark.parametrize("case", ["ties at the cut", "fewer positive than top-k", "top-k 1024", "top-k 1500", "large vocabulary"])
+def test_sample_cuts_and_ties(case):
+    """The cuts where they are decided by order rather than by value: equal probabilities at the top-k and
+    top-p cuts (the first in token-id order stay), probabilities that underflow to zero, and a top-k at and
+    beyond what the short-list kernel holds."""
+    g = gen(12)
+    R, V, T, k, top_p, min_p = 16, 3000, 0.8, 40, 0.9, 0.0
+    logits = rnd(g, R, V, scale=2.5)
+    if case == "ties at the cut":
+        logits = (logits * 2).round() / 2          # steps of 0.5: dozens of tokens share each of the top values
+        k = 12
+    elif case == "fewer positive than top-k":
+        logits, T, k = logits * 40, 0.05, 200      # exp((l - max) / T) underflows for all but a few tokens
+    elif case == "top-k 1024":
+        k, top_p = 1024, 0.97
+    elif case == "top-k 1500":
+        k, top_p = 1500, 0.97
+    elif case == "large vocabulary":
+        V = 130048
+        logits = rnd(g, R, V, scale=3.0)
+        logits[:, 7::1000] += 6.0
+    u = torch.rand(R, generator=g)
+    u[0], u[1] = 0.0, 0.9999999
+    args = [logits, torch.empty(R, V), None, u, T, k, top_p, min_p, 1.0, 0.0, 0.0, torch.empty(R, dtype=torch.int32)]
+    gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args]
+    ops.sample(*gpu)
+    ops_plain.sample(*args)
+    got, ref = gpu[11].cpu(), args[11]
+    assert (got != ref).sum().item() <= 1, f"{case}: {(got != ref).sum().item()} of {R} draws differ: {got} vs {ref}"
+
+
 def test_sample_frequencies_follow_the_filtered_distribution():
     g = gen(11)
     V, R = 50, 4000

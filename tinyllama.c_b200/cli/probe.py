@@ -6,10 +6,11 @@ plays both roles for this library:
 
     bin/probe decode  --batch 8 --layers 2 --prompt 512     three eager one-token steps (for ncu)
     bin/probe prefill --layers 2 --prompt 2048              one prompt, twice (for ncu)
+    bin/probe prefill --batch 16 --unequal --prompt 2048    16 prompts of 64..2048 tokens together, twice
     bin/probe linear  --rows 2048 --n 6704 --k 2048 [--accumulate] [--swiglu] [--bf16-out] [--tile 64|128|256]
     bin/probe kernels --batch 8                             every decode-step kernel, warm, in a CUDA graph
 
-Models are random, with the layer sizes of bench.py (Falcon-H1-1.5B) and --layers layers.
+Models are random, with the layer sizes of bench.py (--sizes 1.5B, 3B or 7B) and --layers layers.
 """
 from __future__ import annotations
 
@@ -18,20 +19,20 @@ import os
 import sys
 
 
-def _model(layers: int):
+def _model(layers: int, sizes: str = "1.5B", room: int = 64 * 1024):
     import tinyllama_c_b200 as tlc
     sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
     import bench
-    cfg = dict(bench.CONFIG_1P5B, num_hidden_layers=layers)
-    return tlc.LLM(tlc.random_model(cfg, seed=0), max_tokens=64 * 1024, max_seqs=64), cfg
+    cfg = dict(bench.CONFIGS[sizes], num_hidden_layers=layers)
+    return tlc.LLM(tlc.random_model(cfg, seed=0), max_tokens=max(room, 64 * 1024), max_seqs=64), cfg
 
 
 def run_steps(args) -> None:
     import torch
     from tinyllama_c_b200.engine import StepEntry
-    llm, cfg = _model(args.layers)
+    B = args.batch if args.what == "decode" or args.unequal else 1
+    llm, cfg = _model(args.layers, args.sizes, B * (args.prompt + 128))
     g = torch.Generator().manual_seed(0)
-    B = args.batch if args.what == "decode" else 1
     slots = [llm.cache.acquire() for _ in range(B)]
     prompts = torch.randint(0, cfg["vocab_size"], (B, args.prompt), generator=g).tolist()
     if args.what == "decode":
@@ -40,6 +41,23 @@ def run_steps(args) -> None:
         torch.cuda.synchronize()
         for _ in range(3):
             llm.step([StepEntry(s, [5], (0,)) for s in slots])
+    elif args.unequal:
+        # prompts of 64..--prompt tokens together, in steps of at most 8192 tokens as generation runs them
+        from tinyllama_c_b200.engine.generate import EngineBackend
+        import tinyllama_c_b200 as tlc
+        lens = torch.randint(64, args.prompt + 1, (B,), generator=g).tolist()
+        backend = EngineBackend(llm.model, llm.cache, tlc.GREEDY)
+        for it in range(2):
+            if it:
+                for s in slots:
+                    llm.cache.release(s)
+                slots = [llm.cache.acquire() for _ in range(B)]
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            backend.step_and_sample([(s, p[:n]) for s, p, n in zip(slots, prompts, lens)], [[]] * B, list(range(B)), [0] * B)
+            e1.record()
+            torch.cuda.synchronize()
+            print(f"{sum(lens)} tokens of {B} prompts: {e0.elapsed_time(e1):.2f} ms", flush=True)
     else:
         for it in range(2):
             s = slots[0] if it == 0 else llm.cache.acquire()
@@ -173,10 +191,12 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--sizes", default="1.5B", choices=["1.5B", "3B", "7B"], help="decode, prefill: layer sizes of the model")
     ap.add_argument("--rows", type=int, default=2048)
     ap.add_argument("--n", type=int, default=6704)
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--accumulate", action="store_true")
+    ap.add_argument("--unequal", action="store_true", help="prefill: --batch prompts of 64..--prompt tokens in one batch")
     ap.add_argument("--tile", type=int, default=0, choices=[0, 64, 128, 256])
     ap.add_argument("--swiglu", action="store_true", help="linear: gate|up rows interleaved by 8, SwiGLU in the epilogue")
     ap.add_argument("--bf16-out", action="store_true", help="linear: bfloat16 output instead of float32")

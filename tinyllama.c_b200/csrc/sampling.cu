@@ -7,12 +7,50 @@
 // renormalise and draw (sampler.c:237-251).  Greedy is the first maximum (sampler.c:92-102).
 //
 // The reference sorts a bounded heap; a GPU block instead finds each cut as a threshold
-// on the probability's bit pattern (31 counting passes), keeps ties in token-id order and
-// draws by inverse CDF over the survivors in token-id order from a uniform number the
-// caller supplies, so the result is a pure function of (logits, parameters, u).
+// on the probability's bit pattern, keeps ties in token-id order and draws by inverse CDF
+// over the survivors in token-id order from a uniform number the caller supplies, so the
+// result is a pure function of (logits, parameters, u).  With a top-k of at most 1024 the
+// threshold comes from a three-pass radix select and the rest works on the survivors in
+// shared memory (sample_topk_kernel); otherwise every cut is found by 31 counting passes
+// over the vocabulary (sample_kernel).
 #include "common.cuh"
 
 #define SAMP_THREADS 1024
+
+// f(value, index) over a row of V floats, the block's threads striding through it: 16 bytes a load where
+// the row allows it (a pass over the vocabulary is bound by the loads one block can keep in flight).
+template <typename F>
+__device__ __forceinline__ void row_read(const float* __restrict__ p, int V, F f) {
+  if ((V & 3) == 0 && (((uintptr_t)p) & 15) == 0) {
+    const float4* p4 = reinterpret_cast<const float4*>(p);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < (V >> 2); i += blockDim.x) {
+      const float4 v = p4[i];
+      f(v.x, 4 * i); f(v.y, 4 * i + 1); f(v.z, 4 * i + 2); f(v.w, 4 * i + 3);
+    }
+  } else {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < V; i += blockDim.x) f(p[i], i);
+  }
+}
+
+// dst[i] = f(src[i], i) over a row (dst may be src)
+template <typename F>
+__device__ __forceinline__ void row_map(const float* src, float* dst, int V, F f) {
+  if ((V & 3) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
+    const float4* s4 = reinterpret_cast<const float4*>(src);
+    float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < (V >> 2); i += blockDim.x) {
+      float4 v = s4[i];
+      v.x = f(v.x, 4 * i); v.y = f(v.y, 4 * i + 1); v.z = f(v.z, 4 * i + 2); v.w = f(v.w, 4 * i + 3);
+      d4[i] = v;
+    }
+  } else {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < V; i += blockDim.x) dst[i] = f(src[i], i);
+  }
+}
 
 __device__ __forceinline__ float block_max(float v, float* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
@@ -119,25 +157,19 @@ __device__ float block_exclusive_scan(float v, float* scan_buf, float* total) {
   return scan_buf[warp] + inc - v;
 }
 
-// Survivor test shared by all passes: p above the cut, or equal to it and among the first
-// `ties` such elements in token-id order (tie ranks are found with a scan where needed).
-//
-// One block per row.  `work` is a [R, V] 32-bit scratch that receives the penalised logits
-// and then the unnormalised probabilities.
-__global__ void __launch_bounds__(SAMP_THREADS)
-sample_kernel(const float* __restrict__ logits, float* __restrict__ work, const int* __restrict__ history,
-              const float* __restrict__ uniforms, SampleParams sp, int V, int* __restrict__ out) {
-  tlc_pdl(logits, work, history, uniforms, out);
-  __shared__ float red[33];
-  __shared__ int redi[33];
-  __shared__ float scan_buf[33];
-  __shared__ unsigned cnt_s;
+// The part every sampling kernel starts with: the row's logits into `p`, the penalties
+// (sampler.c:116-144), the greedy cases (sampler.c:146-151; returns true when the token is chosen),
+// and the softmax numerators exp(l / T - max) in place of the logits with their sum in *total
+// (sampler.c:156-169).
+__device__ bool sample_prologue(const float* __restrict__ logits, float* __restrict__ work, const int* __restrict__ history,
+                                const SampleParams& sp, int V, int* __restrict__ out, float* red, int* redi,
+                                float** p_out, float* total_out, unsigned* hist0 = nullptr) {
   const int row = blockIdx.x;
   const float* lg = logits + (size_t)row * V;
   float* p = work + (size_t)row * V;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) p[i] = lg[i];
+  *p_out = p;
+  row_map(lg, p, V, [](float v, int) { return v; });
   __syncthreads();
-  // ---- penalties (sampler.c:116-144) ----
   if ((sp.repeat_penalty != 1.0f || sp.frequency_penalty != 0.0f || sp.presence_penalty != 0.0f) && sp.n_history > 0) {
     const int* hist = history + (size_t)row * sp.n_history;
     for (int j = threadIdx.x; j < sp.n_history; j += blockDim.x) {
@@ -156,20 +188,49 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, const 
     __syncthreads();
   }
   const bool no_filter = sp.top_k == 0 && sp.top_p >= 1.0f && sp.min_p <= 1e-6f;
-  if (sp.temperature <= 1e-6f || no_filter) {          // sampler.c:146-151
+  if (sp.temperature <= 1e-6f || no_filter) {
     const int r = block_argmax(p, V, red, redi);
     if (threadIdx.x == 0) out[row] = r;
-    return;
+    return true;
   }
-  // ---- softmax numerators (sampler.c:156-169) ----
   const float inv_t = 1.0f / sp.temperature;
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, p[i] * inv_t);
+  row_read(p, V, [&](float v, int) { mx = fmaxf(mx, v * inv_t); });
   mx = block_max(mx, red);
   float s = 0.f;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) { const float e = expf(p[i] * inv_t - mx); p[i] = e; s += e; }
-  const float total = block_sum(s, red);
+  if (hist0 != nullptr) {
+    // the short-list kernel counts the top digit of the probabilities' bit patterns in the same pass
+    row_map(p, p, V, [&](float v, int) {
+      const float e = expf(v * inv_t - mx);
+      s += e;
+      atomicAdd(&hist0[__float_as_uint(e) >> 20], 1u);
+      return e;
+    });
+  } else {
+    row_map(p, p, V, [&](float v, int) { const float e = expf(v * inv_t - mx); s += e; return e; });
+  }
+  *total_out = block_sum(s, red);
   __syncthreads();
+  return false;
+}
+
+// Survivor test shared by all passes: p above the cut, or equal to it and among the first
+// `ties` such elements in token-id order (tie ranks are found with a scan where needed).
+//
+// One block per row.  `work` is a [R, V] 32-bit scratch that receives the penalised logits
+// and then the unnormalised probabilities.
+__global__ void __launch_bounds__(SAMP_THREADS)
+sample_kernel(const float* __restrict__ logits, float* __restrict__ work, const int* __restrict__ history,
+              const float* __restrict__ uniforms, SampleParams sp, int V, int* __restrict__ out) {
+  tlc_pdl(logits, work, history, uniforms, out);
+  __shared__ float red[33];
+  __shared__ int redi[33];
+  __shared__ float scan_buf[33];
+  __shared__ unsigned cnt_s;
+  const int row = blockIdx.x;
+  float* p;
+  float total;
+  if (sample_prologue(logits, work, history, sp, V, out, red, redi, &p, &total)) return;
   // ---- top-k: bit pattern of the k-th largest probability (all are >= 0) ----
   unsigned cut = 0;            // survivors: bits(p) > cut, or == cut for the first `ties`
   unsigned ties = 0xffffffffu;
@@ -278,6 +339,162 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, const 
   if (threadIdx.x == 0) out[row] = (int)cnt_s;
 }
 
+
+#define SAMP_KMAX 1024       // survivors of top-k that the short-list kernel holds in shared memory
+#define SAMP_BINS 2048       // = 2 * SAMP_THREADS: the digit scan gives every thread two bins
+
+// The same selection when 0 < top_k <= SAMP_KMAX: the k-th largest probability is found by a radix
+// select on the bit pattern (three counting passes of 11, 11 and 9 bits instead of 31 of one bit), the at
+// most top_k survivors are gathered into shared memory and put in token-id order, and min-p, top-p and the
+// draw work on that short list.  Which tokens survive, how ties at a cut are broken (token-id order) and
+// the order of the draw are those of the general kernel above; sums over the survivors are taken
+// in token-id order.
+__global__ void __launch_bounds__(SAMP_THREADS)
+sample_topk_kernel(const float* __restrict__ logits, float* __restrict__ work, const int* __restrict__ history,
+                   const float* __restrict__ uniforms, SampleParams sp, int V, int* __restrict__ out) {
+  tlc_pdl(logits, work, history, uniforms, out);
+  __shared__ float red[33];
+  __shared__ int redi[33];
+  __shared__ float scan_buf[33];
+  __shared__ unsigned hist[SAMP_BINS];
+  __shared__ float sv[SAMP_KMAX], sv2[SAMP_KMAX];
+  __shared__ int si[SAMP_KMAX], si2[SAMP_KMAX];
+  __shared__ unsigned s_digit, s_krem, s_count, s_n, s_bits;
+  __shared__ int s_pick, s_last;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  float* p;
+  float total;
+  for (int j = tid; j < SAMP_BINS; j += blockDim.x) hist[j] = 0;
+  __syncthreads();
+  if (sample_prologue(logits, work, history, sp, V, out, red, redi, &p, &total, hist)) return;
+  // ---- top-k: bit pattern of the k-th largest probability (all are >= 0, so bit 31 is clear) ----
+  unsigned prefix = 0, k_rem = (unsigned)sp.top_k, n_at = 0;
+#pragma unroll 1
+  for (int pass = 0; pass < 3; pass++) {
+    const int shift = pass == 0 ? 20 : pass == 1 ? 9 : 0;          // the digit's lowest bit
+    const int above = pass == 0 ? 31 : pass == 1 ? 20 : 9;         // bits from here up are settled
+    const unsigned mask = pass == 2 ? 511u : 2047u;
+    if (pass > 0) {                                                 // the first digit was counted with the numerators
+      for (int j = tid; j < SAMP_BINS; j += blockDim.x) hist[j] = 0;
+      __syncthreads();
+      row_read(p, V, [&](float v, int) {
+        const unsigned b = __float_as_uint(v);
+        if ((b >> above) == (prefix >> above)) atomicAdd(&hist[(b >> shift) & mask], 1u);
+      });
+      __syncthreads();
+    }
+    // from the highest digit down: the digit at which the count reaches what is still wanted
+    const int b1 = SAMP_BINS - 1 - 2 * tid, b0 = b1 - 1;
+    const unsigned c1 = hist[b1], c0 = hist[b0];
+    float tot;
+    const unsigned before = (unsigned)block_exclusive_scan((float)(c1 + c0), scan_buf, &tot);   // counts < 2^24: exact
+    if (before < k_rem && before + c1 + c0 >= k_rem) {
+      if (before + c1 >= k_rem) { s_digit = (unsigned)b1; s_krem = k_rem - before; s_count = c1; }
+      else { s_digit = (unsigned)b0; s_krem = k_rem - before - c1; s_count = c0; }
+    }
+    __syncthreads();
+    prefix |= s_digit << shift;
+    k_rem = s_krem;
+    n_at = s_count;
+    __syncthreads();
+  }
+  const unsigned cut = prefix;      // survivors: bits(p) > cut, and the first k_rem of the n_at elements at the cut
+  if (cut != 0 && n_at > k_rem) {
+    // more elements tie at the cut than may stay: the first k_rem in token-id order do
+    unsigned seen_ties = 0;
+    for (int base = 0; base < V; base += blockDim.x) {
+      const int i = base + tid;
+      const bool is_tie = i < V && __float_as_uint(p[i]) == cut;
+      float tot;
+      const float before = block_exclusive_scan(is_tie ? 1.f : 0.f, scan_buf, &tot);
+      if (is_tie && seen_ties + (unsigned)before >= k_rem) p[i] = 0.f;
+      seen_ties += (unsigned)tot;
+      __syncthreads();
+    }
+  }
+  // ---- the survivors into shared memory (probabilities of zero can never be drawn: left out) ----
+  if (tid == 0) s_n = 0;
+  __syncthreads();
+  row_read(p, V, [&](float v, int i) {
+    const unsigned b = __float_as_uint(v);
+    if (b != 0 && b >= cut) {
+      const unsigned at = atomicAdd(&s_n, 1u);
+      if (at < SAMP_KMAX) { sv[at] = v; si[at] = i; }
+    }
+  });
+  __syncthreads();
+  const int n = (int)min(s_n, (unsigned)SAMP_KMAX);
+  // token-id order: an element's place is the number of survivors with a smaller id
+  if (tid < n) {
+    const int mine = si[tid];
+    int r = 0;
+    for (int j = 0; j < n; j++) r += si[j] < mine;
+    sv2[r] = sv[tid];
+    si2[r] = mine;
+  }
+  __syncthreads();
+  // ---- min-p relative to the best probability, whose numerator is exp(0) = 1 (sampler.c:200-210) ----
+  if (sp.min_p > 1e-6f) {
+    if (tid < n && sv2[tid] < sp.min_p) sv2[tid] = 0.f;
+    __syncthreads();
+  }
+  // ---- top-p: smallest descending prefix whose normalised mass reaches top_p (sampler.c:213-221) ----
+  if (sp.top_p < 1.0f) {
+    const float target = sp.top_p * total;            // compare unnormalised masses
+    if (tid == 0) s_bits = 0;
+    __syncthreads();
+    if (tid < n) {
+      const float v = sv2[tid];
+      if (v > 0.f) {
+        float m = 0.f;
+        for (int j = 0; j < n; j++) { const float w = sv2[j]; if (w >= v) m += w; }
+        if (m >= target) atomicMax(&s_bits, __float_as_uint(v));
+      }
+    }
+    __syncthreads();
+    const unsigned pc = s_bits;     // the largest value whose mass at-or-above reaches the target (0: keep every survivor)
+    if (pc != 0) {
+      float above = 0.f;
+      for (int j = 0; j < n; j++) { const float w = sv2[j]; if (__float_as_uint(w) > pc) above += w; }
+      // ties at the cut enter in token-id order until the mass reaches the target
+      unsigned need = 0;
+      if (above < target) need = (unsigned)ceilf((target - above) / __uint_as_float(pc));
+      if (need == 0 && above < target) need = 1;
+      bool drop = false;
+      if (tid < n) {
+        const unsigned b = __float_as_uint(sv2[tid]);
+        if (b < pc) drop = true;
+        else if (b == pc) {
+          unsigned earlier = 0;
+          for (int j = 0; j < tid; j++) earlier += __float_as_uint(sv2[j]) == pc;
+          drop = earlier >= need;
+        }
+      }
+      __syncthreads();
+      if (drop) sv2[tid] = 0.f;
+      __syncthreads();
+    }
+  }
+  // ---- renormalise and draw by inverse CDF in token-id order (sampler.c:237-251) ----
+  if (tid == 0) { s_pick = 0x7fffffff; s_last = -1; }
+  __syncthreads();
+  float m = 0.f;
+  for (int j = 0; j < n; j++) m += sv2[j];
+  const float target = uniforms[row] * m;
+  if (tid < n) {
+    const float v = sv2[tid];
+    if (v > 0.f) {
+      float before = 0.f;
+      for (int j = 0; j < tid; j++) before += sv2[j];
+      if (target < before + v) atomicMin(&s_pick, tid);
+      atomicMax(&s_last, tid);
+    }
+  }
+  __syncthreads();
+  // rounding may leave the target at the very end: then the last survivor (sampler.c:253-255)
+  if (tid == 0) out[row] = si2[s_pick != 0x7fffffff ? s_pick : max(s_last, 0)];
+}
+
 extern "C" int tlc_sample(const float* logits, float* work, const int* history, const float* uniforms, int R, int V,
                           float temperature, int top_k, float top_p, float min_p, float repeat_penalty,
                           int n_history, float frequency_penalty, float presence_penalty, int* out,
@@ -289,7 +506,10 @@ extern "C" int tlc_sample(const float* logits, float* work, const int* history, 
   TLC_REQUIRE(min_p >= 0.f && min_p <= 1.f, "sample: min-p must be in [0, 1], got %g", min_p);
   SampleParams sp{temperature, top_p, min_p, repeat_penalty, frequency_penalty, presence_penalty, top_k,
                   history ? n_history : 0};
-  tlc_launch(sample_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, logits, work, history, uniforms, sp, V, out);
+  if (top_k > 0 && top_k <= SAMP_KMAX && top_k < V)
+    tlc_launch(sample_topk_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, logits, work, history, uniforms, sp, V, out);
+  else
+    tlc_launch(sample_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, logits, work, history, uniforms, sp, V, out);
   TLC_CHECK_LAUNCH("sample");
   return 0;
 }
