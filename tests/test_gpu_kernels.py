@@ -244,7 +244,9 @@ def test_attention_of_single_token_steps(dtype, H, KV, hd, window):
 def test_attention_of_single_token_steps_in_one_kernel(H, KV, hd, rope, window, longest, write):
     """Rotation, store of the new row and attention in one launch, against the three plain steps;
     run several times so that the arrival counters are seen to come back to zero.  The long
-    contexts take the blocks of 256 keys."""
+    contexts take pieces of 256 keys, several a block; then the number of pieces a block takes one after
+    the other is fixed: two, three, and all of them (one block per row and head group, which writes the
+    output itself)."""
     g = gen(14)
     starts = [0, 200, 63, longest, 127, 128]
     lens = [1] * len(starts)
@@ -265,20 +267,25 @@ def test_attention_of_single_token_steps_in_one_kernel(H, KV, hd, rope, window, 
                             hd, write)
     out_ref = torch.empty(B, H * hd, dtype=torch.bfloat16)
     ops_plain.attention(q_ref, k_ref, v_ref, table, pos, row_seq, slots, out_ref, H, KV, hd, scale, window)
-    for max_keys in (longest + 1, (longest // 1024 + 1) * 1024, longest + 1):
-        k_gpu, v_gpu = k_pages.cuda(), v_pages.cuda()
-        out = torch.empty(B, H * hd, dtype=torch.bfloat16, device="cuda")
-        qkv_gpu = qkv.cuda()
-        assert ops.attention_decode_fused_ok(view(qkv_gpu), torch.bfloat16, H, KV, hd)
-        ops.attention_decode_fused(view(qkv_gpu), 0, H * hd, (H + KV) * hd, k_gpu, v_gpu, inv.cuda(), write, table.cuda(),
-                                   pos.cuda(), row_seq.cuda(), slots.cuda(), out, H, KV, hd, scale, window, max_keys)
-        ref = out_ref.double()
-        assert (ref - out.cpu().double()).abs().max() <= TOL[torch.bfloat16] * 2 * ref.abs().max()
-        for name, got, want in (("keys", k_gpu, k_ref), ("values", v_gpu, v_ref)):
-            d = (got.cpu().double() - want.double()).abs().max()
-            assert d <= TOL[torch.bfloat16] * want.double().abs().max(), f"{name} in the pages differ by {d}"
-            if not write:
-                assert torch.equal(got.cpu(), want), f"{name} were written although the layer only reads"
+    try:
+        for max_keys, passes in ((longest + 1, 0), ((longest // 1024 + 1) * 1024, 0), (longest + 1, 0), (longest + 1, 2),
+                                 ((longest // 1024 + 1) * 1024, 3), (longest + 1, 1000), (longest + 200, 1000)):
+            ops.attention_decode_fused_passes(passes)
+            k_gpu, v_gpu = k_pages.cuda(), v_pages.cuda()
+            out = torch.empty(B, H * hd, dtype=torch.bfloat16, device="cuda")
+            qkv_gpu = qkv.cuda()
+            assert ops.attention_decode_fused_ok(view(qkv_gpu), torch.bfloat16, H, KV, hd)
+            ops.attention_decode_fused(view(qkv_gpu), 0, H * hd, (H + KV) * hd, k_gpu, v_gpu, inv.cuda(), write, table.cuda(),
+                                       pos.cuda(), row_seq.cuda(), slots.cuda(), out, H, KV, hd, scale, window, max_keys)
+            ref = out_ref.double()
+            assert (ref - out.cpu().double()).abs().max() <= TOL[torch.bfloat16] * 2 * ref.abs().max()
+            for name, got, want in (("keys", k_gpu, k_ref), ("values", v_gpu, v_ref)):
+                d = (got.cpu().double() - want.double()).abs().max()
+                assert d <= TOL[torch.bfloat16] * want.double().abs().max(), f"{name} in the pages differ by {d}"
+                if not write:
+                    assert torch.equal(got.cpu(), want), f"{name} were written although the layer only reads"
+    finally:
+        ops.attention_decode_fused_passes(0)
     assert not ops.attention_decode_fused_ok(view(qkv_gpu), torch.bfloat16, H, KV, 80)
 
 

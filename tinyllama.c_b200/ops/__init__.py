@@ -36,6 +36,7 @@ _SIGNATURES = {
     "tlc_attention_decode_fused": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
                                    _i, _i, _i, _i, _f, _i, _i, _vp],
     "tlc_attention_decode_fused_ok": [_i, _i, _i],
+    "tlc_attention_decode_fused_passes": [_i],
     "tlc_attention_prefill": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp,
                               _i, _vp],
     "tlc_attention_prefill_chunks": [_i, _i, _i, _vp],
@@ -389,6 +390,12 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
           inv_freq.data_ptr(), 2 * inv_freq.numel(), int(bool(write_kv)), block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(), out.data_ptr(), part_o.data_ptr(),
           part_ml.data_ptr(), arrivals.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), int(max_keys), _stream())
+
+
+def attention_decode_fused_passes(passes: int) -> None:
+    """Fixes how many rounds of chunks a block of the fused single-token attention takes one after the
+    other (0: chosen from the grid); for tests of the running statistics."""
+    library().tlc_attention_decode_fused_passes(int(passes))
 
 
 DISABLE_SSD = bool(int(os.environ.get("TLC_DISABLE_SSD", "0")))
