@@ -125,6 +125,41 @@ def test_linear(a_dt, w_dt, o_dt, M, N, K):
             assert torch.equal(out_gpu.cpu()[:, N:], untouched), "linear wrote outside its columns"
 
 
+@pytest.mark.parametrize("splits", [0, 2, 3, 7])
+def test_linear_with_the_k_steps_of_a_tile_shared_among_blocks(splits):
+    """Batches of 33..128 rows times narrow matrices: several blocks share a tile's K-steps and the last to
+    arrive adds the shares.  Each product runs three times (the arrival counters come back to zero), and two
+    run at the same time on two streams (their scratch must not be shared)."""
+    g = gen(21)
+    try:
+        ops.linear_split_override(splits)
+        for M, N, K in ((64, 2048, 4096), (100, 200, 520), (40, 136, 264), (128, 1030, 1536)):
+            a = rnd(g, M, K, dtype=torch.bfloat16)
+            w = rnd(g, N, K, dtype=torch.bfloat16, scale=1 / math.sqrt(K))
+            cs, cb = 1 + rnd(g, N, scale=0.3), rnd(g, N)
+            for accumulate, scale, bias, o_dt in ((True, None, None, torch.float32), (False, cs, cb, torch.bfloat16),
+                                                  (True, cs, None, torch.float32)):
+                out_cpu = rnd(g, M, N, dtype=o_dt)
+                ops_plain.linear(a, w, ref := out_cpu.clone(), scale, bias, accumulate)
+                a_gpu, w_gpu = a.cuda(), w.cuda()
+                sc, bi = (None if scale is None else scale.cuda()), (None if bias is None else bias.cuda())
+                side = torch.cuda.Stream()
+                for rep in range(3):
+                    out1, out2 = out_cpu.cuda(), out_cpu.cuda()
+                    torch.cuda.synchronize()
+                    ops.linear(a_gpu, w_gpu, out1, sc, bi, accumulate)
+                    with torch.cuda.stream(side):
+                        ops.linear(a_gpu, w_gpu, out2, sc, bi, accumulate)
+                    torch.cuda.synchronize()
+                    ops.check_errors()
+                    for got in (out1, out2):
+                        err = (ref.double() - got.cpu().double()).abs().max().item()
+                        assert err <= TOL[o_dt] * ref.double().abs().max().item(), f"{M}x{N}x{K}, run {rep}: {err}"
+                    assert torch.equal(out1, out2), "two runs of the same product differ"
+    finally:
+        ops.linear_split_override(0)
+
+
 def _paged_setup(g, B, lens_total, KV, hd, dtype, n_slots=5, extra_pages=3):
     """Random slots and shuffled pages for sequences of the given total lengths."""
     pages_needed = [(n + 63) // 64 for n in lens_total]

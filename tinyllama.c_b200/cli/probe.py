@@ -7,7 +7,7 @@ plays both roles for this library:
     bin/probe decode  --batch 8 --layers 2 --prompt 512     three eager one-token steps (for ncu)
     bin/probe prefill --layers 2 --prompt 2048              one prompt, twice (for ncu)
     bin/probe prefill --batch 16 --unequal --prompt 2048    16 prompts of 64..2048 tokens together, twice
-    bin/probe linear  --rows 2048 --n 6704 --k 2048 [--accumulate] [--swiglu] [--bf16-out] [--tile 64|128|256]
+    bin/probe linear  --rows 2048 --n 6704 --k 2048 [--accumulate] [--swiglu] [--bf16-out] [--tile 64|128|256] [--split n]
     bin/probe kernels --batch 8                             every decode-step kernel, warm, in a CUDA graph
 
 Models are random, with the layer sizes of bench.py (--sizes 1.5B, 3B or 7B) and --layers layers.
@@ -96,6 +96,7 @@ def run_linear(args) -> None:
     from tinyllama_c_b200 import ops
     lib = ops.library()
     lib.tlc_linear_tile_override(args.tile)
+    lib.tlc_linear_split_override(args.split)
     M, N, K = args.rows, args.n, args.k
     a = torch.randn(M, K, device="cuda").bfloat16()
     w = (torch.randn(N, K, device="cuda") * K ** -0.5).bfloat16()      # outputs of order one, as in a model
@@ -106,8 +107,16 @@ def run_linear(args) -> None:
         ops.check_errors()
         return
     out = torch.zeros(M, N, dtype=torch.bfloat16 if args.bf16_out else torch.float32, device="cuda")
-    timeit(f"linear {M}x{N}x{K} tile={args.tile or 'auto'}", lambda: ops.linear(a, w, out, None, None, args.accumulate),
-           flops=2.0 * M * N * K, reps=20)
+    # few rows: the time is that of streaming the weights, so rotate over copies that together exceed the L2
+    ncopy = max(1, int(400e6 // (N * K * 2)) + 1) if M <= 128 else 1
+    ws = [w] + [w.clone() for _ in range(ncopy - 1)]
+    st = {"i": 0}
+
+    def fn():
+        ops.linear(a, ws[st["i"] % ncopy], out, None, None, args.accumulate)
+        st["i"] += 1
+    timeit(f"linear {M}x{N}x{K} tile={args.tile or 'auto'}", fn, nbytes=N * K * 2 if ncopy > 1 else None,
+           flops=2.0 * M * N * K, reps=max(20, ncopy * 2))
     ops.check_errors()
 
 
@@ -198,6 +207,7 @@ def main(argv=None) -> int:
     ap.add_argument("--accumulate", action="store_true")
     ap.add_argument("--unequal", action="store_true", help="prefill: --batch prompts of 64..--prompt tokens in one batch")
     ap.add_argument("--tile", type=int, default=0, choices=[0, 64, 128, 256])
+    ap.add_argument("--split", type=int, default=0, help="linear: blocks that share a tile's K-steps (0: chosen, 1: none)")
     ap.add_argument("--swiglu", action="store_true", help="linear: gate|up rows interleaved by 8, SwiGLU in the epilogue")
     ap.add_argument("--bf16-out", action="store_true", help="linear: bfloat16 output instead of float32")
     args = ap.parse_args(argv)

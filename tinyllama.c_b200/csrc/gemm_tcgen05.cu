@@ -22,6 +22,7 @@
 #include "common.cuh"
 #include "mbarrier.cuh"
 #include <cuda.h>
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
@@ -116,7 +117,8 @@ template <typename TO, int BN, int STAGES, bool SWIGLU>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
-                    const float* __restrict__ colbias, int accumulate, int M, int N, int K, ErrWords* err) {
+                    const float* __restrict__ colbias, int accumulate, int M, int N, int K, ErrWords* err,
+                    int splits, float* __restrict__ part, unsigned* __restrict__ arrivals) {
   // The set-up and the first weight tiles do not depend on the previous kernel of the stream: they go ahead of
   // the wait on it.  The loader waits before its first activation tile, the epilogue warps before they touch
   // `out`; the issuer reads shared memory only.
@@ -134,8 +136,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
+  // splits > 1: a tile's K-steps are shared by `splits` blocks; each leaves its partial accumulator in `part`
+  // [splits, M, N] and the last one to arrive (arrivals[tile * 4 + quarter], back at zero afterwards) adds
+  // them in order and finishes the tile.  Tile index = split * (tiles of the output) + output tile.
+  const int out_tiles = m_tiles * n_tiles;
+  const int total_tiles = out_tiles * splits;
   const int num_k = (K + BK - 1) / BK;
+  const int k_per = (num_k + splits - 1) / splits;     // every split has at least one step (the launcher sees to it)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -161,10 +168,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       int3 pending_a[STAGES];                          // activation tiles (stage, k, m) held back until then
       int n_pending = 0;
       const int my_tiles = (int)blockIdx.x < total_tiles ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-      const int first_run = my_tiles * num_k;          // stage fills this block issues in all
+      const int first_run = my_tiles * (num_k - (splits - 1) * k_per);   // stage fills this block issues at least
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
-        for (int k = 0; k < num_k; k++, it++) {
+        const int ot = tile % out_tiles, sp = tile / out_tiles;
+        const int m0 = (ot % m_tiles) * BM, n0 = (ot / m_tiles) * BN;
+        const int k_end = min(num_k, (sp + 1) * k_per);
+        for (int k = sp * k_per; k < k_end; k++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait(empty0 + 8 * s, ph ^ 1, err, 1);
@@ -200,7 +209,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_tmem = tmem + (uint32_t)(as * BN);
-        for (int k = 0; k < num_k; k++, it++) {
+        const int sp = tile / out_tiles;
+        const int k_begin = sp * k_per, k_end = min(num_k, (sp + 1) * k_per);
+        for (int k = k_begin; k < k_end; k++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait(full0 + 8 * s, ph, err, 2);
@@ -210,7 +221,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; kk++)
             umma(d_tmem, smem_desc(a_addr + kk * UMMA_K * 2), smem_desc(b_addr + kk * UMMA_K * 2), idesc,
-                 (k > 0 || kk > 0) ? 1u : 0u);
+                 (k > k_begin || kk > 0) ? 1u : 0u);
           umma_commit(empty0 + 8 * s);                 // the slot is free once these MMAs have read it
         }
         if (ok) umma_commit(acc_full0 + 8 * as);       // this tile's accumulator is complete
@@ -227,11 +238,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tlc_wait(out);                                     // `out` may still be read or written by the previous kernel
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
       const int as = local & 1;
-      const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+      const int ot = tile % out_tiles, sp = tile / out_tiles;
+      const int m0 = (ot % m_tiles) * BM, n0 = (ot / m_tiles) * BN;
       ok = mbar_wait(acc_full0 + 8 * as, (local >> 1) & 1, err, 3);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int mrow0 = m0 + quarter * 32;
+      const bool split = !SWIGLU && splits > 1;
+      if (split) {
+        // this block's share of the tile's sum goes to scratch; the warp that finds the other shares of its
+        // 32 rows already there adds them up and finishes the rows
+        const int m = mrow0 + lane;
+        const bool vec = (N & 3) == 0;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c++) {
+          const int nc0 = n0 + c * 32;
+          if (nc0 >= N) break;
+          uint32_t r[32];
+          tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN + c * 32), r);
+          if (m < M) {
+            float* dst = part + ((size_t)sp * M + m) * N + nc0;
+            if (vec && nc0 + 32 <= N) {
+#pragma unroll
+              for (int q = 0; q < 8; q++)
+                __stcg(reinterpret_cast<float4*>(dst) + q, make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                                        __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; j++) if (nc0 + j < N) __stcg(dst + j, __uint_as_float(r[j]));
+            }
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * as) : "memory");
+        __threadfence();
+        __syncwarp();
+        unsigned old = 0;
+        if (lane == 0) old = atomicInc(arrivals + (size_t)ot * 4 + quarter, (unsigned)(splits - 1));
+        old = __shfl_sync(0xffffffffu, old, 0);
+        if (old != (unsigned)(splits - 1)) continue;      // another block finishes these rows
+        __threadfence();
+      }
       const bool scaled = colscale != nullptr || colbias != nullptr;
       if (scaled) {
         // the tile's column scales and biases once into the warp's staging area: every lane needs all of them
@@ -248,7 +295,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int nc0 = n0 + c * 32;
         if (nc0 >= N) break;
         uint32_t r[32];
-        tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN + c * 32), r);
+        if (!split) {
+          tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * BN + c * 32), r);
+        } else {
+          // the shares of all splits, added in the order of the splits
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = 0.f;
+          const int m = mrow0 + lane;
+          if (m < M) {
+            const bool vec = (N & 3) == 0 && nc0 + 32 <= N;
+            for (int sx = 0; sx < splits; sx++) {
+              const float* src = part + ((size_t)sx * M + m) * N + nc0;
+              if (vec) {
+                float4 x[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) x[q] = __ldcg(reinterpret_cast<const float4*>(src) + q);
+#pragma unroll
+                for (int q = 0; q < 8; q++) { v[4 * q] += x[q].x; v[4 * q + 1] += x[q].y; v[4 * q + 2] += x[q].z; v[4 * q + 3] += x[q].w; }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) if (nc0 + j < N) v[j] += __ldcg(src + j);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 32; j++) r[j] = __float_as_uint(v[j]);
+        }
         if (SWIGLU) {
           // A lane holds 32 columns of its row: gates 0..7 | ups 8..15 | gates 16..23 | ups 24..31, i.e. 16
           // features whose gate and up are both in its registers.  It writes 16 consecutive values.
@@ -365,9 +438,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         __syncwarp();
       }
-      // hand the accumulator half back to the MMA issuer
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * as) : "memory");
+      // hand the accumulator half back to the MMA issuer (with splits that happened above)
+      if (!split) {
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * as) : "memory");
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -385,6 +460,15 @@ int g_sms = 148;
 ErrWords* g_err_dev = nullptr;   // device memory: the flag kernels read + where its host-visible copy lives
 int* g_err_host = nullptr;       // host-mapped word, written by a kernel on failure only
 std::mutex g_mu;
+// Scratch of the products that share a tile's K-steps among blocks: SPLIT_SLOTS launches in turn, so that
+// two such launches that run at the same time (the two mixers' output projections) never share a slot.
+constexpr int SPLIT_SLOTS = 8;
+constexpr size_t SPLIT_SLOT_BYTES = (size_t)8 << 20;       // partial sums of one launch: splits x M x N floats
+constexpr int SPLIT_SLOT_COUNTERS = 4096;                   // 4 per output tile
+float* g_part = nullptr;
+unsigned* g_part_arrivals = nullptr;                        // zero between launches
+std::atomic<unsigned> g_split_seq{0};
+int g_split_override = 0;                                   // test hook: 0 = choose; n = that many splits (1 = none)
 
 struct MapKey {
   const void* p; int rows, k, ld, box_rows;
@@ -434,6 +518,10 @@ int init_once() {
       cudaHostGetDevicePointer((void**)&host_dev_view, g_err_host, 0) != cudaSuccess ||
       cudaMalloc((void**)&g_err_dev, sizeof(ErrWords)) != cudaSuccess)
     return tlc_fail(-3, "linear: cannot allocate the error words");
+  if (cudaMalloc((void**)&g_part, SPLIT_SLOTS * SPLIT_SLOT_BYTES) != cudaSuccess ||
+      cudaMalloc((void**)&g_part_arrivals, SPLIT_SLOTS * SPLIT_SLOT_COUNTERS * sizeof(unsigned)) != cudaSuccess ||
+      cudaMemset(g_part_arrivals, 0, SPLIT_SLOTS * SPLIT_SLOT_COUNTERS * sizeof(unsigned)) != cudaSuccess)
+    return tlc_fail(-3, "linear: cannot allocate the scratch of split products");
   *g_err_host = 0;
   ErrWords init{0, host_dev_view};
   if (cudaMemcpy(g_err_dev, &init, sizeof(init), cudaMemcpyHostToDevice) != cudaSuccess)
@@ -462,14 +550,34 @@ int get_map(const void* p, int rows, int k, int ld, int box_rows, CUtensorMap* o
   return 0;
 }
 
+// How many blocks share the K-steps of a tile: more than one when the output has one row of tiles and too few
+// of them to occupy the GPU (a batch of 33..128 rows times a narrow matrix) and K is long: a split costs a
+// round trip through scratch and an arrival counter, about 5 us, so every split keeps at least 32 K-steps
+// (64 x 3072 x 12288: 62 us in one piece, 34 us in three; 64 x 2048 x 4096: 23 us, and 18 us in four, but
+// 12 us with the weight-streaming kernel).
+int pick_splits(int M, int N, int K, int bn) {
+  if (M > BM) return 1;
+  const int tiles = (N + bn - 1) / bn, num_k = (K + BK - 1) / BK;
+  int s = g_split_override ? g_split_override : (tiles * 2 > g_sms ? 1 : std::min(std::min(g_sms / tiles, num_k / 32), 16));
+  s = std::min(s, num_k);
+  while (s > 1 && ((size_t)s * M * N * sizeof(float) > SPLIT_SLOT_BYTES || (s - 1) * ((num_k + s - 1) / s) >= num_k)) s--;
+  if (tiles * 4 > SPLIT_SLOT_COUNTERS) s = 1;
+  return std::max(s, 1);
+}
+
 template <typename TO, int BN, int STAGES, bool SWIGLU = false>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, const float* colscale, const float* colbias,
            int accumulate, int M, int N, int K, cudaStream_t stream) {
   using S = Smem<BN, STAGES>;
   auto kern = gemm_tcgen05_kernel<TO, BN, STAGES, SWIGLU>;
-  const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  const int splits = SWIGLU ? 1 : pick_splits(M, N, K, BN);
+  const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * splits;
+  const unsigned slot = splits > 1 ? g_split_seq.fetch_add(1) % SPLIT_SLOTS : 0;
+  float* part = g_part + slot * (SPLIT_SLOT_BYTES / sizeof(float));
+  unsigned* arrivals = g_part_arrivals + slot * SPLIT_SLOT_COUNTERS;
   dim3 grid(tiles < g_sms ? tiles : g_sms);
-  tlc_launch(kern, dim3(grid), dim3(THREADS), S::TOTAL, stream, ma, mb, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, g_err_dev);
+  tlc_launch(kern, dim3(grid), dim3(THREADS), S::TOTAL, stream, ma, mb, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, g_err_dev,
+             splits, part, arrivals);
   TLC_CHECK_LAUNCH("linear(tcgen05)");
   return 0;
 }
@@ -493,6 +601,8 @@ extern "C" int tlc_linear_init() { return init_once(); }
 // Test hook: 0 = choose the tile width from the sizes; 64, 128 or 256 = force it.
 static int g_tile_override = 0;
 extern "C" void tlc_linear_tile_override(int bn) { g_tile_override = bn; }
+// Test hook: 0 = choose how many blocks share a tile's K-steps; n = that many where the sizes allow (1 = none).
+extern "C" void tlc_linear_split_override(int n) { g_split_override = n; }
 
 // Width of the output tile (rows are always 128).  A block works through ceil(tiles / SMs) tiles one after the
 // other, and a tile's time grows with its width, though less than in proportion: per output column a tile of
@@ -563,9 +673,10 @@ extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, in
   if (M == 0 || N == 0) return 0;
   // Up to 32 rows the weight-streaming kernel is always best.  From 33 to 64 rows it re-reads the
   // activations once per 16 output columns, which only pays while the tiled kernel would have too
-  // few tiles to keep the GPU busy (narrow outputs).
+  // few tiles to keep the GPU busy (narrow outputs) and too few K-steps to share among blocks.
   const bool tiled_ok = M >= min_rows_for_tensor_cores && tlc_linear_tcgen05_ok(a_dtype, lda, a, w_dtype, ldw, w, K);
-  if (tlc_linear_skinny_ok(a_dtype, lda, a, w_dtype, ldw, w, M, K) && (M <= 32 || N <= 3072 || !tiled_ok)) {
+  const bool narrow = N <= 3072 && K < 8192;
+  if (tlc_linear_skinny_ok(a_dtype, lda, a, w_dtype, ldw, w, M, K) && (M <= 32 || narrow || !tiled_ok)) {
     TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N,
                 K, lda, ldw, ldo);
     return tlc_linear_skinny(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, accumulate, M, N, K, stream);

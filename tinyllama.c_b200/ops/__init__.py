@@ -220,6 +220,12 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
 TENSOR_CORE_MIN_ROWS = int(os.environ.get("TLC_TENSOR_CORE_MIN_ROWS", "33"))
 
 
+def linear_split_override(splits: int) -> None:
+    """Fixes how many blocks share the K-steps of a tile of the tensor-core product (0: chosen from the
+    sizes, 1: none); for tests."""
+    library().tlc_linear_split_override(int(splits))
+
+
 def linear_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale: Optional[torch.Tensor] = None,
                   colbias: Optional[torch.Tensor] = None) -> None:
     """out[M, F] = silu(gate) * up with gate | up = (a w^T) * colscale + colbias, the 2F rows of w in
