@@ -215,8 +215,13 @@ def attention_mixer(n, W, pre, cfg, d, positions, rnd=_same):
     return linear(rnd(o), W[pre + "self_attn.o_proj.weight"], W.get(pre + "self_attn.o_proj.bias"))
 
 
-def mamba2_mixer(n, W, pre, cfg, d, rnd=_same):
+def mamba2_mixer(n, W, pre, cfg, d, rnd=_same, round_at_scale=1.0):
     """in_proj -> conv -> scan -> gate/norm -> out_proj (falcon_h1.c:342-368).
+
+    round_at_scale: where a rounding function models a bfloat16 engine, the input of out_proj is
+    rounded after a multiplication by this number, which is divided out again afterwards (the
+    engine applies a part of the output multiplier in front of the product); exact arithmetic
+    does not see it.
 
     The in_proj row order is z | x | B | C | dt (cpu_op.c:849, 865, 925-929).  The five
     ssm_multipliers scale those slices after the bias (not in the reference)."""
@@ -236,7 +241,10 @@ def mamba2_mixer(n, W, pre, cfg, d, rnd=_same):
     y = gated_norm(y, z, W.get(pre + "mamba.norm.weight"), cfg["rms_norm_eps"], G,
                    bool(_get(cfg, "mamba_rms_norm", True)) and (pre + "mamba.norm.weight") in W,
                    bool(_get(cfg, "mamba_norm_before_gate", False)))
-    return linear(rnd(y), W[pre + "mamba.out_proj.weight"], W.get(pre + "mamba.out_proj.bias"))
+    if rnd is not _same and round_at_scale != 1.0:
+        y = rnd(y * round_at_scale) / round_at_scale
+    return linear(rnd(y) if rnd is _same or round_at_scale == 1.0 else y, W[pre + "mamba.out_proj.weight"],
+                  W.get(pre + "mamba.out_proj.bias"))
 
 
 def swiglu_mlp(hn, W, pre, cfg, rnd=_same):
@@ -256,8 +264,13 @@ def block(x, W, layer, cfg, d, positions, rnd=_same):
     n = rnd(rms_norm(x, W[pre + "input_layernorm.weight"], eps))
     a = attention_mixer(n * _get(cfg, "attention_in_multiplier", 1.0), W, pre, cfg, d, positions, rnd)
     a = a * _get(cfg, "attention_out_multiplier", 1.0)
-    m = mamba2_mixer(n * _get(cfg, "ssm_in_multiplier", 1.0), W, pre, cfg, d, rnd)
-    m = m * _get(cfg, "ssm_out_multiplier", 1.0)
+    # An engine that runs o_proj and out_proj as one product has one output scale for both, the attention's,
+    # and multiplies the Mamba activations by the ratio of the two before they are rounded; it does so where
+    # both input widths are multiples of 8.
+    a_out, m_out = _get(cfg, "attention_out_multiplier", 1.0), _get(cfg, "ssm_out_multiplier", 1.0)
+    ratio = m_out / a_out if a_out != 0 and (d["H"] * d["hd"]) % 8 == 0 and d["Di"] % 8 == 0 else 1.0
+    m = mamba2_mixer(n * _get(cfg, "ssm_in_multiplier", 1.0), W, pre, cfg, d, rnd, ratio)
+    m = m * m_out
     x = (x + a) + m                                            # falcon_h1.c:372-375
     hn = rnd(rms_norm(x, W[pre + "pre_ff_layernorm.weight"], eps))
     return x + swiglu_mlp(hn, W, pre, cfg, rnd)

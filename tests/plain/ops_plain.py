@@ -31,7 +31,7 @@ def rmsnorm(x, weight, eps, out, rows=None):
     out.copy_((xs * s * _f(weight)).to(out.dtype))
 
 
-def gated_rmsnorm(y, z, weight, eps, n_groups, norm_before_gate, out):
+def gated_rmsnorm(y, z, weight, eps, n_groups, norm_before_gate, out, out_scale=1.0):
     T, Di = y.shape
     y, z = _f(y), _f(z)
     gate = z / (1.0 + torch.exp(-z))
@@ -45,7 +45,7 @@ def gated_rmsnorm(y, z, weight, eps, n_groups, norm_before_gate, out):
             s = 1.0 / torch.sqrt((v * v).sum(-1, keepdim=True) / gs + eps)
             return (v * s).reshape(T, Di) * _f(weight)
         res = norm(y) * gate if norm_before_gate else norm(y * gate)
-    out.copy_(res.to(out.dtype))
+    out.copy_((res * out_scale).to(out.dtype))
 
 
 def _gate_up(gate_up, interleaved):

@@ -325,6 +325,60 @@ def test_attention_of_single_token_steps_in_one_kernel(H, KV, hd, rope, window, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,KV,hd", [(4, 2, 64), (8, 2, 128), (6, 3, 24)])
+def test_outputs_into_columns_of_a_wider_buffer(dtype, H, KV, hd):
+    """Attention (every kernel of it) and the gated norm write into a range of the columns of a wider
+    buffer exactly what they write into a dense output, and nothing beside it; the gated norm's
+    output scale multiplies its result."""
+    g = gen(31)
+    dt = DT[dtype]
+    W, off = H * hd, 40
+    wide = lambda T: torch.full((T, W + 104), 7.0, dtype=dt, device="cuda")
+
+    def both(run, T):
+        dense, buf = torch.empty(T, W, dtype=dt, device="cuda"), wide(T)
+        run(dense)
+        run(buf[:, off:off + W])
+        torch.cuda.synchronize()
+        assert torch.equal(buf[:, off:off + W], dense)
+        assert bool((buf[:, :off] == 7.0).all()) and bool((buf[:, off + W:] == 7.0).all()), "wrote outside its columns"
+        return dense
+
+    scale = 1.0 / math.sqrt(hd)
+    # prompts (the tiled kernel for bfloat16 heads of 64 and 128, whole and in pieces; else a warp per row and head)
+    starts, lens = [0, 130, 5], [700, 70, 65]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    slots, table, k_pages, v_pages = _paged_setup(g, 3, [s + n for s, n in zip(starts, lens)], KV, hd, dt, n_slots=4)
+    T = sum(lens)
+    q = rnd(g, T, W, dtype=dt).cuda()
+    dev = [t.cuda() for t in (k_pages, v_pages, table, pos, row_seq, slots, cu, start_pos)]
+    for max_keys in (0, 700):
+        both(lambda out: ops.attention(q, dev[0], dev[1], dev[2], dev[3], dev[4], dev[5], out, H, KV, hd, scale, 0, 0,
+                                       dev[6], dev[7], max_keys), T)
+    # single-token steps: split keys with a merge, and the one-kernel form
+    starts, lens = [699, 199, 69], [1, 1, 1]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    pos, row_seq = pos.cuda(), row_seq.cuda()
+    q1 = rnd(g, 3, W, dtype=dt).cuda()
+    both(lambda out: ops.attention(q1, dev[0], dev[1], dev[2], pos, row_seq, dev[5], out, H, KV, hd, scale, 0, 700), 3)
+    qkv = rnd(g, 3, (H + 2 * KV) * hd).cuda()
+    inv = (1.0 / torch.pow(torch.tensor(1e4, dtype=torch.float64), torch.arange(hd // 2, dtype=torch.float64) * 2 / hd)).float().cuda()
+    if ops.attention_decode_fused_ok(qkv, dt, H, KV, hd):
+        for max_keys in (700, 128):          # several blocks a row with a merge; one block a row
+            if max_keys == 128:
+                pos = torch.tensor([100, 90, 69], dtype=torch.int32, device="cuda")
+            both(lambda out: ops.attention_decode_fused(qkv, 0, H * hd, (H + KV) * hd, dev[0], dev[1], inv, False, dev[2],
+                                                        pos, row_seq, dev[5], out, H, KV, hd, scale, 0, max_keys), 3)
+    # gated norm: vector and scalar kernels, with and without weights, scaled
+    y = rnd(g, 5, W, scale=2.0).cuda()
+    for zdt, w in ((torch.float32, 1 + rnd(g, W, scale=0.2).cuda()), (dt, 1 + rnd(g, W, scale=0.2).cuda()), (dt, None)):
+        z = rnd(g, 5, W, dtype=zdt).cuda()
+        plain = both(lambda out: ops.gated_rmsnorm(y, z, w, 1e-5, 2, False, out), 5)
+        scaled = both(lambda out: ops.gated_rmsnorm(y, z, w, 1e-5, 2, False, out, 0.75), 5)
+        assert (scaled.double() - 0.75 * plain.double()).abs().max() <= TOL[dt] * 2 * plain.double().abs().max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("Di,G,N,K,Hs,bias", [(48, 1, 16, 4, 3, True), (144, 2, 32, 3, 6, False), (40, 1, 8, 2, 5, True)])
 def test_mamba_conv(dtype, Di, G, N, K, Hs, bias):
     g = gen(7)

@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(128)
 attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                       const int* __restrict__ block_table, int max_pages, const int* __restrict__ positions,
                       const int* __restrict__ row_seq, const int* __restrict__ slots, T* __restrict__ out, int H, int KV,
-                      int hd, float scale, int window) {
+                      int hd, float scale, int window, int out_ld) {
   tlc_pdl(q, k_pages, v_pages, out);
   extern __shared__ float qs_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,7 +133,7 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
     m = m_new;
   }
   const float inv = 1.0f / l;
-  T* o = out + ((size_t)t * H + h) * hd;
+  T* o = out + (size_t)t * out_ld + (size_t)h * hd;
 #pragma unroll
   for (int i = 0; i < ATT_MAXD; i++) {
     const int d = lane + 32 * i;
@@ -144,15 +144,16 @@ attention_warp_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, co
 extern "C" int tlc_attention(const void* q, int dtype, const void* k_pages, const void* v_pages,
                              const int* block_table, int max_pages, const int* positions, const int* row_seq,
                              const int* slots, void* out, int T, int H, int KV, int hd, float scale, int window,
-                             cudaStream_t stream) {
+                             int out_ld, cudaStream_t stream) {
   if (T == 0) return 0;
+  if (out_ld <= 0) out_ld = H * hd;                      // elements between rows of out (0: dense)
   TLC_REQUIRE(KV > 0 && H % KV == 0, "attention: %d heads are not a multiple of %d key/value heads", H, KV);
   TLC_REQUIRE(hd <= 32 * ATT_MAXD, "attention: head size %d exceeds the kernel's limit of %d", hd, 32 * ATT_MAXD);
   dim3 grid(T, (H + 3) / 4);
   const size_t smem = (size_t)4 * hd * sizeof(float);
   TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(attention_warp_kernel<TT>, dim3(grid), dim3(128), smem, stream, 
       (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, (TT*)out,
-      H, KV, hd, scale, window));
+      H, KV, hd, scale, window, out_ld));
   TLC_CHECK_LAUNCH("attention");
   return 0;
 }
@@ -414,9 +415,10 @@ attention_decode_partial_vec_kernel(const __nv_bfloat16* __restrict__ q, const _
 
 template <typename T>
 __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                              T* __restrict__ out, int hd, int n_splits) {
+                                              T* __restrict__ out, int hd, int n_splits, int H, int out_ld) {
   tlc_pdl(part_o, part_ml, out);
   const size_t th = blockIdx.x;                       // row * H + head
+  T* orow = out + (th / H) * (size_t)out_ld + (th % H) * (size_t)hd;
   const float* ml = part_ml + th * n_splits * 2;
   float m = -INFINITY;
   for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
@@ -427,7 +429,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
     float acc = 0.f;
     for (int s = 0; s < n_splits; s++)
       if (ml[2 * s + 1] > 0.f) acc = fmaf(part_o[(th * n_splits + s) * hd + d], expf(ml[2 * s] - m), acc);
-    out[th * hd + d] = from_f32<T>(acc * inv);
+    orow[d] = from_f32<T>(acc * inv);
   }
 }
 
@@ -435,8 +437,9 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ part_o, 
 extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_pages, const void* v_pages,
                                     const int* block_table, int max_pages, const int* positions, const int* row_seq,
                                     const int* slots, void* out, float* part_o, float* part_ml, int T, int H, int KV,
-                                    int hd, float scale, int window, int max_keys, cudaStream_t stream) {
+                                    int hd, float scale, int window, int max_keys, int out_ld, cudaStream_t stream) {
   if (T == 0) return 0;
+  if (out_ld <= 0) out_ld = H * hd;                      // elements between rows of out (0: dense)
   TLC_REQUIRE(KV > 0 && H % KV == 0, "attention: %d heads are not a multiple of %d key/value heads", H, KV);
   TLC_REQUIRE(H / KV <= DEC_MAXG, "attention(decode): %d query heads per key/value head exceed the kernel's limit of %d", H / KV, DEC_MAXG);
   TLC_REQUIRE(KV <= 65535, "attention(decode): too many key/value heads (%d)", KV);
@@ -456,7 +459,7 @@ extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_page
         tlc_launch(attention_decode_partial_vec_kernel<128>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
       else
         tlc_launch(attention_decode_partial_vec_kernel<256>, dim3(grid), dim3(DEC_KEYS), vsmem, stream, qp, kp, vp, block_table, max_pages, positions, row_seq, slots, part_o, part_ml, H, KV, scale, window, n_splits);
-      tlc_launch(attention_decode_merge_kernel<__nv_bfloat16>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits);
+      tlc_launch(attention_decode_merge_kernel<__nv_bfloat16>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (__nv_bfloat16*)out, hd, n_splits, H, out_ld);
       TLC_CHECK_LAUNCH("attention(decode)");
       return 0;
     }
@@ -465,7 +468,7 @@ extern "C" int tlc_attention_decode(const void* q, int dtype, const void* k_page
     tlc_launch(attention_decode_partial_kernel<TT>, dim3(grid), dim3(DEC_KEYS), smem, stream, 
         (const TT*)q, (const TT*)k_pages, (const TT*)v_pages, block_table, max_pages, positions, row_seq, slots, part_o,
         part_ml, H, KV, hd, scale, window, n_splits);
-    tlc_launch(attention_decode_merge_kernel<TT>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (TT*)out, hd, n_splits);
+    tlc_launch(attention_decode_merge_kernel<TT>, dim3(T * H), dim3(128), 0, stream, part_o, part_ml, (TT*)out, hd, n_splits, H, out_ld);
   });
   TLC_CHECK_LAUNCH("attention(decode)");
   return 0;
@@ -509,5 +512,5 @@ extern "C" int tlc_attention_decode_no_alloc(const void* q, int dtype, const voi
   float* part_o = g_decode_scratch_addr[dev];
   float* part_ml = part_o + (size_t)T * H * n_splits * hd;
   return tlc_attention_decode(q, dtype, k_pages, v_pages, block_table, max_pages, positions, row_seq, slots, out, part_o,
-                              part_ml, T, H, KV, hd, scale, window, max_keys, stream);
+                              part_ml, T, H, KV, hd, scale, window, max_keys, 0, stream);
 }

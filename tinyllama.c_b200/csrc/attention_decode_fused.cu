@@ -85,7 +85,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
                             const int* __restrict__ row_seq, const int* __restrict__ slots, float* __restrict__ part_o,
                             float* __restrict__ part_ml, unsigned* __restrict__ arrivals,
                             __nv_bfloat16* __restrict__ out, int H, int KV, float scale, int window, int n_splits,
-                            int passes) {
+                            int passes, int out_ld) {
   // Keys and values of earlier positions were stored by earlier steps and are fetched before the
   // wait on the previous kernel; the row's own projection is read after it.
   asm volatile("griddepcontrol.launch_dependents;");
@@ -328,7 +328,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
       }
       const size_t th = (size_t)t * H + (size_t)g * G + hg;
       if (n_splits == 1) {
-        out[th * HD + d] = __float2bfloat16_rn(o * (1.0f / l));
+        out[(size_t)t * out_ld + ((size_t)g * G + hg) * HD + d] = __float2bfloat16_rn(o * (1.0f / l));
       } else {
         part_o[(th * n_splits + split) * HD + d] = o;
         if (d == 0) { ml[(size_t)hg * n_splits * 2] = M; ml[(size_t)hg * n_splits * 2 + 1] = l; }
@@ -346,7 +346,7 @@ attention_decode_fused_kernel(const float* __restrict__ qkv, int ld, int q_off, 
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  attention_merge_splits<HD, FM_NT>(part_o, part_ml, out, reinterpret_cast<float*>(smraw), smem_floats, t, g, G, H, n_splits);
+  attention_merge_splits<HD, FM_NT>(part_o, part_ml, out, reinterpret_cast<float*>(smraw), smem_floats, t, g, G, H, n_splits, out_ld);
 }
 
 int g_fused_passes = 0;       // > 0: rounds a block takes, for tests (0: chosen from the grid)
@@ -382,8 +382,9 @@ extern "C" int tlc_attention_decode_fused(const float* qkv, int ld, int q_off, i
                                         const int* block_table, int max_pages, const int* positions,
                                         const int* row_seq, const int* slots, void* out, float* part_o, float* part_ml,
                                         unsigned* arrivals, int T, int H, int KV, int hd, float scale, int window,
-                                        int max_keys, cudaStream_t stream) {
+                                        int max_keys, int out_ld, cudaStream_t stream) {
   if (T == 0) return 0;
+  if (out_ld <= 0) out_ld = H * hd;                      // elements between rows of out (0: dense)
   TLC_REQUIRE(tlc_attention_decode_fused_ok(H, KV, hd), "attention(decode, fused): %d heads, %d key/value heads of size %d are outside the kernel's range", H, KV, hd);
   TLC_REQUIRE(rope_dim % 2 == 0 && rope_dim >= 0 && rope_dim <= hd, "attention(decode, fused): rotated width %d must be even and at most head_dim %d", rope_dim, hd);
   TLC_REQUIRE(max_keys >= 1, "attention(decode, fused): %d keys", max_keys);
@@ -412,7 +413,7 @@ extern "C" int tlc_attention_decode_fused(const float* qkv, int ld, int q_off, i
 #define TLC_FM_LAUNCH(HDV, CKV, STV)                                                                                   \
   e = launch_fused<HDV, CKV, STV>(grid, passes, stream, qkv, ld, q_off, k_off, v_off, kp, vp, inv_freq, rope_dim, write_kv, \
                                 block_table, max_pages, positions, row_seq, slots, part_o, part_ml, arrivals, op, H, KV, \
-                                scale, window, n_splits, passes)
+                                scale, window, n_splits, passes, out_ld)
   if (hd == 64) TLC_FM_LAUNCH(64, 32, 4);
   else if (hd == 128) TLC_FM_LAUNCH(128, 32, 2);
   else TLC_FM_LAUNCH(256, 16, 2);

@@ -52,7 +52,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                          const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int H, int KV,
                          float scale_log2, int window, int chunk_tiles, int n_chunks_max, float* __restrict__ part_o,
-                         float* __restrict__ part_ml) {
+                         float* __restrict__ part_ml, int out_ld) {
   tlc_pdl(q, k_pages, v_pages, out, part_o, part_ml);
   constexpr int CH = HD / 8;                  // 16-byte chunks per row
   constexpr int TILE_BYTES = FA_BN * HD * 2;
@@ -246,7 +246,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     const int lr = warp * 16 + gq + 8 * r;
     if (lr < rows) {
       const float inv = 1.0f / l_run[r];
-      __nv_bfloat16* orow = out + ((size_t)(t0 + i0 + lr) * H + h) * HD;
+      __nv_bfloat16* orow = out + (size_t)(t0 + i0 + lr) * out_ld + (size_t)h * HD;
 #pragma unroll
       for (int j = 0; j < HD / 8; j++)
         *reinterpret_cast<uint32_t*>(orow + j * 8 + 2 * tq) = pack_bf16(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(128)
 attention_prefill_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                const int* __restrict__ cu_seqlens, const int* __restrict__ row_seq,
                                const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int H, int hd,
-                               float scale_log2, int window, int chunk_tiles, int n_chunks_max) {
+                               float scale_log2, int window, int chunk_tiles, int n_chunks_max, int out_ld) {
   tlc_pdl(part_o, part_ml, out);
   const int t = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (h >= H) return;
@@ -304,7 +304,7 @@ attention_prefill_merge_kernel(const float* __restrict__ part_o, const float* __
     uint2 o2;
     o2.x = pack_bf16(acc.x * inv, acc.y * inv);
     o2.y = pack_bf16(acc.z * inv, acc.w * inv);
-    *reinterpret_cast<uint2*>(out + ((size_t)t * H + h) * hd + d) = o2;
+    *reinterpret_cast<uint2*>(out + (size_t)t * out_ld + (size_t)h * hd + d) = o2;
   }
 }
 
@@ -344,8 +344,10 @@ extern "C" int tlc_attention_prefill(const void* q, const void* k_pages, const v
                                      int max_pages, const int* cu_seqlens, const int* slots, const int* start_pos,
                                      void* out, int n_seqs, int n_tiles_bound, int H, int KV, int hd, float scale,
                                      int window, int max_tiles, const int* row_seq, float* part_o, float* part_ml, int T,
-                                     cudaStream_t stream) {
+                                     int out_ld, cudaStream_t stream) {
   if (n_seqs == 0 || n_tiles_bound == 0) return 0;
+  if (out_ld <= 0) out_ld = H * hd;                      // elements between rows of out (0: dense)
+  TLC_REQUIRE(out_ld % 4 == 0, "attention(prefill): rows of the output must start on 8-byte boundaries (stride %d)", out_ld);
   TLC_REQUIRE(KV > 0 && H % KV == 0, "attention: %d heads are not a multiple of %d key/value heads", H, KV);
   TLC_REQUIRE(H <= 65535, "attention(prefill): too many heads (%d)", H);
   int chunk_tiles = 1;
@@ -358,15 +360,15 @@ extern "C" int tlc_attention_prefill(const void* q, const void* k_pages, const v
   const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
   const int smem = (FA_BM + 4 * FA_BN) * hd * 2;
   if (hd == 64)
-    tlc_launch(attention_prefill_kernel<64>, dim3(grid), dim3(128), smem, stream, qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window, chunk_tiles, n_chunks, part_o, part_ml);
+    tlc_launch(attention_prefill_kernel<64>, dim3(grid), dim3(128), smem, stream, qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window, chunk_tiles, n_chunks, part_o, part_ml, out_ld);
   else if (hd == 128)
-    tlc_launch(attention_prefill_kernel<128>, dim3(grid), dim3(128), smem, stream, qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window, chunk_tiles, n_chunks, part_o, part_ml);
+    tlc_launch(attention_prefill_kernel<128>, dim3(grid), dim3(128), smem, stream, qp, kp, vp, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, n_seqs, H, KV, scale_log2, window, chunk_tiles, n_chunks, part_o, part_ml, out_ld);
   else
     return tlc_fail(-1, "attention(prefill): head size %d is not built (64 and 128 are)", hd);
   if (n_chunks > 1)
     tlc_launch(attention_prefill_merge_kernel, dim3(T, (H + 3) / 4), dim3(128), 0, stream, (const float*)part_o,
                (const float*)part_ml, cu_seqlens, row_seq, start_pos, (__nv_bfloat16*)out, H, hd, scale_log2, window,
-               chunk_tiles, n_chunks);
+               chunk_tiles, n_chunks, out_ld);
   TLC_CHECK_LAUNCH("attention(prefill)");
   return 0;
 }

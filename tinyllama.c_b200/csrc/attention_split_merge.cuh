@@ -5,12 +5,13 @@
 #pragma once
 #include "common.cuh"
 
-// part_o [T, H, n_splits, HD], part_ml [T, H, n_splits, 2]; sh: the block's dynamic shared memory of
-// smem_floats floats (free by now); NT threads.  All threads of the block call it.
+// part_o [T, H, n_splits, HD], part_ml [T, H, n_splits, 2]; out: rows of out_ld elements, head h at h * HD;
+// sh: the block's dynamic shared memory of smem_floats floats (free by now); NT threads.  All threads of
+// the block call it.
 template <int HD, int NT>
 __device__ __forceinline__ void attention_merge_splits(const float* part_o, const float* part_ml, __nv_bfloat16* out,
                                                        float* sh, int smem_floats, int t, int g, int G, int H,
-                                                       int n_splits) {
+                                                       int n_splits, int out_ld) {
   const int tid = threadIdx.x, lane = tid & 31, wp = tid >> 5;
   constexpr int NW = NT / 32;
   if (2 * G * n_splits <= smem_floats) {
@@ -50,7 +51,7 @@ __device__ __forceinline__ void attention_merge_splits(const float* part_o, cons
         for (int u = 0; u < 8; u++) { const float w = e[2 * (s + u)]; acc = w != 0.f ? fmaf(v[u], w, acc) : acc; }
       }
       for (; s < n_splits; s++) { const float w = e[2 * s]; const float v = __ldcg(po + (size_t)s * HD); acc = w != 0.f ? fmaf(v, w, acc) : acc; }
-      out[th * HD + d] = __float2bfloat16_rn(acc);
+      out[(size_t)t * out_ld + ((size_t)g * G + hg) * HD + d] = __float2bfloat16_rn(acc);
     }
     return;
   }
@@ -71,7 +72,7 @@ __device__ __forceinline__ void attention_merge_splits(const float* part_o, cons
       for (int s = 0; s < n_splits; s++)
         if (__ldcg(mlh + 2 * s + 1) > 0.f)
           acc = fmaf(__ldcg(part_o + (th * n_splits + s) * HD + d), expf(__ldcg(mlh + 2 * s) - m), acc);
-      out[th * HD + d] = __float2bfloat16_rn(acc * inv);
+      out[(size_t)t * out_ld + ((size_t)g * G + hg) * HD + d] = __float2bfloat16_rn(acc * inv);
     }
   }
 }

@@ -159,20 +159,21 @@ extern "C" int tlc_rmsnorm(const float* x, const int* rows, const float* w, floa
 }
 
 // ---- gate and grouped RMSNorm of the scan output ---------------------------------------
-// y [T, Di] 32-bit; z a strided slice of the input projection; one block per (row, group).
+// y [T, Di] 32-bit; z a strided slice of the input projection; out rows of out_ld elements, the whole
+// result times out_scale; one block per (row, group).
 template <typename TZ, typename TO>
 __global__ void __launch_bounds__(256)
 gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int ldz,
                                      const float* __restrict__ w, float eps, int Di, int gs, int norm_before_gate,
-                                     TO* __restrict__ out) {
+                                     TO* __restrict__ out, int out_ld, float out_scale) {
   tlc_pdl(y, z, out);
   __shared__ float red[33];
   const int t = blockIdx.x, g = blockIdx.y;
   const float* yr = y + (size_t)t * Di + (size_t)g * gs;
   const TZ* zr = z + (size_t)t * ldz + (size_t)g * gs;
-  TO* o = out + (size_t)t * Di + (size_t)g * gs;
+  TO* o = out + (size_t)t * out_ld + (size_t)g * gs;
   if (w == nullptr) {                                   // no norm: y * silu(z)
-    for (int d = threadIdx.x; d < gs; d += blockDim.x) o[d] = from_f32<TO>(yr[d] * silu_f(to_f32(zr[d])));
+    for (int d = threadIdx.x; d < gs; d += blockDim.x) o[d] = from_f32<TO>(yr[d] * silu_f(to_f32(zr[d])) * out_scale);
     return;
   }
   const float* wg = w + (size_t)g * gs;
@@ -193,7 +194,7 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int 
       ss += v[i] * v[i];
     }
     ss = block_sum(ss, red);
-    const float s = 1.0f / sqrtf(ss / (float)gs + eps);
+    const float s = out_scale / sqrtf(ss / (float)gs + eps);
 #pragma unroll
     for (int i = 0; i < RMS_MAX_PER_THREAD; i++) {
       const int d = threadIdx.x + i * 256;
@@ -207,7 +208,7 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int 
     ss += v * v;
   }
   ss = block_sum(ss, red);
-  const float s = 1.0f / sqrtf(ss / (float)gs + eps);
+  const float s = out_scale / sqrtf(ss / (float)gs + eps);
   for (int d = threadIdx.x; d < gs; d += blockDim.x) {
     const float gate = silu_f(to_f32(zr[d]));
     float v = yr[d];
@@ -221,7 +222,8 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int 
 template <typename TO, int NT, int PT>
 __global__ void __launch_bounds__(NT)
 gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ z, int ldz, const float* __restrict__ w,
-                         float eps, int Di, int gs, int norm_before_gate, TO* __restrict__ out) {
+                         float eps, int Di, int gs, int norm_before_gate, TO* __restrict__ out, int out_ld,
+                         float out_scale) {
   asm volatile("griddepcontrol.launch_dependents;");
   __shared__ float red[33];
   const int t = blockIdx.x, g = blockIdx.y;
@@ -250,8 +252,8 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ 
     ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
   }
   ss = block_sum(ss, red);
-  const float s = 1.0f / sqrtf(ss / (float)gs + eps);
-  TO* o = out + (size_t)t * Di + (size_t)g * gs;
+  const float s = out_scale / sqrtf(ss / (float)gs + eps);
+  TO* o = out + (size_t)t * out_ld + (size_t)g * gs;
 #pragma unroll
   for (int i = 0; i < PT; i++) {
     const int c = threadIdx.x + i * NT;
@@ -266,25 +268,26 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ 
 }
 
 extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int ldz, const float* w, float eps, int T,
-                                 int Di, int n_groups, int norm_before_gate, void* out, int out_dtype,
-                                 cudaStream_t stream) {
+                                 int Di, int n_groups, int norm_before_gate, void* out, int out_dtype, int out_ld,
+                                 float out_scale, cudaStream_t stream) {
   if (T == 0) return 0;
+  if (out_ld <= 0) out_ld = Di;                          // elements between rows of out (0: dense)
   TLC_REQUIRE(n_groups > 0 && Di % n_groups == 0, "gated_rmsnorm: width %d is not a multiple of %d groups", Di, n_groups);
   const int gs = Di / n_groups;
   dim3 grid(T, n_groups);
   if (w != nullptr && z_dtype == TLC_F32 && gs % 4 == 0 && gs <= 16384 && ldz % 4 == 0 && ((uintptr_t)y % 16) == 0 &&
-      ((uintptr_t)z % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+      ((uintptr_t)z % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0 && out_ld % 4 == 0) {
     const int n4 = gs / 4;
 #define TLC_GRMS_LAUNCH(NT, PT)                                                                                         \
   TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_vec_kernel<TO, NT, PT>, grid, dim3(NT), 0, stream, y,        \
-                                               (const float*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out))
+                                               (const float*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out, out_ld, out_scale))
     TLC_VEC_SHAPES(n4, TLC_GRMS_LAUNCH)
 #undef TLC_GRMS_LAUNCH
     TLC_CHECK_LAUNCH("gated_rmsnorm");
     return 0;
   }
   TLC_DISPATCH_DTYPE(z_dtype, TZ, TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_kernel<TZ, TO>, dim3(grid), dim3(256), 0, stream, 
-      y, (const TZ*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out)));
+      y, (const TZ*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out, out_ld, out_scale)));
   TLC_CHECK_LAUNCH("gated_rmsnorm");
   return 0;
 }

@@ -23,7 +23,7 @@ _vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _SIGNATURES = {
     "tlc_embed": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp],
     "tlc_rmsnorm": [_vp, _vp, _vp, _f, _i, _i, _vp, _i, _vp],
-    "tlc_gated_rmsnorm": [_vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _vp],
+    "tlc_gated_rmsnorm": [_vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _i, _f, _vp],
     "tlc_swiglu": [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp],
     "tlc_gather_rows": [_vp, _vp, _i, _i, _vp, _vp],
     "tlc_linear_simt": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
@@ -31,14 +31,15 @@ _SIGNATURES = {
     "tlc_linear_swiglu": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
     "tlc_rope_kv_store": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
                           _i, _vp],
-    "tlc_attention": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp],
-    "tlc_attention_decode": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "tlc_attention": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
+    "tlc_attention_decode": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i,
+                             _vp],
     "tlc_attention_decode_fused": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
-                                   _i, _i, _i, _i, _f, _i, _i, _vp],
+                                   _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "tlc_attention_decode_fused_ok": [_i, _i, _i],
     "tlc_attention_decode_fused_passes": [_i],
     "tlc_attention_prefill": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp,
-                              _i, _vp],
+                              _i, _i, _vp],
     "tlc_attention_prefill_chunks": [_i, _i, _i, _vp],
     "tlc_mamba_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
                        _i, _i, _i, _i, _vp],
@@ -129,6 +130,14 @@ def _rows(t: torch.Tensor, what: str) -> int:
     return t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
 
 
+def _out_rows(out: torch.Tensor, T: int, width: int, what: str) -> int:
+    """Row stride of an output [T, width] whose rows are dense: the tensor itself, or a range of the
+    columns of a wider buffer (several producers then fill one input of a following product)."""
+    if tuple(out.shape) != (T, width):
+        raise KernelError(f"{what}: output of shape {tuple(out.shape)}, expected {(T, width)}")
+    return _rows(out, what + " output")
+
+
 def _p(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
@@ -177,18 +186,20 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 
 
 def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: Optional[torch.Tensor], eps: float, n_groups: int,
-                  norm_before_gate: bool, out: torch.Tensor) -> None:
-    """Gate y by silu(z) and RMS-normalise per group (either order); weight None = gate only."""
+                  norm_before_gate: bool, out: torch.Tensor, out_scale: float = 1.0) -> None:
+    """Gate y by silu(z) and RMS-normalise per group (either order); weight None = gate only.  The
+    result is multiplied by out_scale; out [T, Di] may be a range of the columns of a wider buffer."""
     _gpu(y, z, weight, out)
     T, Di = y.shape
-    if y.dtype != torch.float32 or not y.is_contiguous() or not out.is_contiguous() or tuple(out.shape) != (T, Di):
-        raise KernelError("gated_rmsnorm: y must be contiguous float32 [T, Di] and out contiguous [T, Di]")
+    if y.dtype != torch.float32 or not y.is_contiguous():
+        raise KernelError("gated_rmsnorm: y must be contiguous float32 [T, Di]")
+    out_ld = _out_rows(out, T, Di, "gated_rmsnorm")
     if z.shape != y.shape:
         raise KernelError("gated_rmsnorm: gate and input differ in shape")
     _f32vec(weight, Di, "gated_rmsnorm weight")
     _call("tlc_gated_rmsnorm", y.data_ptr(), z.data_ptr(), dtype_code(z.dtype), _rows(z, "gate"), _p(weight),
           float(eps), T, Di, int(n_groups), int(bool(norm_before_gate)), out.data_ptr(), dtype_code(out.dtype),
-          _stream())
+          out_ld, float(out_scale), _stream())
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
@@ -320,9 +331,9 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     after this step) it cuts the key range of long rows into pieces that run side by side."""
     _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out)
     T = q.shape[0]
-    if not q.is_contiguous() or not out.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.shape != q.shape \
-            or out.dtype != q.dtype or k_pages.dtype != q.dtype:
-        raise KernelError("attention: q and out must be contiguous [T, H*hd] of the pages' type")
+    if not q.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.dtype != q.dtype or k_pages.dtype != q.dtype:
+        raise KernelError("attention: q must be contiguous [T, H*hd], q and out of the pages' type")
+    out_ld = _out_rows(out, T, H * hd, "attention")
     if decode_max_keys > 0 and H // KV <= 8:
         n_splits = (int(decode_max_keys) + 127) // 128
         part_o = torch.empty((T, H, n_splits, hd), dtype=torch.float32, device=q.device)
@@ -330,7 +341,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         _call("tlc_attention_decode", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
               block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(),
               slots.data_ptr(), out.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), T, H, KV, hd, float(scale),
-              int(window or 0), int(decode_max_keys), _stream())
+              int(window or 0), int(decode_max_keys), out_ld, _stream())
         return
     if decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
             and hd in (64, 128) and not DISABLE_TILED_ATTENTION:
@@ -346,11 +357,11 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         _call("tlc_attention_prefill", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), out.data_ptr(), B,
               n_tiles, H, KV, hd, float(scale), int(window or 0), (int(max_keys) + 63) // 64 if n_chunks > 1 else 0,
-              row_seq.data_ptr(), _p(part_o), _p(part_ml), T, _stream())
+              row_seq.data_ptr(), _p(part_o), _p(part_ml), T, out_ld, _stream())
         return
     _call("tlc_attention", q.data_ptr(), dtype_code(q.dtype), k_pages.data_ptr(), v_pages.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(),
-          out.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), _stream())
+          out.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), out_ld, _stream())
 
 
 DISABLE_FUSED_DECODE_ATTENTION = bool(int(os.environ.get("TLC_DISABLE_FUSED_DECODE_ATTENTION", "0")))
@@ -377,9 +388,10 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
     if qkv.dtype != torch.float32 or k_pages.dtype != torch.bfloat16 or v_pages.dtype != torch.bfloat16 \
             or out.dtype != torch.bfloat16:
         raise KernelError("attention_decode_fused: float32 projections, bfloat16 pages and output")
-    if not out.is_contiguous() or tuple(out.shape) != (T, H * hd) or not k_pages.is_contiguous() \
-            or not v_pages.is_contiguous() or tuple(k_pages.shape[1:]) != (KV, PAGE, hd) or v_pages.shape != k_pages.shape:
-        raise KernelError("attention_decode_fused: out must be contiguous [T, H*hd], pages contiguous [n, KV, 64, hd]")
+    if not k_pages.is_contiguous() or not v_pages.is_contiguous() or tuple(k_pages.shape[1:]) != (KV, PAGE, hd) \
+            or v_pages.shape != k_pages.shape:
+        raise KernelError("attention_decode_fused: pages must be contiguous [n, KV, 64, hd]")
+    out_ld = _out_rows(out, T, H * hd, "attention_decode_fused")
     ld = _rows(qkv, "qkv")
     if max(q_off + H * hd, k_off + KV * hd, v_off + KV * hd) > max(ld, qkv.shape[1]):
         raise KernelError("attention_decode_fused: q, k or v lies outside the projection's row")
@@ -395,7 +407,7 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
     _call("tlc_attention_decode_fused", qkv.data_ptr(), ld, q_off, k_off, v_off, k_pages.data_ptr(), v_pages.data_ptr(),
           inv_freq.data_ptr(), 2 * inv_freq.numel(), int(bool(write_kv)), block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(), out.data_ptr(), part_o.data_ptr(),
-          part_ml.data_ptr(), arrivals.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), int(max_keys), _stream())
+          part_ml.data_ptr(), arrivals.data_ptr(), T, H, KV, hd, float(scale), int(window or 0), int(max_keys), out_ld, _stream())
 
 
 def attention_decode_fused_passes(passes: int) -> None:

@@ -20,6 +20,7 @@ from .linear import StackedLinear
 # input and output projections then run side by side on streams of their own.
 PARALLEL_MIXERS = bool(int(os.environ.get("TLC_PARALLEL_MIXERS", "1")))
 _MAIN_MIXER = int(os.environ["TLC_MAIN_MIXER"]) if "TLC_MAIN_MIXER" in os.environ else None
+FUSE_OUTPUTS = bool(int(os.environ.get("TLC_FUSE_OUTPUTS", "1")))
 
 
 class Block(Part):
@@ -56,6 +57,20 @@ class Block(Part):
             for pr in projs:
                 self.fused_offsets.append((off, pr.out_features))
                 off += pr.out_features
+        # Likewise their output projections, whose results are added into the residual stream: the mixers
+        # write side by side into one buffer, and one product over the weights side by side along K forms
+        # the sum in its accumulator.
+        self.fused_out, self.out_offsets, self.out_scales = None, [], []
+        if self.fused_in is not None and FUSE_OUTPUTS and all(hasattr(m, "output_projection") and hasattr(m, "mix")
+                                                              for m in self.mixers):
+            outs = [m.output_projection() for m in self.mixers]
+            fused = StackedLinear.fuse_bound_inputs(outs, [bool(getattr(m, "mix_takes_scale", False)) for m in self.mixers])
+            if fused is not None:
+                self.fused_out, self.out_scales = fused
+                off = 0
+                for pr in outs:
+                    self.out_offsets.append((off, pr.in_features))
+                    off += pr.in_features
 
     def _mix_in_parallel(self, parts, step: StepInfo, cache: LayerCache, x32: torch.Tensor) -> None:
         """One mixer runs on the current stream, every other on a side stream that starts after the
@@ -72,6 +87,7 @@ class Block(Part):
         fork = torch.cuda.Event()
         fork.record(main)
         acts, done = [None] * len(self.mixers), [None] * len(self.mixers)
+        joint, views = self._joint_activations(x32)
         sides = iter(self._side)
         for i, (m, part) in enumerate(zip(self.mixers, parts)):
             if i == here:
@@ -79,14 +95,34 @@ class Block(Part):
             side = next(sides)
             side.wait_event(fork)
             with torch.cuda.stream(side):
-                acts[i] = m.mix(part, step, cache)
+                acts[i] = self._mix(i, part, step, cache, views[i])
                 done[i] = torch.cuda.Event()
                 done[i].record(side)
-        acts[here] = self.mixers[here].mix(parts[here], step, cache)
+        acts[here] = self._mix(here, parts[here], step, cache, views[here])
         for i, m in enumerate(self.mixers):          # outputs in the mixers' order, whatever ran where
             if done[i] is not None:
                 main.wait_event(done[i])
-            m.output(acts[i], x32)
+            if joint is None:
+                m.output(acts[i], x32)
+        if joint is not None:
+            self.fused_out.forward(joint, x32, accumulate=True)
+
+    def _mix(self, i: int, part: torch.Tensor, step: StepInfo, cache: LayerCache, view: Optional[torch.Tensor]):
+        """Mixer i between its projections; into its columns of the joint buffer, scaled, where there is one."""
+        m = self.mixers[i]
+        if view is None:
+            return m.mix(part, step, cache)
+        if self.out_scales[i] != 1.0:
+            return m.mix(part, step, cache, view, self.out_scales[i])
+        return m.mix(part, step, cache, view)
+
+    def _joint_activations(self, x32: torch.Tensor):
+        """The buffer that the mixers fill side by side for the shared output projection, and each
+        mixer's columns of it; (None, Nones) without a shared output projection."""
+        if self.fused_out is None:
+            return None, [None] * len(self.mixers)
+        joint = torch.empty((x32.shape[0], self.fused_out.in_features), dtype=self.dtype, device=x32.device)
+        return joint, [joint[:, off:off + n] for off, n in self.out_offsets]
 
     def forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
         """Updates the float32 residual stream x32 [T, D] in place."""
@@ -99,6 +135,11 @@ class Block(Part):
                 parts = [proj[:, off:off + n] for off, n in self.fused_offsets]
                 if step.max_new == 1 and x32.is_cuda and PARALLEL_MIXERS and all(hasattr(m, "mix") for m in self.mixers):
                     self._mix_in_parallel(parts, step, cache, x32)
+                elif self.fused_out is not None:
+                    joint, views = self._joint_activations(x32)
+                    for i, (part, view) in enumerate(zip(parts, views)):
+                        self._mix(i, part, step, cache, view)
+                    self.fused_out.forward(joint, x32, accumulate=True)
                 else:
                     for m, part in zip(self.mixers, parts):
                         m.forward_projected(part, step, cache, x32)

@@ -85,7 +85,10 @@ class StackedLinear:
         self.colbias = bias.to(torch.float32).to(device) if any_bias else None
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> torch.Tensor:
-        ops.linear(x, self.weight, out, self.colscale, self.colbias, accumulate)
+        # a part of a product fused along K keeps its weight as a column range of the fused matrix; used on
+        # its own (a mixer outside its block) it multiplies by a dense copy
+        w = self.weight if self.weight.is_contiguous() else self.weight.contiguous()
+        ops.linear(x, w, out, self.colscale, self.colbias, accumulate)
         return out
 
     @staticmethod
@@ -111,3 +114,43 @@ class StackedLinear:
             p.weight = fused.weight[off:off + p.out_features]          # the part's rows inside the fused storage
             off += p.out_features
         return fused
+
+    @staticmethod
+    def fuse_bound_inputs(parts: Sequence["StackedLinear"], can_scale: Sequence[bool]):
+        """One projection for several bound projections whose outputs are added together: their inputs lie
+        side by side in one activation buffer and their weights side by side along K, so the sum forms
+        in one accumulator.  The epilogue has one scale per output column, so the parts' scales must
+        agree up to one number each, by which the part's input has to be multiplied instead
+        (can_scale[i]: whoever fills part i's columns of the buffer can do that).  One part may be unable
+        to: its scale becomes the epilogue's.  Biases add.  Returns (projection, factor per part), or
+        None if the parts cannot share a product.  The parts' own weights become column ranges of the
+        fused matrix."""
+        if len(parts) < 2 or len({p.out_features for p in parts}) != 1 or len({p.weight.dtype for p in parts}) != 1:
+            return None
+        if any(p.in_features % 8 for p in parts):            # every part's columns start on a 16-byte boundary
+            return None
+        fixed = [i for i, ok in enumerate(can_scale) if not ok]
+        if len(fixed) > 1:
+            return None
+        base = fixed[0] if fixed else 0
+        dev, n = parts[0].weight.device, parts[0].out_features
+        vec = lambda p: p.colscale if p.colscale is not None else torch.ones(n, dtype=torch.float32, device=dev)
+        if bool((vec(parts[base]) == 0).any()):
+            return None
+        factors = []
+        for i, p in enumerate(parts):
+            r = vec(p).double() / vec(parts[base]).double()
+            if float((r - r[0]).abs().max()) > 1e-6 * abs(float(r[0])):
+                return None
+            factors.append(1.0 if i == base else float(r[0]))
+        fused = StackedLinear(sum(p.in_features for p in parts))
+        fused.weight = torch.cat([p.weight for p in parts], dim=1).contiguous()
+        fused.colscale = parts[base].colscale
+        if any(p.colbias is not None for p in parts):
+            fused.colbias = torch.stack([p.colbias for p in parts if p.colbias is not None]).double().sum(0).float()
+        fused.segments = [dict(seg) for seg in parts[base].segments]      # the rows of the output (any part's)
+        off = 0
+        for p in parts:
+            p.weight = fused.weight[:, off:off + p.in_features]          # the part's columns inside the fused storage
+            off += p.in_features
+        return fused, factors

@@ -74,14 +74,20 @@ class AttentionMixer(Part):
         """qkv: this mixer's input projection, float32 [T, q|k|v] (rows may be strided)."""
         self.output(self.mix(qkv, step, cache), residual)
 
-    def mix(self, qkv: torch.Tensor, step: StepInfo, cache: LayerCache) -> torch.Tensor:
-        """Everything between the input projection and the output projection: [T, H*hd]."""
+    def output_projection(self) -> StackedLinear:
+        """What turns mix()'s result into this mixer's share of the residual stream (a block may run
+        the output projections of its mixers as one product over their results side by side)."""
+        return self.o
+
+    def mix(self, qkv: torch.Tensor, step: StepInfo, cache: LayerCache, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Everything between the input projection and the output projection: [T, H*hd], written
+        to `out` (rows may be strided) where one is given."""
         T = step.n_rows
         kv = cache.kv[self.cache_key]
         table = getattr(self.position, "rotation_table", None)
         if step.max_new == 1 and table is not None and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
             # one token per sequence: rotation, store and attention in one kernel
-            att = torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
+            att = out if out is not None else torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
             ops.attention_decode_fused(qkv, self.q_off, self.k_off, self.v_off, kv.k_pages, kv.v_pages, table(),
                                        cache.writes, kv.block_table, step.positions, step.row_seq, step.slots, att,
                                        self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
@@ -90,7 +96,7 @@ class AttentionMixer(Part):
         q = torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
         self.position.rotate_and_store(qkv, self.q_off, self.k_off, self.v_off, q, kv, step, self.H, self.KV, self.hd,
                                        cache.writes)
-        att = torch.empty_like(q)
+        att = out if out is not None else torch.empty_like(q)
         ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
                       self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
                       step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos, step.max_context)

@@ -91,8 +91,16 @@ class Mamba2Mixer(Part):
         """proj: this mixer's input projection, float32 [T, z|x|B|C|dt] (rows may be strided)."""
         self.output(self.mix(proj, step, cache), residual)
 
-    def mix(self, proj: torch.Tensor, step: StepInfo, cache: LayerCache) -> torch.Tensor:
-        """Everything between the input projection and the output projection: [T, d_ssm]."""
+    def output_projection(self) -> StackedLinear:
+        return self.out_proj
+
+    mix_takes_scale = True         # mix() can multiply its result by a number on the way out
+
+    def mix(self, proj: torch.Tensor, step: StepInfo, cache: LayerCache, out: Optional[torch.Tensor] = None,
+            out_scale: float = 1.0) -> torch.Tensor:
+        """Everything between the input projection and the output projection: [T, d_ssm] times
+        out_scale, written to `out` (rows may be strided) where one is given.  (A block that runs
+        several output projections as one product moves a part of this one's multiplier here.)"""
         T, f32 = step.n_rows, torch.float32
         conv_state = cache.state[self.cache_key + ".conv"]
         ssm_state = cache.state[self.cache_key + ".ssm"]
@@ -104,8 +112,9 @@ class Mamba2Mixer(Part):
         y = new((T, self.Di), f32)
         ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs, self.P,
                      self.N, self.G, step.chunks, self.A if self.dtype == torch.bfloat16 else None)
-        gated = new((T, self.Di), self.dtype)
-        ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated)
+        gated = out if out is not None else new((T, self.Di), self.dtype)
+        ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated,
+                          out_scale)
         return gated
 
     def output(self, gated: torch.Tensor, residual: torch.Tensor) -> None:
