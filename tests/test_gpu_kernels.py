@@ -59,6 +59,27 @@ def test_rmsnorm(dtype, D):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("D", [72, 1000, 2048, 3072, 4100, 8200])
+def test_norms_of_many_rows(dtype, D):
+    """From 512 rows on the vector kernels take fewer threads a row with several pieces each."""
+    g = gen(3)
+    T = 530
+    x = rnd(g, T, D, scale=3.0)
+    w = 1 + rnd(g, D, scale=0.2)
+    cmp("rmsnorm", [x, w, 1e-5, torch.empty(T, D, dtype=DT[dtype]), None], [3])
+    groups = 1 if D % 3 else 3
+    z = rnd(g, T, D + 4)[:, 4:]
+    for before in (False, True):
+        args = [x, z, w, 1e-5, groups, before, torch.empty(T, D, dtype=DT[dtype])]
+        gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args]
+        gpu[1] = torch.cat([torch.zeros(T, 4), z], dim=1).cuda()[:, 4:]      # a strided slice, as in the model
+        ops.gated_rmsnorm(*gpu)
+        ops_plain.gated_rmsnorm(*args)
+        ref, got = args[6].double(), gpu[6].cpu().double()
+        assert (ref - got).abs().max() <= TOL[DT[dtype]] * ref.abs().max() * 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("groups,before,with_w", [(1, False, True), (3, True, True), (2, False, False)])
 def test_gated_rmsnorm(dtype, groups, before, with_w):
     g = gen(2)

@@ -140,6 +140,18 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ rows, co
   else if ((n4) <= 2048) { LAUNCH(1024, 2); } \
   else { LAUNCH(1024, 4); }
 
+// The same for many rows (prompts): fewer threads a row with up to four float4 each, so that a thread has more
+// loads in flight, more rows share an SM, and the block's sum has fewer warps to join.
+#define TLC_VEC_SHAPES_MANY(n4, LAUNCH)       \
+  if ((n4) <= 128) { LAUNCH(64, 2); }         \
+  else if ((n4) <= 256) { LAUNCH(64, 4); }    \
+  else if ((n4) <= 512) { LAUNCH(128, 4); }   \
+  else if ((n4) <= 768) { LAUNCH(256, 3); }   \
+  else if ((n4) <= 1024) { LAUNCH(256, 4); }  \
+  else if ((n4) <= 2048) { LAUNCH(512, 4); }  \
+  else { LAUNCH(1024, 4); }
+constexpr int VEC_MANY_ROWS = 512;            // from this many rows on
+
 extern "C" int tlc_rmsnorm(const float* x, const int* rows, const float* w, float eps, int R, int D, void* out,
                            int out_dtype, cudaStream_t stream) {
   if (R == 0) return 0;
@@ -148,7 +160,7 @@ extern "C" int tlc_rmsnorm(const float* x, const int* rows, const float* w, floa
 #define TLC_RMS_LAUNCH(NT, PT)                                                                                        \
   TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(rmsnorm_vec_kernel<TO, NT, PT>, dim3(R), dim3(NT), 0, stream, x, rows, w, \
                                                eps, D, (TO*)out))
-    TLC_VEC_SHAPES(n4, TLC_RMS_LAUNCH)
+    if (R >= VEC_MANY_ROWS) { TLC_VEC_SHAPES_MANY(n4, TLC_RMS_LAUNCH) } else { TLC_VEC_SHAPES(n4, TLC_RMS_LAUNCH) }
 #undef TLC_RMS_LAUNCH
     TLC_CHECK_LAUNCH("rmsnorm");
     return 0;
@@ -281,7 +293,7 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int
 #define TLC_GRMS_LAUNCH(NT, PT)                                                                                         \
   TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_vec_kernel<TO, NT, PT>, grid, dim3(NT), 0, stream, y,        \
                                                (const float*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out, out_ld, out_scale))
-    TLC_VEC_SHAPES(n4, TLC_GRMS_LAUNCH)
+    if (T >= VEC_MANY_ROWS) { TLC_VEC_SHAPES_MANY(n4, TLC_GRMS_LAUNCH) } else { TLC_VEC_SHAPES(n4, TLC_GRMS_LAUNCH) }
 #undef TLC_GRMS_LAUNCH
     TLC_CHECK_LAUNCH("gated_rmsnorm");
     return 0;
