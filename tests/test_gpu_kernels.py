@@ -208,26 +208,37 @@ def _step_arrays(starts, lens):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,KV,hd,rope", [(6, 3, 24, 24), (4, 1, 48, 32), (8, 2, 128, 128), (5, 5, 16, 0)])
-def test_rope_kv_store(dtype, H, KV, hd, rope):
+@pytest.mark.parametrize("aligned", [False, True])
+@pytest.mark.parametrize("H,KV,hd,rope", [(6, 3, 24, 24), (4, 1, 48, 32), (8, 2, 128, 128), (5, 5, 16, 0), (3, 1, 80, 64)])
+def test_rope_kv_store(dtype, H, KV, hd, rope, aligned):
+    """aligned: the projection's pieces lie on 16-byte boundaries, which the vector kernel needs (a rotated
+    width that is a multiple of 8, 32-bit projections); otherwise an element at a time."""
     g = gen(5)
+    lead, extra = (4, 8) if aligned else (2, 5)
     starts, lens = [0, 70, 130], [5, 3, 66]
     pos, row_seq, cu, _ = _step_arrays(starts, lens)
     slots, table, k_pages, v_pages = _paged_setup(g, 3, [s + n for s, n in zip(starts, lens)], KV, hd, DT[dtype])
     T = sum(lens)
     width = (H + 2 * KV) * hd
-    qkv = rnd(g, T, width + 5, dtype=torch.float32 if H != 4 else DT[dtype])
+    qkv = rnd(g, T, width + extra, dtype=torch.float32 if H != 4 else DT[dtype])
     inv = (1.0 / torch.pow(torch.tensor(1e6, dtype=torch.float64),
                            torch.arange(rope // 2, dtype=torch.float64) * 2 / max(rope, 1))).float()
-    args = [qkv[:, 2:2 + width], 0, H * hd, (H + KV) * hd, torch.empty(T, H * hd, dtype=DT[dtype]), k_pages, v_pages,
+    args = [qkv[:, lead:lead + width], 0, H * hd, (H + KV) * hd, torch.empty(T, H * hd, dtype=DT[dtype]), k_pages, v_pages,
             inv, pos, row_seq, slots, table, H, KV, hd, True]
     gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args]
-    gpu[0] = qkv.cuda()[:, 2:2 + width]
+    gpu[0] = qkv.cuda()[:, lead:lead + width]
     ops.rope_kv_store(*gpu)
     ops_plain.rope_kv_store(*args)
     for i in (4, 5, 6):
         ref, got = args[i].double(), gpu[i].cpu().double()
         assert (ref - got).abs().max() <= TOL[DT[dtype]] * ref.abs().max() * 2, f"output {i}"
+    # a layer that reads another layer's cache rotates its queries and leaves the pages alone
+    k_before, v_before = gpu[5].clone(), gpu[6].clone()
+    gpu[4].zero_()
+    gpu[-1] = False
+    ops.rope_kv_store(*gpu)
+    assert torch.equal(gpu[5], k_before) and torch.equal(gpu[6], v_before)
+    assert (args[4].double() - gpu[4].cpu().double()).abs().max() <= TOL[DT[dtype]] * args[4].double().abs().max() * 2
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

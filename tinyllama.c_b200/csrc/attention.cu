@@ -59,12 +59,99 @@ __global__ void rope_kv_store_kernel(const TI* __restrict__ qkv, int ld, int q_o
   }
 }
 
+// The same for 32-bit projections whose pieces all lie on 16-byte boundaries (rotated width a multiple of 8, head
+// size and offsets multiples of 4): a block takes ROPE_ROWS rows; a thread takes four consecutive dims of a
+// head's lower half with their partners in the upper half (two 16-byte loads, two stores), or four dims that
+// are only copied (values, dims beyond the rotated width).
+#define ROPE_ROWS 4
+template <typename T> struct Put4;
+template <> struct Put4<float> {
+  static __device__ __forceinline__ void put(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Put4<__nv_bfloat16> {
+  static __device__ __forceinline__ void put(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&lo);
+    u.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+  }
+};
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_store_vec_kernel(const float* __restrict__ qkv, int ld, int q_off, int k_off, int v_off, T* __restrict__ q_out,
+                         T* __restrict__ k_pages, T* __restrict__ v_pages, const float* __restrict__ inv_freq,
+                         int rope_dim, const int* __restrict__ positions, const int* __restrict__ row_seq,
+                         const int* __restrict__ slots, const int* __restrict__ block_table, int max_pages, int n_rows,
+                         int H, int KV, int hd, int write_kv) {
+  tlc_pdl(qkv, q_out, k_pages, v_pages);
+  extern __shared__ float rope_cs[];                 // per row: [half] cos | [half] sin
+  __shared__ int s_page[ROPE_ROWS], s_prow[ROPE_ROWS];
+  const int t0 = blockIdx.x * ROPE_ROWS;
+  const int rows = min(ROPE_ROWS, n_rows - t0);
+  const int half = rope_dim >> 1;
+  if (threadIdx.x < rows) {
+    const int t = t0 + threadIdx.x, pos = positions[t];
+    s_page[threadIdx.x] = write_kv ? block_table[(size_t)slots[row_seq[t]] * max_pages + pos / TLC_PAGE] : -1;
+    s_prow[threadIdx.x] = pos % TLC_PAGE;
+  }
+  for (int i = threadIdx.x; i < rows * half; i += blockDim.x) {
+    const int r = i / half, j = i - r * half;
+    sincosf((float)positions[t0 + r] * inv_freq[j], &rope_cs[r * rope_dim + half + j], &rope_cs[r * rope_dim + j]);
+  }
+  __syncthreads();
+  const int pair_items = half >> 2, tail_items = (hd - rope_dim) >> 2;
+  const int per_head = pair_items + tail_items;          // items of a rotated head
+  const int n_rot = write_kv ? H + KV : H;               // heads that are rotated (queries, keys)
+  const int per_row = n_rot * per_head + (write_kv ? KV * (hd >> 2) : 0);
+  for (int idx = threadIdx.x; idx < rows * per_row; idx += blockDim.x) {
+    const int r = idx / per_row, it = idx - r * per_row;
+    const int t = t0 + r;
+    const float* row = qkv + (size_t)t * ld;
+    const float* cs = rope_cs + r * rope_dim;
+    if (it < n_rot * per_head) {
+      const int head = it / per_head, j = it - head * per_head;
+      const bool is_q = head < H;
+      const int h = is_q ? head : head - H;
+      const float* src = row + (is_q ? q_off : k_off) + (size_t)h * hd;
+      T* dst = is_q ? q_out + (size_t)t * H * hd + (size_t)h * hd
+                    : k_pages + (((size_t)s_page[r] * KV + h) * TLC_PAGE + s_prow[r]) * hd;
+      if (j < pair_items) {
+        const int d = 4 * j;
+        const float4 a = *reinterpret_cast<const float4*>(src + d), b = *reinterpret_cast<const float4*>(src + half + d);
+        const float4 c = *reinterpret_cast<const float4*>(cs + d), sn = *reinterpret_cast<const float4*>(cs + half + d);
+        Put4<T>::put(dst + d, make_float4(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y, a.z * c.z - b.z * sn.z, a.w * c.w - b.w * sn.w));
+        Put4<T>::put(dst + half + d, make_float4(a.x * sn.x + b.x * c.x, a.y * sn.y + b.y * c.y, a.z * sn.z + b.z * c.z, a.w * sn.w + b.w * c.w));
+      } else {
+        const int d = rope_dim + 4 * (j - pair_items);
+        Put4<T>::put(dst + d, *reinterpret_cast<const float4*>(src + d));
+      }
+    } else {
+      const int iv = it - n_rot * per_head;
+      const int h = iv / (hd >> 2), d = 4 * (iv - h * (hd >> 2));
+      Put4<T>::put(v_pages + (((size_t)s_page[r] * KV + h) * TLC_PAGE + s_prow[r]) * hd + d,
+                   *reinterpret_cast<const float4*>(row + v_off + (size_t)h * hd + d));
+    }
+  }
+}
+
 extern "C" int tlc_rope_kv_store(const void* qkv, int in_dtype, int dtype, int ld, int q_off, int k_off, int v_off, void* q_out,
                                  void* k_pages, void* v_pages, const float* inv_freq, int rope_dim,
                                  const int* positions, const int* row_seq, const int* slots, const int* block_table,
                                  int max_pages, int T, int H, int KV, int hd, int write_kv, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(rope_dim % 2 == 0 && rope_dim <= hd, "rope: rotated width %d must be even and at most head_dim %d", rope_dim, hd);
+  if (in_dtype == TLC_F32 && rope_dim % 8 == 0 && hd % 4 == 0 && ld % 4 == 0 && q_off % 4 == 0 && k_off % 4 == 0 && v_off % 4 == 0 &&
+      ((uintptr_t)qkv % 16) == 0 && ((uintptr_t)q_out % 16) == 0 && ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0 &&
+      (size_t)ROPE_ROWS * rope_dim * sizeof(float) <= 40 * 1024) {
+    const dim3 grid((T + ROPE_ROWS - 1) / ROPE_ROWS);
+    const size_t smem = (size_t)ROPE_ROWS * rope_dim * sizeof(float);
+    TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(rope_kv_store_vec_kernel<TT>, dim3(grid), dim3(256), smem, stream, (const float*)qkv, ld,
+        q_off, k_off, v_off, (TT*)q_out, (TT*)k_pages, (TT*)v_pages, inv_freq, rope_dim, positions, row_seq, slots, block_table,
+        max_pages, T, H, KV, hd, write_kv));
+    TLC_CHECK_LAUNCH("rope_kv_store");
+    return 0;
+  }
   TLC_DISPATCH_DTYPE(in_dtype, TI, TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(rope_kv_store_kernel<TI, TT>, dim3(T), dim3(256), (size_t)rope_dim * sizeof(float), stream, 
       (const TI*)qkv, ld, q_off, k_off, v_off, (TT*)q_out, (TT*)k_pages, (TT*)v_pages, inv_freq, rope_dim, positions,
       row_seq, slots, block_table, max_pages, H, KV, hd, write_kv)));
