@@ -157,8 +157,9 @@ template <int N_> __device__ __forceinline__ void cp_async_wait() { asm volatile
 
 // ---- chunk states: S_c[p, n] = sum_j w_j x[j, p] B[j, n],  w_j = exp(cum_last - cum_j) dt_j ----------
 // grid (seg, Hs, N / 128); 8 warps; output P x 128 with K = 128 rows of the chunk.  x and B arrive as they
-// are, by cp.async, all at once; the weights w_j are computed meanwhile and applied to the x fragments in
-// registers, where both operands are rounded to TF32.
+// are, by cp.async, all at once; the weights w_j are computed meanwhile.  x is then scaled by them and rounded
+// to TF32 once, in place (the kernel is bound by instruction issue: every warp needs every x fragment);
+// B is rounded in registers.  A warp owns half of the head's rows and 32 of the columns.
 template <int P>
 __global__ void __launch_bounds__(256)
 ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ cum,
@@ -197,42 +198,52 @@ ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ 
   }
   cp_async_wait<0>();
   __syncthreads();
+  // x times its row's weight, rounded to TF32, once and in place: every warp reads it from there
+  uint32_t* Xt = reinterpret_cast<uint32_t*>(Xs);
+  for (int idx = tid; idx < Q * (P / 4); idx += 256) {
+    const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(Xs + r * LDX + c4);
+    const float wr = ws[r];
+    *reinterpret_cast<uint4*>(Xt + r * LDX + c4) = make_uint4(tf32(v.x * wr), tf32(v.y * wr), tf32(v.z * wr), tf32(v.w * wr));
+  }
+  __syncthreads();
   const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
-  // warp w: columns n in [16w, 16w+16) (2 tiles) x all P rows (P/16 tiles)
-  float acc[P / 16][2][4];
+  // warp w: rows p of half w & 1 of the head (P/32 tiles) x columns n in [32 (w >> 1), +32) (4 tiles)
+  constexpr int MT = P / 32;
+  const int p0 = (warp & 1) * (P / 2), n_w = (warp >> 1) * 32;
+  float acc[MT][4][4];
 #pragma unroll
-  for (int m = 0; m < P / 16; m++)
+  for (int m = 0; m < MT; m++)
 #pragma unroll
-    for (int j = 0; j < 2; j++)
+    for (int jn = 0; jn < 4; jn++)
 #pragma unroll
-      for (int k = 0; k < 4; k++) acc[m][j][k] = 0.f;
+      for (int k = 0; k < 4; k++) acc[m][jn][k] = 0.f;
 #pragma unroll 4
   for (int kk = 0; kk < Q / 8; kk++) {
-    uint32_t b[2][2];
+    uint32_t b[4][2];
 #pragma unroll
-    for (int j = 0; j < 2; j++) {
-      const float* br = Bs + (kk * 8 + tq) * LDB + warp * 16 + j * 8 + gq;
-      b[j][0] = tf32(br[0]);
-      b[j][1] = tf32(br[4 * LDB]);
+    for (int jn = 0; jn < 4; jn++) {
+      const float* br = Bs + (kk * 8 + tq) * LDB + n_w + jn * 8 + gq;
+      b[jn][0] = tf32(br[0]);
+      b[jn][1] = tf32(br[4 * LDB]);
     }
-    const float w0 = ws[kk * 8 + tq], w1 = ws[kk * 8 + tq + 4];
 #pragma unroll
-    for (int m = 0; m < P / 16; m++) {
-      const float* ar = Xs + (kk * 8 + tq) * LDX + m * 16 + gq;              // A(row p, col j) = x[j][p] w_j
-      const uint32_t a0 = tf32(ar[0] * w0), a1 = tf32(ar[8] * w0), a2 = tf32(ar[4 * LDX] * w1), a3 = tf32(ar[4 * LDX + 8] * w1);
+    for (int m = 0; m < MT; m++) {
+      const uint32_t* ar = Xt + (kk * 8 + tq) * LDX + p0 + m * 16 + gq;               // A(row p, col j) = x[j][p] w_j
+      const uint32_t a0 = ar[0], a1 = ar[8], a2 = ar[4 * LDX], a3 = ar[4 * LDX + 8];
 #pragma unroll
-      for (int j = 0; j < 2; j++) mma_tf32(acc[m][j], a0, a1, a2, a3, b[j][0], b[j][1]);
+      for (int jn = 0; jn < 4; jn++) mma_tf32(acc[m][jn], a0, a1, a2, a3, b[jn][0], b[jn][1]);
     }
   }
   float* out = chunk_state + (((size_t)seg * Hs + h) * P) * N;
 #pragma unroll
-  for (int m = 0; m < P / 16; m++)
+  for (int m = 0; m < MT; m++)
 #pragma unroll
-    for (int j = 0; j < 2; j++) {
-      const int n = nb + warp * 16 + j * 8 + 2 * tq;
+    for (int jn = 0; jn < 4; jn++) {
+      const int n = nb + n_w + jn * 8 + 2 * tq;
       if (n < N) {
-        *reinterpret_cast<float2*>(out + (size_t)(m * 16 + gq) * N + n) = make_float2(acc[m][j][0], acc[m][j][1]);
-        *reinterpret_cast<float2*>(out + (size_t)(m * 16 + gq + 8) * N + n) = make_float2(acc[m][j][2], acc[m][j][3]);
+        *reinterpret_cast<float2*>(out + (size_t)(p0 + m * 16 + gq) * N + n) = make_float2(acc[m][jn][0], acc[m][jn][1]);
+        *reinterpret_cast<float2*>(out + (size_t)(p0 + m * 16 + gq + 8) * N + n) = make_float2(acc[m][jn][2], acc[m][jn][3]);
       }
     }
 }
