@@ -36,6 +36,19 @@ __device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Four 8 x 8 matrices of 16-bit elements, i.e. four blocks of 8 rows x 4 32-bit words: thread T gets word T % 4 of
+// row T / 4 of each, which is the layout of the TF32 fragments wherever K runs along the rows in memory.
+__device__ __forceinline__ void ldsm_x4_b32(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t tf32_bits(uint32_t v) { return tf32(__uint_as_float(v)); }
+// 2^x by the special-function unit (two units in the last place; the result becomes a TF32 operand)
+__device__ __forceinline__ float ex2_quick(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
 // ---- cumulative log-decay per (chunk, head) --------------------------------------------------------
 // cum[t, h] = sum of dt*A over the chunk's rows up to t; chunk_decay[seg, h] = exp(cum at the last row)
 __global__ void __launch_bounds__(128)
@@ -309,7 +322,7 @@ ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt
   fetch_slab(0, 0);
   if (tid < Q) {
     const int r = min(tid, L - 1);
-    cums[tid] = cum[(size_t)(t0 + r) * Hs + h];
+    cums[tid] = cum[(size_t)(t0 + r) * Hs + h] * 1.4426950408889634f;      // in powers of two from here on
     dts[tid] = tid < L ? dt[(size_t)(t0 + tid) * Hs + h] : 0.f;
   }
   __syncthreads();
@@ -330,10 +343,11 @@ ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt
       uint4 d = make_uint4(0u, 0u, 0u, 0u);
       if (j4 <= i && i < L) {
         const float ci = cums[i];
-        d.x = tf32(v[u].x * expf(ci - cums[j4]) * dts[j4]);
-        if (j4 + 1 <= i) d.y = tf32(v[u].y * expf(ci - cums[j4 + 1]) * dts[j4 + 1]);
-        if (j4 + 2 <= i) d.z = tf32(v[u].z * expf(ci - cums[j4 + 2]) * dts[j4 + 2]);
-        if (j4 + 3 <= i) d.w = tf32(v[u].w * expf(ci - cums[j4 + 3]) * dts[j4 + 3]);
+        const float4 cj = *reinterpret_cast<const float4*>(cums + j4), dj = *reinterpret_cast<const float4*>(dts + j4);
+        d.x = tf32(v[u].x * ex2_quick(ci - cj.x) * dj.x);
+        if (j4 + 1 <= i) d.y = tf32(v[u].y * ex2_quick(ci - cj.y) * dj.y);
+        if (j4 + 2 <= i) d.z = tf32(v[u].z * ex2_quick(ci - cj.z) * dj.z);
+        if (j4 + 3 <= i) d.w = tf32(v[u].w * ex2_quick(ci - cj.w) * dj.w);
       }
       *reinterpret_cast<uint4*>(Ms + il * LDM + j4) = d;
     }
@@ -364,16 +378,20 @@ ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt
     cp_async_wait<0>();
     __syncthreads();                       // slab sl is in shared memory; everybody is done with slab sl-1
     if (sl + 1 < n_slabs) fetch_slab((sl + 1) * SL, (sl + 1) & 1);
-    const float* Cs = Cb + (size_t)(sl & 1) * R * LDS;
-    const float* Ss = Sb + (size_t)(sl & 1) * P * LDS;
+    // C and the state have K (the state column) along their rows: whole fragments come by ldmatrix
+    const uint32_t cs_u = cb0 + (uint32_t)((sl & 1) * R * LDS) * 4, ss_u = sb0 + (uint32_t)((sl & 1) * P * LDS) * 4;
 #pragma unroll
     for (int kk = 0; kk < SL / 8; kk++) {
-      const float* ar = Cs + (il_base + gq) * LDS + kk * 8 + tq;
-      const uint32_t a0 = tf32(ar[0]), a1 = tf32(ar[8 * LDS]), a2 = tf32(ar[4]), a3 = tf32(ar[8 * LDS + 4]);
+      uint32_t a0, a1, a2, a3;     // rows 0-7 | 8-15 of the warp's strip, columns kk*8 + (0-3 | 4-7)
+      ldsm_x4_b32(cs_u + (uint32_t)((il_base + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS + kk * 8 + (lane >> 4) * 4) * 4, a0, a1, a2, a3);
+      a0 = tf32_bits(a0); a1 = tf32_bits(a1); a2 = tf32_bits(a2); a3 = tf32_bits(a3);
 #pragma unroll
-      for (int j = 0; j < NT; j++) {
-        const float* br = Ss + (p_base + j * 8 + gq) * LDS + kk * 8 + tq;       // B(k = n, col = p) = S_in[p][n]
-        mma_tf32(acc2[j], a0, a1, a2, a3, tf32(br[0]), tf32(br[4]));
+      for (int jp = 0; jp < NT / 2; jp++) {
+        uint32_t b00, b01, b10, b11;   // B(k = n, col = p) = S_in[p][n]: rows p of two tiles, columns kk*8 + (0-3 | 4-7)
+        ldsm_x4_b32(ss_u + (uint32_t)((p_base + jp * 16 + (lane & 7) + (lane >> 4) * 8) * LDS + kk * 8 + ((lane >> 3) & 1) * 4) * 4,
+                    b00, b01, b10, b11);
+        mma_tf32(acc2[2 * jp], a0, a1, a2, a3, tf32_bits(b00), tf32_bits(b01));
+        mma_tf32(acc2[2 * jp + 1], a0, a1, a2, a3, tf32_bits(b10), tf32_bits(b11));
       }
     }
   }
@@ -382,7 +400,7 @@ ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt
   for (int r = 0; r < 2; r++) {
     const int i = i_base + gq + 8 * r;
     if (i < L) {
-      const float e = expf(cums[i]);
+      const float e = exp2f(cums[i]);
 #pragma unroll
       for (int j = 0; j < NT; j++) {
         const int p = p_base + j * 8 + 2 * tq;
