@@ -56,3 +56,44 @@ def test_cuts_and_batches_equal_whole_sequences(tmp_path, cpu_kernels, name):
         cache.release(s)
     cache.check()
     assert cache.slots.n_held == 0 and all(g.pool.n_held == 0 for g in cache.kv_groups)
+
+
+def _bound(in_features, out_features, scale, bias, seed):
+    from tinyllama_c_b200.parts.linear import StackedLinear
+    g = torch.Generator().manual_seed(seed)
+    lin = StackedLinear(in_features)
+    lin.add("w", out_features, "b" if bias else None, 1.0, scale)
+    tensors = {"w": torch.randn(out_features, in_features, generator=g)}
+    if bias:
+        tensors["b"] = torch.randn(out_features, generator=g)
+    lin.bind(tensors, torch.float32, "cpu")
+    return lin
+
+
+def test_output_projections_as_one_product(cpu_kernels):
+    """Projections whose results are added share one product over their inputs side by side when their
+    output scales agree up to a number each, which goes to whoever can scale its input; the sum, the
+    biases and the scales come out as from the separate products."""
+    from tinyllama_c_b200.parts.linear import StackedLinear
+    g = torch.Generator().manual_seed(0)
+    a, b = _bound(16, 24, 0.8, True, 1), _bound(40, 24, 0.9, False, 2)
+    xa, xb = torch.randn(5, 16, generator=g), torch.randn(5, 40, generator=g)
+    want = torch.ones(5, 24)
+    a.forward(xa, want, accumulate=True)
+    b.forward(xb, want, accumulate=True)
+    fused, factors = StackedLinear.fuse_bound_inputs([a, b], [False, True])
+    assert factors[0] == 1.0 and abs(factors[1] - 0.9 / 0.8) < 1e-6 and fused.in_features == 56
+    got = torch.ones(5, 24)
+    fused.forward(torch.cat([xa, xb * factors[1]], dim=1), got, accumulate=True)
+    assert (got - want).abs().max() < 1e-5 * want.abs().max()
+    # the parts still work on their own, from their columns of the fused matrix
+    again = torch.ones(5, 24)
+    a.forward(xa, again, accumulate=True)
+    b.forward(xb, again, accumulate=True)
+    assert torch.equal(again, want)
+    # refused: nobody can take the second part's factor; widths off 16-byte boundaries; scales that differ by row
+    assert StackedLinear.fuse_bound_inputs([_bound(16, 24, 0.8, False, 1), _bound(40, 24, 0.9, False, 2)], [False, False]) is None
+    assert StackedLinear.fuse_bound_inputs([_bound(12, 24, 1.0, False, 1), _bound(40, 24, 1.0, False, 2)], [True, True]) is None
+    rows = [1.0] * 12 + [2.0] * 12
+    assert StackedLinear.fuse_bound_inputs([_bound(16, 24, 1.0, False, 1), _bound(40, 24, rows, False, 2)], [False, True]) is None
+    assert StackedLinear.fuse_bound_inputs([_bound(16, 24, 1.0, False, 1), _bound(40, 32, 1.0, False, 2)], [True, True]) is None
