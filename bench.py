@@ -14,9 +14,12 @@ printed is one JSON object:
   prefill    one 2,048-token prompt: tokens per second, milliseconds, fraction of the bf16 peak
   roofline   bytes a decode step has to read (every weight once + the live cache) / its time,
              against the measured HBM bandwidth
-  points     decode at batch 1 and 64
-The reference publishes no Falcon-H1 number and runs the model on the CPU only
-(falcon_h1.c:78-83), so vs_baseline is null; --impl reference reports why it is unavailable.
+  points     decode at batch 1, 16, 32 and 64, at batch 8 with 3,800-token prompts, and the workloads of the
+             3B and 7B layer sizes (16 unequal prompts with 256 sampled tokens each; batch-64 decode from
+             1,024-token prompts and one 8,192-token prompt)
+The reference publishes no Falcon-H1 number (vs_baseline is null) and runs the model on the CPU only
+(falcon_h1.c:78-83); --impl reference builds the unmodified reference and measures that CPU engine on the
+same layer sizes at batch 1, the only batch it has (baseline/reference_arm.py).
 """
 import argparse
 import json
@@ -126,29 +129,25 @@ class Clocks:
 
 
 def time_decode(llm, tlc, batch, prompt_len, steps, warmup, seed):
-    """Device time of `steps` replays of the captured decode step for `batch` sequences."""
+    """Device time of `steps` decode steps of `batch` sequences through the engine's own decode step
+    (EngineBackend.decode_step: reserve, upload, replay of the captured step, read-back, commit)."""
     import torch
     from tinyllama_c_b200 import ops
-    from tinyllama_c_b200.engine import StepEntry
-    from tinyllama_c_b200.engine.decode_graph import DecodeGraph
+    from tinyllama_c_b200.engine import EngineBackend, StepEntry
     g = torch.Generator().manual_seed(seed)
     V = llm.config.vocab_size
     slots = [llm.cache.acquire() for _ in range(batch)]
     prompts = torch.randint(0, V, (batch, prompt_len), generator=g).tolist()
-    # prompts in groups of 8 sequences to bound activation memory
-    for i in range(0, batch, 8):
-        llm.step([StepEntry(s, p, ()) for s, p in zip(slots[i:i + 8], prompts[i:i + 8])])
-    from tinyllama_c_b200.engine.generate import context_bucket
-    graph = DecodeGraph(llm.model, llm.cache, tlc.GREEDY, batch, context_bucket(prompt_len + max(3, warmup) + steps + 1))
+    # prompts in groups that bound activation memory
+    group = max(1, 8192 // prompt_len)
+    for i in range(0, batch, group):
+        llm.step([StepEntry(s, p, ()) for s, p in zip(slots[i:i + group], prompts[i:i + group])])
+    backend = EngineBackend(llm.model, llm.cache, tlc.GREEDY, llm._graphs, True)
     toks = torch.randint(0, V, (batch,), generator=g).tolist()
 
     def one():
         nonlocal toks
-        pos = [llm.cache.reserve(s, 1) for s in slots]
-        llm.cache.upload_tables()
-        toks = graph.run(slots, toks, pos)
-        for s in slots:
-            llm.cache.commit(s, 1)
+        toks = backend.decode_step([(s, [t]) for s, t in zip(slots, toks)])
 
     for _ in range(max(3, warmup)):
         one()
@@ -240,13 +239,15 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--generate", type=int, default=0, metavar="N",
                     help="also generate 256 tokens for N prompts of 64..2048 tokens at temperature 0.7")
+    ap.add_argument("--prefill-only", action="store_true", help="time the prompt of --prefill-tokens tokens only "
+                    "(--steps repetitions when fewer than 8): what a profiler capture of the prompt kernels runs")
+    ap.add_argument("--no-big", dest="big", action="store_false", help="skip the 3B and 7B workloads among the points")
+    ap.add_argument("--ref-budget", type=float, default=600.0, help="seconds the reference arm may take (it runs fewer "
+                    "layers, and says so, where all of them would take longer)")
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "tinyllama.c is a C program, not a Python package (pip: neither setup.py nor pyproject.toml "
-                          "found), publishes no Falcon-H1 number and forces Falcon-H1 onto the CPU (falcon_h1.c:78-83)"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU; --gpus {args.gpus} is not supported by this single-GPU library")
         return 2
@@ -263,8 +264,17 @@ def main() -> int:
     model = tlc.random_model(cfg, seed=0, dtype="bfloat16")
     # room for 64 sequences of prompt + decoded tokens, for the long prompt and for the unequal batch
     per_seq = -(-(args.prompt_len + 2 * args.steps + 80) // 64) * 64
-    room = max(64 * 1024, max(64, args.batch) * per_seq, args.prefill_tokens + 64, args.generate * (2048 + 256 + 64))
+    room = max(64 * 1024, max(64, args.batch) * per_seq, args.prefill_tokens + 64, args.generate * (2048 + 256 + 64),
+               8 * 3968)
     llm = tlc.LLM(model, max_tokens=room, max_seqs=max(64, args.batch, args.generate))
+
+    if args.prefill_only:
+        T = args.prefill_tokens
+        pms = time_prefill(llm, T, seed=3, reps=args.steps if args.steps < 8 else 3)
+        print(json.dumps({"prefill": {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
+                                      "frac": round(prefill_flops(cfg, T) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                          "layers": args.layers}))
+        return 0
 
     ms, launches, clocks, ctx = time_decode(llm, tlc, args.batch, args.prompt_len, args.steps, args.warmup, seed=1)
     value = args.batch * 1000.0 / ms
@@ -297,12 +307,88 @@ def main() -> int:
         rec["prefill"] = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
                           "frac": round(fl / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
         pts = {}
-        for b in (1, 64):
-            m, _, _, _ = time_decode(llm, tlc, b, args.prompt_len, max(8, args.steps // 2), 3, seed=4 + b)
+        for b in (1, 16, 32, 64):
+            m, _, _, c = time_decode(llm, tlc, b, args.prompt_len, max(16, args.steps // 2), 3, seed=4 + b)
             pts[f"decode_b{b}"] = round(b * 1000.0 / m, 1)
+            pts[f"decode_b{b}_hbm_frac"] = round(decode_bytes(cfg, b, c) / (m * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+        m, _, _, c = time_decode(llm, tlc, 8, 3800, max(16, args.steps // 2), 3, seed=31)
+        pts["decode_b8_ctx3800"] = round(8 * 1000.0 / m, 1)
+        pts["decode_b8_ctx3800_hbm_frac"] = round(decode_bytes(cfg, 8, c) / (m * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         rec["points"] = pts
     if args.generate:
         rec["generate"] = time_generate(llm, tlc, args.generate, 64, 2048, 256, 0.7, seed=9)
+    if args.big and not args.no_points and args.sizes == "1.5B":
+        del llm, model
+        torch.cuda.empty_cache()
+        rec["points"].update(big_workloads(tlc, pk))
+    print(json.dumps(rec))
+    return 0
+
+
+def big_workloads(tlc, pk):
+    """The workloads of the 3B and 7B layer sizes: 16 unequal prompts of 64..2,048 tokens with 256 tokens sampled
+    for each at temperature 0.7 (3B); decode at batch 64 from 1,024-token prompts and one 8,192-token prompt (7B)."""
+    import torch
+    out = {}
+    cfg = CONFIGS["3B"]
+    llm = tlc.LLM(tlc.random_model(cfg, seed=0, dtype="bfloat16"), max_tokens=16 * (2048 + 256 + 64), max_seqs=16)
+    g = time_generate(llm, tlc, 16, 64, 2048, 256, 0.7, seed=9)
+    out["3b_generate_16_tok_s"] = g["tok_s"]
+    out["3b_generate_16_wall_s"] = g["wall_s"]
+    m, _, _, c = time_decode(llm, tlc, 16, 512, 16, 3, seed=41)
+    out["3b_decode_b16"] = round(16 * 1000.0 / m, 1)
+    out["3b_decode_b16_hbm_frac"] = round(decode_bytes(cfg, 16, c) / (m * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+    del llm
+    torch.cuda.empty_cache()
+    cfg = CONFIGS["7B"]
+    llm = tlc.LLM(tlc.random_model(cfg, seed=0, dtype="bfloat16"), max_tokens=64 * 1152, max_seqs=64)
+    m, _, _, c = time_decode(llm, tlc, 64, 1024, 16, 3, seed=42)
+    out["7b_decode_b64"] = round(64 * 1000.0 / m, 1)
+    out["7b_decode_b64_hbm_frac"] = round(decode_bytes(cfg, 64, c) / (m * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+    pms = time_prefill(llm, 8192, seed=43, reps=2)
+    out["7b_prefill_8192_tok_s"] = round(8192 * 1000.0 / pms, 1)
+    out["7b_prefill_8192_bf16_frac"] = round(prefill_flops(cfg, 8192) / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)
+    del llm
+    torch.cuda.empty_cache()
+    return out
+
+
+def reference_arm(args) -> int:
+    """The unmodified reference (its CPU engine, the only path it has for Falcon-H1) on the same layer sizes:
+    decode at batch 1 after a prompt of --prompt-len tokens, and one prompt of --prefill-tokens tokens."""
+    try:
+        from baseline import reference_arm as ra
+        cfg = dict(CONFIGS[args.sizes])
+        steps, warmup = max(1, min(args.steps, 32)), max(3, min(args.warmup, 4))
+        r = ra.measure(cfg, steps, warmup, args.prompt_len, args.prefill_tokens, budget_s=args.ref_budget,
+                       layers=args.layers)
+    except Exception as e:                                  # noqa: BLE001 -- any failure is reported, never raised
+        msg = " ".join(str(e).split())[:300]
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference's CPU engine could not be built or run: {msg}"}))
+        return 0
+    s = sizes(cfg)
+    tok_s = r["steps"] / r["decode_s"]
+    rec = {
+        "impl": "reference",
+        "metric": f"decode tok/s at batch 1 (CodeClaper/tinyllama.c's CPU engine, {r['threads']} threads; Falcon-H1-"
+                  f"{args.sizes} sizes, {args.prompt_len}-token prompt, context {cfg['max_position_embeddings']})",
+        "value": round(tok_s, 3), "unit": "tok/s", "n_gpus": 0, "steps": r["steps"], "warmup": warmup,
+        "ms_per_step": round(1000.0 * r["decode_s"] / r["steps"], 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16 weights, fp32 arithmetic (the reference's CPU path)",
+        "data": "synthetic (random weights in a GGUF file, pseudo-random token ids)",
+        "config": {"model": f"Falcon-H1-{args.sizes} sizes", "global_batch": 1, "seq_len": cfg["max_position_embeddings"],
+                   "prompt_len": args.prompt_len, "parallelism": f"CPU, {r['threads']} threads", "layers": r["layers"],
+                   "layers_full": r["layers_full"], "hidden": cfg["hidden_size"], "heads": f"{s['H']}q/{s['KV']}kv x{s['hd']}",
+                   "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "mamba": f"{s['Hs']} heads x{s['P']}, state {s['N']}, groups {s['G']}, conv {s['K']}",
+                   "tied": cfg["tie_word_embeddings"], "gguf_gb": round(r["gguf_bytes"] / 1e9, 2)},
+        "e2e": {"value": round(tok_s, 3), "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "note": "host token ids in and out is the reference's only interface; no device is involved"},
+        "gpu_launches": 0,
+    }
+    if r["prefill_s"] > 0:
+        rec["prefill"] = {"value": round(args.prefill_tokens / r["prefill_s"], 1), "tokens": args.prefill_tokens,
+                          "ms": round(1000.0 * r["prefill_s"], 1)}
     print(json.dumps(rec))
     return 0
 

@@ -1,13 +1,17 @@
-"""The bfloat16 kernels at the layer sizes of the 1.5B, 3B and 7B models (one layer each, random
-weights) against the library's own 32-bit path, which the tiny configurations tie to the plain
-implementation.  These sizes take the code paths that the tiny ones do not: tcgen05 tiles, the
-tensor-core attention of prompts, the chunked scan in matrix form, the weight-streaming products."""
+"""One layer at the sizes of the 1.5B and 3B models with a small vocabulary against the plain
+implementation, in 32-bit and in bfloat16; and the bfloat16 kernels at the full sizes of the 1.5B, 3B
+and 7B models (vocabulary-sized head included) against the library's own 32-bit path.  These sizes take
+the code paths that the tiny configurations do not: tcgen05 tiles, the tensor-core attention of prompts,
+the chunked scan in matrix form, the weight-streaming products."""
 import numpy as np
 import pytest
 import torch
 
 import tinyllama_c_b200 as tlc
 from tinyllama_c_b200.engine import StepEntry
+
+from helpers import make_model_dir
+from test_gpu_model import check, expected
 
 pytestmark = pytest.mark.gpu
 
@@ -55,3 +59,25 @@ def test_bfloat16_follows_the_32_bit_path_at_model_sizes(name):
     clear = (margin[:, -1] - margin[:, -2]) > 0.05 * scale
     assert (top_ref[clear] == top_got[clear]).all()
 
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["1.5B", "3B"])
+def test_one_layer_at_model_sizes_against_the_plain_implementation(tmp_path, name, dtype):
+    """head size 128, Mamba heads of 64 (1.5B) or 128 (3B) with a state of 256, the real widths; a vocabulary
+    of 512 keeps the plain implementation quick.  A 300-token and a 37-token prompt together, then three
+    single-token steps of both."""
+    cfg = dict(SIZES[name], vocab_size=512, max_position_embeddings=512)
+    d = make_model_dir(tmp_path, cfg, seed=11, std=0.02, name="layer")
+    g = np.random.default_rng(6)
+    prompts = [g.integers(0, cfg["vocab_size"], n).tolist() for n in (300, 37)]
+    want = [expected(d, p, dtype) for p in prompts]
+    llm = tlc.LLM(d, dtype=dtype, max_tokens=1024, max_seqs=2)
+    slots = [llm.cache.acquire() for _ in prompts]
+    got = llm.step([StepEntry(s, p[:-3], [0, len(p) - 4]) for s, p in zip(slots, prompts)]).cpu().numpy()
+    for i, p in enumerate(prompts):
+        check(got[2 * i:2 * i + 2], want[i][[0, len(p) - 4]], dtype, f"{name} layer, prompt {i}")
+    for k in range(3, 0, -1):
+        got = llm.step([StepEntry(s, [p[-k]], [0]) for s, p in zip(slots, prompts)]).cpu().numpy()
+        for i, p in enumerate(prompts):
+            check(got[i:i + 1], want[i][len(p) - k:len(p) - k + 1], dtype, f"{name} layer, token -{k} of prompt {i}")

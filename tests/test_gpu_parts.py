@@ -130,7 +130,8 @@ def test_position_encoding_alone(built, name, dtype):
     def forward(x, step, lc):
         kv = lc.kv[mixer.cache_key]
         q = torch.empty(step.n_rows, H * hd, dtype=DT[dtype], device="cuda")
-        mixer.position.rotate_and_store(x, 0, H * hd, (H + KV) * hd, q, kv, step, H, KV, hd, True)
+        ops.rope_kv_store(x, 0, H * hd, (H + KV) * hd, q, kv.k_pages, kv.v_pages, mixer.position.rotation_table(),
+                          step.positions, step.row_seq, step.slots, kv.block_table, H, KV, hd, True)
         # read the rows' keys and values back from the pages
         pos, seq = step.positions.long(), step.row_seq.long()
         page = kv.block_table[step.slots.long()[seq], pos // 64].long()

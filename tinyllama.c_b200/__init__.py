@@ -18,14 +18,14 @@ import torch
 from . import models as _models  # noqa: F401  (registers the architectures)
 from .cache import Cache, CacheError
 from .config import ConfigError, FalconH1Config, load_config, register_architecture, registered_architectures
-from .engine import EngineBackend, GenerationResult, StepEntry, StepError, generate, step
-from .parts import (KVRequest, LayerRun, LayerSpec, Part, PartSpec, StateRequest, StepInfo, WeightSpec,
+from .engine import Continuation, EngineBackend, GenerationResult, StepEntry, StepError, generate, step
+from .parts import (ChunkRequest, KVRequest, LayerRun, LayerSpec, Part, PartSpec, Position, StateRequest, StepInfo, WeightSpec,
                     register_feed_forward, register_mixer, register_norm, register_position)
 from .sampling import GREEDY, Sampler, SamplingParams
 from .weights import WeightError, build_model, load_model, write_random_model
 
 __all__ = ["LLM", "SamplingParams", "GREEDY", "load_model", "write_random_model", "Cache", "StepEntry", "step",
-           "generate", "GenerationResult", "register_architecture", "register_mixer", "register_feed_forward",
+           "generate", "GenerationResult", "Continuation", "register_architecture", "register_mixer", "register_feed_forward",
            "register_norm", "register_position", "ConfigError", "WeightError", "CacheError", "StepError"]
 
 
@@ -60,44 +60,22 @@ class LLM:
 
     def generate(self, prompts: Sequence[Sequence[int]], params: SamplingParams = SamplingParams(),
                  max_new_tokens: int = 128, stop_ids: Optional[Sequence[int]] = None, max_batch: int = 64,
-                 ignore_eos: bool = False, max_step_tokens: int = 8192) -> List[GenerationResult]:
-        """Token ids in, token ids out (host lists)."""
+                 ignore_eos: bool = False, max_step_tokens: int = 8192,
+                 continuations: Optional[Sequence[Optional[Continuation]]] = None, on_token=None) -> List[GenerationResult]:
+        """Token ids in, token ids out (host lists).  continuations[i] lets request i go on in a slot the
+        caller holds (a further turn of a conversation); on_token(i, token) sees every token as it is made."""
         if stop_ids is None:
             stop_ids = getattr(self.config, "stop_token_ids", ())
         backend = EngineBackend(self.model, self.cache, params, self._graphs, self.use_graphs, max_step_tokens)
         try:
-            return generate(backend, prompts, max_new_tokens, stop_ids, max_batch, self.max_context, ignore_eos)
+            return generate(backend, prompts, max_new_tokens, stop_ids, max_batch, self.max_context, ignore_eos,
+                            continuations, on_token)
         finally:
             self.last_stats = backend.stats
 
 
 def random_model(config: dict, seed: int = 0, dtype: Union[str, torch.dtype] = "bfloat16", device: str = "cuda:0",
                  std: Optional[float] = None, run_dtype: Union[str, torch.dtype, None] = None):
-    """A model with random weights drawn on the device (no folder is written): for benchmarks
-    of configurations too large to be worth a round trip through a file.  `dtype` is what the
-    matrices are stored as, `run_dtype` (default: the same) what the model computes in: bfloat16
-    weights in a float32 run are widened exactly."""
-    from .config import config_from_dict
-    from .weights.loader import run_dtype as _run_dtype
-    cfg = config_from_dict(dict(config))
-    model = build_model(cfg)
-    rd = _run_dtype(dtype)
-    gen = torch.Generator(device=device)
-    gen.manual_seed(seed)
-    std = float(std if std is not None else getattr(cfg, "initializer_range", 0.02))
-    tensors = {}
-    for s in model.weight_specs():
-        if s.init in ("normal", "conv"):
-            t = torch.empty(s.shape, dtype=torch.float32, device=device).normal_(0.0, std, generator=gen).to(rd)
-        elif s.init in ("ones", "d_skip"):
-            t = 1.0 + torch.empty(s.shape, dtype=torch.float32, device=device).normal_(0.0, 0.1, generator=gen)
-        elif s.init == "a_log":
-            t = torch.log(1.0 + 15.0 * torch.rand(s.shape, generator=gen, device=device))
-        elif s.init == "dt_bias":
-            step = torch.exp(torch.rand(s.shape, generator=gen, device=device) * 4.605170186 - 6.907755279)
-            t = step + torch.log(-torch.expm1(-step))
-        else:
-            t = torch.zeros(s.shape, dtype=rd, device=device)
-        tensors[s.name] = t
-    model.bind(tensors, rd if run_dtype is None else _run_dtype(run_dtype), torch.device(device))
-    return model
+    """A model with random weights drawn on the device (see weights.loader.random_model)."""
+    from .weights.loader import random_model as _random_model
+    return _random_model(config, seed, dtype, device, std, run_dtype)

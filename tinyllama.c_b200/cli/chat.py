@@ -23,17 +23,14 @@ def main(argv=None) -> int:
     ap.add_argument("-nt", "--no-thinking", action="store_true", help="ignored (a template switch of the reference)")
     args = ap.parse_args(argv)
     import tinyllama_c_b200 as tlc
-    from tinyllama_c_b200.engine import StepEntry
-    from tinyllama_c_b200.sampling import Sampler
     ctx = args.ctx if args.ctx > 0 else 0
     llm = tlc.LLM(args.model, dtype=args.dtype, max_tokens=ctx or 4096, max_seqs=1)
-    ctx = min(ctx or llm.max_context, llm.max_context)
+    llm.max_context = ctx = min(ctx or llm.max_context, llm.max_context)
     params = sampling_params(args)
-    sampler = Sampler(params, llm.model.device)
-    stop = set() if args.ignore_eos else set(llm.config.stop_token_ids)
     system = parse_ids(args.system) if args.system else []
-    slot, history, n_draw = llm.cache.acquire(), [], 0
-    pending = list(system)
+    # cached: the tokens the slot's cache holds; pending: tokens the next turn opens with (the system prompt
+    # of a new sequence, or the last emitted token of a turn that ended at its budget before the model ran it)
+    slot, cached, pending, n_draw = llm.cache.acquire(), [], list(system), 0
     print("token ids per line; /clear starts over, /quit ends", file=sys.stderr)
     for line in sys.stdin:
         line = line.strip()
@@ -41,35 +38,28 @@ def main(argv=None) -> int:
             break
         if line == "/clear":
             llm.cache.release(slot)
-            slot, history, pending = llm.cache.acquire(), [], list(system)
+            slot, cached, pending = llm.cache.acquire(), [], list(system)
             continue
         turn = pending + parse_ids(line)
-        pending = []
         if not turn:
             continue
-        room = ctx - len(history) - 1
+        room = ctx - len(cached) - 1
         if room <= 0:
             print("context is full; /clear to start over", file=sys.stderr)
             continue
         turn = turn[:room]                                        # chat.c:289-294
-        out = []
-        for i in range(0, len(turn), max(1, args.ubatch)):        # prompt in pieces of at most ubatch tokens
-            chunk = turn[i:i + max(1, args.ubatch)]
-            last = i + len(chunk) >= len(turn)
-            logits = llm.step([StepEntry(slot, chunk, [len(chunk) - 1] if last else [])])
-        history += turn
-        while len(out) < args.tokens and len(history) < ctx:
-            tok = int(sampler.sample(logits, [history], [0], [n_draw]).cpu()[0])
-            n_draw += 1
-            if tok in stop:
-                break
-            out.append(tok)
-            history.append(tok)
-            print(tok, end=" ", flush=True)
-            if len(history) >= ctx:
-                break
-            logits = llm.step([StepEntry(slot, [tok], [0])])
+        pending = []
+        # the turn goes on in the held slot through the same loop as every other generation: prompt in
+        # pieces of at most ubatch tokens, captured decode steps, stop tokens, budget, full context
+        r = llm.generate([turn], params, max_new_tokens=args.tokens, ignore_eos=args.ignore_eos,
+                         max_step_tokens=max(1, args.ubatch),
+                         continuations=[tlc.Continuation(slot, cached, n_draw)],
+                         on_token=lambda i, tok: print(tok, end=" ", flush=True))[0]
         print(flush=True)
+        n_draw += len(r.tokens) + (1 if r.finish_reason == "stop" else 0)
+        run = len(r.tokens) - r.uncached
+        cached = cached + turn + r.tokens[:run]
+        pending = r.tokens[run:]
     llm.cache.release(slot)
     return 0
 

@@ -10,12 +10,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
-#define TLC_F32 0
-#define TLC_BF16 1
+#include "tinyllama_c_b200.h"   // every exported function: a definition that strays from its declaration does not compile
 
-#define TLC_PAGE 64   // tokens per page of the paged key/value store
-
-extern "C" const char* tlc_last_error();
 int tlc_fail(int code, const char* fmt, ...);
 
 #define TLC_CHECK_LAUNCH(name)                                                  \
@@ -37,7 +33,6 @@ int tlc_fail(int code, const char* fmt, ...);
 // loaded): a step is hundreds of short kernels, and this hides the gap between one kernel's last
 // block and the next kernel's first.
 extern int g_tlc_pdl;
-extern "C" void tlc_set_pdl(int on);
 
 //
 // The wait takes the pointers through which the kernel reads what earlier kernels of the stream
@@ -58,8 +53,8 @@ template <typename... P> __device__ __forceinline__ void tlc_pdl(P&... ptrs) {
 }
 
 template <typename... KArgs, typename... Args>
-inline cudaError_t tlc_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              Args&&... args) {
+inline cudaError_t tlc_launch_as(bool programmatic, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -69,8 +64,28 @@ inline cudaError_t tlc_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = g_tlc_pdl ? 1 : 0;
+  cfg.numAttrs = (programmatic && g_tlc_pdl) ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t tlc_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  return tlc_launch_as(true, kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
+}
+
+// The step boundary.  Some kernels fetch, BEFORE their wait, cache contents that an earlier step wrote (a
+// sequence's state, its convolution window, its old keys and values).  With programmatic launches alone that
+// is a matter of timing: the kernel that wrote them may be many launches upstream and still running, since
+// every kernel releases its successor at once.  So the first kernel of every step (the embedding) is launched
+// WITHOUT the programmatic attribute: it starts only when all earlier work of the stream has completed and is
+// visible, and no kernel of the step can be scheduled before it has started.  What a kernel may fetch ahead of
+// its wait is therefore: weights and tables, and cache contents written by an earlier step -- never anything
+// written by a kernel of the same step.
+template <typename... KArgs, typename... Args>
+inline cudaError_t tlc_launch_step_boundary(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t stream, Args&&... args) {
+  return tlc_launch_as(false, kernel, grid, block, smem, stream, static_cast<Args&&>(args)...);
 }
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);

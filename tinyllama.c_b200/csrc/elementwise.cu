@@ -35,8 +35,9 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
 extern "C" int tlc_embed(const int* tokens, const void* table, int table_dtype, int T, int D, int V, float scale,
                          float* out, cudaStream_t stream) {
   if (T == 0) return 0;
-  TLC_DISPATCH_DTYPE(table_dtype, TW,
-                     tlc_launch(embed_kernel<TW>, dim3(T), dim3(256), 0, stream, tokens, (const TW*)table, D, V, scale, out));
+  // the first kernel of a step: a full dependency on everything before it (see tlc_launch_step_boundary)
+  TLC_DISPATCH_DTYPE(table_dtype, TW, tlc_launch_step_boundary(embed_kernel<TW>, dim3(T), dim3(256), 0, stream, tokens,
+                                                               (const TW*)table, D, V, scale, out));
   TLC_CHECK_LAUNCH("embed");
   return 0;
 }

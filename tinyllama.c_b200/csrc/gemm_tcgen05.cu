@@ -26,15 +26,6 @@
 #include <mutex>
 #include <unordered_map>
 
-extern "C" int tlc_linear_simt(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,
-                               int out_dtype, int ldo, const float* colscale, const float* colbias, int accumulate,
-                               int M, int N, int K, cudaStream_t stream);
-
-extern "C" int tlc_linear_skinny_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int M, int K);
-extern "C" int tlc_linear_skinny(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
-                                 const float* colscale, const float* colbias, int accumulate, int M, int N, int K,
-                                 cudaStream_t stream);
-
 namespace {
 
 constexpr int BM = 128;
@@ -460,14 +451,17 @@ int g_sms = 148;
 ErrWords* g_err_dev = nullptr;   // device memory: the flag kernels read + where its host-visible copy lives
 int* g_err_host = nullptr;       // host-mapped word, written by a kernel on failure only
 std::mutex g_mu;
-// Scratch of the products that share a tile's K-steps among blocks: SPLIT_SLOTS launches in turn, so that
-// two such launches that run at the same time (the two mixers' output projections) never share a slot.
-constexpr int SPLIT_SLOTS = 8;
+// Scratch of the products that share a tile's K-steps among blocks: one slot per stream.  Launches of one
+// stream are ordered (a kernel touches the scratch only after its wait on its predecessor), so they share a
+// slot; launches of different streams (two mixers' output projections side by side, two models) never do.
+// A stream beyond the SPLIT_SLOTS-th runs its products without sharing K-steps (a framework's stream pool has
+// a few dozen streams, and every captured graph is recorded on one of them).
+constexpr int SPLIT_SLOTS = 40;
 constexpr size_t SPLIT_SLOT_BYTES = (size_t)8 << 20;       // partial sums of one launch: splits x M x N floats
 constexpr int SPLIT_SLOT_COUNTERS = 4096;                   // 4 per output tile
 float* g_part = nullptr;
 unsigned* g_part_arrivals = nullptr;                        // zero between launches
-std::atomic<unsigned> g_split_seq{0};
+std::unordered_map<cudaStream_t, int> g_split_slot_of;      // guarded by g_mu
 int g_split_override = 0;                                   // test hook: 0 = choose; n = that many splits (1 = none)
 
 struct MapKey {
@@ -523,7 +517,7 @@ int init_once() {
       cudaMemset(g_part_arrivals, 0, SPLIT_SLOTS * SPLIT_SLOT_COUNTERS * sizeof(unsigned)) != cudaSuccess)
     return tlc_fail(-3, "linear: cannot allocate the scratch of split products");
   *g_err_host = 0;
-  ErrWords init{0, host_dev_view};
+  ErrWords init{0, host_dev_view, TLC_WAIT_LIMIT_CYCLES};
   if (cudaMemcpy(g_err_dev, &init, sizeof(init), cudaMemcpyHostToDevice) != cudaSuccess)
     return tlc_fail(-3, "linear: cannot initialise the error words");
   g_encode = (EncodeTiled)fn;
@@ -570,9 +564,16 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, con
            int accumulate, int M, int N, int K, cudaStream_t stream) {
   using S = Smem<BN, STAGES>;
   auto kern = gemm_tcgen05_kernel<TO, BN, STAGES, SWIGLU>;
-  const int splits = SWIGLU ? 1 : pick_splits(M, N, K, BN);
+  int splits = SWIGLU ? 1 : pick_splits(M, N, K, BN);
+  int slot = 0;
+  if (splits > 1) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_split_slot_of.find(stream);
+    if (it != g_split_slot_of.end()) slot = it->second;
+    else if ((int)g_split_slot_of.size() < SPLIT_SLOTS) slot = g_split_slot_of[stream] = (int)g_split_slot_of.size();
+    else splits = 1;
+  }
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * splits;
-  const unsigned slot = splits > 1 ? g_split_seq.fetch_add(1) % SPLIT_SLOTS : 0;
   float* part = g_part + slot * (SPLIT_SLOT_BYTES / sizeof(float));
   unsigned* arrivals = g_part_arrivals + slot * SPLIT_SLOT_COUNTERS;
   dim3 grid(tiles < g_sms ? tiles : g_sms);
@@ -628,11 +629,6 @@ extern "C" int tlc_linear_tcgen05_ok(int a_dtype, int lda, const void* a, int w_
   return a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
          ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0);
 }
-
-// The linear layer of the library: tensor cores where the operands allow it, CUDA cores otherwise.
-extern "C" int tlc_linear_skinny_swiglu(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
-                                        const float* colscale, const float* colbias, int M, int N, int K,
-                                        cudaStream_t stream);
 
 // The fused feed-forward front: out[M, N/2] = silu(gate) * up, where the rows of w come in groups of
 // 16 (8 gate rows, then their 8 up rows) and gate/up = (a w^T) * colscale + colbias.  Returns 1 if no

@@ -2,7 +2,7 @@
 #pragma once
 #include "common.cuh"
 
-constexpr long long TLC_WAIT_LIMIT_CYCLES = 2000000000LL;   // about a second
+constexpr long long TLC_WAIT_LIMIT_CYCLES = 2000000000LL;   // the default limit of a wait: about a second
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -26,12 +26,14 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // Bounded wait: false (and the error code recorded) if the phase does not complete in time.
 // `err` points at two words: [0] in device memory (what kernels read), [1] the address of a
 // host-mapped word that is written on failure only, so that the host can look without a copy.
-struct ErrWords { int flag; int* host; };
+// [2] how many cycles a wait may spin (tlc_wait_limit_cycles sets it; read on the slow path only).
+struct ErrWords { int flag; int* host; long long limit; };
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, ErrWords* err, int code) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
+  const long long limit = *(volatile long long*)&err->limit;
   while (!mbar_try(bar, parity)) {
-    if (clock64() - t0 > TLC_WAIT_LIMIT_CYCLES) {
+    if (clock64() - t0 > limit) {
       atomicExch(&err->flag, code);
       *(volatile int*)err->host = code;
       return false;

@@ -24,6 +24,18 @@ class GenerationResult:
     prompt: List[int]
     tokens: List[int] = field(default_factory=list)
     finish_reason: str = ""              # "stop" | "length" | "context"
+    uncached: int = 0                    # emitted tokens at the end that the model has not run yet (0 or 1)
+
+
+@dataclass
+class Continuation:
+    """A request that goes on in a slot the caller holds (a further turn of a conversation, chat.c:296:
+    history is never recomputed).  `history`: the tokens the slot's cache holds, in order (they count
+    towards the context limit and the penalty window); `draws`: how many tokens were sampled for this
+    sequence before (the sampler's draws are keyed by it).  The slot stays held when generation ends."""
+    slot: int
+    history: Sequence[int] = ()
+    draws: int = 0
 
 
 class EngineBackend:
@@ -60,7 +72,7 @@ class EngineBackend:
         t0 = time.perf_counter()
         decode = all(len(t) == 1 for _, t in entries)
         if decode and self.use_graphs:
-            out = self._graph_step(entries, histories, sequence_ids, steps, uniform)
+            out = self.decode_step(entries, histories, sequence_ids, steps)
         else:
             out = self._prompt_steps(entries, histories, sequence_ids, steps)
         dt = time.perf_counter() - t0
@@ -103,14 +115,25 @@ class EngineBackend:
                 for k, t in zip(finished, toks):
                     out[k] = t
             i = j
+        from .. import ops
+        ops.check_errors()     # the tokens above were read after the step ran: a wait that ran out in it shows here
         return out
 
     MAX_GRAPHS = 24
 
-    def _graph_step(self, entries, histories, sequence_ids, steps, uniform) -> List[int]:
-        """A one-token step through the captured graph of this batch size."""
+    def decode_step(self, entries, histories=None, sequence_ids=None, steps=None) -> List[int]:
+        """A one-token step of every entry through the captured graph of this batch size and context
+        bucket (captured at first use): reserves the positions, uploads the step's integers, replays,
+        reads the sampled tokens back, commits.  Generation and the benchmark both step through here."""
         from .. import ops
+        from ..sampling.sampler import uniform
         from .decode_graph import DecodeGraph
+        if histories is None:
+            histories = [()] * len(entries)
+        if sequence_ids is None:
+            sequence_ids = list(range(len(entries)))
+        if steps is None:
+            steps = [0] * len(entries)
         B = len(entries)
         slots = [s for s, _ in entries]
         positions = [self.cache.reserve(s, 1) for s in slots]
@@ -161,13 +184,21 @@ def plan_batches(prompt_lens: Sequence[int], max_new_tokens: int, max_batch: int
 
 def generate(backend, prompts: Sequence[Sequence[int]], max_new_tokens: int = 128,
              stop_ids: Sequence[int] = (), max_batch: int = 64, max_context: int = 1 << 30,
-             ignore_eos: bool = False) -> List[GenerationResult]:
-    """Generates up to max_new_tokens for every prompt; returns results in the prompts' order."""
+             ignore_eos: bool = False, continuations: Optional[Sequence[Optional[Continuation]]] = None,
+             on_token=None) -> List[GenerationResult]:
+    """Generates up to max_new_tokens for every prompt; returns results in the prompts' order.
+
+    continuations[i], where given, makes request i go on in a slot the caller holds (see Continuation);
+    on_token(i, token) is called for every emitted token as soon as it is known."""
+    conts = list(continuations) if continuations is not None else [None] * len(prompts)
+    if len(conts) != len(prompts):
+        raise ValueError("one continuation (or None) per prompt")
+    past = [list(c.history) if c is not None else [] for c in conts]
     for i, p in enumerate(prompts):
         if len(p) == 0:
             raise ValueError(f"prompt {i} is empty")
-        if len(p) >= max_context:
-            raise ValueError(f"prompt {i} has {len(p)} tokens, the context holds {max_context}")
+        if len(past[i]) + len(p) >= max_context:
+            raise ValueError(f"prompt {i} has {len(past[i]) + len(p)} tokens, the context holds {max_context}")
     results = [GenerationResult(list(p)) for p in prompts]
     if max_new_tokens <= 0:
         for r in results:
@@ -175,18 +206,21 @@ def generate(backend, prompts: Sequence[Sequence[int]], max_new_tokens: int = 12
         return results
     stop = set() if ignore_eos else {int(s) for s in stop_ids}
     free_slots, free_pages = backend.capacity()
-    if free_slots < 1:
+    if free_slots < 1 and any(c is None for c in conts):
         raise ValueError("no free sequence slot")
-    for batch in plan_batches([len(p) for p in prompts], max_new_tokens, max_batch, free_slots, free_pages,
-                              max_context):
-        live = {i: backend.acquire() for i in batch}                   # request -> slot
+    # a request that continues a held slot already owns the pages of its history
+    lens = [len(past[i]) % 64 + len(p) if conts[i] is not None else len(p) for i, p in enumerate(prompts)]
+    n_held = sum(c is not None for c in conts)
+    for batch in plan_batches(lens, max_new_tokens, max_batch, free_slots + n_held, free_pages, max_context):
+        live = {i: (conts[i].slot if conts[i] is not None else backend.acquire()) for i in batch}    # request -> slot
         pending = {i: list(prompts[i]) for i in batch}                 # tokens the next step brings
         n_step = 0
         while live:
             order = sorted(live)
             entries = [(live[i], pending[i]) for i in order]
-            histories = [results[i].prompt + results[i].tokens for i in order]
-            nxt = backend.step_and_sample(entries, histories, order, [n_step] * len(order))
+            histories = [past[i] + results[i].prompt + results[i].tokens for i in order]
+            draws = [n_step + (conts[i].draws if conts[i] is not None else 0) for i in order]
+            nxt = backend.step_and_sample(entries, histories, order, draws)
             n_step += 1
             for i, tok in zip(order, nxt):
                 r = results[i]
@@ -194,12 +228,17 @@ def generate(backend, prompts: Sequence[Sequence[int]], max_new_tokens: int = 12
                     r.finish_reason = "stop"
                 else:
                     r.tokens.append(int(tok))
+                    if on_token is not None:
+                        on_token(i, int(tok))
                     if len(r.tokens) >= max_new_tokens:
                         r.finish_reason = "length"
-                    elif len(r.prompt) + len(r.tokens) >= max_context:    # chat.c:332-335
+                    elif len(past[i]) + len(r.prompt) + len(r.tokens) >= max_context:    # chat.c:332-335
                         r.finish_reason = "context"
+                    r.uncached = 1 if r.finish_reason else 0
                 if r.finish_reason:
-                    backend.release(live.pop(i))
+                    slot = live.pop(i)
+                    if conts[i] is None:
+                        backend.release(slot)
                     pending.pop(i)
                 else:
                     pending[i] = [int(tok)]

@@ -15,9 +15,10 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
+from .. import ops
 from ..cache import Cache, CacheError
 from ..models.model import Model
-from ..parts.base import SCAN_CHUNK, StepInfo
+from ..parts.base import StepInfo
 
 
 @dataclass
@@ -33,9 +34,28 @@ class StepError(ValueError):
     pass
 
 
-def pack(entries: Sequence[StepEntry], starts: Sequence[int], vocab: int, device) -> Tuple[StepInfo, torch.Tensor, int]:
+def chunk_table(lens: Sequence[int], rows: int):
+    """Cuts sequences of `lens` new rows, packed back to back, into chunks of at most `rows` rows:
+    (first packed row of every chunk + the total [n+1], sequence of every chunk [n], first chunk of every
+    sequence [B+1]); None when no sequence is longer than a chunk."""
+    if not any(n > rows for n in lens):
+        return None
+    seg_start, seg_seq, seq_seg_start, t0 = [], [], [0], 0
+    for b, n in enumerate(lens):
+        for off in range(0, n, rows):
+            seg_start.append(t0 + off)
+            seg_seq.append(b)
+        seq_seg_start.append(len(seg_seq))
+        t0 += n
+    seg_start.append(t0)
+    return seg_start, seg_seq, seq_seg_start
+
+
+def pack(entries: Sequence[StepEntry], starts: Sequence[int], vocab: int, device,
+         chunk_rows: Sequence[int] = ()) -> Tuple[StepInfo, torch.Tensor, int]:
     """Host lists -> one int32 buffer -> one copy to the device -> StepInfo views.
-    Returns (step, packed rows whose logits are wanted, their count)."""
+    Returns (step, packed rows whose logits are wanted, their count).  chunk_rows: the chunk lengths
+    that parts of the model asked for (ChunkRequest); the step gets one table for each."""
     tokens, positions, row_seq, cu, want_rows = [], [], [], [0], []
     for b, (e, start) in enumerate(zip(entries, starts)):
         n = len(e.tokens)
@@ -51,19 +71,12 @@ def pack(entries: Sequence[StepEntry], starts: Sequence[int], vocab: int, device
         row_seq += [b] * n
         cu.append(cu[-1] + n)
     T, B, W = len(tokens), len(entries), len(want_rows)
-    # chunk table for recurrent mixers: sequences longer than a chunk are cut so that chunks run in parallel
-    seg_start, seg_seq, seq_seg_start = [], [], [0]
-    if any(len(e.tokens) > SCAN_CHUNK for e in entries):
-        for b, e in enumerate(entries):
-            for off in range(0, len(e.tokens), SCAN_CHUNK):
-                seg_start.append(cu[b] + off)
-                seg_seq.append(b)
-            seq_seg_start.append(len(seg_seq))
-        seg_start.append(T)
-    n_seg = len(seg_seq)
+    lens = [len(e.tokens) for e in entries]
+    tables = {int(r): chunk_table(lens, int(r)) for r in sorted(set(chunk_rows))}
     flat = tokens + positions + row_seq + cu + [e.slot for e in entries] + list(starts) + want_rows
-    if n_seg:
-        flat += seg_start + seg_seq + seq_seg_start
+    for tab in tables.values():
+        if tab is not None:
+            flat += tab[0] + tab[1] + tab[2]
     host = torch.tensor(flat, dtype=torch.int32)
     if torch.device(device).type == "cuda":
         host = host.pin_memory()
@@ -76,14 +89,13 @@ def pack(entries: Sequence[StepEntry], starts: Sequence[int], vocab: int, device
         o += n
         return v
 
-    lens = [len(e.tokens) for e in entries]
     step = StepInfo(n_rows=T, n_seqs=B, tokens=take(T), positions=take(T), row_seq=take(T), cu_seqlens=take(B + 1),
                     slots=take(B), start_pos=take(B), max_new=max(lens) if lens else 0,
                     max_context=max((s + n for s, n in zip(starts, lens)), default=0),
                     host_lens=tuple(lens), host_start=tuple(starts), host_slots=tuple(e.slot for e in entries))
     want = take(W)
-    if n_seg:
-        step.chunks = (take(n_seg + 1), take(n_seg), take(B + 1))
+    for rows, tab in tables.items():
+        step.chunks[rows] = None if tab is None else (take(len(tab[0])), take(len(tab[1])), take(len(tab[2])))
     return step, want, W
 
 
@@ -102,9 +114,10 @@ def step(model: Model, cache: Cache, entries: Sequence[StepEntry]) -> Optional[t
         if len(e.tokens) == 0:
             raise StepError("a step entry brings no tokens")
     starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
-    info, want_rows, n_want = pack(entries, starts, model.vocab, model.device)
+    info, want_rows, n_want = pack(entries, starts, model.vocab, model.device, model.chunk_rows)
     cache.upload_tables()
     logits = model.forward(info, cache, want_rows if n_want else None)
     for e in entries:
         cache.commit(e.slot, len(e.tokens))
+    ops.check_errors()        # a kernel that gave up on a bounded wait (this or an earlier step); does not synchronise
     return logits

@@ -13,7 +13,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .. import ops
-from ..parts.base import LayerCache, LayerRun, LayerSpec, Part, PartSpec, StepInfo, WeightSpec
+from ..parts.base import ChunkRequest, LayerCache, LayerRun, LayerSpec, Part, PartSpec, StateRequest, StepInfo, WeightSpec
 from ..parts.block import Block
 from ..parts.linear import StackedLinear, matrix_dtype
 
@@ -32,6 +32,12 @@ class Model:
                 raise ValueError(f"run-order entry {r} names layer {run.layer}, which does not exist")
             if run.cache is not None and not (0 <= run.cache < len(self.schedule) and self.schedule[run.cache].cache is None):
                 raise ValueError(f"run-order entry {r} reads the cache of entry {run.cache}, which has none of its own")
+            if run.cache is not None and any(isinstance(q, StateRequest) for q in self.layers[run.layer].cache_requests()):
+                raise ValueError(f"run-order entry {r} reads the cache of entry {run.cache} but layer {run.layer} has a "
+                                 f"mixer with state of its own: only keys and values can be read without storing")
+        # chunk lengths that parts want the step function to cut sequences into (one table each, every step)
+        self.chunk_rows = tuple(sorted({q.rows for layer in self.layers for q in layer.step_requests()
+                                        if isinstance(q, ChunkRequest)}))
         self.final_norm = final_norm.build()
         self.embed_name, self.head_name = embed_name, head_name            # head_name None: tied (core.c:1246-1249)
         self.embed_scale = float(embed_scale)
@@ -75,7 +81,11 @@ class Model:
     # ---- forward ------------------------------------------------------------------------------
     def forward(self, step: StepInfo, cache, want_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Runs the step's rows through every scheduled layer; returns float32 logits
-        [n_wanted, vocab] for the packed rows in want_rows (None: no logits)."""
+        [n_wanted, vocab] for the packed rows in want_rows (None: no logits).
+
+        The embedding is the step's first kernel and is launched with a full dependency on everything
+        before it on the stream: kernels of this step may therefore fetch, ahead of their own dependency
+        wait, what earlier steps left in the cache (never what a kernel of this step writes)."""
         x = torch.empty((step.n_rows, self.hidden), dtype=torch.float32, device=self.device)
         ops.embed(step.tokens, self.embed_table, self.embed_scale, x)
         for r, run in enumerate(self.schedule):

@@ -17,37 +17,69 @@ import torch
 from ..csrc import build as _build
 
 F32, BF16 = 0, 1
-PAGE = 64          # tokens per page of the key/value store (TLC_PAGE in common.cuh)
+PAGE = 64          # tokens per page of the key/value store (TLC_PAGE in tinyllama_c_b200.h)
+# What the kernels are built for; a part checks its sizes against these when it is constructed, so that a
+# configuration they do not cover is refused when the model is built, not at its first step.
+MAX_HEAD_DIM = 256        # attention.cu: ATT_MAXD lanes-strided dims of a head (32 * 8)
+MAX_STATE_SIZE = 256      # mamba.cu: state columns a warp keeps in registers (32 * 8)
+MAX_CONV_TAPS = 17        # mamba.cu: CONV_MAX_TAPS + 1
+MAX_HEADS = 65535         # a grid dimension
+SSD_CHUNK = 128           # mamba_ssd.cu: rows of a chunk of the scan in matrix form
 
-_vp, _i, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_vp, _i, _f, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+# Every function that csrc/tinyllama_c_b200.h declares: name -> (result, arguments).  A test parses the
+# header and compares the kinds (pointer, int, float, long long), so that this table cannot drift from
+# the definitions the compiler checked against the same header.
 _SIGNATURES = {
-    "tlc_embed": [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp],
-    "tlc_rmsnorm": [_vp, _vp, _vp, _f, _i, _i, _vp, _i, _vp],
-    "tlc_gated_rmsnorm": [_vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _i, _f, _vp],
-    "tlc_swiglu": [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp],
-    "tlc_gather_rows": [_vp, _vp, _i, _i, _vp, _vp],
-    "tlc_linear_simt": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
-    "tlc_linear": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "tlc_linear_swiglu": [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp],
-    "tlc_rope_kv_store": [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
-                          _i, _vp],
-    "tlc_attention": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp],
-    "tlc_attention_decode": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _i,
-                             _vp],
-    "tlc_attention_decode_fused": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
-                                   _i, _i, _i, _i, _f, _i, _i, _i, _vp],
-    "tlc_attention_decode_fused_ok": [_i, _i, _i],
-    "tlc_attention_decode_fused_passes": [_i],
-    "tlc_attention_prefill": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _vp,
-                              _i, _i, _vp],
-    "tlc_attention_prefill_chunks": [_i, _i, _i, _vp],
-    "tlc_mamba_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
-                       _i, _i, _i, _i, _vp],
-    "tlc_ssm_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
-    "tlc_ssm_scan_chunked": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "tlc_ssm_scan_ssd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
-    "tlc_argmax": [_vp, _i, _i, _vp, _vp],
-    "tlc_sample": [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp],
+    "tlc_last_error": (ctypes.c_char_p, []),
+    "tlc_set_pdl": (None, [_i]),
+    "tlc_linear_init": (_i, []),
+    "tlc_attention_prefill_init": (_i, []),
+    "tlc_ssd_init": (_i, []),
+    "tlc_linear_error": (_i, []),
+    "tlc_linear_error_clear": (None, []),
+    "tlc_wait_limit_cycles": (_i, [_ll]),
+    "tlc_selftest_bounded_wait": (_i, [_vp]),
+    "tlc_embed": (_i, [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp]),
+    "tlc_rmsnorm": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp, _i, _vp]),
+    "tlc_gated_rmsnorm": (_i, [_vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _i, _f, _vp]),
+    "tlc_swiglu": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp]),
+    "tlc_gather_rows": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
+    "tlc_linear": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "tlc_linear_swiglu": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "tlc_linear_simt": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "tlc_linear_skinny_ok": (_i, [_i, _i, _vp, _i, _i, _vp, _i, _i]),
+    "tlc_linear_skinny": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "tlc_linear_skinny_swiglu": (_i, [_vp, _i, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
+    "tlc_linear_tcgen05_ok": (_i, [_i, _i, _vp, _i, _i, _vp, _i]),
+    "tlc_linear_tile_override": (None, [_i]),
+    "tlc_linear_split_override": (None, [_i]),
+    "tlc_rope_kv_store": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
+                               _i, _i, _vp]),
+    "tlc_attention": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp]),
+    "tlc_attention_decode": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
+                                  _i, _vp]),
+    "tlc_attention_decode_fused_ok": (_i, [_i, _i, _i]),
+    "tlc_attention_decode_fused_passes": (_i, [_i]),
+    "tlc_attention_decode_fused": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp,
+                                        _vp, _i, _i, _i, _i, _f, _i, _i, _i, _vp]),
+    "tlc_attention_prefill_ok": (_i, [_i, _i]),
+    "tlc_attention_prefill_chunks": (_i, [_i, _i, _i, _vp]),
+    "tlc_attention_prefill": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
+                                   _vp, _i, _i, _vp]),
+    "tlc_mamba_conv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
+                            _i, _i, _i, _i, _vp]),
+    "tlc_ssm_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "tlc_ssm_scan_chunked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
+                                  _vp]),
+    "tlc_ssd_ok": (_i, [_i, _i, _i, _i, _i]),
+    "tlc_ssd_scratch_floats": (_ll, [_i, _i, _i, _i, _i, _i]),
+    "tlc_ssm_scan_ssd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
+                              _vp]),
+    "tlc_argmax": (_i, [_vp, _i, _i, _vp, _vp]),
+    "tlc_sample": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp]),
+    "tlc_attention_decode_no_alloc": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
+                                           _vp]),
 }
 _lib = None
 
@@ -61,13 +93,10 @@ def library() -> ctypes.CDLL:
     global _lib
     if _lib is None:
         lib = _build.load()
-        for name, argtypes in _SIGNATURES.items():
+        for name, (restype, argtypes) in _SIGNATURES.items():
             fn = getattr(lib, name)
             fn.argtypes = argtypes
-            fn.restype = ctypes.c_int
-        lib.tlc_last_error.restype = ctypes.c_char_p
-        lib.tlc_linear_error.restype = ctypes.c_int
-        lib.tlc_ssd_scratch_floats.restype = ctypes.c_longlong
+            fn.restype = restype
         _lib = lib
         if torch.cuda.is_available():                                     # before any stream capture
             for init in (lib.tlc_linear_init, lib.tlc_attention_prefill_init, lib.tlc_ssd_init):
@@ -120,6 +149,11 @@ def _gpu(*tensors) -> None:
         if t is not None and not t.is_cuda:
             raise KernelError("tinyllama.c_b200 kernels run on a CUDA device only (got a CPU tensor); "
                               "there is no CPU path")
+
+
+def _gpu_required() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError("tinyllama.c_b200 kernels need a CUDA device; there is no CPU path")
 
 
 def _rows(t: torch.Tensor, what: str) -> int:
@@ -269,8 +303,23 @@ def check_errors() -> None:
     code = library().tlc_linear_error()
     if code:
         library().tlc_linear_error_clear()
-        raise KernelError(f"a tensor-core linear kernel gave up waiting (code {code}: 1 loader, 2 issuer, "
-                          f"3 epilogue, 4 drain); its output is incomplete")
+        raise KernelError(f"a kernel gave up on a bounded wait (code {code}: 1 loader, 2 issuer, 3 epilogue, 4 drain, "
+                          f"5 accumulator of the tensor-core product; 9 the self-test); its output is incomplete")
+
+
+def wait_limit_cycles(cycles: int) -> None:
+    """How many clock cycles a bounded wait inside a kernel may spin before it gives up and reports
+    (0: the default, about a second)."""
+    lib = library()
+    if lib.tlc_wait_limit_cycles(int(cycles)) != 0:
+        raise KernelError(f"tlc_wait_limit_cycles: {lib.tlc_last_error().decode()}")
+
+
+def selftest_bounded_wait() -> None:
+    """Launches the error channel's self-test: a block waits on a barrier nobody arrives at, gives up at the
+    limit and records code 9; check_errors() raises once the kernel has run."""
+    _gpu_required()
+    _call("tlc_selftest_bounded_wait", _stream())
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale: Optional[torch.Tensor] = None,
@@ -365,7 +414,10 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
 
 
 DISABLE_FUSED_DECODE_ATTENTION = bool(int(os.environ.get("TLC_DISABLE_FUSED_DECODE_ATTENTION", "0")))
-_arrivals: dict = {}      # device -> counters of the fused single-token attention (zero between launches)
+# (device, stream) -> arrival counters of the fused single-token attention (zero between launches).  Launches
+# of one stream are ordered, so they can share counters; two models, or two streams of one model, that run at
+# the same time each get their own.
+_arrivals: dict = {}
 
 
 def attention_decode_fused_ok(qkv: torch.Tensor, cache_dtype: torch.dtype, H: int, KV: int, hd: int) -> bool:
@@ -399,11 +451,10 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
     n_splits = (int(max_keys) + 127) // 128
     part_o = torch.empty((T, H, n_splits, hd), dtype=torch.float32, device=qkv.device)
     part_ml = torch.empty((T, H, n_splits, 2), dtype=torch.float32, device=qkv.device)
-    # One array of counters per device: launches that use it must not overlap on the GPU (those of
-    # one model never do: its attention layers follow one another).
-    arrivals = _arrivals.get(qkv.device.index)
+    key = (qkv.device.index, _stream())
+    arrivals = _arrivals.get(key)
     if arrivals is None or arrivals.numel() < T * KV:
-        arrivals = _arrivals[qkv.device.index] = torch.zeros(max(65536, 2 * T * KV), dtype=torch.int32, device=qkv.device)
+        arrivals = _arrivals[key] = torch.zeros(max(65536, 2 * T * KV), dtype=torch.int32, device=qkv.device)
     _call("tlc_attention_decode_fused", qkv.data_ptr(), ld, q_off, k_off, v_off, k_pages.data_ptr(), v_pages.data_ptr(),
           inv_freq.data_ptr(), 2 * inv_freq.numel(), int(bool(write_kv)), block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(), out.data_ptr(), part_o.data_ptr(),

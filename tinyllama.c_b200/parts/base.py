@@ -11,11 +11,13 @@ choose a different mixer or feed-forward for every layer.
 Interfaces
 ----------
 Norm          forward(x32 [R, D] float32, out [R, D], rows=None)
-Position      rotate_and_store(qkv, offsets, q_out, kv, step, n_heads, n_kv, head_dim, write)
+Position      rotation_table() -> inverse frequencies (the kernels rotate q and k themselves), or None and
+              transform(qkv, q_off, k_off, step, n_heads, n_kv, head_dim): changes the q and k columns of
+              the 32-bit projection in place; storing keys and values is the mixer's business
 Mixer         forward(normed [T, D], step, cache, residual [T, D] float32)  adds its output into residual
 FeedForward   forward(normed [T, D], residual [T, D] float32)               adds its output into residual
 All of them   weight_specs() -> [WeightSpec], bind(tensors, dtype, device)
-Mixers also   cache_requests() -> [KVRequest | StateRequest]
+Mixers also   cache_requests() -> [KVRequest | StateRequest], step_requests() -> [ChunkRequest]
 """
 from __future__ import annotations
 
@@ -53,6 +55,16 @@ class StateRequest:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class ChunkRequest:
+    """A table, built by the step function for every step, that cuts each sequence's new rows into
+    chunks of at most ``rows`` rows (a recurrent mixer scans chunks in parallel and carries the state
+    between them).  The mixer finds it as ``step.chunks[rows]``: None when no sequence of the step is
+    longer than a chunk, else (first row of every chunk [n+1], sequence of every chunk [n], first chunk
+    of every sequence [B+1]), int32 on the device."""
+    rows: int
+
+
 # ---- what a step gives every part ------------------------------------------------------------
 @dataclass
 class StepInfo:
@@ -75,12 +87,8 @@ class StepInfo:
     host_lens: Tuple[int, ...] = ()
     host_start: Tuple[int, ...] = ()
     host_slots: Tuple[int, ...] = ()
-    # sequences cut into chunks of SCAN_CHUNK rows (None when no sequence is longer than a chunk):
-    # (first row of every chunk [n+1], sequence of every chunk [n], first chunk of every sequence [B+1])
-    chunks: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None
-
-
-SCAN_CHUNK = 128      # rows per chunk of a recurrent mixer's parallel scan
+    # one table per chunk length that a part asked for with a ChunkRequest (see there)
+    chunks: Dict[int, Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]] = field(default_factory=dict)
 
 
 @dataclass
@@ -112,6 +120,29 @@ class Part:
 
     def cache_requests(self) -> list:
         return []
+
+    def step_requests(self) -> list:
+        """What the step function must prepare for this part in every step (ChunkRequest)."""
+        return []
+
+
+class Position(Part):
+    """Base of position encodings of an attention mixer.  A part answers one of two ways:
+
+    * ``rotation_table()`` returns inverse frequencies (float32 [r/2], r <= head_dim; an empty tensor
+      rotates nothing): q and k are rotated split-half by angle = position * frequency inside the
+      kernels that store keys and values, and single-token attention does all of it in one kernel;
+    * it returns None and ``transform(qkv, q_off, k_off, step, n_heads, n_kv, head_dim)`` changes the q
+      columns [q_off, q_off + n_heads*head_dim) and the k columns of the 32-bit projection ``qkv``
+      [T, *] in place, in whatever way it likes (``step.positions`` holds the rows' positions); the
+      mixer then stores keys and values and attends.  A part that leaves q and k alone does nothing."""
+
+    def rotation_table(self) -> Optional[torch.Tensor]:
+        return None
+
+    def transform(self, qkv: torch.Tensor, q_off: int, k_off: int, step: "StepInfo", n_heads: int, n_kv: int,
+                  head_dim: int) -> None:
+        pass
 
 
 # ---- registries -------------------------------------------------------------------------------

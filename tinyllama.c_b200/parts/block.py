@@ -41,6 +41,9 @@ class Block(Part):
     def cache_requests(self) -> list:
         return [r for m in self.mixers for r in m.cache_requests()]
 
+    def step_requests(self) -> list:
+        return [r for p in self.parts() for r in p.step_requests()]
+
     def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
         self.dtype = dtype
         for p in self.parts():

@@ -25,6 +25,11 @@ class AttentionMixer(Part):
                  out_scale: float = 1.0, key_scale: float = 1.0, cache_key: str = "kv"):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} key/value heads")
+        if not (1 <= int(head_dim) <= ops.MAX_HEAD_DIM):
+            raise ValueError(f"attention: head size {head_dim} is outside what the kernels are built for "
+                             f"(1..{ops.MAX_HEAD_DIM})")
+        if int(n_heads) > ops.MAX_HEADS:
+            raise ValueError(f"attention: {n_heads} heads exceed the kernels' limit of {ops.MAX_HEADS}")
         self.hidden, self.H, self.KV, self.hd = int(hidden), int(n_heads), int(n_kv_heads), int(head_dim)
         self.window = int(window) if window else None
         self.cache_key = cache_key
@@ -43,7 +48,7 @@ class AttentionMixer(Part):
         """Kernels that mix() launches in a one-token step: one where the fused kernel serves (a
         bfloat16 cache, a head size it is built for, a position part with a rotation table), else
         rotation + split keys + merge."""
-        fused = self.dtype == torch.bfloat16 and hasattr(self.position, "rotation_table") \
+        fused = self.dtype == torch.bfloat16 and self.position.rotation_table() is not None \
             and ops.library().tlc_attention_decode_fused_ok(self.H, self.KV, self.hd) \
             and not ops.DISABLE_FUSED_DECODE_ATTENTION
         return 1 if fused else 3
@@ -59,6 +64,7 @@ class AttentionMixer(Part):
         self.qkv.bind(tensors, dtype, device)
         self.o.bind(tensors, dtype, device)
         self.position.bind(tensors, dtype, device)
+        self._no_rotation = torch.zeros(0, dtype=torch.float32, device=device)
 
     def input_projection(self) -> StackedLinear:
         """What this mixer computes from the normed input before anything else (a block may stack
@@ -84,18 +90,22 @@ class AttentionMixer(Part):
         to `out` (rows may be strided) where one is given."""
         T = step.n_rows
         kv = cache.kv[self.cache_key]
-        table = getattr(self.position, "rotation_table", None)
-        if step.max_new == 1 and table is not None and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
+        table = self.position.rotation_table()
+        if table is None:
+            # not a rotation: the part changes q and k in place; what is stored below is its result
+            self.position.transform(qkv, self.q_off, self.k_off, step, self.H, self.KV, self.hd)
+            table = self._no_rotation
+        if step.max_new == 1 and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
             # one token per sequence: rotation, store and attention in one kernel
             att = out if out is not None else torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
-            ops.attention_decode_fused(qkv, self.q_off, self.k_off, self.v_off, kv.k_pages, kv.v_pages, table(),
+            ops.attention_decode_fused(qkv, self.q_off, self.k_off, self.v_off, kv.k_pages, kv.v_pages, table,
                                        cache.writes, kv.block_table, step.positions, step.row_seq, step.slots, att,
                                        self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
                                        step.max_context)
             return att
         q = torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
-        self.position.rotate_and_store(qkv, self.q_off, self.k_off, self.v_off, q, kv, step, self.H, self.KV, self.hd,
-                                       cache.writes)
+        ops.rope_kv_store(qkv, self.q_off, self.k_off, self.v_off, q, kv.k_pages, kv.v_pages, table, step.positions,
+                          step.row_seq, step.slots, kv.block_table, self.H, self.KV, self.hd, cache.writes)
         att = out if out is not None else torch.empty_like(q)
         ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
                       self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,

@@ -18,7 +18,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ... import ops
-from ..base import LayerCache, Part, StateRequest, StepInfo, WeightSpec, act_empty, register_mixer, to_vec
+from ..base import ChunkRequest, LayerCache, Part, StateRequest, StepInfo, WeightSpec, act_empty, register_mixer, to_vec
 from ..linear import StackedLinear
 
 
@@ -29,14 +29,27 @@ class Mamba2Mixer(Part):
     def __init__(self, hidden: int, d_ssm: int, n_heads: int, d_head: int, n_groups: int, d_state: int, d_conv: int,
                  prefix: str, eps: float, conv_bias: bool = True, proj_bias: bool = False, rms_norm: bool = True,
                  norm_before_gate: bool = False, slice_scales: Sequence[float] = (1.0,) * 5, in_scale: float = 1.0,
-                 out_scale: float = 1.0, cache_key: str = "mamba"):
+                 out_scale: float = 1.0, cache_key: str = "mamba", scan_chunk: int = ops.SSD_CHUNK):
         if n_heads * d_head != d_ssm or n_heads % n_groups or d_ssm % n_groups:
             raise ValueError("mamba2: n_heads*d_head must equal d_ssm and both be multiples of n_groups")
+        if not (1 <= int(d_state) <= ops.MAX_STATE_SIZE):
+            raise ValueError(f"mamba2: state size {d_state} is outside what the kernels are built for "
+                             f"(1..{ops.MAX_STATE_SIZE})")
+        if not (1 <= int(d_conv) <= ops.MAX_CONV_TAPS):
+            raise ValueError(f"mamba2: {d_conv} convolution taps are outside what the kernels are built for "
+                             f"(1..{ops.MAX_CONV_TAPS})")
+        if int(n_heads) > ops.MAX_HEADS:
+            raise ValueError(f"mamba2: {n_heads} heads exceed the kernels' limit of {ops.MAX_HEADS}")
         self.hidden, self.Di, self.Hs, self.P = int(hidden), int(d_ssm), int(n_heads), int(d_head)
         self.G, self.N, self.K = int(n_groups), int(d_state), int(d_conv)
         self.Cd = self.Di + 2 * self.G * self.N                      # falcon_h1.c:124
         self.eps, self.rms_norm, self.norm_before_gate = float(eps), bool(rms_norm), bool(norm_before_gate)
         self.prefix, self.cache_key = prefix, cache_key
+        # rows of a chunk of the parallel scan of prompts: the result does not depend on it (the state is
+        # linear in its initial value); the tensor-core form takes chunks of ops.SSD_CHUNK rows only
+        self.scan_chunk = int(scan_chunk)
+        if self.scan_chunk < 1:
+            raise ValueError(f"mamba2: a scan chunk of {scan_chunk} rows")
         self.conv_bias = bool(conv_bias)
         mz, mx, mb, mc, mdt = [float(v) for v in slice_scales]
         rows = [mz] * self.Di + [mx] * self.Di + [mb] * (self.G * self.N) + [mc] * (self.G * self.N) + [mdt] * self.Hs
@@ -65,6 +78,9 @@ class Mamba2Mixer(Part):
     def cache_requests(self) -> list:
         return [StateRequest(self.cache_key + ".conv", (self.K - 1, self.Cd)),
                 StateRequest(self.cache_key + ".ssm", (self.Hs, self.P, self.N))]
+
+    def step_requests(self) -> list:
+        return [ChunkRequest(self.scan_chunk)]
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
         p = self.prefix
@@ -101,6 +117,9 @@ class Mamba2Mixer(Part):
         """Everything between the input projection and the output projection: [T, d_ssm] times
         out_scale, written to `out` (rows may be strided) where one is given.  (A block that runs
         several output projections as one product moves a part of this one's multiplier here.)"""
+        if not cache.writes:
+            raise ValueError("mamba2: a recurrent mixer cannot run on another layer's cache without storing "
+                             "(its window and state would advance twice in one step)")
         T, f32 = step.n_rows, torch.float32
         conv_state = cache.state[self.cache_key + ".conv"]
         ssm_state = cache.state[self.cache_key + ".ssm"]
@@ -111,7 +130,8 @@ class Mamba2Mixer(Part):
                        step.max_new == 1, self.dtype == torch.bfloat16)
         y = new((T, self.Di), f32)
         ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs, self.P,
-                     self.N, self.G, step.chunks, self.A if self.dtype == torch.bfloat16 else None)
+                     self.N, self.G, step.chunks.get(self.scan_chunk),
+                     self.A if self.dtype == torch.bfloat16 and self.scan_chunk == ops.SSD_CHUNK else None)
         gated = out if out is not None else new((T, self.Di), self.dtype)
         ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated,
                           out_scale)

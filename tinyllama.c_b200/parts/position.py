@@ -5,8 +5,10 @@ theta_i = 1/base^(2i/r), angle = position * theta_i, (a, b) = (x[i], x[i + r/2])
 (a cos - b sin, a sin + b cos); dims past r are copied (CodeClaper/tinyllama.c
 cpu_op.c:637-651).  The reference recomputes powf/cosf/sinf per element; here the
 inverse frequencies are a table built once in 64-bit and rounded to 32-bit, and the
-angle is the 32-bit product with the integer position.  The rotation is fused with the
-store of keys and values into the cache pages.  "none" rotates nothing.
+angle is the 32-bit product with the integer position.  A rotation is described to the
+mixer by its table: the kernels that store keys and values (and single-token attention)
+rotate by themselves.  "none" rotates nothing.  Any other encoding of positions in q and k
+is a Position part with a transform() of its own (see parts/base.py).
 """
 from __future__ import annotations
 
@@ -14,12 +16,11 @@ from typing import Optional
 
 import torch
 
-from .. import ops
-from .base import KVView, Part, StepInfo, register_position
+from .base import Position, register_position
 
 
 @register_position("rope_neox")
-class RotaryNeox(Part):
+class RotaryNeox(Position):
     def __init__(self, head_dim: int, theta: float, rope_dim: Optional[int] = None):
         self.head_dim = int(head_dim)
         self.rope_dim = int(rope_dim) if rope_dim else self.head_dim      # falcon_h1.c:265
@@ -33,14 +34,8 @@ class RotaryNeox(Part):
         inv = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64), 2.0 * i / self.rope_dim)
         self.inv_freq = inv.to(torch.float32).to(device).contiguous()
 
-    def rotate_and_store(self, qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor,
-                         kv: KVView, step: StepInfo, n_heads: int, n_kv: int, head_dim: int, write: bool) -> None:
-        ops.rope_kv_store(qkv, q_off, k_off, v_off, q_out, kv.k_pages, kv.v_pages, self.inv_freq, step.positions,
-                          step.row_seq, step.slots, kv.block_table, n_heads, n_kv, head_dim, write)
-
-
     def rotation_table(self) -> torch.Tensor:
-        """The inverse frequencies (float32 [rope_dim/2]) for kernels that rotate by themselves."""
+        """The inverse frequencies (float32 [rope_dim/2]) for the kernels, which rotate by themselves."""
         return self.inv_freq
 
 

@@ -99,36 +99,57 @@ def _generator(seed: int, name: str) -> torch.Generator:
     return g
 
 
+def draw_tensor(spec, generator: torch.Generator, dtype: torch.dtype, std: float, norm_std: float = 0.1) -> torch.Tensor:
+    """One weight by its init rule, drawn from `generator` on the generator's device.  Matrices,
+    embeddings, biases and conv taps are N(0, std), norm weights 1 + N(0, norm_std), A_log =
+    log U(1, 16), dt_bias the inverse softplus of a log-uniform time step in [1e-3, 0.1], D = 1 +
+    N(0, norm_std).  Matrices are stored in `dtype`; the per-head SSM constants in float32."""
+    dev, f32 = generator.device, torch.float32
+    if spec.init in ("normal", "conv"):
+        t = torch.empty(spec.shape, dtype=f32, device=dev).normal_(0.0, std, generator=generator).to(dtype)
+    elif spec.init == "ones":
+        t = (1.0 + torch.empty(spec.shape, dtype=f32, device=dev).normal_(0.0, norm_std, generator=generator)).to(dtype)
+    elif spec.init == "zeros":
+        t = torch.zeros(spec.shape, dtype=dtype, device=dev)
+    elif spec.init == "a_log":
+        t = torch.log(1.0 + 15.0 * torch.rand(spec.shape, generator=generator, dtype=f32, device=dev))
+    elif spec.init == "dt_bias":
+        u = torch.rand(spec.shape, generator=generator, dtype=f32, device=dev)
+        step = torch.exp(u * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3))
+        t = step + torch.log(-torch.expm1(-step))
+    elif spec.init == "d_skip":
+        t = 1.0 + torch.empty(spec.shape, dtype=f32, device=dev).normal_(0.0, norm_std, generator=generator)
+    else:
+        raise ValueError(f"weight {spec.name}: unknown init rule '{spec.init}'")
+    return t.contiguous()
+
+
 def random_tensors(model: Model, seed: int, dtype: torch.dtype = torch.bfloat16, std: Optional[float] = None,
                    norm_std: float = 0.1) -> Dict[str, torch.Tensor]:
-    """One tensor per declared weight, each drawn from its own generator keyed by (seed, name),
-    so a tensor does not depend on which others exist.  Matrices, embeddings, biases and conv
-    taps are N(0, std) (std defaults to the config's initializer_range, else 0.02), norm
-    weights 1 + N(0, norm_std), A_log = log U(1, 16), dt_bias the inverse softplus of a
-    log-uniform time step in [1e-3, 0.1], D = 1 + N(0, norm_std).  Matrices are stored in
-    `dtype`; the per-head SSM constants in float32."""
+    """One tensor per declared weight (see draw_tensor), each drawn from its own generator keyed by
+    (seed, name), so a tensor does not depend on which others exist; std defaults to the config's
+    initializer_range, else 0.02."""
     std = float(std if std is not None else getattr(model.config, "initializer_range", 0.02))
-    out = {}
-    for s in model.weight_specs():
-        g = _generator(seed, s.name)
-        if s.init in ("normal", "conv"):
-            t = (torch.randn(s.shape, generator=g, dtype=torch.float32) * std).to(dtype)
-        elif s.init == "ones":
-            t = (1.0 + torch.randn(s.shape, generator=g, dtype=torch.float32) * norm_std).to(dtype)
-        elif s.init == "zeros":
-            t = torch.zeros(s.shape, dtype=dtype)
-        elif s.init == "a_log":
-            t = torch.log(1.0 + 15.0 * torch.rand(s.shape, generator=g, dtype=torch.float32))
-        elif s.init == "dt_bias":
-            u = torch.rand(s.shape, generator=g, dtype=torch.float32)
-            step = torch.exp(u * (math.log(0.1) - math.log(1e-3)) + math.log(1e-3))
-            t = step + torch.log(-torch.expm1(-step))
-        elif s.init == "d_skip":
-            t = 1.0 + torch.randn(s.shape, generator=g, dtype=torch.float32) * norm_std
-        else:
-            raise ValueError(f"weight {s.name}: unknown init rule '{s.init}'")
-        out[s.name] = t.contiguous()
-    return out
+    return {s.name: draw_tensor(s, _generator(seed, s.name), dtype, std, norm_std) for s in model.weight_specs()}
+
+
+def random_model(config: Union[ModelConfig, dict], seed: int = 0, dtype: Union[str, torch.dtype] = "bfloat16",
+                 device: str = "cuda:0", std: Optional[float] = None,
+                 compute_dtype: Union[str, torch.dtype, None] = None) -> Model:
+    """A model bound to random weights drawn on `device` by the rules of draw_tensor (one generator for
+    all tensors; no folder is written): for benchmarks of configurations too large to be worth a round
+    trip through a file.  `dtype` is what the matrices are stored as, `compute_dtype` (default: the same)
+    what the model computes in: bfloat16 weights in a float32 run are widened exactly."""
+    if isinstance(config, dict):
+        config = config_from_dict(dict(config))
+    model = build_model(config)
+    rd = run_dtype(dtype)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    std = float(std if std is not None else getattr(config, "initializer_range", 0.02))
+    tensors = {s.name: draw_tensor(s, gen, rd, std) for s in model.weight_specs()}
+    model.bind(tensors, rd if compute_dtype is None else run_dtype(compute_dtype), torch.device(device))
+    return model
 
 
 def write_random_model(config: Union[ModelConfig, dict], out_dir: str, seed: int = 0,
