@@ -54,8 +54,9 @@ def derived(cfg: dict) -> dict:
 def bf16_round(x):
     """Round to the nearest bfloat16 (ties to even), keeping the array's type.  Passed as
     ``rnd`` to forward() it models a bfloat16 engine that keeps 32-bit accumulators: the
-    inputs of every matrix product and the stored queries, keys and values are rounded,
-    nothing else is."""
+    inputs of every matrix product are rounded -- activations that a projection reads, the
+    stored queries, keys and values, the softmax numerators that multiply the values, and
+    x|B|C as the convolution hands them to the scan -- nothing else is."""
     x32 = np.ascontiguousarray(x, dtype=np.float32)
     u = x32.view(np.uint32).astype(np.uint64)
     u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
@@ -120,12 +121,13 @@ def rope_neox(x, positions, n_heads, head_dim, rope_dim, theta):
     return x.reshape(T, n_heads * head_dim)
 
 
-def causal_attention(q, k, v, n_heads, n_kv, head_dim, window=0):
+def causal_attention(q, k, v, n_heads, n_kv, head_dim, window=0, rnd=_same):
     """Causal grouped-query attention of one whole sequence (cpu_op.c:1010-1062).
 
     kv head = h / (H/KV); keys 0..p inclusive; scale 1/sqrt(head_dim)
     (graph.c:1275); softmax with max subtraction (cpu_op.c:338-349); a window w
-    keeps the last w keys including the current one (cpu_op.c:1019-1022)."""
+    keeps the last w keys including the current one (cpu_op.c:1019-1022).  rnd rounds the
+    softmax numerators where they enter the product with the values (their sum is exact)."""
     T = q.shape[0]
     q = q.reshape(T, n_heads, head_dim)
     k = k.reshape(T, n_kv, head_dim)
@@ -140,8 +142,7 @@ def causal_attention(q, k, v, n_heads, n_kv, head_dim, window=0):
             start = n_keys - window if (window and n_keys > window) else 0
             s = (k[start:n_keys, g] @ q[t, h]) * scale
             e = np.exp(s - s.max())
-            p = e / e.sum()
-            out[t, h] = p @ v[start:n_keys, g]
+            out[t, h] = (rnd(e) @ v[start:n_keys, g]) / e.sum()
     return out.reshape(T, n_heads * head_dim)
 
 
@@ -211,7 +212,7 @@ def attention_mixer(n, W, pre, cfg, d, positions, rnd=_same):
     rope_dim = d["hd"]                                         # falcon_h1.c:265
     q = rnd(rope_neox(q, positions, d["H"], d["hd"], rope_dim, theta))
     k = rnd(rope_neox(k, positions, d["KV"], d["hd"], rope_dim, theta))
-    o = causal_attention(q, k, rnd(v), d["H"], d["KV"], d["hd"], int(_get(cfg, "sliding_window", 0) or 0))
+    o = causal_attention(q, k, rnd(v), d["H"], d["KV"], d["hd"], int(_get(cfg, "sliding_window", 0) or 0), rnd)
     return linear(rnd(o), W[pre + "self_attn.o_proj.weight"], W.get(pre + "self_attn.o_proj.bias"))
 
 
@@ -233,7 +234,7 @@ def mamba2_mixer(n, W, pre, cfg, d, rnd=_same, round_at_scale=1.0):
     proj = proj * mup
     z, xbc, dt = proj[:, :Di], proj[:, Di:Di + Cd], proj[:, Di + Cd:]
     cw = W[pre + "mamba.conv1d.weight"].reshape(Cd, -1)
-    cv = mamba2_conv(xbc, cw, W.get(pre + "mamba.conv1d.bias"))
+    cv = rnd(mamba2_conv(xbc, cw, W.get(pre + "mamba.conv1d.bias")))      # the scan's operands
     x, B, C = cv[:, :Di], cv[:, Di:Di + G * N], cv[:, Di + G * N:]
     A = -np.exp(W[pre + "mamba.A_log"].astype(n.dtype))       # cpu_op.c:806-808, 934
     y = mamba2_scan(x, B, C, dt, A, W[pre + "mamba.D"], W[pre + "mamba.dt_bias"],

@@ -131,7 +131,7 @@ def attention(q, k_pages, v_pages, block_table, positions, row_seq, slots, out, 
 
 
 def mamba_conv(proj, xbc_off, dt_off, w, bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos,
-               xbc_out, dt_out, dA_out, single_rows=False, quick=False):
+               xbc_out, dt_out, dA_out, single_rows=False, bf16_run=False):
     Cd, K = w.shape
     Hs = dt_bias.numel()
     wf = _f(w)
@@ -148,7 +148,10 @@ def mamba_conv(proj, xbc_off, dt_off, w, bias, dt_bias, A, conv_state, cu_seqlen
             acc += full[k:k + (t1 - t0)] * wf[:, k][None, :]
         if bias is not None:
             acc = acc + _f(bias)
-        xbc_out[t0:t1] = (acc / (1.0 + torch.exp(-acc))).to(xbc_out.dtype)
+        act = acc / (1.0 + torch.exp(-acc))
+        if bf16_run:
+            act = act.to(torch.bfloat16).to(torch.float64)
+        xbc_out[t0:t1] = act.to(xbc_out.dtype)
         if K > 1:
             conv_state[slot] = full[-(K - 1):].to(conv_state.dtype)
     d = _f(proj[:, dt_off:dt_off + Hs]) + _f(dt_bias)

@@ -28,9 +28,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 # rounded to bfloat16 at the same places).  What remains is 32-bit accumulation order, which now
 # and then tips a rounding by 2^-8 of a value; the allowance is the rounding noise itself: the
 # engine must agree with the bfloat16 model at least as closely as that model agrees with exact
-# arithmetic on the same request (`Want.noise_max`, `Want.noise_mean`; measured: the engine uses
-# less than half of it).  A cache or batching fault moves logits by about their own size,
-# fifty times more.
+# arithmetic on the same request (`Want.noise_max`, `Want.noise_mean`).  Where only a few rows are
+# compared (a single decoded token), their mean error is held to the mean noise of the request's
+# noisiest row instead of the request-wide mean: one row's mean is not an average over rows, and rows
+# differ in noise by a factor of two or three.  A cache or batching fault moves logits by about their
+# own size, fifty times more.
 TOL = {"float32": 1e-4}
 MEAN_TOL = {"float32": 2e-5}
 
@@ -38,15 +40,17 @@ MEAN_TOL = {"float32": 2e-5}
 class Want(np.ndarray):
     """Expected logits [T, V] that carry the request's allowance in absolute units."""
 
-    def __new__(cls, arr, noise_max, noise_mean):
+    def __new__(cls, arr, noise_max, noise_mean, noise_row_mean=None):
         o = np.asarray(arr).view(cls)
         o.noise_max, o.noise_mean = float(noise_max), float(noise_mean)
+        o.noise_row_mean = float(noise_row_mean if noise_row_mean is not None else noise_mean)
         return o
 
     def __array_finalize__(self, obj):
         if obj is not None:
             self.noise_max = getattr(obj, "noise_max", None)
             self.noise_mean = getattr(obj, "noise_mean", None)
+            self.noise_row_mean = getattr(obj, "noise_row_mean", None)
 
 
 def expected(model_dir, toks, dtype) -> Want:
@@ -56,15 +60,16 @@ def expected(model_dir, toks, dtype) -> Want:
         return Want(exact, TOL[dtype] * scale, MEAN_TOL[dtype] * scale)
     model = plain_logits(model_dir, toks, "bfloat16")
     noise = np.abs(model - exact)
-    return Want(model, noise.max(), noise.mean())
+    return Want(model, noise.max(), noise.mean(), noise.mean(axis=1).max())
 
 
 def check(got, want, dtype, what):
     err = np.abs(got - np.asarray(want))
+    mean_allowed = want.noise_mean if err.shape[0] >= 8 else want.noise_row_mean
     record(dtype, "max", err.max() / want.noise_max)
-    record(dtype, "mean", err.mean() / want.noise_mean)
+    record(dtype, "mean", err.mean() / mean_allowed)
     assert err.max() <= want.noise_max, f"{what}: max error {err.max():.3e}, allowed {want.noise_max:.3e}"
-    assert err.mean() <= want.noise_mean, f"{what}: mean error {err.mean():.3e}, allowed {want.noise_mean:.3e}"
+    assert err.mean() <= mean_allowed, f"{what}: mean error {err.mean():.3e}, allowed {mean_allowed:.3e}"
 
 
 @pytest.fixture(scope="module")

@@ -7,6 +7,7 @@ import pytest
 import torch
 
 import tinyllama_c_b200 as tlc
+from tinyllama_c_b200 import ops
 from tinyllama_c_b200.cache import Cache
 from tinyllama_c_b200.engine.step import StepEntry, pack
 from tinyllama_c_b200.weights import load_model
@@ -68,7 +69,7 @@ def inputs(width, dtype, seed, scale=1.0):
     return rows
 
 
-def run_steps(part_forward, requests, rows, dtype, in_dtype=None):
+def run_steps(part_forward, requests, rows, dtype, in_dtype=None, step_requests=()):
     """Feeds the sequences through part_forward(x [T, width], step, layer cache) -> [T, out]: all prompts in
     one step, then one token each; returns what came out per sequence, in order.  The cache has the run's
     type; x has in_dtype (default: the run's type)."""
@@ -81,7 +82,7 @@ def run_steps(part_forward, requests, rows, dtype, in_dtype=None):
         counts = LENS if s == 0 else [1] * len(LENS)
         entries = [StepEntry(slot, [0] * n, ()) for slot, n in zip(slots, counts)]
         starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
-        step, _, _ = pack(entries, starts, 1, "cuda")
+        step, _, _ = pack(entries, starts, 1, "cuda", [q.rows for q in step_requests])
         cache.upload_tables()
         x = np.concatenate([rows[b][done[b]:done[b] + n] for b, n in enumerate(counts)])
         out = part_forward(torch.tensor(x, dtype=in_dtype, device="cuda"), step, cache.layer_view(0))
@@ -161,7 +162,7 @@ def _mixer_alone(built, name, dtype, index, plain_fn, in_mult, out_mult, what):
         mixer.forward(x, step, lc, residual)
         return residual
 
-    got = run_steps(forward, mixer.cache_requests(), rows, dtype)
+    got = run_steps(forward, mixer.cache_requests(), rows, dtype, step_requests=mixer.step_requests())
     want = [plain_fn(r * cfg.get(in_mult, 1.0), np.arange(len(r))) * cfg.get(out_mult, 1.0) for r in rows]
     compare(got, want, dtype, what)
 

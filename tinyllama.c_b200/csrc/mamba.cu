@@ -13,19 +13,26 @@
 #define CONV_MAX_TAPS 16
 
 // ---- convolution + SiLU over packed rows, and softplus / decay of dt ---------------------
+// In a bfloat16 run (QUICK) x|B|C are operands of the scan's matrix products: they are rounded to bfloat16
+// here, whatever type they are stored in, so that a row's values do not depend on which scan reads them (the
+// matrix form of long prompts, the row-by-row scan of short ones and of single-token steps).
+template <bool BF16_RUN> __device__ __forceinline__ float as_operand(float v) {
+  return BF16_RUN ? __bfloat162float(__float2bfloat16_rn(v)) : v;
+}
+
 // grid (ceil(T / 8), ceil(Cd/256)): a thread owns one channel of 8 consecutive rows.  It reads the
 // raw samples of those rows and of the K-1 rows before them once (all loads issued together), and
 // takes a tap from the sequence's stored window only where the row is among the first K-1 of a
 // sequence that continues from a slot.  Also writes dt and dA of the rows (first blocks along y).
 #define CONV_ROWS 8
-template <typename T, int K, bool QUICK>
+template <typename T, typename TO, int K, bool QUICK>
 __global__ void __launch_bounds__(256)
 mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_off,
                   const float* __restrict__ w, const float* __restrict__ bias,
                   const float* __restrict__ dt_bias, const float* __restrict__ A,
                   const float* __restrict__ conv_state, const int* __restrict__ cu_seqlens,
                   const int* __restrict__ row_seq, const int* __restrict__ slots,
-                  const int* __restrict__ start_pos, float* __restrict__ xbc_out,
+                  const int* __restrict__ start_pos, TO* __restrict__ xbc_out,
                   float* __restrict__ dt_out, float* __restrict__ dA_out, int n_rows, int Cd, int Hs) {
   tlc_pdl(proj, conv_state, xbc_out, dt_out, dA_out);
   __shared__ int s_i[CONV_ROWS], s_has[CONV_ROWS], s_slot[CONV_ROWS];
@@ -70,7 +77,7 @@ mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_o
         else x = s_has[r] ? conv_state[((size_t)s_slot[r] * (K - 1) + (K - 1 + j)) * Cd + c] : 0.f;
         sum = fmaf(x, wk[k], sum);
       }
-      xbc_out[(size_t)t * Cd + c] = silu_of<QUICK>(sum + bv);
+      xbc_out[(size_t)t * Cd + c] = from_f32<TO>(as_operand<QUICK>(silu_of<QUICK>(sum + bv)));
     }
   }
   if (c < Hs) {
@@ -87,14 +94,15 @@ mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_o
 }
 
 // Any number of taps: grid (T, ceil(Cd/256)), a thread per (row, channel).
-template <typename T>
+template <typename T, typename TO>
 __global__ void mamba_conv_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_off,
                                   const float* __restrict__ w, const float* __restrict__ bias,
                                   const float* __restrict__ dt_bias, const float* __restrict__ A,
                                   const float* __restrict__ conv_state, const int* __restrict__ cu_seqlens,
                                   const int* __restrict__ row_seq, const int* __restrict__ slots,
-                                  const int* __restrict__ start_pos, float* __restrict__ xbc_out,
-                                  float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs) {
+                                  const int* __restrict__ start_pos, TO* __restrict__ xbc_out,
+                                  float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs,
+                                  int bf16_run) {
   tlc_pdl(proj, conv_state, xbc_out, dt_out, dA_out);
   const int t = blockIdx.x;
   const int b = row_seq[t];
@@ -112,7 +120,8 @@ __global__ void mamba_conv_kernel(const T* __restrict__ proj, int ld, int xbc_of
       sum = fmaf(x, w[(size_t)c * K + k], sum);
     }
     if (bias) sum += bias[c];
-    xbc_out[(size_t)t * Cd + c] = silu_f(sum);
+    const float v = silu_f(sum);
+    xbc_out[(size_t)t * Cd + c] = from_f32<TO>(bf16_run ? as_operand<true>(v) : v);
   }
   if (c < Hs) {
     const float dtv = softplus_f(to_f32(proj[(size_t)t * ld + dt_off + c]) + dt_bias[c]);
@@ -157,7 +166,8 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
                                          const float* __restrict__ dt_bias, const float* __restrict__ A,
                                          float* __restrict__ conv_state, const int* __restrict__ slots,
                                          const int* __restrict__ start_pos, float* __restrict__ xbc_out,
-                                         float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs) {
+                                         float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs,
+                                         int bf16_run) {
   // The window was stored by the step before and the weights never change: both are fetched before the
   // wait on the previous kernel; only the row's projection is read after it.
   asm volatile("griddepcontrol.launch_dependents;");
@@ -188,7 +198,8 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
 #pragma unroll
     for (int k = 0; k <= CONV_MAX_TAPS; k++) if (k == K - 1) wl = wk[k];
     sum = fmaf(cur, wl, sum);
-    xbc_out[(size_t)b * Cd + c] = silu_f(sum);
+    const float v = silu_f(sum);
+    xbc_out[(size_t)b * Cd + c] = bf16_run ? as_operand<true>(v) : v;
 #pragma unroll
     for (int k = 0; k < CONV_MAX_TAPS; k++) {
       if (k < K - 2) st[(size_t)k * Cd + c] = prev[k + 1];
@@ -202,15 +213,18 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
   }
 }
 
-#define TLC_CONV_ROWS_Q(KT, QK)                                                                                           \
-  tlc_launch(mamba_conv_rows_kernel<TT, KT, QK>, dim3(grid8), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, \
-             w, bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out, dA_out, T, Cd, Hs)
+#define TLC_CONV_ROWS_Q(KT, QK)                                                                                        \
+  tlc_launch(mamba_conv_rows_kernel<TT, TO, KT, QK>, dim3(grid8), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off,  \
+             dt_off, w, bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, (TO*)xbc_out, dt_out,     \
+             dA_out, T, Cd, Hs)
 #define TLC_CONV_ROWS(KT) do { if (quick) TLC_CONV_ROWS_Q(KT, true); else TLC_CONV_ROWS_Q(KT, false); } while (0)
+// xbc_dtype: the element type of xbc_out [T, Cd].  Single-token steps and the 32-bit scans take float; the scan
+// of prompts in matrix form takes its operands in bfloat16 and gets them in that type at once.
 extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, int dt_off, const float* w,
                               const float* bias, const float* dt_bias, const float* A, float* conv_state,
                               const int* cu_seqlens, const int* row_seq, const int* slots, const int* start_pos,
-                              float* xbc_out, float* dt_out, float* dA_out, int T, int B, int Cd, int K, int Hs,
-                              int single_rows, int quick, cudaStream_t stream) {
+                              void* xbc_out, int xbc_dtype, float* dt_out, float* dA_out, int T, int B, int Cd, int K,
+                              int Hs, int single_rows, int quick, cudaStream_t stream) {
   if (T == 0) return 0;
   TLC_REQUIRE(K >= 1 && K - 1 <= CONV_MAX_TAPS, "mamba_conv: %d taps exceed the kernel's limit of %d", K, CONV_MAX_TAPS + 1);
   TLC_REQUIRE(Hs <= Cd, "mamba_conv: more heads (%d) than conv channels (%d)", Hs, Cd);
@@ -218,24 +232,24 @@ extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, 
   dim3 grid8((T + CONV_ROWS - 1) / CONV_ROWS, (Cd + 255) / 256);
   dim3 grid2(B, (Cd + 255) / 256);
   if (single_rows && T == B) {
-    TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(mamba_conv_decode_kernel<TT>, dim3(grid2), dim3(256), 0, stream, 
-        (const TT*)proj, ld, xbc_off, dt_off, w, bias, dt_bias, A, conv_state, slots, start_pos, xbc_out, dt_out, dA_out,
-        Cd, K, Hs));
+    TLC_REQUIRE(xbc_dtype == TLC_F32, "mamba_conv: single-token steps write 32-bit x|B|C");
+    TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(mamba_conv_decode_kernel<TT>, dim3(grid2), dim3(256), 0, stream,
+        (const TT*)proj, ld, xbc_off, dt_off, w, bias, dt_bias, A, conv_state, slots, start_pos, (float*)xbc_out, dt_out, dA_out,
+        Cd, K, Hs, quick));
     TLC_CHECK_LAUNCH("mamba_conv(decode)");
     return 0;
   }
-  TLC_DISPATCH_DTYPE(dtype, TT, {
+  TLC_DISPATCH_DTYPE(dtype, TT, TLC_DISPATCH_DTYPE(xbc_dtype, TO, {
     if (K == 4) TLC_CONV_ROWS(4);
     else if (K == 3) TLC_CONV_ROWS(3);
     else if (K == 2) TLC_CONV_ROWS(2);
     else
-      tlc_launch(mamba_conv_kernel<TT>, dim3(grid), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, w, bias, dt_bias, A,
-                                                    conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out,
-                                                    dA_out, Cd, K, Hs);
+      tlc_launch(mamba_conv_kernel<TT, TO>, dim3(grid), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, w, bias,
+                 dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, (TO*)xbc_out, dt_out, dA_out, Cd, K, Hs, quick);
     if (K > 1)
-      tlc_launch(mamba_conv_state_kernel<TT>, dim3(grid2), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, conv_state, cu_seqlens, slots,
-                                                             start_pos, Cd, K);
-  });
+      tlc_launch(mamba_conv_state_kernel<TT>, dim3(grid2), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, conv_state,
+                 cu_seqlens, slots, start_pos, Cd, K);
+  }));
   TLC_CHECK_LAUNCH("mamba_conv");
   return 0;
 }

@@ -1,4 +1,4 @@
-// Selective scan of long prompts in chunked matrix form, on the tensor cores.
+// Selective scan of prompts in chunked matrix form, on the tensor cores, with the state kept on chip.
 //
 // The recurrence is the reference's (cpu_op.c:932-951):
 //     S_t = S_{t-1} * exp(dt_t A) + (dt_t x_t) (x) B_t ,   y_t = S_t . C_t + D x_t
@@ -6,161 +6,57 @@
 //     y_i  = sum_{j<=i} (C_i . B_j) exp(cum_i - cum_j) dt_j x_j        "inside the chunk"
 //          + exp(cum_i) * (S_in C_i)                                  "what came before"
 //          + D x_i
-//     S_c  = sum_j exp(cum_last - cum_j) dt_j x_j (x) B_j               the chunk's own contribution
-//     S_in(c+1) = exp(cum_last) S_in(c) + S_c                           carried in chunk order
-// Kernels: cumulative decay per (chunk, head); C B^T per (chunk, group) (shared by the group's
-// heads); the chunk states; the carry (ssm_state_pass in mamba.cu); the outputs.  The products
-// run on mma.sync.m16n8k8 with TF32 operands (10-bit mantissa; the 32-bit path of the library
-// never comes here) and 32-bit accumulation; decays are exponentials of non-positive numbers.
-// State, cumulative sums and all scalings are 32-bit.
+//     S_out = exp(cum_last) S_in + sum_j exp(cum_last - cum_j) dt_j x_j (x) B_j
+// Two kernels:
+//   ssd_cb_kernel    C B^T of every (chunk, group), shared by the group's heads (bfloat16 in and out);
+//   ssd_walk_kernel  one block per (sequence, head, 32 rows p of the head) walks the sequence's chunks in
+//                    order.  The state S[32, N] lives in the accumulator registers of the last product from
+//                    the slot's state before the first chunk to the slot's state after the last; it is never
+//                    written to global memory in between.  Per chunk: the state goes to shared memory in
+//                    bfloat16 for C S^T; the score matrix M[i, j] = cb exp(cum_i - cum_j) dt_j is built in
+//                    registers, as the operand fragments of M X, by the warp that owns rows i; x scaled by
+//                    its row's weight is the operand of the state update.  C, C B^T and B of the next chunk
+//                    arrive by cp.async while the current chunk is multiplied (each buffer is refilled as soon
+//                    as its product is done).
+// Products are mma.sync.m16n8k16 with bfloat16 operands and 32-bit accumulation.  Cumulative sums, decay
+// factors, the carried state, D x and every accumulator are 32-bit; decays are exponentials of non-positive
+// numbers.  The 32-bit path of the library never comes here (mamba.cu has its three-pass scan).
 #include "common.cuh"
-
-int tlc_ssm_state_pass_launch(const float* chunk_decay, float* state, float* chunk_state, const int* seq_seg_start,
-                              const int* slots, const int* start_pos, int B, int Hs, int PN, int write_final,
-                              cudaStream_t stream);
 
 namespace {
 
-constexpr int Q = 128;       // rows per chunk (SCAN_CHUNK of the engine)
+constexpr int Q = 128;       // rows per chunk
+constexpr int PB = 32;       // rows p of a head per block of the walk
+constexpr float LOG2E = 1.4426950408889634f;
 
-__device__ __forceinline__ uint32_t tf32(float v) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
-  return r;
-}
-__device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-
-// Four 8 x 8 matrices of 16-bit elements, i.e. four blocks of 8 rows x 4 32-bit words: thread T gets word T % 4 of
-// row T / 4 of each, which is the layout of the TF32 fragments wherever K runs along the rows in memory.
-__device__ __forceinline__ void ldsm_x4_b32(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
-__device__ __forceinline__ uint32_t tf32_bits(uint32_t v) { return tf32(__uint_as_float(v)); }
-// 2^x by the special-function unit (two units in the last place; the result becomes a TF32 operand)
-__device__ __forceinline__ float ex2_quick(float x) {
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_t(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ float ex2_quick(float x) {     // 2^x by the special-function unit
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
 }
-
-// ---- cumulative log-decay per (chunk, head) --------------------------------------------------------
-// cum[t, h] = sum of dt*A over the chunk's rows up to t; chunk_decay[seg, h] = exp(cum at the last row)
-__global__ void __launch_bounds__(128)
-ssd_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A, const int* __restrict__ seg_start,
-                  float* __restrict__ cum, float* __restrict__ chunk_decay, int Hs) {
-  tlc_pdl(dt, cum, chunk_decay);
-  // a warp per (chunk, head): lane l owns rows 4l .. 4l+3 of the chunk; prefix sums by shuffles
-  const int seg = blockIdx.x;
-  const int h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (h >= Hs) return;
-  const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
-  const float a = A[h];
-  float d[Q / 32];
-#pragma unroll
-  for (int u = 0; u < Q / 32; u++) {
-    const int r = lane * (Q / 32) + u;
-    d[u] = r < L ? dt[(size_t)(t0 + r) * Hs + h] * a : 0.f;
-  }
-#pragma unroll
-  for (int u = 1; u < Q / 32; u++) d[u] += d[u - 1];
-  float run = d[Q / 32 - 1];                            // inclusive sum of the lanes up to this one
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const float v = __shfl_up_sync(0xffffffffu, run, o);
-    if (lane >= o) run += v;
-  }
-  const float before = run - d[Q / 32 - 1];
-#pragma unroll
-  for (int u = 0; u < Q / 32; u++) {
-    const int r = lane * (Q / 32) + u;
-    if (r < L) cum[(size_t)(t0 + r) * Hs + h] = before + d[u];
-  }
-  if (lane == 31) chunk_decay[(size_t)seg * Hs + h] = expf(run);   // rows past L add nothing
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
 }
-
-// ---- C B^T per (chunk, group): cb[seg, g, i, j] for j <= i -----------------------------------------
-// grid (seg, G, 8): a block of 4 warps computes a strip of 16 rows x 128 columns, warp w the columns
-// [32 w, 32 w + 32); K = N in slabs of 64.
-__global__ void __launch_bounds__(128)
-ssd_cb_kernel(const float* __restrict__ xbc, const int* __restrict__ seg_start, float* __restrict__ cb, int Di, int N,
-              int G, int Cd) {
-  tlc_pdl(xbc, cb);
-  constexpr int LD = 68;
-  extern __shared__ uint32_t ssd_sm[];
-  uint32_t* Cs = ssd_sm;                 // [16][LD]   rows i, columns n
-  uint32_t* Bs = ssd_sm + 16 * LD;       // [Q][LD]    rows j, columns n
-  const int seg = blockIdx.x, g = blockIdx.y;
-  const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-  const int i_base = blockIdx.z * 16;                      // the block's 16 rows
-  if (i_base >= L) return;
-  const int n_tiles = min(16, (i_base + 16 + 7) / 8);      // columns j <= i only
-  const int j_rows = min(Q, n_tiles * 8);                  // rows of B that matter
-  float acc[4][4];
-#pragma unroll
-  for (int j = 0; j < 4; j++)
-#pragma unroll
-    for (int k = 0; k < 4; k++) acc[j][k] = 0.f;
-  const float* Bg = xbc + Di + (size_t)g * N;
-  const float* Cg = xbc + Di + (size_t)G * N + (size_t)g * N;
-  for (int n0 = 0; n0 < N; n0 += 64) {
-    __syncthreads();
-    // 16 float4 per row; all loads of a batch are issued before the first conversion
-#pragma unroll 1
-    for (int it0 = 0; it0 < 16; it0 += 8) {
-      float4 bv[8], cv[8];
-#pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int idx = threadIdx.x + (it0 + u) * 128;
-        const int r = idx >> 4, c4 = (idx & 15) * 4;
-        bv[u] = cv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (r < L && r < j_rows && n0 + c4 < N) bv[u] = *reinterpret_cast<const float4*>(Bg + (size_t)(t0 + r) * Cd + n0 + c4);
-        const int ri = i_base + r;
-        if (r < 16 && ri < L && n0 + c4 < N) cv[u] = *reinterpret_cast<const float4*>(Cg + (size_t)(t0 + ri) * Cd + n0 + c4);
-      }
-#pragma unroll
-      for (int u = 0; u < 8; u++) {
-        const int idx = threadIdx.x + (it0 + u) * 128;
-        const int r = idx >> 4, c4 = (idx & 15) * 4;
-        uint32_t* bd = Bs + r * LD + c4;
-        bd[0] = tf32(bv[u].x); bd[1] = tf32(bv[u].y); bd[2] = tf32(bv[u].z); bd[3] = tf32(bv[u].w);
-        if (r < 16) {
-          uint32_t* cd = Cs + r * LD + c4;
-          cd[0] = tf32(cv[u].x); cd[1] = tf32(cv[u].y); cd[2] = tf32(cv[u].z); cd[3] = tf32(cv[u].w);
-        }
-      }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int kk = 0; kk < 8; kk++) {
-      const uint32_t* ar = Cs + gq * LD + kk * 8 + tq;
-      const uint32_t a0 = ar[0], a1 = ar[8 * LD], a2 = ar[4], a3 = ar[8 * LD + 4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        if (warp * 4 + j < n_tiles) {
-          const uint32_t* br = Bs + ((warp * 4 + j) * 8 + gq) * LD + kk * 8 + tq;
-          mma_tf32(acc[j], a0, a1, a2, a3, br[0], br[4]);
-        }
-      }
-    }
-  }
-  float* out = cb + (((size_t)seg * G + g) * Q) * Q;
-#pragma unroll
-  for (int j = 0; j < 4; j++) {
-    if (warp * 4 + j < n_tiles) {
-      const int col = (warp * 4 + j) * 8 + 2 * tq;
-      *reinterpret_cast<float2*>(out + (size_t)(i_base + gq) * Q + col) = make_float2(acc[j][0], acc[j][1]);
-      *reinterpret_cast<float2*>(out + (size_t)(i_base + gq + 8) * Q + col) = make_float2(acc[j][2], acc[j][3]);
-    }
-  }
+__device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
 }
-
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool pred) {
   const int bytes = pred ? 16 : 0;                 // 0: the 16 bytes are filled with zeros, nothing is read
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
@@ -168,318 +64,433 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool p
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N_> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_) : "memory"); }
 
-// ---- chunk states: S_c[p, n] = sum_j w_j x[j, p] B[j, n],  w_j = exp(cum_last - cum_j) dt_j ----------
-// grid (seg, Hs, N / 128); 8 warps; output P x 128 with K = 128 rows of the chunk.  x and B arrive as they
-// are, by cp.async, all at once; the weights w_j are computed meanwhile.  x is then scaled by them and rounded
-// to TF32 once, in place (the kernel is bound by instruction issue: every warp needs every x fragment);
-// B is rounded in registers.  A warp owns half of the head's rows and 32 of the columns.
-template <int P>
-__global__ void __launch_bounds__(256)
-ssd_chunk_state_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ cum,
-                       const int* __restrict__ seg_start, float* __restrict__ chunk_state, int Hs, int N, int G, int Cd) {
-  tlc_pdl(xbc, dt, cum, chunk_state);
-  constexpr int LDX = P + 8, LDB = 128 + 8;
-  extern __shared__ __align__(16) uint32_t ssd_sm[];
-  float* Xs = reinterpret_cast<float*>(ssd_sm);     // [j][p]   raw x
-  float* Bs = Xs + Q * LDX;                         // [j][n]   128 columns of B, raw
-  float* ws = Bs + Q * LDB;                         // [j]      w_j
-  const int seg = blockIdx.x, h = blockIdx.y, nb = blockIdx.z * 128;
-  const int g = h / (Hs / G);
-  const int Di = Hs * P;
+// Rows in shared memory are padded by 16 bytes: the row strides used here are then 16 or 80 modulo 128, so that
+// the eight rows an ldmatrix reads lie in eight different 16-byte columns of the banks.
+__host__ __device__ constexpr int padded(int row_bytes) { return row_bytes + 16; }
+
+// ---- C B^T per (chunk, group): cb[seg, g, i, j] for j <= i (bfloat16) -------------------------------------
+// grid (seg, G, 2), 4 warps: a block owns 64 rows i, warp w the rows [16 w, 16 w + 16) of them and the columns
+// j up to its diagonal; K = N.
+__global__ void __launch_bounds__(128)
+ssd_cb_kernel(const __nv_bfloat16* __restrict__ xbc, const int* __restrict__ seg_start, __nv_bfloat16* __restrict__ cb,
+              int Di, int N, int G, int Cd) {
+  tlc_pdl(xbc, cb);
+  extern __shared__ __align__(16) unsigned char ssd_sm[];
+  const int LDN = padded(N * 2);
+  unsigned char* Cs = ssd_sm;                     // [64][LDN]   rows i
+  unsigned char* Bs = ssd_sm + 64 * LDN;          // [Q][LDN]    rows j
+  const int seg = blockIdx.x, g = blockIdx.y, i_blk = blockIdx.z * 64;
   const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
-  const int tid = threadIdx.x;
-  const uint32_t xs0 = (uint32_t)__cvta_generic_to_shared(Xs), bs0 = (uint32_t)__cvta_generic_to_shared(Bs);
-  for (int idx = tid; idx < Q * (P / 4); idx += 256) {
-    const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
-    const bool in = r < L;
-    cp_async16(xs0 + (uint32_t)(r * LDX + c4) * 4, xbc + (size_t)(t0 + (in ? r : 0)) * Cd + (size_t)h * P + c4, in);
+  if (i_blk >= L) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+  const int j_rows = min(L, i_blk + 64);          // rows of B that matter
+  const __nv_bfloat16* Bg = xbc + Di + (size_t)g * N;
+  const __nv_bfloat16* Cg = xbc + Di + (size_t)G * N + (size_t)g * N;
+  const uint32_t cs0 = (uint32_t)__cvta_generic_to_shared(Cs), bs0 = (uint32_t)__cvta_generic_to_shared(Bs);
+  const int pieces = N / 8;                       // 16-byte pieces of a row
+  for (int idx = tid; idx < 64 * pieces; idx += 128) {
+    const int r = idx / pieces, c = idx % pieces;
+    const bool in = i_blk + r < L;
+    cp_async16(cs0 + r * LDN + c * 16, Cg + (size_t)(t0 + (in ? i_blk + r : 0)) * Cd + c * 8, in);
   }
-  for (int idx = tid; idx < Q * 32; idx += 256) {
-    const int r = idx >> 5, c4 = (idx & 31) * 4;
-    const bool in = r < L && nb + c4 < N;
-    cp_async16(bs0 + (uint32_t)(r * LDB + c4) * 4,
-               xbc + (size_t)(t0 + (r < L ? r : 0)) * Cd + Di + (size_t)g * N + (in ? nb + c4 : 0), in);
+  for (int idx = tid; idx < Q * pieces; idx += 128) {
+    const int r = idx / pieces, c = idx % pieces;
+    const bool in = r < j_rows;
+    cp_async16(bs0 + r * LDN + c * 16, Bg + (size_t)(t0 + (in ? r : 0)) * Cd + c * 8, in);
   }
   cp_async_commit();
-  if (tid < Q) {
-    float w = 0.f;
-    if (tid < L) {
-      const float cum_last = cum[(size_t)(t0 + L - 1) * Hs + h];
-      w = expf(cum_last - cum[(size_t)(t0 + tid) * Hs + h]) * dt[(size_t)(t0 + tid) * Hs + h];
-    }
-    ws[tid] = w;
-  }
   cp_async_wait<0>();
   __syncthreads();
-  // x times its row's weight, rounded to TF32, once and in place: every warp reads it from there
-  uint32_t* Xt = reinterpret_cast<uint32_t*>(Xs);
-  for (int idx = tid; idx < Q * (P / 4); idx += 256) {
-    const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
-    const float4 v = *reinterpret_cast<const float4*>(Xs + r * LDX + c4);
-    const float wr = ws[r];
-    *reinterpret_cast<uint4*>(Xt + r * LDX + c4) = make_uint4(tf32(v.x * wr), tf32(v.y * wr), tf32(v.z * wr), tf32(v.w * wr));
-  }
-  __syncthreads();
-  const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
-  // warp w: rows p of half w & 1 of the head (P/32 tiles) x columns n in [32 (w >> 1), +32) (4 tiles)
-  constexpr int MT = P / 32;
-  const int p0 = (warp & 1) * (P / 2), n_w = (warp >> 1) * 32;
-  float acc[MT][4][4];
+  const int i_base = i_blk + warp * 16;           // the warp's 16 rows
+  if (i_base >= L) return;
+  const int n_pairs = (i_base + 16) / 16;         // pairs of 8-column tiles up to and including the diagonal
+  float acc[16][4];
 #pragma unroll
-  for (int m = 0; m < MT; m++)
+  for (int j = 0; j < 16; j++)
 #pragma unroll
-    for (int jn = 0; jn < 4; jn++)
+    for (int k = 0; k < 4; k++) acc[j][k] = 0.f;
+  const uint32_t a_addr = cs0 + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDN + (lane >> 4) * 16;
+  const uint32_t b_addr = bs0 + ((lane & 7) + (lane >> 4) * 8) * LDN + ((lane >> 3) & 1) * 16;
+  for (int ks = 0; ks < N / 16; ks++) {
+    uint32_t a0, a1, a2, a3;
+    ldsm_x4(a_addr + ks * 32, a0, a1, a2, a3);
 #pragma unroll
-      for (int k = 0; k < 4; k++) acc[m][jn][k] = 0.f;
-#pragma unroll 4
-  for (int kk = 0; kk < Q / 8; kk++) {
-    uint32_t b[4][2];
-#pragma unroll
-    for (int jn = 0; jn < 4; jn++) {
-      const float* br = Bs + (kk * 8 + tq) * LDB + n_w + jn * 8 + gq;
-      b[jn][0] = tf32(br[0]);
-      b[jn][1] = tf32(br[4 * LDB]);
-    }
-#pragma unroll
-    for (int m = 0; m < MT; m++) {
-      const uint32_t* ar = Xt + (kk * 8 + tq) * LDX + p0 + m * 16 + gq;               // A(row p, col j) = x[j][p] w_j
-      const uint32_t a0 = ar[0], a1 = ar[8], a2 = ar[4 * LDX], a3 = ar[4 * LDX + 8];
-#pragma unroll
-      for (int jn = 0; jn < 4; jn++) mma_tf32(acc[m][jn], a0, a1, a2, a3, b[jn][0], b[jn][1]);
-    }
-  }
-  float* out = chunk_state + (((size_t)seg * Hs + h) * P) * N;
-#pragma unroll
-  for (int m = 0; m < MT; m++)
-#pragma unroll
-    for (int jn = 0; jn < 4; jn++) {
-      const int n = nb + n_w + jn * 8 + 2 * tq;
-      if (n < N) {
-        *reinterpret_cast<float2*>(out + (size_t)(p0 + m * 16 + gq) * N + n) = make_float2(acc[m][jn][0], acc[m][jn][1]);
-        *reinterpret_cast<float2*>(out + (size_t)(p0 + m * 16 + gq + 8) * N + n) = make_float2(acc[m][jn][2], acc[m][jn][3]);
+    for (int jp = 0; jp < 8; jp++) {
+      if (jp < n_pairs) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(b_addr + jp * 16 * LDN + ks * 32, b0, b1, b2, b3);
+        mma_bf16(acc[2 * jp], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acc[2 * jp + 1], a0, a1, a2, a3, b2, b3);
       }
     }
+  }
+  __nv_bfloat16* out = cb + (((size_t)seg * G + g) * Q) * Q;
+#pragma unroll
+  for (int jp = 0; jp < 8; jp++) {
+    if (jp < n_pairs) {
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const int col = (2 * jp + u) * 8 + 2 * tq;
+        *reinterpret_cast<uint32_t*>(out + (size_t)(i_base + gq) * Q + col) = pack_bf16(acc[2 * jp + u][0], acc[2 * jp + u][1]);
+        *reinterpret_cast<uint32_t*>(out + (size_t)(i_base + gq + 8) * Q + col) = pack_bf16(acc[2 * jp + u][2], acc[2 * jp + u][3]);
+      }
+    }
+  }
 }
 
-// ---- chunk outputs ------------------------------------------------------------------------------------
-// grid (seg, Hs, 2); a block of 8 warps owns 64 rows of the chunk: warp w has rows [16 (w & 3), +16) and
-// the columns of half w >> 2 of the head.
-//   acc  = M X,        M[i,j] = cb[i,j] exp(cum_i - cum_j) dt_j (j <= i),  X[j,p] = x[j,p]
-//   acc2 = C S_in^T    (the state the chunk starts from), scaled by exp(cum_i) at the end
-//   y = acc + exp(cum_i) acc2 + D x
-// M is built in shared memory by the block (it needs the exponentials); X, C and S_in arrive as they
-// are, by cp.async, and are rounded to TF32 in registers: X and the first slab of 32 state columns
-// are on their way while M is built, and each further slab while the one before it is multiplied.
-constexpr int OUT_R = 64;                  // rows of the chunk per block
-constexpr int OUT_SL = 32;                 // state columns per slab
-constexpr int OUT_LDM = Q + 4, OUT_LDS = OUT_SL + 4;
+// ---- the walk over a sequence's chunks ------------------------------------------------------------------
+// NT: state columns / 64 (1..4).  8 warps.  Warp w owns
+//   * rows i in [16 w, 16 w + 16) of the chunk in the products that give y (all 32 columns p of the block),
+//   * the state columns n in [8 NT w, 8 NT (w + 1)) in the state update (all 32 rows p).
+struct WalkSmem {
+  int ldn, c, b, cb, x, xw, s, f, total;          // byte offsets
+  __host__ __device__ WalkSmem(int N) {
+    ldn = padded(N * 2);
+    c = 0;
+    b = c + Q * ldn;
+    cb = b + Q * ldn;
+    x = cb + Q * padded(Q * 2);
+    xw = x + 2 * Q * padded(PB * 2);
+    s = xw + Q * padded(PB * 2);
+    f = s + PB * ldn;
+    total = f + (4 * Q + 8) * 4;
+  }
+};
 
-template <int P>
-__global__ void __launch_bounds__(256)
-ssd_chunk_out_kernel(const float* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ cum,
-                     const float* __restrict__ cb, const float* __restrict__ s_in, const float* __restrict__ Dskip,
-                     const int* __restrict__ seg_start, float* __restrict__ y, int Hs, int N, int G, int Cd) {
-  tlc_pdl(xbc, dt, cum, cb, s_in, y);
-  constexpr int R = OUT_R, LDM = OUT_LDM, LDX = P + 8, LDS = OUT_LDS, SL = OUT_SL;
-  constexpr int NT = P / 16;               // 8-column tiles of a warp's half of the head
-  extern __shared__ __align__(16) uint32_t ssd_sm[];
-  uint32_t* Ms = ssd_sm;                   // [R][j]            TF32
-  float* Xs = reinterpret_cast<float*>(Ms + R * LDM);        // [j][p]            raw
-  float* Cb = Xs + Q * LDX;                // [2][R][slab]      raw
-  float* Sb = Cb + 2 * R * LDS;            // [2][p][slab]      raw
-  float* cums = Sb + 2 * P * LDS;          // [Q]
-  float* dts = cums + Q;                   // [Q]
-  const int seg = blockIdx.x, h = blockIdx.y, r0 = blockIdx.z * R;
+template <int NT>
+__global__ void __launch_bounds__(256, 1)
+ssd_walk_kernel(const __nv_bfloat16* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ A,
+                const float* __restrict__ Dskip, const __nv_bfloat16* __restrict__ cb, float* __restrict__ state,
+                const int* __restrict__ seg_start, const int* __restrict__ seq_seg_start, const int* __restrict__ slots,
+                const int* __restrict__ start_pos, float* __restrict__ y, int Hs, int P, int G, int Cd) {
+  tlc_pdl(xbc, dt, cb, state, y);
+  constexpr int N = 64 * NT;
+  constexpr int LDX = padded(PB * 2), LDCB = padded(Q * 2);
+  const WalkSmem lay(N);
+  const int LDN = lay.ldn;
+  extern __shared__ __align__(16) unsigned char ssd_sm[];
+  float* cums = reinterpret_cast<float*>(ssd_sm + lay.f);     // [Q] cumulative log2 decay
+  float* dts = cums + Q;                                      // [Q]
+  float* ws = dts + Q;                                        // [Q] weight of row j in the state update
+  float* es = ws + Q;                                         // [Q] 2^cum
+  float* wsum = es + Q;                                       // [4] warp totals of the prefix sum
+  const uint32_t sm0 = (uint32_t)__cvta_generic_to_shared(ssd_sm);
+  const uint32_t cs0 = sm0 + lay.c, bs0 = sm0 + lay.b, cb0 = sm0 + lay.cb, xs0 = sm0 + lay.x, xw0 = sm0 + lay.xw,
+                 ss0 = sm0 + lay.s;
+  const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PB;
   const int g = h / (Hs / G);
   const int Di = Hs * P;
-  const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
-  if (r0 >= L) return;
-  const int jmax = min(L, r0 + R);         // columns j < jmax matter for these rows
-  const int tid = threadIdx.x;
-  const float* Cg = xbc + Di + (size_t)G * N + (size_t)g * N;
-  const float* Sg = s_in + (((size_t)seg * Hs + h) * P) * N;
-  const uint32_t xs0 = (uint32_t)__cvta_generic_to_shared(Xs), cb0 = (uint32_t)__cvta_generic_to_shared(Cb),
-                 sb0 = (uint32_t)__cvta_generic_to_shared(Sb);
-  // X: rows j < jmax, zeros below
-  for (int idx = tid; idx < Q * (P / 4); idx += 256) {
-    const int r = idx / (P / 4), c4 = (idx % (P / 4)) * 4;
-    const bool in = r < jmax;
-    cp_async16(xs0 + (uint32_t)(r * LDX + c4) * 4, xbc + (size_t)(t0 + (in ? r : 0)) * Cd + (size_t)h * P + c4, in);
-  }
-  cp_async_commit();
-  auto fetch_slab = [&](int n0, int buf) {
-    for (int idx = tid; idx < R * (SL / 4); idx += 256) {           // C rows of this block
-      const int rl = idx / (SL / 4), c4 = (idx % (SL / 4)) * 4;
-      const bool in = r0 + rl < L;
-      cp_async16(cb0 + (uint32_t)((buf * R + rl) * LDS + c4) * 4, Cg + (size_t)(t0 + (in ? r0 + rl : 0)) * Cd + n0 + c4, in);
-    }
-    for (int idx = tid; idx < P * (SL / 4); idx += 256) {           // the incoming state
-      const int p = idx / (SL / 4), c4 = (idx % (SL / 4)) * 4;
-      cp_async16(sb0 + (uint32_t)((buf * P + p) * LDS + c4) * 4, Sg + (size_t)p * N + n0 + c4, true);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+  const int c0 = seq_seg_start[b], c1 = seq_seg_start[b + 1];
+  if (c1 <= c0) return;
+  const float a_log2 = A[h] * LOG2E, Dh = Dskip[h];
+  const __nv_bfloat16* Xg = xbc + (size_t)h * P + p0;
+  const __nv_bfloat16* Bg = xbc + Di + (size_t)g * N;
+  const __nv_bfloat16* Cg = xbc + Di + (size_t)G * N + (size_t)g * N;
+
+  // ---- what moves the inputs of a chunk: three groups of copies, each into the buffer of one product ----
+  auto fetch_xc = [&](int c, int buf) {            // x (this block's 32 columns) and C
+    if (c < c1) {
+      const int t0 = seg_start[c], L = seg_start[c + 1] - t0;
+      for (int idx = tid; idx < Q * (PB / 8); idx += 256) {
+        const int r = idx / (PB / 8), k = idx % (PB / 8);
+        const bool in = r < L;
+        cp_async16(xs0 + (buf * Q + r) * LDX + k * 16, Xg + (size_t)(t0 + (in ? r : 0)) * Cd + k * 8, in);
+      }
+      for (int idx = tid; idx < Q * (N / 8); idx += 256) {
+        const int r = idx / (N / 8), k = idx % (N / 8);
+        const bool in = r < L;
+        cp_async16(cs0 + r * LDN + k * 16, Cg + (size_t)(t0 + (in ? r : 0)) * Cd + k * 8, in);
+      }
     }
     cp_async_commit();
   };
-  fetch_slab(0, 0);
-  if (tid < Q) {
-    const int r = min(tid, L - 1);
-    cums[tid] = cum[(size_t)(t0 + r) * Hs + h] * 1.4426950408889634f;      // in powers of two from here on
-    dts[tid] = tid < L ? dt[(size_t)(t0 + tid) * Hs + h] : 0.f;
-  }
-  __syncthreads();
-  // M: R rows x 32 float4, 8 loads in flight per thread
-  const float* cbg = cb + (((size_t)seg * G + g) * Q) * Q;
-  {
-    float4 v[8];
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-      const int idx = tid + u * 256;
-      const int i = r0 + (idx >> 5), j4 = (idx & 31) * 4;
-      v[u] = (j4 <= i && i < L) ? *reinterpret_cast<const float4*>(cbg + (size_t)i * Q + j4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-#pragma unroll
-    for (int u = 0; u < 8; u++) {
-      const int idx = tid + u * 256;
-      const int il = idx >> 5, i = r0 + il, j4 = (idx & 31) * 4;
-      uint4 d = make_uint4(0u, 0u, 0u, 0u);
-      if (j4 <= i && i < L) {
-        const float ci = cums[i];
-        const float4 cj = *reinterpret_cast<const float4*>(cums + j4), dj = *reinterpret_cast<const float4*>(dts + j4);
-        d.x = tf32(v[u].x * ex2_quick(ci - cj.x) * dj.x);
-        if (j4 + 1 <= i) d.y = tf32(v[u].y * ex2_quick(ci - cj.y) * dj.y);
-        if (j4 + 2 <= i) d.z = tf32(v[u].z * ex2_quick(ci - cj.z) * dj.z);
-        if (j4 + 3 <= i) d.w = tf32(v[u].w * ex2_quick(ci - cj.w) * dj.w);
-      }
-      *reinterpret_cast<uint4*>(Ms + il * LDM + j4) = d;
-    }
-  }
-  cp_async_wait<1>();                      // X has arrived (the first slab may still be on its way)
-  __syncthreads();
-  const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
-  const int il_base = (warp & 3) * 16, i_base = r0 + il_base, p_base = (warp >> 2) * (P / 2);
-  float acc[NT][4], acc2[NT][4];
-#pragma unroll
-  for (int j = 0; j < NT; j++)
-#pragma unroll
-    for (int k = 0; k < 4; k++) acc[j][k] = acc2[j][k] = 0.f;
-  // inside the chunk: columns j <= i only
-  const int k_steps = (i_base + 16) / 8;
-  for (int kk = 0; kk < k_steps; kk++) {
-    const uint32_t* ar = Ms + (il_base + gq) * LDM + kk * 8 + tq;
-    const uint32_t a0 = ar[0], a1 = ar[8 * LDM], a2 = ar[4], a3 = ar[8 * LDM + 4];
-#pragma unroll
-    for (int j = 0; j < NT; j++) {
-      const float* br = Xs + (kk * 8 + tq) * LDX + p_base + j * 8 + gq;
-      mma_tf32(acc[j], a0, a1, a2, a3, tf32(br[0]), tf32(br[4 * LDX]));
-    }
-  }
-  // what came before the chunk: C times the incoming state, a slab of state columns at a time
-  const int n_slabs = N / SL;
-  for (int sl = 0; sl < n_slabs; sl++) {
-    cp_async_wait<0>();
-    __syncthreads();                       // slab sl is in shared memory; everybody is done with slab sl-1
-    if (sl + 1 < n_slabs) fetch_slab((sl + 1) * SL, (sl + 1) & 1);
-    // C and the state have K (the state column) along their rows: whole fragments come by ldmatrix
-    const uint32_t cs_u = cb0 + (uint32_t)((sl & 1) * R * LDS) * 4, ss_u = sb0 + (uint32_t)((sl & 1) * P * LDS) * 4;
-#pragma unroll
-    for (int kk = 0; kk < SL / 8; kk++) {
-      uint32_t a0, a1, a2, a3;     // rows 0-7 | 8-15 of the warp's strip, columns kk*8 + (0-3 | 4-7)
-      ldsm_x4_b32(cs_u + (uint32_t)((il_base + (lane & 7) + ((lane >> 3) & 1) * 8) * LDS + kk * 8 + (lane >> 4) * 4) * 4, a0, a1, a2, a3);
-      a0 = tf32_bits(a0); a1 = tf32_bits(a1); a2 = tf32_bits(a2); a3 = tf32_bits(a3);
-#pragma unroll
-      for (int jp = 0; jp < NT / 2; jp++) {
-        uint32_t b00, b01, b10, b11;   // B(k = n, col = p) = S_in[p][n]: rows p of two tiles, columns kk*8 + (0-3 | 4-7)
-        ldsm_x4_b32(ss_u + (uint32_t)((p_base + jp * 16 + (lane & 7) + (lane >> 4) * 8) * LDS + kk * 8 + ((lane >> 3) & 1) * 4) * 4,
-                    b00, b01, b10, b11);
-        mma_tf32(acc2[2 * jp], a0, a1, a2, a3, tf32_bits(b00), tf32_bits(b01));
-        mma_tf32(acc2[2 * jp + 1], a0, a1, a2, a3, tf32_bits(b10), tf32_bits(b11));
+  auto fetch_cb = [&](int c) {
+    if (c < c1) {
+      const int L = seg_start[c + 1] - seg_start[c];
+      const __nv_bfloat16* src = cb + (((size_t)c * G + g) * Q) * Q;
+      for (int idx = tid; idx < Q * (Q / 8); idx += 256) {
+        const int r = idx / (Q / 8), k = idx % (Q / 8);
+        const bool in = r < L && k * 8 <= r;        // columns beyond the diagonal's piece are never read
+        cp_async16(cb0 + r * LDCB + k * 16, src + (size_t)(in ? r : 0) * Q + (in ? k * 8 : 0), in);
       }
     }
-  }
-  const float Dh = Dskip[h];
-#pragma unroll
-  for (int r = 0; r < 2; r++) {
-    const int i = i_base + gq + 8 * r;
-    if (i < L) {
-      const float e = exp2f(cums[i]);
-#pragma unroll
-      for (int j = 0; j < NT; j++) {
-        const int p = p_base + j * 8 + 2 * tq;
-        const float2 xv = *reinterpret_cast<const float2*>(Xs + i * LDX + p);
-        *reinterpret_cast<float2*>(y + (size_t)(t0 + i) * Di + (size_t)h * P + p) =
-            make_float2(acc[j][2 * r] + e * acc2[j][2 * r] + Dh * xv.x, acc[j][2 * r + 1] + e * acc2[j][2 * r + 1] + Dh * xv.y);
+    cp_async_commit();
+  };
+  auto fetch_b = [&](int c) {
+    if (c < c1) {
+      const int t0 = seg_start[c], L = seg_start[c + 1] - t0;
+      for (int idx = tid; idx < Q * (N / 8); idx += 256) {
+        const int r = idx / (N / 8), k = idx % (N / 8);
+        const bool in = r < L;
+        cp_async16(bs0 + r * LDN + k * 16, Bg + (size_t)(t0 + (in ? r : 0)) * Cd + k * 8, in);
       }
     }
+    cp_async_commit();
+  };
+  auto load_dt = [&](int c) -> float {             // dt of row tid of chunk c (threads 0..127)
+    if (c < c1 && tid < Q) {
+      const int t0 = seg_start[c], L = seg_start[c + 1] - t0;
+      if (tid < L) return dt[(size_t)(t0 + tid) * Hs + h];
+    }
+    return 0.f;
+  };
+
+  fetch_xc(c0, 0);
+  fetch_cb(c0);
+  fetch_b(c0);
+  float dt_reg = load_dt(c0);
+
+  // ---- the state: rows p0 + 16 mt + gq (+ 8), columns 8 NT warp + 8 nt + 2 tq (+ 1) --------------------
+  float S[2][NT][4];
+  float* slot = state + (((size_t)slots[b] * Hs + h) * P + p0) * N;
+  bool have_state = start_pos[b] > 0;
+#pragma unroll
+  for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      const int n = 8 * NT * warp + 8 * nt + 2 * tq;
+      float2 lo = make_float2(0.f, 0.f), hi = lo;
+      if (have_state) {
+        lo = *reinterpret_cast<const float2*>(slot + (size_t)(16 * mt + gq) * N + n);
+        hi = *reinterpret_cast<const float2*>(slot + (size_t)(16 * mt + gq + 8) * N + n);
+      }
+      S[mt][nt][0] = lo.x; S[mt][nt][1] = lo.y; S[mt][nt][2] = hi.x; S[mt][nt][3] = hi.y;
+    }
+
+  const int i_base = warp * 16;
+#pragma unroll 1
+  for (int c = c0; c < c1; c++) {
+    const int buf = (c - c0) & 1;
+    const int t0 = seg_start[c], L = seg_start[c + 1] - t0;
+    // ---- cumulative log2 decay of the chunk's rows, and what follows from it ----
+    float v = dt_reg * a_log2;                     // 0 for rows past L
+    if (tid < Q) {
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float u = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += u;
+      }
+      if (lane == 31) wsum[warp] = v;
+    }
+    __syncthreads();
+    const float total = wsum[0] + wsum[1] + wsum[2] + wsum[3];
+    if (tid < Q) {
+      float off = 0.f;
+#pragma unroll
+      for (int k = 0; k < 3; k++) if (k < warp) off += wsum[k];
+      const float cum = v + off;
+      cums[tid] = cum;
+      dts[tid] = dt_reg;
+      ws[tid] = ex2_quick(total - cum) * dt_reg;
+      es[tid] = ex2_quick(cum);
+    }
+    const float decay = exp2f(total);
+    // ---- the state as the chunk finds it, in bfloat16, for C S^T ----
+    if (have_state) {
+#pragma unroll
+      for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          const int n = 8 * NT * warp + 8 * nt + 2 * tq;
+          *reinterpret_cast<uint32_t*>(ssd_sm + lay.s + (16 * mt + gq) * LDN + n * 2) = pack_bf16(S[mt][nt][0], S[mt][nt][1]);
+          *reinterpret_cast<uint32_t*>(ssd_sm + lay.s + (16 * mt + gq + 8) * LDN + n * 2) = pack_bf16(S[mt][nt][2], S[mt][nt][3]);
+        }
+    }
+    cp_async_wait<2>();                            // x and C of this chunk (C B^T and B may still be on their way)
+    __syncthreads();
+    float acc[4][4];                               // y of rows i_base + gq (+ 8), columns 8 nt + 2 tq (+ 1)
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+    const bool rows_live = i_base < L;
+    if (have_state && rows_live) {
+      // what came before: C S^T, K = the state columns
+      const uint32_t a_addr = cs0 + (i_base + (lane & 7) + ((lane >> 3) & 1) * 8) * LDN + (lane >> 4) * 16;
+      const uint32_t b_addr = ss0 + ((lane & 7) + (lane >> 4) * 8) * LDN + ((lane >> 3) & 1) * 16;
+#pragma unroll 4
+      for (int ks = 0; ks < N / 16; ks++) {
+        uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+        ldsm_x4(a_addr + ks * 32, a0, a1, a2, a3);
+        ldsm_x4(b_addr + ks * 32, b0, b1, b2, b3);
+        mma_bf16(acc[0], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acc[1], a0, a1, a2, a3, b2, b3);
+        ldsm_x4(b_addr + 16 * LDN + ks * 32, b0, b1, b2, b3);
+        mma_bf16(acc[2], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acc[3], a0, a1, a2, a3, b2, b3);
+      }
+      const float e_lo = es[i_base + gq], e_hi = es[i_base + gq + 8];
+#pragma unroll
+      for (int nt = 0; nt < 4; nt++) { acc[nt][0] *= e_lo; acc[nt][1] *= e_lo; acc[nt][2] *= e_hi; acc[nt][3] *= e_hi; }
+    }
+    __syncthreads();                               // everybody is done with C and with the state's copy
+    fetch_xc(c + 1, buf ^ 1);
+    dt_reg = load_dt(c + 1);
+    cp_async_wait<2>();                            // C B^T of this chunk
+    __syncthreads();
+    const uint32_t xb = xs0 + buf * Q * LDX;
+    if (rows_live) {
+      // inside the chunk: M X with M built in registers from C B^T; K = rows j up to the diagonal block
+      const float ci_lo = cums[i_base + gq], ci_hi = cums[i_base + gq + 8];
+      const uint32_t a_addr = cb0 + (i_base + (lane & 7) + ((lane >> 3) & 1) * 8) * LDCB + (lane >> 4) * 16;
+      const uint32_t b_addr = xb + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDX + (lane >> 4) * 16;
+#pragma unroll 1
+      for (int ks = 0; ks <= warp; ks++) {
+        uint32_t r[4];
+        ldsm_x4(a_addr + ks * 32, r[0], r[1], r[2], r[3]);
+        const int j0 = 16 * ks + 2 * tq;
+        const float2 cj0 = *reinterpret_cast<const float2*>(cums + j0), cj1 = *reinterpret_cast<const float2*>(cums + j0 + 8);
+        const float2 dj0 = *reinterpret_cast<const float2*>(dts + j0), dj1 = *reinterpret_cast<const float2*>(dts + j0 + 8);
+        const bool diag = ks == warp;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          // register q: row i_base + gq + 8 (q & 1), columns j0 + 8 (q >> 1) + {0, 1}
+          const float ci = (q & 1) ? ci_hi : ci_lo;
+          const float2 cj = (q >> 1) ? cj1 : cj0, dj = (q >> 1) ? dj1 : dj0;
+          const float2 m = unpack_bf16(r[q]);
+          float m0 = m.x * ex2_quick(ci - cj.x) * dj.x, m1 = m.y * ex2_quick(ci - cj.y) * dj.y;
+          if (diag) {
+            const int il = gq + 8 * (q & 1), jl = 2 * tq + 8 * (q >> 1);
+            if (jl > il) m0 = 0.f;
+            if (jl + 1 > il) m1 = 0.f;
+          }
+          r[q] = pack_bf16(m0, m1);
+        }
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(b_addr + ks * 16 * LDX, b0, b1, b2, b3);
+        mma_bf16(acc[0], r[0], r[1], r[2], r[3], b0, b1);
+        mma_bf16(acc[1], r[0], r[1], r[2], r[3], b2, b3);
+        ldsm_x4_t(b_addr + ks * 16 * LDX + 32, b0, b1, b2, b3);
+        mma_bf16(acc[2], r[0], r[1], r[2], r[3], b0, b1);
+        mma_bf16(acc[3], r[0], r[1], r[2], r[3], b2, b3);
+      }
+      // y = acc + D x
+#pragma unroll
+      for (int half = 0; half < 2; half++) {
+        const int i = i_base + gq + 8 * half;
+        if (i < L) {
+          float* yr = y + (size_t)(t0 + i) * Di + (size_t)h * P + p0;
+#pragma unroll
+          for (int nt = 0; nt < 4; nt++) {
+            const int p = 8 * nt + 2 * tq;
+            const float2 xv = unpack_bf16(*reinterpret_cast<const uint32_t*>(ssd_sm + lay.x + (buf * Q + i) * LDX + p * 2));
+            *reinterpret_cast<float2*>(yr + p) = make_float2(acc[nt][2 * half] + Dh * xv.x, acc[nt][2 * half + 1] + Dh * xv.y);
+          }
+        }
+      }
+    }
+    // x times its row's weight, the operand of the state update
+    for (int idx = tid; idx < Q * (PB / 2); idx += 256) {
+      const int r = idx / (PB / 2), k = idx % (PB / 2);
+      const float2 xv = unpack_bf16(*reinterpret_cast<const uint32_t*>(ssd_sm + lay.x + (buf * Q + r) * LDX + k * 4));
+      const float w = ws[r];
+      *reinterpret_cast<uint32_t*>(ssd_sm + lay.xw + r * LDX + k * 4) = pack_bf16(xv.x * w, xv.y * w);
+    }
+    __syncthreads();                               // everybody is done with C B^T; the scaled x is in place
+    fetch_cb(c + 1);
+    cp_async_wait<2>();                            // B of this chunk
+    __syncthreads();
+    // ---- S = decay S + (w x)^T B,  K = the chunk's rows ----
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) { S[mt][nt][0] *= decay; S[mt][nt][1] *= decay; S[mt][nt][2] *= decay; S[mt][nt][3] *= decay; }
+    {
+      const int k_steps = (L + 15) / 16;
+      const uint32_t a_addr = xw0 + ((lane & 7) + (lane >> 4) * 8) * LDX + ((lane >> 3) & 1) * 16;
+      const uint32_t b_addr = bs0 + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDN + (8 * NT * warp) * 2 + (lane >> 4) * 16;
+#pragma unroll 2
+      for (int ks = 0; ks < k_steps; ks++) {
+        uint32_t a[2][4];
+        ldsm_x4_t(a_addr + ks * 16 * LDX, a[0][0], a[0][1], a[0][2], a[0][3]);
+        ldsm_x4_t(a_addr + ks * 16 * LDX + 32, a[1][0], a[1][1], a[1][2], a[1][3]);
+#pragma unroll
+        for (int np = 0; np < NT / 2; np++) {
+          uint32_t b0, b1, b2, b3;
+          ldsm_x4_t(b_addr + ks * 16 * LDN + np * 32, b0, b1, b2, b3);
+#pragma unroll
+          for (int mt = 0; mt < 2; mt++) {
+            mma_bf16(S[mt][2 * np], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+            mma_bf16(S[mt][2 * np + 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b2, b3);
+          }
+        }
+        if (NT & 1) {
+          uint32_t b0, b1;
+          ldsm_x2_t(b_addr + ks * 16 * LDN + (NT / 2) * 32, b0, b1);
+#pragma unroll
+          for (int mt = 0; mt < 2; mt++) mma_bf16(S[mt][NT - 1], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b0, b1);
+        }
+      }
+    }
+    have_state = true;
+    __syncthreads();                               // everybody is done with B and with the scaled x
+    fetch_b(c + 1);
   }
+  cp_async_wait<0>();
+  // ---- the state after the sequence's last chunk goes to its slot ----
+#pragma unroll
+  for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      const int n = 8 * NT * warp + 8 * nt + 2 * tq;
+      *reinterpret_cast<float2*>(slot + (size_t)(16 * mt + gq) * N + n) = make_float2(S[mt][nt][0], S[mt][nt][1]);
+      *reinterpret_cast<float2*>(slot + (size_t)(16 * mt + gq + 8) * N + n) = make_float2(S[mt][nt][2], S[mt][nt][3]);
+    }
 }
 
-// The state after a sequence's last chunk, decay * S_in + S_c, is what the carry would hand to a
-// next chunk; the carry kernel (ssm_state_pass_kernel in mamba.cu) writes it to the slot.
+size_t cb_smem(int N) { return (size_t)(64 + Q) * padded(N * 2); }
 
-inline size_t pad64(size_t n) { return (n + 63) / 64 * 64; }
-
-template <int P> size_t state_smem() { return (size_t)(Q * (P + 8) + Q * 136 + Q) * 4; }
-template <int P> size_t out_smem() {
-  return (size_t)(OUT_R * OUT_LDM + Q * (P + 8) + 2 * OUT_R * OUT_LDS + 2 * P * OUT_LDS + 2 * Q) * 4;
-}
-
-template <int P> int configure() {
-  if (cudaFuncSetAttribute(ssd_chunk_state_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)state_smem<P>()) != cudaSuccess ||
-      cudaFuncSetAttribute(ssd_chunk_out_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)out_smem<P>()) != cudaSuccess)
-    return tlc_fail(-2, "ssm_scan(chunked): cannot reserve shared memory");
-  return 0;
-}
-
-template <int P>
-int run(const float* xbc, const float* dt, const float* A, const float* Dskip, float* state, float* scratch,
-        const int* seg_start, const int* seg_seq, const int* seq_seg_start, const int* slots, const int* start_pos, float* y,
-        int B, int n_seg, int T, int Hs, int N, int G, int Cd, cudaStream_t stream) {
-  const int Di = Hs * P;
-  // every part starts on a 256-byte boundary of the scratch (float4 loads need 16)
-  float* chunk_state = scratch;                                          // [n_seg, Hs, P, N]
-  float* chunk_decay = chunk_state + pad64((size_t)n_seg * Hs * P * N);  // [n_seg, Hs]
-  float* cum = chunk_decay + pad64((size_t)n_seg * Hs);                  // [T, Hs]
-  float* cb = cum + pad64((size_t)T * Hs);                               // [n_seg, G, Q, Q]
-  tlc_launch(ssd_cumsum_kernel, dim3(n_seg, (Hs + 3) / 4), dim3(128), 0, stream, dt, A, seg_start, cum, chunk_decay, Hs);
-  tlc_launch(ssd_cb_kernel, dim3(n_seg, G, Q / 16), dim3(128), (16 + Q) * 68 * 4, stream, xbc, seg_start, cb, Di, N, G, Cd);
-  tlc_launch(ssd_chunk_state_kernel<P>, dim3(n_seg, Hs, (N + 127) / 128), dim3(256), state_smem<P>(), stream, xbc, dt,
-             (const float*)cum, seg_start, chunk_state, Hs, N, G, Cd);
-  TLC_CHECK_LAUNCH("ssm_scan(chunk states)");
-  if (int rc = tlc_ssm_state_pass_launch(chunk_decay, state, chunk_state, seq_seg_start, slots, start_pos, B, Hs, P * N, 1, stream))
-    return rc;
-  tlc_launch(ssd_chunk_out_kernel<P>, dim3(n_seg, Hs, 2), dim3(256), out_smem<P>(), stream, xbc, dt, (const float*)cum,
-             (const float*)cb, (const float*)chunk_state, Dskip, seg_start, y, Hs, N, G, Cd);
-  TLC_CHECK_LAUNCH("ssm_scan(chunk outputs)");
+template <int NT>
+int launch_walk(const __nv_bfloat16* xbc, const float* dt, const float* A, const float* Dskip, const __nv_bfloat16* cb,
+                float* state, const int* seg_start, const int* seq_seg_start, const int* slots, const int* start_pos,
+                float* y, int B, int Hs, int P, int G, int Cd, cudaStream_t stream) {
+  const WalkSmem lay(64 * NT);
+  tlc_launch(ssd_walk_kernel<NT>, dim3(B, Hs, P / PB), dim3(256), (size_t)lay.total, stream, xbc, dt, A, Dskip, cb, state,
+             seg_start, seq_seg_start, slots, start_pos, y, Hs, P, G, Cd);
+  TLC_CHECK_LAUNCH("ssm_scan(chunk walk)");
   return 0;
 }
 
 }  // namespace
 
 extern "C" int tlc_ssd_init() {
-  if (cudaFuncSetAttribute(ssd_cb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (16 + Q) * 68 * 4) != cudaSuccess)
+  if (cudaFuncSetAttribute(ssd_cb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cb_smem(256)) != cudaSuccess ||
+      cudaFuncSetAttribute(ssd_walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, WalkSmem(64).total) != cudaSuccess ||
+      cudaFuncSetAttribute(ssd_walk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, WalkSmem(128).total) != cudaSuccess ||
+      cudaFuncSetAttribute(ssd_walk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, WalkSmem(192).total) != cudaSuccess ||
+      cudaFuncSetAttribute(ssd_walk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, WalkSmem(256).total) != cudaSuccess)
     return tlc_fail(-2, "ssm_scan(chunked): cannot reserve shared memory");
-  if (int rc = configure<64>()) return rc;
-  return configure<128>();
+  return 0;
 }
 
-// Sizes this form is built for: head size 64 or 128, state size a multiple of 64, 16-byte aligned rows.
+// Sizes this form is built for: heads whose size is a multiple of 32, a state of 64, 128, 192 or 256 columns,
+// rows of x|B|C that start on 16-byte boundaries in bfloat16.
 extern "C" int tlc_ssd_ok(int Hs, int P, int N, int G, int Cd) {
-  return (P == 64 || P == 128) && N % 64 == 0 && N >= 64 && Cd % 4 == 0 && G > 0 && Hs % G == 0;
+  return P % PB == 0 && P >= PB && N % 64 == 0 && N >= 64 && N <= 256 && Cd % 8 == 0 && G > 0 && Hs % G == 0 &&
+         Hs <= 65535 && G <= 65535 && P / PB <= 65535;
 }
 
-// floats of scratch for n_seg chunks of T rows in all
+// floats of scratch for n_seg chunks: C B^T of every (chunk, group) in bfloat16
 extern "C" long long tlc_ssd_scratch_floats(int n_seg, int T, int Hs, int P, int N, int G) {
-  return (long long)(pad64((size_t)n_seg * Hs * P * N) + pad64((size_t)n_seg * Hs) + pad64((size_t)T * Hs) +
-                     pad64((size_t)n_seg * G * Q * Q));
+  return ((long long)n_seg * G * Q * Q + 1) / 2;
 }
 
-extern "C" int tlc_ssm_scan_ssd(const float* xbc, const float* dt, const float* A, const float* Dskip, float* state,
+extern "C" int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A, const float* Dskip, float* state,
                                 float* scratch, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
                                 const int* slots, const int* start_pos, float* y, int B, int n_seg, int T, int Hs, int P,
                                 int N, int G, int Cd, cudaStream_t stream) {
   if (B == 0 || n_seg == 0) return 0;
-  TLC_REQUIRE(tlc_ssd_ok(Hs, P, N, G, Cd), "ssm_scan(chunked, tensor cores): sizes Hs=%d P=%d N=%d G=%d are not built", Hs, P, N, G);
-  TLC_REQUIRE(Hs <= 65535 && G <= 65535, "ssm_scan: too many heads or groups");
-  if (P == 64)
-    return run<64>(xbc, dt, A, Dskip, state, scratch, seg_start, seg_seq, seq_seg_start, slots, start_pos, y, B, n_seg, T, Hs, N, G, Cd, stream);
-  return run<128>(xbc, dt, A, Dskip, state, scratch, seg_start, seg_seq, seq_seg_start, slots, start_pos, y, B, n_seg, T, Hs, N, G, Cd, stream);
+  TLC_REQUIRE(tlc_ssd_ok(Hs, P, N, G, Cd), "ssm_scan(chunked, tensor cores): sizes Hs=%d P=%d N=%d G=%d Cd=%d are not built",
+              Hs, P, N, G, Cd);
+  TLC_REQUIRE(((uintptr_t)xbc % 16) == 0 && ((uintptr_t)scratch % 16) == 0 && ((uintptr_t)state % 8) == 0 &&
+              ((uintptr_t)y % 8) == 0, "ssm_scan(chunked, tensor cores): misaligned buffers");
+  const __nv_bfloat16* x = (const __nv_bfloat16*)xbc;
+  __nv_bfloat16* cb = (__nv_bfloat16*)scratch;
+  tlc_launch(ssd_cb_kernel, dim3(n_seg, G, 2), dim3(128), cb_smem(N), stream, x, seg_start, cb, Hs * P, N, G, Cd);
+  TLC_CHECK_LAUNCH("ssm_scan(C B^T)");
+  switch (N / 64) {
+    case 1: return launch_walk<1>(x, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);
+    case 2: return launch_walk<2>(x, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);
+    case 3: return launch_walk<3>(x, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);
+    default: return launch_walk<4>(x, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);
+  }
 }

@@ -144,12 +144,14 @@ int tlc_attention_prefill(const void* q, const void* k_pages, const void* v_page
 
 /* ---- Mamba2 (mamba.cu, mamba_ssd.cu) ----------------------------------------------------------------- */
 /* Causal depthwise convolution + SiLU over the x|B|C columns of proj, continuing each sequence's window
- * conv_state [n_slots, K-1, Cd] (updated in place); dt = softplus(dt + dt_bias), dA = exp(dt * A). */
+ * conv_state [n_slots, K-1, Cd] (updated in place); dt = softplus(dt + dt_bias), dA = exp(dt * A).
+ * xbc_out [T, Cd] has the type xbc_dtype: float for single-token steps and the 32-bit scans, bfloat16
+ * for the scan of prompts in matrix form (tlc_ssm_scan_ssd). */
 int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, int dt_off, const float* w,
                    const float* bias, const float* dt_bias, const float* A, float* conv_state,
                    const int* cu_seqlens, const int* row_seq, const int* slots, const int* start_pos,
-                   float* xbc_out, float* dt_out, float* dA_out, int T, int B, int Cd, int K, int Hs,
-                   int single_rows, int quick, cudaStream_t stream);
+                   void* xbc_out, int xbc_dtype, float* dt_out, float* dA_out, int T, int B, int Cd, int K,
+                   int Hs, int single_rows, int quick, cudaStream_t stream);
 /* S = S * dA + B (x dt), y = S.C + x D, row by row from each slot's state [n_slots, Hs, P, N] (zero at
  * position 0), which is updated in place. */
 int tlc_ssm_scan(const float* xbc, const float* dt, const float* dA, const float* Dskip, float* state,
@@ -161,10 +163,13 @@ int tlc_ssm_scan_chunked(const float* xbc, const float* dt, const float* dA, con
                          float* chunk_state, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
                          const int* slots, const int* start_pos, float* y, int B, int n_seg, int Hs, int P, int N,
                          int G, int Cd, cudaStream_t stream);
-/* The chunks in matrix form on the tensor cores (bfloat16 runs); scratch of tlc_ssd_scratch_floats floats. */
+/* The chunks (of 128 rows at most) in matrix form on the tensor cores, for bfloat16 runs: xbc is bfloat16
+ * [T, Cd]; C B^T of every chunk goes through `scratch` (tlc_ssd_scratch_floats floats); one block per
+ * (sequence, head, 32 rows of the head) then walks the sequence's chunks in order with the state in its
+ * registers, from the slot's state to the slot's state. */
 int tlc_ssd_ok(int Hs, int P, int N, int G, int Cd);
 long long tlc_ssd_scratch_floats(int n_seg, int T, int Hs, int P, int N, int G);
-int tlc_ssm_scan_ssd(const float* xbc, const float* dt, const float* A, const float* Dskip, float* state,
+int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A, const float* Dskip, float* state,
                      float* scratch, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
                      const int* slots, const int* start_pos, float* y, int B, int n_seg, int T, int Hs, int P,
                      int N, int G, int Cd, cudaStream_t stream);

@@ -67,8 +67,8 @@ _SIGNATURES = {
     "tlc_attention_prefill_chunks": (_i, [_i, _i, _i, _vp]),
     "tlc_attention_prefill": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
                                    _vp, _i, _i, _vp]),
-    "tlc_mamba_conv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i,
-                            _i, _i, _i, _i, _vp]),
+    "tlc_mamba_conv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i,
+                            _i, _i, _i, _i, _i, _vp]),
     "tlc_ssm_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "tlc_ssm_scan_chunked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
                                   _vp]),
@@ -474,12 +474,15 @@ DISABLE_SSD = bool(int(os.environ.get("TLC_DISABLE_SSD", "0")))
 def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, bias: Optional[torch.Tensor],
                dt_bias: torch.Tensor, A: torch.Tensor, conv_state: torch.Tensor, cu_seqlens: torch.Tensor,
                row_seq: torch.Tensor, slots: torch.Tensor, start_pos: torch.Tensor, xbc_out: torch.Tensor,
-               dt_out: torch.Tensor, dA_out: torch.Tensor, single_rows: bool = False, quick: bool = False) -> None:
+               dt_out: torch.Tensor, dA_out: torch.Tensor, single_rows: bool = False, bf16_run: bool = False) -> None:
     """Causal depthwise convolution + SiLU of the xBC columns of proj, continuing each
     sequence's window (conv_state [n_slots, K-1, Cd], updated in place); also
     dt = softplus(dt + dt_bias) and dA = exp(dt * A) per row and head.  single_rows says
-    that every sequence brings exactly one row (row b belongs to sequence b); quick allows the
-    SiLU of prompts its fast exponential and reciprocal (bfloat16 runs)."""
+    that every sequence brings exactly one row (row b belongs to sequence b); bf16_run says that the
+    model computes in bfloat16: x|B|C, operands of the scan's matrix products, are then rounded to
+    bfloat16 values whatever type they are stored in, and the SiLU of prompts takes the fast exponential
+    and reciprocal.  xbc_out is float32, or
+    bfloat16 where the scan that follows takes its operands in that type (ssm_scan with A)."""
     _gpu(proj, w, bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out, dA_out)
     T = proj.shape[0]
     Cd, K = w.shape
@@ -493,13 +496,20 @@ def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, b
         _i32(t, n)
     if conv_state.dtype != torch.float32 or not conv_state.is_contiguous() or tuple(conv_state.shape[1:]) != (K - 1, Cd):
         raise KernelError("mamba_conv: conv_state must be contiguous float32 [n_slots, K-1, Cd]")
-    for t, shp, n in ((xbc_out, (T, Cd), "xbc_out"), (dt_out, (T, Hs), "dt_out"), (dA_out, (T, Hs), "dA_out")):
+    for t, shp, n in ((dt_out, (T, Hs), "dt_out"), (dA_out, (T, Hs), "dA_out")):
         if t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != shp:
             raise KernelError(f"mamba_conv: {n} must be contiguous float32 {shp}")
+    if not xbc_out.is_contiguous() or tuple(xbc_out.shape) != (T, Cd):
+        raise KernelError(f"mamba_conv: xbc_out must be contiguous {(T, Cd)}")
     _call("tlc_mamba_conv", proj.data_ptr(), dtype_code(proj.dtype), _rows(proj, "proj"), xbc_off, dt_off,
           w.data_ptr(), _p(bias), dt_bias.data_ptr(), A.data_ptr(), conv_state.data_ptr(), cu_seqlens.data_ptr(),
-          row_seq.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), xbc_out.data_ptr(), dt_out.data_ptr(),
-          dA_out.data_ptr(), T, B, Cd, K, Hs, int(bool(single_rows)), int(bool(quick)), _stream())
+          row_seq.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), xbc_out.data_ptr(), dtype_code(xbc_out.dtype),
+          dt_out.data_ptr(), dA_out.data_ptr(), T, B, Cd, K, Hs, int(bool(single_rows)), int(bool(bf16_run)), _stream())
+
+
+def ssd_ok(Hs: int, P: int, N: int, G: int) -> bool:
+    """Whether the scan of prompts in matrix form (bfloat16 operands, ssm_scan with A) is built for these sizes."""
+    return bool(not DISABLE_SSD and library().tlc_ssd_ok(Hs, P, N, G, Hs * P + 2 * G * N))
 
 
 def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch.Tensor, state: torch.Tensor,
@@ -508,19 +518,23 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch
     """Selective scan of every sequence in order, from its slot's state (zero at position 0);
     state [n_slots, Hs, P, N] float32 is updated in place; y [T, Hs*P] float32 is before gating.
     chunks = (seg_start [n+1], seg_seq [n], seq_seg_start [B+1]) cuts the sequences into
-    chunks that run in parallel (same result up to rounding).  With A (the per-head decay rate,
-    dA = exp(dt * A)) the chunks run in matrix form on the tensor cores with TF32 operands, for
-    head sizes of 64 or 128 and state sizes that are multiples of 64; a 32-bit run passes no A."""
+    chunks that run in parallel (same result up to rounding).  With a bfloat16 xbc and A (the per-head
+    decay rate, dA = exp(dt * A)) the chunks, of at most 128 rows, run in matrix form on the tensor cores
+    with bfloat16 operands (see ssd_ok for the sizes); every 32-bit run passes a float32 xbc."""
     _gpu(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y)
     T, Cd = xbc.shape
     if Cd != Hs * P + 2 * G * N:
         raise KernelError("ssm_scan: xbc width does not match Hs*P + 2*G*N")
+    matrix_form = xbc.dtype == torch.bfloat16
     for t, shp, n in ((xbc, (T, Cd), "xbc"), (dt, (T, Hs), "dt"), (dA, (T, Hs), "dA"), (y, (T, Hs * P), "y")):
-        if t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != shp:
-            raise KernelError(f"ssm_scan: {n} must be contiguous float32 {shp}")
+        want = torch.bfloat16 if (n == "xbc" and matrix_form) else torch.float32
+        if t.dtype != want or not t.is_contiguous() or tuple(t.shape) != shp:
+            raise KernelError(f"ssm_scan: {n} must be contiguous {want} {shp}")
     _f32vec(Dskip, Hs, "D")
     if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (Hs, P, N):
         raise KernelError("ssm_scan: state must be contiguous float32 [n_slots, Hs, P, N]")
+    if matrix_form and (chunks is None or A is None or not ssd_ok(Hs, P, N, G)):
+        raise KernelError("ssm_scan: a bfloat16 x|B|C is for the chunked scan in matrix form (chunks, A, sizes of ssd_ok)")
     if chunks is not None:
         seg_start, seg_seq, seq_seg_start = chunks
         for t, n in ((seg_start, "seg_start"), (seg_seq, "seg_seq"), (seq_seg_start, "seq_seg_start")):
@@ -528,7 +542,7 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch
             _i32(t, n)
         n_seg = seg_seq.numel()
         lib = library()
-        if A is not None and lib.tlc_ssd_ok(Hs, P, N, G, Cd) and not DISABLE_SSD:
+        if matrix_form:
             _f32vec(A, Hs, "A")
             scratch = torch.empty(lib.tlc_ssd_scratch_floats(n_seg, T, Hs, P, N, G), dtype=torch.float32, device=xbc.device)
             _call("tlc_ssm_scan_ssd", xbc.data_ptr(), dt.data_ptr(), A.data_ptr(), Dskip.data_ptr(), state.data_ptr(),

@@ -124,14 +124,19 @@ class Mamba2Mixer(Part):
         conv_state = cache.state[self.cache_key + ".conv"]
         ssm_state = cache.state[self.cache_key + ".ssm"]
         new = lambda shape, dtype: torch.empty(shape, dtype=dtype, device=proj.device)
-        xbc, dt, dA = new((T, self.Cd), f32), new((T, self.Hs), f32), new((T, self.Hs), f32)
+        # prompts cut into chunks of a bfloat16 run: the scan in matrix form, whose operands x|B|C the convolution
+        # writes in bfloat16 at once; everything else scans 32-bit values
+        chunks = step.chunks.get(self.scan_chunk)
+        matrix_form = chunks is not None and self.dtype == torch.bfloat16 and self.scan_chunk <= ops.SSD_CHUNK \
+            and ops.ssd_ok(self.Hs, self.P, self.N, self.G)
+        xbc = new((T, self.Cd), torch.bfloat16 if matrix_form else f32)
+        dt, dA = new((T, self.Hs), f32), new((T, self.Hs), f32)
         ops.mamba_conv(proj, self.Di, self.Di + self.Cd, self.conv_w, self.conv_b, self.dt_bias, self.A, conv_state,
                        step.cu_seqlens, step.row_seq, step.slots, step.start_pos, xbc, dt, dA,
                        step.max_new == 1, self.dtype == torch.bfloat16)
         y = new((T, self.Di), f32)
         ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs, self.P,
-                     self.N, self.G, step.chunks.get(self.scan_chunk),
-                     self.A if self.dtype == torch.bfloat16 and self.scan_chunk == ops.SSD_CHUNK else None)
+                     self.N, self.G, chunks, self.A if matrix_form else None)
         gated = out if out is not None else new((T, self.Di), self.dtype)
         ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated,
                           out_scale)
