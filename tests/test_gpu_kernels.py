@@ -334,6 +334,7 @@ def test_attention_of_single_token_steps_in_one_kernel(H, KV, hd, rope, window, 
                             hd, write)
     out_ref = torch.empty(B, H * hd, dtype=torch.bfloat16)
     ops_plain.attention(q_ref, k_ref, v_ref, table, pos, row_seq, slots, out_ref, H, KV, hd, scale, window)
+    counters = ops.new_arrival_counters("cuda")
     try:
         for max_keys, passes in ((longest + 1, 0), ((longest // 1024 + 1) * 1024, 0), (longest + 1, 0), (longest + 1, 2),
                                  ((longest // 1024 + 1) * 1024, 3), (longest + 1, 1000), (longest + 200, 1000)):
@@ -343,7 +344,9 @@ def test_attention_of_single_token_steps_in_one_kernel(H, KV, hd, rope, window, 
             qkv_gpu = qkv.cuda()
             assert ops.attention_decode_fused_ok(view(qkv_gpu), torch.bfloat16, H, KV, hd)
             ops.attention_decode_fused(view(qkv_gpu), 0, H * hd, (H + KV) * hd, k_gpu, v_gpu, inv.cuda(), write, table.cuda(),
-                                       pos.cuda(), row_seq.cuda(), slots.cuda(), out, H, KV, hd, scale, window, max_keys)
+                                       pos.cuda(), row_seq.cuda(), slots.cuda(), out, H, KV, hd, scale, window, max_keys,
+                                       counters)
+            assert int(counters.abs().sum()) == 0        # every launch leaves its counters at zero
             ref = out_ref.double()
             assert (ref - out.cpu().double()).abs().max() <= TOL[torch.bfloat16] * 2 * ref.abs().max()
             for name, got, want in (("keys", k_gpu, k_ref), ("values", v_gpu, v_ref)):
@@ -396,11 +399,12 @@ def test_outputs_into_columns_of_a_wider_buffer(dtype, H, KV, hd):
     qkv = rnd(g, 3, (H + 2 * KV) * hd).cuda()
     inv = (1.0 / torch.pow(torch.tensor(1e4, dtype=torch.float64), torch.arange(hd // 2, dtype=torch.float64) * 2 / hd)).float().cuda()
     if ops.attention_decode_fused_ok(qkv, dt, H, KV, hd):
+        counters = ops.new_arrival_counters("cuda")
         for max_keys in (700, 128):          # several blocks a row with a merge; one block a row
             if max_keys == 128:
                 pos = torch.tensor([100, 90, 69], dtype=torch.int32, device="cuda")
             both(lambda out: ops.attention_decode_fused(qkv, 0, H * hd, (H + KV) * hd, dev[0], dev[1], inv, False, dev[2],
-                                                        pos, row_seq, dev[5], out, H, KV, hd, scale, 0, max_keys), 3)
+                                                        pos, row_seq, dev[5], out, H, KV, hd, scale, 0, max_keys, counters), 3)
     # gated norm: vector and scalar kernels, with and without weights, scaled
     y = rnd(g, 5, W, scale=2.0).cuda()
     for zdt, w in ((torch.float32, 1 + rnd(g, W, scale=0.2).cuda()), (dt, 1 + rnd(g, W, scale=0.2).cuda()), (dt, None)):
@@ -509,23 +513,34 @@ def test_ssm_scan_in_matrix_form_on_tensor_cores(Hs, P, N, G):
     dA = torch.exp(dt * A)
     args = [rnd(g, T, Cd, dtype=torch.bfloat16), dt, dA, 1 + rnd(g, Hs, scale=0.1), rnd(g, 4, Hs, P, N), cu, slots, start_pos,
             torch.empty(T, Di), Hs, P, N, G, (i32(seg_start), i32(seg_seq), i32(seq_seg_start)), A]
-    gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args]
-    gpu[13] = tuple(t.cuda() for t in args[13])
+    args0 = [a.clone() if isinstance(a, torch.Tensor) else a for a in args]       # the plain scan updates its state in place
     assert ops.ssd_ok(Hs, P, N, G)
-    ops.ssm_scan(*gpu)
     ops_plain.ssm_scan(*args)
-    for i in (4, 8):
-        ref, got = args[i].double(), gpu[i].cpu().double()
-        # bfloat16 operands carry 8 bits: C B^T, the score matrix, the weighted x and the carried state's copy are
-        # each rounded to 2^-9 of their size before a product; sums over up to 128 rows and N columns of them
-        assert (ref - got).abs().max() <= 1.5e-2 * ref.abs().max(), f"output {i}: {(ref - got).abs().max()} of {ref.abs().max()}"
-        assert (ref - got).abs().mean() <= 1.5e-3 * ref.abs().max(), f"output {i} (mean)"
+    # states of 128 or 256 columns: the walk with tcgen05.mma and the state in tensor memory, and the mma.sync walk
+    for mode in ((0, 1) if N in (128, 256) else (0,)):
+        gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args0]
+        gpu[13] = tuple(t.cuda() for t in args0[13])
+        ops.ssd_walk_override(mode)
+        try:
+            ops.ssm_scan(*gpu)
+            torch.cuda.synchronize()
+            ops.check_errors()
+        finally:
+            ops.ssd_walk_override(0)
+        for i in (4, 8):
+            ref, got = args[i].double(), gpu[i].cpu().double()
+            # bfloat16 operands carry 8 bits: C B^T, the score matrix, the weighted x and the carried state's copy are
+            # each rounded to 2^-9 of their size before a product; sums over up to 128 rows and N columns of them
+            assert (ref - got).abs().max() <= 1.5e-2 * ref.abs().max(), \
+                f"walk {mode}, output {i}: {(ref - got).abs().max()} of {ref.abs().max()}"
+            assert (ref - got).abs().mean() <= 1.5e-3 * ref.abs().max(), f"walk {mode}, output {i} (mean)"
 
 
-def test_ssm_scan_in_matrix_form_finds_one_far_row():
+@pytest.mark.parametrize("N", [64, 128, 256])
+def test_ssm_scan_in_matrix_form_finds_one_far_row(N):
     """One row's x is 100 times the others' and decay is slow: its contribution must reach rows in later chunks
     through the carried state with the right decay (a chunk's state dropped or doubled shows at once)."""
-    Hs, P, N, G = 2, 64, 64, 1
+    Hs, P, G = 2, 64, 1
     g = gen(16)
     Di, Cd = Hs * P, Hs * P + 2 * G * N
     lens, starts = [400], [0]

@@ -23,6 +23,13 @@
 // numbers.  The 32-bit path of the library never comes here (mamba.cu has its three-pass scan).
 #include "common.cuh"
 
+// the same walk with tcgen05.mma and the state in tensor memory (mamba_ssd_tc.cu), for states of 128 or 256 columns
+int tlc_ssd_tc_init();
+int tlc_ssd_tc_run(const __nv_bfloat16* xbc, const float* dt, const float* A, const float* Dskip, const __nv_bfloat16* cb,
+                   __nv_bfloat16* bt, float* state, const int* seg_start, const int* seq_seg_start, const int* slots,
+                   const int* start_pos, float* y, int B, int n_seg, int T, int Hs, int P, int N, int G, int Cd,
+                   cudaStream_t stream);
+
 namespace {
 
 constexpr int Q = 128;       // rows per chunk
@@ -459,8 +466,13 @@ extern "C" int tlc_ssd_init() {
       cudaFuncSetAttribute(ssd_walk_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, WalkSmem(192).total) != cudaSuccess ||
       cudaFuncSetAttribute(ssd_walk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, WalkSmem(256).total) != cudaSuccess)
     return tlc_fail(-2, "ssm_scan(chunked): cannot reserve shared memory");
-  return 0;
+  return tlc_ssd_tc_init();
 }
+
+// Test hook: which walk runs where both are built (0: tcgen05 for states of 128 or 256 columns, else mma.sync;
+// 1: always mma.sync).
+static int g_ssd_walk = 0;
+extern "C" void tlc_ssd_walk_override(int mode) { g_ssd_walk = mode; }
 
 // Sizes this form is built for: heads whose size is a multiple of 32, a state of 64, 128, 192 or 256 columns,
 // rows of x|B|C that start on 16-byte boundaries in bfloat16.
@@ -469,9 +481,9 @@ extern "C" int tlc_ssd_ok(int Hs, int P, int N, int G, int Cd) {
          Hs <= 65535 && G <= 65535 && P / PB <= 65535;
 }
 
-// floats of scratch for n_seg chunks: C B^T of every (chunk, group) in bfloat16
+// floats of scratch for n_seg chunks: C B^T [128, 128] and B^T [N, 128] of every (chunk, group) in bfloat16
 extern "C" long long tlc_ssd_scratch_floats(int n_seg, int T, int Hs, int P, int N, int G) {
-  return ((long long)n_seg * G * Q * Q + 1) / 2;
+  return ((long long)n_seg * G * Q * (Q + N) + 1) / 2;
 }
 
 extern "C" int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A, const float* Dskip, float* state,
@@ -487,6 +499,9 @@ extern "C" int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A
   __nv_bfloat16* cb = (__nv_bfloat16*)scratch;
   tlc_launch(ssd_cb_kernel, dim3(n_seg, G, 2), dim3(128), cb_smem(N), stream, x, seg_start, cb, Hs * P, N, G, Cd);
   TLC_CHECK_LAUNCH("ssm_scan(C B^T)");
+  if ((N == 128 || N == 256) && g_ssd_walk == 0)
+    return tlc_ssd_tc_run(x, dt, A, Dskip, cb, cb + (size_t)n_seg * G * Q * Q, state, seg_start, seq_seg_start, slots,
+                          start_pos, y, B, n_seg, T, Hs, P, N, G, Cd, stream);
   switch (N / 64) {
     case 1: return launch_walk<1>(x, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);
     case 2: return launch_walk<2>(x, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);

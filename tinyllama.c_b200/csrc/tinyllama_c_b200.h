@@ -168,6 +168,9 @@ int tlc_ssm_scan_chunked(const float* xbc, const float* dt, const float* dA, con
  * (sequence, head, 32 rows of the head) then walks the sequence's chunks in order with the state in its
  * registers, from the slot's state to the slot's state. */
 int tlc_ssd_ok(int Hs, int P, int N, int G, int Cd);
+/* Test hook: 0 = the walk uses tcgen05.mma with the state in tensor memory where it is built (states of 128
+ * or 256 columns) and mma.sync with the state in registers elsewhere; 1 = always the latter. */
+void tlc_ssd_walk_override(int mode);
 long long tlc_ssd_scratch_floats(int n_seg, int T, int Hs, int P, int N, int G);
 int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A, const float* Dskip, float* state,
                      float* scratch, const int* seg_start, const int* seg_seq, const int* seq_seg_start,

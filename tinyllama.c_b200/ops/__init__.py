@@ -73,6 +73,7 @@ _SIGNATURES = {
     "tlc_ssm_scan_chunked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
                                   _vp]),
     "tlc_ssd_ok": (_i, [_i, _i, _i, _i, _i]),
+    "tlc_ssd_walk_override": (None, [_i]),
     "tlc_ssd_scratch_floats": (_ll, [_i, _i, _i, _i, _i, _i]),
     "tlc_ssm_scan_ssd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
                               _vp]),
@@ -414,25 +415,32 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
 
 
 DISABLE_FUSED_DECODE_ATTENTION = bool(int(os.environ.get("TLC_DISABLE_FUSED_DECODE_ATTENTION", "0")))
-# (device, stream) -> arrival counters of the fused single-token attention (zero between launches).  Launches
-# of one stream are ordered, so they can share counters; two models, or two streams of one model, that run at
-# the same time each get their own.
-_arrivals: dict = {}
+FUSED_DECODE_COUNTERS = 65536      # arrival counters a caller of attention_decode_fused provides (rows x kv heads at most)
+
+
+def new_arrival_counters(device) -> torch.Tensor:
+    """Zeroed arrival counters for attention_decode_fused.  They belong to whoever launches the kernel (an
+    attention mixer keeps its own): launches that share counters must not overlap on the GPU; every launch
+    leaves them at zero.  Allocate them outside any stream capture."""
+    return torch.zeros(FUSED_DECODE_COUNTERS, dtype=torch.int32, device=device)
 
 
 def attention_decode_fused_ok(qkv: torch.Tensor, cache_dtype: torch.dtype, H: int, KV: int, hd: int) -> bool:
     """Whether attention_decode_fused takes this projection, cache type and these sizes."""
     return bool(qkv.is_cuda and qkv.dtype == torch.float32 and cache_dtype == torch.bfloat16
+                and qkv.shape[0] * KV <= FUSED_DECODE_COUNTERS
                 and not DISABLE_FUSED_DECODE_ATTENTION and library().tlc_attention_decode_fused_ok(H, KV, hd))
 
 
 def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, k_pages: torch.Tensor,
                            v_pages: torch.Tensor, inv_freq: torch.Tensor, write_kv: bool, block_table: torch.Tensor,
                            positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
-                           H: int, KV: int, hd: int, scale: float, window: int, max_keys: int) -> None:
+                           H: int, KV: int, hd: int, scale: float, window: int, max_keys: int,
+                           arrivals: torch.Tensor) -> None:
     """Single-token steps in one kernel: rotates the row's queries and new key (2 * len(inv_freq)
     leading dims of each head), stores the new key/value row into its page when write_kv, attends
-    over the sequence's pages and writes out [T, H*hd] bfloat16.  qkv is float32 with dense rows."""
+    over the sequence's pages and writes out [T, H*hd] bfloat16.  qkv is float32 with dense rows.
+    arrivals: the caller's counters (new_arrival_counters)."""
     _gpu(qkv, k_pages, v_pages, inv_freq, block_table, positions, row_seq, slots, out)
     T = qkv.shape[0]
     for t, n in ((positions, "positions"), (row_seq, "row_seq"), (slots, "slots"), (block_table, "block_table")):
@@ -451,10 +459,11 @@ def attention_decode_fused(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int
     n_splits = (int(max_keys) + 127) // 128
     part_o = torch.empty((T, H, n_splits, hd), dtype=torch.float32, device=qkv.device)
     part_ml = torch.empty((T, H, n_splits, 2), dtype=torch.float32, device=qkv.device)
-    key = (qkv.device.index, _stream())
-    arrivals = _arrivals.get(key)
-    if arrivals is None or arrivals.numel() < T * KV:
-        arrivals = _arrivals[key] = torch.zeros(max(65536, 2 * T * KV), dtype=torch.int32, device=qkv.device)
+    _gpu(arrivals)
+    _i32(arrivals, "arrival counters")
+    if arrivals.numel() < T * KV:
+        raise KernelError(f"attention_decode_fused: {T * KV} (row, kv head) pairs need as many arrival counters, "
+                          f"{arrivals.numel()} given")
     _call("tlc_attention_decode_fused", qkv.data_ptr(), ld, q_off, k_off, v_off, k_pages.data_ptr(), v_pages.data_ptr(),
           inv_freq.data_ptr(), 2 * inv_freq.numel(), int(bool(write_kv)), block_table.data_ptr(), block_table.shape[1],
           positions.data_ptr(), row_seq.data_ptr(), slots.data_ptr(), out.data_ptr(), part_o.data_ptr(),
@@ -505,6 +514,12 @@ def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, b
           w.data_ptr(), _p(bias), dt_bias.data_ptr(), A.data_ptr(), conv_state.data_ptr(), cu_seqlens.data_ptr(),
           row_seq.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), xbc_out.data_ptr(), dtype_code(xbc_out.dtype),
           dt_out.data_ptr(), dA_out.data_ptr(), T, B, Cd, K, Hs, int(bool(single_rows)), int(bool(bf16_run)), _stream())
+
+
+def ssd_walk_override(mode: int) -> None:
+    """Which kernel walks a sequence's chunks where both are built (0: tcgen05 with the state in tensor memory for
+    states of 128 or 256 columns; 1: always mma.sync with the state in registers); for tests."""
+    library().tlc_ssd_walk_override(int(mode))
 
 
 def ssd_ok(Hs: int, P: int, N: int, G: int) -> bool:

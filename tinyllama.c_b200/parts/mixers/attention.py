@@ -65,6 +65,9 @@ class AttentionMixer(Part):
         self.o.bind(tensors, dtype, device)
         self.position.bind(tensors, dtype, device)
         self._no_rotation = torch.zeros(0, dtype=torch.float32, device=device)
+        # arrival counters of the one-kernel attention of single-token steps: this mixer's own, so that no other
+        # mixer, model or stream ever shares them; made here, outside any stream capture
+        self._arrivals = ops.new_arrival_counters(device) if torch.device(device).type == "cuda" else None
 
     def input_projection(self) -> StackedLinear:
         """What this mixer computes from the normed input before anything else (a block may stack
@@ -101,7 +104,7 @@ class AttentionMixer(Part):
             ops.attention_decode_fused(qkv, self.q_off, self.k_off, self.v_off, kv.k_pages, kv.v_pages, table,
                                        cache.writes, kv.block_table, step.positions, step.row_seq, step.slots, att,
                                        self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
-                                       step.max_context)
+                                       step.max_context, self._arrivals)
             return att
         q = torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
         ops.rope_kv_store(qkv, self.q_off, self.k_off, self.v_off, q, kv.k_pages, kv.v_pages, table, step.positions,
