@@ -24,7 +24,7 @@ __global__ void selftest_bounded_wait_kernel(ErrWords* err) {
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    mbar_wait(smem_u32(&bar), 0, err, 9);        // phase 0 never completes: the wait runs out and records 9
+    mbar_wait(smem_u32(&bar), 0, err, 9, mbar_wait_limit(err));        // phase 0 never completes: the wait runs out and records 9
   }
 }
 

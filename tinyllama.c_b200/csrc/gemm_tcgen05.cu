@@ -74,6 +74,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long wait_limit = mbar_wait_limit(err);
   const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   // splits > 1: a tile's K-steps are shared by `splits` blocks; each leaves its partial accumulator in `part`
   // [splits, M, N] and the last one to arrive (arrivals[tile * 4 + quarter], back at zero afterwards) adds
@@ -115,7 +116,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int k = sp * k_per; k < k_end; k++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          ok = mbar_wait(empty0 + 8 * s, ph ^ 1, err, 1);
+          ok = mbar_wait(empty0 + 8 * s, ph ^ 1, err, 1, wait_limit);
           if (!ok) break;
           mbar_expect_tx(full0 + 8 * s, S::A_BYTES + S::B_BYTES);
           tma_load_2d(smem_u32(b_tiles + s * S::B_BYTES), &map_b, full0 + 8 * s, k * BK, n0);
@@ -134,7 +135,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!ok || *(volatile int*)&err->flag != 0) {
         // something went wrong: let the copies still in flight land before the block exits
         for (int i = max(0, issued - STAGES); i < issued; i++)
-          mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, err, 4);
+          mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, err, 4, wait_limit);
       }
     }
   } else if (warp == 1) {
@@ -144,7 +145,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
         const int as = local & 1;
-        ok = mbar_wait(acc_empty0 + 8 * as, ((local >> 1) & 1) ^ 1, err, 5);   // the epilogue has drained this half
+        ok = mbar_wait(acc_empty0 + 8 * as, ((local >> 1) & 1) ^ 1, err, 5, wait_limit);   // the epilogue has drained this half
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t d_tmem = tmem + (uint32_t)(as * BN);
@@ -153,7 +154,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int k = k_begin; k < k_end; k++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          ok = mbar_wait(full0 + 8 * s, ph, err, 2);
+          ok = mbar_wait(full0 + 8 * s, ph, err, 2, wait_limit);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_addr = smem_u32(a_tiles + s * S::A_BYTES), b_addr = smem_u32(b_tiles + s * S::B_BYTES);
@@ -179,7 +180,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int as = local & 1;
       const int ot = tile % out_tiles, sp = tile / out_tiles;
       const int m0 = (ot % m_tiles) * BM, n0 = (ot / m_tiles) * BN;
-      ok = mbar_wait(acc_full0 + 8 * as, (local >> 1) & 1, err, 3);
+      ok = mbar_wait(acc_full0 + 8 * as, (local >> 1) & 1, err, 3, wait_limit);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int mrow0 = m0 + quarter * 32;

@@ -77,12 +77,33 @@ __host__ __device__ constexpr int padded(int row_bytes) { return row_bytes + 16;
 
 // ---- C B^T per (chunk, group): cb[seg, g, i, j] for j <= i (bfloat16) -------------------------------------
 // grid (seg, G, 2), 4 warps: a block owns 64 rows i, warp w the rows [16 w, 16 w + 16) of them and the columns
-// j up to its diagonal; K = N.
+// j up to its diagonal; K = N.  With bt (the walk on tcgen05 wants B transposed) the grid has N / 64 more blocks
+// along z, each of which writes bt[seg, g, n, j] = B[row j of the chunk, n] for 64 columns n (zero past the chunk).
 __global__ void __launch_bounds__(128)
 ssd_cb_kernel(const __nv_bfloat16* __restrict__ xbc, const int* __restrict__ seg_start, __nv_bfloat16* __restrict__ cb,
-              int Di, int N, int G, int Cd) {
-  tlc_pdl(xbc, cb);
+              __nv_bfloat16* __restrict__ bt, int Di, int N, int G, int Cd) {
+  tlc_pdl(xbc, cb, bt);
   extern __shared__ __align__(16) unsigned char ssd_sm[];
+  if (blockIdx.z >= 2) {
+    unsigned short (*tile)[64 + 2] = reinterpret_cast<unsigned short (*)[64 + 2]>(ssd_sm);     // [Q][66]
+    const int seg = blockIdx.x, g = blockIdx.y, n0 = (blockIdx.z - 2) * 64;
+    const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
+    const unsigned short* Bg = reinterpret_cast<const unsigned short*>(xbc) + Di + (size_t)g * N + n0;
+    for (int idx = threadIdx.x; idx < Q * 32; idx += 128) {
+      const int j = idx >> 5, c = (idx & 31) * 2;
+      uint32_t v = 0;
+      if (j < L) v = *reinterpret_cast<const uint32_t*>(Bg + (size_t)(t0 + j) * Cd + c);
+      tile[j][c] = (unsigned short)(v & 0xffffu);
+      tile[j][c + 1] = (unsigned short)(v >> 16);
+    }
+    __syncthreads();
+    unsigned short* out = reinterpret_cast<unsigned short*>(bt) + (((size_t)seg * G + g) * N + n0) * Q;
+    for (int idx = threadIdx.x; idx < 64 * (Q / 2); idx += 128) {
+      const int n = idx / (Q / 2), j = (idx % (Q / 2)) * 2;
+      *reinterpret_cast<uint32_t*>(out + (size_t)n * Q + j) = (uint32_t)tile[j][n] | ((uint32_t)tile[j + 1][n] << 16);
+    }
+    return;
+  }
   const int LDN = padded(N * 2);
   unsigned char* Cs = ssd_sm;                     // [64][LDN]   rows i
   unsigned char* Bs = ssd_sm + 64 * LDN;          // [Q][LDN]    rows j
@@ -497,11 +518,14 @@ extern "C" int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A
               ((uintptr_t)y % 8) == 0, "ssm_scan(chunked, tensor cores): misaligned buffers");
   const __nv_bfloat16* x = (const __nv_bfloat16*)xbc;
   __nv_bfloat16* cb = (__nv_bfloat16*)scratch;
-  tlc_launch(ssd_cb_kernel, dim3(n_seg, G, 2), dim3(128), cb_smem(N), stream, x, seg_start, cb, Hs * P, N, G, Cd);
+  const bool tc = (N == 128 || N == 256) && g_ssd_walk == 0;
+  __nv_bfloat16* bt = tc ? cb + (size_t)n_seg * G * Q * Q : nullptr;
+  tlc_launch(ssd_cb_kernel, dim3(n_seg, G, 2 + (tc ? N / 64 : 0)), dim3(128), cb_smem(N), stream, x, seg_start, cb, bt, Hs * P,
+             N, G, Cd);
   TLC_CHECK_LAUNCH("ssm_scan(C B^T)");
-  if ((N == 128 || N == 256) && g_ssd_walk == 0)
-    return tlc_ssd_tc_run(x, dt, A, Dskip, cb, cb + (size_t)n_seg * G * Q * Q, state, seg_start, seq_seg_start, slots,
-                          start_pos, y, B, n_seg, T, Hs, P, N, G, Cd, stream);
+  if (tc)
+    return tlc_ssd_tc_run(x, dt, A, Dskip, cb, bt, state, seg_start, seq_seg_start, slots, start_pos, y, B, n_seg, T, Hs, P, N,
+                          G, Cd, stream);
   switch (N / 64) {
     case 1: return launch_walk<1>(x, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);
     case 2: return launch_walk<2>(x, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);

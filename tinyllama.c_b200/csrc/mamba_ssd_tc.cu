@@ -1,15 +1,17 @@
 // The walk over a sequence's chunks (see mamba_ssd.cu for the math) with the products on the 5th-generation
 // tensor cores: tcgen05.mma from shared-memory operands into tensor memory, for states of 128 or 256 columns.
 //
-// One block per (sequence, head, 32 rows p of the head), 8 warps.  Tensor memory holds the state transposed,
+// One block per (sequence, head, 32 rows p of the head): 8 warps of workers and one warp whose first lane issues
+// the copies and the products.  Tensor memory holds the state transposed,
 // S^T[n, p] (lanes = state columns, two tiles of 128 for N = 256), from the slot's state before the first
 // chunk to the slot's state after the last, and the two accumulators of a chunk's outputs.  Per chunk:
 //   * C [128 rows, N] and B^T [N, 128 rows] arrive by TMA (128-byte swizzle, K along the rows of shared memory:
-//     the state columns for C, the chunk's rows for B^T, which ssd_bt_kernel wrote transposed);
+//     the state columns for C, the chunk's rows for B^T, which ssd_cb_kernel wrote transposed beside C B^T);
 //   * the threads read the state back (tcgen05.ld), leave a bfloat16 copy [p, n] in shared memory for C S^T,
 //     scale it by the chunk's decay and store it again (tcgen05.st); they build the score matrix
 //     M[i, j] = cb exp(cum_i - cum_j) dt_j, x^T and (w x)^T in shared memory in the layout tcgen05.mma reads;
-//   * one thread issues D1 = C S^T, D2 = M x, S^T += B^T (w x) and commits them to mbarriers;
+//   * the issuing thread starts D1 = C S^T, D2 = M x and S^T += B^T (w x), commits them to mbarriers, and
+//     refills C's and B^T's buffers for the next chunk as soon as the products that read them are done;
 //   * the threads read D1 and D2 back and write y = exp(cum_i) D1 + D2 + D x.
 // Every operand is K-major with the 128-byte swizzle, the layout of the linear layers' tiles.  Every wait on an
 // mbarrier is bounded; a wait that runs out is recorded in the library's error word, the walk goes on without
@@ -52,31 +54,6 @@ __device__ __forceinline__ uint32_t sw128(int row, int k, int slab_bytes) {
   return (uint32_t)((k >> 6) * slab_bytes + row * 128 + ((((k & 63) >> 3) ^ (row & 7)) << 4) + (k & 7) * 2);
 }
 
-// ---- B^T per (chunk, group): bt[seg, g, n, j] = B[row j of the chunk, n], zero for rows past the chunk ----
-// grid (seg, G, N / 64), 256 threads: a 128 x 64 tile through shared memory.
-__global__ void __launch_bounds__(256)
-ssd_bt_kernel(const __nv_bfloat16* __restrict__ xbc, const int* __restrict__ seg_start, __nv_bfloat16* __restrict__ bt,
-              int Di, int N, int G, int Cd) {
-  tlc_pdl(xbc, bt);
-  __shared__ unsigned short tile[Q][64 + 2];
-  const int seg = blockIdx.x, g = blockIdx.y, n0 = blockIdx.z * 64;
-  const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
-  const unsigned short* Bg = reinterpret_cast<const unsigned short*>(xbc) + Di + (size_t)g * N + n0;
-  for (int idx = threadIdx.x; idx < Q * 32; idx += 256) {
-    const int j = idx >> 5, c = (idx & 31) * 2;
-    uint32_t v = 0;
-    if (j < L) v = *reinterpret_cast<const uint32_t*>(Bg + (size_t)(t0 + j) * Cd + c);
-    tile[j][c] = (unsigned short)(v & 0xffffu);
-    tile[j][c + 1] = (unsigned short)(v >> 16);
-  }
-  __syncthreads();
-  unsigned short* out = reinterpret_cast<unsigned short*>(bt) + (((size_t)seg * G + g) * N + n0) * Q;
-  for (int idx = threadIdx.x; idx < 64 * (Q / 2); idx += 256) {
-    const int n = idx / (Q / 2), j = (idx % (Q / 2)) * 2;
-    *reinterpret_cast<uint32_t*>(out + (size_t)n * Q + j) = (uint32_t)tile[j][n] | ((uint32_t)tile[j + 1][n] << 16);
-  }
-}
-
 // Shared memory of the walk (byte offsets from a 1024-byte boundary).  NTILES = N / 128.
 template <int NTILES>
 struct TcSmem {
@@ -84,15 +61,18 @@ struct TcSmem {
   static constexpr int C_SLAB = Q * 128, C = 0, C_BYTES = (N / 64) * C_SLAB;            // [128 rows i][N], slabs of 64 n
   static constexpr int BT_SLAB = N * 128, BT = C + C_BYTES, BT_BYTES = 2 * BT_SLAB;      // [N rows n][128 j], slabs of 64 j
   static constexpr int M_SLAB = Q * 128, M = BT + BT_BYTES, M_BYTES = 2 * M_SLAB;        // [128 rows i][128 j]
-  static constexpr int X_SLAB = PB * 128, XT = M + M_BYTES, XWT = XT + 2 * X_SLAB;       // [32 rows p][128 j] each
-  static constexpr int S_SLAB = PB * 128, S = XWT + 2 * X_SLAB, S_BYTES = (N / 64) * S_SLAB;   // [32 rows p][N]
+  static constexpr int X_SLAB = PB * 128, XT = M + M_BYTES, XWT = XT + 2 * X_SLAB;       // [32 rows p][128 j]; (w x)^T twice
+  static constexpr int S_SLAB = PB * 128, S = XWT + 4 * X_SLAB, S_BYTES = (N / 64) * S_SLAB;   // [32 rows p][N]
   static constexpr int F = S + S_BYTES;                                                  // floats: cums, dts, ws, es, wsum
   static constexpr int BARS = F + (4 * Q + 8) * 4;                                       // 4 mbarriers, tmem slot, dead flag
   static constexpr int TOTAL = BARS + 64 + 1024;                                         // + alignment slack
 };
 
+constexpr int WORKERS = 256, THREADS = WORKERS + 32;
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
 template <int NTILES>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(THREADS, 1)
 ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_bt,
                    const __nv_bfloat16* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ A,
                    const float* __restrict__ Dskip, const __nv_bfloat16* __restrict__ cb, float* __restrict__ state,
@@ -122,6 +102,7 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
   const int c0 = seq_seg_start[b], c1 = seq_seg_start[b + 1];
   if (c1 <= c0) return;
   const float a_log2 = A[h] * LOG2E, Dh = Dskip[h];
+  const long long wait_limit = mbar_wait_limit(err);
   const unsigned short* Xg = reinterpret_cast<const unsigned short*>(xbc) + (size_t)h * P + p0;
   const int c_col0 = Di + G * N + g * N;               // first column of this group's C in a row of x|B|C
 
@@ -136,6 +117,8 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  // the score matrix's pieces above the diagonal are never written again: zero once
+  for (int i = tid; i < L_::M_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(sm + L_::M)[i] = make_uint4(0u, 0u, 0u, 0u);
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -144,7 +127,7 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
   // a bounded wait; once one has run out, no further wait is attempted
   auto wait = [&](uint32_t bar, uint32_t parity, int code) {
     if (*dead) return;
-    if (!mbar_wait(bar, parity, err, code)) *dead = 1;
+    if (!mbar_wait(bar, parity, err, code, wait_limit)) *dead = 1;
   };
   auto fetch_c = [&](int c) {                          // thread 0: C of chunk c
     mbar_expect_tx(bar_c, L_::C_BYTES);
@@ -162,10 +145,64 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
     }
     return 0.f;
   };
-  if (tid == 0) { fetch_c(c0); fetch_bt(c0); }
+  if (warp == WORKERS / 32) {
+    // ---- the issuing warp: its first lane starts copies and products; nothing else runs here ----
+    constexpr uint32_t idesc = instr_desc(128, PB);
+    if (lane == 0) {
+      fetch_c(c0);
+      fetch_bt(c0);
+    }
+    __syncwarp();
+#pragma unroll 1
+    for (int c = c0; c < c1; c++) {
+      const uint32_t ph = (uint32_t)((c - c0) & 1);
+      const int xw_off = L_::XWT + (int)ph * 2 * L_::X_SLAB;
+      asm volatile("bar.sync 2, %0;" ::"n"(THREADS) : "memory");      // the workers' operands of this chunk are in place
+      if (lane == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        wait(bar_c, ph, 11);                           // C of this chunk has landed
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // D1 = C S^T (K = the state columns)
+#pragma unroll
+        for (int s = 0; s < N / 64; s++)
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++)
+            umma(tmem + 64u, smem_desc(sm0 + L_::C + s * L_::C_SLAB + kk * 32), smem_desc(sm0 + L_::S + s * L_::S_SLAB + kk * 32),
+                 idesc, (s > 0 || kk > 0) ? 1u : 0u);
+        // D2 = M x (K = the chunk's rows)
+#pragma unroll
+        for (int s = 0; s < 2; s++)
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++)
+            umma(tmem + 96u, smem_desc(sm0 + L_::M + s * L_::M_SLAB + kk * 32), smem_desc(sm0 + L_::XT + s * L_::X_SLAB + kk * 32),
+                 idesc, (s > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar_y);
+        wait(bar_bt, ph, 12);                          // B^T of this chunk has landed
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // S^T += B^T (w x) (K = the chunk's rows), a tile of 128 state columns at a time
+#pragma unroll
+        for (int t = 0; t < NTILES; t++)
+#pragma unroll
+          for (int s = 0; s < 2; s++)
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++)
+              umma(tmem + (uint32_t)(32 * t), smem_desc(sm0 + L_::BT + s * L_::BT_SLAB + t * (128 * 128) + kk * 32),
+                   smem_desc(sm0 + xw_off + s * L_::X_SLAB + kk * 32), idesc, 1u);
+        umma_commit(bar_s);
+        if (c + 1 < c1) {
+          wait(bar_y, ph, 14);                         // C's buffer is free again
+          fetch_c(c + 1);
+          wait(bar_s, ph, 13);                         // and B^T's
+          fetch_bt(c + 1);
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+  // ---- the workers ----
   float dt_reg = load_dt(c0);
 
-  // ---- the state: this thread holds column n = 128 tile + 32 quarter + lane of S^T, all 32 rows p ----
+  // the state: this thread holds column n = 128 tile + 32 quarter + lane of S^T, all 32 rows p
   const int tile = NTILES == 1 ? 0 : (warp >> 2), quarter = warp & 3;
   const bool owns_state = NTILES == 2 || warp < 4;     // with one tile, warps 4..7 hold no state
   const int n_mine = 128 * tile + 32 * quarter + lane;
@@ -180,27 +217,51 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
     for (int p = 0; p < 32; p++) sreg[p] = have ? __float_as_uint(slot[(size_t)p * N + n_mine]) : 0u;
   }
 
+  // What a thread reads from global memory for a chunk, fetched one chunk ahead.
+  // Of C B^T: rows r = tid / 4 and 127 - r have 17 pieces of 8 columns up to their diagonals between them; the four
+  // threads of the pair take every fourth piece (the first a fifth one), so that every thread has four or five.
+  // Of x: row mi = tid % 128, columns [16 mhalf, 16 mhalf + 16) of the block's 32; the same values serve x^T, (w x)^T
+  // and the D x of the output row mi.
+  const int mi = tid & 127, mhalf = tid >> 7;
+  const int pr = tid >> 2, pu = tid & 3, n_first = (pr >> 3) + 1;      // pieces of row pr; row 127 - pr has 17 - n_first
+  uint4 cbv[5], xv[2], xv_next[2];
+  auto piece = [&](int e, int& row, int& q) {            // piece e of the pair's 17: its row and its index in the row
+    const bool first = e < n_first;
+    row = first ? pr : 127 - pr;
+    q = first ? e : e - n_first;
+  };
+  auto load_cb = [&](int c) {
+    if (c < c1) {
+      const int L = seg_start[c + 1] - seg_start[c];
+      const __nv_bfloat16* base = cb + (((size_t)c * G + g) * Q) * Q;
+#pragma unroll
+      for (int u = 0; u < 5; u++) {
+        const int e = pu + 4 * u;
+        int row, q;
+        piece(e, row, q);
+        if (e < 17 && row < L) cbv[u] = __ldg(reinterpret_cast<const uint4*>(base + (size_t)row * Q + 8 * q));
+      }
+    }
+  };
+  auto load_x = [&](int c, uint4 (&dst)[2]) {
+    dst[0] = dst[1] = make_uint4(0u, 0u, 0u, 0u);
+    if (c < c1) {
+      const int t0 = seg_start[c], L = seg_start[c + 1] - t0;
+      if (mi < L) {
+        const uint4* src = reinterpret_cast<const uint4*>(Xg + (size_t)(t0 + mi) * Cd + 16 * mhalf);
+        dst[0] = __ldg(src);
+        dst[1] = __ldg(src + 1);
+      }
+    }
+  };
+  load_cb(c0);
+  load_x(c0, xv);
+
 #pragma unroll 1
   for (int c = c0; c < c1; c++) {
-    const uint32_t ph = (uint32_t)((c - c0) & 1);
+    const int k = c - c0;
+    const uint32_t ph = (uint32_t)(k & 1);
     const int t0 = seg_start[c], L = seg_start[c + 1] - t0;
-    // this thread's share of C B^T: row i = tid % 128, columns [64 half, 64 half + 64); on its way while the rest is prepared
-    const int mi = tid & 127, mhalf = tid >> 7;
-    const bool m_live = mi < L && 64 * mhalf <= mi;
-    uint4 cbv[8];
-    if (m_live) {
-      const uint4* src = reinterpret_cast<const uint4*>(cb + ((((size_t)c * G + g) * Q) + mi) * Q + 64 * mhalf);
-#pragma unroll
-      for (int q = 0; q < 8; q++) cbv[q] = (64 * mhalf + 8 * q <= mi) ? __ldg(src + q) : make_uint4(0u, 0u, 0u, 0u);
-    }
-    // this thread's share of x: row j = tid % 128, columns [16 xhalf, 16 xhalf + 16) of the block's 32
-    const int xj = tid & 127, xhalf = tid >> 7;
-    uint4 xv[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
-    if (xj < L) {
-      const uint4* src = reinterpret_cast<const uint4*>(Xg + (size_t)(t0 + xj) * Cd + 16 * xhalf);
-      xv[0] = __ldg(src);
-      xv[1] = __ldg(src + 1);
-    }
     // ---- cumulative log2 decay of the chunk's rows ----
     float v = dt_reg * a_log2;
     if (tid < Q) {
@@ -211,12 +272,12 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
       }
       if (lane == 31) wsum[warp] = v;
     }
-    __syncthreads();
+    workers_sync();
     const float total = wsum[0] + wsum[1] + wsum[2] + wsum[3];
     if (tid < Q) {
       float off = 0.f;
 #pragma unroll
-      for (int k = 0; k < 3; k++) if (k < warp) off += wsum[k];
+      for (int q = 0; q < 3; q++) if (q < warp) off += wsum[q];
       const float cum = v + off;
       cums[tid] = cum;
       dts[tid] = dt_reg;
@@ -225,11 +286,59 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
     }
     const float decay = exp2f(total);
     dt_reg = load_dt(c + 1);
+    if (c > c0) {
+      wait(bar_y, ph ^ 1, 14);                         // the products that read M, x^T and the state's copy are done
+    }
+    workers_sync();                                    // cums, dts, ws, es are in place
+    // ---- the score matrix M, K-major: row i, the pieces of 8 columns up to the diagonal ----
+#pragma unroll
+    for (int u = 0; u < 5; u++) {
+      const int e = pu + 4 * u;
+      int row, q;
+      piece(e, row, q);
+      if (e < 17 && row < L) {
+        const int j0 = 8 * q;
+        const float ci = cums[row];
+        const float4 cj0 = *reinterpret_cast<const float4*>(cums + j0), cj1 = *reinterpret_cast<const float4*>(cums + j0 + 4);
+        const float4 dj0 = *reinterpret_cast<const float4*>(dts + j0), dj1 = *reinterpret_cast<const float4*>(dts + j0 + 4);
+        const float cj[8] = {cj0.x, cj0.y, cj0.z, cj0.w, cj1.x, cj1.y, cj1.z, cj1.w};
+        const float dj[8] = {dj0.x, dj0.y, dj0.z, dj0.w, dj1.x, dj1.y, dj1.z, dj1.w};
+        const uint32_t w4[4] = {cbv[u].x, cbv[u].y, cbv[u].z, cbv[u].w};
+        uint32_t r4[4];
+#pragma unroll
+        for (int x = 0; x < 4; x++) {
+          const float2 m = unpack_bf16(w4[x]);
+          const int j = j0 + 2 * x;
+          const float m0 = j <= row ? m.x * ex2_quick(ci - cj[2 * x]) * dj[2 * x] : 0.f;
+          const float m1 = j + 1 <= row ? m.y * ex2_quick(ci - cj[2 * x + 1]) * dj[2 * x + 1] : 0.f;
+          r4[x] = pack_bf16(m0, m1);
+        }
+        *reinterpret_cast<uint4*>(sm + L_::M + (q >> 3) * L_::M_SLAB + row * 128 + (((q & 7) ^ (row & 7)) << 4)) =
+            make_uint4(r4[0], r4[1], r4[2], r4[3]);
+      }
+    }
+    load_cb(c + 1);                                    // its registers are free: the next chunk's share is on its way
+    // ---- x^T and (w x)^T, K-major: row p, column j.  (w x)^T alternates between two buffers: the state update of
+    // the chunk before may still be reading the other ----
+    const int xw_off = L_::XWT + (k & 1) * 2 * L_::X_SLAB;
+    {
+      const float w = ws[mi];
+      const uint32_t w8[8] = {xv[0].x, xv[0].y, xv[0].z, xv[0].w, xv[1].x, xv[1].y, xv[1].z, xv[1].w};
+#pragma unroll
+      for (int e = 0; e < 8; e++) {
+        const int p = 16 * mhalf + 2 * e;
+        const float2 x2 = unpack_bf16(w8[e]);
+        *reinterpret_cast<unsigned short*>(sm + L_::XT + sw128(p, mi, L_::X_SLAB)) = (unsigned short)(w8[e] & 0xffffu);
+        *reinterpret_cast<unsigned short*>(sm + L_::XT + sw128(p + 1, mi, L_::X_SLAB)) = (unsigned short)(w8[e] >> 16);
+        *reinterpret_cast<unsigned short*>(sm + xw_off + sw128(p, mi, L_::X_SLAB)) = bf16_bits(x2.x * w);
+        *reinterpret_cast<unsigned short*>(sm + xw_off + sw128(p + 1, mi, L_::X_SLAB)) = bf16_bits(x2.y * w);
+      }
+    }
+    load_x(c + 1, xv_next);
     // ---- the state: wait for the last update, copy it in bfloat16 for C S^T, decay it, hand it back ----
     if (c > c0) {
       wait(bar_s, ph ^ 1, 13);                         // the state update of the chunk before
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (tid == 0) fetch_bt(c);                       // B^T's buffer is free again
       __syncwarp();
       if (owns_state) tmem_ld32(t_state, sreg);
     }
@@ -243,111 +352,34 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
       __syncwarp();
       tmem_st32(t_state, sreg);
     }
-    __syncthreads();                                   // cums, dts, ws, es are in place
-    // ---- the score matrix M, K-major: row i, columns j <= i ----
-    {
-      const float ci = cums[mi];
-#pragma unroll
-      for (int q = 0; q < 8; q++) {
-        uint4 o = make_uint4(0u, 0u, 0u, 0u);
-        const int j0 = 64 * mhalf + 8 * q;
-        if (m_live && j0 <= mi) {
-          const float4 cj0 = *reinterpret_cast<const float4*>(cums + j0), cj1 = *reinterpret_cast<const float4*>(cums + j0 + 4);
-          const float4 dj0 = *reinterpret_cast<const float4*>(dts + j0), dj1 = *reinterpret_cast<const float4*>(dts + j0 + 4);
-          const float cj[8] = {cj0.x, cj0.y, cj0.z, cj0.w, cj1.x, cj1.y, cj1.z, cj1.w};
-          const float dj[8] = {dj0.x, dj0.y, dj0.z, dj0.w, dj1.x, dj1.y, dj1.z, dj1.w};
-          const uint32_t w4[4] = {cbv[q].x, cbv[q].y, cbv[q].z, cbv[q].w};
-          uint32_t r4[4];
-#pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const float2 m = unpack_bf16(w4[e]);
-            const int j = j0 + 2 * e;
-            const float m0 = j <= mi ? m.x * ex2_quick(ci - cj[2 * e]) * dj[2 * e] : 0.f;
-            const float m1 = j + 1 <= mi ? m.y * ex2_quick(ci - cj[2 * e + 1]) * dj[2 * e + 1] : 0.f;
-            r4[e] = pack_bf16(m0, m1);
-          }
-          o = make_uint4(r4[0], r4[1], r4[2], r4[3]);
-        }
-        *reinterpret_cast<uint4*>(sm + L_::M + mhalf * L_::M_SLAB + mi * 128 + ((q ^ (mi & 7)) << 4)) = o;
-      }
-    }
-    // ---- x^T and (w x)^T, K-major: row p, column j ----
-    {
-      const float w = ws[xj];
-      const uint32_t w8[8] = {xv[0].x, xv[0].y, xv[0].z, xv[0].w, xv[1].x, xv[1].y, xv[1].z, xv[1].w};
-#pragma unroll
-      for (int e = 0; e < 8; e++) {
-        const int p = 16 * xhalf + 2 * e;
-        const float2 x2 = unpack_bf16(w8[e]);
-        *reinterpret_cast<unsigned short*>(sm + L_::XT + sw128(p, xj, L_::X_SLAB)) = (unsigned short)(w8[e] & 0xffffu);
-        *reinterpret_cast<unsigned short*>(sm + L_::XT + sw128(p + 1, xj, L_::X_SLAB)) = (unsigned short)(w8[e] >> 16);
-        *reinterpret_cast<unsigned short*>(sm + L_::XWT + sw128(p, xj, L_::X_SLAB)) = bf16_bits(x2.x * w);
-        *reinterpret_cast<unsigned short*>(sm + L_::XWT + sw128(p + 1, xj, L_::X_SLAB)) = bf16_bits(x2.y * w);
-      }
-    }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // what the threads wrote, before the tensor cores read it
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      constexpr uint32_t idesc = instr_desc(128, PB);
-      wait(bar_c, ph, 11);                             // C of this chunk has landed
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // D1 = C S^T (K = the state columns)
-#pragma unroll
-      for (int s = 0; s < N / 64; s++)
-#pragma unroll
-        for (int kk = 0; kk < 4; kk++)
-          umma(tmem + 64u, smem_desc(sm0 + L_::C + s * L_::C_SLAB + kk * 32), smem_desc(sm0 + L_::S + s * L_::S_SLAB + kk * 32),
-               idesc, (s > 0 || kk > 0) ? 1u : 0u);
-      // D2 = M x (K = the chunk's rows)
-#pragma unroll
-      for (int s = 0; s < 2; s++)
-#pragma unroll
-        for (int kk = 0; kk < 4; kk++)
-          umma(tmem + 96u, smem_desc(sm0 + L_::M + s * L_::M_SLAB + kk * 32), smem_desc(sm0 + L_::XT + s * L_::X_SLAB + kk * 32),
-               idesc, (s > 0 || kk > 0) ? 1u : 0u);
-      umma_commit(bar_y);
-      wait(bar_bt, ph, 12);                            // B^T of this chunk has landed
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // S^T += B^T (w x) (K = the chunk's rows), a tile of 128 state columns at a time
-#pragma unroll
-      for (int t = 0; t < NTILES; t++)
-#pragma unroll
-        for (int s = 0; s < 2; s++)
-#pragma unroll
-          for (int kk = 0; kk < 4; kk++)
-            umma(tmem + (uint32_t)(32 * t), smem_desc(sm0 + L_::BT + s * L_::BT_SLAB + t * (128 * 128) + kk * 32),
-                 smem_desc(sm0 + L_::XWT + s * L_::X_SLAB + kk * 32), idesc, 1u);
-      umma_commit(bar_s);
-    }
-    // ---- y = exp(cum_i) D1 + D2 + D x for row i = 32 quarter + lane, 16 columns p ----
+    asm volatile("bar.sync 2, %0;" ::"n"(THREADS) : "memory");       // hands the chunk to the issuing thread
+    // ---- y = exp(cum_i) D1 + D2 + D x for row i = 32 quarter + lane (= mi), columns [16 mhalf, 16 mhalf + 16) ----
     wait(bar_y, ph, 14);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (tid == 0 && c + 1 < c1) fetch_c(c + 1);        // C's buffer is free again
     {
       uint32_t d1[16], d2[16];
       __syncwarp();
       tmem_ld16(t_d1, d1);
       tmem_ld16(t_d2, d2);
-      const int i = 32 * quarter + lane, pc = 16 * (warp >> 2);
-      if (i < L) {
-        const float e = es[i];
-        const uint4* xs = reinterpret_cast<const uint4*>(Xg + (size_t)(t0 + i) * Cd + pc);
-        const uint4 xa = __ldg(xs), xb = __ldg(xs + 1);
-        const uint32_t x8[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+      if (mi < L) {
+        const float e = es[mi];
+        const uint32_t x8[8] = {xv[0].x, xv[0].y, xv[0].z, xv[0].w, xv[1].x, xv[1].y, xv[1].z, xv[1].w};
         float out[16];
 #pragma unroll
-        for (int k = 0; k < 8; k++) {
-          const float2 x2 = unpack_bf16(x8[k]);
-          out[2 * k] = fmaf(e, __uint_as_float(d1[2 * k]), __uint_as_float(d2[2 * k])) + Dh * x2.x;
-          out[2 * k + 1] = fmaf(e, __uint_as_float(d1[2 * k + 1]), __uint_as_float(d2[2 * k + 1])) + Dh * x2.y;
+        for (int q = 0; q < 8; q++) {
+          const float2 x2 = unpack_bf16(x8[q]);
+          out[2 * q] = fmaf(e, __uint_as_float(d1[2 * q]), __uint_as_float(d2[2 * q])) + Dh * x2.x;
+          out[2 * q + 1] = fmaf(e, __uint_as_float(d1[2 * q + 1]), __uint_as_float(d2[2 * q + 1])) + Dh * x2.y;
         }
-        float4* yr = reinterpret_cast<float4*>(y + (size_t)(t0 + i) * Di + (size_t)h * P + p0 + pc);
+        float4* yr = reinterpret_cast<float4*>(y + (size_t)(t0 + mi) * Di + (size_t)h * P + p0 + 16 * mhalf);
 #pragma unroll
-        for (int k = 0; k < 4; k++) yr[k] = make_float4(out[4 * k], out[4 * k + 1], out[4 * k + 2], out[4 * k + 3]);
+        for (int q = 0; q < 4; q++) yr[q] = make_float4(out[4 * q], out[4 * q + 1], out[4 * q + 2], out[4 * q + 3]);
       }
     }
+    xv[0] = xv_next[0];
+    xv[1] = xv_next[1];
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   }
   // ---- the state after the sequence's last chunk goes to its slot ----
@@ -359,6 +391,7 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
 #pragma unroll
     for (int p = 0; p < 32; p++) slot[(size_t)p * N + n_mine] = __uint_as_float(sreg[p]);
   }
+  }   // workers
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0)
@@ -376,7 +409,7 @@ int launch(const CUtensorMap& mc, const CUtensorMap& mbt, const __nv_bfloat16* x
       return tlc_fail(-2, "ssm_scan(chunk walk, tcgen05): cannot reserve %d bytes of shared memory", TcSmem<NTILES>::TOTAL);
     configured = true;
   }
-  tlc_launch(ssd_walk_tc_kernel<NTILES>, dim3(B, Hs, P / PB), dim3(256), (size_t)TcSmem<NTILES>::TOTAL, stream, mc, mbt, xbc, dt,
+  tlc_launch(ssd_walk_tc_kernel<NTILES>, dim3(B, Hs, P / PB), dim3(THREADS), (size_t)TcSmem<NTILES>::TOTAL, stream, mc, mbt, xbc, dt,
              A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, Hs, P, G, Cd, tlc_error_words());
   TLC_CHECK_LAUNCH("ssm_scan(chunk walk, tcgen05)");
   return 0;
@@ -392,7 +425,7 @@ int tlc_ssd_tc_init() {
   return 0;
 }
 
-// B^T of every chunk, then the walk.  N is 128 or 256; bt: scratch of n_seg * G * N * 128 bfloat16.
+// The walk.  N is 128 or 256; bt [n_seg, G, N, 128]: B of every chunk transposed (ssd_cb_kernel writes it beside C B^T).
 int tlc_ssd_tc_run(const __nv_bfloat16* xbc, const float* dt, const float* A, const float* Dskip, const __nv_bfloat16* cb,
                    __nv_bfloat16* bt, float* state, const int* seg_start, const int* seq_seg_start, const int* slots,
                    const int* start_pos, float* y, int B, int n_seg, int T, int Hs, int P, int N, int G, int Cd,
@@ -402,8 +435,6 @@ int tlc_ssd_tc_run(const __nv_bfloat16* xbc, const float* dt, const float* A, co
   CUtensorMap mc, mbt;
   if (int rc = tlc_tensor_map_bf16(xbc, T, Cd, Cd, 64, Q, &mc)) return rc;
   if (int rc = tlc_tensor_map_bf16(bt, (long long)n_seg * G * N, Q, Q, 64, N, &mbt)) return rc;
-  tlc_launch(ssd_bt_kernel, dim3(n_seg, G, N / 64), dim3(256), 0, stream, xbc, seg_start, bt, Hs * P, N, G, Cd);
-  TLC_CHECK_LAUNCH("ssm_scan(B^T)");
   if (N == 128)
     return launch<1>(mc, mbt, xbc, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);
   return launch<2>(mc, mbt, xbc, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);

@@ -26,12 +26,14 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 // Bounded wait: false (and the error code recorded) if the phase does not complete in time.
 // `err` points at two words: [0] in device memory (what kernels read), [1] the address of a
 // host-mapped word that is written on failure only, so that the host can look without a copy.
-// [2] how many cycles a wait may spin (tlc_wait_limit_cycles sets it; read on the slow path only).
+// [2] how many cycles a wait may spin (tlc_wait_limit_cycles sets it).  A kernel reads the limit once, when it
+// starts (mbar_wait_limit), and hands it to every wait: a load from global memory inside the wait would cost
+// more than most waits last.
 struct ErrWords { int flag; int* host; long long limit; };
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, ErrWords* err, int code) {
+__device__ __forceinline__ long long mbar_wait_limit(const ErrWords* err) { return *(const volatile long long*)&err->limit; }
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, ErrWords* err, int code, long long limit) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
-  const long long limit = *(volatile long long*)&err->limit;
   while (!mbar_try(bar, parity)) {
     if (clock64() - t0 > limit) {
       atomicExch(&err->flag, code);
