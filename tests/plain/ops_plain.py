@@ -178,7 +178,7 @@ def ssm_scan(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, Hs, P, 
         state[slot] = S.to(state.dtype)
 
 
-def argmax(logits, out):
+def argmax(logits, out, work=None):
     out.copy_(torch.argmax(logits, dim=1).to(torch.int32))
 
 

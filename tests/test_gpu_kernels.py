@@ -572,6 +572,17 @@ def test_argmax_takes_the_first_maximum():
     logits[2, 17] = logits[2, 900] = 50.0
     logits[4, 999] = 60.0
     cmp("argmax", [logits, torch.empty(6, dtype=torch.int32)], [1], tol_of=0.0)
+    # a row spread over blocks of 2,048 values: ties across blocks, negative rows, a vocabulary that is no multiple
+    # of the slice; the workspace is zero again afterwards, so a second launch on it works
+    big = rnd(g, 5, 70001)
+    big[0, 5] = big[0, 69999] = 90.0          # equal maxima in the first and the last slice: the first wins
+    big[1] = -big[1].abs() - 1.0
+    big[1, 4097] = -0.5
+    big[3, 70000] = 95.0
+    work = ops.new_argmax_work(5, "cuda")
+    for _ in range(2):
+        cmp("argmax", [big, torch.empty(5, dtype=torch.int32), work], [1], tol_of=0.0)
+        assert int(work.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("params", [

@@ -107,9 +107,44 @@ __global__ void __launch_bounds__(SAMP_THREADS) argmax_kernel(const float* __res
   if (threadIdx.x == 0) out[blockIdx.x] = r;
 }
 
-extern "C" int tlc_argmax(const float* logits, int R, int V, int* out, cudaStream_t stream) {
+// A row spread over several blocks (a decode step has a few rows of a large vocabulary: one block a row would
+// leave the GPU to a handful of SMs).  Each block finds the first maximum of its slice and folds it into the
+// row's 64-bit key by atomicMax: the value mapped to an unsigned number of the same order in the high half,
+// ~index in the low half, so that the larger value wins and, among equal values, the smaller index.  The block
+// that arrives last writes the row's result and sets key and counter back to zero.
+// work: R keys (64-bit) followed by R counters (32-bit), all zero between launches.
+constexpr int ARGMAX_SLICE = 2048;
+__global__ void __launch_bounds__(SAMP_THREADS)
+argmax_split_kernel(const float* __restrict__ logits, int V, int* __restrict__ out, unsigned long long* __restrict__ keys,
+                    unsigned* __restrict__ counters) {
+  tlc_pdl(logits, out, keys, counters);
+  __shared__ float red[33];
+  __shared__ int redi[33];
+  const int r = blockIdx.x, v0 = blockIdx.y * ARGMAX_SLICE, n = min(ARGMAX_SLICE, V - v0);
+  const float* row = logits + (size_t)r * V + v0;
+  const int bi = block_argmax(row, n, red, redi);
+  if (threadIdx.x == 0) {
+    const unsigned u = __float_as_uint(row[bi]);
+    const unsigned ordered = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    atomicMax(keys + r, ((unsigned long long)ordered << 32) | (unsigned long long)(0xffffffffu - (unsigned)(v0 + bi)));
+    __threadfence();
+    if (atomicInc(counters + r, gridDim.y - 1) == gridDim.y - 1) {
+      __threadfence();
+      const unsigned long long best = atomicExch(keys + r, 0ull);
+      out[r] = (int)(0xffffffffu - (unsigned)(best & 0xffffffffull));
+    }
+  }
+}
+
+extern "C" int tlc_argmax(const float* logits, int R, int V, int* out, void* work, cudaStream_t stream) {
   if (R == 0) return 0;
-  tlc_launch(argmax_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, logits, V, out);
+  const int slices = (V + ARGMAX_SLICE - 1) / ARGMAX_SLICE;
+  if (work != nullptr && slices > 1 && slices <= 65535 && ((uintptr_t)work % 8) == 0) {
+    unsigned long long* keys = (unsigned long long*)work;
+    tlc_launch(argmax_split_kernel, dim3(R, slices), dim3(SAMP_THREADS), 0, stream, logits, V, out, keys, (unsigned*)(keys + R));
+  } else {
+    tlc_launch(argmax_kernel, dim3(R), dim3(SAMP_THREADS), 0, stream, logits, V, out);
+  }
   TLC_CHECK_LAUNCH("argmax");
   return 0;
 }

@@ -178,8 +178,10 @@ int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A, const flo
                      int N, int G, int Cd, cudaStream_t stream);
 
 /* ---- sampling (sampling.cu) ------------------------------------------------------------------------ */
-/* out[r] = first index of the maximum of logits[r]. */
-int tlc_argmax(const float* logits, int R, int V, int* out, cudaStream_t stream);
+/* out[r] = first index of the maximum of logits[r].  work: NULL (one block a row), or 12 * R bytes, 8-byte
+ * aligned and zero (R 64-bit keys, R counters), which every launch leaves zero: a row is then spread over
+ * blocks of 2,048 values.  Launches that share `work` must not overlap on the GPU. */
+int tlc_argmax(const float* logits, int R, int V, int* out, void* work, cudaStream_t stream);
 /* Penalties over history [R, n_history] (-1 = empty), temperature, top-k, min-p, top-p, then one draw per
  * row from uniforms [R]; work: R*V floats of scratch. */
 int tlc_sample(const float* logits, float* work, const int* history, const float* uniforms, int R, int V,

@@ -49,6 +49,7 @@ class DecodeGraph:
         self.work = torch.empty(B * model.vocab, dtype=torch.float32, device=dev) \
             if not (params.is_greedy and not params.has_penalties) else None
         self.out = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.argmax_work = ops.new_argmax_work(B, dev) if dev.type == "cuda" else None
         self.out_host = torch.zeros(B, dtype=torch.int32).pin_memory()
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -58,7 +59,7 @@ class DecodeGraph:
         p = self.params
         self.logits = self.model.forward(self.info, self.cache, self.want)
         if p.is_greedy and not p.has_penalties:
-            ops.argmax(self.logits, self.out)
+            ops.argmax(self.logits, self.out, self.argmax_work)
         else:
             ops.sample(self.logits, self.work, self.history, self.uniforms, p.temperature, p.top_k, p.top_p, p.min_p,
                        p.repeat_penalty, p.frequency_penalty, p.presence_penalty, self.out)

@@ -77,7 +77,7 @@ _SIGNATURES = {
     "tlc_ssd_scratch_floats": (_ll, [_i, _i, _i, _i, _i, _i]),
     "tlc_ssm_scan_ssd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
                               _vp]),
-    "tlc_argmax": (_i, [_vp, _i, _i, _vp, _vp]),
+    "tlc_argmax": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "tlc_sample": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp]),
     "tlc_attention_decode_no_alloc": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
                                            _vp]),
@@ -575,13 +575,22 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch
 
 
 # ---- sampling -------------------------------------------------------------------------------------
-def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
-    """out[r] = first index of the maximum of logits[r]."""
-    _gpu(logits, out)
+def new_argmax_work(rows: int, device) -> torch.Tensor:
+    """Zeroed workspace for argmax over `rows` rows (every launch leaves it zero); its owner's launches must not
+    overlap on the GPU.  Allocate it outside any stream capture."""
+    return torch.zeros(2 * max(1, int(rows)), dtype=torch.int64, device=device)
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, work: Optional[torch.Tensor] = None) -> None:
+    """out[r] = first index of the maximum of logits[r].  With `work` (new_argmax_work) a row is spread over
+    many blocks; without, one block takes a row."""
+    _gpu(logits, out, work)
     _i32(out, "argmax out")
     if logits.dtype != torch.float32 or not logits.is_contiguous():
         raise KernelError("argmax: logits must be contiguous float32")
-    _call("tlc_argmax", logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(), _stream())
+    if work is not None and (work.dtype != torch.int64 or not work.is_contiguous() or work.numel() < 2 * logits.shape[0]):
+        raise KernelError("argmax: work must be a contiguous int64 tensor of at least 2 values per row")
+    _call("tlc_argmax", logits.data_ptr(), logits.shape[0], logits.shape[1], out.data_ptr(), _p(work), _stream())
 
 
 def sample(logits: torch.Tensor, work: torch.Tensor, history: Optional[torch.Tensor], uniforms: torch.Tensor,
