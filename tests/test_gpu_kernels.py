@@ -273,6 +273,33 @@ def test_attention_of_prompts_on_tensor_cores(H, KV, hd, window):
     cmp("attention", args, [7], tol_of=TOL[torch.bfloat16] * 2.5)
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 128, 0), (6, 3, 64, 0), (4, 4, 128, 100), (2, 1, 64, 17), (3, 1, 128, 0)])
+def test_attention_of_prompts_on_tcgen05(H, KV, hd, window, mode):
+    """The tcgen05 kernel (mode 0) and the mma.sync one (mode 1) on the same step: prompts that cross 128-row tiles,
+    one that continues at position 130, single rows, a window.  One early key and one late key are scaled up: the
+    late one makes a row's maximum jump by far more than 2^8 in a late key tile, which is where the output
+    accumulator in tensor memory is rescaled."""
+    g = gen(33)
+    starts, lens = [0, 130, 63, 5, 0], [333, 200, 2, 129, 1]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    totals = [s + n for s, n in zip(starts, lens)]
+    slots, table, k_pages, v_pages = _paged_setup(g, 5, totals, KV, hd, torch.bfloat16, n_slots=7)
+    T = sum(lens)
+    q = rnd(g, T, H * hd, dtype=torch.bfloat16)
+    k_pages[int(table[int(slots[0]), 0]), :, 5, :] *= 5.0        # position 5: stands out from the first tile on
+    k_pages[int(table[int(slots[0]), 3]), :, 10, :] *= 12.0      # position 202: a jump in the fourth key tile
+    args = [q, k_pages, v_pages, table, pos, row_seq, slots, torch.empty(T, H * hd, dtype=torch.bfloat16), H, KV, hd,
+            1.0 / math.sqrt(hd), window, 0, cu, start_pos, max(totals)]
+    ops.prompt_attention_override(mode)
+    try:
+        cmp("attention", args, [7], tol_of=TOL[torch.bfloat16] * 2.5)
+        torch.cuda.synchronize()
+        ops.check_errors()
+    finally:
+        ops.prompt_attention_override(0)
+
+
 @pytest.mark.parametrize("H,KV,hd,window", [(4, 2, 128, 0), (2, 1, 64, 0), (4, 4, 64, 700)])
 def test_attention_of_long_prompts_in_pieces(H, KV, hd, window):
     """Key ranges of more than 8 pages are cut into pieces that run side by side and are merged: a prompt of

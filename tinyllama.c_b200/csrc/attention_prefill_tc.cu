@@ -1,0 +1,416 @@
+// Attention for the prompts of a step on the 5th-generation tensor cores (sm_100a).
+//
+// Same math as the reference's op_attn (cpu_op.c:1010-1062): causal grouped-query attention, scale
+// 1/sqrt(head_dim), max-subtracted softmax, optional window.  A block takes 128 consecutive new rows of one
+// sequence and one query head and walks the sequence's key tiles (a page of 64 keys each) up to the diagonal:
+//   * Q [128, hd] is loaded once by TMA; K tiles [64 keys, hd] come by TMA straight from the cache pages;
+//     V tiles come transposed, [hd, 64 keys], from a scratch that attention_vt_kernel fills first (a page of V
+//     is [keys, hd]; tcgen05.mma wants K, here the keys, along the rows of shared memory);
+//   * one thread of a ninth warp issues S = Q K^T (M 128, N 64, K hd) into one of two score buffers in tensor
+//     memory and O += P V (M 128, N hd, K 64) into the output accumulator, also in tensor memory;
+//   * eight worker warps read a score tile back (tcgen05.ld; a thread owns half a row), scale, mask, take the
+//     row's maximum (the two halves meet in shared memory), write P = 2^(s - m) in bfloat16 into shared memory
+//     in the layout tcgen05.mma reads, and keep their share of the row's sum;
+//   * the running maximum a row's numerators refer to moves only when the true maximum has grown by more than
+//     2^8: the output accumulator is then read back, scaled and stored again (tcgen05.ld / st); P stays below
+//     2^8, far inside bfloat16's range, and the sum is 32-bit.
+// Sequences of unequal length are packed back to back; a block finds its sequence from cu_seqlens.  Every wait
+// on an mbarrier is bounded (codes 21-27 of the error word); after one that ran out the block goes on without
+// waiting, frees its tensor memory and returns, and the host raises.
+#include "common.cuh"
+#include "mbarrier.cuh"
+#include "tcgen05.cuh"
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;                  // query rows per block
+constexpr int BN = 64;                   // keys per tile = one page
+static_assert(BN == TLC_PAGE, "a key tile is one page");
+constexpr int KS = 3, VS = 3;            // stages of the K and V rings
+constexpr int WORKERS = 256, THREADS = WORKERS + 32;
+constexpr float TAU = 8.0f;              // how far (in powers of two) a row's maximum may run ahead of its reference
+
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float ex2_quick(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// ---- V transposed per (sequence, page, kv head): vt[((b * P_max + page) * KV + g)][d][key], zero past the end ----
+// grid (B, KV, P_max), 256 threads: a 64 x hd tile through shared memory.
+__global__ void __launch_bounds__(256)
+attention_vt_kernel(const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
+                    const int* __restrict__ cu_seqlens, const int* __restrict__ slots, const int* __restrict__ start_pos,
+                    __nv_bfloat16* __restrict__ vt, int KV, int hd, int window, int p_max) {
+  tlc_pdl(v_pages, vt);
+  extern __shared__ unsigned short vt_tile[];            // [64][hd + 2]
+  const int b = blockIdx.x, g = blockIdx.y, page = blockIdx.z;
+  const int n_new = cu_seqlens[b + 1] - cu_seqlens[b];
+  const int len = start_pos[b] + n_new;                  // keys of the sequence after this step
+  const int first = window > 0 ? max(0, start_pos[b] + 1 - window) / BN : 0;
+  if (n_new <= 0 || page * BN >= len || page < first) return;
+  const int ld = hd + 2;
+  const unsigned short* src = reinterpret_cast<const unsigned short*>(v_pages) +
+                              (((size_t)block_table[(size_t)slots[b] * max_pages + page] * KV + g) * BN) * hd;
+  for (int idx = threadIdx.x; idx < BN * (hd / 2); idx += 256) {
+    const int k = idx / (hd / 2), d = (idx % (hd / 2)) * 2;
+    uint32_t v = 0;
+    if (page * BN + k < len) v = *reinterpret_cast<const uint32_t*>(src + (size_t)k * hd + d);
+    vt_tile[k * ld + d] = (unsigned short)(v & 0xffffu);
+    vt_tile[k * ld + d + 1] = (unsigned short)(v >> 16);
+  }
+  __syncthreads();
+  unsigned short* dst = reinterpret_cast<unsigned short*>(vt) + ((((size_t)b * p_max + page) * KV + g) * hd) * BN;
+  for (int idx = threadIdx.x; idx < hd * (BN / 2); idx += 256) {
+    const int d = idx / (BN / 2), k = (idx % (BN / 2)) * 2;
+    *reinterpret_cast<uint32_t*>(dst + (size_t)d * BN + k) = (uint32_t)vt_tile[k * ld + d] | ((uint32_t)vt_tile[(k + 1) * ld + d] << 16);
+  }
+}
+
+template <int HD>
+struct FaSmem {
+  static constexpr int Q_SLAB = BM * 128, Q = 0, Q_BYTES = (HD / 64) * Q_SLAB;
+  static constexpr int K_SLAB = BN * 128, K_STAGE = (HD / 64) * K_SLAB, K = Q + Q_BYTES;
+  static constexpr int V_STAGE = HD * 128, V = K + KS * K_STAGE;
+  static constexpr int P_BUF = BM * 128, P = V + VS * V_STAGE;
+  static constexpr int X = P + 2 * P_BUF;                 // [2][2][128] floats: the halves' maxima (and sums at the end)
+  static constexpr int BARS = X + 2 * 2 * BM * 4;         // mbarriers, tmem slot, dead flag
+  static constexpr int N_BARS = 1 + 2 * KS + 2 * VS + 8;
+  static constexpr int TABLE = BARS + N_BARS * 8 + 16;    // the block's page indices
+  static int total(int max_tiles) { return TABLE + max_tiles * 4 + 1024; }
+};
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_vt, const int* __restrict__ block_table, int max_pages,
+                            const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
+                            const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int H, int KV,
+                            float scale_log2, int window, int p_max, int out_ld, ErrWords* err) {
+  tlc_pdl(out);
+  using L_ = FaSmem<HD>;
+  constexpr int TCOLS = 256;                              // scores 0..63 and 64..127, output from 128
+  extern __shared__ uint8_t fa_raw[];
+  uint8_t* sm = (uint8_t*)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
+  float* xch = reinterpret_cast<float*>(sm + L_::X);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + L_::BARS);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L_::N_BARS);
+  volatile int* dead = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* pages = reinterpret_cast<int*>(sm + L_::TABLE);
+  __shared__ int s_seq, s_row0;
+  const uint32_t sm0 = smem_u32(sm);
+  const uint32_t bar_q = smem_u32(bars);
+  auto k_full = [&](int s) { return smem_u32(bars + 1 + s); };
+  auto k_empty = [&](int s) { return smem_u32(bars + 1 + KS + s); };
+  auto v_full = [&](int s) { return smem_u32(bars + 1 + 2 * KS + s); };
+  auto v_empty = [&](int s) { return smem_u32(bars + 1 + 2 * KS + VS + s); };
+  auto s_full = [&](int i) { return smem_u32(bars + 1 + 2 * KS + 2 * VS + i); };
+  auto s_free = [&](int i) { return smem_u32(bars + 1 + 2 * KS + 2 * VS + 2 + i); };
+  auto p_ready = [&](int i) { return smem_u32(bars + 1 + 2 * KS + 2 * VS + 4 + i); };
+  auto pv_done = [&](int i) { return smem_u32(bars + 1 + 2 * KS + 2 * VS + 6 + i); };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // which sequence, and which of its 128-row tiles, is this block's (the last tiles, with the most keys, first)
+  if (tid == 0) {
+    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, found = -1, row0 = 0;
+    for (int b = 0; b < n_seqs; b++) {
+      const int nt = (cu_seqlens[b + 1] - cu_seqlens[b] + BM - 1) / BM;
+      if (tile < nt) { found = b; row0 = tile * BM; break; }
+      tile -= nt;
+    }
+    s_seq = found;
+    s_row0 = row0;
+    for (int i = 0; i < L_::N_BARS; i++) {
+      const uint32_t bar = bar_q + 8 * i;               // the workers all arrive on s_free and p_ready, one agent on the rest
+      mbar_init(bar, (bar == s_free(0) || bar == s_free(1) || bar == p_ready(0) || bar == p_ready(1)) ? WORKERS : 1);
+    }
+    *dead = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  const int b = s_seq;
+  if (b < 0) return;
+  const int i0 = s_row0;
+  const int h = blockIdx.y, g = h / (H / KV);
+  const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
+  const int rows = min(BM, n_new - i0);
+  const int p0 = start_pos[b] + i0;                       // position of the block's first row
+  const int tile_hi = (p0 + rows - 1) / BN;
+  const int tile_lo = window > 0 ? max(0, p0 + 1 - window) / BN : 0;
+  const int n = tile_hi - tile_lo + 1;                    // key tiles of this block
+  const long long wait_limit = mbar_wait_limit(err);
+  for (int i = tid; i < n; i += THREADS) pages[i] = block_table[(size_t)slots[b] * max_pages + tile_lo + i];
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TCOLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_slot;
+  auto wait = [&](uint32_t bar, uint32_t parity, int code) {
+    if (*dead) return;
+    if (!mbar_wait(bar, parity, err, code, wait_limit)) *dead = 1;
+  };
+
+  if (warp == WORKERS / 32) {
+    // ---- the issuing warp: its first lane starts copies and products ----
+    if (lane == 0) {
+      auto load_k = [&](int t) {
+        const int s = t % KS;
+        mbar_expect_tx(k_full(s), L_::K_STAGE);
+        for (int c = 0; c < HD / 64; c++)
+          tma_load_2d(sm0 + L_::K + s * L_::K_STAGE + c * L_::K_SLAB, &map_k, k_full(s), 64 * c, (pages[t] * KV + g) * BN);
+      };
+      auto load_v = [&](int t) {
+        const int s = t % VS;
+        mbar_expect_tx(v_full(s), L_::V_STAGE);
+        tma_load_2d(sm0 + L_::V + s * L_::V_STAGE, &map_vt, v_full(s), 0, (((b * p_max) + tile_lo + t) * KV + g) * HD);
+      };
+      constexpr uint32_t idesc_s = instr_desc(BM, BN), idesc_o = instr_desc(BM, HD);
+      auto issue_s = [&](int t) {
+        const uint32_t d = tmem + (uint32_t)((t & 1) * BN);
+        const uint32_t kb = sm0 + L_::K + (t % KS) * L_::K_STAGE;
+#pragma unroll
+        for (int c = 0; c < HD / 64; c++)
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++)
+            umma(d, smem_desc(sm0 + L_::Q + c * L_::Q_SLAB + kk * 32), smem_desc(kb + c * L_::K_SLAB + kk * 32), idesc_s,
+                 (c > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(s_full(t & 1));
+        umma_commit(k_empty(t % KS));
+      };
+      mbar_expect_tx(bar_q, L_::Q_BYTES);
+      for (int c = 0; c < HD / 64; c++) tma_load_2d(sm0 + L_::Q + c * L_::Q_SLAB, &map_q, bar_q, h * HD + 64 * c, t0 + i0);
+      for (int t = 0; t < min(n, KS); t++) load_k(t);
+      for (int t = 0; t < min(n, VS); t++) load_v(t);
+      wait(bar_q, 0, 21);
+      wait(k_full(0), 0, 22);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      issue_s(0);
+      for (int j = 0; j < n; j++) {
+        if (j + 1 < n) {
+          const int t = j + 1;
+          wait(k_full(t % KS), (uint32_t)((t / KS) & 1), 22);
+          if (t >= 2) wait(s_free(t & 1), (uint32_t)(((t - 2) >> 1) & 1), 23);     // the workers have read scores t - 2
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(t);
+        }
+        wait(p_ready(j & 1), (uint32_t)((j >> 1) & 1), 24);                        // P of tile j is in shared memory
+        wait(v_full(j % VS), (uint32_t)((j / VS) & 1), 25);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        {
+          const uint32_t pb = sm0 + L_::P + (j & 1) * L_::P_BUF, vb = sm0 + L_::V + (j % VS) * L_::V_STAGE;
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++)
+            umma(tmem + 128u, smem_desc(pb + kk * 32), smem_desc(vb + kk * 32), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(pv_done(j & 1));
+          umma_commit(v_empty(j % VS));
+        }
+        if (j + KS < n) {                                   // K's stage of tile j is free once S(j) is done
+          wait(k_empty(j % KS), (uint32_t)((j / KS) & 1), 26);
+          load_k(j + KS);
+        }
+        if (j >= 1 && j - 1 + VS < n) {                     // V's stage of tile j - 1 is free once P V (j - 1) is done
+          wait(v_empty((j - 1) % VS), (uint32_t)(((j - 1) / VS) & 1), 27);
+          load_v(j - 1 + VS);
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---- the workers: thread (quarter, lane) owns row r of the tile; half 0 the first 32 keys of a key tile
+    // and the first hd/2 output columns, half 1 the rest ----
+    const int quarter = warp & 3, half = warp >> 2, r = 32 * quarter + lane;
+    const uint32_t lanes = (uint32_t)(quarter * 32) << 16;
+    const int pr = p0 + r;                                // this row's position
+    float m_used = -INFINITY, l = 0.f;
+    for (int j = 0; j < n; j++) {
+      wait(s_full(j & 1), (uint32_t)((j >> 1) & 1), 28);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      uint32_t sr[32];
+      __syncwarp();
+      tmem_ld32(tmem + lanes + (uint32_t)((j & 1) * BN + 32 * half), sr);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(s_free(j & 1));
+      float s2[32];
+      const int kbase = (tile_lo + j) * BN + 32 * half;
+      const bool need_mask = window > 0 || (tile_lo + j) * BN + BN - 1 > p0;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 32; c++) {
+        float v = __uint_as_float(sr[c]) * scale_log2;
+        if (need_mask) {
+          const int kp = kbase + c;
+          if (!(kp <= pr && (window <= 0 || kp > pr - window))) v = -INFINITY;
+        }
+        s2[c] = v;
+        mx = fmaxf(mx, v);
+      }
+      float* xm = xch + (j & 1) * 2 * BM;
+      xm[half * BM + r] = mx;
+      workers_sync();
+      mx = fmaxf(mx, xm[(half ^ 1) * BM + r]);
+      // the reference maximum moves only when the true one has run ahead of it by more than 2^TAU
+      const bool grow = mx > m_used + TAU || (m_used == -INFINITY && mx > -INFINITY);
+      float factor = 1.f;
+      if (grow) {
+        factor = m_used == -INFINITY ? 0.f : ex2_quick(m_used - mx);
+        m_used = mx;
+        l *= factor;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        wait(pv_done((j - 1) & 1), (uint32_t)(((j - 1) >> 1) & 1), 29);           // every product into O so far is done
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        __syncwarp();
+#pragma unroll
+        for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+          uint32_t o[32];
+          const uint32_t at = tmem + lanes + 128u + (uint32_t)(half * (HD / 2) + c0);
+          tmem_ld32(at, o);
+#pragma unroll
+          for (int c = 0; c < 32; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+          tmem_st32(at, o);
+        }
+      }
+      const float m_ref = m_used == -INFINITY ? 0.f : m_used;
+      float sum = 0.f;
+      uint32_t pk[16];
+#pragma unroll
+      for (int c = 0; c < 16; c++) {
+        const float a = ex2_quick(s2[2 * c] - m_ref), bq = ex2_quick(s2[2 * c + 1] - m_ref);
+        sum += a + bq;
+        pk[c] = pack_bf16(a, bq);
+      }
+      l += sum;
+      if (j >= 2) wait(pv_done(j & 1), (uint32_t)(((j - 2) >> 1) & 1), 29);        // P's buffer of tile j - 2 is free
+      uint8_t* prow = sm + L_::P + (j & 1) * L_::P_BUF + r * 128;
+#pragma unroll
+      for (int q = 0; q < 4; q++)
+        *reinterpret_cast<uint4*>(prow + (((4 * half + q) ^ (r & 7)) << 4)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(p_ready(j & 1));
+    }
+    // ---- the row's sum (both halves), the output ----
+    wait(pv_done((n - 1) & 1), (uint32_t)(((n - 1) >> 1) & 1), 29);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    float* xl = xch + (n & 1) * 2 * BM;
+    xl[half * BM + r] = l;
+    workers_sync();
+    const float inv = 1.0f / (l + xl[(half ^ 1) * BM + r]);
+    __syncwarp();
+#pragma unroll
+    for (int c0 = 0; c0 < HD / 2; c0 += 32) {
+      uint32_t o[32];
+      tmem_ld32(tmem + lanes + 128u + (uint32_t)(half * (HD / 2) + c0), o);
+      if (r < rows) {
+        uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(t0 + i0 + r) * out_ld + (size_t)h * HD + half * (HD / 2) + c0);
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+          dst[q] = make_uint4(pack_bf16(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv),
+                              pack_bf16(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv),
+                              pack_bf16(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv),
+                              pack_bf16(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv));
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TCOLS) : "memory");
+}
+
+// tensor maps of the cache pages, which stay where they are for the cache's lifetime
+struct MapKey {
+  const void* p; long long rows; int cols;
+  bool operator==(const MapKey& o) const { return p == o.p && rows == o.rows && cols == o.cols; }
+};
+struct MapHash { size_t operator()(const MapKey& k) const { return (size_t)k.p * 1000003u ^ (size_t)k.rows * 31u ^ (size_t)k.cols; } };
+std::unordered_map<MapKey, CUtensorMap, MapHash> g_page_maps;
+std::mutex g_page_mu;
+
+int page_map(const void* pages, long long rows, int hd, CUtensorMap* out) {
+  MapKey key{pages, rows, hd};
+  std::lock_guard<std::mutex> lk(g_page_mu);
+  auto it = g_page_maps.find(key);
+  if (it != g_page_maps.end()) { *out = it->second; return 0; }
+  CUtensorMap m;
+  if (int rc = tlc_tensor_map_bf16(pages, rows, hd, hd, 64, BN, &m)) return rc;
+  if (g_page_maps.size() > 1024) g_page_maps.clear();
+  g_page_maps[key] = m;
+  *out = m;
+  return 0;
+}
+
+template <int HD>
+int run(const __nv_bfloat16* q, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, long long n_page_rows,
+        const int* block_table, int max_pages, const int* cu_seqlens, const int* slots, const int* start_pos,
+        __nv_bfloat16* out, __nv_bfloat16* vt, int n_seqs, int n_tiles_bound, int H, int KV, float scale, int window,
+        int p_max, int T, int out_ld, cudaStream_t stream) {
+  static bool configured = false;
+  const int smem = FaSmem<HD>::total(p_max);
+  TLC_REQUIRE(smem <= 220 * 1024, "attention(prefill, tcgen05): %d key tiles need %d bytes of shared memory", p_max, smem);
+  if (!configured) {
+    if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_vt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
+      return tlc_fail(-2, "attention(prefill, tcgen05): cannot reserve shared memory");
+    configured = true;
+  }
+  CUtensorMap mq, mk, mvt;
+  if (int rc = tlc_tensor_map_bf16(q, T, (long long)H * HD, (long long)H * HD, 64, BM, &mq)) return rc;
+  if (int rc = page_map(k_pages, n_page_rows, HD, &mk)) return rc;
+  if (int rc = tlc_tensor_map_bf16(vt, (long long)n_seqs * p_max * KV * HD, BN, BN, 64, HD, &mvt)) return rc;
+  tlc_launch(attention_vt_kernel, dim3(n_seqs, KV, p_max), dim3(256), (size_t)BN * (HD + 2) * 2, stream, v_pages, block_table,
+             max_pages, cu_seqlens, slots, start_pos, vt, KV, HD, window, p_max);
+  TLC_CHECK_LAUNCH("attention(prefill, transposed values)");
+  tlc_launch(attention_prefill_tc_kernel<HD>, dim3(n_tiles_bound, H), dim3(THREADS), (size_t)smem, stream, mq, mk, mvt,
+             block_table, max_pages, cu_seqlens, slots, start_pos, out, n_seqs, H, KV, scale * 1.4426950408889634f, window, p_max,
+             out_ld, tlc_error_words());
+  TLC_CHECK_LAUNCH("attention(prefill, tcgen05)");
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int tlc_attention_prefill_tc_ok(int dtype, int hd, int H, int KV) {
+  return dtype == TLC_BF16 && (hd == 64 || hd == 128) && KV > 0 && H % KV == 0 && H <= 65535 && KV <= 65535;
+}
+
+// bfloat16 elements of scratch for the transposed values of n_seqs sequences of at most max_keys keys
+extern "C" long long tlc_attention_prefill_tc_scratch(int n_seqs, int max_keys, int KV, int hd) {
+  return (long long)n_seqs * ((max_keys + BN - 1) / BN) * KV * hd * BN;
+}
+
+// n_tiles_bound: an upper bound of sum_b ceil(n_new_b / 128) (e.g. T / 128 + n_seqs); max_keys: keys of the longest
+// sequence after this step; n_pages: pages of the cache (k_pages and v_pages are [n_pages, KV, 64, hd]); vt: scratch of
+// tlc_attention_prefill_tc_scratch elements.
+extern "C" int tlc_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
+                                        const int* block_table, int max_pages, const int* cu_seqlens, const int* slots,
+                                        const int* start_pos, void* out, void* vt, int n_seqs, int n_tiles_bound, int H, int KV,
+                                        int hd, float scale, int window, int max_keys, int T, int out_ld, cudaStream_t stream) {
+  if (n_seqs == 0 || n_tiles_bound == 0 || T == 0) return 0;
+  if (out_ld <= 0) out_ld = H * hd;
+  TLC_REQUIRE(tlc_attention_prefill_tc_ok(TLC_BF16, hd, H, KV), "attention(prefill, tcgen05): %d heads, %d key/value heads of size %d are not built", H, KV, hd);
+  TLC_REQUIRE(out_ld % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)vt % 16) == 0 &&
+              ((uintptr_t)k_pages % 16) == 0, "attention(prefill, tcgen05): rows must start on 16-byte boundaries");
+  TLC_REQUIRE(tlc_error_words() != nullptr, "attention(prefill, tcgen05): the library is not set up (tlc_linear_init)");
+  const int p_max = (max_keys + BN - 1) / BN;
+  TLC_REQUIRE(p_max >= 1 && p_max <= 65535, "attention(prefill, tcgen05): %d keys", max_keys);
+  const long long rows = (long long)n_pages * KV * BN;
+  const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
+  if (hd == 64)
+    return run<64>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, (__nv_bfloat16*)vt,
+                   n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, stream);
+  return run<128>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, (__nv_bfloat16*)vt,
+                  n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, stream);
+}

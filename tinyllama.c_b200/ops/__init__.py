@@ -67,6 +67,10 @@ _SIGNATURES = {
     "tlc_attention_prefill_chunks": (_i, [_i, _i, _i, _vp]),
     "tlc_attention_prefill": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
                                    _vp, _i, _i, _vp]),
+    "tlc_attention_prefill_tc_ok": (_i, [_i, _i, _i, _i]),
+    "tlc_attention_prefill_tc_scratch": (_ll, [_i, _i, _i, _i]),
+    "tlc_attention_prefill_tc": (_i, [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i,
+                                      _i, _i, _vp]),
     "tlc_mamba_conv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i,
                             _i, _i, _i, _i, _i, _vp]),
     "tlc_ssm_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
@@ -344,6 +348,16 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale: Option
 
 # ---- attention -------------------------------------------------------------------------------
 DISABLE_TILED_ATTENTION = bool(int(os.environ.get("TLC_DISABLE_TILED_ATTENTION", "0")))
+# Prompt attention on tcgen05 (0) or the mma.sync kernel everywhere (1); TLC_PROMPT_ATTENTION sets the start value,
+# prompt_attention_override() changes it (tests run both).
+_prompt_attention = int(os.environ.get("TLC_PROMPT_ATTENTION", "0"))
+
+
+def prompt_attention_override(mode: int) -> None:
+    """0: prompts of a bfloat16 cache with heads of 64 or 128 take the tcgen05 attention kernel; 1: the mma.sync one."""
+    global _prompt_attention
+    _prompt_attention = int(mode)
+
 
 def rope_kv_store(qkv: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, k_pages: torch.Tensor,
                   v_pages: torch.Tensor, inv_freq: torch.Tensor, positions: torch.Tensor, row_seq: torch.Tensor,
@@ -393,8 +407,19 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               slots.data_ptr(), out.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), T, H, KV, hd, float(scale),
               int(window or 0), int(decode_max_keys), out_ld, _stream())
         return
-    if decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
-            and hd in (64, 128) and not DISABLE_TILED_ATTENTION:
+    tiled = decode_max_keys <= 0 and cu_seqlens is not None and start_pos is not None and q.dtype == torch.bfloat16 \
+        and hd in (64, 128) and not DISABLE_TILED_ATTENTION
+    if tiled and _prompt_attention == 0 and max_keys > 0 and out_ld % 8 == 0 \
+            and library().tlc_attention_prefill_tc_ok(BF16, hd, H, KV):
+        B = slots.numel()
+        lib = library()
+        vt = torch.empty(lib.tlc_attention_prefill_tc_scratch(B, int(max_keys), KV, hd), dtype=torch.bfloat16, device=q.device)
+        _call("tlc_attention_prefill_tc", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
+              block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(),
+              out.data_ptr(), vt.data_ptr(), B, T // 128 + B, H, KV, hd, float(scale), int(window or 0), int(max_keys), T,
+              out_ld, _stream())
+        return
+    if tiled:
         B = slots.numel()
         n_tiles = T // 64 + B
         chunk = ctypes.c_int(0)
