@@ -6,11 +6,14 @@
 //   * Q [128, hd] is loaded once by TMA; K tiles [64 keys, hd] come by TMA straight from the cache pages;
 //     V tiles come transposed, [hd, 64 keys], from a scratch that attention_vt_kernel fills first (a page of V
 //     is [keys, hd]; tcgen05.mma wants K, here the keys, along the rows of shared memory);
-//   * one thread of a ninth warp issues S = Q K^T (M 128, N 64, K hd) into one of two score buffers in tensor
-//     memory and O += P V (M 128, N hd, K 64) into the output accumulator, also in tensor memory;
-//   * eight worker warps read a score tile back (tcgen05.ld; a thread owns half a row), scale, mask, take the
-//     row's maximum (the two halves meet in shared memory), write P = 2^(s - m) in bfloat16 into shared memory
-//     in the layout tcgen05.mma reads, and keep their share of the row's sum;
+//   * three warps of one agent each, on three schedulers: one starts the copies, one issues S = Q K^T (M 128,
+//     N 64, K hd) into one of two score buffers in tensor memory, two tiles ahead of the workers, and one issues
+//     O += P V (M 128, N hd, K 64) into the output accumulator, also in tensor memory;
+//   * sixteen worker warps read a score tile back (tcgen05.ld; a thread owns a quarter of a row: the exponentials
+//     and the tensor-memory loads of one warp hide behind the other three of its scheduler), scale, mask, take the
+//     row's maximum (the quarters meet in shared memory), write P = 2^(s - m) in bfloat16 into shared memory in
+//     the layout tcgen05.mma reads, and keep their share of the row's sum; the scores of the next tile are
+//     fetched into registers before the exponentials of this one;
 //   * the running maximum a row's numerators refer to moves only when the true maximum has grown by more than
 //     2^8: the output accumulator is then read back, scaled and stored again (tcgen05.ld / st); P stays below
 //     2^8, far inside bfloat16's range, and the sum is 32-bit.
@@ -28,11 +31,14 @@ namespace {
 constexpr int BM = 128;                  // query rows per block
 constexpr int BN = 64;                   // keys per tile = one page
 static_assert(BN == TLC_PAGE, "a key tile is one page");
-constexpr int KS = 3, VS = 3;            // stages of the K and V rings
-constexpr int WORKERS = 256, THREADS = WORKERS + 32;
+constexpr int KS = 4, VS = 3;            // stages of the K and V rings
+constexpr int WORKERS = 512, THREADS = WORKERS + 96;
+constexpr int NCG = WORKERS / 128;       // column groups: threads that share a row
+constexpr int CW = BN / NCG;             // key columns of a thread in a tile
 constexpr float TAU = 8.0f;              // how far (in powers of two) a row's maximum may run ahead of its reference
 
-__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(WORKERS) : "memory"); }
+static_assert(CW == 16, "a thread takes 16 key columns of a tile");
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -80,8 +86,8 @@ struct FaSmem {
   static constexpr int K_SLAB = BN * 128, K_STAGE = (HD / 64) * K_SLAB, K = Q + Q_BYTES;
   static constexpr int V_STAGE = HD * 128, V = K + KS * K_STAGE;
   static constexpr int P_BUF = BM * 128, P = V + VS * V_STAGE;
-  static constexpr int X = P + 2 * P_BUF;                 // [2][2][128] floats: the halves' maxima (and sums at the end)
-  static constexpr int BARS = X + 2 * 2 * BM * 4;         // mbarriers, tmem slot, dead flag
+  static constexpr int X = P + 2 * P_BUF;                 // [2][NCG][128] floats: the column groups' maxima (and sums at the end)
+  static constexpr int BARS = X + 2 * NCG * BM * 4;       // mbarriers, tmem slot, dead flag
   static constexpr int N_BARS = 1 + 2 * KS + 2 * VS + 8;
   static constexpr int TABLE = BARS + N_BARS * 8 + 16;    // the block's page indices
   static int total(int max_tiles) { return TABLE + max_tiles * 4 + 1024; }
@@ -128,8 +134,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     s_seq = found;
     s_row0 = row0;
     for (int i = 0; i < L_::N_BARS; i++) {
-      const uint32_t bar = bar_q + 8 * i;               // the workers all arrive on s_free and p_ready, one agent on the rest
-      mbar_init(bar, (bar == s_free(0) || bar == s_free(1) || bar == p_ready(0) || bar == p_ready(1)) ? WORKERS : 1);
+      const uint32_t bar = bar_q + 8 * i;               // every worker warp arrives once on s_free and p_ready, one agent on the rest
+      mbar_init(bar, (bar == s_free(0) || bar == s_free(1) || bar == p_ready(0) || bar == p_ready(1)) ? WORKERS / 32 : 1);
     }
     *dead = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -162,104 +168,116 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (!mbar_wait(bar, parity, err, code, wait_limit)) *dead = 1;
   };
 
-  if (warp == WORKERS / 32) {
-    // ---- the issuing warp: its first lane starts copies and products ----
-    if (lane == 0) {
-      auto load_k = [&](int t) {
-        const int s = t % KS;
-        mbar_expect_tx(k_full(s), L_::K_STAGE);
-        for (int c = 0; c < HD / 64; c++)
-          tma_load_2d(sm0 + L_::K + s * L_::K_STAGE + c * L_::K_SLAB, &map_k, k_full(s), 64 * c, (pages[t] * KV + g) * BN);
-      };
-      auto load_v = [&](int t) {
-        const int s = t % VS;
-        mbar_expect_tx(v_full(s), L_::V_STAGE);
-        tma_load_2d(sm0 + L_::V + s * L_::V_STAGE, &map_vt, v_full(s), 0, (((b * p_max) + tile_lo + t) * KV + g) * HD);
-      };
-      constexpr uint32_t idesc_s = instr_desc(BM, BN), idesc_o = instr_desc(BM, HD);
-      auto issue_s = [&](int t) {
-        const uint32_t d = tmem + (uint32_t)((t & 1) * BN);
-        const uint32_t kb = sm0 + L_::K + (t % KS) * L_::K_STAGE;
-#pragma unroll
-        for (int c = 0; c < HD / 64; c++)
-#pragma unroll
-          for (int kk = 0; kk < 4; kk++)
-            umma(d, smem_desc(sm0 + L_::Q + c * L_::Q_SLAB + kk * 32), smem_desc(kb + c * L_::K_SLAB + kk * 32), idesc_s,
-                 (c > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(s_full(t & 1));
-        umma_commit(k_empty(t % KS));
-      };
+  if (warp >= WORKERS / 32) {
+    // ---- three warps of one agent each (their first lanes), on three schedulers: the copies, the products
+    // S = Q K^T, the products O += P V.  One thread for all three was the kernel's bound: its instructions
+    // share a scheduler's issue slots with four worker warps. ----
+    const int role = warp - WORKERS / 32;
+    constexpr uint32_t DESC_HI = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);      // see smem_desc
+    auto desc_lo = [](uint32_t addr) { return ((addr & 0x3FFFFu) >> 4) | (1u << 16); };
+    if (lane == 0 && role == 0) {
       mbar_expect_tx(bar_q, L_::Q_BYTES);
       for (int c = 0; c < HD / 64; c++) tma_load_2d(sm0 + L_::Q + c * L_::Q_SLAB, &map_q, bar_q, h * HD + 64 * c, t0 + i0);
-      for (int t = 0; t < min(n, KS); t++) load_k(t);
-      for (int t = 0; t < min(n, VS); t++) load_v(t);
-      wait(bar_q, 0, 21);
-      wait(k_full(0), 0, 22);
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      issue_s(0);
-      for (int j = 0; j < n; j++) {
-        if (j + 1 < n) {
-          const int t = j + 1;
-          wait(k_full(t % KS), (uint32_t)((t / KS) & 1), 22);
-          if (t >= 2) wait(s_free(t & 1), (uint32_t)(((t - 2) >> 1) & 1), 23);     // the workers have read scores t - 2
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_s(t);
-        }
-        wait(p_ready(j & 1), (uint32_t)((j >> 1) & 1), 24);                        // P of tile j is in shared memory
-        wait(v_full(j % VS), (uint32_t)((j / VS) & 1), 25);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (int t = 0; t < n; t++) {
         {
-          const uint32_t pb = sm0 + L_::P + (j & 1) * L_::P_BUF, vb = sm0 + L_::V + (j % VS) * L_::V_STAGE;
+          const int st = t % KS;
+          if (t >= KS) wait(k_empty(st), (uint32_t)(((t - KS) / KS) & 1), 26);       // S of tile t - KS is done
+          mbar_expect_tx(k_full(st), L_::K_STAGE);
+          for (int c = 0; c < HD / 64; c++)
+            tma_load_2d(sm0 + L_::K + st * L_::K_STAGE + c * L_::K_SLAB, &map_k, k_full(st), 64 * c, (pages[t] * KV + g) * BN);
+        }
+        {
+          const int st = t % VS;
+          if (t >= VS) wait(v_empty(st), (uint32_t)(((t - VS) / VS) & 1), 27);       // P V of tile t - VS is done
+          mbar_expect_tx(v_full(st), L_::V_STAGE);
+          tma_load_2d(sm0 + L_::V + st * L_::V_STAGE, &map_vt, v_full(st), 0, (((b * p_max) + tile_lo + t) * KV + g) * HD);
+        }
+      }
+    } else if (lane == 0 && role == 1) {
+      // the scores run two tiles ahead of the workers: both score buffers are in use from the start
+      constexpr uint32_t idesc_s = instr_desc(BM, BN);
+      const uint32_t q_lo = desc_lo(sm0 + L_::Q);
+      wait(bar_q, 0, 21);
+      for (int t = 0; t < n; t++) {
+        const int st = t % KS;
+        wait(k_full(st), (uint32_t)((t / KS) & 1), 22);
+        if (t >= 2) wait(s_free(t & 1), (uint32_t)(((t - 2) >> 1) & 1), 23);         // the workers hold scores t - 2 in registers
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d = tmem + (uint32_t)((t & 1) * BN);
+        const uint32_t k_lo = desc_lo(sm0 + L_::K + st * L_::K_STAGE);
+#pragma unroll
+        for (int c = 0; c < HD / 64; c++)
 #pragma unroll
           for (int kk = 0; kk < 4; kk++)
-            umma(tmem + 128u, smem_desc(pb + kk * 32), smem_desc(vb + kk * 32), idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(pv_done(j & 1));
-          umma_commit(v_empty(j % VS));
-        }
-        if (j + KS < n) {                                   // K's stage of tile j is free once S(j) is done
-          wait(k_empty(j % KS), (uint32_t)((j / KS) & 1), 26);
-          load_k(j + KS);
-        }
-        if (j >= 1 && j - 1 + VS < n) {                     // V's stage of tile j - 1 is free once P V (j - 1) is done
-          wait(v_empty((j - 1) % VS), (uint32_t)(((j - 1) / VS) & 1), 27);
-          load_v(j - 1 + VS);
-        }
+            umma_halves(d, q_lo + (uint32_t)((c * L_::Q_SLAB + kk * 32) >> 4), k_lo + (uint32_t)((c * L_::K_SLAB + kk * 32) >> 4),
+                        DESC_HI, idesc_s, (c > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(s_full(t & 1));
+        umma_commit(k_empty(st));
+      }
+    } else if (lane == 0 && role == 2) {
+      constexpr uint32_t idesc_o = instr_desc(BM, HD);
+      for (int j = 0; j < n; j++) {
+        const int st = j % VS;
+        wait(v_full(st), (uint32_t)((j / VS) & 1), 25);
+        wait(p_ready(j & 1), (uint32_t)((j >> 1) & 1), 24);                          // P of tile j is in shared memory
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t p_lo = desc_lo(sm0 + L_::P + (j & 1) * L_::P_BUF), v_lo = desc_lo(sm0 + L_::V + st * L_::V_STAGE);
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++)
+          umma_halves(tmem + 128u, p_lo + (uint32_t)(kk * 2), v_lo + (uint32_t)(kk * 2), DESC_HI, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(pv_done(j & 1));
+        umma_commit(v_empty(st));
       }
     }
     __syncwarp();
   } else {
-    // ---- the workers: thread (quarter, lane) owns row r of the tile; half 0 the first 32 keys of a key tile
-    // and the first hd/2 output columns, half 1 the rest ----
-    const int quarter = warp & 3, half = warp >> 2, r = 32 * quarter + lane;
+    // ---- the workers: thread (quarter, lane) of column group cg owns row r of the tile, 16 key columns of every key
+    // tile and hd / 4 output columns ----
+    const int quarter = warp & 3, cg = warp >> 2, r = 32 * quarter + lane;
     const uint32_t lanes = (uint32_t)(quarter * 32) << 16;
     const int pr = p0 + r;                                // this row's position
+    constexpr int OC = HD / NCG;                          // output columns of a thread: 32 or 16
     float m_used = -INFINITY, l = 0.f;
+    uint32_t sr[CW];
+    wait(s_full(0), 0u, 28);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncwarp();
+    tmem_ld16(tmem + lanes + (uint32_t)(CW * cg), sr);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive(s_free(0));
     for (int j = 0; j < n; j++) {
-      wait(s_full(j & 1), (uint32_t)((j >> 1) & 1), 28);
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      uint32_t sr[32];
-      __syncwarp();
-      tmem_ld32(tmem + lanes + (uint32_t)((j & 1) * BN + 32 * half), sr);
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(s_free(j & 1));
-      float s2[32];
-      const int kbase = (tile_lo + j) * BN + 32 * half;
+      float s2[CW];
+      const int kbase = (tile_lo + j) * BN + CW * cg;
       const bool need_mask = window > 0 || (tile_lo + j) * BN + BN - 1 > p0;
       float mx = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < 32; c++) {
-        float v = __uint_as_float(sr[c]) * scale_log2;
-        if (need_mask) {
+        for (int c = 0; c < CW; c++) {
           const int kp = kbase + c;
-          if (!(kp <= pr && (window <= 0 || kp > pr - window))) v = -INFINITY;
+          const float v = (kp <= pr && (window <= 0 || kp > pr - window)) ? __uint_as_float(sr[c]) * scale_log2 : -INFINITY;
+          s2[c] = v;
+          mx = fmaxf(mx, v);
         }
-        s2[c] = v;
-        mx = fmaxf(mx, v);
+      } else {
+#pragma unroll
+        for (int c = 0; c < CW; c++) {
+          s2[c] = __uint_as_float(sr[c]) * scale_log2;
+          mx = fmaxf(mx, s2[c]);
+        }
       }
-      float* xm = xch + (j & 1) * 2 * BM;
-      xm[half * BM + r] = mx;
+      float* xm = xch + (j & 1) * NCG * BM;
+      xm[cg * BM + r] = mx;
+      // the next tile's scores on their way into registers while this tile's exponentials run
+      if (j + 1 < n) {
+        wait(s_full((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1), 28);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        __syncwarp();
+        tmem_ld16_nowait(tmem + lanes + (uint32_t)(((j + 1) & 1) * BN + CW * cg), sr);
+      }
       workers_sync();
-      mx = fmaxf(mx, xm[(half ^ 1) * BM + r]);
+#pragma unroll
+      for (int o = 0; o < NCG; o++) mx = fmaxf(mx, xm[o * BM + r]);
       // the reference maximum moves only when the true one has run ahead of it by more than 2^TAU
       const bool grow = mx > m_used + TAU || (m_used == -INFINITY && mx > -INFINITY);
       float factor = 1.f;
@@ -272,21 +290,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         wait(pv_done((j - 1) & 1), (uint32_t)(((j - 1) >> 1) & 1), 29);           // every product into O so far is done
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         __syncwarp();
+        if (j + 1 < n) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");   // the scores in flight first
+        uint32_t o[OC];
+        const uint32_t at = tmem + lanes + 128u + (uint32_t)(cg * OC);
+        tmem_ldn(at, o);
 #pragma unroll
-        for (int c0 = 0; c0 < HD / 2; c0 += 32) {
-          uint32_t o[32];
-          const uint32_t at = tmem + lanes + 128u + (uint32_t)(half * (HD / 2) + c0);
-          tmem_ld32(at, o);
-#pragma unroll
-          for (int c = 0; c < 32; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
-          tmem_st32(at, o);
-        }
+        for (int c = 0; c < OC; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
+        tmem_stn(at, o);
       }
       const float m_ref = m_used == -INFINITY ? 0.f : m_used;
       float sum = 0.f;
-      uint32_t pk[16];
+      uint32_t pk[CW / 2];
 #pragma unroll
-      for (int c = 0; c < 16; c++) {
+      for (int c = 0; c < CW / 2; c++) {
         const float a = ex2_quick(s2[2 * c] - m_ref), bq = ex2_quick(s2[2 * c + 1] - m_ref);
         sum += a + bq;
         pk[c] = pack_bf16(a, bq);
@@ -295,28 +311,37 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (j >= 2) wait(pv_done(j & 1), (uint32_t)(((j - 2) >> 1) & 1), 29);        // P's buffer of tile j - 2 is free
       uint8_t* prow = sm + L_::P + (j & 1) * L_::P_BUF + r * 128;
 #pragma unroll
-      for (int q = 0; q < 4; q++)
-        *reinterpret_cast<uint4*>(prow + (((4 * half + q) ^ (r & 7)) << 4)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+      for (int q = 0; q < CW / 8; q++)
+        *reinterpret_cast<uint4*>(prow + ((((CW / 8) * cg + q) ^ (r & 7)) << 4)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      if (j + 1 < n) {
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");               // the next tile's scores have arrived
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(s_free((j + 1) & 1));
+      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(p_ready(j & 1));
+      __syncwarp();                                         // the warp's rows of P are written and fenced
+      if (lane == 0) mbar_arrive(p_ready(j & 1));
     }
-    // ---- the row's sum (both halves), the output ----
+    // ---- the row's sum (all column groups), the output ----
     wait(pv_done((n - 1) & 1), (uint32_t)(((n - 1) >> 1) & 1), 29);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    float* xl = xch + (n & 1) * 2 * BM;
-    xl[half * BM + r] = l;
+    float* xl = xch + (n & 1) * NCG * BM;
+    xl[cg * BM + r] = l;
     workers_sync();
-    const float inv = 1.0f / (l + xl[(half ^ 1) * BM + r]);
+    float l_all = 0.f;
+#pragma unroll
+    for (int o = 0; o < NCG; o++) l_all += xl[o * BM + r];
+    const float inv = 1.0f / l_all;
     __syncwarp();
-#pragma unroll
-    for (int c0 = 0; c0 < HD / 2; c0 += 32) {
-      uint32_t o[32];
-      tmem_ld32(tmem + lanes + 128u + (uint32_t)(half * (HD / 2) + c0), o);
+    {
+      uint32_t o[OC];
+      tmem_ldn(tmem + lanes + 128u + (uint32_t)(cg * OC), o);
       if (r < rows) {
-        uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(t0 + i0 + r) * out_ld + (size_t)h * HD + half * (HD / 2) + c0);
+        uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(t0 + i0 + r) * out_ld + (size_t)h * HD + cg * OC);
 #pragma unroll
-        for (int q = 0; q < 4; q++)
+        for (int q = 0; q < OC / 8; q++)
           dst[q] = make_uint4(pack_bf16(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv),
                               pack_bf16(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv),
                               pack_bf16(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv),
