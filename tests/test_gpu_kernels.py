@@ -181,6 +181,38 @@ def test_linear_with_the_k_steps_of_a_tile_shared_among_blocks(splits):
         ops.linear_split_override(0)
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 128, 64), (129, 257, 200), (2048, 384, 512), (100, 1000, 520), (256, 512, 4096),
+                                   (1000, 520, 264), (513, 776, 1096)])
+def test_linear_on_pairs_of_blocks(M, N, K):
+    """Tiles of 256 x 256 shared by two blocks (tcgen05.mma.cta_group::2), forced at sizes whose edges fall inside
+    a tile, inside one block's half of it, and between the two blocks; plain, into a 32-bit sum, with column
+    scales, and with the SwiGLU epilogue.  Twice each: the ring and the barriers' phases carry on across tiles."""
+    assert ops.linear_pairs() > 0, "this GPU runs no clusters of two blocks of the product"
+    g = gen(33)
+    a = rnd(g, M, K, dtype=torch.bfloat16)
+    w = rnd(g, N, K, dtype=torch.bfloat16, scale=1 / math.sqrt(K))
+    cs, cb = 1 + rnd(g, N, scale=0.3), rnd(g, N)
+    try:
+        ops.linear_pair_override(2)
+        for accumulate, scale, bias, o_dt in ((True, None, None, torch.float32), (False, cs, cb, torch.bfloat16),
+                                              (False, None, None, torch.bfloat16)):
+            out_cpu = rnd(g, M, N, dtype=o_dt)
+            ops_plain.linear(a, w, ref := out_cpu.clone(), scale, bias, accumulate)
+            for rep in range(2):
+                out = out_cpu.cuda()
+                ops.linear(a.cuda(), w.cuda(), out, None if scale is None else scale.cuda(),
+                           None if bias is None else bias.cuda(), accumulate)
+                torch.cuda.synchronize()
+                ops.check_errors()
+                err = (ref.double() - out.cpu().double()).abs().max().item()
+                assert err <= TOL[o_dt] * ref.double().abs().max().item(), f"{M}x{N}x{K}, run {rep}: {err}"
+        if N % 16 == 0:
+            cmp("linear_swiglu", [a, w, torch.empty(M, N // 2, dtype=torch.bfloat16), cs, cb], [2], tol_of=TOL[torch.bfloat16] * 2)
+            ops.check_errors()
+    finally:
+        ops.linear_pair_override(0)
+
+
 def _paged_setup(g, B, lens_total, KV, hd, dtype, n_slots=5, extra_pages=3):
     """Random slots and shuffled pages for sequences of the given total lengths."""
     pages_needed = [(n + 63) // 64 for n in lens_total]

@@ -36,10 +36,11 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool PAIR = false>
 struct Smem {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;        // weight rows a block stages: each block of a pair half of the tile's
+  static constexpr int B_BYTES = B_ROWS * BK * 2;
   static constexpr int TILES = STAGES * (A_BYTES + B_BYTES);
   static constexpr int STAGING = 4 * (32 * 33 + 2 * BN) * 4;   // per epilogue warp: a padded 32x32 float tile, the tile's column scales and biases
   static constexpr int N_BARS = 2 * STAGES + 4;            // full, empty per stage; accumulator full, empty x2
@@ -52,7 +53,12 @@ struct Smem {
 // one tile overlaps the products of the next.
 // With SWIGLU the weight rows come in groups of 16 = 8 gate rows followed by their 8 up rows;
 // the epilogue writes silu(gate) * up, half as many columns ([M, N/2], row stride ldo).
-template <typename TO, int BN, int STAGES, bool SWIGLU>
+// With PAIR two blocks (a cluster of two) share a tile of 256 rows x BN columns: each stages its 128 rows of the
+// activations and its BN / 2 rows of the weights, the block of rank 0 issues tcgen05.mma.cta_group::2 (M = 256)
+// over both blocks' shared memory, and each finds its 128 rows of the result in its own tensor memory.  A block
+// then reads (128 + BN / 2) x 64 operand values for 128 x BN x 64 products where a single block reads
+// (128 + BN) x 64: a third less traffic into and out of shared memory, which bounds the single-block tile.
+template <typename TO, int BN, int STAGES, bool SWIGLU, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
@@ -62,7 +68,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   // the wait on it.  The loader waits before its first activation tile, the epilogue warps before they touch
   // `out`; the issuer reads shared memory only.
   asm volatile("griddepcontrol.launch_dependents;");
-  using S = Smem<BN, STAGES>;
+  using S = Smem<BN, STAGES, PAIR>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* a_tiles = smem;
@@ -75,7 +81,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long wait_limit = mbar_wait_limit(err);
-  const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  constexpr int TM = PAIR ? 2 * BM : BM;               // rows of a tile
+  const uint32_t rank = PAIR ? cluster_rank() : 0u;    // which block of the pair
+  const int walker = PAIR ? (int)blockIdx.x >> 1 : (int)blockIdx.x;      // blocks, or pairs, walk the tiles
+  const int walkers = PAIR ? (int)gridDim.x >> 1 : (int)gridDim.x;
+  const int m_tiles = (M + TM - 1) / TM, n_tiles = (N + BN - 1) / BN;
   // splits > 1: a tile's K-steps are shared by `splits` blocks; each leaves its partial accumulator in `part`
   // [splits, M, N] and the last one to arrive (arrivals[tile * 4 + quarter], back at zero afterwards) adds
   // them in order and finishes the tile.  Tile index = split * (tiles of the output) + output tile.
@@ -86,17 +96,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    for (int s = 0; s < 2; s++) { mbar_init(acc_full0 + 8 * s, 1); mbar_init(acc_empty0 + 8 * s, 4); }
+    for (int s = 0; s < 2; s++) { mbar_init(acc_full0 + 8 * s, 1); mbar_init(acc_empty0 + 8 * s, PAIR ? 8 : 4); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) {   // the whole warp allocates two accumulators of BN columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (warp == 1) {   // the whole warp (of both blocks of a pair) allocates two accumulators of BN columns
+    if constexpr (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync();                  // the other block's mbarriers are initialised too
+  else __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
 
@@ -107,43 +124,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool waited = false;                             // on the previous kernel of the stream
       int3 pending_a[STAGES];                          // activation tiles (stage, k, m) held back until then
       int n_pending = 0;
-      const int my_tiles = (int)blockIdx.x < total_tiles ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+      const int my_tiles = walker < total_tiles ? (total_tiles - 1 - walker) / walkers + 1 : 0;
       const int first_run = my_tiles * (num_k - (splits - 1) * k_per);   // stage fills this block issues at least
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      // a pair's copies all count on the mbarriers of the block of rank 0, whose issuer waits for them
+      const uint32_t full_bar0 = PAIR ? cluster_address(full0, 0) : full0;
+      auto load = [&](uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+        if constexpr (PAIR) tma_load_2d_pair(dst, map, bar, c0, c1);
+        else tma_load_2d(dst, map, bar, c0, c1);
+      };
+      for (int tile = walker; tile < total_tiles && ok; tile += walkers) {
         const int ot = tile % out_tiles, sp = tile / out_tiles;
-        const int m0 = (ot % m_tiles) * BM, n0 = (ot / m_tiles) * BN;
+        const int m0 = (ot % m_tiles) * TM + (int)rank * BM, n0 = (ot / m_tiles) * BN + (int)rank * S::B_ROWS;
         const int k_end = min(num_k, (sp + 1) * k_per);
         for (int k = sp * k_per; k < k_end; k++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           ok = mbar_wait(empty0 + 8 * s, ph ^ 1, err, 1, wait_limit);
           if (!ok) break;
-          mbar_expect_tx(full0 + 8 * s, S::A_BYTES + S::B_BYTES);
-          tma_load_2d(smem_u32(b_tiles + s * S::B_BYTES), &map_b, full0 + 8 * s, k * BK, n0);
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, (PAIR ? 2 : 1) * (S::A_BYTES + S::B_BYTES));
+          load(smem_u32(b_tiles + s * S::B_BYTES), &map_b, full_bar0 + 8 * s, k * BK, n0);
           if (!waited) {
             // the weight tiles of the first stages are on their way; the activations need the previous kernel
             if (it + 1 < STAGES && it + 1 < first_run) { pending_a[n_pending++] = make_int3(s, k * BK, m0); issued = it + 1; continue; }
             asm volatile("griddepcontrol.wait;" ::: "memory");
             waited = true;
             for (int i = 0; i < n_pending; i++)
-              tma_load_2d(smem_u32(a_tiles + pending_a[i].x * S::A_BYTES), &map_a, full0 + 8 * pending_a[i].x, pending_a[i].y, pending_a[i].z);
+              load(smem_u32(a_tiles + pending_a[i].x * S::A_BYTES), &map_a, full_bar0 + 8 * pending_a[i].x, pending_a[i].y, pending_a[i].z);
           }
-          tma_load_2d(smem_u32(a_tiles + s * S::A_BYTES), &map_a, full0 + 8 * s, k * BK, m0);
+          load(smem_u32(a_tiles + s * S::A_BYTES), &map_a, full_bar0 + 8 * s, k * BK, m0);
           issued = it + 1;
         }
       }
-      if (!ok || *(volatile int*)&err->flag != 0) {
-        // something went wrong: let the copies still in flight land before the block exits
+      if (rank == 0 && (!ok || *(volatile int*)&err->flag != 0)) {
+        // something went wrong: let the copies still in flight land before the block exits (a pair's count on
+        // these mbarriers, and no block of a pair leaves before both have come to the kernel's end)
         for (int i = max(0, issued - STAGES); i < issued; i++)
           mbar_wait(full0 + 8 * (i % STAGES), (i / STAGES) & 1, err, 4, wait_limit);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {                                   // ---- MMA issuer ----
-      constexpr uint32_t idesc = instr_desc(BM, BN);
+    if (lane == 0 && rank == 0) {                      // ---- MMA issuer ----
+      constexpr uint32_t idesc = instr_desc(TM, BN);
       int it = 0, local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
+      for (int tile = walker; tile < total_tiles && ok; tile += walkers, local++) {
         const int as = local & 1;
         ok = mbar_wait(acc_empty0 + 8 * as, ((local >> 1) & 1) ^ 1, err, 5, wait_limit);   // the epilogue has drained this half
         if (!ok) break;
@@ -159,12 +183,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_addr = smem_u32(a_tiles + s * S::A_BYTES), b_addr = smem_u32(b_tiles + s * S::B_BYTES);
 #pragma unroll
-          for (int kk = 0; kk < BK / UMMA_K; kk++)
-            umma(d_tmem, smem_desc(a_addr + kk * UMMA_K * 2), smem_desc(b_addr + kk * UMMA_K * 2), idesc,
-                 (k > k_begin || kk > 0) ? 1u : 0u);
-          umma_commit(empty0 + 8 * s);                 // the slot is free once these MMAs have read it
+          for (int kk = 0; kk < BK / UMMA_K; kk++) {
+            const uint64_t da = smem_desc(a_addr + kk * UMMA_K * 2), db = smem_desc(b_addr + kk * UMMA_K * 2);
+            if constexpr (PAIR) umma_pair(d_tmem, da, db, idesc, (k > k_begin || kk > 0) ? 1u : 0u);
+            else umma(d_tmem, da, db, idesc, (k > k_begin || kk > 0) ? 1u : 0u);
+          }
+          // the slot is free (in both blocks of a pair) once these MMAs have read it
+          if constexpr (PAIR) umma_commit_pair(empty0 + 8 * s);
+          else umma_commit(empty0 + 8 * s);
         }
-        if (ok) umma_commit(acc_full0 + 8 * as);       // this tile's accumulator is complete
+        if (ok) {                                      // this tile's accumulator is complete
+          if constexpr (PAIR) umma_commit_pair(acc_full0 + 8 * as);
+          else umma_commit(acc_full0 + 8 * as);
+        }
       }
     }
   } else {                                             // ---- epilogue, warps 2..5 ----
@@ -176,10 +207,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // a lane can write 32 consecutive columns of its row 16 bytes at a time when rows start on 16-byte boundaries
     const bool rows_aligned = (((uintptr_t)out) & 15) == 0 && ((size_t)ldo * sizeof(TO)) % 16 == 0;
     tlc_wait(out);                                     // `out` may still be read or written by the previous kernel
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, local++) {
+    for (int tile = walker; tile < total_tiles && ok; tile += walkers, local++) {
       const int as = local & 1;
       const int ot = tile % out_tiles, sp = tile / out_tiles;
-      const int m0 = (ot % m_tiles) * BM, n0 = (ot / m_tiles) * BN;
+      const int m0 = (ot % m_tiles) * TM + (int)rank * BM, n0 = (ot / m_tiles) * BN;
       ok = mbar_wait(acc_full0 + 8 * as, (local >> 1) & 1, err, 3, wait_limit);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -381,14 +412,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // hand the accumulator half back to the MMA issuer (with splits that happened above)
       if (!split) {
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * as) : "memory");
+        if (lane == 0) {
+          if constexpr (PAIR) mbar_arrive_cluster(cluster_address(acc_empty0 + 8 * as, 0));   // the issuer's block
+          else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * as) : "memory");
+        }
       }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-  __syncthreads();
-  if (warp == 1)
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+  if constexpr (PAIR) {
+    cluster_sync();                                    // neither block's memories are in use by the other any more
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+  } else {
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * BN) : "memory");
+  }
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -426,12 +464,36 @@ struct MapHash {
 };
 std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;
 
-template <typename TO, int BN, int STAGES, bool SWIGLU = false>
+int g_pairs = 0;                                            // pairs of blocks the GPU runs at once (0: none)
+constexpr int PAIR_BN = 256, PAIR_STAGES = 6;               // the pair's tile is 256 x 256; a stage is 32 KB a block
+
+template <typename TO, int BN, int STAGES, bool SWIGLU = false, bool PAIR = false>
 int configure() {
-  if (cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, BN, STAGES, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           Smem<BN, STAGES>::TOTAL) != cudaSuccess)
-    return tlc_fail(-2, "linear: cannot reserve %d bytes of shared memory", Smem<BN, STAGES>::TOTAL);
+  if (cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, BN, STAGES, SWIGLU, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           Smem<BN, STAGES, PAIR>::TOTAL) != cudaSuccess)
+    return tlc_fail(-2, "linear: cannot reserve %d bytes of shared memory", Smem<BN, STAGES, PAIR>::TOTAL);
   return 0;
+}
+
+// How many clusters of two blocks of the pair kernel fit on the GPU at once.
+int count_pairs() {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * g_sms);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = Smem<PAIR_BN, PAIR_STAGES, true>::TOTAL;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_kernel<__nv_bfloat16, PAIR_BN, PAIR_STAGES, false, true>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
 }
 
 int init_once() {
@@ -449,9 +511,14 @@ int init_once() {
   if (int rc = configure<__nv_bfloat16, 128, 6, true>()) return rc;
   if (int rc = configure<float, 256, 4, true>()) return rc;
   if (int rc = configure<__nv_bfloat16, 256, 4, true>()) return rc;
+  if (int rc = configure<float, PAIR_BN, PAIR_STAGES, false, true>()) return rc;
+  if (int rc = configure<__nv_bfloat16, PAIR_BN, PAIR_STAGES, false, true>()) return rc;
+  if (int rc = configure<float, PAIR_BN, PAIR_STAGES, true, true>()) return rc;
+  if (int rc = configure<__nv_bfloat16, PAIR_BN, PAIR_STAGES, true, true>()) return rc;
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
   if (g_sms <= 0) g_sms = 148;
+  g_pairs = count_pairs();
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult q;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn)
@@ -535,7 +602,7 @@ template <typename TO, int BN, int STAGES, bool SWIGLU = false>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, const float* colscale, const float* colbias,
            int accumulate, int M, int N, int K, cudaStream_t stream) {
   using S = Smem<BN, STAGES>;
-  auto kern = gemm_tcgen05_kernel<TO, BN, STAGES, SWIGLU>;
+  auto kern = gemm_tcgen05_kernel<TO, BN, STAGES, SWIGLU, false>;
   int splits = SWIGLU ? 1 : pick_splits(M, N, K, BN);
   int slot = 0;
   if (splits > 1) {
@@ -552,6 +619,32 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, con
   tlc_launch(kern, dim3(grid), dim3(THREADS), S::TOTAL, stream, ma, mb, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, g_err_dev,
              splits, part, arrivals);
   TLC_CHECK_LAUNCH("linear(tcgen05)");
+  return 0;
+}
+
+// Pairs of blocks on tiles of 256 x 256: a cluster of two per tile, as many pairs as the GPU runs at once.
+template <typename TO, bool SWIGLU = false>
+int launch_pairs(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, const float* colscale, const float* colbias,
+                 int accumulate, int M, int N, int K, cudaStream_t stream) {
+  using S = Smem<PAIR_BN, PAIR_STAGES, true>;
+  const int tiles = ((N + PAIR_BN - 1) / PAIR_BN) * ((M + 2 * BM - 1) / (2 * BM));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * std::min(tiles, g_pairs));
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = S::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_tlc_pdl ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<TO, PAIR_BN, PAIR_STAGES, SWIGLU, true>, ma, mb, (TO*)out, ldo, colscale, colbias,
+                     accumulate, M, N, K, g_err_dev, 1, (float*)nullptr, (unsigned*)nullptr);
+  TLC_CHECK_LAUNCH("linear(tcgen05, pairs)");
   return 0;
 }
 
@@ -597,6 +690,20 @@ static int pick_tile(int M, int N) {
   return bn;
 }
 
+// Test hook: 0 = pairs of blocks where they pay, 1 = never, 2 = wherever the GPU can run them.
+static int g_pair_override = 0;
+extern "C" void tlc_linear_pair_override(int mode) { g_pair_override = mode; }
+// How many pairs of blocks the GPU runs at once (0: it cannot, and every product runs on single blocks).
+extern "C" int tlc_linear_pairs() { return init_once() ? 0 : g_pairs; }
+
+// Pairs of blocks on 256 x 256 tiles: when there are more than 128 rows and single blocks would take tiles
+// of 256 columns anyway (wide outputs, many rows).
+static bool pick_pairs(int M, int N) {
+  if (g_pairs <= 0 || g_pair_override == 1) return false;
+  if (g_pair_override == 2) return true;
+  return M > BM && !g_tile_override && pick_tile(M, N) == 256;
+}
+
 extern "C" int tlc_linear_tcgen05_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int K) {
   return a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 &&
          ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0);
@@ -619,6 +726,11 @@ extern "C" int tlc_linear_swiglu(const void* a, int a_dtype, int lda, const void
   if (int rc = init_once()) return rc;
   CUtensorMap ma, mb;
   if (int rc = get_map(a, M, K, lda, BM, &ma)) return rc;
+  if (pick_pairs(M, N)) {
+    if (int rc = get_map(w, N, K, ldw, PAIR_BN / 2, &mb)) return rc;
+    return out_dtype == TLC_F32 ? launch_pairs<float, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream)
+                                : launch_pairs<__nv_bfloat16, true>(ma, mb, out, ldo, colscale, colbias, 0, M, N, K, stream);
+  }
   const int bn = pick_tile(M, N);
   if (bn == 256) {
     if (int rc = get_map(w, N, K, ldw, 256, &mb)) return rc;
@@ -658,6 +770,11 @@ extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, in
   CUtensorMap ma, mb;
   if (out_dtype != TLC_F32 && out_dtype != TLC_BF16) return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
   if (int rc = get_map(a, M, K, lda, BM, &ma)) return rc;
+  if (pick_pairs(M, N)) {
+    if (int rc = get_map(w, N, K, ldw, PAIR_BN / 2, &mb)) return rc;
+    return out_dtype == TLC_F32 ? launch_pairs<float>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream)
+                                : launch_pairs<__nv_bfloat16>(ma, mb, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  }
   const int bn = pick_tile(M, N);
   if (bn == 256) {
     if (int rc = get_map(w, N, K, ldw, 256, &mb)) return rc;

@@ -103,6 +103,11 @@ int tlc_linear_tcgen05_ok(int a_dtype, int lda, const void* a, int w_dtype, int 
 /* Test hooks: force the tile width (0, 64, 128, 256) / how many blocks share a tile's K-steps (0 = choose). */
 void tlc_linear_tile_override(int bn);
 void tlc_linear_split_override(int n);
+/* Test hook: pairs of blocks on 256 x 256 tiles (tcgen05.mma.cta_group::2): 0 = where they pay, 1 = never,
+ * 2 = wherever the GPU can run them. */
+void tlc_linear_pair_override(int mode);
+/* How many pairs of blocks the GPU runs at once; 0 if it runs none (every product then takes single blocks). */
+int tlc_linear_pairs(void);
 
 /* ---- attention (attention.cu, attention_decode_fused.cu, attention_prefill.cu) ------------------- */
 /* Rotates q and k (split-half pairs over the first rope_dim dims, angle = position * inv_freq[i]); writes

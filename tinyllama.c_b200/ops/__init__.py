@@ -54,6 +54,8 @@ _SIGNATURES = {
     "tlc_linear_tcgen05_ok": (_i, [_i, _i, _vp, _i, _i, _vp, _i]),
     "tlc_linear_tile_override": (None, [_i]),
     "tlc_linear_split_override": (None, [_i]),
+    "tlc_linear_pair_override": (None, [_i]),
+    "tlc_linear_pairs": (_i, []),
     "tlc_rope_kv_store": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                _i, _i, _vp]),
     "tlc_attention": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp]),
@@ -274,6 +276,17 @@ def linear_split_override(splits: int) -> None:
     """Fixes how many blocks share the K-steps of a tile of the tensor-core product (0: chosen from the
     sizes, 1: none); for tests."""
     library().tlc_linear_split_override(int(splits))
+
+
+def linear_pair_override(mode: int) -> None:
+    """Pairs of blocks on 256 x 256 tiles in the tensor-core product: 0 where they pay, 1 never, 2 wherever
+    the GPU can run them; for tests."""
+    library().tlc_linear_pair_override(int(mode))
+
+
+def linear_pairs() -> int:
+    """How many pairs of blocks (clusters of two) of the tensor-core product the GPU runs at once."""
+    return int(library().tlc_linear_pairs())
 
 
 def linear_swiglu(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, colscale: Optional[torch.Tensor] = None,
