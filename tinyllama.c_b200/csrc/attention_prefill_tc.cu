@@ -9,14 +9,18 @@
 //   * three warps of one agent each, on three schedulers: one starts the copies, one issues S = Q K^T (M 128,
 //     N 64, K hd) into one of two score buffers in tensor memory, two tiles ahead of the workers, and one issues
 //     O += P V (M 128, N hd, K 64) into the output accumulator, also in tensor memory;
-//   * sixteen worker warps read a score tile back (tcgen05.ld; a thread owns a quarter of a row: the exponentials
-//     and the tensor-memory loads of one warp hide behind the other three of its scheduler), scale, mask, take the
-//     row's maximum (the quarters meet in shared memory), write P = 2^(s - m) in bfloat16 into shared memory in
-//     the layout tcgen05.mma reads, and keep their share of the row's sum; the scores of the next tile are
-//     fetched into registers before the exponentials of this one;
-//   * the running maximum a row's numerators refer to moves only when the true maximum has grown by more than
-//     2^8: the output accumulator is then read back, scaled and stored again (tcgen05.ld / st); P stays below
-//     2^8, far inside bfloat16's range, and the sum is 32-bit.
+//   * eight worker warps in two groups: group w takes key tiles w, w + 2, ... with a score buffer, a P buffer
+//     and an output accumulator of its own.  A thread owns a row of its group's tile: it reads the row's 64 scores
+//     (tcgen05.ld), masks, takes the maximum, writes P = 2^(s - m) in bfloat16 into shared memory in the layout
+//     tcgen05.mma reads, and keeps the row's sum.  Threads share nothing until the end, so the groups drift half
+//     a tile apart: one's exponentials run under the other's loads and products;
+//   * the maximum a row's numerators refer to moves only when the true maximum has grown by more than 2^8: the
+//     row of the group's output accumulator is then read back, scaled and stored again (tcgen05.ld / st); P stays
+//     below 2^8, far inside bfloat16's range, and the sum is 32-bit;
+//   * at the end the groups' maxima and sums meet in shared memory and each group writes half of the columns of
+//     O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)).
+// A tcgen05.mma of M 128, N 64, K 16 takes about 64 cycles here and one of N 128 about 96 (measured with clock
+// stamps around the issue): 32 + N / 2, so the products take about 900 of the 1,300 cycles a tile costs.
 // Sequences of unequal length are packed back to back; a block finds its sequence from cu_seqlens.  Every wait
 // on an mbarrier is bounded (codes 21-27 of the error word); after one that ran out the block goes on without
 // waiting, frees its tensor memory and returns, and the host raises.
@@ -32,13 +36,12 @@ constexpr int BM = 128;                  // query rows per block
 constexpr int BN = 64;                   // keys per tile = one page
 static_assert(BN == TLC_PAGE, "a key tile is one page");
 constexpr int KS = 4, VS = 3;            // stages of the K and V rings
-constexpr int WORKERS = 512, THREADS = WORKERS + 96;
-constexpr int NCG = WORKERS / 128;       // column groups: threads that share a row
-constexpr int CW = BN / NCG;             // key columns of a thread in a tile
+constexpr int WORKERS = 256, THREADS = WORKERS + 96;
+constexpr int NG = WORKERS / 128;        // worker groups: each takes every NG-th key tile, with an output accumulator of its own
+static_assert(NG == 2, "two groups of workers");
 constexpr float TAU = 8.0f;              // how far (in powers of two) a row's maximum may run ahead of its reference
 
 __device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(WORKERS) : "memory"); }
-static_assert(CW == 16, "a thread takes 16 key columns of a tile");
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
@@ -86,8 +89,8 @@ struct FaSmem {
   static constexpr int K_SLAB = BN * 128, K_STAGE = (HD / 64) * K_SLAB, K = Q + Q_BYTES;
   static constexpr int V_STAGE = HD * 128, V = K + KS * K_STAGE;
   static constexpr int P_BUF = BM * 128, P = V + VS * V_STAGE;
-  static constexpr int X = P + 2 * P_BUF;                 // [2][NCG][128] floats: the column groups' maxima (and sums at the end)
-  static constexpr int BARS = X + 2 * NCG * BM * 4;       // mbarriers, tmem slot, dead flag
+  static constexpr int X = P + 2 * P_BUF;                 // [2][NG][128] floats: the groups' reference maxima and sums, at the end
+  static constexpr int BARS = X + 2 * NG * BM * 4;        // mbarriers, tmem slot, dead flag
   static constexpr int N_BARS = 1 + 2 * KS + 2 * VS + 8;
   static constexpr int TABLE = BARS + N_BARS * 8 + 16;    // the block's page indices
   static int total(int max_tiles) { return TABLE + max_tiles * 4 + 1024; }
@@ -102,7 +105,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             float scale_log2, int window, int p_max, int out_ld, ErrWords* err) {
   tlc_pdl(out);
   using L_ = FaSmem<HD>;
-  constexpr int TCOLS = 256;                              // scores 0..63 and 64..127, output from 128
+  constexpr int TCOLS = HD == 128 ? 512 : 256;            // the groups' scores at 0 and 64, their outputs at 128 and 128 + hd
   extern __shared__ uint8_t fa_raw[];
   uint8_t* sm = (uint8_t*)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
   float* xch = reinterpret_cast<float*>(sm + L_::X);
@@ -135,7 +138,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     s_row0 = row0;
     for (int i = 0; i < L_::N_BARS; i++) {
       const uint32_t bar = bar_q + 8 * i;               // every worker warp arrives once on s_free and p_ready, one agent on the rest
-      mbar_init(bar, (bar == s_free(0) || bar == s_free(1) || bar == p_ready(0) || bar == p_ready(1)) ? WORKERS / 32 : 1);
+      mbar_init(bar, (bar == s_free(0) || bar == s_free(1) || bar == p_ready(0) || bar == p_ready(1)) ? 4 : 1);
     }
     *dead = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -224,128 +227,125 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t p_lo = desc_lo(sm0 + L_::P + (j & 1) * L_::P_BUF), v_lo = desc_lo(sm0 + L_::V + st * L_::V_STAGE);
 #pragma unroll
         for (int kk = 0; kk < 4; kk++)
-          umma_halves(tmem + 128u, p_lo + (uint32_t)(kk * 2), v_lo + (uint32_t)(kk * 2), DESC_HI, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_halves(tmem + 128u + (uint32_t)((j & 1) * HD), p_lo + (uint32_t)(kk * 2), v_lo + (uint32_t)(kk * 2), DESC_HI, idesc_o,
+                      (j >= 2 || kk > 0) ? 1u : 0u);
         umma_commit(pv_done(j & 1));
         umma_commit(v_empty(st));
       }
     }
     __syncwarp();
   } else {
-    // ---- the workers: thread (quarter, lane) of column group cg owns row r of the tile, 16 key columns of every key
-    // tile and hd / 4 output columns ----
-    const int quarter = warp & 3, cg = warp >> 2, r = 32 * quarter + lane;
+    // ---- the workers: two groups of four warps; group w takes key tiles w, w + 2, ... and owns a score buffer, a
+    // P buffer and an output accumulator.  Thread (quarter, lane) of a group owns row r of the tile: all 64
+    // scores of a key tile and its row of the group's output.  Nothing is shared between threads until the end:
+    // the groups run half a tile apart, one's exponentials under the other's loads and products. ----
+    const int wg = warp >> 2, quarter = warp & 3, r = 32 * quarter + lane;
     const uint32_t lanes = (uint32_t)(quarter * 32) << 16;
     const int pr = p0 + r;                                // this row's position
-    constexpr int OC = HD / NCG;                          // output columns of a thread: 32 or 16
-    float m_used = -INFINITY, l = 0.f;
-    uint32_t sr[CW];
-    wait(s_full(0), 0u, 28);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    __syncwarp();
-    tmem_ld16(tmem + lanes + (uint32_t)(CW * cg), sr);
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncwarp();
-    if (lane == 0) mbar_arrive(s_free(0));
-    for (int j = 0; j < n; j++) {
-      float s2[CW];
-      const int kbase = (tile_lo + j) * BN + CW * cg;
-      const bool need_mask = window > 0 || (tile_lo + j) * BN + BN - 1 > p0;
-      float mx = -INFINITY;
-      if (need_mask) {
+    const uint32_t s_at = tmem + lanes + (uint32_t)(wg * BN);
+    const uint32_t o_at = tmem + lanes + 128u + (uint32_t)(wg * HD);
+    float m_ref = -INFINITY, l = 0.f;                     // the maximum the numerators refer to (scaled, log2), the sum
+    int mine = 0;                                         // tiles this group has done
+    for (int j = wg; j < n; j += NG, mine++) {
+      uint32_t sr[64];
+      wait(s_full(wg), (uint32_t)(mine & 1), 28);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      __syncwarp();
+      tmem_ld32_nowait(s_at, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+      tmem_ld32_nowait(s_at + 32u, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_free(wg));             // the scores are in registers: the buffer may take tile j + 2
+      const int kbase = (tile_lo + j) * BN;
+      if (window > 0 || kbase + BN - 1 > p0) {
 #pragma unroll
-        for (int c = 0; c < CW; c++) {
+        for (int c = 0; c < 64; c++) {
           const int kp = kbase + c;
-          const float v = (kp <= pr && (window <= 0 || kp > pr - window)) ? __uint_as_float(sr[c]) * scale_log2 : -INFINITY;
-          s2[c] = v;
-          mx = fmaxf(mx, v);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < CW; c++) {
-          s2[c] = __uint_as_float(sr[c]) * scale_log2;
-          mx = fmaxf(mx, s2[c]);
+          if (!(kp <= pr && (window <= 0 || kp > pr - window))) sr[c] = 0xff800000u;     // -inf
         }
       }
-      float* xm = xch + (j & 1) * NCG * BM;
-      xm[cg * BM + r] = mx;
-      // the next tile's scores on their way into registers while this tile's exponentials run
-      if (j + 1 < n) {
-        wait(s_full((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1), 28);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        __syncwarp();
-        tmem_ld16_nowait(tmem + lanes + (uint32_t)(((j + 1) & 1) * BN + CW * cg), sr);
-      }
-      workers_sync();
+      float mx = -INFINITY;
 #pragma unroll
-      for (int o = 0; o < NCG; o++) mx = fmaxf(mx, xm[o * BM + r]);
+      for (int c = 0; c < 64; c++) mx = fmaxf(mx, __uint_as_float(sr[c]));
+      mx *= scale_log2;
       // the reference maximum moves only when the true one has run ahead of it by more than 2^TAU
-      const bool grow = mx > m_used + TAU || (m_used == -INFINITY && mx > -INFINITY);
-      float factor = 1.f;
-      if (grow) {
-        factor = m_used == -INFINITY ? 0.f : ex2_quick(m_used - mx);
-        m_used = mx;
-        l *= factor;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        wait(pv_done((j - 1) & 1), (uint32_t)(((j - 1) >> 1) & 1), 29);           // every product into O so far is done
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (j + 1 < n) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");   // the scores in flight first
-        uint32_t o[OC];
-        const uint32_t at = tmem + lanes + 128u + (uint32_t)(cg * OC);
-        tmem_ldn(at, o);
+      const bool grow = mx > m_ref + TAU || (m_ref == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        float factor = 1.f;
+        if (grow) {
+          factor = m_ref == -INFINITY ? 0.f : ex2_quick(m_ref - mx);
+          m_ref = mx;
+          l *= factor;
+        }
+        if (mine > 0) {
+          wait(pv_done(wg), (uint32_t)((mine - 1) & 1), 29);                          // every product into this output so far is done
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          __syncwarp();
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; c++) {
+            uint32_t o[32];
+            tmem_ld32(o_at + (uint32_t)(32 * c), o);
 #pragma unroll
-        for (int c = 0; c < OC; c++) o[c] = __float_as_uint(__uint_as_float(o[c]) * factor);
-        tmem_stn(at, o);
+            for (int e = 0; e < 32; e++) o[e] = __float_as_uint(__uint_as_float(o[e]) * factor);
+            tmem_st32(o_at + (uint32_t)(32 * c), o);
+          }
+        }
       }
-      const float m_ref = m_used == -INFINITY ? 0.f : m_used;
+      const float neg = m_ref == -INFINITY ? 0.f : -m_ref;
       float sum = 0.f;
-      uint32_t pk[CW / 2];
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < CW / 2; c++) {
-        const float a = ex2_quick(s2[2 * c] - m_ref), bq = ex2_quick(s2[2 * c + 1] - m_ref);
+      for (int c = 0; c < 32; c++) {
+        const float a = ex2_quick(fmaf(__uint_as_float(sr[2 * c]), scale_log2, neg));
+        const float bq = ex2_quick(fmaf(__uint_as_float(sr[2 * c + 1]), scale_log2, neg));
         sum += a + bq;
         pk[c] = pack_bf16(a, bq);
       }
       l += sum;
-      if (j >= 2) wait(pv_done(j & 1), (uint32_t)(((j - 2) >> 1) & 1), 29);        // P's buffer of tile j - 2 is free
-      uint8_t* prow = sm + L_::P + (j & 1) * L_::P_BUF + r * 128;
+      if (mine > 0) wait(pv_done(wg), (uint32_t)((mine - 1) & 1), 29);               // the group's P buffer is free
+      uint8_t* prow = sm + L_::P + wg * L_::P_BUF + r * 128;
 #pragma unroll
-      for (int q = 0; q < CW / 8; q++)
-        *reinterpret_cast<uint4*>(prow + ((((CW / 8) * cg + q) ^ (r & 7)) << 4)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+      for (int q = 0; q < 8; q++)
+        *reinterpret_cast<uint4*>(prow + ((q ^ (r & 7)) << 4)) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      if (j + 1 < n) {
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");               // the next tile's scores have arrived
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(s_free((j + 1) & 1));
-      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();                                         // the warp's rows of P are written and fenced
-      if (lane == 0) mbar_arrive(p_ready(j & 1));
+      if (lane == 0) mbar_arrive(p_ready(wg));
     }
-    // ---- the row's sum (all column groups), the output ----
-    wait(pv_done((n - 1) & 1), (uint32_t)(((n - 1) >> 1) & 1), 29);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    float* xl = xch + (n & 1) * NCG * BM;
-    xl[cg * BM + r] = l;
+    // ---- the two groups' results meet: O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / (l_0 2^(m_0 - m) + l_1 2^(m_1 - m)) ----
+    if (mine > 0) wait(pv_done(wg), (uint32_t)((mine - 1) & 1), 29);
+    xch[wg * BM + r] = m_ref;
+    xch[(NG + wg) * BM + r] = l;
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     workers_sync();
-    float l_all = 0.f;
-#pragma unroll
-    for (int o = 0; o < NCG; o++) l_all += xl[o * BM + r];
-    const float inv = 1.0f / l_all;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const float m0 = xch[r], m1 = xch[BM + r];
+    const float m_all = fmaxf(m0, m1);
+    const float w0 = m0 == -INFINITY ? 0.f : ex2_quick(m0 - m_all), w1 = m1 == -INFINITY ? 0.f : ex2_quick(m1 - m_all);
+    const float inv = 1.0f / (xch[NG * BM + r] * w0 + xch[(NG + 1) * BM + r] * w1);
+    const float f0 = w0 * inv, f1 = w1 * inv;
+    const bool has1 = n > 1;                              // the second group had a tile at all (else its output is not written)
     __syncwarp();
-    {
-      uint32_t o[OC];
-      tmem_ldn(tmem + lanes + 128u + (uint32_t)(cg * OC), o);
-      if (r < rows) {
-        uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(t0 + i0 + r) * out_ld + (size_t)h * HD + cg * OC);
+#pragma unroll 1
+    for (int c = 0; c < HD / 64; c++) {                   // the group's half of the output columns, 32 at a time
+      const int col = wg * (HD / 2) + 32 * c;
+      uint32_t o[32];
+      float acc[32];
+      tmem_ld32(tmem + lanes + 128u + (uint32_t)col, o);
 #pragma unroll
-        for (int q = 0; q < OC / 8; q++)
-          dst[q] = make_uint4(pack_bf16(__uint_as_float(o[8 * q]) * inv, __uint_as_float(o[8 * q + 1]) * inv),
-                              pack_bf16(__uint_as_float(o[8 * q + 2]) * inv, __uint_as_float(o[8 * q + 3]) * inv),
-                              pack_bf16(__uint_as_float(o[8 * q + 4]) * inv, __uint_as_float(o[8 * q + 5]) * inv),
-                              pack_bf16(__uint_as_float(o[8 * q + 6]) * inv, __uint_as_float(o[8 * q + 7]) * inv));
+      for (int e = 0; e < 32; e++) acc[e] = __uint_as_float(o[e]) * f0;
+      if (has1) {
+        tmem_ld32(tmem + lanes + 128u + (uint32_t)(HD + col), o);
+#pragma unroll
+        for (int e = 0; e < 32; e++) acc[e] = fmaf(__uint_as_float(o[e]), f1, acc[e]);
+      }
+      if (r < rows) {
+        uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(t0 + i0 + r) * out_ld + (size_t)h * HD + col);
+#pragma unroll
+        for (int q = 0; q < 4; q++)
+          dst[q] = make_uint4(pack_bf16(acc[8 * q], acc[8 * q + 1]), pack_bf16(acc[8 * q + 2], acc[8 * q + 3]),
+                              pack_bf16(acc[8 * q + 4], acc[8 * q + 5]), pack_bf16(acc[8 * q + 6], acc[8 * q + 7]));
       }
     }
   }
