@@ -3,9 +3,12 @@
 // Same math as the reference's op_attn (cpu_op.c:1010-1062): causal grouped-query attention, scale
 // 1/sqrt(head_dim), max-subtracted softmax, optional window.  A block takes 128 consecutive new rows of one
 // sequence and one query head and walks the sequence's key tiles (a page of 64 keys each) up to the diagonal:
-//   * Q [128, hd] is loaded once by TMA; K tiles [64 keys, hd] come by TMA straight from the cache pages;
-//     V tiles come transposed, [hd, 64 keys], from a scratch that attention_vt_kernel fills first (a page of V
-//     is [keys, hd]; tcgen05.mma wants K, here the keys, along the rows of shared memory);
+//   * Q [128, hd] is loaded once by TMA; K and V tiles [64 keys, hd] come by TMA straight from the cache pages.
+//     For S = Q K^T the keys are the rows of the B operand (K-major, as the pages have them); for O += P V the keys
+//     are the reduction and hd runs along the rows of shared memory: V is an MN-major operand (its descriptor has
+//     the 8-key groups 1,024 bytes apart and the 64-column halves of hd a slab apart), so no copy is transposed.
+//     Keys past a sequence's end have P = 0; the values there must be finite (a cache starts as zeros and only
+//     kernels write it), since 0 x NaN would spoil the row;
 //   * three warps of one agent each, on three schedulers: one starts the copies, one issues S = Q K^T (M 128,
 //     N 64, K hd) into one of two score buffers in tensor memory, two tiles ahead of the workers, and one issues
 //     O += P V (M 128, N hd, K 64) into the output accumulator, also in tensor memory;
@@ -52,37 +55,6 @@ __device__ __forceinline__ float ex2_quick(float x) {
   return r;
 }
 
-// ---- V transposed per (sequence, page, kv head): vt[((b * P_max + page) * KV + g)][d][key], zero past the end ----
-// grid (B, KV, P_max), 256 threads: a 64 x hd tile through shared memory.
-__global__ void __launch_bounds__(256)
-attention_vt_kernel(const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
-                    const int* __restrict__ cu_seqlens, const int* __restrict__ slots, const int* __restrict__ start_pos,
-                    __nv_bfloat16* __restrict__ vt, int KV, int hd, int window, int p_max) {
-  tlc_pdl(v_pages, vt);
-  extern __shared__ unsigned short vt_tile[];            // [64][hd + 2]
-  const int b = blockIdx.x, g = blockIdx.y, page = blockIdx.z;
-  const int n_new = cu_seqlens[b + 1] - cu_seqlens[b];
-  const int len = start_pos[b] + n_new;                  // keys of the sequence after this step
-  const int first = window > 0 ? max(0, start_pos[b] + 1 - window) / BN : 0;
-  if (n_new <= 0 || page * BN >= len || page < first) return;
-  const int ld = hd + 2;
-  const unsigned short* src = reinterpret_cast<const unsigned short*>(v_pages) +
-                              (((size_t)block_table[(size_t)slots[b] * max_pages + page] * KV + g) * BN) * hd;
-  for (int idx = threadIdx.x; idx < BN * (hd / 2); idx += 256) {
-    const int k = idx / (hd / 2), d = (idx % (hd / 2)) * 2;
-    uint32_t v = 0;
-    if (page * BN + k < len) v = *reinterpret_cast<const uint32_t*>(src + (size_t)k * hd + d);
-    vt_tile[k * ld + d] = (unsigned short)(v & 0xffffu);
-    vt_tile[k * ld + d + 1] = (unsigned short)(v >> 16);
-  }
-  __syncthreads();
-  unsigned short* dst = reinterpret_cast<unsigned short*>(vt) + ((((size_t)b * p_max + page) * KV + g) * hd) * BN;
-  for (int idx = threadIdx.x; idx < hd * (BN / 2); idx += 256) {
-    const int d = idx / (BN / 2), k = (idx % (BN / 2)) * 2;
-    *reinterpret_cast<uint32_t*>(dst + (size_t)d * BN + k) = (uint32_t)vt_tile[k * ld + d] | ((uint32_t)vt_tile[(k + 1) * ld + d] << 16);
-  }
-}
-
 template <int HD>
 struct FaSmem {
   static constexpr int Q_SLAB = BM * 128, Q = 0, Q_BYTES = (HD / 64) * Q_SLAB;
@@ -99,10 +71,10 @@ struct FaSmem {
 template <int HD>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                            const __grid_constant__ CUtensorMap map_vt, const int* __restrict__ block_table, int max_pages,
+                            const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_pages,
                             const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                             const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int H, int KV,
-                            float scale_log2, int window, int p_max, int out_ld, ErrWords* err) {
+                            float scale_log2, int window, int out_ld, ErrWords* err) {
   tlc_pdl(out);
   using L_ = FaSmem<HD>;
   constexpr int TCOLS = HD == 128 ? 512 : 256;            // the groups' scores at 0 and 64, their outputs at 128 and 128 + hd
@@ -193,7 +165,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           const int st = t % VS;
           if (t >= VS) wait(v_empty(st), (uint32_t)(((t - VS) / VS) & 1), 27);       // P V of tile t - VS is done
           mbar_expect_tx(v_full(st), L_::V_STAGE);
-          tma_load_2d(sm0 + L_::V + st * L_::V_STAGE, &map_vt, v_full(st), 0, (((b * p_max) + tile_lo + t) * KV + g) * HD);
+          for (int c = 0; c < HD / 64; c++)
+            tma_load_2d(sm0 + L_::V + st * L_::V_STAGE + c * L_::K_SLAB, &map_v, v_full(st), 64 * c, (pages[t] * KV + g) * BN);
         }
       }
     } else if (lane == 0 && role == 1) {
@@ -218,16 +191,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         umma_commit(k_empty(st));
       }
     } else if (lane == 0 && role == 2) {
-      constexpr uint32_t idesc_o = instr_desc(BM, HD);
+      constexpr uint32_t idesc_o = instr_desc(BM, HD) | (1u << 16);                   // V is MN-major: hd runs along its rows
       for (int j = 0; j < n; j++) {
         const int st = j % VS;
         wait(v_full(st), (uint32_t)((j / VS) & 1), 25);
         wait(p_ready(j & 1), (uint32_t)((j >> 1) & 1), 24);                          // P of tile j is in shared memory
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t p_lo = desc_lo(sm0 + L_::P + (j & 1) * L_::P_BUF), v_lo = desc_lo(sm0 + L_::V + st * L_::V_STAGE);
+        const uint32_t p_lo = desc_lo(sm0 + L_::P + (j & 1) * L_::P_BUF), v_lo = (desc_lo(sm0 + L_::V + st * L_::V_STAGE) & 0xFFFFu) | ((uint32_t)(L_::K_SLAB >> 4) << 16);
 #pragma unroll
         for (int kk = 0; kk < 4; kk++)
-          umma_halves(tmem + 128u + (uint32_t)((j & 1) * HD), p_lo + (uint32_t)(kk * 2), v_lo + (uint32_t)(kk * 2), DESC_HI, idesc_o,
+          umma_halves(tmem + 128u + (uint32_t)((j & 1) * HD), p_lo + (uint32_t)(kk * 2), v_lo + (uint32_t)(kk * (16 * 128 >> 4)), DESC_HI, idesc_o,
                       (j >= 2 || kk > 0) ? 1u : 0u);
         umma_commit(pv_done(j & 1));
         umma_commit(v_empty(st));
@@ -380,27 +353,23 @@ int page_map(const void* pages, long long rows, int hd, CUtensorMap* out) {
 template <int HD>
 int run(const __nv_bfloat16* q, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, long long n_page_rows,
         const int* block_table, int max_pages, const int* cu_seqlens, const int* slots, const int* start_pos,
-        __nv_bfloat16* out, __nv_bfloat16* vt, int n_seqs, int n_tiles_bound, int H, int KV, float scale, int window,
+        __nv_bfloat16* out, int n_seqs, int n_tiles_bound, int H, int KV, float scale, int window,
         int p_max, int T, int out_ld, cudaStream_t stream) {
   static bool configured = false;
   const int smem = FaSmem<HD>::total(p_max);
   TLC_REQUIRE(smem <= 220 * 1024, "attention(prefill, tcgen05): %d key tiles need %d bytes of shared memory", p_max, smem);
   if (!configured) {
-    if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess ||
-        cudaFuncSetAttribute(attention_vt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
+    if (cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess)
       return tlc_fail(-2, "attention(prefill, tcgen05): cannot reserve shared memory");
     configured = true;
   }
-  CUtensorMap mq, mk, mvt;
+  CUtensorMap mq, mk, mv;
   if (int rc = tlc_tensor_map_bf16(q, T, (long long)H * HD, (long long)H * HD, 64, BM, &mq)) return rc;
   if (int rc = page_map(k_pages, n_page_rows, HD, &mk)) return rc;
-  if (int rc = tlc_tensor_map_bf16(vt, (long long)n_seqs * p_max * KV * HD, BN, BN, 64, HD, &mvt)) return rc;
-  tlc_launch(attention_vt_kernel, dim3(n_seqs, KV, p_max), dim3(256), (size_t)BN * (HD + 2) * 2, stream, v_pages, block_table,
-             max_pages, cu_seqlens, slots, start_pos, vt, KV, HD, window, p_max);
-  TLC_CHECK_LAUNCH("attention(prefill, transposed values)");
-  tlc_launch(attention_prefill_tc_kernel<HD>, dim3(n_tiles_bound, H), dim3(THREADS), (size_t)smem, stream, mq, mk, mvt,
-             block_table, max_pages, cu_seqlens, slots, start_pos, out, n_seqs, H, KV, scale * 1.4426950408889634f, window, p_max,
-             out_ld, tlc_error_words());
+  if (int rc = page_map(v_pages, n_page_rows, HD, &mv)) return rc;
+  tlc_launch(attention_prefill_tc_kernel<HD>, dim3(n_tiles_bound, H), dim3(THREADS), (size_t)smem, stream, mq, mk, mv,
+             block_table, max_pages, cu_seqlens, slots, start_pos, out, n_seqs, H, KV, scale * 1.4426950408889634f, window, out_ld,
+             tlc_error_words());
   TLC_CHECK_LAUNCH("attention(prefill, tcgen05)");
   return 0;
 }
@@ -411,31 +380,25 @@ extern "C" int tlc_attention_prefill_tc_ok(int dtype, int hd, int H, int KV) {
   return dtype == TLC_BF16 && (hd == 64 || hd == 128) && KV > 0 && H % KV == 0 && H <= 65535 && KV <= 65535;
 }
 
-// bfloat16 elements of scratch for the transposed values of n_seqs sequences of at most max_keys keys
-extern "C" long long tlc_attention_prefill_tc_scratch(int n_seqs, int max_keys, int KV, int hd) {
-  return (long long)n_seqs * ((max_keys + BN - 1) / BN) * KV * hd * BN;
-}
-
 // n_tiles_bound: an upper bound of sum_b ceil(n_new_b / 128) (e.g. T / 128 + n_seqs); max_keys: keys of the longest
-// sequence after this step; n_pages: pages of the cache (k_pages and v_pages are [n_pages, KV, 64, hd]); vt: scratch of
-// tlc_attention_prefill_tc_scratch elements.
+// sequence after this step; n_pages: pages of the cache (k_pages and v_pages are [n_pages, KV, 64, hd]).
 extern "C" int tlc_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                                         const int* block_table, int max_pages, const int* cu_seqlens, const int* slots,
-                                        const int* start_pos, void* out, void* vt, int n_seqs, int n_tiles_bound, int H, int KV,
+                                        const int* start_pos, void* out, int n_seqs, int n_tiles_bound, int H, int KV,
                                         int hd, float scale, int window, int max_keys, int T, int out_ld, cudaStream_t stream) {
   if (n_seqs == 0 || n_tiles_bound == 0 || T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;
   TLC_REQUIRE(tlc_attention_prefill_tc_ok(TLC_BF16, hd, H, KV), "attention(prefill, tcgen05): %d heads, %d key/value heads of size %d are not built", H, KV, hd);
-  TLC_REQUIRE(out_ld % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)q % 16) == 0 && ((uintptr_t)vt % 16) == 0 &&
-              ((uintptr_t)k_pages % 16) == 0, "attention(prefill, tcgen05): rows must start on 16-byte boundaries");
+  TLC_REQUIRE(out_ld % 8 == 0 && ((uintptr_t)out % 16) == 0 && ((uintptr_t)q % 16) == 0 &&
+              ((uintptr_t)k_pages % 16) == 0 && ((uintptr_t)v_pages % 16) == 0, "attention(prefill, tcgen05): rows must start on 16-byte boundaries");
   TLC_REQUIRE(tlc_error_words() != nullptr, "attention(prefill, tcgen05): the library is not set up (tlc_linear_init)");
   const int p_max = (max_keys + BN - 1) / BN;
   TLC_REQUIRE(p_max >= 1 && p_max <= 65535, "attention(prefill, tcgen05): %d keys", max_keys);
   const long long rows = (long long)n_pages * KV * BN;
   const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
   if (hd == 64)
-    return run<64>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, (__nv_bfloat16*)vt,
+    return run<64>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out,
                    n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, stream);
-  return run<128>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out, (__nv_bfloat16*)vt,
+  return run<128>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out,
                   n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, stream);
 }

@@ -147,14 +147,13 @@ int tlc_attention_prefill(const void* q, const void* k_pages, const void* v_page
                           int max_tiles, const int* row_seq, float* part_o, float* part_ml, int T, int out_ld,
                           cudaStream_t stream);
 
-/* The same on tcgen05.mma (attention_prefill_tc.cu): 128-row tiles, Q and the K pages by TMA, V transposed into
- * `vt` (tlc_attention_prefill_tc_scratch bfloat16 elements) by a first kernel, scores and output in tensor
- * memory.  n_tiles_bound >= sum_b ceil(n_new_b / 128); n_pages: pages of k_pages / v_pages. */
+/* The same on tcgen05.mma (attention_prefill_tc.cu): 128-row tiles, Q and the K and V pages by TMA, scores and
+ * output in tensor memory.  n_tiles_bound >= sum_b ceil(n_new_b / 128); n_pages: pages of k_pages / v_pages.
+ * Values in pages past a sequence's end must be finite. */
 int tlc_attention_prefill_tc_ok(int dtype, int hd, int H, int KV);
-long long tlc_attention_prefill_tc_scratch(int n_seqs, int max_keys, int KV, int hd);
 int tlc_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                              const int* block_table, int max_pages, const int* cu_seqlens, const int* slots,
-                             const int* start_pos, void* out, void* vt, int n_seqs, int n_tiles_bound, int H, int KV,
+                             const int* start_pos, void* out, int n_seqs, int n_tiles_bound, int H, int KV,
                              int hd, float scale, int window, int max_keys, int T, int out_ld, cudaStream_t stream);
 
 /* ---- Mamba2 (mamba.cu, mamba_ssd.cu) ----------------------------------------------------------------- */

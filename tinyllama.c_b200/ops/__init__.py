@@ -70,8 +70,7 @@ _SIGNATURES = {
     "tlc_attention_prefill": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp,
                                    _vp, _i, _i, _vp]),
     "tlc_attention_prefill_tc_ok": (_i, [_i, _i, _i, _i]),
-    "tlc_attention_prefill_tc_scratch": (_ll, [_i, _i, _i, _i]),
-    "tlc_attention_prefill_tc": (_i, [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i,
+    "tlc_attention_prefill_tc": (_i, [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i,
                                       _i, _i, _vp]),
     "tlc_mamba_conv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i,
                             _i, _i, _i, _i, _i, _vp]),
@@ -425,11 +424,9 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     if tiled and _prompt_attention == 0 and max_keys > 0 and out_ld % 8 == 0 \
             and library().tlc_attention_prefill_tc_ok(BF16, hd, H, KV):
         B = slots.numel()
-        lib = library()
-        vt = torch.empty(lib.tlc_attention_prefill_tc_scratch(B, int(max_keys), KV, hd), dtype=torch.bfloat16, device=q.device)
         _call("tlc_attention_prefill_tc", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
               block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(),
-              out.data_ptr(), vt.data_ptr(), B, T // 128 + B, H, KV, hd, float(scale), int(window or 0), int(max_keys), T,
+              out.data_ptr(), B, T // 128 + B, H, KV, hd, float(scale), int(window or 0), int(max_keys), T,
               out_ld, _stream())
         return
     if tiled:
