@@ -243,6 +243,8 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true", help="time the prompt of --prefill-tokens tokens only "
                     "(--steps repetitions when fewer than 8): what a profiler capture of the prompt kernels runs")
     ap.add_argument("--no-big", dest="big", action="store_false", help="skip the 3B and 7B workloads among the points")
+    ap.add_argument("--no-pairs", action="store_true", help="run the linear layers on single blocks (128 x 256 tiles) instead "
+                    "of pairs of blocks on 256 x 256 tiles: the comparison behind profiles/linear_tcgen05_prefill_2048.md")
     ap.add_argument("--ref-budget", type=float, default=600.0, help="seconds the reference arm may take (it runs fewer "
                     "layers, and says so, where all of them would take longer)")
     args = ap.parse_args()
@@ -255,6 +257,9 @@ def main() -> int:
 
     import torch
     import tinyllama_c_b200 as tlc
+    if args.no_pairs:
+        from tinyllama_c_b200 import ops
+        ops.linear_pair_override(1)
     full_layers = CONFIGS[args.sizes]["num_hidden_layers"]
     if args.layers is None:
         args.layers = full_layers
