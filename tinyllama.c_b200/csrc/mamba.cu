@@ -35,8 +35,10 @@ mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_o
                   const int* __restrict__ start_pos, TO* __restrict__ xbc_out,
                   float* __restrict__ dt_out, float* __restrict__ dA_out, int n_rows, int Cd, int Hs) {
   tlc_pdl(proj, conv_state, xbc_out, dt_out, dA_out);
-  __shared__ int s_i[CONV_ROWS], s_has[CONV_ROWS], s_slot[CONV_ROWS];
+  __shared__ int s_i[CONV_ROWS], s_has[CONV_ROWS], s_slot[CONV_ROWS], s_plain;
   const int t0 = blockIdx.x * CONV_ROWS;
+  if (threadIdx.x == 0) s_plain = 1;
+  __syncthreads();
   if (threadIdx.x < CONV_ROWS) {
     const int t = t0 + threadIdx.x;
     int i = 0, has = 0, slot = 0;
@@ -49,10 +51,30 @@ mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_o
     s_i[threadIdx.x] = i;
     s_has[threadIdx.x] = has;
     s_slot[threadIdx.x] = slot;
+    // plain: all of the block's rows exist and every tap of every row reads a row of this step
+    if (t >= n_rows || i < K - 1) s_plain = 0;
   }
   __syncthreads();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
-  if (c < Cd) {
+  // The common block is kept free of the window's address arithmetic and of per-row branches: the kernel is bound by
+  // its instruction count, not by memory.  Row t0 + r reads raw rows r .. r + K - 1 (raw[0] is row t0 - (K-1)).
+  if (c < Cd && s_plain) {
+    const T* src = proj + (size_t)(t0 - (K - 1)) * ld + xbc_off + c;
+    float raw[CONV_ROWS + K - 1], wk[K];
+#pragma unroll
+    for (int q = 0; q < CONV_ROWS + K - 1; q++) raw[q] = to_f32(src[(size_t)q * ld]);
+#pragma unroll
+    for (int k = 0; k < K; k++) wk[k] = w[(size_t)c * K + k];
+    const float bv = bias ? bias[c] : 0.f;
+    TO* dst = xbc_out + (size_t)t0 * Cd + c;
+#pragma unroll
+    for (int r = 0; r < CONV_ROWS; r++) {
+      float sum = 0.f;
+#pragma unroll
+      for (int k = 0; k < K; k++) sum = fmaf(raw[r + k], wk[k], sum);
+      dst[(size_t)r * Cd] = from_f32<TO>(as_operand<QUICK>(silu_of<QUICK>(sum + bv)));
+    }
+  } else if (c < Cd) {
     // raw[q] is the sample of packed row t0 - (K-1) + q; rows before the step's first are never used
     float raw[CONV_ROWS + K - 1], wk[K];
 #pragma unroll
@@ -69,13 +91,20 @@ mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_o
       if (t >= n_rows) break;
       const int i = s_i[r];
       float sum = 0.f;
+      if (i >= K - 1) {
+        // every tap reads a row of this step: row t - (K-1-k) is raw row r + k (the common case, kept free of the
+        // window's address arithmetic: the kernel is bound by its instruction count, not by memory)
 #pragma unroll
-      for (int k = 0; k < K; k++) {
-        const int j = i - (K - 1 - k);                // new-token index that tap k reads
-        float x;
-        if (j >= 0) x = raw[r + k];                   // row t - (K-1-k) is raw row (t - (K-1-k)) - (t0 - (K-1)) = r + k
-        else x = s_has[r] ? conv_state[((size_t)s_slot[r] * (K - 1) + (K - 1 + j)) * Cd + c] : 0.f;
-        sum = fmaf(x, wk[k], sum);
+        for (int k = 0; k < K; k++) sum = fmaf(raw[r + k], wk[k], sum);
+      } else {
+#pragma unroll
+        for (int k = 0; k < K; k++) {
+          const int j = i - (K - 1 - k);              // new-token index that tap k reads
+          float x;
+          if (j >= 0) x = raw[r + k];
+          else x = s_has[r] ? conv_state[((size_t)s_slot[r] * (K - 1) + (K - 1 + j)) * Cd + c] : 0.f;
+          sum = fmaf(x, wk[k], sum);
+        }
       }
       xbc_out[(size_t)t * Cd + c] = from_f32<TO>(as_operand<QUICK>(silu_of<QUICK>(sum + bv)));
     }
