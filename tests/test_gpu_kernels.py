@@ -494,6 +494,16 @@ def test_mamba_conv(dtype, Di, G, N, K, Hs, bias):
     args16[7], args16[12] = state.clone(), torch.empty(T, Cd, dtype=torch.bfloat16)
     cmp("mamba_conv", args16, [12], tol_of=6e-3)
     cmp("mamba_conv", args16[:7] + [state.clone()] + args16[8:], [7, 13, 14], tol_of=2e-5)
+    # long sequences: blocks of 8 rows that lie inside one sequence, three or more rows from its start, take a path
+    # of their own (no window, no per-row branches); the blocks around them (a sequence's first rows, a block across
+    # two sequences, the last rows of the step) do not
+    starts, lens = [0, 40, 0, 5], [45, 3, 26, 13]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    T = sum(lens)
+    for o_dt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 6e-3)):
+        long_args = [rnd(g, T, Pd, dtype=DT[dtype]), Di, Di + Cd, args[3], args[4], args[5], args[6], state.clone(), cu, row_seq,
+                     slots, start_pos, torch.empty(T, Cd, dtype=o_dt), torch.empty(T, Hs), torch.empty(T, Hs)]
+        cmp("mamba_conv", long_args, [7, 12, 13, 14], tol_of=tol)
     # one row per sequence: the fused kernel of decode steps
     starts, lens = [0, 9, 1, 31, 2], [1, 1, 1, 1, 1]
     pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
