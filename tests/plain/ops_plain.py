@@ -31,9 +31,11 @@ def rmsnorm(x, weight, eps, out, rows=None):
     out.copy_((xs * s * _f(weight)).to(out.dtype))
 
 
-def gated_rmsnorm(y, z, weight, eps, n_groups, norm_before_gate, out, out_scale=1.0):
+def gated_rmsnorm(y, z, weight, eps, n_groups, norm_before_gate, out, out_scale=1.0, y_add=None):
     T, Di = y.shape
     y, z = _f(y), _f(z)
+    if y_add is not None:
+        y = y + _f(y_add)
     gate = z / (1.0 + torch.exp(-z))
     if weight is None:
         res = y * gate
@@ -160,7 +162,10 @@ def mamba_conv(proj, xbc_off, dt_off, w, bias, dt_bias, A, conv_state, cu_seqlen
     dA_out.copy_(torch.exp(dtv * _f(A)).to(dA_out.dtype))
 
 
-def ssm_scan(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, Hs, P, N, G, chunks=None, A=None):
+def ssm_scan(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, Hs, P, N, G, chunks=None, A=None, y_part=None):
+    # y_part: the engine may leave its outputs as two summands there and in y; the plain scan has one
+    if y_part is not None:
+        y_part.zero_()
     Di = Hs * P
     for b in range(slots.numel()):
         t0, t1 = int(cu_seqlens[b]), int(cu_seqlens[b + 1])

@@ -95,6 +95,16 @@ def test_gated_rmsnorm(dtype, groups, before, with_w):
     ops_plain.gated_rmsnorm(*args)
     ref, got = args[6].double(), gpu[6].cpu().double()
     assert (ref - got).abs().max() <= TOL[DT[dtype]] * ref.abs().max() * 2
+    # the input as two summands (what the scan of prompts leaves), on the vector kernel (aligned) and the plain one
+    for Dv, zoff in ((Di, 4), (6 * 24, 0)):
+        y1, y2 = rnd(g, T, Dv, scale=2.0), rnd(g, T, Dv, scale=2.0)
+        pr = rnd(g, T, Dv + 12, dtype=torch.float32 if zoff == 0 else DT[dtype])
+        wv = None if w is None else w[:Dv].contiguous()
+        out_cpu, out_gpu = torch.empty(T, Dv, dtype=DT[dtype]), torch.empty(T, Dv, dtype=DT[dtype], device="cuda")
+        ops.gated_rmsnorm(y1.cuda(), pr.cuda()[:, zoff:zoff + Dv], None if wv is None else wv.cuda(), 1e-5, groups, before, out_gpu,
+                          0.5, y2.cuda())
+        ops_plain.gated_rmsnorm(y1, pr[:, zoff:zoff + Dv], wv, 1e-5, groups, before, out_cpu, 0.5, y2)
+        assert (out_cpu.double() - out_gpu.cpu().double()).abs().max() <= TOL[DT[dtype]] * out_cpu.double().abs().max() * 2
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -585,17 +595,22 @@ def test_ssm_scan_in_matrix_form_on_tensor_cores(Hs, P, N, G):
     args0 = [a.clone() if isinstance(a, torch.Tensor) else a for a in args]       # the plain scan updates its state in place
     assert ops.ssd_ok(Hs, P, N, G)
     ops_plain.ssm_scan(*args)
-    # states of 128 or 256 columns: the walk with tcgen05.mma and the state in tensor memory, and the mma.sync walk
-    for mode in ((0, 1) if N in (128, 256) else (0,)):
+    # states of 128 or 256 columns: the walk with tcgen05.mma and the state in tensor memory (the outputs in one
+    # piece, and as two summands of which one is computed on a second stream), and the mma.sync walk
+    for mode, in_two in (((0, False), (0, True), (1, False), (1, True)) if N in (128, 256) else ((0, False), (0, True))):
         gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args0]
         gpu[13] = tuple(t.cuda() for t in args0[13])
+        y_part = torch.full((T, Di), float("nan"), device="cuda") if in_two else None
         ops.ssd_walk_override(mode)
         try:
-            ops.ssm_scan(*gpu)
+            used = ops.ssm_scan(*gpu, y_part=y_part)
             torch.cuda.synchronize()
             ops.check_errors()
         finally:
             ops.ssd_walk_override(0)
+        assert used == (in_two and mode == 0 and N in (128, 256)), "which walks leave two summands"
+        if used:
+            gpu[8] = gpu[8] + y_part
         for i in (4, 8):
             ref, got = args[i].double(), gpu[i].cpu().double()
             # bfloat16 operands carry 8 bits: C B^T, the score matrix, the weighted x and the carried state's copy are

@@ -176,17 +176,18 @@ extern "C" int tlc_rmsnorm(const float* x, const int* rows, const float* w, floa
 // result times out_scale; one block per (row, group).
 template <typename TZ, typename TO>
 __global__ void __launch_bounds__(256)
-gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int ldz,
+gated_rmsnorm_kernel(const float* __restrict__ y, const float* __restrict__ y2, const TZ* __restrict__ z, int ldz,
                                      const float* __restrict__ w, float eps, int Di, int gs, int norm_before_gate,
                                      TO* __restrict__ out, int out_ld, float out_scale) {
-  tlc_pdl(y, z, out);
+  tlc_pdl(y, y2, z, out);
   __shared__ float red[33];
   const int t = blockIdx.x, g = blockIdx.y;
   const float* yr = y + (size_t)t * Di + (size_t)g * gs;
+  const float* y2r = y2 ? y2 + (size_t)t * Di + (size_t)g * gs : nullptr;    // a second summand of the input
   const TZ* zr = z + (size_t)t * ldz + (size_t)g * gs;
   TO* o = out + (size_t)t * out_ld + (size_t)g * gs;
   if (w == nullptr) {                                   // no norm: y * silu(z)
-    for (int d = threadIdx.x; d < gs; d += blockDim.x) o[d] = from_f32<TO>(yr[d] * silu_f(to_f32(zr[d])) * out_scale);
+    for (int d = threadIdx.x; d < gs; d += blockDim.x) o[d] = from_f32<TO>((yr[d] + (y2r ? y2r[d] : 0.f)) * silu_f(to_f32(zr[d])) * out_scale);
     return;
   }
   const float* wg = w + (size_t)g * gs;
@@ -198,7 +199,7 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int 
     for (int i = 0; i < RMS_MAX_PER_THREAD; i++) {          // every load is issued before the first exp
       const int d = threadIdx.x + i * 256;
       gate[i] = d < gs ? to_f32(zr[d]) : 0.f;
-      v[i] = d < gs ? yr[d] : 0.f;
+      v[i] = d < gs ? yr[d] + (y2r ? y2r[d] : 0.f) : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < RMS_MAX_PER_THREAD; i++) {
@@ -216,7 +217,7 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int 
     return;
   }
   for (int d = threadIdx.x; d < gs; d += blockDim.x) {
-    float v = yr[d];
+    float v = yr[d] + (y2r ? y2r[d] : 0.f);
     if (!norm_before_gate) v *= silu_f(to_f32(zr[d]));
     ss += v * v;
   }
@@ -224,7 +225,7 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int 
   const float s = out_scale / sqrtf(ss / (float)gs + eps);
   for (int d = threadIdx.x; d < gs; d += blockDim.x) {
     const float gate = silu_f(to_f32(zr[d]));
-    float v = yr[d];
+    float v = yr[d] + (y2r ? y2r[d] : 0.f);
     v = norm_before_gate ? (v * s * wg[d]) * gate : (v * gate) * s * wg[d];
     o[d] = from_f32<TO>(v);
   }
@@ -234,7 +235,7 @@ gated_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z, int 
 // the weight is fetched before the wait on the previous kernel.
 template <typename TO, int NT, int PT>
 __global__ void __launch_bounds__(NT)
-gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ z, int ldz, const float* __restrict__ w,
+gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ y2, const float* __restrict__ z, int ldz, const float* __restrict__ w,
                          float eps, int Di, int gs, int norm_before_gate, TO* __restrict__ out, int out_ld,
                          float out_scale) {
   asm volatile("griddepcontrol.launch_dependents;");
@@ -247,14 +248,19 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ 
     const int c = threadIdx.x + i * NT;
     wv[i] = c < n4 ? __ldg(reinterpret_cast<const float4*>(w + (size_t)g * gs) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  tlc_wait(y, z, out);
+  tlc_wait(y, y2, z, out);
   const float4* yr = reinterpret_cast<const float4*>(y + (size_t)t * Di + (size_t)g * gs);
+  const float4* y2r = y2 ? reinterpret_cast<const float4*>(y2 + (size_t)t * Di + (size_t)g * gs) : nullptr;
   const float4* zr = reinterpret_cast<const float4*>(z + (size_t)t * ldz + (size_t)g * gs);
 #pragma unroll
   for (int i = 0; i < PT; i++) {
     const int c = threadIdx.x + i * NT;
     v[i] = c < n4 ? yr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     gate[i] = c < n4 ? zr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (y2r != nullptr && c < n4) {                     // the input comes as two summands
+      const float4 u = y2r[c];
+      v[i] = make_float4(v[i].x + u.x, v[i].y + u.y, v[i].z + u.z, v[i].w + u.w);
+    }
   }
   float ss = 0.f;
 #pragma unroll
@@ -280,7 +286,7 @@ gated_rmsnorm_vec_kernel(const float* __restrict__ y, const float* __restrict__ 
   }
 }
 
-extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int ldz, const float* w, float eps, int T,
+extern "C" int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z, int z_dtype, int ldz, const float* w, float eps, int T,
                                  int Di, int n_groups, int norm_before_gate, void* out, int out_dtype, int out_ld,
                                  float out_scale, cudaStream_t stream) {
   if (T == 0) return 0;
@@ -289,10 +295,11 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int
   const int gs = Di / n_groups;
   dim3 grid(T, n_groups);
   if (w != nullptr && z_dtype == TLC_F32 && gs % 4 == 0 && gs <= 16384 && ldz % 4 == 0 && ((uintptr_t)y % 16) == 0 &&
-      ((uintptr_t)z % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0 && out_ld % 4 == 0) {
+      ((uintptr_t)z % 16) == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)out % 16) == 0 && out_ld % 4 == 0 &&
+      ((uintptr_t)y2 % 16) == 0) {
     const int n4 = gs / 4;
 #define TLC_GRMS_LAUNCH(NT, PT)                                                                                         \
-  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_vec_kernel<TO, NT, PT>, grid, dim3(NT), 0, stream, y,        \
+  TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_vec_kernel<TO, NT, PT>, grid, dim3(NT), 0, stream, y, y2,    \
                                                (const float*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out, out_ld, out_scale))
     if (T >= VEC_MANY_ROWS) { TLC_VEC_SHAPES_MANY(n4, TLC_GRMS_LAUNCH) } else { TLC_VEC_SHAPES(n4, TLC_GRMS_LAUNCH) }
 #undef TLC_GRMS_LAUNCH
@@ -300,7 +307,7 @@ extern "C" int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int
     return 0;
   }
   TLC_DISPATCH_DTYPE(z_dtype, TZ, TLC_DISPATCH_DTYPE(out_dtype, TO, tlc_launch(gated_rmsnorm_kernel<TZ, TO>, dim3(grid), dim3(256), 0, stream, 
-      y, (const TZ*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out, out_ld, out_scale)));
+      y, y2, (const TZ*)z, ldz, w, eps, Di, gs, norm_before_gate, (TO*)out, out_ld, out_scale)));
   TLC_CHECK_LAUNCH("gated_rmsnorm");
   return 0;
 }

@@ -7,8 +7,11 @@
 //          + exp(cum_i) * (S_in C_i)                                  "what came before"
 //          + D x_i
 //     S_out = exp(cum_last) S_in + sum_j exp(cum_last - cum_j) dt_j x_j (x) B_j
-// Two kernels:
-//   ssd_cb_kernel    C B^T of every (chunk, group), shared by the group's heads (bfloat16 in and out);
+// The kernels:
+//   ssd_cb_kernel    C B^T of every (chunk, group), shared by the group's heads (bfloat16 in and out); for the walk
+//                    on tcgen05 also B transposed and, in blocks of their own, the rows' decays;
+//   ssd_intra_kernel (with the walk on tcgen05) the first and third terms of y for every (chunk, head) at once:
+//                    they need no state, so they stand beside the walk, on a second stream where there is one;
 //   ssd_walk_kernel  one block per (sequence, head, 32 rows p of the head) walks the sequence's chunks in
 //                    order.  The state S[32, N] lives in the accumulator registers of the last product from
 //                    the slot's state before the first chunk to the slot's state after the last; it is never
@@ -25,9 +28,9 @@
 
 // the same walk with tcgen05.mma and the state in tensor memory (mamba_ssd_tc.cu), for states of 128 or 256 columns
 int tlc_ssd_tc_init();
-int tlc_ssd_tc_run(const __nv_bfloat16* xbc, const float* dt, const float* A, const float* Dskip, const __nv_bfloat16* cb,
+int tlc_ssd_tc_run(const __nv_bfloat16* xbc, const float* row_w, const float* row_e, const float* seg_decay,
                    __nv_bfloat16* bt, float* state, const int* seg_start, const int* seq_seg_start, const int* slots,
-                   const int* start_pos, float* y, int B, int n_seg, int T, int Hs, int P, int N, int G, int Cd,
+                   const int* start_pos, float* y, int add_to_y, int B, int n_seg, int T, int Hs, int P, int N, int G, int Cd,
                    cudaStream_t stream);
 
 namespace {
@@ -78,12 +81,53 @@ __host__ __device__ constexpr int padded(int row_bytes) { return row_bytes + 16;
 // ---- C B^T per (chunk, group): cb[seg, g, i, j] for j <= i (bfloat16) -------------------------------------
 // grid (seg, G, 2), 4 warps: a block owns 64 rows i, warp w the rows [16 w, 16 w + 16) of them and the columns
 // j up to its diagonal; K = N.  With bt (the walk on tcgen05 wants B transposed) the grid has N / 64 more blocks
-// along z, each of which writes bt[seg, g, n, j] = B[row j of the chunk, n] for 64 columns n (zero past the chunk).
+// along z, each of which writes bt[seg, g, n, j] = B[row j of the chunk, n] for 64 columns n (zero past the chunk),
+// and from z_decay on blocks that scan the decays of the chunk's rows for four heads each.
 __global__ void __launch_bounds__(128)
 ssd_cb_kernel(const __nv_bfloat16* __restrict__ xbc, const int* __restrict__ seg_start, __nv_bfloat16* __restrict__ cb,
-              __nv_bfloat16* __restrict__ bt, int Di, int N, int G, int Cd) {
-  tlc_pdl(xbc, cb, bt);
+              __nv_bfloat16* __restrict__ bt, int Di, int N, int G, int Cd, const float* __restrict__ dt,
+              const float* __restrict__ A, int Hs, float* __restrict__ row_w, float* __restrict__ row_e,
+              float* __restrict__ seg_decay, int z_decay) {
+  tlc_pdl(xbc, cb, bt, dt, row_w, row_e, seg_decay);
   extern __shared__ __align__(16) unsigned char ssd_sm[];
+  if (z_decay > 0 && (int)blockIdx.z >= z_decay) {
+    // The rows' decays for the walk, four heads of the group a block (a warp each): for row i of the chunk the
+    // cumulative log2 decay cum_i, then its weight in the chunk's state update w = 2^(total - cum) dt, its factor
+    // e = 2^cum on C S^T, and the chunk's decay 2^total.  A lane takes four consecutive rows.
+    const int seg = blockIdx.x, g = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hg = 4 * ((int)blockIdx.z - z_decay) + warp;
+    if (hg >= Hs / G) return;
+    const int h = g * (Hs / G) + hg;
+    const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
+    const float a_log2 = A[h] * LOG2E;
+    float d[4], c[4];
+    float run = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const int i = 4 * lane + k;
+      d[k] = i < L ? dt[(size_t)(t0 + i) * Hs + h] : 0.f;
+      run += d[k] * a_log2;
+      c[k] = run;
+    }
+    float incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float u = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += u;
+    }
+    const float before = incl - run, total = __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const int i = 4 * lane + k;
+      if (i < L) {
+        const float cum = before + c[k];
+        row_w[(size_t)(t0 + i) * Hs + h] = ex2_quick(total - cum) * d[k];
+        row_e[(size_t)(t0 + i) * Hs + h] = ex2_quick(cum);
+      }
+    }
+    if (lane == 0) seg_decay[(size_t)seg * Hs + h] = exp2f(total);
+    return;
+  }
   if (blockIdx.z >= 2) {
     unsigned short (*tile)[64 + 2] = reinterpret_cast<unsigned short (*)[64 + 2]>(ssd_sm);     // [Q][66]
     const int seg = blockIdx.x, g = blockIdx.y, n0 = (blockIdx.z - 2) * 64;
@@ -161,6 +205,117 @@ ssd_cb_kernel(const __nv_bfloat16* __restrict__ xbc, const int* __restrict__ seg
         const int col = (2 * jp + u) * 8 + 2 * tq;
         *reinterpret_cast<uint32_t*>(out + (size_t)(i_base + gq) * Q + col) = pack_bf16(acc[2 * jp + u][0], acc[2 * jp + u][1]);
         *reinterpret_cast<uint32_t*>(out + (size_t)(i_base + gq + 8) * Q + col) = pack_bf16(acc[2 * jp + u][2], acc[2 * jp + u][3]);
+      }
+    }
+  }
+}
+
+// ---- the part of a chunk's outputs that needs no state: y = M x + D x ------------------------------------
+// M[i, j] = cb[i, j] 2^(cum_i - cum_j) dt_j for j <= i.  grid (seg, Hs, P / PBI), 4 warps: every chunk of every
+// sequence at once, so that the walk that follows has only the state's share on its path.  Warp w owns the 16-row
+// tiles w and 7 - w of the chunk (nine tiles of 16 columns j up to their diagonals between them).  M is never
+// stored: a thread computes the elements of its mma.sync A fragment from C B^T, read in the fragment's own
+// pattern (the matrix of a chunk is 32 KB and shared by all heads of its group), and the cumulative sums; x [j, p]
+// lies in shared memory as it lies in x|B|C, and ldmatrix.trans turns it into B fragments.
+template <int PBI>
+__global__ void __launch_bounds__(128, 6)
+ssd_intra_kernel(const __nv_bfloat16* __restrict__ xbc, const float* __restrict__ dt, const float* __restrict__ A,
+                 const float* __restrict__ Dskip, const __nv_bfloat16* __restrict__ cb, const int* __restrict__ seg_start,
+                 float* __restrict__ y, int Hs, int P, int G, int Cd) {
+  tlc_pdl(xbc, dt, cb, y);
+  constexpr int LDX = padded(PBI * 2);                    // bytes per row of the x tile
+  constexpr int NT = PBI / 8;
+  __shared__ __align__(16) unsigned char xs[Q * LDX];
+  __shared__ __align__(16) float cums[Q], ljs[Q];         // lj = cum_j - log2(dt_j): M = cb 2^(cum_i - lj)
+  __shared__ float wsum[4];
+  const int seg = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PBI;
+  const int g = h / (Hs / G), Di = Hs * P;
+  const int t0 = seg_start[seg], L = seg_start[seg + 1] - t0;
+  if (L <= 0) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+  const __nv_bfloat16* Xg = xbc + (size_t)h * P + p0;
+  const uint32_t xs0 = (uint32_t)__cvta_generic_to_shared(xs);
+  constexpr int pieces = PBI / 8;
+  for (int idx = tid; idx < Q * pieces; idx += 128) {
+    const int r = idx / pieces, c = idx % pieces;
+    const bool in = r < L;
+    cp_async16(xs0 + r * LDX + c * 16, Xg + (size_t)(t0 + (in ? r : 0)) * Cd + c * 8, in);
+  }
+  cp_async_commit();
+  // cumulative log2 decay of the chunk's rows (row = thread)
+  const float dt_reg = tid < L ? dt[(size_t)(t0 + tid) * Hs + h] : 0.f;
+  float v = dt_reg * (A[h] * LOG2E);
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float u = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += u;
+  }
+  if (lane == 31) wsum[warp] = v;
+  __syncthreads();
+  {
+    float off = 0.f;
+#pragma unroll
+    for (int q = 0; q < 3; q++) if (q < warp) off += wsum[q];
+    cums[tid] = v + off;
+    ljs[tid] = v + off - log2f(dt_reg);                  // +inf past the chunk's end (dt = 0): those columns of M are 0
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  const __nv_bfloat16* cbg = cb + (((size_t)seg * G + g) * Q) * Q;
+  const float Dh = Dskip[h];
+#pragma unroll 1
+  for (int half = 0; half < 2; half++) {
+    const int rt = half == 0 ? warp : 7 - warp;
+    const int r0 = 16 * rt;
+    if (r0 >= L) continue;
+    const int ra = r0 + gq, rb = ra + 8;
+    const float ca = cums[ra], cq = cums[rb];
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int k = 0; k < 4; k++) acc[nt][k] = 0.f;
+#pragma unroll 1
+    for (int kt = 0; kt <= rt; kt++) {
+      const int j0 = 16 * kt, ja = j0 + 2 * tq, jb = ja + 8;
+      const uint32_t v0 = __ldg(reinterpret_cast<const uint32_t*>(cbg + (size_t)ra * Q + ja));
+      const uint32_t v1 = __ldg(reinterpret_cast<const uint32_t*>(cbg + (size_t)rb * Q + ja));
+      const uint32_t v2 = __ldg(reinterpret_cast<const uint32_t*>(cbg + (size_t)ra * Q + jb));
+      const uint32_t v3 = __ldg(reinterpret_cast<const uint32_t*>(cbg + (size_t)rb * Q + jb));
+      const float2 la = *reinterpret_cast<const float2*>(ljs + ja), lb = *reinterpret_cast<const float2*>(ljs + jb);
+      const bool diag = kt == rt;
+      auto elems = [&](uint32_t vv, float ci, float2 lj, int row, int col) -> uint32_t {
+        const float2 m = unpack_bf16(vv);
+        float e0 = m.x * ex2_quick(ci - lj.x), e1 = m.y * ex2_quick(ci - lj.y);
+        if (diag) {
+          if (col > row) e0 = 0.f;
+          if (col + 1 > row) e1 = 0.f;
+        }
+        return pack_bf16(e0, e1);
+      };
+      const uint32_t a0 = elems(v0, ca, la, ra, ja), a1 = elems(v1, cq, la, rb, ja);
+      const uint32_t a2 = elems(v2, ca, lb, ra, jb), a3 = elems(v3, cq, lb, rb, jb);
+      const uint32_t b_addr = xs0 + (j0 + (lane & 15)) * LDX + (lane >> 4) * 16;
+#pragma unroll
+      for (int np = 0; np < NT / 2; np++) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(b_addr + np * 32, b0, b1, b2, b3);
+        mma_bf16(acc[2 * np], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      const int col = 8 * nt + 2 * tq;
+      if (ra < L) {
+        const float2 x2 = unpack_bf16(*reinterpret_cast<const uint32_t*>(xs + ra * LDX + col * 2));
+        *reinterpret_cast<float2*>(y + (size_t)(t0 + ra) * Di + (size_t)h * P + p0 + col) =
+            make_float2(fmaf(Dh, x2.x, acc[nt][0]), fmaf(Dh, x2.y, acc[nt][1]));
+      }
+      if (rb < L) {
+        const float2 x2 = unpack_bf16(*reinterpret_cast<const uint32_t*>(xs + rb * LDX + col * 2));
+        *reinterpret_cast<float2*>(y + (size_t)(t0 + rb) * Di + (size_t)h * P + p0 + col) =
+            make_float2(fmaf(Dh, x2.x, acc[nt][2]), fmaf(Dh, x2.y, acc[nt][3]));
       }
     }
   }
@@ -502,30 +657,75 @@ extern "C" int tlc_ssd_ok(int Hs, int P, int N, int G, int Cd) {
          Hs <= 65535 && G <= 65535 && P / PB <= 65535;
 }
 
-// floats of scratch for n_seg chunks: C B^T [128, 128] and B^T [N, 128] of every (chunk, group) in bfloat16
+// floats of scratch for n_seg chunks of T rows in all: per row and head the weight of the row in its chunk's state
+// update and its factor on C S^T, per chunk and head the chunk's decay; then C B^T [128, 128] and B^T [N, 128] of
+// every (chunk, group) in bfloat16
+static long long ssd_row_floats(int n_seg, int T, int Hs) { return (2LL * T * Hs + (long long)n_seg * Hs + 3) / 4 * 4; }
 extern "C" long long tlc_ssd_scratch_floats(int n_seg, int T, int Hs, int P, int N, int G) {
-  return ((long long)n_seg * G * Q * (Q + N) + 1) / 2;
+  return ssd_row_floats(n_seg, T, Hs) + ((long long)n_seg * G * Q * (Q + N) + 1) / 2;
 }
 
+// y_part, aux: with the walk on tcgen05 the part of the outputs that needs no state (M x + D x) goes to y_part
+// [T, Hs*P] and only the state's share to y; *used_part = 1 then tells the caller to add the two.  That part
+// does not stand on the walk's path: with a second stream `aux` (not while capturing) it runs there, beside the
+// walk, and `stream` waits for it before this function returns.  Without y_part everything is added up in y.
 extern "C" int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A, const float* Dskip, float* state,
                                 float* scratch, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
-                                const int* slots, const int* start_pos, float* y, int B, int n_seg, int T, int Hs, int P,
-                                int N, int G, int Cd, cudaStream_t stream) {
+                                const int* slots, const int* start_pos, float* y, float* y_part, int* used_part, int B,
+                                int n_seg, int T, int Hs, int P, int N, int G, int Cd, cudaStream_t stream,
+                                cudaStream_t aux) {
+  if (used_part) *used_part = 0;
   if (B == 0 || n_seg == 0) return 0;
   TLC_REQUIRE(tlc_ssd_ok(Hs, P, N, G, Cd), "ssm_scan(chunked, tensor cores): sizes Hs=%d P=%d N=%d G=%d Cd=%d are not built",
               Hs, P, N, G, Cd);
   TLC_REQUIRE(((uintptr_t)xbc % 16) == 0 && ((uintptr_t)scratch % 16) == 0 && ((uintptr_t)state % 8) == 0 &&
-              ((uintptr_t)y % 8) == 0, "ssm_scan(chunked, tensor cores): misaligned buffers");
+              ((uintptr_t)y % 8) == 0 && ((uintptr_t)y_part % 8) == 0, "ssm_scan(chunked, tensor cores): misaligned buffers");
   const __nv_bfloat16* x = (const __nv_bfloat16*)xbc;
-  __nv_bfloat16* cb = (__nv_bfloat16*)scratch;
+  float* row_w = scratch;                         // [T, Hs], [T, Hs], [n_seg, Hs]: the rows' decays, for the walk
+  float* row_e = row_w + (size_t)T * Hs;
+  float* seg_decay = row_e + (size_t)T * Hs;
+  __nv_bfloat16* cb = (__nv_bfloat16*)(scratch + ssd_row_floats(n_seg, T, Hs));
   const bool tc = (N == 128 || N == 256) && g_ssd_walk == 0;
   __nv_bfloat16* bt = tc ? cb + (size_t)n_seg * G * Q * Q : nullptr;
-  tlc_launch(ssd_cb_kernel, dim3(n_seg, G, 2 + (tc ? N / 64 : 0)), dim3(128), cb_smem(N), stream, x, seg_start, cb, bt, Hs * P,
-             N, G, Cd);
+  const int z_cb = 2 + (tc ? N / 64 : 0), z_decay = tc ? (Hs / G + 3) / 4 : 0;
+  tlc_launch(ssd_cb_kernel, dim3(n_seg, G, z_cb + z_decay), dim3(128), cb_smem(N), stream, x, seg_start, cb, bt, Hs * P, N, G, Cd,
+             dt, A, Hs, row_w, row_e, seg_decay, tc ? z_cb : 0);
   TLC_CHECK_LAUNCH("ssm_scan(C B^T)");
-  if (tc)
-    return tlc_ssd_tc_run(x, dt, A, Dskip, cb, bt, state, seg_start, seq_seg_start, slots, start_pos, y, B, n_seg, T, Hs, P, N,
-                          G, Cd, stream);
+  if (tc) {
+    const bool apart = y_part != nullptr && used_part != nullptr;
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(stream, &capturing);
+    const bool beside = apart && aux != nullptr && aux != stream && capturing == cudaStreamCaptureStatusNone;
+    cudaStream_t s_part = beside ? aux : stream;
+    cudaEvent_t e_cb = nullptr, e_part = nullptr;
+    if (beside) {
+      if (cudaEventCreateWithFlags(&e_cb, cudaEventDisableTiming) != cudaSuccess ||
+          cudaEventCreateWithFlags(&e_part, cudaEventDisableTiming) != cudaSuccess)
+        return tlc_fail(-3, "ssm_scan: cannot create events");
+      cudaEventRecord(e_cb, stream);
+      cudaStreamWaitEvent(aux, e_cb, 0);
+    }
+    float* y_free = apart ? y_part : y;            // where M x + D x goes
+    // every chunk's outputs as far as they need no state
+    if (P % 64 == 0)
+      tlc_launch_as(!beside, ssd_intra_kernel<64>, dim3(n_seg, Hs, P / 64), dim3(128), 0, s_part, x, dt, A, Dskip, cb, seg_start, y_free,
+                    Hs, P, G, Cd);
+    else
+      tlc_launch_as(!beside, ssd_intra_kernel<32>, dim3(n_seg, Hs, P / 32), dim3(128), 0, s_part, x, dt, A, Dskip, cb, seg_start, y_free,
+                    Hs, P, G, Cd);
+    TLC_CHECK_LAUNCH("ssm_scan(chunk outputs without the state)");
+    if (beside) cudaEventRecord(e_part, aux);
+    // the walk: the state's share, written to y (added to what is there when the other part went there too)
+    int rc = tlc_ssd_tc_run(x, row_w, row_e, seg_decay, bt, state, seg_start, seq_seg_start, slots, start_pos, y, apart ? 0 : 1, B,
+                            n_seg, T, Hs, P, N, G, Cd, stream);
+    if (beside) {
+      cudaStreamWaitEvent(stream, e_part, 0);
+      cudaEventDestroy(e_cb);                       // destroyed once the work that uses them is done
+      cudaEventDestroy(e_part);
+    }
+    if (rc == 0 && apart) *used_part = 1;
+    return rc;
+  }
   switch (N / 64) {
     case 1: return launch_walk<1>(x, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);
     case 2: return launch_walk<2>(x, dt, A, Dskip, cb, state, seg_start, seq_seg_start, slots, start_pos, y, B, Hs, P, G, Cd, stream);

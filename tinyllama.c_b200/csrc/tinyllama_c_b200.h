@@ -66,9 +66,9 @@ int tlc_embed(const int* tokens, const void* table, int table_dtype, int T, int 
 /* out[r] = x[rows ? rows[r] : r] / sqrt(mean(x^2) + eps) * w;  x float [*, D], out [R, D] of out_dtype. */
 int tlc_rmsnorm(const float* x, const int* rows, const float* w, float eps, int R, int D, void* out,
                 int out_dtype, cudaStream_t stream);
-/* Gate y by silu(z) and RMS-normalise per group, in either order; w NULL: gate only.  out [T, Di] with
- * row stride out_ld, multiplied by out_scale. */
-int tlc_gated_rmsnorm(const float* y, const void* z, int z_dtype, int ldz, const float* w, float eps, int T,
+/* Gate y (+ y2, where y2 is not NULL: an input that comes as two summands) by silu(z) and RMS-normalise per group,
+ * in either order; w NULL: gate only.  out [T, Di] with row stride out_ld, multiplied by out_scale. */
+int tlc_gated_rmsnorm(const float* y, const float* y2, const void* z, int z_dtype, int ldz, const float* w, float eps, int T,
                       int Di, int n_groups, int norm_before_gate, void* out, int out_dtype, int out_ld,
                       float out_scale, cudaStream_t stream);
 /* out[T, F] = silu(gate) * up; gu holds gate | up as halves, or (interleave) 8 gates then their 8 ups. */
@@ -186,10 +186,14 @@ int tlc_ssd_ok(int Hs, int P, int N, int G, int Cd);
  * or 256 columns) and mma.sync with the state in registers elsewhere; 1 = always the latter. */
 void tlc_ssd_walk_override(int mode);
 long long tlc_ssd_scratch_floats(int n_seg, int T, int Hs, int P, int N, int G);
+/* y_part [T, Hs*P] and used_part may be NULL.  Where the walk runs on tcgen05 and they are given, the outputs come as
+ * two summands: what needs no state (M x + D x) in y_part, the state's share in y, and *used_part = 1.  With a second
+ * stream `aux` (NULL: none) the first summand is computed there, beside the walk; `stream` has waited for it when the
+ * call returns.  Otherwise *used_part = 0 and y holds the outputs. */
 int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A, const float* Dskip, float* state,
                      float* scratch, const int* seg_start, const int* seg_seq, const int* seq_seg_start,
-                     const int* slots, const int* start_pos, float* y, int B, int n_seg, int T, int Hs, int P,
-                     int N, int G, int Cd, cudaStream_t stream);
+                     const int* slots, const int* start_pos, float* y, float* y_part, int* used_part, int B, int n_seg,
+                     int T, int Hs, int P, int N, int G, int Cd, cudaStream_t stream, cudaStream_t aux);
 
 /* ---- sampling (sampling.cu) ------------------------------------------------------------------------ */
 /* out[r] = first index of the maximum of logits[r].  work: NULL (one block a row), or 12 * R bytes, 8-byte

@@ -42,7 +42,7 @@ _SIGNATURES = {
     "tlc_selftest_bounded_wait": (_i, [_vp]),
     "tlc_embed": (_i, [_vp, _vp, _i, _i, _i, _i, _f, _vp, _vp]),
     "tlc_rmsnorm": (_i, [_vp, _vp, _vp, _f, _i, _i, _vp, _i, _vp]),
-    "tlc_gated_rmsnorm": (_i, [_vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _i, _f, _vp]),
+    "tlc_gated_rmsnorm": (_i, [_vp, _vp, _vp, _i, _i, _vp, _f, _i, _i, _i, _i, _vp, _i, _i, _f, _vp]),
     "tlc_swiglu": (_i, [_vp, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "tlc_gather_rows": (_i, [_vp, _vp, _i, _i, _vp, _vp]),
     "tlc_linear": (_i, [_vp, _i, _i, _vp, _i, _i, _vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
@@ -80,8 +80,8 @@ _SIGNATURES = {
     "tlc_ssd_ok": (_i, [_i, _i, _i, _i, _i]),
     "tlc_ssd_walk_override": (None, [_i]),
     "tlc_ssd_scratch_floats": (_ll, [_i, _i, _i, _i, _i, _i]),
-    "tlc_ssm_scan_ssd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i,
-                              _vp]),
+    "tlc_ssm_scan_ssd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
+                              _i, _i, _vp, _vp]),
     "tlc_argmax": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "tlc_sample": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _f, _f, _f, _i, _f, _f, _vp, _vp]),
     "tlc_attention_decode_no_alloc": (_i, [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
@@ -226,18 +226,22 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 
 
 def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: Optional[torch.Tensor], eps: float, n_groups: int,
-                  norm_before_gate: bool, out: torch.Tensor, out_scale: float = 1.0) -> None:
+                  norm_before_gate: bool, out: torch.Tensor, out_scale: float = 1.0,
+                  y_add: Optional[torch.Tensor] = None) -> None:
     """Gate y by silu(z) and RMS-normalise per group (either order); weight None = gate only.  The
-    result is multiplied by out_scale; out [T, Di] may be a range of the columns of a wider buffer."""
-    _gpu(y, z, weight, out)
+    result is multiplied by out_scale; out [T, Di] may be a range of the columns of a wider buffer.
+    y_add: a second summand of the input (the scan of prompts leaves its outputs as two), same shape as y."""
+    _gpu(y, z, weight, out, y_add)
     T, Di = y.shape
     if y.dtype != torch.float32 or not y.is_contiguous():
         raise KernelError("gated_rmsnorm: y must be contiguous float32 [T, Di]")
+    if y_add is not None and (y_add.dtype != torch.float32 or not y_add.is_contiguous() or y_add.shape != y.shape):
+        raise KernelError("gated_rmsnorm: y_add must be contiguous float32 of y's shape")
     out_ld = _out_rows(out, T, Di, "gated_rmsnorm")
     if z.shape != y.shape:
         raise KernelError("gated_rmsnorm: gate and input differ in shape")
     _f32vec(weight, Di, "gated_rmsnorm weight")
-    _call("tlc_gated_rmsnorm", y.data_ptr(), z.data_ptr(), dtype_code(z.dtype), _rows(z, "gate"), _p(weight),
+    _call("tlc_gated_rmsnorm", y.data_ptr(), _p(y_add), z.data_ptr(), dtype_code(z.dtype), _rows(z, "gate"), _p(weight),
           float(eps), T, Di, int(n_groups), int(bool(norm_before_gate)), out.data_ptr(), dtype_code(out.dtype),
           out_ld, float(out_scale), _stream())
 
@@ -562,16 +566,32 @@ def ssd_ok(Hs: int, P: int, N: int, G: int) -> bool:
     return bool(not DISABLE_SSD and library().tlc_ssd_ok(Hs, P, N, G, Hs * P + 2 * G * N))
 
 
+_aux_streams: dict = {}
+
+
+def _aux_stream(device) -> "torch.cuda.Stream":
+    """A second stream per device and current stream, for work that runs beside a kernel chain of the current one."""
+    key = (torch.device(device).index, torch.cuda.current_stream(device).cuda_stream)
+    if key not in _aux_streams:
+        if len(_aux_streams) > 64:
+            _aux_streams.clear()
+        _aux_streams[key] = torch.cuda.Stream(device=device)
+    return _aux_streams[key]
+
+
 def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch.Tensor, state: torch.Tensor,
              cu_seqlens: torch.Tensor, slots: torch.Tensor, start_pos: torch.Tensor, y: torch.Tensor, Hs: int, P: int,
-             N: int, G: int, chunks=None, A: Optional[torch.Tensor] = None) -> None:
+             N: int, G: int, chunks=None, A: Optional[torch.Tensor] = None, y_part: Optional[torch.Tensor] = None) -> bool:
     """Selective scan of every sequence in order, from its slot's state (zero at position 0);
     state [n_slots, Hs, P, N] float32 is updated in place; y [T, Hs*P] float32 is before gating.
     chunks = (seg_start [n+1], seg_seq [n], seq_seg_start [B+1]) cuts the sequences into
     chunks that run in parallel (same result up to rounding).  With a bfloat16 xbc and A (the per-head
     decay rate, dA = exp(dt * A)) the chunks, of at most 128 rows, run in matrix form on the tensor cores
-    with bfloat16 operands (see ssd_ok for the sizes); every 32-bit run passes a float32 xbc."""
-    _gpu(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y)
+    with bfloat16 operands (see ssd_ok for the sizes); every 32-bit run passes a float32 xbc.
+    y_part (float32, y's shape; matrix form only): the outputs may then come as two summands, what needs no state in
+    y_part (computed on a second stream beside the walk over the chunks) and the state's share in y; returns True
+    if they did (the caller adds them), False if y holds the outputs."""
+    _gpu(xbc, dt, dA, Dskip, state, cu_seqlens, slots, start_pos, y, y_part)
     T, Cd = xbc.shape
     if Cd != Hs * P + 2 * G * N:
         raise KernelError("ssm_scan: xbc width does not match Hs*P + 2*G*N")
@@ -595,18 +615,24 @@ def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dA: torch.Tensor, Dskip: torch
         if matrix_form:
             _f32vec(A, Hs, "A")
             scratch = torch.empty(lib.tlc_ssd_scratch_floats(n_seg, T, Hs, P, N, G), dtype=torch.float32, device=xbc.device)
+            if y_part is not None and (y_part.dtype != torch.float32 or not y_part.is_contiguous() or y_part.shape != y.shape):
+                raise KernelError("ssm_scan: y_part must be contiguous float32 of y's shape")
+            used = ctypes.c_int(0)
+            aux = _aux_stream(xbc.device).cuda_stream if y_part is not None and not torch.cuda.is_current_stream_capturing() else None
             _call("tlc_ssm_scan_ssd", xbc.data_ptr(), dt.data_ptr(), A.data_ptr(), Dskip.data_ptr(), state.data_ptr(),
                   scratch.data_ptr(), seg_start.data_ptr(), seg_seq.data_ptr(), seq_seg_start.data_ptr(),
-                  slots.data_ptr(), start_pos.data_ptr(), y.data_ptr(), slots.numel(), n_seg, T, Hs, P, N, G, Cd, _stream())
-            return
+                  slots.data_ptr(), start_pos.data_ptr(), y.data_ptr(), _p(y_part), ctypes.byref(used), slots.numel(), n_seg,
+                  T, Hs, P, N, G, Cd, _stream(), aux)
+            return bool(used.value)
         scratch = torch.empty(n_seg * Hs * (P * N + 1), dtype=torch.float32, device=xbc.device)
         _call("tlc_ssm_scan_chunked", xbc.data_ptr(), dt.data_ptr(), dA.data_ptr(), Dskip.data_ptr(), state.data_ptr(),
               scratch.data_ptr(), seg_start.data_ptr(), seg_seq.data_ptr(), seq_seg_start.data_ptr(), slots.data_ptr(),
               start_pos.data_ptr(), y.data_ptr(), slots.numel(), n_seg, Hs, P, N, G, Cd, _stream())
-        return
+        return False
     _call("tlc_ssm_scan", xbc.data_ptr(), dt.data_ptr(), dA.data_ptr(), Dskip.data_ptr(), state.data_ptr(),
           cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), y.data_ptr(), slots.numel(), Hs, P, N, G, Cd,
           _stream())
+    return False
 
 
 # ---- sampling -------------------------------------------------------------------------------------

@@ -135,11 +135,14 @@ class Mamba2Mixer(Part):
                        step.cu_seqlens, step.row_seq, step.slots, step.start_pos, xbc, dt, dA,
                        step.max_new == 1, self.dtype == torch.bfloat16)
         y = new((T, self.Di), f32)
-        ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs, self.P,
-                     self.N, self.G, chunks, self.A if matrix_form else None)
+        # in matrix form the outputs may come as two summands, the one that needs no state computed beside the walk
+        # over the chunks; the gated norm adds them
+        y_part = new((T, self.Di), f32) if matrix_form else None
+        in_two = ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs,
+                              self.P, self.N, self.G, chunks, self.A if matrix_form else None, y_part)
         gated = out if out is not None else new((T, self.Di), self.dtype)
         ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated,
-                          out_scale)
+                          out_scale, y_part if in_two else None)
         return gated
 
     def output(self, gated: torch.Tensor, residual: torch.Tensor) -> None:
