@@ -697,11 +697,15 @@ extern "C" int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A
     cudaStreamIsCapturing(stream, &capturing);
     const bool beside = apart && aux != nullptr && aux != stream && capturing == cudaStreamCaptureStatusNone;
     cudaStream_t s_part = beside ? aux : stream;
-    cudaEvent_t e_cb = nullptr, e_part = nullptr;
+    // the two events of a calling thread are made once: a record overwrites an event's last state, and each wait
+    // below follows its record in this thread's program order
+    static thread_local cudaEvent_t e_cb = nullptr, e_part = nullptr;
     if (beside) {
-      if (cudaEventCreateWithFlags(&e_cb, cudaEventDisableTiming) != cudaSuccess ||
-          cudaEventCreateWithFlags(&e_part, cudaEventDisableTiming) != cudaSuccess)
+      if (e_cb == nullptr && (cudaEventCreateWithFlags(&e_cb, cudaEventDisableTiming) != cudaSuccess ||
+                              cudaEventCreateWithFlags(&e_part, cudaEventDisableTiming) != cudaSuccess)) {
+        e_cb = e_part = nullptr;
         return tlc_fail(-3, "ssm_scan: cannot create events");
+      }
       cudaEventRecord(e_cb, stream);
       cudaStreamWaitEvent(aux, e_cb, 0);
     }
@@ -718,11 +722,7 @@ extern "C" int tlc_ssm_scan_ssd(const void* xbc, const float* dt, const float* A
     // the walk: the state's share, written to y (added to what is there when the other part went there too)
     int rc = tlc_ssd_tc_run(x, row_w, row_e, seg_decay, bt, state, seg_start, seq_seg_start, slots, start_pos, y, apart ? 0 : 1, B,
                             n_seg, T, Hs, P, N, G, Cd, stream);
-    if (beside) {
-      cudaStreamWaitEvent(stream, e_part, 0);
-      cudaEventDestroy(e_cb);                       // destroyed once the work that uses them is done
-      cudaEventDestroy(e_part);
-    }
+    if (beside) cudaStreamWaitEvent(stream, e_part, 0);
     if (rc == 0 && apart) *used_part = 1;
     return rc;
   }

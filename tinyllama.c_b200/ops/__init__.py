@@ -138,7 +138,16 @@ def _call(name: str, *args) -> None:
         raise KernelError(f"{name}: {lib.tlc_last_error().decode()}")
 
 
+# The current stream's handle is asked for by every call; torch.cuda.current_stream() builds a Stream object each
+# time (several microseconds: a prompt step makes hundreds of calls and is bound by the host up to about 2,000
+# tokens), torch's own raw query does not.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_get_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> int:
+    if _raw_stream is not None and _get_device is not None:
+        return _raw_stream(_get_device())
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -86,11 +86,15 @@ class Block(Part):
         main = torch.cuda.current_stream()
         if not hasattr(self, "_side"):
             self._side = [torch.cuda.Stream(device=x32.device) for _ in self.mixers[1:]]
+            # events are made once: a record overwrites the event's last state, and every wait of this block follows
+            # its record in program order
+            self._fork = torch.cuda.Event()
+            self._done = [torch.cuda.Event() for _ in self.mixers]
         # the mixer with the longest chain of kernels stays on the current stream, where every
         # kernel follows its predecessor by a programmatic edge
         lengths = [int(getattr(m, "single_token_launches", 1)) for m in self.mixers]
         here = _MAIN_MIXER if _MAIN_MIXER is not None else lengths.index(max(lengths))
-        fork = torch.cuda.Event()
+        fork = self._fork
         fork.record(main)
         acts, done = [None] * len(self.mixers), [None] * len(self.mixers)
         joint, views = self._joint_activations(x32)
@@ -102,7 +106,7 @@ class Block(Part):
             side.wait_event(fork)
             with torch.cuda.stream(side):
                 acts[i] = self._mix(i, part, step, cache, views[i])
-                done[i] = torch.cuda.Event()
+                done[i] = self._done[i]
                 done[i].record(side)
         acts[here] = self._mix(here, parts[here], step, cache, views[here])
         for i, m in enumerate(self.mixers):          # outputs in the mixers' order, whatever ran where
