@@ -191,6 +191,37 @@ def test_linear_with_the_k_steps_of_a_tile_shared_among_blocks(splits):
         ops.linear_split_override(0)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 40, 2056), (8, 2048, 4096), (5, 67, 4104), (16, 130, 1096), (13, 2000, 3000), (3, 16, 8200)])
+def test_linear_of_few_rows_with_k_halved_between_two_blocks(M, N, K):
+    """Few rows times a matrix with fewer 16-column tiles than the GPU has SMs and more than one round of K:
+    two blocks of a cluster take one half of K each and the second hands its sums to the first through
+    distributed shared memory.  Odd numbers of K-steps, a last tile past N, one and two groups of eight rows;
+    plain, into a 32-bit sum and with column scales; twice each, and the same bits both times."""
+    g = gen(35)
+    a = rnd(g, M, K, dtype=torch.bfloat16)
+    w = rnd(g, N, K, dtype=torch.bfloat16, scale=1 / math.sqrt(K))
+    cs, cb = 1 + rnd(g, N, scale=0.3), rnd(g, N)
+    for accumulate, scale, bias, o_dt in ((True, None, None, torch.float32), (False, cs, cb, torch.bfloat16),
+                                          (False, None, None, torch.float32)):
+        out_cpu = rnd(g, M, N, dtype=o_dt)
+        ops_plain.linear(a, w, ref := out_cpu.clone(), scale, bias, accumulate)
+        outs = []
+        for paired in (True, True, False):
+            try:
+                ops.linear_skinny_pairs(paired)
+                out = out_cpu.cuda()
+                ops.linear(a.cuda(), w.cuda(), out, None if scale is None else scale.cuda(),
+                           None if bias is None else bias.cuda(), accumulate)
+                torch.cuda.synchronize()
+            finally:
+                ops.linear_skinny_pairs(True)
+            ops.check_errors()
+            err = (ref.double() - out.cpu().double()).abs().max().item()
+            assert err <= TOL[o_dt] * ref.double().abs().max().item(), f"{M}x{N}x{K}, paired {paired}: {err}"
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1]), "two runs of the same product differ"
+
+
 @pytest.mark.parametrize("M,N,K", [(300, 128, 64), (129, 257, 200), (2048, 384, 512), (100, 1000, 520), (256, 512, 4096),
                                    (1000, 520, 264), (513, 776, 1096)])
 def test_linear_on_pairs_of_blocks(M, N, K):

@@ -204,22 +204,31 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
 }
 
 constexpr int SK_WARPS = 16;          // warps per block, each with its own slices of K
+static int g_skinny_pairs = 1;        // 0: never two blocks a tile (for comparisons)
 
 // With SWIGLU a block's 16 weight rows are 8 gate rows followed by their 8 up rows, and the block
 // writes silu(gate) * up for its 8 features (out is [M, N/2]).
-template <typename TO, int MG, int U, bool SWIGLU>
+//
+// With PAIR two blocks of a cluster share a tile of 16 columns, each with one half of K: a matrix with few
+// rows (N / 16 tiles for 148 SMs that hold two blocks each) and a long K otherwise needs several trips to
+// memory on half of the SMs' load slots.  The second block leaves its sums in the first block's shared memory
+// (distributed shared memory); the first adds them to its own, always in this order, and stores.
+template <typename TO, int MG, int U, bool SWIGLU, bool PAIR>
 __global__ void __launch_bounds__(SK_WARPS * 32, ((MG == 1 && U <= 4) || (MG == 2 && U <= 2) || (MG == 4 && U == 1)) ? 2 : 1)
 gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_bfloat16* __restrict__ w, int ldw,
                        TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                        const float* __restrict__ colbias, int accumulate, int M, int N, int K) {
+  static_assert(!(PAIR && SWIGLU), "the paired form has no SwiGLU epilogue");
   // The weights do not depend on the previous kernel of the stream, the activations do: when this
   // kernel is launched early (programmatic dependent launch), the first round of weight loads is
   // in flight while the previous kernel is still finishing; only then does it wait for it.
   asm volatile("griddepcontrol.launch_dependents;");
   __shared__ float red[SK_WARPS][MG < 4 ? MG : 4][32][4];
+  __shared__ float other[PAIR ? MG * 128 : 1];                       // the second block's sums, by output value
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int n0 = blockIdx.x * 16;
+  const int rank = PAIR ? (int)(blockIdx.x & 1) : 0;                 // clusters are pairs of consecutive blocks
+  const int n0 = (PAIR ? blockIdx.x >> 1 : blockIdx.x) * 16;
   const int r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);     // clamped rows are never stored
   const uint4* w0 = reinterpret_cast<const uint4*>(w + (size_t)r0 * ldw);
   const uint4* w1 = reinterpret_cast<const uint4*>(w + (size_t)r1 * ldw);
@@ -229,9 +238,12 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
   const int K8 = K >> 3;                                             // 16-byte chunks per row
-  const int n_steps = (K8 + 3) >> 2;                                 // a step is 4 chunks = 32 values of K
+  const int all_steps = (K8 + 3) >> 2;                               // a step is 4 chunks = 32 values of K
+  const int half_steps = (all_steps + 1) >> 1;
+  const int s_first = PAIR ? rank * half_steps : 0;                  // this block's steps
+  const int n_steps = PAIR ? min(all_steps, s_first + half_steps) : all_steps;
   // all of a warp's loads of one round are issued before the first multiply: one trip to memory
-  for (int s0 = warp * U; s0 < n_steps; s0 += SK_WARPS * U) {
+  for (int s0 = s_first + warp * U; s0 < n_steps; s0 += SK_WARPS * U) {
     uint4 wa[U], wb[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
@@ -240,7 +252,7 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
       wa[u] = in ? __ldg(w0 + c) : make_uint4(0, 0, 0, 0);
       wb[u] = in ? __ldg(w1 + c) : make_uint4(0, 0, 0, 0);
     }
-    if (s0 == warp * U) tlc_wait(a, out);                                      // first round only
+    if (s0 == s_first + warp * U) tlc_wait(a, out);                            // first round only
     // the activations of every row group, too, before the first multiply
     uint4 xq[MG][U];
 #pragma unroll
@@ -262,7 +274,7 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
       }
     }
   }
-  if (warp * U >= n_steps) tlc_wait(a, out);                                   // warps without a round of their own
+  if (s_first + warp * U >= n_steps) tlc_wait(a, out);                         // warps without a round of their own
   // the warps' partial sums meet in shared memory, at most four row groups at a time
   constexpr int RG = MG < 4 ? MG : 4;
 #pragma unroll 1
@@ -292,11 +304,28 @@ gemm_skinny_mma_kernel(const __nv_bfloat16* __restrict__ a, int lda, const __nv_
       continue;
     }
     // one thread per output value: sum the warps' partial sums in warp order, epilogue, store
+    if constexpr (PAIR) {
+      if (rank == 1) {
+        for (int idx = threadIdx.x; idx < RG * 128; idx += blockDim.x) {
+          const int mg = idx >> 7, ln = (idx & 127) >> 2, j = idx & 3;
+          float v = 0.f;
+#pragma unroll
+          for (int ww = 0; ww < SK_WARPS; ww++) v += red[ww][mg][ln][j];
+          uint32_t dst;                                              // the same word of block 0's `other`
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(dst) : "r"((uint32_t)__cvta_generic_to_shared(&other[g0 * 128 + idx])), "r"(0));
+          asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(v) : "memory");
+        }
+      }
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+      if (rank == 1) continue;
+    }
     for (int idx = threadIdx.x; idx < RG * 128; idx += blockDim.x) {
       const int mg = idx >> 7, ln = (idx & 127) >> 2, j = idx & 3;
       float v = 0.f;
 #pragma unroll
       for (int ww = 0; ww < SK_WARPS; ww++) v += red[ww][mg][ln][j];
+      if constexpr (PAIR) v += other[g0 * 128 + idx];
       const int n = n0 + (ln >> 2) + (j >= 2 ? 8 : 0);
       const int m = (g0 + mg) * 8 + 2 * (ln & 3) + (j & 1);
       if (n < N && m < M) {
@@ -316,14 +345,41 @@ static void launch_skinny_mg(const __nv_bfloat16* a, int lda, const __nv_bfloat1
                              cudaStream_t stream) {
   const unsigned blocks = (unsigned)((N + 15) / 16);
   const int n_steps = ((K >> 3) + 3) >> 2;
+  if constexpr (!SWIGLU) {
+    // few tiles and more than one round of K: two blocks a tile, each with half of K
+    static int sms = 0;
+    if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+    const int per_round = SK_WARPS * (MG == 2 ? 2 : 4);
+    if (g_skinny_pairs && MG <= 2 && (int)blocks <= sms && n_steps > per_round) {     // MG <= 2: two blocks fit on an SM
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * blocks);
+      cfg.blockDim = dim3(SK_WARPS * 32);
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = g_tlc_pdl ? 2 : 1;
+      const int half = (n_steps + 1) / 2;
+      if (half <= SK_WARPS * 2 || MG == 2)
+        cudaLaunchKernelEx(&cfg, gemm_skinny_mma_kernel<TO, MG, 2, false, true>, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+      else
+        cudaLaunchKernelEx(&cfg, gemm_skinny_mma_kernel<TO, MG, 4, false, true>, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+      return;
+    }
+  }
   // U steps per warp and round: with one row group and U <= 4, or two and U = 2, two blocks fit on an SM
   // (a warp holds the weights and the activations of a round in registers)
   if (MG == 4 && blocks > 296)      // 17..32 rows, many row tiles: one step a round keeps two blocks on an SM
-    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 1, SWIGLU>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 1, SWIGLU, false>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
   else if (n_steps <= SK_WARPS * 2 || MG == 2)
-    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 2, SWIGLU>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 2, SWIGLU, false>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
   else
-    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 4, SWIGLU>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
+    tlc_launch(gemm_skinny_mma_kernel<TO, MG, 4, SWIGLU, false>, dim3(blocks), dim3(SK_WARPS * 32), 0, stream, a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K);
 }
 
 template <typename TO, bool SWIGLU>
@@ -354,6 +410,8 @@ extern "C" int tlc_linear_skinny(const void* a, int lda, const void* w, int ldw,
     return launch_skinny_mma<__nv_bfloat16, false>(a, lda, w, ldw, out, ldo, colscale, colbias, accumulate, M, N, K, stream);
   return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
 }
+
+extern "C" void tlc_linear_skinny_pairs(int on) { g_skinny_pairs = on; }
 
 extern "C" int tlc_linear_skinny_swiglu(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
                                         const float* colscale, const float* colbias, int M, int N, int K,

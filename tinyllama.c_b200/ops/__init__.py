@@ -55,6 +55,7 @@ _SIGNATURES = {
     "tlc_linear_tile_override": (None, [_i]),
     "tlc_linear_split_override": (None, [_i]),
     "tlc_linear_pair_override": (None, [_i]),
+    "tlc_linear_skinny_pairs": (None, [_i]),
     "tlc_linear_pairs": (_i, []),
     "tlc_rope_kv_store": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                _i, _i, _vp]),
@@ -294,6 +295,12 @@ def linear_pair_override(mode: int) -> None:
     """Pairs of blocks on 256 x 256 tiles in the tensor-core product: 0 where they pay, 1 never, 2 wherever
     the GPU can run them; for tests."""
     library().tlc_linear_pair_override(int(mode))
+
+
+def linear_skinny_pairs(on: bool) -> None:
+    """Whether the few-row product may give a tile of 16 columns to two blocks of a cluster, each with one half
+    of K (it does where the matrix has fewer tiles than the GPU has SMs); for tests and comparisons."""
+    library().tlc_linear_skinny_pairs(int(bool(on)))
 
 
 def linear_pairs() -> int:
