@@ -191,6 +191,43 @@ def test_linear_with_the_k_steps_of_a_tile_shared_among_blocks(splits):
         ops.linear_split_override(0)
 
 
+@pytest.mark.parametrize("pairs", [1, 2])
+@pytest.mark.parametrize("M,N,K,pad", [(300, 128, 64, 0), (129, 260, 200, 4), (2048, 384, 512, 0), (100, 1000, 520, 8), (513, 776, 1096, 0),
+                                       (70, 2072, 264, 0), (1000, 8240, 136, 0)])
+def test_linear_32_bit_outputs_through_the_copy_engine(M, N, K, pad, pairs):
+    """32-bit outputs leave the tensor-core product as 32 x 32 tiles by bulk tensor copies: plain stores, and
+    adds made at the L2 when the product is summed into its output.  Edges inside a tile in both directions,
+    rows longer than N (the columns past N stay as they were), column scales and biases, single blocks and
+    pairs; twice each (the staging tile is used again), and the same bits as the epilogue of plain stores."""
+    g = gen(36)
+    a = rnd(g, M, K, dtype=torch.bfloat16)
+    w = rnd(g, N, K, dtype=torch.bfloat16, scale=1 / math.sqrt(K))
+    cs, cb = 1 + rnd(g, N, scale=0.3), rnd(g, N)
+    try:
+        ops.linear_pair_override(pairs)
+        for accumulate, scale, bias in ((True, None, None), (False, cs, cb), (True, cs, None), (False, None, None)):
+            out_cpu = rnd(g, M, N + pad)
+            ops_plain.linear(a, w, (ref := out_cpu.clone())[:, :N], scale, bias, accumulate)
+            outs = []
+            for tma in (True, True, False):
+                try:
+                    ops.linear_tma_out(tma)
+                    out = out_cpu.cuda()
+                    ops.linear(a.cuda(), w.cuda(), out[:, :N], None if scale is None else scale.cuda(),
+                               None if bias is None else bias.cuda(), accumulate)
+                    torch.cuda.synchronize()
+                finally:
+                    ops.linear_tma_out(True)
+                ops.check_errors()
+                err = (ref.double() - out.cpu().double()).abs().max().item()
+                assert err <= TOL[torch.float32] * ref.double().abs().max().item(), f"copy engine {tma}: {err}"
+                assert torch.equal(out.cpu()[:, N:], out_cpu[:, N:]), "wrote past N"
+                outs.append(out)
+            assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), "the two epilogues differ"
+    finally:
+        ops.linear_pair_override(0)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 40, 2056), (8, 2048, 4096), (5, 67, 4104), (16, 130, 1096), (13, 2000, 3000), (3, 16, 8200)])
 def test_linear_of_few_rows_with_k_halved_between_two_blocks(M, N, K):
     """Few rows times a matrix with fewer 16-column tiles than the GPU has SMs and more than one round of K:

@@ -42,7 +42,8 @@ struct Smem {
   static constexpr int B_ROWS = PAIR ? BN / 2 : BN;        // weight rows a block stages: each block of a pair half of the tile's
   static constexpr int B_BYTES = B_ROWS * BK * 2;
   static constexpr int TILES = STAGES * (A_BYTES + B_BYTES);
-  static constexpr int STAGING = 4 * (32 * 33 + 2 * BN) * 4;   // per epilogue warp: a padded 32x32 float tile, the tile's column scales and biases
+  static constexpr int STAGE_TILE = 1280;                  // floats per epilogue warp: a padded 32 x 33 tile, or 32 x 32 for the copy engine (5 KB: tiles start on 1 KB)
+  static constexpr int STAGING = 4 * (STAGE_TILE + 2 * BN) * 4;   // per epilogue warp: that tile, the tile's column scales and biases
   static constexpr int N_BARS = 2 * STAGES + 4;            // full, empty per stage; accumulator full, empty x2
   static constexpr int TOTAL = TILES + STAGING + N_BARS * 8 + 16 + 1024;   // + tmem slot + alignment slack
 };
@@ -63,7 +64,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     TO* __restrict__ out, int ldo, const float* __restrict__ colscale,
                     const float* __restrict__ colbias, int accumulate, int M, int N, int K, ErrWords* err,
-                    int splits, float* __restrict__ part, unsigned* __restrict__ arrivals) {
+                    int splits, float* __restrict__ part, unsigned* __restrict__ arrivals,
+                    const __grid_constant__ CUtensorMap map_o, int tma_out) {
   // The set-up and the first weight tiles do not depend on the previous kernel of the stream: they go ahead of
   // the wait on it.  The loader waits before its first activation tile, the epilogue warps before they touch
   // `out`; the issuer reads shared memory only.
@@ -200,8 +202,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
   } else {                                             // ---- epilogue, warps 2..5 ----
     const int quarter = warp & 3;                      // a warp may touch lanes 32*(warp%4) .. +31 only
-    float* st = staging + quarter * (32 * 33 + 2 * BN);
-    float* sc = st + 32 * 33;                          // [BN] column scales | [BN] column biases of the tile
+    float* st = staging + quarter * S::STAGE_TILE;
+    float* sc = staging + 4 * S::STAGE_TILE + quarter * 2 * BN;   // [BN] column scales | [BN] column biases of the tile
     int local = 0;
     bool ok = true;
     // a lane can write 32 consecutive columns of its row 16 bytes at a time when rows start on 16-byte boundaries
@@ -328,6 +330,41 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           }
           continue;
         }
+        if constexpr (!SWIGLU && sizeof(TO) == 4) {
+          if (tma_out && !split) {
+            // 32-bit output through the copy engine: the lane writes the 32 columns of its row into a 32 x 32
+            // tile of shared memory (128-byte rows, 16-byte pieces swizzled as the tensor map expects) and one
+            // bulk tensor copy stores it, or adds it to what is there (the sum is made at the L2: no read of
+            // the old values by the SM, no 32 separate lines per store instruction).  The copy clips at M and N.
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the tile's last use
+            __syncwarp();
+            const uint32_t row = smem_u32(st) + (uint32_t)lane * 128u;
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+              float v0 = __uint_as_float(r[4 * q]), v1 = __uint_as_float(r[4 * q + 1]), v2 = __uint_as_float(r[4 * q + 2]),
+                    v3 = __uint_as_float(r[4 * q + 3]);
+              if (scaled) {
+                const int j = c * 32 + 4 * q;
+                v0 = v0 * sc[j] + sc[BN + j]; v1 = v1 * sc[j + 1] + sc[BN + j + 1];
+                v2 = v2 * sc[j + 2] + sc[BN + j + 2]; v3 = v3 * sc[j + 3] + sc[BN + j + 3];
+              }
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(row + (uint32_t)((q ^ (lane & 7)) << 4)), "f"(v0),
+                           "f"(v1), "f"(v2), "f"(v3) : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0 && mrow0 < M) {
+              if (accumulate)
+                asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_o),
+                             "r"(smem_u32(st)), "r"(nc0), "r"(mrow0) : "memory");
+              else
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_o),
+                             "r"(smem_u32(st)), "r"(nc0), "r"(mrow0) : "memory");
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+            continue;
+          }
+        }
         if (rows_aligned && nc0 + 32 <= N && (nc0 * sizeof(TO)) % 16 == 0) {
           // the whole piece lies inside the matrix: a lane finishes the 32 columns of its row in registers and
           // writes them 16 bytes at a time (no trip through shared memory)
@@ -418,6 +455,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
       }
     }
+    // bulk copies out of the staging tile: shared memory stays until they have read it
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   if constexpr (PAIR) {
@@ -560,6 +599,35 @@ int get_map(const void* p, int rows, int k, int ld, int box_rows, CUtensorMap* o
   return 0;
 }
 
+// The output as the copy engine sees it: 32-bit values, [M, N] with ldo between rows, boxes of 32 x 32 with the
+// 128-byte swizzle.  *ok = 0 where the output cannot go that way (its rows do not start and end on 16-byte
+// boundaries, or the test hook is off); *out is then some valid map that the kernel does not use.
+int g_tma_out = 1;
+int get_out_map(const void* p, int M, int N, int ldo, const CUtensorMap& dummy, CUtensorMap* out, int* ok) {
+  *out = dummy;
+  *ok = 0;
+  // the engine clips at the matrix's edge in pieces of 16 bytes: a row of N values must end on one
+  if (!g_tma_out || ((uintptr_t)p & 15) != 0 || (ldo & 3) != 0 || (N & 3) != 0) return 0;
+  MapKey key{p, M, N, ldo, -32};
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) { *out = it->second; *ok = 1; return 0; }
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)ldo * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(p), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return tlc_fail(-3, "linear: cuTensorMapEncodeTiled failed with %d for the output (M %d, N %d, ldo %d)", (int)r, M, N, ldo);
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps[key] = m;
+  *out = m;
+  *ok = 1;
+  return 0;
+}
+
 }  // namespace
 
 // A tensor map of a row-major bfloat16 matrix [rows, cols] with `ld` elements between rows, for boxes of
@@ -616,8 +684,12 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ldo, con
   float* part = g_part + slot * (SPLIT_SLOT_BYTES / sizeof(float));
   unsigned* arrivals = g_part_arrivals + slot * SPLIT_SLOT_COUNTERS;
   dim3 grid(tiles < g_sms ? tiles : g_sms);
+  CUtensorMap mo = ma;
+  int tma_out = 0;
+  if (std::is_same<TO, float>::value && !SWIGLU && splits == 1)
+    if (int rc = get_out_map(out, M, N, ldo, ma, &mo, &tma_out)) return rc;
   tlc_launch(kern, dim3(grid), dim3(THREADS), S::TOTAL, stream, ma, mb, (TO*)out, ldo, colscale, colbias, accumulate, M, N, K, g_err_dev,
-             splits, part, arrivals);
+             splits, part, arrivals, mo, tma_out);
   TLC_CHECK_LAUNCH("linear(tcgen05)");
   return 0;
 }
@@ -642,8 +714,12 @@ int launch_pairs(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int ld
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = g_tlc_pdl ? 2 : 1;
+  CUtensorMap mo = ma;
+  int tma_out = 0;
+  if (std::is_same<TO, float>::value && !SWIGLU)
+    if (int rc = get_out_map(out, M, N, ldo, ma, &mo, &tma_out)) return rc;
   cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<TO, PAIR_BN, PAIR_STAGES, SWIGLU, true>, ma, mb, (TO*)out, ldo, colscale, colbias,
-                     accumulate, M, N, K, g_err_dev, 1, (float*)nullptr, (unsigned*)nullptr);
+                     accumulate, M, N, K, g_err_dev, 1, (float*)nullptr, (unsigned*)nullptr, mo, tma_out);
   TLC_CHECK_LAUNCH("linear(tcgen05, pairs)");
   return 0;
 }
@@ -689,6 +765,9 @@ static int pick_tile(int M, int N) {
   }
   return bn;
 }
+
+// Test hook: 0 = 32-bit outputs never leave through the copy engine (bulk tensor stores and adds).
+extern "C" void tlc_linear_tma_out(int on) { g_tma_out = on; }
 
 // Test hook: 0 = pairs of blocks where they pay, 1 = never, 2 = wherever the GPU can run them.
 static int g_pair_override = 0;

@@ -92,6 +92,7 @@ int tlc_linear_swiglu(const void* a, int a_dtype, int lda, const void* w, int w_
 int tlc_linear_simt(const void* a, int a_dtype, int lda, const void* w, int w_dtype, int ldw, void* out,
                     int out_dtype, int ldo, const float* colscale, const float* colbias, int accumulate,
                     int M, int N, int K, cudaStream_t stream);
+void tlc_linear_tma_out(int on);        // 0: the tensor-core product's 32-bit outputs never leave through the copy engine (for comparisons)
 void tlc_linear_skinny_pairs(int on);   // 0: the skinny product never splits K over a pair of blocks (for comparisons)
 int tlc_linear_skinny_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int M, int K);
 int tlc_linear_skinny(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,

@@ -56,6 +56,7 @@ _SIGNATURES = {
     "tlc_linear_split_override": (None, [_i]),
     "tlc_linear_pair_override": (None, [_i]),
     "tlc_linear_skinny_pairs": (None, [_i]),
+    "tlc_linear_tma_out": (None, [_i]),
     "tlc_linear_pairs": (_i, []),
     "tlc_rope_kv_store": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                _i, _i, _vp]),
@@ -295,6 +296,12 @@ def linear_pair_override(mode: int) -> None:
     """Pairs of blocks on 256 x 256 tiles in the tensor-core product: 0 where they pay, 1 never, 2 wherever
     the GPU can run them; for tests."""
     library().tlc_linear_pair_override(int(mode))
+
+
+def linear_tma_out(on: bool) -> None:
+    """Whether 32-bit outputs of the tensor-core product leave through the copy engine (bulk tensor stores, and
+    adds made at the L2 for sums into the output); for tests and comparisons."""
+    library().tlc_linear_tma_out(int(bool(on)))
 
 
 def linear_skinny_pairs(on: bool) -> None:
