@@ -133,7 +133,7 @@ def attention(q, k_pages, v_pages, block_table, positions, row_seq, slots, out, 
 
 
 def mamba_conv(proj, xbc_off, dt_off, w, bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos,
-               xbc_out, dt_out, dA_out, single_rows=False, bf16_run=False):
+               xbc_out, dt_out, dA_out, single_rows=False, bf16_run=False, all_fresh=False):
     Cd, K = w.shape
     Hs = dt_bias.numel()
     wf = _f(w)

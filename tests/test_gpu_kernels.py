@@ -582,6 +582,15 @@ def test_mamba_conv(dtype, Di, G, N, K, Hs, bias):
         long_args = [rnd(g, T, Pd, dtype=DT[dtype]), Di, Di + Cd, args[3], args[4], args[5], args[6], state.clone(), cu, row_seq,
                      slots, start_pos, torch.empty(T, Cd, dtype=o_dt), torch.empty(T, Hs), torch.empty(T, Hs)]
         cmp("mamba_conv", long_args, [7, 12, 13, 14], tol_of=tol)
+    # every sequence at position 0: the rows' kernel leaves the new windows itself (sequences shorter than the
+    # window, of exactly its length, ending inside a block of 8 rows and on its last row)
+    starts, lens = [0, 0, 0, 0], [1, K - 1, 30, 9]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    T = sum(lens)
+    for o_dt, tol in ((torch.float32, 2e-5), (torch.bfloat16, 6e-3)):
+        fresh_args = [rnd(g, T, Pd, dtype=DT[dtype]), Di, Di + Cd, args[3], args[4], args[5], args[6], state.clone(), cu, row_seq,
+                      slots, start_pos, torch.empty(T, Cd, dtype=o_dt), torch.empty(T, Hs), torch.empty(T, Hs), False, False, True]
+        cmp("mamba_conv", fresh_args, [7, 12, 13, 14], tol_of=tol)
     # one row per sequence: the fused kernel of decode steps
     starts, lens = [0, 9, 1, 31, 2], [1, 1, 1, 1, 1]
     pos, row_seq, cu, start_pos = _step_arrays(starts, lens)

@@ -160,10 +160,10 @@ class Cache:
                 if need - len(have) > g.pool.n_free:
                     raise CacheError(f"cache is full: {need - len(have)} more pages needed for slot {slot}, "
                                      f"{g.pool.n_free} of {g.pool.n} free")
-                for i in range(len(have), need):
-                    p = g.pool.alloc()
-                    have.append(p)
-                    g.table_host[slot, i] = p
+                first = len(have)
+                fresh = [g.pool.alloc() for _ in range(first, need)]
+                have.extend(fresh)
+                g.table_host[slot, first:need] = torch.tensor(fresh, dtype=g.table_host.dtype)   # one write, not one a page
                 g.dirty.add(slot)
         return start
 

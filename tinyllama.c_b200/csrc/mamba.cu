@@ -24,6 +24,10 @@ template <bool BF16_RUN> __device__ __forceinline__ float as_operand(float v) {
 // raw samples of those rows and of the K-1 rows before them once (all loads issued together), and
 // takes a tap from the sequence's stored window only where the row is among the first K-1 of a
 // sequence that continues from a slot.  Also writes dt and dA of the rows (first blocks along y).
+// With write_state (every sequence of the step starts at position 0, so that no block reads a stored window)
+// the block that holds a sequence's last row also leaves the sequence's new window: its last K-1 raw samples,
+// zeros before its first row.  A step with a sequence that continues leaves that to mamba_conv_state_kernel,
+// which runs when every reader of the old windows has finished.
 #define CONV_ROWS 8
 template <typename T, typename TO, int K, bool QUICK>
 __global__ void __launch_bounds__(256)
@@ -33,24 +37,28 @@ mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_o
                   const float* __restrict__ conv_state, const int* __restrict__ cu_seqlens,
                   const int* __restrict__ row_seq, const int* __restrict__ slots,
                   const int* __restrict__ start_pos, TO* __restrict__ xbc_out,
-                  float* __restrict__ dt_out, float* __restrict__ dA_out, int n_rows, int Cd, int Hs) {
-  tlc_pdl(proj, conv_state, xbc_out, dt_out, dA_out);
-  __shared__ int s_i[CONV_ROWS], s_has[CONV_ROWS], s_slot[CONV_ROWS], s_plain;
+                  float* __restrict__ dt_out, float* __restrict__ dA_out, int n_rows, int Cd, int Hs,
+                  float* state_out, int write_state) {   // state_out is conv_state, written only when nothing reads it
+  tlc_pdl(proj, conv_state, xbc_out, dt_out, dA_out, state_out);
+  __shared__ int s_i[CONV_ROWS], s_has[CONV_ROWS], s_slot[CONV_ROWS], s_last[CONV_ROWS], s_plain, s_any_last;
   const int t0 = blockIdx.x * CONV_ROWS;
-  if (threadIdx.x == 0) s_plain = 1;
+  if (threadIdx.x == 0) { s_plain = 1; s_any_last = 0; }
   __syncthreads();
   if (threadIdx.x < CONV_ROWS) {
     const int t = t0 + threadIdx.x;
-    int i = 0, has = 0, slot = 0;
+    int i = 0, has = 0, slot = 0, last = 0;
     if (t < n_rows) {
       const int b = row_seq[t];
       i = t - cu_seqlens[b];                          // index of the row inside its sequence's new tokens
       has = start_pos[b] > 0;
       slot = slots[b];
+      last = write_state && t == cu_seqlens[b + 1] - 1;
     }
     s_i[threadIdx.x] = i;
     s_has[threadIdx.x] = has;
     s_slot[threadIdx.x] = slot;
+    s_last[threadIdx.x] = last;
+    if (last) s_any_last = 1;
     // plain: all of the block's rows exist and every tap of every row reads a row of this step
     if (t >= n_rows || i < K - 1) s_plain = 0;
   }
@@ -107,6 +115,16 @@ mamba_conv_rows_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_o
         }
       }
       xbc_out[(size_t)t * Cd + c] = from_f32<TO>(as_operand<QUICK>(silu_of<QUICK>(sum + bv)));
+    }
+  }
+  if (s_any_last && c < Cd) {
+    for (int r = 0; r < CONV_ROWS; r++) {
+      if (!s_last[r]) continue;
+      const int t = t0 + r, n = s_i[r] + 1;           // the sequence's last row and its number of rows
+      float* st = state_out + (size_t)s_slot[r] * (K - 1) * Cd + c;
+#pragma unroll
+      for (int j = 0; j < K - 1; j++)                 // window row j is the sequence's row n - (K-1) + j
+        st[(size_t)j * Cd] = j >= K - 1 - n ? to_f32(proj[(size_t)(t - (K - 2) + j) * ld + xbc_off + c]) : 0.f;
     }
   }
   if (c < Hs) {
@@ -245,7 +263,7 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
 #define TLC_CONV_ROWS_Q(KT, QK)                                                                                        \
   tlc_launch(mamba_conv_rows_kernel<TT, TO, KT, QK>, dim3(grid8), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off,  \
              dt_off, w, bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, (TO*)xbc_out, dt_out,     \
-             dA_out, T, Cd, Hs)
+             dA_out, T, Cd, Hs, conv_state, fused_state)
 #define TLC_CONV_ROWS(KT) do { if (quick) TLC_CONV_ROWS_Q(KT, true); else TLC_CONV_ROWS_Q(KT, false); } while (0)
 // xbc_dtype: the element type of xbc_out [T, Cd].  Single-token steps and the 32-bit scans take float; the scan
 // of prompts in matrix form takes its operands in bfloat16 and gets them in that type at once.
@@ -253,8 +271,10 @@ extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, 
                               const float* bias, const float* dt_bias, const float* A, float* conv_state,
                               const int* cu_seqlens, const int* row_seq, const int* slots, const int* start_pos,
                               void* xbc_out, int xbc_dtype, float* dt_out, float* dA_out, int T, int B, int Cd, int K,
-                              int Hs, int single_rows, int quick, cudaStream_t stream) {
+                              int Hs, int single_rows, int quick, int all_fresh, cudaStream_t stream) {
   if (T == 0) return 0;
+  // every sequence starts at position 0: nothing reads a stored window, and the rows' kernel writes the new ones
+  const int fused_state = all_fresh && K >= 2 && K <= 4;
   TLC_REQUIRE(K >= 1 && K - 1 <= CONV_MAX_TAPS, "mamba_conv: %d taps exceed the kernel's limit of %d", K, CONV_MAX_TAPS + 1);
   TLC_REQUIRE(Hs <= Cd, "mamba_conv: more heads (%d) than conv channels (%d)", Hs, Cd);
   dim3 grid(T, (Cd + 255) / 256);
@@ -275,7 +295,7 @@ extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, 
     else
       tlc_launch(mamba_conv_kernel<TT, TO>, dim3(grid), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, w, bias,
                  dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, (TO*)xbc_out, dt_out, dA_out, Cd, K, Hs, quick);
-    if (K > 1)
+    if (K > 1 && !fused_state)
       tlc_launch(mamba_conv_state_kernel<TT>, dim3(grid2), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, conv_state,
                  cu_seqlens, slots, start_pos, Cd, K);
   }));

@@ -167,7 +167,7 @@ int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, int dt_off,
                    const float* bias, const float* dt_bias, const float* A, float* conv_state,
                    const int* cu_seqlens, const int* row_seq, const int* slots, const int* start_pos,
                    void* xbc_out, int xbc_dtype, float* dt_out, float* dA_out, int T, int B, int Cd, int K,
-                   int Hs, int single_rows, int quick, cudaStream_t stream);
+                   int Hs, int single_rows, int quick, int all_fresh, cudaStream_t stream);
 /* S = S * dA + B (x dt), y = S.C + x D, row by row from each slot's state [n_slots, Hs, P, N] (zero at
  * position 0), which is updated in place. */
 int tlc_ssm_scan(const float* xbc, const float* dt, const float* dA, const float* Dskip, float* state,

@@ -13,6 +13,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -53,34 +54,46 @@ def chunk_table(lens: Sequence[int], rows: int):
 
 def pack(entries: Sequence[StepEntry], starts: Sequence[int], vocab: int, device,
          chunk_rows: Sequence[int] = ()) -> Tuple[StepInfo, torch.Tensor, int]:
-    """Host lists -> one int32 buffer -> one copy to the device -> StepInfo views.
+    """Host lists -> one int32 buffer (pinned for a GPU) -> one copy to the device -> StepInfo views.
     Returns (step, packed rows whose logits are wanted, their count).  chunk_rows: the chunk lengths
-    that parts of the model asked for (ChunkRequest); the step gets one table for each."""
-    tokens, positions, row_seq, cu, want_rows = [], [], [], [0], []
-    for b, (e, start) in enumerate(zip(entries, starts)):
-        n = len(e.tokens)
-        for t in e.tokens:
-            if not (0 <= int(t) < vocab):
-                raise StepError(f"token id {t} is outside the vocabulary 0..{vocab - 1}")
-        for w in e.want:
-            if not (0 <= int(w) < n):
-                raise StepError(f"wanted index {w} is outside this step's {n} tokens")
-            want_rows.append(cu[-1] + int(w))
-        tokens += [int(t) for t in e.tokens]
-        positions += list(range(start, start + n))
-        row_seq += [b] * n
-        cu.append(cu[-1] + n)
-    T, B, W = len(tokens), len(entries), len(want_rows)
+    that parts of the model asked for (ChunkRequest); the step gets one table for each.
+
+    The GPU waits while this runs (a prompt step starts with it), so rows are filled as arrays, not one by one."""
+    B = len(entries)
     lens = [len(e.tokens) for e in entries]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    want_rows: List[int] = []
+    for b, e in enumerate(entries):
+        for w in e.want:
+            if not (0 <= int(w) < lens[b]):
+                raise StepError(f"wanted index {w} is outside this step's {lens[b]} tokens")
+            want_rows.append(cu[b] + int(w))
+    W = len(want_rows)
     tables = {int(r): chunk_table(lens, int(r)) for r in sorted(set(chunk_rows))}
-    flat = tokens + positions + row_seq + cu + [e.slot for e in entries] + list(starts) + want_rows
+    tail: List[int] = cu + [e.slot for e in entries] + [int(s) for s in starts] + want_rows
     for tab in tables.values():
         if tab is not None:
-            flat += tab[0] + tab[1] + tab[2]
-    host = torch.tensor(flat, dtype=torch.int32)
-    if torch.device(device).type == "cuda":
-        host = host.pin_memory()
-    dev = host.to(device, non_blocking=True)
+            tail += tab[0] + tab[1] + tab[2]
+    on_gpu = torch.device(device).type == "cuda"
+    host = torch.empty(3 * T + len(tail), dtype=torch.int32, pin_memory=on_gpu)
+    flat = host.numpy()
+    for b, (e, start) in enumerate(zip(entries, starts)):
+        n, o = lens[b], cu[b]
+        try:
+            ids = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+        except (TypeError, ValueError, OverflowError):
+            ids = np.asarray([int(t) for t in e.tokens], dtype=np.int64)
+        bad = np.flatnonzero((ids < 0) | (ids >= vocab))
+        if bad.size:
+            raise StepError(f"token id {int(ids[bad[0]])} is outside the vocabulary 0..{vocab - 1}")
+        flat[o:o + n] = ids
+        flat[T + o:T + o + n] = np.arange(start, start + n, dtype=np.int64)
+        flat[2 * T + o:2 * T + o + n] = b
+    flat[3 * T:] = tail
+    dev = host.to(device, non_blocking=True) if on_gpu else host
     o = 0
 
     def take(n):

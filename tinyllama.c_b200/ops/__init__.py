@@ -75,7 +75,7 @@ _SIGNATURES = {
     "tlc_attention_prefill_tc": (_i, [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i,
                                       _i, _i, _vp]),
     "tlc_mamba_conv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i,
-                            _i, _i, _i, _i, _i, _vp]),
+                            _i, _i, _i, _i, _i, _i, _vp]),
     "tlc_ssm_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "tlc_ssm_scan_chunked": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i,
                                   _vp]),
@@ -545,7 +545,8 @@ DISABLE_SSD = bool(int(os.environ.get("TLC_DISABLE_SSD", "0")))
 def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, bias: Optional[torch.Tensor],
                dt_bias: torch.Tensor, A: torch.Tensor, conv_state: torch.Tensor, cu_seqlens: torch.Tensor,
                row_seq: torch.Tensor, slots: torch.Tensor, start_pos: torch.Tensor, xbc_out: torch.Tensor,
-               dt_out: torch.Tensor, dA_out: torch.Tensor, single_rows: bool = False, bf16_run: bool = False) -> None:
+               dt_out: torch.Tensor, dA_out: torch.Tensor, single_rows: bool = False, bf16_run: bool = False,
+               all_fresh: bool = False) -> None:
     """Causal depthwise convolution + SiLU of the xBC columns of proj, continuing each
     sequence's window (conv_state [n_slots, K-1, Cd], updated in place); also
     dt = softplus(dt + dt_bias) and dA = exp(dt * A) per row and head.  single_rows says
@@ -553,7 +554,9 @@ def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, b
     model computes in bfloat16: x|B|C, operands of the scan's matrix products, are then rounded to
     bfloat16 values whatever type they are stored in, and the SiLU of prompts takes the fast exponential
     and reciprocal.  xbc_out is float32, or
-    bfloat16 where the scan that follows takes its operands in that type (ssm_scan with A)."""
+    bfloat16 where the scan that follows takes its operands in that type (ssm_scan with A).  all_fresh says that
+    every sequence of the step starts at position 0 (the caller knows the start positions on the host): no stored
+    window is read then, and the convolution's own kernel leaves the new windows (one launch less)."""
     _gpu(proj, w, bias, dt_bias, A, conv_state, cu_seqlens, row_seq, slots, start_pos, xbc_out, dt_out, dA_out)
     T = proj.shape[0]
     Cd, K = w.shape
@@ -575,7 +578,8 @@ def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, b
     _call("tlc_mamba_conv", proj.data_ptr(), dtype_code(proj.dtype), _rows(proj, "proj"), xbc_off, dt_off,
           w.data_ptr(), _p(bias), dt_bias.data_ptr(), A.data_ptr(), conv_state.data_ptr(), cu_seqlens.data_ptr(),
           row_seq.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), xbc_out.data_ptr(), dtype_code(xbc_out.dtype),
-          dt_out.data_ptr(), dA_out.data_ptr(), T, B, Cd, K, Hs, int(bool(single_rows)), int(bool(bf16_run)), _stream())
+          dt_out.data_ptr(), dA_out.data_ptr(), T, B, Cd, K, Hs, int(bool(single_rows)), int(bool(bf16_run)),
+          int(bool(all_fresh)), _stream())
 
 
 def ssd_walk_override(mode: int) -> None:

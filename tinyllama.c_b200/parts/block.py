@@ -108,23 +108,35 @@ class Block(Part):
                 acts[i] = self._mix(i, part, step, cache, views[i])
                 done[i] = self._done[i]
                 done[i].record(side)
-        acts[here] = self._mix(here, parts[here], step, cache, views[here])
+        # The wait for the side streams breaks the chain of programmatic launches on this stream.  A mixer that
+        # offers to (mix_takes_join) places it before its own last kernel; otherwise it comes after the mixer.
+        joined = []
+
+        def join():
+            if not joined:
+                joined.append(True)
+                for ev in done:
+                    if ev is not None:
+                        main.wait_event(ev)
+
+        early = getattr(self.mixers[here], "mix_takes_join", False)
+        acts[here] = self._mix(here, parts[here], step, cache, views[here], join if early else None)
+        join()
         for i, m in enumerate(self.mixers):          # outputs in the mixers' order, whatever ran where
-            if done[i] is not None:
-                main.wait_event(done[i])
             if joint is None:
                 m.output(acts[i], x32)
         if joint is not None:
             self.fused_out.forward(joint, x32, accumulate=True)
 
-    def _mix(self, i: int, part: torch.Tensor, step: StepInfo, cache: LayerCache, view: Optional[torch.Tensor]):
+    def _mix(self, i: int, part: torch.Tensor, step: StepInfo, cache: LayerCache, view: Optional[torch.Tensor], join=None):
         """Mixer i between its projections; into its columns of the joint buffer, scaled, where there is one."""
         m = self.mixers[i]
+        more = {} if join is None else {"join": join}
         if view is None:
-            return m.mix(part, step, cache)
+            return m.mix(part, step, cache, **more)
         if self.out_scales[i] != 1.0:
-            return m.mix(part, step, cache, view, self.out_scales[i])
-        return m.mix(part, step, cache, view)
+            return m.mix(part, step, cache, view, self.out_scales[i], **more)
+        return m.mix(part, step, cache, view, **more)
 
     def _joint_activations(self, x32: torch.Tensor):
         """The buffer that the mixers fill side by side for the shared output projection, and each

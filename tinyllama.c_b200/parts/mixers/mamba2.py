@@ -13,7 +13,7 @@ counterpart in the reference.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
 
@@ -111,12 +111,16 @@ class Mamba2Mixer(Part):
         return self.out_proj
 
     mix_takes_scale = True         # mix() can multiply its result by a number on the way out
+    mix_takes_join = True          # mix() calls `join` once, before its last kernel
 
     def mix(self, proj: torch.Tensor, step: StepInfo, cache: LayerCache, out: Optional[torch.Tensor] = None,
-            out_scale: float = 1.0) -> torch.Tensor:
+            out_scale: float = 1.0, join: Optional[Callable[[], None]] = None) -> torch.Tensor:
         """Everything between the input projection and the output projection: [T, d_ssm] times
         out_scale, written to `out` (rows may be strided) where one is given.  (A block that runs
-        several output projections as one product moves a part of this one's multiplier here.)"""
+        several output projections as one product moves a part of this one's multiplier here.)
+        `join`, where given, is called once on the current stream before the last kernel: a block that runs
+        other mixers on other streams waits for them there, where this stream waits for another one anyway
+        (the scan's second stream), so that the kernel after this mixer follows its last one directly."""
         if not cache.writes:
             raise ValueError("mamba2: a recurrent mixer cannot run on another layer's cache without storing "
                              "(its window and state would advance twice in one step)")
@@ -133,7 +137,8 @@ class Mamba2Mixer(Part):
         dt, dA = new((T, self.Hs), f32), new((T, self.Hs), f32)
         ops.mamba_conv(proj, self.Di, self.Di + self.Cd, self.conv_w, self.conv_b, self.dt_bias, self.A, conv_state,
                        step.cu_seqlens, step.row_seq, step.slots, step.start_pos, xbc, dt, dA,
-                       step.max_new == 1, self.dtype == torch.bfloat16)
+                       step.max_new == 1, self.dtype == torch.bfloat16,
+                       len(step.host_start) == step.n_seqs and not any(step.host_start))
         y = new((T, self.Di), f32)
         # in matrix form the outputs may come as two summands, the one that needs no state computed beside the walk
         # over the chunks; the gated norm adds them
@@ -141,6 +146,8 @@ class Mamba2Mixer(Part):
         in_two = ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs,
                               self.P, self.N, self.G, chunks, self.A if matrix_form else None, y_part)
         gated = out if out is not None else new((T, self.Di), self.dtype)
+        if join is not None:
+            join()
         ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated,
                           out_scale, y_part if in_two else None)
         return gated
