@@ -410,6 +410,35 @@ def test_attention_of_prompts_on_tcgen05(H, KV, hd, window, mode):
         ops.prompt_attention_override(0)
 
 
+@pytest.mark.parametrize("max_blocks", [1, 3, 7, 1000])
+@pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 128, 0), (3, 1, 64, 0), (4, 4, 128, 100)])
+def test_attention_of_prompts_on_a_bounded_number_of_blocks(H, KV, hd, window, max_blocks):
+    """The tcgen05 kernel with fewer blocks than (tile, head) items: a block works through several items one after
+    the other (long and short ones, tiles of different sequences and heads, tiles past the step's last), its
+    barriers made anew in between, tensor memory and shared memory used again.  The same bits as one block an item."""
+    g = gen(34)
+    starts, lens = [0, 130, 63, 5, 0], [333, 200, 2, 129, 1]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    totals = [s + n for s, n in zip(starts, lens)]
+    slots, table, k_pages, v_pages = _paged_setup(g, 5, totals, KV, hd, torch.bfloat16, n_slots=7)
+    T = sum(lens)
+    q = rnd(g, T, H * hd, dtype=torch.bfloat16)
+    k_pages[int(table[int(slots[0]), 3]), :, 10, :] *= 12.0      # a jump of a row's maximum in the fourth key tile
+    args = [q, k_pages, v_pages, table, pos, row_seq, slots, torch.empty(T, H * hd, dtype=torch.bfloat16), H, KV, hd,
+            1.0 / math.sqrt(hd), window, 0, cu, start_pos, max(totals)]
+    cmp("attention", args + [max_blocks], [7], tol_of=TOL[torch.bfloat16] * 2.5)
+    outs = []
+    for mb in (0, max_blocks, max_blocks):
+        out = torch.empty(T, H * hd, dtype=torch.bfloat16, device="cuda")
+        gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args]
+        gpu[7] = out
+        ops.attention(*gpu, mb)
+        torch.cuda.synchronize()
+        ops.check_errors()
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2]), "the result depends on the number of blocks"
+
+
 @pytest.mark.parametrize("H,KV,hd,window", [(4, 2, 128, 0), (2, 1, 64, 0), (4, 4, 64, 700)])
 def test_attention_of_long_prompts_in_pieces(H, KV, hd, window):
     """Key ranges of more than 8 pages are cut into pieces that run side by side and are merged: a prompt of

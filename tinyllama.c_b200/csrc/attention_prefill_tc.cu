@@ -73,8 +73,8 @@ __global__ void __launch_bounds__(THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_pages,
                             const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
-                            const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int H, int KV,
-                            float scale_log2, int window, int out_ld, ErrWords* err) {
+                            const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int n_tiles, int H,
+                            int KV, float scale_log2, int window, int out_ld, ErrWords* err) {
   tlc_pdl(out);
   using L_ = FaSmem<HD>;
   constexpr int TCOLS = HD == 128 ? 512 : 256;            // the groups' scores at 0 and 64, their outputs at 128 and 128 + hd
@@ -98,37 +98,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   auto pv_done = [&](int i) { return smem_u32(bars + 1 + 2 * KS + 2 * VS + 6 + i); };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // which sequence, and which of its 128-row tiles, is this block's (the last tiles, with the most keys, first)
-  if (tid == 0) {
-    int tile = (int)gridDim.x - 1 - (int)blockIdx.x, found = -1, row0 = 0;
-    for (int b = 0; b < n_seqs; b++) {
-      const int nt = (cu_seqlens[b + 1] - cu_seqlens[b] + BM - 1) / BM;
-      if (tile < nt) { found = b; row0 = tile * BM; break; }
-      tile -= nt;
-    }
-    s_seq = found;
-    s_row0 = row0;
-    for (int i = 0; i < L_::N_BARS; i++) {
-      const uint32_t bar = bar_q + 8 * i;               // every worker warp arrives once on s_free and p_ready, one agent on the rest
-      mbar_init(bar, (bar == s_free(0) || bar == s_free(1) || bar == p_ready(0) || bar == p_ready(1)) ? 4 : 1);
-    }
-    *dead = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
-  __syncthreads();
-  const int b = s_seq;
-  if (b < 0) return;
-  const int i0 = s_row0;
-  const int h = blockIdx.y, g = h / (H / KV);
-  const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
-  const int rows = min(BM, n_new - i0);
-  const int p0 = start_pos[b] + i0;                       // position of the block's first row
-  const int tile_hi = (p0 + rows - 1) / BN;
-  const int tile_lo = window > 0 ? max(0, p0 + 1 - window) / BN : 0;
-  const int n = tile_hi - tile_lo + 1;                    // key tiles of this block
   const long long wait_limit = mbar_wait_limit(err);
-  for (int i = tid; i < n; i += THREADS) pages[i] = block_table[(size_t)slots[b] * max_pages + tile_lo + i];
+  if (tid == 0) *dead = 0;
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TCOLS)
                  : "memory");
@@ -142,6 +113,49 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (*dead) return;
     if (!mbar_wait(bar, parity, err, code, wait_limit)) *dead = 1;
   };
+  // An item is a 128-row tile of a sequence and a head; items are numbered with the tiles of most keys first and
+  // a tile's heads side by side.  With one block an item (the launcher's choice when the GPU is the kernel's
+  // alone) the loop below runs once.  With fewer blocks, block x takes items x, 2 nb - 1 - x, 2 nb + x, ...
+  // (back and forth, so that every block gets long and short ones): the kernel then holds nb SMs, each for
+  // about the same time, and leaves the others to kernels of other streams.  Between items the barriers are
+  // made anew; tensor memory and the tiles of shared memory are simply used again.
+  const int n_items = n_tiles * H, nb = (int)gridDim.x;
+#pragma unroll 1
+  for (int round = 0;; round++) {
+  const int item = round * nb + ((round & 1) ? nb - 1 - (int)blockIdx.x : (int)blockIdx.x);
+  if (item >= n_items) break;
+  const int h = item % H;
+  // which sequence, and which of its 128-row tiles, is this item's
+  if (tid == 0) {
+    int tile = n_tiles - 1 - item / H, found = -1, row0 = 0;
+    for (int b = 0; b < n_seqs; b++) {
+      const int nt = (cu_seqlens[b + 1] - cu_seqlens[b] + BM - 1) / BM;
+      if (tile < nt) { found = b; row0 = tile * BM; break; }
+      tile -= nt;
+    }
+    s_seq = found;
+    s_row0 = row0;
+    for (int i = 0; i < L_::N_BARS; i++) {
+      const uint32_t bar = bar_q + 8 * i;               // every worker warp arrives once on s_free and p_ready, one agent on the rest
+      if (round > 0) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");   // nothing is pending on it (see the loader's last waits)
+      mbar_init(bar, (bar == s_free(0) || bar == s_free(1) || bar == p_ready(0) || bar == p_ready(1)) ? 4 : 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  const int b = s_seq;
+  if (b >= 0) {
+  const int i0 = s_row0;
+  const int g = h / (H / KV);
+  const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
+  const int rows = min(BM, n_new - i0);
+  const int p0 = start_pos[b] + i0;                       // position of the block's first row
+  const int tile_hi = (p0 + rows - 1) / BN;
+  const int tile_lo = window > 0 ? max(0, p0 + 1 - window) / BN : 0;
+  const int n = tile_hi - tile_lo + 1;                    // key tiles of this item
+  for (int i = tid; i < n; i += THREADS) pages[i] = block_table[(size_t)slots[b] * max_pages + tile_lo + i];
+  __syncthreads();
 
   if (warp >= WORKERS / 32) {
     // ---- three warps of one agent each (their first lanes), on three schedulers: the copies, the products
@@ -169,6 +183,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tma_load_2d(sm0 + L_::V + st * L_::V_STAGE + c * L_::K_SLAB, &map_v, v_full(st), 64 * c, (pages[t] * KV + g) * BN);
         }
       }
+      // the last arrivals on the stages' barriers (the products' commits), which nothing else waits for: after
+      // them no barrier of this item has anything pending, and the next item may make them anew
+      for (int t = max(0, n - KS); t < n; t++) wait(k_empty(t % KS), (uint32_t)((t / KS) & 1), 26);
+      for (int t = max(0, n - VS); t < n; t++) wait(v_empty(t % VS), (uint32_t)((t / VS) & 1), 27);
     } else if (lane == 0 && role == 1) {
       // the scores run two tiles ahead of the workers: both score buffers are in use from the start
       constexpr uint32_t idesc_s = instr_desc(BM, BN);
@@ -322,8 +340,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
     }
   }
+  }  // b >= 0
+  // every agent is done with the item: its copies have landed, its products have completed (the workers read
+  // their last results, the loader saw the last commits), tensor memory and shared memory may be written again
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }  // items
   if (warp == 0)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TCOLS) : "memory");
 }
@@ -354,7 +377,7 @@ template <int HD>
 int run(const __nv_bfloat16* q, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, long long n_page_rows,
         const int* block_table, int max_pages, const int* cu_seqlens, const int* slots, const int* start_pos,
         __nv_bfloat16* out, int n_seqs, int n_tiles_bound, int H, int KV, float scale, int window,
-        int p_max, int T, int out_ld, cudaStream_t stream) {
+        int p_max, int T, int out_ld, int max_blocks, cudaStream_t stream) {
   static bool configured = false;
   const int smem = FaSmem<HD>::total(p_max);
   TLC_REQUIRE(smem <= 220 * 1024, "attention(prefill, tcgen05): %d key tiles need %d bytes of shared memory", p_max, smem);
@@ -367,9 +390,11 @@ int run(const __nv_bfloat16* q, const __nv_bfloat16* k_pages, const __nv_bfloat1
   if (int rc = tlc_tensor_map_bf16(q, T, (long long)H * HD, (long long)H * HD, 64, BM, &mq)) return rc;
   if (int rc = page_map(k_pages, n_page_rows, HD, &mk)) return rc;
   if (int rc = page_map(v_pages, n_page_rows, HD, &mv)) return rc;
-  tlc_launch(attention_prefill_tc_kernel<HD>, dim3(n_tiles_bound, H), dim3(THREADS), (size_t)smem, stream, mq, mk, mv,
-             block_table, max_pages, cu_seqlens, slots, start_pos, out, n_seqs, H, KV, scale * 1.4426950408889634f, window, out_ld,
-             tlc_error_words());
+  const long long items = (long long)n_tiles_bound * H;
+  const int blocks = (int)(max_blocks > 0 && max_blocks < items ? max_blocks : items);
+  tlc_launch(attention_prefill_tc_kernel<HD>, dim3(blocks), dim3(THREADS), (size_t)smem, stream, mq, mk, mv,
+             block_table, max_pages, cu_seqlens, slots, start_pos, out, n_seqs, n_tiles_bound, H, KV, scale * 1.4426950408889634f,
+             window, out_ld, tlc_error_words());
   TLC_CHECK_LAUNCH("attention(prefill, tcgen05)");
   return 0;
 }
@@ -382,10 +407,13 @@ extern "C" int tlc_attention_prefill_tc_ok(int dtype, int hd, int H, int KV) {
 
 // n_tiles_bound: an upper bound of sum_b ceil(n_new_b / 128) (e.g. T / 128 + n_seqs); max_keys: keys of the longest
 // sequence after this step; n_pages: pages of the cache (k_pages and v_pages are [n_pages, KV, 64, hd]).
+// max_blocks: 0, or how many blocks (hence SMs) the kernel may hold: it then works through its (tile, head) items
+// with that many blocks, for callers that run other kernels beside it.
 extern "C" int tlc_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                                         const int* block_table, int max_pages, const int* cu_seqlens, const int* slots,
                                         const int* start_pos, void* out, int n_seqs, int n_tiles_bound, int H, int KV,
-                                        int hd, float scale, int window, int max_keys, int T, int out_ld, cudaStream_t stream) {
+                                        int hd, float scale, int window, int max_keys, int T, int out_ld, int max_blocks,
+                                        cudaStream_t stream) {
   if (n_seqs == 0 || n_tiles_bound == 0 || T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;
   TLC_REQUIRE(tlc_attention_prefill_tc_ok(TLC_BF16, hd, H, KV), "attention(prefill, tcgen05): %d heads, %d key/value heads of size %d are not built", H, KV, hd);
@@ -398,7 +426,7 @@ extern "C" int tlc_attention_prefill_tc(const void* q, const void* k_pages, cons
   const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
   if (hd == 64)
     return run<64>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out,
-                   n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, stream);
+                   n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, stream);
   return run<128>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out,
-                  n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, stream);
+                  n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, stream);
 }

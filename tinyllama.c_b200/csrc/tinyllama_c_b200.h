@@ -156,7 +156,8 @@ int tlc_attention_prefill_tc_ok(int dtype, int hd, int H, int KV);
 int tlc_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                              const int* block_table, int max_pages, const int* cu_seqlens, const int* slots,
                              const int* start_pos, void* out, int n_seqs, int n_tiles_bound, int H, int KV,
-                             int hd, float scale, int window, int max_keys, int T, int out_ld, cudaStream_t stream);
+                             int hd, float scale, int window, int max_keys, int T, int out_ld, int max_blocks,
+                             cudaStream_t stream);
 
 /* ---- Mamba2 (mamba.cu, mamba_ssd.cu) ----------------------------------------------------------------- */
 /* Causal depthwise convolution + SiLU over the x|B|C columns of proj, continuing each sequence's window

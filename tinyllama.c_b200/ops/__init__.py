@@ -73,7 +73,7 @@ _SIGNATURES = {
                                    _vp, _i, _i, _vp]),
     "tlc_attention_prefill_tc_ok": (_i, [_i, _i, _i, _i]),
     "tlc_attention_prefill_tc": (_i, [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i,
-                                      _i, _i, _vp]),
+                                      _i, _i, _i, _vp]),
     "tlc_mamba_conv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i,
                             _i, _i, _i, _i, _i, _i, _vp]),
     "tlc_ssm_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
@@ -425,13 +425,15 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, H: int, KV: int,
               hd: int, scale: float, window: int = 0, decode_max_keys: int = 0,
               cu_seqlens: Optional[torch.Tensor] = None, start_pos: Optional[torch.Tensor] = None,
-              max_keys: int = 0) -> None:
+              max_keys: int = 0, max_blocks: int = 0) -> None:
     """Causal grouped-query attention of every row over its sequence's pages (keys 0..position,
     or the last `window` of them).  decode_max_keys > 0 says that the rows are single-token
     steps of sequences no longer than that: keys are then split across blocks.  With
     cu_seqlens and start_pos (rows of a sequence are consecutive positions from start_pos) the
     tiled tensor-core kernel serves bfloat16 heads of 64 or 128; with max_keys (the longest sequence
-    after this step) it cuts the key range of long rows into pieces that run side by side."""
+    after this step) it cuts the key range of long rows into pieces that run side by side.  max_blocks > 0
+    bounds how many blocks (hence SMs) the tensor-core kernel of prompts holds at a time, for a caller that runs
+    other kernels beside it; the result does not depend on it."""
     _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out)
     T = q.shape[0]
     if not q.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.dtype != q.dtype or k_pages.dtype != q.dtype:
@@ -454,7 +456,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
         _call("tlc_attention_prefill_tc", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
               block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(),
               out.data_ptr(), B, T // 128 + B, H, KV, hd, float(scale), int(window or 0), int(max_keys), T,
-              out_ld, _stream())
+              out_ld, int(max_blocks), _stream())
         return
     if tiled:
         B = slots.numel()

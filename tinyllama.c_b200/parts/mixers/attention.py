@@ -88,9 +88,13 @@ class AttentionMixer(Part):
         the output projections of its mixers as one product over their results side by side)."""
         return self.o
 
-    def mix(self, qkv: torch.Tensor, step: StepInfo, cache: LayerCache, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    mix_takes_max_blocks = True    # mix() can bound how many SMs its prompt kernel holds
+
+    def mix(self, qkv: torch.Tensor, step: StepInfo, cache: LayerCache, out: Optional[torch.Tensor] = None,
+            max_blocks: int = 0) -> torch.Tensor:
         """Everything between the input projection and the output projection: [T, H*hd], written
-        to `out` (rows may be strided) where one is given."""
+        to `out` (rows may be strided) where one is given.  max_blocks > 0: the attention kernel of a prompt
+        holds at most that many SMs (a block that runs another mixer beside this one leaves it the rest)."""
         T = step.n_rows
         kv = cache.kv[self.cache_key]
         table = self.position.rotation_table()
@@ -112,7 +116,8 @@ class AttentionMixer(Part):
         att = out if out is not None else torch.empty_like(q)
         ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
                       self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
-                      step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos, step.max_context)
+                      step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos, step.max_context,
+                      max_blocks)
         return att
 
     def output(self, att: torch.Tensor, residual: torch.Tensor) -> None:
