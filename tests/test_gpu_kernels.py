@@ -191,6 +191,46 @@ def test_linear_with_the_k_steps_of_a_tile_shared_among_blocks(splits):
         ops.linear_split_override(0)
 
 
+@pytest.mark.parametrize("split", [0, 1, 2, 4, 8])
+@pytest.mark.parametrize("M,N,K", [(33, 2048, 4096), (64, 8240, 2048), (20, 200, 520), (64, 1000, 1096), (48, 128, 264), (17, 272, 136),
+                                   (32, 336, 2056)])
+def test_linear_of_17_to_64_rows_with_the_weights_on_the_wide_side(M, N, K, split):
+    """Products of 17..64 rows: tiles of 128 weight rows x 32 or 64 activation rows on tcgen05.mma, the K-steps of a
+    tile shared among the 1, 2, 4 or 8 blocks of a cluster whose sums meet through distributed shared memory (more
+    blocks than K-steps: some have none).  A last tile past N, K that ends inside a stage, fewer rows than the tile
+    has columns; plain, into a 32-bit sum, with column scales and biases, and the SwiGLU epilogue; twice each, the
+    same bits both times; and within rounding of the kernels that run these sizes otherwise."""
+    g = gen(37)
+    a = rnd(g, M, K, dtype=torch.bfloat16)
+    w = rnd(g, N, K, dtype=torch.bfloat16, scale=1 / math.sqrt(K))
+    cs, cb = 1 + rnd(g, N, scale=0.3), rnd(g, N)
+    try:
+        for accumulate, scale, bias, o_dt in ((True, None, None, torch.float32), (False, cs, cb, torch.bfloat16),
+                                              (False, None, None, torch.float32)):
+            out_cpu = rnd(g, M, N + 3, dtype=o_dt)
+            ops_plain.linear(a, w, (ref := out_cpu.clone())[:, :N], scale, bias, accumulate)
+            outs = []
+            for on in (True, True, False):
+                ops.linear_few_rows(on, split)
+                out = out_cpu.cuda()
+                ops.linear(a.cuda(), w.cuda(), out[:, :N], None if scale is None else scale.cuda(),
+                           None if bias is None else bias.cuda(), accumulate)
+                torch.cuda.synchronize()
+                ops.check_errors()
+                err = (ref.double() - out.cpu().double()).abs().max().item()
+                assert err <= TOL[o_dt] * ref.double().abs().max().item(), f"{M}x{N}x{K}, few-rows kernel {on}: {err}"
+                assert torch.equal(out.cpu()[:, N:], out_cpu[:, N:]), "wrote past N"
+                outs.append(out)
+            assert torch.equal(outs[0], outs[1]), "two runs of the same product differ"
+        if N % 16 == 0:
+            ops.linear_few_rows(True, split)
+            for o_dt in (torch.bfloat16, torch.float32):
+                cmp("linear_swiglu", [a, w, torch.empty(M, N // 2, dtype=o_dt), cs, cb], [2], tol_of=TOL[torch.bfloat16] * 2)
+            ops.check_errors()
+    finally:
+        ops.linear_few_rows(True, 0)
+
+
 @pytest.mark.parametrize("pairs", [1, 2])
 @pytest.mark.parametrize("M,N,K,pad", [(300, 128, 64, 0), (129, 260, 200, 4), (2048, 384, 512, 0), (100, 1000, 520, 8), (513, 776, 1096, 0),
                                        (70, 2072, 264, 0), (1000, 8240, 136, 0)])

@@ -26,6 +26,13 @@
 #include <mutex>
 #include <unordered_map>
 
+// gemm_tcgen05_few_rows.cu
+int tlc_linear_few_rows_run(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
+                            const float* colscale, const float* colbias, int accumulate, int M, int N, int K,
+                            cudaStream_t stream);
+int tlc_linear_few_rows_swiglu(const void* a, int lda, const void* w, int ldw, void* out, int out_dtype, int ldo,
+                               const float* colscale, const float* colbias, int M, int N, int K, cudaStream_t stream);
+
 namespace {
 
 constexpr int BM = 128;
@@ -799,6 +806,10 @@ extern "C" int tlc_linear_swiglu(const void* a, int a_dtype, int lda, const void
   TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N / 2, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N, K,
               lda, ldw, ldo);
   if (out_dtype != TLC_F32 && out_dtype != TLC_BF16) return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
+  if (min_rows_for_tensor_cores <= 64 && tlc_linear_few_rows_ok(a_dtype, lda, a, w_dtype, ldw, w, M, N, K)) {
+    if (int rc = init_once()) return rc;
+    return tlc_linear_few_rows_swiglu(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, M, N, K, stream);
+  }
   if (M <= 32 && tlc_linear_skinny_ok(a_dtype, lda, a, w_dtype, ldw, w, M, K))
     return tlc_linear_skinny_swiglu(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, M, N, K, stream);
   if (M < min_rows_for_tensor_cores) return 1;
@@ -833,6 +844,14 @@ extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, in
   // Up to 32 rows the weight-streaming kernel is always best.  From 33 to 64 rows it re-reads the
   // activations once per 16 output columns, which only pays while the tiled kernel would have too
   // few tiles to keep the GPU busy (narrow outputs) and too few K-steps to share among blocks.
+  // (a threshold above 64 rows keeps every tensor-core kernel out, this one too)
+  if (min_rows_for_tensor_cores <= 64 && (out_dtype == TLC_F32 || out_dtype == TLC_BF16) &&
+      tlc_linear_few_rows_ok(a_dtype, lda, a, w_dtype, ldw, w, M, N, K)) {
+    TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N, K,
+                lda, ldw, ldo);
+    if (int rc = init_once()) return rc;
+    return tlc_linear_few_rows_run(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, accumulate, M, N, K, stream);
+  }
   const bool tiled_ok = M >= min_rows_for_tensor_cores && tlc_linear_tcgen05_ok(a_dtype, lda, a, w_dtype, ldw, w, K);
   const bool narrow = N <= 3072 && K < 8192;
   if (tlc_linear_skinny_ok(a_dtype, lda, a, w_dtype, ldw, w, M, K) && (M <= 32 || narrow || !tiled_ok)) {

@@ -57,6 +57,8 @@ _SIGNATURES = {
     "tlc_linear_pair_override": (None, [_i]),
     "tlc_linear_skinny_pairs": (None, [_i]),
     "tlc_linear_tma_out": (None, [_i]),
+    "tlc_linear_few_rows": (None, [_i]),
+    "tlc_linear_few_rows_split": (None, [_i]),
     "tlc_linear_pairs": (_i, []),
     "tlc_rope_kv_store": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
                                _i, _i, _vp]),
@@ -296,6 +298,14 @@ def linear_pair_override(mode: int) -> None:
     """Pairs of blocks on 256 x 256 tiles in the tensor-core product: 0 where they pay, 1 never, 2 wherever
     the GPU can run them; for tests."""
     library().tlc_linear_pair_override(int(mode))
+
+
+def linear_few_rows(on: bool, split: int = 0) -> None:
+    """Whether products of 17..64 rows take the tensor-core kernel that puts the weights on the 128-row side and
+    shares a tile's K-steps among the blocks of a cluster; split fixes the number of blocks per tile (1, 2, 4, 8;
+    0: chosen from the sizes).  For tests and comparisons."""
+    library().tlc_linear_few_rows(int(bool(on)))
+    library().tlc_linear_few_rows_split(int(split))
 
 
 def linear_tma_out(on: bool) -> None:
