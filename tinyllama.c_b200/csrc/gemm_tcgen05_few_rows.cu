@@ -218,6 +218,7 @@ gemm_few_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 
 int g_few_rows = 1;                     // test hook: 0 = never this kernel
 int g_force_split = 0;                  // test hook: blocks per tile (0: chosen)
+int g_min_tiles = 0;                    // test hook: outputs of fewer tiles of 128 weight rows stay with the other kernels (0: by the rows)
 bool g_configured = false;
 int g_max_split[4] = {0, 0, 0, 0};      // [log2 split]: how many clusters of that size run at once (0: that size is not available)
 
@@ -292,14 +293,17 @@ int run_few(const void* a, int lda, const void* w, int ldw, void* out, int out_d
 // Test hooks: whether products of 17..64 rows may take this kernel; a fixed number of blocks per tile (0: chosen).
 extern "C" void tlc_linear_few_rows(int on) { g_few_rows = on; }
 extern "C" void tlc_linear_few_rows_split(int split) { g_force_split = split; }
+extern "C" void tlc_linear_few_rows_min_tiles(int tiles) { g_min_tiles = tiles; }
 
-// bfloat16 operands with 16-byte aligned rows, 17..64 rows, and a wide output: from 32 tiles of 128 weight rows on
-// (measured at 48 and 64 rows, microseconds in a captured loop over operand sets larger than the L2: N = 8240,
-// K = 2048: 11.5 against 14.2 for the kernels that run these sizes otherwise; N = 8192 with SwiGLU 12.3 against
-// 13.5; N = 2048, K = 4096: 12.0 against 12.0, so narrow outputs stay where they were).  With a forced split
-// (tests) any output of at least one tile qualifies.
+// bfloat16 operands with 16-byte aligned rows, 17..64 rows, and an output that is wide enough: from 32 tiles of 128
+// weight rows on, from 16 with more than 32 rows.  Measured at 48 and 64 rows, microseconds in a captured loop over
+// operand sets larger than the L2: N = 8240, K = 2048: 11.5 against 14.2 for the kernels that run these sizes
+// otherwise; N = 8192 with SwiGLU 12.3 against 13.5; N = 2048, K = 4096: 12.0 against 12.0 alone, but inside the
+// captured decode step at batch 64 the two products with N = 2048 make 4.08 -> 3.79 ms a step (the
+// weight-streaming kernel re-reads 64 rows of activations per 16 columns), at batch 32 and 24 2.40 -> 2.44 and
+// 2.13 -> 2.17.  With a forced split (tests) any output of at least one tile qualifies.
 extern "C" int tlc_linear_few_rows_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int M, int N, int K) {
-  return g_few_rows && a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && M > 16 && M <= 64 && N >= (g_force_split > 0 ? WM : 32 * WM) &&
+  return g_few_rows && a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && M > 16 && M <= 64 && N >= (g_force_split > 0 ? 1 : g_min_tiles > 0 ? g_min_tiles : M > 32 ? 16 : 32) * WM &&
          K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
          tlc_error_words() != nullptr;
 }
