@@ -303,6 +303,11 @@ extern "C" void tlc_linear_few_rows_min_tiles(int tiles) { g_min_tiles = tiles; 
 // weight-streaming kernel re-reads 64 rows of activations per 16 columns), at batch 32 and 24 2.40 -> 2.44 and
 // 2.13 -> 2.17.  With a forced split (tests) any output of at least one tile qualifies.
 extern "C" int tlc_linear_few_rows_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int M, int N, int K) {
+  // more tiles than two an SM (a vocabulary-sized output: 512 tiles) are better served by the persistent tiles of
+  // the product for prompts: 55 us against 62 for 64 x 65,536 x 2,048
+  static int sms = 0;
+  if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  if (g_force_split == 0 && (N + WM - 1) / WM > 2 * sms) return 0;
   return g_few_rows && a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && M > 16 && M <= 64 && N >= (g_force_split > 0 ? 1 : g_min_tiles > 0 ? g_min_tiles : M > 32 ? 16 : 32) * WM &&
          K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
          tlc_error_words() != nullptr;
