@@ -207,7 +207,9 @@ __global__ void mamba_conv_state_kernel(const T* __restrict__ proj, int ld, int 
 
 // One-token steps: every sequence brings exactly one row, so a thread owns one (sequence, channel):
 // it reads the window, convolves, and writes the shifted window back -- one kernel instead of two.
-template <typename T>
+// KT: the number of taps when it is 2, 3 or 4 (the window then takes KT - 1 registers instead of the limit's 16),
+// else 0 and K is read at run time.
+template <typename T, int KT>
 __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int xbc_off, int dt_off,
                                          const float* __restrict__ w, const float* __restrict__ bias,
                                          const float* __restrict__ dt_bias, const float* __restrict__ A,
@@ -215,6 +217,8 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
                                          const int* __restrict__ start_pos, float* __restrict__ xbc_out,
                                          float* __restrict__ dt_out, float* __restrict__ dA_out, int Cd, int K, int Hs,
                                          int bf16_run) {
+  constexpr int TAPS = KT > 0 ? KT - 1 : CONV_MAX_TAPS;     // window rows held in registers
+  if (KT > 0) K = KT;
   // The window was stored by the step before and the weights never change: both are fetched before the
   // wait on the previous kernel; only the row's projection is read after it.
   asm volatile("griddepcontrol.launch_dependents;");
@@ -222,15 +226,15 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   const bool has_state = start_pos[b] > 0;
   float* st = conv_state + (size_t)slots[b] * (K - 1) * Cd;
-  float prev[CONV_MAX_TAPS], wk[CONV_MAX_TAPS + 1];
+  float prev[TAPS], wk[TAPS + 1];
   float bv = 0.f, db = 0.f, Ac = 0.f;
   if (c < Cd) {
 #pragma unroll
-    for (int k = 0; k < CONV_MAX_TAPS; k++) {
+    for (int k = 0; k < TAPS; k++) {
       prev[k] = (k < K - 1 && has_state) ? st[(size_t)k * Cd + c] : 0.f;
       wk[k] = k < K ? w[(size_t)c * K + k] : 0.f;
     }
-    wk[CONV_MAX_TAPS] = CONV_MAX_TAPS < K ? w[(size_t)c * K + CONV_MAX_TAPS] : 0.f;
+    wk[TAPS] = TAPS < K ? w[(size_t)c * K + TAPS] : 0.f;
     if (bias) bv = bias[c];
   }
   if (c < Hs) { db = dt_bias[c]; Ac = A[c]; }
@@ -239,16 +243,16 @@ __global__ void mamba_conv_decode_kernel(const T* __restrict__ proj, int ld, int
     const float cur = to_f32(proj[(size_t)b * ld + xbc_off + c]);
     float sum = bv;
 #pragma unroll
-    for (int k = 0; k < CONV_MAX_TAPS; k++)
+    for (int k = 0; k < TAPS; k++)
       if (k < K - 1) sum = fmaf(prev[k], wk[k], sum);
     float wl = 0.f;
 #pragma unroll
-    for (int k = 0; k <= CONV_MAX_TAPS; k++) if (k == K - 1) wl = wk[k];
+    for (int k = 0; k <= TAPS; k++) if (k == K - 1) wl = wk[k];
     sum = fmaf(cur, wl, sum);
     const float v = silu_f(sum);
     xbc_out[(size_t)b * Cd + c] = bf16_run ? as_operand<true>(v) : v;
 #pragma unroll
-    for (int k = 0; k < CONV_MAX_TAPS; k++) {
+    for (int k = 0; k < TAPS; k++) {
       if (k < K - 2) st[(size_t)k * Cd + c] = prev[k + 1];
       else if (k == K - 2) st[(size_t)k * Cd + c] = cur;
     }
@@ -282,9 +286,16 @@ extern "C" int tlc_mamba_conv(const void* proj, int dtype, int ld, int xbc_off, 
   dim3 grid2(B, (Cd + 255) / 256);
   if (single_rows && T == B) {
     TLC_REQUIRE(xbc_dtype == TLC_F32, "mamba_conv: single-token steps write 32-bit x|B|C");
-    TLC_DISPATCH_DTYPE(dtype, TT, tlc_launch(mamba_conv_decode_kernel<TT>, dim3(grid2), dim3(256), 0, stream,
-        (const TT*)proj, ld, xbc_off, dt_off, w, bias, dt_bias, A, conv_state, slots, start_pos, (float*)xbc_out, dt_out, dA_out,
-        Cd, K, Hs, quick));
+#define TLC_CONV_DECODE(KT)                                                                                          \
+  tlc_launch(mamba_conv_decode_kernel<TT, KT>, dim3(grid2), dim3(256), 0, stream, (const TT*)proj, ld, xbc_off, dt_off, w,  \
+             bias, dt_bias, A, conv_state, slots, start_pos, (float*)xbc_out, dt_out, dA_out, Cd, K, Hs, quick)
+    TLC_DISPATCH_DTYPE(dtype, TT, {
+      if (K == 4) TLC_CONV_DECODE(4);
+      else if (K == 3) TLC_CONV_DECODE(3);
+      else if (K == 2) TLC_CONV_DECODE(2);
+      else TLC_CONV_DECODE(0);
+    });
+#undef TLC_CONV_DECODE
     TLC_CHECK_LAUNCH("mamba_conv(decode)");
     return 0;
   }
