@@ -81,3 +81,25 @@ def test_one_layer_at_model_sizes_against_the_plain_implementation(tmp_path, nam
         got = llm.step([StepEntry(s, [p[-k]], [0]) for s, p in zip(slots, prompts)]).cpu().numpy()
         for i, p in enumerate(prompts):
             check(got[i:i + 1], want[i][len(p) - k:len(p) - k + 1], dtype, f"{name} layer, token -{k} of prompt {i}")
+
+
+@pytest.mark.parametrize("n_seqs", [24, 40])
+def test_steps_of_17_to_64_sequences_at_model_sizes_against_the_plain_implementation(tmp_path, n_seqs):
+    """One layer at the 1.5B sizes in bfloat16 with 24 and with 40 sequences: their short prompts in one step
+    (some 300 to 500 rows: the tiled products), then two single-token steps of all of them together, which is where
+    products of 17..64 rows run (weights on the wide side of the tensor-core instruction, a tile's K shared among
+    the blocks of a cluster: the wide outputs with 24 rows, the narrow ones too with 40)."""
+    cfg = dict(SIZES["1.5B"], vocab_size=512, max_position_embeddings=512)
+    d = make_model_dir(tmp_path, cfg, seed=12, std=0.02, name="layer")
+    g = np.random.default_rng(7)
+    prompts = [g.integers(0, cfg["vocab_size"], int(n)).tolist() for n in g.integers(6, 20, n_seqs)]
+    want = [expected(d, p, "bfloat16") for p in prompts]
+    llm = tlc.LLM(d, dtype="bfloat16", max_tokens=64 * n_seqs, max_seqs=n_seqs)
+    slots = [llm.cache.acquire() for _ in prompts]
+    got = llm.step([StepEntry(s, p[:-2], [len(p) - 3]) for s, p in zip(slots, prompts)]).cpu().numpy()
+    for i, p in enumerate(prompts):
+        check(got[i:i + 1], want[i][len(p) - 3:len(p) - 2], "bfloat16", f"{n_seqs} sequences, prompt {i}")
+    for k in (2, 1):
+        got = llm.step([StepEntry(s, [p[-k]], [0]) for s, p in zip(slots, prompts)]).cpu().numpy()
+        for i, p in enumerate(prompts):
+            check(got[i:i + 1], want[i][len(p) - k:len(p) - k + 1], "bfloat16", f"{n_seqs} sequences, token -{k} of {i}")
