@@ -34,6 +34,23 @@ PARALLEL_PROMPT_MIXERS = bool(int(os.environ.get("TLC_PARALLEL_PROMPT_MIXERS", "
 PROMPT_SIDE_BLOCKS = int(os.environ.get("TLC_PROMPT_SIDE_BLOCKS", "0"))
 
 
+_streams = {}
+
+
+def _current_stream(device) -> "torch.cuda.Stream":
+    """The current stream of the device as a torch object.  torch.cuda.current_stream() takes some 10 us of Python
+    a call and a block asks once a layer, so the object is kept by the stream's handle (which torch's raw query
+    gives in a fraction of that) and made anew only when the handle is a new one."""
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    handle = torch._C._cuda_getCurrentRawStream(index)
+    hit = _streams.get((index, handle))
+    if hit is None:
+        if len(_streams) > 64:
+            _streams.clear()
+        hit = _streams[(index, handle)] = torch.cuda.current_stream(index)
+    return hit
+
+
 class Block(Part):
     def __init__(self, spec: LayerSpec, act_dtype_of=None):
         self.spec = spec
@@ -91,7 +108,7 @@ class Block(Part):
         shared input projection.  Output projections add into the residual stream one after the
         other on the current stream, in the mixers' order, each after its mixer has finished.  (Under stream capture the
         side streams become parallel branches of the graph.)"""
-        main = torch.cuda.current_stream()
+        main = _current_stream(x32.device)
         if not hasattr(self, "_side"):
             self._side = [torch.cuda.Stream(device=x32.device) for _ in self.mixers[1:]]
             # events are made once: a record overwrites the event's last state, and every wait of this block follows
@@ -112,11 +129,14 @@ class Block(Part):
                 continue
             side = next(sides)
             side.wait_event(fork)
-            with torch.cuda.stream(side):
+            torch.cuda.set_stream(side)              # (the context manager asks for the current stream again: 10 us)
+            try:
                 bound = PROMPT_SIDE_BLOCKS if step.max_new > 1 and getattr(m, "mix_takes_max_blocks", False) else 0
                 acts[i] = self._mix(i, part, step, cache, views[i], max_blocks=bound)
                 done[i] = self._done[i]
                 done[i].record(side)
+            finally:
+                torch.cuda.set_stream(main)
         # The wait for the side streams breaks the chain of programmatic launches on this stream.  A mixer that
         # offers to (mix_takes_join) places it before its own last kernel; otherwise it comes after the mixer.
         joined = []
