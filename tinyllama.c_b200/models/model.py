@@ -13,7 +13,8 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from .. import ops
-from ..parts.base import ChunkRequest, LayerCache, LayerRun, LayerSpec, Part, PartSpec, StateRequest, StepInfo, WeightSpec
+from ..parts.base import (ChunkRequest, LayerCache, LayerRun, LayerSpec, Part, PartSpec, StateRequest, StepInfo, WeightSpec,
+                          step_scratch)
 from ..parts.block import Block
 from ..parts.linear import StackedLinear, matrix_dtype
 
@@ -88,8 +89,9 @@ class Model:
         wait, what earlier steps left in the cache (never what a kernel of this step writes)."""
         x = torch.empty((step.n_rows, self.hidden), dtype=torch.float32, device=self.device)
         ops.embed(step.tokens, self.embed_table, self.embed_scale, x)
-        for r, run in enumerate(self.schedule):
-            self.layers[run.layer].forward(x, step, cache.layer_view(r if run.cache is None else run.cache, run.writes))
+        with step_scratch(step):                       # the layers share the step's temporaries
+            for r, run in enumerate(self.schedule):
+                self.layers[run.layer].forward(x, step, cache.layer_view(r if run.cache is None else run.cache, run.writes))
         if want_rows is None or want_rows.numel() == 0:
             return None
         n = want_rows.numel()

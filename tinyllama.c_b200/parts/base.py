@@ -89,6 +89,8 @@ class StepInfo:
     host_slots: Tuple[int, ...] = ()
     # one table per chunk length that a part asked for with a ChunkRequest (see there)
     chunks: Dict[int, Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]]] = field(default_factory=dict)
+    # the step's temporaries (see scratch_buf)
+    scratch: Dict = field(default_factory=dict)
 
 
 @dataclass
@@ -221,3 +223,43 @@ def to_vec(t: torch.Tensor, device) -> torch.Tensor:
 def act_empty(shape, like: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """Uninitialised activation buffer on `like`'s device (its type unless `dtype` is given)."""
     return torch.empty(shape, dtype=dtype or like.dtype, device=like.device)
+
+
+# A step's temporaries.  Every layer needs the same dozen buffers (normed rows, projections, the scan's outputs,
+# ...) and an allocation costs some 3 us of host time, which is what short prompts are made of.  While a model
+# runs a step (Model.forward enters `step_scratch`), `scratch_buf` hands out one buffer per (tag, shape, type)
+# and the next layer gets the same one.  That is safe for the reason the allocator's own reuse is: a buffer's
+# next writer is launched on the model's stream after everything that read it (kernels of side streams are
+# waited for before the layer's output projection), and a kernel writes only after its wait on its predecessor.
+# Two buffers that are alive at the same time carry different tags.  The buffers go when the step's StepInfo
+# goes (a captured step keeps its StepInfo, and so its buffers, for as long as the graph lives).
+_scratch: Optional[dict] = None
+
+
+class step_scratch:
+    """Context manager: temporaries asked for inside come from (and stay in) `step.scratch`."""
+
+    def __init__(self, step: "StepInfo"):
+        self.store = step.scratch
+
+    def __enter__(self):
+        global _scratch
+        self.before, _scratch = _scratch, self.store
+        return self
+
+    def __exit__(self, *exc):
+        global _scratch
+        _scratch = self.before
+        return False
+
+
+def scratch_buf(tag: str, shape, dtype: torch.dtype, device) -> torch.Tensor:
+    """An uninitialised buffer for a temporary of the running step; the same one for the same (tag, shape, type)
+    until the step ends.  Outside a step it is a plain allocation."""
+    if _scratch is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    key = (tag, tuple(shape), dtype)
+    t = _scratch.get(key)
+    if t is None:
+        t = _scratch[key] = torch.empty(shape, dtype=dtype, device=device)
+    return t

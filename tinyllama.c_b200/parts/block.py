@@ -12,7 +12,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from .base import LayerCache, LayerSpec, Part, StepInfo, WeightSpec, act_empty
+from .base import LayerCache, LayerSpec, Part, StepInfo, WeightSpec, act_empty, scratch_buf
 from .linear import StackedLinear
 
 
@@ -175,16 +175,16 @@ class Block(Part):
         mixer's columns of it; (None, Nones) without a shared output projection."""
         if self.fused_out is None:
             return None, [None] * len(self.mixers)
-        joint = torch.empty((x32.shape[0], self.fused_out.in_features), dtype=self.dtype, device=x32.device)
+        joint = scratch_buf("block.joint", (x32.shape[0], self.fused_out.in_features), self.dtype, x32.device)
         return joint, [joint[:, off:off + n] for off, n in self.out_offsets]
 
     def forward(self, x32: torch.Tensor, step: StepInfo, cache: LayerCache) -> None:
         """Updates the float32 residual stream x32 [T, D] in place."""
         if self.mixers:
-            normed = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+            normed = scratch_buf("block.normed", x32.shape, self.dtype, x32.device)
             self.mixer_norm.forward(x32, normed)
             if self.fused_in is not None:
-                proj = torch.empty((x32.shape[0], self.fused_in.out_features), dtype=torch.float32, device=x32.device)
+                proj = scratch_buf("block.proj", (x32.shape[0], self.fused_in.out_features), torch.float32, x32.device)
                 self.fused_in.forward(normed, proj)
                 parts = [proj[:, off:off + n] for off, n in self.fused_offsets]
                 if (step.max_new == 1 or PARALLEL_PROMPT_MIXERS) and x32.is_cuda and PARALLEL_MIXERS and all(hasattr(m, "mix") for m in self.mixers):
@@ -201,6 +201,6 @@ class Block(Part):
                 for m in self.mixers:
                     m.forward(normed, step, cache, x32)
         if self.ffn is not None:
-            normed = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+            normed = scratch_buf("block.ffn_normed", x32.shape, self.dtype, x32.device)
             self.ffn_norm.forward(x32, normed)
             self.ffn.forward(normed, x32)

@@ -12,7 +12,7 @@ from typing import Dict, List
 import torch
 
 from .. import ops
-from .base import Part, WeightSpec, act_empty, register_feed_forward
+from .base import Part, WeightSpec, act_empty, register_feed_forward, scratch_buf
 from .linear import StackedLinear
 
 
@@ -48,11 +48,11 @@ class SwiGLU(Part):
 
     def forward(self, normed: torch.Tensor, residual: torch.Tensor) -> None:
         T = normed.shape[0]
-        act = act_empty((T, self.F), normed)
+        act = scratch_buf("swiglu.act", (T, self.F), normed.dtype, normed.device)
         if self.interleaved:
             ops.linear_swiglu(normed, self.gate_up.weight, act, self.gate_up.colscale, self.gate_up.colbias)
         else:
-            gu = act_empty((T, 2 * self.F), normed, torch.float32)
+            gu = scratch_buf("swiglu.gate_up", (T, 2 * self.F), torch.float32, normed.device)
             self.gate_up.forward(normed, gu)
             ops.swiglu(gu, act)
         self.down.forward(act, residual, accumulate=True)

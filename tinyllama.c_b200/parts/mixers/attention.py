@@ -14,7 +14,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ... import ops
-from ..base import KVRequest, LayerCache, Part, PartSpec, StepInfo, WeightSpec, act_empty, register_mixer
+from ..base import KVRequest, LayerCache, Part, PartSpec, StepInfo, WeightSpec, act_empty, register_mixer, scratch_buf
 from ..linear import StackedLinear
 
 
@@ -104,16 +104,16 @@ class AttentionMixer(Part):
             table = self._no_rotation
         if step.max_new == 1 and ops.attention_decode_fused_ok(qkv, self.dtype, self.H, self.KV, self.hd):
             # one token per sequence: rotation, store and attention in one kernel
-            att = out if out is not None else torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
+            att = out if out is not None else scratch_buf(f"attention.{self.cache_key}.out", (T, self.H * self.hd), self.dtype, qkv.device)
             ops.attention_decode_fused(qkv, self.q_off, self.k_off, self.v_off, kv.k_pages, kv.v_pages, table,
                                        cache.writes, kv.block_table, step.positions, step.row_seq, step.slots, att,
                                        self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
                                        step.max_context, self._arrivals)
             return att
-        q = torch.empty((T, self.H * self.hd), dtype=self.dtype, device=qkv.device)
+        q = scratch_buf(f"attention.{self.cache_key}.q", (T, self.H * self.hd), self.dtype, qkv.device)
         ops.rope_kv_store(qkv, self.q_off, self.k_off, self.v_off, q, kv.k_pages, kv.v_pages, table, step.positions,
                           step.row_seq, step.slots, kv.block_table, self.H, self.KV, self.hd, cache.writes)
-        att = out if out is not None else torch.empty_like(q)
+        att = out if out is not None else scratch_buf(f"attention.{self.cache_key}.out", (T, self.H * self.hd), self.dtype, qkv.device)
         ops.attention(q, kv.k_pages, kv.v_pages, kv.block_table, step.positions, step.row_seq, step.slots, att,
                       self.H, self.KV, self.hd, 1.0 / math.sqrt(self.hd), self.window or 0,
                       step.max_context if step.max_new == 1 else 0, step.cu_seqlens, step.start_pos, step.max_context,

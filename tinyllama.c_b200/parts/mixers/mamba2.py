@@ -18,7 +18,7 @@ from typing import Callable, Dict, List, Optional, Sequence
 import torch
 
 from ... import ops
-from ..base import ChunkRequest, LayerCache, Part, StateRequest, StepInfo, WeightSpec, act_empty, register_mixer, to_vec
+from ..base import ChunkRequest, LayerCache, Part, StateRequest, StepInfo, WeightSpec, act_empty, register_mixer, scratch_buf, to_vec
 from ..linear import StackedLinear
 
 
@@ -127,25 +127,25 @@ class Mamba2Mixer(Part):
         T, f32 = step.n_rows, torch.float32
         conv_state = cache.state[self.cache_key + ".conv"]
         ssm_state = cache.state[self.cache_key + ".ssm"]
-        new = lambda shape, dtype: torch.empty(shape, dtype=dtype, device=proj.device)
+        new = lambda tag, shape, dtype: scratch_buf(f"mamba2.{self.cache_key}.{tag}", shape, dtype, proj.device)   # (two mixers of a layer have two keys)
         # prompts cut into chunks of a bfloat16 run: the scan in matrix form, whose operands x|B|C the convolution
         # writes in bfloat16 at once; everything else scans 32-bit values
         chunks = step.chunks.get(self.scan_chunk)
         matrix_form = chunks is not None and self.dtype == torch.bfloat16 and self.scan_chunk <= ops.SSD_CHUNK \
             and ops.ssd_ok(self.Hs, self.P, self.N, self.G)
-        xbc = new((T, self.Cd), torch.bfloat16 if matrix_form else f32)
-        dt, dA = new((T, self.Hs), f32), new((T, self.Hs), f32)
+        xbc = new("xbc", (T, self.Cd), torch.bfloat16 if matrix_form else f32)
+        dt, dA = new("dt", (T, self.Hs), f32), new("dA", (T, self.Hs), f32)
         ops.mamba_conv(proj, self.Di, self.Di + self.Cd, self.conv_w, self.conv_b, self.dt_bias, self.A, conv_state,
                        step.cu_seqlens, step.row_seq, step.slots, step.start_pos, xbc, dt, dA,
                        step.max_new == 1, self.dtype == torch.bfloat16,
                        len(step.host_start) == step.n_seqs and not any(step.host_start))
-        y = new((T, self.Di), f32)
+        y = new("y", (T, self.Di), f32)
         # in matrix form the outputs may come as two summands, the one that needs no state computed beside the walk
         # over the chunks; the gated norm adds them
-        y_part = new((T, self.Di), f32) if matrix_form else None
+        y_part = new("y_part", (T, self.Di), f32) if matrix_form else None
         in_two = ops.ssm_scan(xbc, dt, dA, self.D, ssm_state, step.cu_seqlens, step.slots, step.start_pos, y, self.Hs,
                               self.P, self.N, self.G, chunks, self.A if matrix_form else None, y_part)
-        gated = out if out is not None else new((T, self.Di), self.dtype)
+        gated = out if out is not None else new("gated", (T, self.Di), self.dtype)
         if join is not None:
             join()
         ops.gated_rmsnorm(y, proj[:, :self.Di], self.norm_w, self.eps, self.G, self.norm_before_gate, gated,
