@@ -35,11 +35,11 @@ class StepError(ValueError):
     pass
 
 
-def chunk_table(lens: Sequence[int], rows: int):
+def chunk_table(lens: Sequence[int], rows: int, from_rows: Optional[int] = None):
     """Cuts sequences of `lens` new rows, packed back to back, into chunks of at most `rows` rows:
     (first packed row of every chunk + the total [n+1], sequence of every chunk [n], first chunk of every
-    sequence [B+1]); None when no sequence is longer than a chunk."""
-    if not any(n > rows for n in lens):
+    sequence [B+1]); None when no sequence has more than `from_rows` rows (a chunk's length unless given)."""
+    if not any(n > (rows if from_rows is None else from_rows) for n in lens):
         return None
     seg_start, seg_seq, seq_seg_start, t0 = [], [], [0], 0
     for b, n in enumerate(lens):
@@ -53,10 +53,11 @@ def chunk_table(lens: Sequence[int], rows: int):
 
 
 def pack(entries: Sequence[StepEntry], starts: Sequence[int], vocab: int, device,
-         chunk_rows: Sequence[int] = ()) -> Tuple[StepInfo, torch.Tensor, int]:
+         chunk_rows: Sequence[int] = (), chunk_from: Optional[dict] = None) -> Tuple[StepInfo, torch.Tensor, int]:
     """Host lists -> one int32 buffer (pinned for a GPU) -> one copy to the device -> StepInfo views.
     Returns (step, packed rows whose logits are wanted, their count).  chunk_rows: the chunk lengths
-    that parts of the model asked for (ChunkRequest); the step gets one table for each.
+    that parts of the model asked for (ChunkRequest); the step gets one table for each.  chunk_from: for a chunk
+    length, the number of rows a sequence must exceed for its table to be made (the length itself unless given).
 
     The GPU waits while this runs (a prompt step starts with it), so rows are filled as arrays, not one by one."""
     B = len(entries)
@@ -72,7 +73,7 @@ def pack(entries: Sequence[StepEntry], starts: Sequence[int], vocab: int, device
                 raise StepError(f"wanted index {w} is outside this step's {lens[b]} tokens")
             want_rows.append(cu[b] + int(w))
     W = len(want_rows)
-    tables = {int(r): chunk_table(lens, int(r)) for r in sorted(set(chunk_rows))}
+    tables = {int(r): chunk_table(lens, int(r), (chunk_from or {}).get(int(r))) for r in sorted(set(chunk_rows))}
     tail: List[int] = cu + [e.slot for e in entries] + [int(s) for s in starts] + want_rows
     for tab in tables.values():
         if tab is not None:
@@ -127,7 +128,8 @@ def step(model: Model, cache: Cache, entries: Sequence[StepEntry]) -> Optional[t
         if len(e.tokens) == 0:
             raise StepError("a step entry brings no tokens")
     starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
-    info, want_rows, n_want = pack(entries, starts, model.vocab, model.device, model.chunk_rows)
+    info, want_rows, n_want = pack(entries, starts, model.vocab, model.device, model.chunk_rows,
+                                   getattr(model, "chunk_from", None))
     cache.upload_tables()
     logits = model.forward(info, cache, want_rows if n_want else None)
     for e in entries:

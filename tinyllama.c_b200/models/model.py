@@ -37,8 +37,15 @@ class Model:
                 raise ValueError(f"run-order entry {r} reads the cache of entry {run.cache} but layer {run.layer} has a "
                                  f"mixer with state of its own: only keys and values can be read without storing")
         # chunk lengths that parts want the step function to cut sequences into (one table each, every step)
-        self.chunk_rows = tuple(sorted({q.rows for layer in self.layers for q in layer.step_requests()
-                                        if isinstance(q, ChunkRequest)}))
+        # as (rows, from how many rows of a sequence the table is wanted): the smallest threshold asked for a length
+        asked: Dict[int, int] = {}
+        for layer in self.layers:
+            for q in layer.step_requests():
+                if isinstance(q, ChunkRequest):
+                    start = q.rows if q.from_rows is None else min(q.rows, q.from_rows)
+                    asked[q.rows] = min(asked.get(q.rows, start), start)
+        self.chunk_rows = tuple(sorted(asked))
+        self.chunk_from = dict(asked)               # chunk length -> rows a sequence must exceed for the table to be made
         self.final_norm = final_norm.build()
         self.embed_name, self.head_name = embed_name, head_name            # head_name None: tied (core.c:1246-1249)
         self.embed_scale = float(embed_scale)

@@ -59,10 +59,12 @@ class StateRequest:
 class ChunkRequest:
     """A table, built by the step function for every step, that cuts each sequence's new rows into
     chunks of at most ``rows`` rows (a recurrent mixer scans chunks in parallel and carries the state
-    between them).  The mixer finds it as ``step.chunks[rows]``: None when no sequence of the step is
-    longer than a chunk, else (first row of every chunk [n+1], sequence of every chunk [n], first chunk
-    of every sequence [B+1]), int32 on the device."""
+    between them).  The mixer finds it as ``step.chunks[rows]``: None when no sequence of the step brings
+    more than ``from_rows`` rows (a chunk's length unless given: a mixer whose chunked form already pays for
+    shorter sequences says from how many rows), else (first row of every chunk [n+1], sequence of every chunk
+    [n], first chunk of every sequence [B+1]), int32 on the device."""
     rows: int
+    from_rows: Optional[int] = None
 
 
 # ---- what a step gives every part ------------------------------------------------------------

@@ -42,7 +42,10 @@ def _current_stream(device) -> "torch.cuda.Stream":
     a call and a block asks once a layer, so the object is kept by the stream's handle (which torch's raw query
     gives in a fraction of that) and made anew only when the handle is a new one."""
     index = device.index if device.index is not None else torch.cuda.current_device()
-    handle = torch._C._cuda_getCurrentRawStream(index)
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is None:
+        return torch.cuda.current_stream(index)
+    handle = raw(index)
     hit = _streams.get((index, handle))
     if hit is None:
         if len(_streams) > 64:

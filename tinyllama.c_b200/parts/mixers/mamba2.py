@@ -79,8 +79,13 @@ class Mamba2Mixer(Part):
         return [StateRequest(self.cache_key + ".conv", (self.K - 1, self.Cd)),
                 StateRequest(self.cache_key + ".ssm", (self.Hs, self.P, self.N))]
 
+    # The row-by-row scan of a sequence takes 1 to 2 us a row and layer (a 128-token prompt of the 1.5B sizes: 9.5 ms,
+    # against 4.7 ms for 129 tokens, whose chunks run in matrix form); from this many rows on a sequence is
+    # scanned as chunks even when it is no longer than one.
+    CHUNKS_FROM_ROWS = 32
+
     def step_requests(self) -> list:
-        return [ChunkRequest(self.scan_chunk)]
+        return [ChunkRequest(self.scan_chunk, min(self.scan_chunk, self.CHUNKS_FROM_ROWS))]
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
         p = self.prefix
