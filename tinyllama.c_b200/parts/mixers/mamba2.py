@@ -79,10 +79,14 @@ class Mamba2Mixer(Part):
         return [StateRequest(self.cache_key + ".conv", (self.K - 1, self.Cd)),
                 StateRequest(self.cache_key + ".ssm", (self.Hs, self.P, self.N))]
 
-    # The row-by-row scan of a sequence takes 1 to 2 us a row and layer (a 128-token prompt of the 1.5B sizes: 9.5 ms,
-    # against 4.7 ms for 129 tokens, whose chunks run in matrix form); from this many rows on a sequence is
-    # scanned as chunks even when it is no longer than one.
-    CHUNKS_FROM_ROWS = 32
+    # The row-by-row scan of a sequence takes 1 to 2 us a row and layer, more in a batch (a 128-token prompt of the
+    # 1.5B sizes: 9.5 ms against 4.8 ms as one chunk in matrix form; 32 prompts of 128 tokens: 55 ms against 14.8;
+    # 64 of 20 tokens: 20.4 against 11.8).  So the step's chunk table is asked for as soon as a sequence brings
+    # more than CHUNKS_FROM_ROWS rows, and used when a sequence has more than 32 rows or the step has at least
+    # 128: a few short sequences are quicker row by row (one prompt of 30 tokens: 4.0 ms against 4.5, the chunked
+    # form's extra launches).
+    CHUNKS_FROM_ROWS = 8
+    CHUNKS_WORTH_ROWS, CHUNKS_WORTH_STEP = 32, 128
 
     def step_requests(self) -> list:
         return [ChunkRequest(self.scan_chunk, min(self.scan_chunk, self.CHUNKS_FROM_ROWS))]
@@ -136,6 +140,8 @@ class Mamba2Mixer(Part):
         # prompts cut into chunks of a bfloat16 run: the scan in matrix form, whose operands x|B|C the convolution
         # writes in bfloat16 at once; everything else scans 32-bit values
         chunks = step.chunks.get(self.scan_chunk)
+        if chunks is not None and step.max_new <= self.CHUNKS_WORTH_ROWS and step.n_rows < self.CHUNKS_WORTH_STEP:
+            chunks = None
         matrix_form = chunks is not None and self.dtype == torch.bfloat16 and self.scan_chunk <= ops.SSD_CHUNK \
             and ops.ssd_ok(self.Hs, self.P, self.N, self.G)
         xbc = new("xbc", (T, self.Cd), torch.bfloat16 if matrix_form else f32)
