@@ -111,7 +111,7 @@ def rope_kv_store(qkv, q_off, k_off, v_off, q_out, k_pages, v_pages, inv_freq, p
 
 
 def attention(q, k_pages, v_pages, block_table, positions, row_seq, slots, out, H, KV, hd, scale, window=0,
-              decode_max_keys=0, cu_seqlens=None, start_pos=None, max_keys=0, max_blocks=0):
+              decode_max_keys=0, cu_seqlens=None, start_pos=None, max_keys=0, max_blocks=0, key_ranges=0):
     T = q.shape[0]
     res = torch.zeros((T, H, hd), dtype=torch.float64)
     qf = _f(q).reshape(T, H, hd)

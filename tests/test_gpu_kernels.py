@@ -479,6 +479,28 @@ def test_attention_of_prompts_on_a_bounded_number_of_blocks(H, KV, hd, window, m
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2]), "the result depends on the number of blocks"
 
 
+@pytest.mark.parametrize("key_ranges", [0, 2, 3, 8])
+@pytest.mark.parametrize("H,KV,hd,window", [(8, 2, 128, 0), (3, 1, 64, 0), (4, 4, 128, 700)])
+def test_attention_of_prompt_pieces_with_the_keys_in_ranges(H, KV, hd, window, key_ranges):
+    """The tcgen05 kernel with the keys of every row tile cut into ranges that run as items of their own and are added
+    up by a second kernel: a 70-row piece at position 3,000 (what the kernel chooses ranges for by itself), a
+    200-row piece at position 130, short sequences most of whose ranges are empty, a window; a far key stands out."""
+    g = gen(38)
+    starts, lens = [3000, 130, 0, 2100], [70, 200, 3, 129]
+    pos, row_seq, cu, start_pos = _step_arrays(starts, lens)
+    totals = [s + n for s, n in zip(starts, lens)]
+    slots, table, k_pages, v_pages = _paged_setup(g, 4, totals, KV, hd, torch.bfloat16, n_slots=6)
+    T = sum(lens)
+    q = rnd(g, T, H * hd, dtype=torch.bfloat16)
+    k_pages[int(table[int(slots[0]), 1]), :, 9, :] *= 4.0        # position 73 of the long sequence: in the first range
+    k_pages[int(table[int(slots[0]), 40]), :, 10, :] *= 6.0      # position 2,570: in a late range
+    args = [q, k_pages, v_pages, table, pos, row_seq, slots, torch.empty(T, H * hd, dtype=torch.bfloat16), H, KV, hd,
+            1.0 / math.sqrt(hd), window, 0, cu, start_pos, max(totals), 0, key_ranges]
+    cmp("attention", args, [7], tol_of=TOL[torch.bfloat16] * 2.5)
+    torch.cuda.synchronize()
+    ops.check_errors()
+
+
 @pytest.mark.parametrize("H,KV,hd,window", [(4, 2, 128, 0), (2, 1, 64, 0), (4, 4, 64, 700)])
 def test_attention_of_long_prompts_in_pieces(H, KV, hd, window):
     """Key ranges of more than 8 pages are cut into pieces that run side by side and are merged: a prompt of

@@ -74,7 +74,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table, int max_pages,
                             const int* __restrict__ cu_seqlens, const int* __restrict__ slots,
                             const int* __restrict__ start_pos, __nv_bfloat16* __restrict__ out, int n_seqs, int n_tiles, int H,
-                            int KV, float scale_log2, int window, int out_ld, ErrWords* err) {
+                            int KV, float scale_log2, int window, int out_ld, int n_split, float* __restrict__ part_o,
+                            float* __restrict__ part_ml, ErrWords* err) {
   tlc_pdl(out);
   using L_ = FaSmem<HD>;
   constexpr int TCOLS = HD == 128 ? 512 : 256;            // the groups' scores at 0 and 64, their outputs at 128 and 128 + hd
@@ -119,15 +120,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   // (back and forth, so that every block gets long and short ones): the kernel then holds nb SMs, each for
   // about the same time, and leaves the others to kernels of other streams.  Between items the barriers are
   // made anew; tensor memory and the tiles of shared memory are simply used again.
-  const int n_items = n_tiles * H, nb = (int)gridDim.x;
+  // With n_split > 1 (few row tiles and many keys: a piece of a long prompt) an item is also one of n_split
+  // ranges of the tile's key tiles: it leaves its rows' maxima, sums and unnormalised outputs in part_ml
+  // [T, H, n_split, 2] and part_o [T, H, n_split, hd], and attention_tc_merge_kernel adds the ranges up.
+  const int n_items = n_tiles * H * n_split, nb = (int)gridDim.x;
 #pragma unroll 1
   for (int round = 0;; round++) {
   const int item = round * nb + ((round & 1) ? nb - 1 - (int)blockIdx.x : (int)blockIdx.x);
   if (item >= n_items) break;
-  const int h = item % H;
+  const int key_range = item % n_split, h = (item / n_split) % H;
   // which sequence, and which of its 128-row tiles, is this item's
   if (tid == 0) {
-    int tile = n_tiles - 1 - item / H, found = -1, row0 = 0;
+    int tile = n_tiles - 1 - item / (H * n_split), found = -1, row0 = 0;
     for (int b = 0; b < n_seqs; b++) {
       const int nt = (cu_seqlens[b + 1] - cu_seqlens[b] + BM - 1) / BM;
       if (tile < nt) { found = b; row0 = tile * BM; break; }
@@ -151,9 +155,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int t0 = cu_seqlens[b], n_new = cu_seqlens[b + 1] - t0;
   const int rows = min(BM, n_new - i0);
   const int p0 = start_pos[b] + i0;                       // position of the block's first row
-  const int tile_hi = (p0 + rows - 1) / BN;
-  const int tile_lo = window > 0 ? max(0, p0 + 1 - window) / BN : 0;
-  const int n = tile_hi - tile_lo + 1;                    // key tiles of this item
+  const int tile_hi_all = (p0 + rows - 1) / BN;
+  const int tile_lo_all = window > 0 ? max(0, p0 + 1 - window) / BN : 0;
+  const int per_range = (tile_hi_all - tile_lo_all + n_split) / n_split;             // key tiles of a range, rounded up
+  const int tile_lo = tile_lo_all + key_range * per_range;
+  const int tile_hi = min(tile_hi_all, tile_lo + per_range - 1);
+  const int n = max(0, tile_hi - tile_lo + 1);            // key tiles of this item (none: a range past the tile's keys)
   for (int i = tid; i < n; i += THREADS) pages[i] = block_table[(size_t)slots[b] * max_pages + tile_lo + i];
   __syncthreads();
 
@@ -314,24 +321,37 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const float m0 = xch[r], m1 = xch[BM + r];
     const float m_all = fmaxf(m0, m1);
     const float w0 = m0 == -INFINITY ? 0.f : ex2_quick(m0 - m_all), w1 = m1 == -INFINITY ? 0.f : ex2_quick(m1 - m_all);
-    const float inv = 1.0f / (xch[NG * BM + r] * w0 + xch[(NG + 1) * BM + r] * w1);
+    const float l_all = xch[NG * BM + r] * w0 + xch[(NG + 1) * BM + r] * w1;
+    const bool whole = n_split == 1;                      // else the sums stay unnormalised: another kernel adds the ranges
+    const float inv = whole ? 1.0f / l_all : 1.0f;
     const float f0 = w0 * inv, f1 = w1 * inv;
-    const bool has1 = n > 1;                              // the second group had a tile at all (else its output is not written)
+    const bool has0 = n > 0, has1 = n > 1;                // the group had a tile at all (else its accumulator was never written)
+    const size_t part_at = whole ? 0 : (((size_t)(t0 + i0 + r) * H + h) * n_split + key_range);
+    if (!whole && wg == 0 && r < rows) {
+      part_ml[part_at * 2] = has0 ? m_all : -INFINITY;
+      part_ml[part_at * 2 + 1] = has0 ? l_all : 0.f;
+    }
     __syncwarp();
 #pragma unroll 1
     for (int c = 0; c < HD / 64; c++) {                   // the group's half of the output columns, 32 at a time
       const int col = wg * (HD / 2) + 32 * c;
       uint32_t o[32];
       float acc[32];
-      tmem_ld32(tmem + lanes + 128u + (uint32_t)col, o);
+      if (has0) tmem_ld32(tmem + lanes + 128u + (uint32_t)col, o);
 #pragma unroll
-      for (int e = 0; e < 32; e++) acc[e] = __uint_as_float(o[e]) * f0;
+      for (int e = 0; e < 32; e++) acc[e] = has0 ? __uint_as_float(o[e]) * f0 : 0.f;
       if (has1) {
         tmem_ld32(tmem + lanes + 128u + (uint32_t)(HD + col), o);
 #pragma unroll
         for (int e = 0; e < 32; e++) acc[e] = fmaf(__uint_as_float(o[e]), f1, acc[e]);
       }
-      if (r < rows) {
+      if (!whole) {
+        if (r < rows) {
+          float4* dst = reinterpret_cast<float4*>(part_o + part_at * HD + col);
+#pragma unroll
+          for (int q = 0; q < 8; q++) dst[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+        }
+      } else if (r < rows) {
         uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(t0 + i0 + r) * out_ld + (size_t)h * HD + col);
 #pragma unroll
         for (int q = 0; q < 4; q++)
@@ -349,6 +369,45 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }  // items
   if (warp == 0)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TCOLS) : "memory");
+}
+
+// The ranges of a row's keys added up: out = sum_z o_z 2^(m_z - m) / sum_z l_z 2^(m_z - m), m the largest m_z of a
+// range that had keys (the maxima are in the scaled log2 domain already).  grid (T, ceil(H / 4)), a warp per
+// (row, head), a lane per 4 head dims (and their next 128).
+constexpr int TC_MAX_SPLIT = 8;
+__global__ void __launch_bounds__(128)
+attention_tc_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
+                          int H, int hd, int n_split, int out_ld) {
+  tlc_pdl(part_o, part_ml, out);
+  const int t = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (h >= H) return;
+  const size_t at = ((size_t)t * H + h) * n_split;
+  float mz[TC_MAX_SPLIT], lz[TC_MAX_SPLIT], m = -INFINITY;
+#pragma unroll
+  for (int z = 0; z < TC_MAX_SPLIT; z++) {
+    mz[z] = z < n_split ? part_ml[(at + z) * 2] : -INFINITY;
+    lz[z] = z < n_split ? part_ml[(at + z) * 2 + 1] : 0.f;
+    if (lz[z] > 0.f) m = fmaxf(m, mz[z]);
+  }
+  float w[TC_MAX_SPLIT], l = 0.f;
+#pragma unroll
+  for (int z = 0; z < TC_MAX_SPLIT; z++) {
+    w[z] = lz[z] > 0.f ? exp2f(mz[z] - m) : 0.f;
+    l += lz[z] * w[z];
+  }
+  const float inv = 1.0f / l;
+  for (int d = lane * 4; d < hd; d += 128) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int z = 0; z < TC_MAX_SPLIT; z++) {
+      if (z < n_split && w[z] != 0.f) {
+        const float4 v = *reinterpret_cast<const float4*>(part_o + (at + z) * hd + d);
+        acc.x = fmaf(v.x, w[z], acc.x); acc.y = fmaf(v.y, w[z], acc.y); acc.z = fmaf(v.z, w[z], acc.z); acc.w = fmaf(v.w, w[z], acc.w);
+      }
+    }
+    __nv_bfloat16* o = out + (size_t)t * out_ld + (size_t)h * hd + d;
+    *reinterpret_cast<uint2*>(o) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));
+  }
 }
 
 // tensor maps of the cache pages, which stay where they are for the cache's lifetime
@@ -377,7 +436,7 @@ template <int HD>
 int run(const __nv_bfloat16* q, const __nv_bfloat16* k_pages, const __nv_bfloat16* v_pages, long long n_page_rows,
         const int* block_table, int max_pages, const int* cu_seqlens, const int* slots, const int* start_pos,
         __nv_bfloat16* out, int n_seqs, int n_tiles_bound, int H, int KV, float scale, int window,
-        int p_max, int T, int out_ld, int max_blocks, cudaStream_t stream) {
+        int p_max, int T, int out_ld, int max_blocks, int n_split, float* part_o, float* part_ml, cudaStream_t stream) {
   static bool configured = false;
   const int smem = FaSmem<HD>::total(p_max);
   TLC_REQUIRE(smem <= 220 * 1024, "attention(prefill, tcgen05): %d key tiles need %d bytes of shared memory", p_max, smem);
@@ -390,16 +449,34 @@ int run(const __nv_bfloat16* q, const __nv_bfloat16* k_pages, const __nv_bfloat1
   if (int rc = tlc_tensor_map_bf16(q, T, (long long)H * HD, (long long)H * HD, 64, BM, &mq)) return rc;
   if (int rc = page_map(k_pages, n_page_rows, HD, &mk)) return rc;
   if (int rc = page_map(v_pages, n_page_rows, HD, &mv)) return rc;
-  const long long items = (long long)n_tiles_bound * H;
+  const long long items = (long long)n_tiles_bound * H * n_split;
   const int blocks = (int)(max_blocks > 0 && max_blocks < items ? max_blocks : items);
   tlc_launch(attention_prefill_tc_kernel<HD>, dim3(blocks), dim3(THREADS), (size_t)smem, stream, mq, mk, mv,
              block_table, max_pages, cu_seqlens, slots, start_pos, out, n_seqs, n_tiles_bound, H, KV, scale * 1.4426950408889634f,
-             window, out_ld, tlc_error_words());
+             window, out_ld, n_split, part_o, part_ml, tlc_error_words());
   TLC_CHECK_LAUNCH("attention(prefill, tcgen05)");
+  if (n_split > 1) {
+    tlc_launch(attention_tc_merge_kernel, dim3(T, (H + 3) / 4), dim3(128), 0, stream, (const float*)part_o, (const float*)part_ml, out, H,
+               HD, n_split, out_ld);
+    TLC_CHECK_LAUNCH("attention(prefill, tcgen05, merge)");
+  }
   return 0;
 }
 
 }  // namespace
+
+// How many ranges to cut the keys of every row tile into: more than one when the (tile, head) items leave more than
+// half of the SMs idle and the longest sequence has at least 32 key tiles (a piece of a long prompt: 512 new rows
+// at position 33,000 of the 1.5B sizes are 40 items of 530 key tiles, 13.2 ms a step; in three ranges 7 ms).
+extern "C" int tlc_attention_prefill_tc_splits(int n_tiles_bound, int H, int max_keys) {
+  static int sms = 0;
+  if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  const long long items = (long long)n_tiles_bound * H;
+  const int p_max = (max_keys + BN - 1) / BN;
+  if (items <= 0 || items * 2 > sms || p_max < 32) return 1;
+  const int n = (int)std::min<long long>(std::min<long long>(TC_MAX_SPLIT, sms / items), p_max / 16);
+  return n < 2 ? 1 : n;
+}
 
 extern "C" int tlc_attention_prefill_tc_ok(int dtype, int hd, int H, int KV) {
   return dtype == TLC_BF16 && (hd == 64 || hd == 128) && KV > 0 && H % KV == 0 && H <= 65535 && KV <= 65535;
@@ -409,11 +486,14 @@ extern "C" int tlc_attention_prefill_tc_ok(int dtype, int hd, int H, int KV) {
 // sequence after this step; n_pages: pages of the cache (k_pages and v_pages are [n_pages, KV, 64, hd]).
 // max_blocks: 0, or how many blocks (hence SMs) the kernel may hold: it then works through its (tile, head) items
 // with that many blocks, for callers that run other kernels beside it.
+// n_split > 1 (at most 8; tlc_attention_prefill_tc_splits suggests it): the keys of every row tile are cut into
+// that many ranges that run as items of their own; part_o [T, H, n_split, hd] and part_ml [T, H, n_split, 2]
+// (32-bit) hold the ranges' results until a second kernel has added them up.
 extern "C" int tlc_attention_prefill_tc(const void* q, const void* k_pages, const void* v_pages, int n_pages,
                                         const int* block_table, int max_pages, const int* cu_seqlens, const int* slots,
                                         const int* start_pos, void* out, int n_seqs, int n_tiles_bound, int H, int KV,
                                         int hd, float scale, int window, int max_keys, int T, int out_ld, int max_blocks,
-                                        cudaStream_t stream) {
+                                        int n_split, float* part_o, float* part_ml, cudaStream_t stream) {
   if (n_seqs == 0 || n_tiles_bound == 0 || T == 0) return 0;
   if (out_ld <= 0) out_ld = H * hd;
   TLC_REQUIRE(tlc_attention_prefill_tc_ok(TLC_BF16, hd, H, KV), "attention(prefill, tcgen05): %d heads, %d key/value heads of size %d are not built", H, KV, hd);
@@ -422,11 +502,14 @@ extern "C" int tlc_attention_prefill_tc(const void* q, const void* k_pages, cons
   TLC_REQUIRE(tlc_error_words() != nullptr, "attention(prefill, tcgen05): the library is not set up (tlc_linear_init)");
   const int p_max = (max_keys + BN - 1) / BN;
   TLC_REQUIRE(p_max >= 1 && p_max <= 65535, "attention(prefill, tcgen05): %d keys", max_keys);
+  if (n_split < 1) n_split = 1;
+  TLC_REQUIRE(n_split <= TC_MAX_SPLIT && (n_split == 1 || (part_o != nullptr && part_ml != nullptr && ((uintptr_t)part_o % 16) == 0)),
+              "attention(prefill, tcgen05): %d key ranges need 16-byte aligned scratch (at most %d ranges)", n_split, TC_MAX_SPLIT);
   const long long rows = (long long)n_pages * KV * BN;
   const __nv_bfloat16 *qp = (const __nv_bfloat16*)q, *kp = (const __nv_bfloat16*)k_pages, *vp = (const __nv_bfloat16*)v_pages;
   if (hd == 64)
     return run<64>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out,
-                   n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, stream);
+                   n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, n_split, part_o, part_ml, stream);
   return run<128>(qp, kp, vp, rows, block_table, max_pages, cu_seqlens, slots, start_pos, (__nv_bfloat16*)out,
-                  n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, stream);
+                  n_seqs, n_tiles_bound, H, KV, scale, window, p_max, T, out_ld, max_blocks, n_split, part_o, part_ml, stream);
 }

@@ -162,7 +162,8 @@ int tlc_attention_prefill_tc(const void* q, const void* k_pages, const void* v_p
                              const int* block_table, int max_pages, const int* cu_seqlens, const int* slots,
                              const int* start_pos, void* out, int n_seqs, int n_tiles_bound, int H, int KV,
                              int hd, float scale, int window, int max_keys, int T, int out_ld, int max_blocks,
-                             cudaStream_t stream);
+                             int n_split, float* part_o, float* part_ml, cudaStream_t stream);
+int tlc_attention_prefill_tc_splits(int n_tiles_bound, int H, int max_keys);   // suggested n_split (1: none)
 
 /* ---- Mamba2 (mamba.cu, mamba_ssd.cu) ----------------------------------------------------------------- */
 /* Causal depthwise convolution + SiLU over the x|B|C columns of proj, continuing each sequence's window

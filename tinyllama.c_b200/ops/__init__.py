@@ -77,7 +77,8 @@ _SIGNATURES = {
                                    _vp, _i, _i, _vp]),
     "tlc_attention_prefill_tc_ok": (_i, [_i, _i, _i, _i]),
     "tlc_attention_prefill_tc": (_i, [_vp, _vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _i,
-                                      _i, _i, _i, _vp]),
+                                      _i, _i, _i, _i, _vp, _vp, _vp]),
+    "tlc_attention_prefill_tc_splits": (_i, [_i, _i, _i]),
     "tlc_mamba_conv": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i,
                             _i, _i, _i, _i, _i, _i, _vp]),
     "tlc_ssm_scan": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
@@ -437,7 +438,7 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
               positions: torch.Tensor, row_seq: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, H: int, KV: int,
               hd: int, scale: float, window: int = 0, decode_max_keys: int = 0,
               cu_seqlens: Optional[torch.Tensor] = None, start_pos: Optional[torch.Tensor] = None,
-              max_keys: int = 0, max_blocks: int = 0) -> None:
+              max_keys: int = 0, max_blocks: int = 0, key_ranges: int = 0) -> None:
     """Causal grouped-query attention of every row over its sequence's pages (keys 0..position,
     or the last `window` of them).  decode_max_keys > 0 says that the rows are single-token
     steps of sequences no longer than that: keys are then split across blocks.  With
@@ -445,7 +446,8 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     tiled tensor-core kernel serves bfloat16 heads of 64 or 128; with max_keys (the longest sequence
     after this step) it cuts the key range of long rows into pieces that run side by side.  max_blocks > 0
     bounds how many blocks (hence SMs) the tensor-core kernel of prompts holds at a time, for a caller that runs
-    other kernels beside it; the result does not depend on it."""
+    other kernels beside it; the result does not depend on it.  key_ranges > 0 fixes into how many ranges that
+    kernel cuts the keys of a row tile (0: chosen: more than one for few rows over many keys)."""
     _gpu(q, k_pages, v_pages, block_table, positions, row_seq, slots, out)
     T = q.shape[0]
     if not q.is_contiguous() or tuple(q.shape) != (T, H * hd) or out.dtype != q.dtype or k_pages.dtype != q.dtype:
@@ -465,10 +467,16 @@ def attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, blo
     if tiled and _prompt_attention == 0 and max_keys > 0 and out_ld % 8 == 0 \
             and library().tlc_attention_prefill_tc_ok(BF16, hd, H, KV):
         B = slots.numel()
+        # few row tiles and many keys (a piece of a long prompt): the keys in ranges that run side by side
+        n_split = key_ranges if key_ranges > 0 else library().tlc_attention_prefill_tc_splits(T // 128 + B, H, int(max_keys))
+        part_o = part_ml = None
+        if n_split > 1:
+            part_o = torch.empty((T, H, n_split, hd), dtype=torch.float32, device=q.device)
+            part_ml = torch.empty((T, H, n_split, 2), dtype=torch.float32, device=q.device)
         _call("tlc_attention_prefill_tc", q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0],
               block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), slots.data_ptr(), start_pos.data_ptr(),
               out.data_ptr(), B, T // 128 + B, H, KV, hd, float(scale), int(window or 0), int(max_keys), T,
-              out_ld, int(max_blocks), _stream())
+              out_ld, int(max_blocks), int(n_split), _p(part_o), _p(part_ml), _stream())
         return
     if tiled:
         B = slots.numel()
