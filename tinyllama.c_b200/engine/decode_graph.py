@@ -95,11 +95,12 @@ class DecodeGraph:
             self.uniforms.copy_(self.uhost, non_blocking=True)
         if self.history is not None and histories is not None:
             n = self.history.shape[1]
-            self.hhost.fill_(-1)
+            hh = self.hhost.numpy()                  # (a row at a time through torch costs 8 us a row: 0.5 ms at batch 64)
+            hh.fill(-1)
             for r, hist in enumerate(histories):
-                hh = list(hist)[-n:]
-                if hh:
-                    self.hhost[r, :len(hh)] = torch.tensor(hh, dtype=torch.int32)
+                tail = hist[-n:] if isinstance(hist, (list, tuple)) else list(hist)[-n:]
+                if tail:
+                    hh[r, :len(tail)] = tail
             self.history.copy_(self.hhost, non_blocking=True)
         if self.graph is None:
             self.capture()          # the capture itself does not execute; the replay below does

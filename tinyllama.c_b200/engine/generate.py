@@ -214,11 +214,12 @@ def generate(backend, prompts: Sequence[Sequence[int]], max_new_tokens: int = 12
     for batch in plan_batches(lens, max_new_tokens, max_batch, free_slots + n_held, free_pages, max_context):
         live = {i: (conts[i].slot if conts[i] is not None else backend.acquire()) for i in batch}    # request -> slot
         pending = {i: list(prompts[i]) for i in batch}                 # tokens the next step brings
+        seen = {i: past[i] + results[i].prompt for i in batch}         # every token of the request so far: grows by one a step
         n_step = 0
         while live:
             order = sorted(live)
             entries = [(live[i], pending[i]) for i in order]
-            histories = [past[i] + results[i].prompt + results[i].tokens for i in order]
+            histories = [seen[i] for i in order]
             draws = [n_step + (conts[i].draws if conts[i] is not None else 0) for i in order]
             nxt = backend.step_and_sample(entries, histories, order, draws)
             n_step += 1
@@ -228,6 +229,7 @@ def generate(backend, prompts: Sequence[Sequence[int]], max_new_tokens: int = 12
                     r.finish_reason = "stop"
                 else:
                     r.tokens.append(int(tok))
+                    seen[i].append(int(tok))
                     if on_token is not None:
                         on_token(i, int(tok))
                     if len(r.tokens) >= max_new_tokens:
