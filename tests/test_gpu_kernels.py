@@ -193,9 +193,9 @@ def test_linear_with_the_k_steps_of_a_tile_shared_among_blocks(splits):
 
 @pytest.mark.parametrize("split", [0, 1, 2, 4, 8])
 @pytest.mark.parametrize("M,N,K", [(33, 2048, 4096), (64, 8240, 2048), (20, 200, 520), (64, 1000, 1096), (48, 128, 264), (17, 272, 136),
-                                   (32, 336, 2056)])
+                                   (32, 336, 2056), (100, 2048, 520), (128, 1000, 1096), (65, 400, 264)])
 def test_linear_of_17_to_64_rows_with_the_weights_on_the_wide_side(M, N, K, split):
-    """Products of 17..64 rows: tiles of 128 weight rows x 32 or 64 activation rows on tcgen05.mma, the K-steps of a
+    """Products of 17..128 rows: tiles of 128 weight rows x 32, 64 or 128 activation rows on tcgen05.mma, the K-steps of a
     tile shared among the 1, 2, 4 or 8 blocks of a cluster whose sums meet through distributed shared memory (more
     blocks than K-steps: some have none).  A last tile past N, K that ends inside a stage, fewer rows than the tile
     has columns; plain, into a 32-bit sum, with column scales and biases, and the SwiGLU epilogue; twice each, the

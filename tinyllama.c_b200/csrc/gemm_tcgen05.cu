@@ -806,7 +806,7 @@ extern "C" int tlc_linear_swiglu(const void* a, int a_dtype, int lda, const void
   TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N / 2, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N, K,
               lda, ldw, ldo);
   if (out_dtype != TLC_F32 && out_dtype != TLC_BF16) return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
-  if (min_rows_for_tensor_cores <= 64 && tlc_linear_few_rows_ok(a_dtype, lda, a, w_dtype, ldw, w, M, N, K)) {
+  if (min_rows_for_tensor_cores <= 128 && tlc_linear_few_rows_ok(a_dtype, lda, a, w_dtype, ldw, w, M, N, K)) {
     if (int rc = init_once()) return rc;
     return tlc_linear_few_rows_swiglu(a, lda, w, ldw, out, out_dtype, ldo, colscale, colbias, M, N, K, stream);
   }
@@ -844,8 +844,8 @@ extern "C" int tlc_linear(const void* a, int a_dtype, int lda, const void* w, in
   // Up to 32 rows the weight-streaming kernel is always best.  From 33 to 64 rows it re-reads the
   // activations once per 16 output columns, which only pays while the tiled kernel would have too
   // few tiles to keep the GPU busy (narrow outputs) and too few K-steps to share among blocks.
-  // (a threshold above 64 rows keeps every tensor-core kernel out, this one too)
-  if (min_rows_for_tensor_cores <= 64 && (out_dtype == TLC_F32 || out_dtype == TLC_BF16) &&
+  // (a threshold above 128 rows keeps every tensor-core kernel out, this one too)
+  if (min_rows_for_tensor_cores <= 128 && (out_dtype == TLC_F32 || out_dtype == TLC_BF16) &&
       tlc_linear_few_rows_ok(a_dtype, lda, a, w_dtype, ldw, w, M, N, K)) {
     TLC_REQUIRE(K > 0 && lda >= K && ldw >= K && ldo >= N, "linear: bad sizes M=%d N=%d K=%d lda=%d ldw=%d ldo=%d", M, N, K,
                 lda, ldw, ldo);

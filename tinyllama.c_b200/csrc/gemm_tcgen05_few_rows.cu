@@ -1,10 +1,10 @@
-// bfloat16 linear layer for 17..64 rows (decode steps of 17..64 sequences) on the 5th-generation tensor cores,
+// bfloat16 linear layer for 17..128 rows (decode steps of that many sequences, short prompts) on the 5th-generation tensor cores,
 // with the WEIGHTS on the M side of tcgen05.mma:  out[M, N] (+)= (A[M, K] @ W[N, K]^T) * colscale + colbias.
 //
 // With so few rows the time is the time to stream the weights once.  The product for prompts puts the activations
 // on the 128-row side and pads them, and has too few tiles for the GPU where N is small; the weight-streaming
 // mma.sync kernel of the smallest batches re-reads the activations for every 16 output columns.  Here a tile is
-// 128 weight rows x (up to) 64 activation rows: D[n, m] = sum_k W[n, k] A[m, k], an accumulator of 128 lanes x NB
+// 128 weight rows x 32, 64 or 128 activation rows: D[n, m] = sum_k W[n, k] A[m, k], an accumulator of 128 lanes x NB
 // columns of tensor memory.  Weight tiles [128, 64] and activation tiles [NB, 64] arrive by TMA (128-byte
 // swizzle, rows past the matrices read as zero) in a ring of shared-memory stages; one thread issues the
 // products; four warps take the result out of tensor memory, a thread per weight row.
@@ -218,6 +218,7 @@ gemm_few_rows_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_con
 
 int g_few_rows = 1;                     // test hook: 0 = never this kernel
 int g_force_split = 0;                  // test hook: blocks per tile (0: chosen)
+int g_max_rows = 128;                   // test hook: products of more rows go to the tiles of the prompt product
 int g_min_tiles = 0;                    // test hook: outputs of fewer tiles of 128 weight rows stay with the other kernels (0: by the rows)
 bool g_configured = false;
 int g_max_split[4] = {0, 0, 0, 0};      // [log2 split]: how many clusters of that size run at once (0: that size is not available)
@@ -276,14 +277,15 @@ int run_few(const void* a, int lda, const void* w, int ldw, void* out, int out_d
             const float* colbias, int accumulate, int M, int N, int K, int force_split, cudaStream_t stream) {
   static int sms = 0;
   if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
-  const int NB = M <= 32 ? 32 : 64;
+  const int NB = M <= 32 ? 32 : M <= 64 ? 64 : 128;
   const int split = force_split > 0 ? force_split : pick_split(N, K, NB, sms);
   CUtensorMap mw, mx;
   if (int rc = tlc_tensor_map_bf16(w, N, K, ldw, FBK, WM, &mw)) return rc;
   if (int rc = tlc_tensor_map_bf16(a, M, K, lda, FBK, NB, &mx)) return rc;
-#define TLC_FEW(TO_, NB_) launch_few<TO_, NB_, FR_STAGES, SWIGLU>(mw, mx, out, ldo, colscale, colbias, accumulate, M, N, K, split, stream)
-  if (out_dtype == TLC_F32) return NB == 32 ? TLC_FEW(float, 32) : TLC_FEW(float, 64);
-  if (out_dtype == TLC_BF16) return NB == 32 ? TLC_FEW(__nv_bfloat16, 32) : TLC_FEW(__nv_bfloat16, 64);
+  // (with 128 activation rows a stage is 32 KB: three of them, so that two blocks still share an SM)
+#define TLC_FEW(TO_, NB_) launch_few<TO_, NB_, (NB_ == 128 ? 3 : FR_STAGES), SWIGLU>(mw, mx, out, ldo, colscale, colbias, accumulate, M, N, K, split, stream)
+  if (out_dtype == TLC_F32) return NB == 32 ? TLC_FEW(float, 32) : NB == 64 ? TLC_FEW(float, 64) : TLC_FEW(float, 128);
+  if (out_dtype == TLC_BF16) return NB == 32 ? TLC_FEW(__nv_bfloat16, 32) : NB == 64 ? TLC_FEW(__nv_bfloat16, 64) : TLC_FEW(__nv_bfloat16, 128);
 #undef TLC_FEW
   return tlc_fail(-1, "linear: unknown output dtype %d", out_dtype);
 }
@@ -294,6 +296,7 @@ int run_few(const void* a, int lda, const void* w, int ldw, void* out, int out_d
 extern "C" void tlc_linear_few_rows(int on) { g_few_rows = on; }
 extern "C" void tlc_linear_few_rows_split(int split) { g_force_split = split; }
 extern "C" void tlc_linear_few_rows_min_tiles(int tiles) { g_min_tiles = tiles; }
+extern "C" void tlc_linear_few_rows_max_rows(int rows) { g_max_rows = rows; }
 
 // bfloat16 operands with 16-byte aligned rows, 17..64 rows, and an output that is wide enough: from 32 tiles of 128
 // weight rows on, from 16 with more than 32 rows.  Measured at 48 and 64 rows, microseconds in a captured loop over
@@ -308,7 +311,7 @@ extern "C" int tlc_linear_few_rows_ok(int a_dtype, int lda, const void* a, int w
   static int sms = 0;
   if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
   if (g_force_split == 0 && (N + WM - 1) / WM > 2 * sms) return 0;
-  return g_few_rows && a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && M > 16 && M <= 64 && N >= (g_force_split > 0 ? 1 : g_min_tiles > 0 ? g_min_tiles : M > 32 ? 16 : 32) * WM &&
+  return g_few_rows && a_dtype == TLC_BF16 && w_dtype == TLC_BF16 && M > 16 && M <= g_max_rows && N >= (g_force_split > 0 ? 1 : g_min_tiles > 0 ? g_min_tiles : M > 32 ? 16 : 32) * WM &&
          K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
          tlc_error_words() != nullptr;
 }

@@ -96,6 +96,7 @@ int tlc_linear_simt(const void* a, int a_dtype, int lda, const void* w, int w_dt
 void tlc_linear_few_rows(int on);          // 0: never this kernel (for comparisons)
 void tlc_linear_few_rows_split(int split); // 0: the number of blocks per tile is chosen; 1, 2, 4, 8: fixed (for tests)
 void tlc_linear_few_rows_min_tiles(int tiles);   // outputs of fewer tiles of 128 weight rows stay with the other kernels (0: 16 tiles with more than 32 rows, else 32)
+void tlc_linear_few_rows_max_rows(int rows);     // products of more rows go to the tiles of the prompt product (128; for comparisons)
 int tlc_linear_few_rows_ok(int a_dtype, int lda, const void* a, int w_dtype, int ldw, const void* w, int M, int N, int K);
 void tlc_linear_tma_out(int on);        // 0: the tensor-core product's 32-bit outputs never leave through the copy engine (for comparisons)
 void tlc_linear_skinny_pairs(int on);   // 0: the skinny product never splits K over a pair of blocks (for comparisons)

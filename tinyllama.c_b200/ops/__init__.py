@@ -60,6 +60,7 @@ _SIGNATURES = {
     "tlc_linear_few_rows": (None, [_i]),
     "tlc_linear_few_rows_split": (None, [_i]),
     "tlc_linear_few_rows_min_tiles": (None, [_i]),
+    "tlc_linear_few_rows_max_rows": (None, [_i]),
     "tlc_linear_few_rows_ok": (_i, [_i, _i, _vp, _i, _i, _vp, _i, _i, _i]),
     "tlc_linear_pairs": (_i, []),
     "tlc_rope_kv_store": (_i, [_vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i,
