@@ -178,3 +178,49 @@ def test_plan_batches_respects_slots_and_pages():
     assert plan_batches([100, 100, 10], 28, max_batch=8, free_slots=8, free_pages=4, max_context=1000) == [[0, 1], [2]]
     with pytest.raises(ValueError, match="needs"):
         plan_batches([1000], 10, 8, 8, 4, 2000)
+
+
+# ---- the step's packing and its temporaries ------------------------------------------------------
+def test_chunk_tables_follow_the_requests_thresholds():
+    """A table is made when a sequence brings more rows than the request's threshold (a chunk's length unless the
+    part says from how many rows its chunked form pays), and cuts every sequence into chunks of the chunk length."""
+    from tinyllama_c_b200.engine.step import chunk_table, pack, StepEntry, StepError
+    assert chunk_table([5, 128, 1], 128) is None                       # nothing longer than a chunk
+    assert chunk_table([5, 128, 1], 128, 32) == ([0, 5, 133, 134], [0, 1, 2], [0, 1, 2, 3])
+    assert chunk_table([5, 20], 128, 32) is None
+    assert chunk_table([130, 3], 64) == ([0, 64, 128, 130, 133], [0, 0, 0, 1], [0, 3, 4])
+    entries = [StepEntry(0, list(range(40)), (39,)), StepEntry(3, [7], (0,))]
+    info, want, n = pack(entries, [0, 9], 100, "cpu", (128, 16), {128: 32})
+    assert n == 2 and want.tolist() == [39, 40]
+    assert info.tokens.tolist() == list(range(40)) + [7] and info.positions.tolist() == list(range(40)) + [9]
+    assert info.row_seq.tolist() == [0] * 40 + [1] and info.cu_seqlens.tolist() == [0, 40, 41]
+    assert info.slots.tolist() == [0, 3] and info.start_pos.tolist() == [0, 9] and info.max_new == 40 and info.max_context == 40
+    seg_start, seg_seq, seq_seg_start = info.chunks[128]               # 40 rows > 32: one chunk a sequence
+    assert seg_start.tolist() == [0, 40, 41] and seg_seq.tolist() == [0, 1] and seq_seg_start.tolist() == [0, 1, 2]
+    assert [t.tolist() for t in info.chunks[16]] == [[0, 16, 32, 40, 41], [0, 0, 0, 1], [0, 3, 4]]
+    info, _, _ = pack([StepEntry(0, list(range(30)), ())], [0], 100, "cpu", (128,), {128: 32})
+    assert info.chunks[128] is None
+    with pytest.raises(StepError, match="token id 100 is outside"):
+        pack([StepEntry(0, [1, 100], ())], [0], 100, "cpu")
+    with pytest.raises(StepError, match="wanted index 2"):
+        pack([StepEntry(0, [1, 2], (2,))], [0], 100, "cpu")
+
+
+def test_a_steps_temporaries_are_shared_inside_the_step_only():
+    from tinyllama_c_b200.parts.base import StepInfo, scratch_buf, step_scratch
+    z = torch.zeros(1, dtype=torch.int32)
+    step = StepInfo(n_rows=1, n_seqs=1, tokens=z, positions=z, row_seq=z, cu_seqlens=z, slots=z, start_pos=z)
+    outside = scratch_buf("a", (2, 3), torch.float32, "cpu")
+    assert scratch_buf("a", (2, 3), torch.float32, "cpu") is not outside           # no step: plain allocations
+    with step_scratch(step):
+        a = scratch_buf("a", (2, 3), torch.float32, "cpu")
+        assert scratch_buf("a", (2, 3), torch.float32, "cpu") is a                # the next layer gets the same buffer
+        assert scratch_buf("b", (2, 3), torch.float32, "cpu") is not a            # another tag, shape or type: another
+        assert scratch_buf("a", (2, 4), torch.float32, "cpu") is not a
+        assert scratch_buf("a", (2, 3), torch.bfloat16, "cpu") is not a
+        other = StepInfo(n_rows=1, n_seqs=1, tokens=z, positions=z, row_seq=z, cu_seqlens=z, slots=z, start_pos=z)
+        with step_scratch(other):                                                  # a step inside a step has its own
+            assert scratch_buf("a", (2, 3), torch.float32, "cpu") is not a
+        assert scratch_buf("a", (2, 3), torch.float32, "cpu") is a
+    assert len(step.scratch) == 4 and len(other.scratch) == 1
+    assert scratch_buf("a", (2, 3), torch.float32, "cpu") is not a
