@@ -765,17 +765,23 @@ def test_ssm_scan_in_matrix_form_on_tensor_cores(Hs, P, N, G):
     ops_plain.ssm_scan(*args)
     # states of 128 or 256 columns: the walk with tcgen05.mma and the state in tensor memory (the outputs in one
     # piece, and as two summands of which one is computed on a second stream), and the mma.sync walk
-    for mode, in_two in (((0, False), (0, True), (1, False), (1, True)) if N in (128, 256) else ((0, False), (0, True))):
+    # (and the tcgen05 walk with one block and with three for all of its (sequence, head, rows) items: a block then
+    # walks several sequences in turn, its barriers made anew and its tensor memory used again)
+    variants = ((0, False, 0), (0, True, 0), (1, False, 0), (1, True, 0), (0, True, 1), (0, False, 3)) if N in (128, 256) \
+        else ((0, False, 0), (0, True, 0))
+    for mode, in_two, blocks in variants:
         gpu = [a.cuda() if isinstance(a, torch.Tensor) else a for a in args0]
         gpu[13] = tuple(t.cuda() for t in args0[13])
         y_part = torch.full((T, Di), float("nan"), device="cuda") if in_two else None
         ops.ssd_walk_override(mode)
+        ops.ssd_walk_blocks(blocks)
         try:
             used = ops.ssm_scan(*gpu, y_part=y_part)
             torch.cuda.synchronize()
             ops.check_errors()
         finally:
             ops.ssd_walk_override(0)
+            ops.ssd_walk_blocks(0)
         assert used == (in_two and mode == 0 and N in (128, 256)), "which walks leave two summands"
         if used:
             gpu[8] = gpu[8] + y_part

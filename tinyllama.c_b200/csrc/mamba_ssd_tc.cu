@@ -83,7 +83,8 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
                    const __nv_bfloat16* __restrict__ xbc, const float* __restrict__ row_w, const float* __restrict__ row_e,
                    const float* __restrict__ seg_decay, float* __restrict__ state,
                    const int* __restrict__ seg_start, const int* __restrict__ seq_seg_start, const int* __restrict__ slots,
-                   const int* __restrict__ start_pos, float* __restrict__ y, int add_to_y, int Hs, int P, int G, int Cd, ErrWords* err) {
+                   const int* __restrict__ start_pos, float* __restrict__ y, int add_to_y, int n_seqs, int Hs, int P, int G, int Cd,
+                   ErrWords* err) {
   tlc_pdl(xbc, row_w, row_e, seg_decay, state, y);
   using L_ = TcSmem<NTILES>;
   constexpr int N = L_::N;
@@ -96,22 +97,10 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
   const uint32_t sm0 = smem_u32(sm);
   const uint32_t bar_c = smem_u32(bars), bar_bt = smem_u32(bars + 1), bar_y = smem_u32(bars + 2), bar_s = smem_u32(bars + 3);
 
-  const int b = blockIdx.x, h = blockIdx.y, p0 = blockIdx.z * PB;
-  const int g = h / (Hs / G);
   const int Di = Hs * P;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int c0 = seq_seg_start[b], c1 = seq_seg_start[b + 1];
-  if (c1 <= c0) return;
   const long long wait_limit = mbar_wait_limit(err);
-  const unsigned short* Xg = reinterpret_cast<const unsigned short*>(xbc) + (size_t)h * P + p0;
-  const int c_col0 = Di + G * N + g * N;               // first column of this group's C in a row of x|B|C
-
-  if (tid == 0) {
-    for (int i = 0; i < 4; i++) mbar_init(bar_c + 8 * i, 1);
-    *dead = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  }
+  if (tid == 0) *dead = 0;
   if (warp == 0) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TCOLS)
                  : "memory");
@@ -121,6 +110,33 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem = *tmem_slot;
+
+  // An item is (sequence, head, 32 rows of the head).  A block takes items blockIdx.x, + gridDim.x, ...: with many
+  // short sequences (32 prompts of 64 tokens are 3,072 items of one chunk each) a block an item spent more time on
+  // its start-up (tensor-memory allocation, barriers, the first copies) than on its chunk.  Consecutive items are
+  // the heads of one sequence, so a block's items are of many sequences, long and short.  Tensor memory is
+  // allocated once; the four barriers are made anew per item, after a block-wide barrier behind which nothing is
+  // pending on them (every copy and every commit of an item is waited for by somebody before the item ends).
+  const int per_seq = Hs * (P / PB);
+  bool first = true;
+#pragma unroll 1
+  for (int item = blockIdx.x; item < n_seqs * per_seq; item += gridDim.x) {
+  const int b = item / per_seq, h = (item % per_seq) / (P / PB), p0 = (item % (P / PB)) * PB;
+  const int g = h / (Hs / G);
+  const int c0 = seq_seg_start[b], c1 = seq_seg_start[b + 1];
+  if (c1 <= c0) continue;
+  const unsigned short* Xg = reinterpret_cast<const unsigned short*>(xbc) + (size_t)h * P + p0;
+  const int c_col0 = Di + G * N + g * N;               // first column of this group's C in a row of x|B|C
+  if (tid == 0) {
+    for (int i = 0; i < 4; i++) {
+      if (!first) asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar_c + 8 * i) : "memory");
+      mbar_init(bar_c + 8 * i, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  first = false;
+  __syncthreads();
 
   // a bounded wait; once one has run out, no further wait is attempted
   auto wait = [&](uint32_t bar, uint32_t parity, int code) {
@@ -324,11 +340,16 @@ ssd_walk_tc_kernel(const __grid_constant__ CUtensorMap map_c, const __grid_const
     for (int p = 0; p < 32; p++) slot[(size_t)p * N + n_mine] = __uint_as_float(sreg[p]);
   }
   }   // workers
+  // every agent is done with the item: tensor memory, shared memory and the barriers may be used again
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }   // items
   if (warp == 0)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TCOLS) : "memory");
 }
+
+int g_walk_blocks = 0;       // test hook: the grid of the walk (0: one block an SM, at most one an item)
 
 template <int NTILES>
 int launch(const CUtensorMap& mc, const CUtensorMap& mbt, const __nv_bfloat16* xbc, const float* row_w, const float* row_e,
@@ -341,13 +362,20 @@ int launch(const CUtensorMap& mc, const CUtensorMap& mbt, const __nv_bfloat16* x
       return tlc_fail(-2, "ssm_scan(chunk walk, tcgen05): cannot reserve %d bytes of shared memory", TcSmem<NTILES>::TOTAL);
     configured = true;
   }
-  tlc_launch(ssd_walk_tc_kernel<NTILES>, dim3(B, Hs, P / PB), dim3(THREADS), (size_t)TcSmem<NTILES>::TOTAL, stream, mc, mbt, xbc, row_w,
-             row_e, seg_decay, state, seg_start, seq_seg_start, slots, start_pos, y, add_to_y, Hs, P, G, Cd, tlc_error_words());
+  static int sms = 0;
+  if (sms == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  const long long items = (long long)B * Hs * (P / PB);
+  const int blocks = (int)std::min<long long>(items, g_walk_blocks > 0 ? g_walk_blocks : sms);      // one block an SM (shared memory)
+  tlc_launch(ssd_walk_tc_kernel<NTILES>, dim3(blocks), dim3(THREADS), (size_t)TcSmem<NTILES>::TOTAL, stream, mc, mbt, xbc, row_w,
+             row_e, seg_decay, state, seg_start, seq_seg_start, slots, start_pos, y, add_to_y, B, Hs, P, G, Cd, tlc_error_words());
   TLC_CHECK_LAUNCH("ssm_scan(chunk walk, tcgen05)");
   return 0;
 }
 
 }  // namespace
+
+// Test hook: how many blocks walk the items (0: chosen); with 1 one block walks every sequence and head in turn.
+extern "C" void tlc_ssd_walk_blocks(int blocks) { g_walk_blocks = blocks; }
 
 // Prepares the kernels' attributes outside any stream capture (called from tlc_ssd_init).
 int tlc_ssd_tc_init() {

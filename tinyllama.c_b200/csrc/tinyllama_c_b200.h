@@ -195,6 +195,7 @@ int tlc_ssd_ok(int Hs, int P, int N, int G, int Cd);
 /* Test hook: 0 = the walk uses tcgen05.mma with the state in tensor memory where it is built (states of 128
  * or 256 columns) and mma.sync with the state in registers elsewhere; 1 = always the latter. */
 void tlc_ssd_walk_override(int mode);
+void tlc_ssd_walk_blocks(int blocks);      // the grid of the tcgen05 walk (0: one block an SM at most; for tests)
 long long tlc_ssd_scratch_floats(int n_seg, int T, int Hs, int P, int N, int G);
 /* y_part [T, Hs*P] and used_part may be NULL.  Where the walk runs on tcgen05 and they are given, the outputs come as
  * two summands: what needs no state (M x + D x) in y_part, the state's share in y, and *used_part = 1.  With a second

@@ -87,6 +87,7 @@ _SIGNATURES = {
                                   _vp]),
     "tlc_ssd_ok": (_i, [_i, _i, _i, _i, _i]),
     "tlc_ssd_walk_override": (None, [_i]),
+    "tlc_ssd_walk_blocks": (None, [_i]),
     "tlc_ssd_scratch_floats": (_ll, [_i, _i, _i, _i, _i, _i]),
     "tlc_ssm_scan_ssd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i,
                               _i, _i, _vp, _vp]),
@@ -603,6 +604,12 @@ def mamba_conv(proj: torch.Tensor, xbc_off: int, dt_off: int, w: torch.Tensor, b
           row_seq.data_ptr(), slots.data_ptr(), start_pos.data_ptr(), xbc_out.data_ptr(), dtype_code(xbc_out.dtype),
           dt_out.data_ptr(), dA_out.data_ptr(), T, B, Cd, K, Hs, int(bool(single_rows)), int(bool(bf16_run)),
           int(bool(all_fresh)), _stream())
+
+
+def ssd_walk_blocks(blocks: int) -> None:
+    """How many blocks of the tcgen05 walk work through the (sequence, head, rows) items (0: one an SM at most);
+    for tests: with few blocks each walks many sequences in turn."""
+    library().tlc_ssd_walk_blocks(int(blocks))
 
 
 def ssd_walk_override(mode: int) -> None:
