@@ -132,6 +132,30 @@ def test_generation_crosses_a_context_bucket(folders, dtype, monkeypatch):
     assert llm.cache.slots.n_held == 0
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_requests_that_end_at_different_times_share_captured_steps(folders, dtype):
+    """Seven requests whose stop tokens end them one by one: the captured steps are those of batch sizes 8, 4, 3, 2, 1
+    (seven, six and five sequences run in the graph of eight, filled up with rows of a spare slot), the tokens are
+    the ones that steps without captured graphs give, and every slot and page is back at the end."""
+    cfg = read_config(folders["long"])
+    V = cfg["vocab_size"]
+    prompts = [random_tokens(V, n, 900 + n) for n in (30, 9, 17, 40, 12, 25, 33)]
+    eager = tlc.LLM(folders["long"], dtype=dtype, max_tokens=64 * 16, max_seqs=8, use_graphs=False)
+    free = eager.generate(prompts, tlc.GREEDY, max_new_tokens=24, ignore_eos=True)
+    # every request gets a stop token out of its own greedy continuation, at a different step
+    stops = {free[i].tokens[3 * i + 2] for i in range(len(prompts))}
+    want = eager.generate(prompts, tlc.GREEDY, max_new_tokens=24, stop_ids=sorted(stops))
+    assert len({len(r.tokens) for r in want}) >= 4, "the requests should end at different steps"
+    llm = tlc.LLM(folders["long"], dtype=dtype, max_tokens=64 * 16, max_seqs=8)
+    pages = [g.pool.n_free for g in llm.cache.kv_groups]
+    got = llm.generate(prompts, tlc.GREEDY, max_new_tokens=24, stop_ids=sorted(stops))
+    assert [r.tokens for r in got] == [r.tokens for r in want]
+    assert [r.finish_reason for r in got] == [r.finish_reason for r in want]
+    sizes = sorted({k[1] for k in llm._graphs})
+    assert set(sizes) <= {1, 2, 3, 4, 8} and 8 in sizes, sizes
+    assert llm.cache.slots.n_held == 0 and [g.pool.n_free for g in llm.cache.kv_groups] == pages
+
+
 def test_a_turn_continues_in_a_held_slot(folders):
     """generate() with a Continuation: a second turn in the slot of the first equals one request that
     brings both turns' tokens (history is not recomputed, chat.c:296)."""
