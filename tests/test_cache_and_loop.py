@@ -180,6 +180,17 @@ def test_plan_batches_respects_slots_and_pages():
         plan_batches([1000], 10, 8, 8, 4, 2000)
 
 
+def test_padded_batch_sizes_are_few_and_never_smaller():
+    """The captured step that serves n sequences has at least n rows, at most 3 (up to 16) or 7 more, and the
+    sizes that 1..256 sequences use are a short list: what bounds the number of captures of a run."""
+    from tinyllama_c_b200.engine.generate import EngineBackend
+    sizes = [EngineBackend.padded_batch(n) for n in range(1, 257)]
+    assert all(p >= n and p - n <= (3 if n <= 16 else 7) for n, p in zip(range(1, 257), sizes))
+    assert sizes == sorted(sizes) and sizes[:4] == [1, 2, 3, 4] and sizes[4] == 8
+    assert all(EngineBackend.padded_batch(p) == p for p in sizes)            # a padded size pads no further
+    assert len(set(sizes)) == 4 + 3 + 30                                     # 1..4; 8, 12, 16; 24, 32, .. 256
+
+
 # ---- the step's packing and its temporaries ------------------------------------------------------
 def test_chunk_tables_follow_the_requests_thresholds():
     """A table is made when a sequence brings more rows than the request's threshold (a chunk's length unless the
