@@ -191,6 +191,12 @@ def test_padded_batch_sizes_are_few_and_never_smaller():
     assert len(set(sizes)) == 4 + 3 + 30                                     # 1..4; 8, 12, 16; 24, 32, .. 256
 
 
+def test_context_buckets_are_powers_of_two_from_512():
+    from tinyllama_c_b200.engine.generate import context_bucket
+    assert [context_bucket(n) for n in (1, 512, 513, 1024, 1025, 40000)] == [512, 512, 1024, 1024, 2048, 65536]
+    assert all(context_bucket(n) >= n and context_bucket(n) < 2 * max(n, 512) for n in range(1, 5000, 37))
+
+
 # ---- the step's packing and its temporaries ------------------------------------------------------
 def test_chunk_tables_follow_the_requests_thresholds():
     """A table is made when a sequence brings more rows than the request's threshold (a chunk's length unless the
